@@ -1,0 +1,313 @@
+"""ctypes binding of libb200.so and a host-side mirror of arrayjit's backend interface.
+
+The classes follow the user-facing signatures of arrayjit/lib/backend_intf.ml:
+`Backend.compile` / `link` (:319-336), `routine` (:59-70), `context` (:134-149), device
+`await` / `all_work` (:97-126) and the host copies `from_host` / `to_host`
+(arrayjit/lib/backends.ml:113-158).  `Context.link` restates `Raise_backend.allocate_delta`
+(arrayjit/lib/backends.ml:529-614): nodes of the routine that the parent context does not
+hold yet are bump-packed into one new pool, zero-initialised unless the routine zeroes them
+itself, and the child context records their {pool, offset}.
+
+Everything that computes goes through the C ABI of include/b200.h; when the library or a
+GPU is missing the calls raise — there is no CPU fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+import os
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from .low_level import PREC_BYTES, Routine as IrRoutine, Tnode
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libb200.so")
+
+NP_DTYPE = {"byte": np.uint8, "uint16": np.uint16, "int32": np.int32, "uint32": np.uint32,
+            "int64": np.int64, "uint64": np.uint64, "half": np.float16, "bfloat16": np.uint16,
+            "single": np.float32, "double": np.float64}
+
+
+class B200Error(RuntimeError):
+    """Non-zero status from the C ABI; `.code` < 0 is a B200_E_* value, > 0 a CUDA /
+    NVRTC / NCCL result."""
+
+    def __init__(self, code: int, msg: str):
+        super().__init__("b200 error %d: %s" % (code, msg))
+        self.code = code
+
+
+class UserError(B200Error):
+    """Utils.User_error of the reference: bad static index, missing binding."""
+
+
+class Binding(ctypes.Structure):
+    _fields_ = [("tn_id", ctypes.c_int32), ("pool_id", ctypes.c_int32), ("offset", ctypes.c_uint64)]
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Loads libb200.so (built in-tree by `python -m ocannl_b200.build`)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise B200Error(-2, "libb200.so is not built: run `python -m ocannl_b200.build`")
+        L = ctypes.CDLL(LIB_PATH)
+        L.b200_last_error.restype = ctypes.c_char_p
+        L.b200_version.restype = ctypes.c_char_p
+        _lib = L
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        msg = lib().b200_last_error().decode(errors="replace")
+        raise (UserError if rc == -5 else B200Error)(rc, msg)
+
+
+def _vp(x) -> ctypes.c_void_p:
+    return ctypes.c_void_p(x)
+
+
+class Event:
+    def __init__(self, h):
+        self.h = h
+
+    def sync(self):
+        check(lib().b200_event_sync(self.h))
+
+    def is_done(self) -> bool:
+        d = ctypes.c_int(0)
+        check(lib().b200_event_query(self.h, ctypes.byref(d)))
+        return bool(d.value)
+
+    def elapsed_ms(self, later: "Event") -> float:
+        ms = ctypes.c_float(0)
+        check(lib().b200_event_elapsed_ms(self.h, later.h, ctypes.byref(ms)))
+        return ms.value
+
+    def free(self):
+        if self.h:
+            lib().b200_event_free(self.h)
+            self.h = None
+
+
+class Device:
+    """One GPU with its stream and pool table (Backend_intf.device)."""
+
+    def __init__(self, ordinal: int = 0):
+        h = ctypes.c_void_p()
+        check(lib().b200_device_open(ctypes.c_int(ordinal), ctypes.byref(h)))
+        self.h = h
+        self.ordinal = ordinal
+        self._next_pool = 1            # pool id 0 is the merge buffer (backend_intf.ml:131-132)
+
+    def props(self) -> dict:
+        buf = ctypes.create_string_buffer(1024)
+        check(lib().b200_device_props(self.h, buf, ctypes.c_size_t(1024)))
+        return json.loads(buf.value.decode())
+
+    def alloc_pool(self, size_in_bytes: int, pool_id: Optional[int] = None, alignment: int = 256) -> int:
+        if pool_id is None:
+            pool_id = self._next_pool
+            self._next_pool += 1
+        check(lib().b200_pool_alloc(self.h, ctypes.c_int(pool_id), ctypes.c_size_t(size_in_bytes),
+                                    ctypes.c_size_t(alignment)))
+        return pool_id
+
+    def free_pool(self, pool_id: int):
+        check(lib().b200_pool_free(self.h, ctypes.c_int(pool_id)))
+
+    def memset_zero(self, pool_id: int, offset: int, size_in_bytes: int):
+        check(lib().b200_pool_memset0(self.h, ctypes.c_int(pool_id), ctypes.c_size_t(offset),
+                                      ctypes.c_size_t(size_in_bytes)))
+
+    def pool_address(self, pool_id: int) -> Tuple[int, int]:
+        p, n = ctypes.c_uint64(0), ctypes.c_size_t(0)
+        check(lib().b200_pool_address(self.h, ctypes.c_int(pool_id), ctypes.byref(p), ctypes.byref(n)))
+        return p.value, n.value
+
+    def from_host(self, pool_id: int, offset: int, arr: np.ndarray):
+        assert arr.flags["C_CONTIGUOUS"]
+        check(lib().b200_h2d(self.h, ctypes.c_int(pool_id), ctypes.c_size_t(offset), _vp(arr.ctypes.data),
+                             ctypes.c_size_t(arr.nbytes)))
+
+    def to_host(self, pool_id: int, offset: int, arr: np.ndarray):
+        assert arr.flags["C_CONTIGUOUS"] and arr.flags["WRITEABLE"]
+        check(lib().b200_d2h(self.h, ctypes.c_int(pool_id), ctypes.c_size_t(offset), _vp(arr.ctypes.data),
+                             ctypes.c_size_t(arr.nbytes)))
+
+    def all_work(self) -> Event:
+        e = ctypes.c_void_p()
+        check(lib().b200_event_record(self.h, ctypes.byref(e)))
+        return Event(e)
+
+    def will_wait_for(self, ev: Event):
+        check(lib().b200_stream_wait(self.h, ev.h))
+
+    def await_(self):
+        check(lib().b200_await(self.h))
+
+    def is_idle(self) -> bool:
+        d = ctypes.c_int(0)
+        check(lib().b200_is_idle(self.h, ctypes.byref(d)))
+        return bool(d.value)
+
+    def stream_handle(self) -> int:
+        s = ctypes.c_uint64(0)
+        check(lib().b200_stream_handle(self.h, ctypes.byref(s)))
+        return s.value
+
+    def get_used_memory(self) -> int:
+        n = ctypes.c_size_t(0)
+        check(lib().b200_used_memory(self.h, ctypes.byref(n)))
+        return n.value
+
+    def get_debug_info(self) -> dict:
+        buf = ctypes.create_string_buffer(1024)
+        check(lib().b200_debug_info(self.h, buf, ctypes.c_size_t(1024)))
+        return json.loads(buf.value.decode())
+
+
+def num_devices() -> int:
+    n = ctypes.c_int(0)
+    check(lib().b200_num_devices(ctypes.byref(n)))
+    return n.value
+
+
+class PinnedBuffer:
+    """Page-locked host memory viewed as a numpy array (for from_host / to_host)."""
+
+    def __init__(self, shape, dtype):
+        self.nbytes = int(np.prod(shape)) * np.dtype(dtype).itemsize
+        p = ctypes.c_void_p()
+        check(lib().b200_host_alloc(ctypes.c_size_t(max(self.nbytes, 1)), ctypes.byref(p)))
+        self.ptr = p
+        raw = (ctypes.c_char * max(self.nbytes, 1)).from_address(p.value)
+        self.array = np.frombuffer(raw, dtype=dtype, count=int(np.prod(shape))).reshape(shape)
+
+    def free(self):
+        if self.ptr:
+            self.array = None
+            lib().b200_host_free(self.ptr)
+            self.ptr = None
+
+
+class Code:
+    """Device-independent compiled routine (`Backend.compile`)."""
+
+    def __init__(self, ir: IrRoutine, options: Optional[str] = None, name: Optional[str] = None):
+        self.ir = ir
+        text = ir.to_b200ir().encode()
+        h = ctypes.c_void_p()
+        check(lib().b200_compile((name or "").encode(), text, ctypes.c_size_t(len(text)),
+                                 options.encode() if options else None, ctypes.byref(h)))
+        self.h = h
+
+    def info(self) -> dict:
+        buf = ctypes.create_string_buffer(1 << 16)
+        check(lib().b200_code_info(self.h, buf, ctypes.c_size_t(1 << 16)))
+        return json.loads(buf.value.decode())
+
+    def source(self, stage: int = -1) -> str:
+        need = ctypes.c_size_t(0)
+        check(lib().b200_code_source(self.h, ctypes.c_int(stage), None, ctypes.c_size_t(0), ctypes.byref(need)))
+        buf = ctypes.create_string_buffer(need.value)
+        check(lib().b200_code_source(self.h, ctypes.c_int(stage), buf, ctypes.c_size_t(need.value), None))
+        return buf.value.decode()
+
+    def free(self):
+        if self.h:
+            lib().b200_code_free(self.h)
+            self.h = None
+
+
+def compile(ir: IrRoutine, options: Optional[str] = None) -> Code:  # noqa: A001 (mirrors Backend.compile)
+    return Code(ir, options)
+
+
+class Context:
+    """`Backend_intf.context`: a device plus the {node -> (pool, offset)} map of the nodes it
+    holds.  Contexts are persistent: `link` returns a routine whose `.context` is the child."""
+
+    def __init__(self, device: Device, arrays: Optional[Dict[str, Tuple[int, int, Tnode]]] = None):
+        self.device = device
+        self.arrays: Dict[str, Tuple[int, int, Tnode]] = dict(arrays or {})   # ident -> (pool, offset, tn)
+
+    def link(self, code: Code) -> "Routine":
+        dev = self.device
+        new: List[Tnode] = [t for t in code.ir.params() if t.ident not in self.arrays]
+        arrays = dict(self.arrays)
+        if new:
+            # bump-pack the delta into one pool (allocate_delta, backends.ml:529-614)
+            offs, total = [], 0
+            for t in new:
+                align = 256
+                total = (total + align - 1) // align * align
+                offs.append(total)
+                total += t.size_in_bytes
+            pool = dev.alloc_pool(max(total, 1))
+            dev.memset_zero(pool, 0, max(total, 1))
+            for t, o in zip(new, offs):
+                arrays[t.ident] = (pool, o, t)
+        for t in code.ir.params():
+            have = arrays[t.ident][2]
+            if have.prec != t.prec or tuple(have.dims) != tuple(t.dims):
+                raise UserError(-5, "link: node '%s' is held with another precision or shape" % t.ident)
+        params = code.ir.params()
+        binds = (Binding * max(len(params), 1))()
+        for i, t in enumerate(params):
+            pool, off, _ = arrays[t.ident]
+            binds[i] = Binding(t.id, pool, off)
+        h = ctypes.c_void_p()
+        check(lib().b200_link(dev.h, code.h, binds, ctypes.c_int(len(params)), ctypes.byref(h)))
+        return Routine(Context(dev, arrays), code, h)
+
+    # ---- host access (Context.set_values / get_values, arrayjit/lib/context.ml:322-395)
+    def from_host(self, ident: str, arr: np.ndarray):
+        pool, off, t = self.arrays[ident]
+        a = np.ascontiguousarray(arr, dtype=NP_DTYPE[t.prec]).reshape(-1)
+        if a.size != t.num_elems:
+            raise UserError(-5, "from_host: '%s' has %d elements, got %d" % (ident, t.num_elems, a.size))
+        self.device.from_host(pool, off, a)
+        self.device.await_()     # the staging array may be a temporary
+
+    def to_host(self, ident: str) -> np.ndarray:
+        pool, off, t = self.arrays[ident]
+        out = np.empty(t.dims if t.dims else (1,), NP_DTYPE[t.prec])
+        self.device.to_host(pool, off, out)
+        self.device.await_()
+        return out
+
+
+class Routine:
+    """`Backend_intf.routine`: a linked routine; `run` schedules it on the device stream
+    (`Task.run routine.schedule`, lib/train.ml:42)."""
+
+    def __init__(self, context: Context, code: Code, h):
+        self.context = context
+        self.code = code
+        self.h = h
+        self.static_syms = [s for s, _ in code.ir.static]
+
+    def run(self, **static):
+        n = len(self.static_syms)
+        vals = (ctypes.c_int64 * max(n, 1))(*[int(static[s]) for s in self.static_syms])
+        check(lib().b200_launch(self.h, vals, ctypes.c_int(n)))
+
+    def use_graph(self, on: bool = True):
+        check(lib().b200_routine_use_graph(self.h, ctypes.c_int(int(on))))
+
+    def kernels_per_run(self) -> int:
+        k = ctypes.c_int64(0)
+        check(lib().b200_routine_launch_count(self.h, ctypes.byref(k)))
+        return k.value
+
+    def free(self):
+        if self.h:
+            lib().b200_routine_free(self.h)
+            self.h = None

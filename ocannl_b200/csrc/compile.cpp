@@ -1,0 +1,498 @@
+// Routine compilation: cut the body into stages, find the parallel loops of each stage and
+// generate its kernel.  See compile.hpp.
+//
+// The reference runs a routine as ONE sequential function (cc: arrayjit/lib/cc_backend.ml:325-343;
+// cuda: one thread of one block, arrayjit/lib/cuda_backend.ml:357-360,1043).  Here every
+// top-level loop nest (`loop_accum` emits one per assignment, arrayjit/lib/assignments.ml:311-488)
+// becomes a kernel whose threads own disjoint iterations of the nest's independent loops.
+#include "compile.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <functional>
+#include <set>
+#include <sstream>
+
+#include "emit.hpp"
+
+namespace b200 {
+
+bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& body, bool zeroed_before,
+                const CompileOptions& opt, Stage* out);  // gemm_match.cpp
+std::string gemm_translation_unit(const Program& P, Stage& st, const std::string& kernel_name,
+                                  const CompileOptions& opt);
+
+namespace {
+
+// ---- walking helpers
+void walk_scalar(const Scalar& e, const std::function<void(const Scalar&)>& fs,
+                 const std::function<void(const Stmt&)>& ft);
+void walk_stmt(const Stmt& s, const std::function<void(const Scalar&)>& fs, const std::function<void(const Stmt&)>& ft) {
+  ft(s);
+  switch (s.kind) {
+    case Stmt::Seq:
+      for (auto& x : s.items) walk_stmt(*x, fs, ft);
+      break;
+    case Stmt::For: walk_stmt(*s.body, fs, ft); break;
+    case Stmt::Set:
+    case Stmt::SetLocal: walk_scalar(*s.value, fs, ft); break;
+    default: break;
+  }
+}
+void walk_scalar(const Scalar& e, const std::function<void(const Scalar&)>& fs,
+                 const std::function<void(const Stmt&)>& ft) {
+  fs(e);
+  if (e.kind == Scalar::LocalScope) walk_stmt(*e.body, fs, ft);
+  for (auto& a : e.args) walk_scalar(*a.s, fs, ft);
+}
+
+// Is loop symbol `s` safe to run in parallel over `body`?  Sufficient condition: every
+// node written in the body is written only at positions that carry `s` as a plain iterator
+// on one fixed axis, and every read of such a node carries `s` on that same axis — so
+// distinct values of `s` touch disjoint slices of everything that is written.
+bool parallel_safe(const std::string& s, const Stmt& body) {
+  std::map<int, int> axis_of;  // written node -> axis that carries s
+  bool ok = true;
+  auto axis_with = [&](const Indices& idcs) {
+    for (size_t a = 0; a < idcs.size(); ++a)
+      if (idcs[a].kind == Index::Iter && idcs[a].sym == s) return (int)a;
+    return -1;
+  };
+  walk_stmt(
+      body, [](const Scalar&) {},
+      [&](const Stmt& st) {
+        if (st.kind == Stmt::ZeroOut) ok = false;
+        if (st.kind == Stmt::Set) {
+          int a = axis_with(st.idcs);
+          if (a < 0) { ok = false; return; }
+          // the symbol must not appear on any other axis of the write
+          for (size_t k = 0; k < st.idcs.size(); ++k)
+            if ((int)k != a && st.idcs[k].uses(s)) ok = false;
+          auto it = axis_of.find(st.tn);
+          if (it == axis_of.end()) axis_of[st.tn] = a;
+          else if (it->second != a) ok = false;
+        }
+      });
+  if (!ok) return false;
+  walk_stmt(
+      body,
+      [&](const Scalar& e) {
+        if (e.kind == Scalar::Get || e.kind == Scalar::GetDyn) {
+          auto it = axis_of.find(e.tn);
+          if (it == axis_of.end()) return;
+          if (e.kind == Scalar::GetDyn) { ok = false; return; }
+          int a = it->second;
+          if (a >= (int)e.idcs.size() || e.idcs[a].kind != Index::Iter || e.idcs[a].sym != s) ok = false;
+          for (size_t k = 0; k < e.idcs.size(); ++k)
+            if ((int)k != a && e.idcs[k].uses(s)) ok = false;
+        }
+      },
+      [](const Stmt&) {});
+  return ok;
+}
+
+bool body_has_set(const Stmt& s) {
+  bool any = false;
+  walk_stmt(s, [](const Scalar&) {}, [&](const Stmt& st) {
+    if (st.kind == Stmt::Set || st.kind == Stmt::ZeroOut) any = true;
+  });
+  return any;
+}
+
+// Does the statement tree mention a function-scope scalar local (declared outside it)?
+void collect_scopes(const Stmt& s, std::set<std::pair<int, int>>& declared, std::set<std::pair<int, int>>& used) {
+  walk_stmt(
+      s,
+      [&](const Scalar& e) {
+        if (e.kind == Scalar::LocalScope) declared.insert({e.scope_id, e.tn});
+        if (e.kind == Scalar::GetLocal) used.insert({e.scope_id, e.tn});
+      },
+      [&](const Stmt& st) {
+        if (st.kind == Stmt::DeclareLocal) declared.insert({st.scope_id, st.tn});
+        if (st.kind == Stmt::SetLocal) used.insert({st.scope_id, st.tn});
+      });
+}
+
+// Cooperative row reduction: the stage's body is `Set t[..] := E` where E holds Local_scope
+// reductions `v := neutral; for k { v := v (+|max|min) f(k) }` over loops long enough that a
+// warp per output element pays.  Returns the lane-strided symbol or "".
+struct CoopInfo {
+  std::string sym;
+  std::vector<std::pair<int, std::string>> scopes;  // (scope id, combine op)
+};
+
+bool accum_form(const Stmt& st, int sid, int tn, std::string* op) {
+  // Set_local(id, Binop(op, Get_local id, x)) | Binop(op, x, Get_local id) | FMA(a, b, Get_local id)
+  if (st.kind != Stmt::SetLocal || st.scope_id != sid || st.tn != tn) return false;
+  const Scalar& v = *st.value;
+  auto is_self = [&](const Scalar& e) { return e.kind == Scalar::GetLocal && e.scope_id == sid && e.tn == tn; };
+  auto mentions_self = [&](const Scalar& e) {
+    bool m = false;
+    walk_scalar(e, [&](const Scalar& x) { if (is_self(x)) m = true; }, [](const Stmt&) {});
+    return m;
+  };
+  if (v.kind == Scalar::Tern && v.op == "fma") {
+    if (is_self(*v.args[2].s) && !mentions_self(*v.args[0].s) && !mentions_self(*v.args[1].s)) {
+      *op = "add";
+      return true;
+    }
+    return false;
+  }
+  if (v.kind == Scalar::Bin && (v.op == "add" || v.op == "max" || v.op == "min")) {
+    if (is_self(*v.args[0].s) && !mentions_self(*v.args[1].s)) { *op = v.op; return true; }
+    if (is_self(*v.args[1].s) && !mentions_self(*v.args[0].s)) { *op = v.op; return true; }
+  }
+  return false;
+}
+
+}  // namespace
+
+double GemmPlan::flops() const {
+  double f = 2.0 * (double)m.extent * (double)n.extent * (double)k.extent;
+  for (auto& b : batch) f *= (double)b.extent;
+  return f;
+}
+
+std::string Code::describe() const {
+  std::ostringstream o;
+  o << "{\"name\":\"" << prog.name << "\",\"stages\":[";
+  for (size_t i = 0; i < stages.size(); ++i) {
+    const Stage& s = stages[i];
+    if (i) o << ",";
+    o << "{\"kind\":\"" << (s.kind == Stage::Memset ? "memset" : s.kind == Stage::Gemm ? "gemm" : "generic") << "\"";
+    o << ",\"kernel\":\"" << s.kernel << "\",\"total\":" << s.total << ",\"coop\":" << s.coop;
+    if (s.kind == Stage::Gemm) {
+      o << ",\"m\":" << s.gemm.m.extent << ",\"n\":" << s.gemm.n.extent << ",\"k\":" << s.gemm.k.extent;
+      int64_t b = 1;
+      for (auto& d : s.gemm.batch) b *= d.extent;
+      o << ",\"batch\":" << b << ",\"a_kmajor\":" << (s.gemm.a_kmajor ? 1 : 0) << ",\"b_kmajor\":" << (s.gemm.b_kmajor ? 1 : 0)
+        << ",\"accumulate\":" << (s.gemm.accumulate ? 1 : 0) << ",\"flops\":" << s.gemm.flops();
+    }
+    o << ",\"note\":\"" << s.note << "\"}";
+  }
+  o << "]}";
+  return o.str();
+}
+
+namespace {
+
+struct Builder {
+  Code& code;
+  const CompileOptions& opt;
+  std::ostringstream src;
+  int next_kernel = 0;
+
+  std::string kernel_name() { return code.prog.name + "_s" + std::to_string(next_kernel++); }
+
+  void emit_params(std::ostringstream& o, Stage& st, const Emitter& em, const std::set<int>& written) {
+    // parameters in node declaration order, then the static-index table, then the merge buffer
+    bool first = true;
+    for (auto& t : code.prog.tnodes) {
+      if (!em.used_nodes.count(t.id)) continue;
+      if (t.mode == Mode::Virtual) continue;
+      if (!first) o << ", ";
+      first = false;
+      const bool ro = !written.count(t.id);
+      o << (ro ? "const " : "") << Emitter::ctype(t.prec) << "* " << (ro ? "__restrict__ " : "") << t.ident;
+      st.args.push_back({KArg::Node, t.id});
+    }
+    if (em.uses_statics) {
+      if (!first) o << ", ";
+      first = false;
+      o << "const unsigned int* __restrict__ b200_statics";
+      st.args.push_back({KArg::Statics, -1});
+    }
+    if (em.uses_merge) {
+      if (!first) o << ", ";
+      first = false;
+      o << "const " << Emitter::ctype(code.prog.tn(code.prog.merge_node).prec) << "* __restrict__ merge_buffer";
+      st.args.push_back({KArg::Merge, -1});
+    }
+  }
+
+  std::string static_prologue(const std::string& body_text, Emitter& em, int ind) {
+    // static index symbols are read from the table the launcher fills
+    std::string out;
+    for (size_t i = 0; i < code.prog.statics.size(); ++i) {
+      const std::string& s = code.prog.statics[i].sym;
+      // whole-word search
+      size_t p = 0;
+      bool found = false;
+      while ((p = body_text.find(s, p)) != std::string::npos) {
+        auto isid = [](char c) { return isalnum((unsigned char)c) || c == '_'; };
+        bool l = p == 0 || !isid(body_text[p - 1]);
+        bool r = p + s.size() >= body_text.size() || !isid(body_text[p + s.size()]);
+        if (l && r) { found = true; break; }
+        p += s.size();
+      }
+      if (found) {
+        out += std::string((size_t)ind, ' ') + "const unsigned int " + s + " = b200_statics[" + std::to_string(i) + "];\n";
+        em.uses_statics = true;
+      }
+    }
+    return out;
+  }
+
+  // Tries to find a lane-strided loop for a warp-per-element reduction.
+  CoopInfo find_coop(const Stmt& body, int64_t par_total) {
+    CoopInfo ci;
+    if (!opt.enable_coop) return ci;
+    if (body.kind != Stmt::Set) return ci;
+    // every Local_scope directly inside the expression must be `init; for k {accum}` over the
+    // same extent; nested scopes inside the accumulated term are not handled
+    std::vector<const Scalar*> scopes;
+    bool nested = false;
+    std::function<void(const Scalar&, int)> rec = [&](const Scalar& e, int depth) {
+      if (e.kind == Scalar::LocalScope) {
+        if (depth > 0) nested = true;
+        scopes.push_back(&e);
+        walk_stmt(*e.body, [&](const Scalar& x) { if (x.kind == Scalar::LocalScope) nested = true; }, [](const Stmt&) {});
+        return;
+      }
+      for (auto& a : e.args) rec(*a.s, depth);
+    };
+    rec(*body.value, 0);
+    if (scopes.empty() || nested) return ci;
+    int64_t extent = -1;
+    for (auto* sc : scopes) {
+      const Stmt& b = *sc->body;
+      const Stmt* loop = nullptr;
+      const Stmt* init = nullptr;
+      if (b.kind == Stmt::For) loop = &b;
+      else if (b.kind == Stmt::Seq && b.items.size() == 2 && b.items[0]->kind == Stmt::SetLocal && b.items[1]->kind == Stmt::For) {
+        init = b.items[0].get();
+        loop = b.items[1].get();
+      } else return CoopInfo{};
+      if (init && (init->scope_id != sc->scope_id || init->value->kind != Scalar::Const)) return CoopInfo{};
+      std::string op;
+      if (!accum_form(*loop->body, sc->scope_id, sc->tn, &op)) return CoopInfo{};
+      Prec p = code.prog.tn(sc->tn).prec;
+      if (p != Prec::Single && !(p == Prec::Double && op == "add")) return CoopInfo{};
+      // the initial value must be the neutral element of the combine
+      double want = op == "add" ? 0.0 : (op == "max" ? -INFINITY : INFINITY);
+      if (init && init->value->cval != want) return CoopInfo{};
+      if (!init && op != "add") return CoopInfo{};
+      int64_t ext = loop->to - loop->from + 1;
+      if (extent < 0) extent = ext;
+      else if (ext != extent) return CoopInfo{};
+      ci.scopes.push_back({sc->scope_id, op});
+    }
+    // worth it when rows are long and a thread per row would leave the GPU idle or uncoalesced
+    if (extent < 64) return CoopInfo{};
+    (void)par_total;
+    ci.sym = "*";  // every scope loop is strided (each has its own symbol)
+    return ci;
+  }
+
+  void generic_stage(const std::vector<LoopDim>& nest, const StmtP& body) {
+    Stage st;
+    st.kind = Stage::Generic;
+    st.kernel = kernel_name();
+    // which loops are independent
+    Stmt probe;  // the nest's innermost body is what writes
+    std::vector<bool> par(nest.size(), false);
+    for (size_t i = 0; i < nest.size(); ++i) par[i] = nest[i].extent() > 0 && parallel_safe(nest[i].sym, *body);
+    for (size_t i = 0; i < nest.size(); ++i) (par[i] ? st.par : st.ser).push_back(nest[i]);
+    st.total = 1;
+    for (auto& d : st.par) st.total *= d.extent();
+    for (auto& d : nest)
+      if (d.extent() <= 0) st.total = 0;
+
+    Emitter em(code.prog);
+    em.large_models = opt.large_models;
+
+    CoopInfo ci;
+    if (st.ser.empty() && st.total > 0) ci = find_coop(*body, st.total);
+    std::set<int> written;
+    walk_stmt(*body, [](const Scalar&) {}, [&](const Stmt& s) {
+      if (s.kind == Stmt::Set || s.kind == Stmt::ZeroOut) written.insert(s.tn);
+    });
+
+    std::string inner;
+    int ind = 4 + 2 * (int)st.ser.size();
+    if (!ci.sym.empty()) {
+      st.coop = 32;
+      inner = coop_body(em, *body, ci, ind);
+    } else {
+      inner = em.stmt(*body, ind);
+    }
+    // serial loops wrap the body in their original order
+    std::string open, close;
+    int k = 4;
+    for (auto& d : st.ser) {
+      open += std::string((size_t)k, ' ') + "for (unsigned int " + d.sym + " = " + std::to_string(d.from) + "; " + d.sym +
+              " <= " + std::to_string(d.to) + "; ++" + d.sym + ") {\n";
+      k += 2;
+    }
+    for (size_t i = st.ser.size(); i-- > 0;) {
+      k -= 2;
+      close += std::string((size_t)k, ' ') + "}\n";
+    }
+    std::string body_text = open + inner + close;
+
+    // index decomposition: the innermost parallel loop varies fastest across threads
+    std::string decomp;
+    {
+      std::string rem = "b200_g";
+      for (size_t i = st.par.size(); i-- > 0;) {
+        const LoopDim& d = st.par[i];
+        std::string ext = std::to_string(d.extent()) + "ull";
+        std::string val = i == 0 ? rem : "(" + rem + " % " + ext + ")";
+        decomp += "    const unsigned int " + d.sym + " = (unsigned int)" + val +
+                  (d.from ? " + " + std::to_string(d.from) : std::string()) + ";\n";
+        if (i != 0) {
+          std::string nr = "b200_r" + std::to_string(i);
+          decomp += "    const unsigned long long " + nr + " = " + rem + " / " + ext + ";\n";
+          rem = nr;
+        }
+      }
+    }
+    std::string statics = static_prologue(body_text + decomp, em, 2);
+
+    std::ostringstream k_src;
+    k_src << "extern \"C\" __global__ void __launch_bounds__(256) " << st.kernel << "(";
+    emit_params(k_src, st, em, written);
+    k_src << ") {\n" << statics;
+    if (st.coop) {
+      k_src << "  const unsigned int b200_lane = threadIdx.x & 31u;\n";
+      k_src << "  const unsigned long long b200_warp = ((unsigned long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;\n";
+      k_src << "  const unsigned long long b200_nwarps = ((unsigned long long)gridDim.x * blockDim.x) >> 5;\n";
+      k_src << "  for (unsigned long long b200_g = b200_warp; b200_g < " << st.total << "ull; b200_g += b200_nwarps) {\n";
+    } else {
+      k_src << "  for (unsigned long long b200_g = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; b200_g < "
+            << st.total << "ull; b200_g += (unsigned long long)gridDim.x * blockDim.x) {\n";
+    }
+    k_src << decomp << body_text << "  }\n}\n\n";
+    src << k_src.str();
+    std::ostringstream note;
+    note << "par=" << st.par.size() << " ser=" << st.ser.size() << (st.coop ? " warp-per-element" : "");
+    st.note = note.str();
+    code.stages.push_back(st);
+  }
+
+  // One warp per output element: each Local_scope reduction loop is strided over the lanes,
+  // the partial results are combined with shuffles, and lane 0 evaluates and stores the rest.
+  std::string coop_body(Emitter& em, const Stmt& set, const CoopInfo& ci, int ind) {
+    std::string out;
+    std::string padding((size_t)ind, ' ');
+    const Tnode& t = code.prog.tn(set.tn);
+    // 1. emit each scope's reduction with a lane-strided loop
+    std::function<void(const Scalar&)> rec = [&](const Scalar& e) {
+      if (e.kind == Scalar::LocalScope) {
+        std::string op;
+        for (auto& s : ci.scopes)
+          if (s.first == e.scope_id) op = s.second;
+        Prec p = code.prog.tn(e.tn).prec;
+        const Stmt& b = *e.body;
+        const Stmt* loop = b.kind == Stmt::For ? &b : b.items[1].get();
+        std::string name = em.scope_name(e.scope_id, e.tn);
+        double neutral = op == "add" ? 0.0 : (op == "max" ? -INFINITY : INFINITY);
+        out += padding + Emitter::ctype(p) + " " + name + " = " + em.constant(neutral, p) + ";\n";
+        em.coop_sym = loop->index;
+        out += em.stmt(*loop, ind);
+        em.coop_sym.clear();
+        out += padding + name + " = b200_warp_" + (op == "add" ? "sum" : op) + "(" + name + ");\n";
+        em.scope_subst[e.scope_id] = name;
+        return;
+      }
+      for (auto& a : e.args) rec(*a.s);
+    };
+    rec(*set.value);
+    Emitter::Res v = em.scalar(t.prec, *set.value);
+    em.used_nodes.insert(set.tn);
+    out += padding + "if (b200_lane == 0) " + t.ident + "[" + em.offset(set.idcs, t.dims) + "] = " + v.expr + ";\n";
+    em.scope_subst.clear();
+    return out;
+  }
+
+  void memset_stage(int tn) {
+    Stage st;
+    st.kind = Stage::Memset;
+    st.memset_tn = tn;
+    st.note = "zero_out";
+    code.stages.push_back(st);
+  }
+
+  void top_level(const StmtP& s, std::vector<StmtP>& flat) {
+    if (s->kind == Stmt::Seq)
+      for (auto& x : s->items) top_level(x, flat);
+    else if (s->kind != Stmt::Noop && s->kind != Stmt::Comment)
+      flat.push_back(s);
+  }
+
+  void run() {
+    std::vector<StmtP> flat;
+    top_level(code.prog.body, flat);
+    src << kNumericsSource << "\n";
+    std::set<int> zeroed;  // nodes zeroed by the previous stage (for beta = 0 contractions)
+    for (size_t i = 0; i < flat.size(); ++i) {
+      const StmtP& s = flat[i];
+      if (s->kind == Stmt::DeclareLocal || s->kind == Stmt::SetLocal)
+        throw Error(-4, "function-scope scalar locals (cross-statement hoisting) are not supported by the b200 backend");
+      if (s->kind == Stmt::ZeroOut) {
+        const Tnode& t = code.prog.tn(s->tn);
+        if (t.mode == Mode::Virtual) continue;
+        // a zero_out that a following contraction absorbs (beta = 0) is dropped below
+        bool absorbed = false;
+        if (opt.enable_gemm && i + 1 < flat.size() && flat[i + 1]->kind == Stmt::For) {
+          std::vector<LoopDim> nest;
+          StmtP body = flat[i + 1];
+          while (body->kind == Stmt::For) {
+            nest.push_back({body->index, body->from, body->to});
+            body = body->body;
+          }
+          Stage g;
+          if (body->kind == Stmt::Set && body->tn == s->tn && match_gemm(code.prog, nest, *body, true, opt, &g)) {
+            g.kernel = kernel_name();
+            g.gemm_source = gemm_translation_unit(code.prog, g, g.kernel, opt);
+            code.stages.push_back(g);
+            absorbed = true;
+            ++i;
+          }
+        }
+        if (!absorbed) memset_stage(s->tn);
+        continue;
+      }
+      // peel the perfect loop nest
+      std::vector<LoopDim> nest;
+      StmtP body = s;
+      while (body->kind == Stmt::For) {
+        nest.push_back({body->index, body->from, body->to});
+        body = body->body;
+      }
+      if (!body_has_set(*body)) continue;
+      {
+        std::set<std::pair<int, int>> declared, used;
+        collect_scopes(*body, declared, used);
+        for (auto& u : used)
+          if (!declared.count(u))
+            throw Error(-4, "function-scope scalar locals (cross-statement hoisting) are not supported by the b200 backend");
+      }
+      if (opt.enable_gemm && body->kind == Stmt::Set) {
+        Stage g;
+        if (match_gemm(code.prog, nest, *body, false, opt, &g)) {
+          g.kernel = kernel_name();
+          g.gemm_source = gemm_translation_unit(code.prog, g, g.kernel, opt);
+          code.stages.push_back(g);
+          continue;
+        }
+      }
+      generic_stage(nest, body);
+    }
+    code.source = src.str();
+    for (auto& t : code.prog.tnodes)
+      if (t.mode == Mode::Local) code.local_nodes.push_back(t.id);
+  }
+};
+
+}  // namespace
+
+Code compile_program(Program prog, const CompileOptions& opt) {
+  Code code;
+  code.prog = std::move(prog);
+  Builder b{code, opt};
+  b.run();
+  return code;
+}
+
+}  // namespace b200

@@ -1,0 +1,79 @@
+// Device-independent compilation of a routine: the b200ir body is cut into stages, each
+// stage is classified (memset / generic loop nest / dense contraction) and CUDA source is
+// generated for it.  Mirrors the role of `Lowered_backend.compile`
+// (arrayjit/lib/backend_impl.ml:334-367): no device or context is touched here.
+#pragma once
+#include <string>
+#include <vector>
+
+#include "ir.hpp"
+
+namespace b200 {
+
+struct LoopDim {
+  std::string sym;
+  int64_t from = 0, to = 0;  // inclusive, as in Low_level.For_loop
+  int64_t extent() const { return to >= from ? to - from + 1 : 0; }
+};
+
+// One kernel argument: a tensor node pointer (in-context node, or a routine-local node that
+// lives in the routine's scratch slab), the static-index table, or the merge buffer.
+struct KArg {
+  enum Kind { Node, Statics, Merge } kind;
+  int tn = -1;
+};
+
+// A dense contraction recognised in the loop nest, in GEMM terms:
+//   D[batch, m, n] (+)= sum_k A[batch, m, k] * B[batch, n, k]
+// Every symbol group carries its extent and the element stride it has in each tensor.
+struct GemmDim {
+  int64_t extent = 1;
+  int64_t sa = 0, sb = 0, sd = 0;  // element strides in A, B and the output
+};
+struct GemmPlan {
+  int a_tn = -1, b_tn = -1, d_tn = -1;  // d_tn: the node the epilogue's Set writes
+  GemmDim m, n, k;
+  std::vector<GemmDim> batch;        // outermost first, at most 2
+  int64_t a_off = 0, b_off = 0;      // constant element offsets (fixed indices)
+  bool a_kmajor = true, b_kmajor = true;
+  bool accumulate = false;           // beta = 1: add to the existing output (form B without zero_out)
+  Prec in_prec = Prec::Bfloat16;     // operand precision (bf16 / half; single runs as tf32)
+  std::string epilogue;              // generated device code, see codegen
+  double flops() const;
+};
+
+struct Stage {
+  enum Kind { Memset, Generic, Gemm } kind = Generic;
+  int memset_tn = -1;
+  std::string kernel;            // kernel symbol in the routine's module
+  std::vector<KArg> args;
+  std::vector<LoopDim> par, ser;
+  int64_t total = 1;             // parallel iterations
+  int block = 256;
+  int coop = 0;                  // >0: lanes cooperating on one output element (row reductions)
+  GemmPlan gemm;
+  std::string gemm_source;       // full translation unit of this stage's contraction kernel
+  std::string note;              // human-readable classification, for debug info
+};
+
+struct Code {
+  Program prog;
+  std::vector<Stage> stages;
+  std::string source;            // one translation unit holding every generic kernel
+  std::vector<int> local_nodes;  // routine-local nodes that need scratch
+  std::string describe() const;  // JSON-ish summary for b200_code_info
+};
+
+struct CompileOptions {
+  bool enable_gemm = true;
+  bool enable_coop = true;
+  bool large_models = false;
+};
+
+Code compile_program(Program prog, const CompileOptions& opt);
+
+// The numeric helper prelude shared by every generated kernel (embedded at build time).
+extern const char* kNumericsSource;
+extern const char* kGemmSource;
+
+}  // namespace b200

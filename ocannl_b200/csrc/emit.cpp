@@ -1,0 +1,477 @@
+// CUDA C emission of Low_level statements and scalars (see emit.hpp for the contract).
+#include "emit.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+
+namespace b200 {
+
+namespace {
+bool same_index(const Index& a, const Index& b) {
+  return a.kind == b.kind && a.fixed == b.fixed && a.sym == b.sym && a.terms == b.terms;
+}
+bool same_indices(const Indices& a, const Indices& b) {
+  if (a.size() != b.size()) return false;
+  for (size_t i = 0; i < a.size(); ++i)
+    if (!same_index(a[i], b[i])) return false;
+  return true;
+}
+std::string pad(int n) { return std::string((size_t)n, ' '); }
+bool lowp(Prec p) { return p == Prec::Bfloat16 || p == Prec::Half; }
+const char* up_fn(Prec p) { return p == Prec::Bfloat16 ? "b200_bf2f(" : "b200_h2f("; }
+const char* down_fn(Prec p) { return p == Prec::Bfloat16 ? "b200_f2bf(" : "b200_f2h("; }
+}  // namespace
+
+const char* Emitter::ctype(Prec p) {
+  switch (p) {
+    case Prec::Byte: return "unsigned char";
+    case Prec::Uint16: return "unsigned short";
+    case Prec::Int32: return "int";
+    case Prec::Uint32: return "unsigned int";
+    case Prec::Int64: return "long long";
+    case Prec::Uint64: return "unsigned long long";
+    case Prec::Half: return "unsigned short";
+    case Prec::Bfloat16: return "unsigned short";
+    case Prec::Single: return "float";
+    case Prec::Double: return "double";
+    case Prec::Uint4x32: return "b200_u4x32";
+    case Prec::Fp8: break;
+  }
+  throw Error(-4, "precision fp8 is not supported by the b200 backend");
+}
+
+// Ops.c_convert_precision (arrayjit/lib/ops.ml:798-863) for the device spellings.
+std::pair<std::string, std::string> Emitter::convert(Prec from, Prec to) {
+  if (from == to) return {"", ""};
+  if (from == Prec::Fp8 || to == Prec::Fp8) throw Error(-4, "precision fp8 is not supported by the b200 backend");
+  if (from == Prec::Uint4x32 || to == Prec::Uint4x32) {
+    if (to == Prec::Uint4x32 && (from == Prec::Uint32 || from == Prec::Int32)) return {"b200_u32_widen((b200_u32)(", "))"};
+    throw Error(-4, "unsupported uint4x32 conversion");
+  }
+  auto is_plain_int = [](Prec p) {
+    return p == Prec::Byte || p == Prec::Uint16 || p == Prec::Int32 || p == Prec::Uint32 || p == Prec::Int64 ||
+           p == Prec::Uint64;
+  };
+  if (from == Prec::Bfloat16) {
+    if (to == Prec::Single) return {"b200_bf2f(", ")"};
+    if (to == Prec::Double) return {"(double)b200_bf2f(", ")"};
+    if (to == Prec::Half) return {"b200_f2h(b200_bf2f(", "))"};
+    return {std::string("(") + ctype(to) + ")b200_bf2f(", ")"};
+  }
+  if (to == Prec::Bfloat16) {
+    if (from == Prec::Single) return {"b200_f2bf(", ")"};
+    if (from == Prec::Half) return {"b200_f2bf(b200_h2f(", "))"};
+    return {"b200_f2bf((float)", ")"};  // double and the integer types
+  }
+  if (from == Prec::Half) {
+    if (to == Prec::Single) return {"b200_h2f(", ")"};
+    if (to == Prec::Double) return {"(double)b200_h2f(", ")"};
+    return {std::string("(") + ctype(to) + ")b200_h2f(", ")"};
+  }
+  if (to == Prec::Half) {
+    if (from == Prec::Single) return {"b200_f2h(", ")"};
+    return {"b200_f2h((float)", ")"};
+  }
+  (void)is_plain_int;
+  return {std::string("(") + ctype(to) + ")(", ")"};
+}
+
+std::string Emitter::index(const Index& ix) {
+  switch (ix.kind) {
+    case Index::Fixed: return std::to_string(ix.fixed);
+    case Index::Iter: return ix.sym;
+    case Index::SubAxis: return "";
+    case Index::Affine: {
+      std::string r;
+      for (auto& t : ix.terms) {
+        if (!r.empty()) r += "+";
+        r += t.first == 1 ? t.second : std::to_string(t.first) + "*" + t.second;
+      }
+      if (ix.fixed > 0) r += (r.empty() ? "" : "+") + std::to_string(ix.fixed);
+      else if (ix.fixed < 0) r += (r.empty() ? "" : "+") + std::string("-") + std::to_string(-ix.fixed);
+      return r.empty() ? "0" : r;
+    }
+  }
+  return "0";
+}
+
+// C_syntax.pp_array_offset (arrayjit/lib/c_syntax.ml:367-379)
+std::string Emitter::offset(const Indices& idcs, const std::vector<int64_t>& dims, int dyn_axis,
+                            const std::string& dyn_doc) {
+  if (idcs.empty()) return "0";
+  if (idcs.size() != dims.size()) throw Error(-3, "b200ir: index count does not match the node's rank");
+  auto ax = [&](size_t k) { return (int)k == dyn_axis ? dyn_doc : index(idcs[k]); };
+  std::string doc = ax(0);
+  for (size_t k = 1; k < idcs.size(); ++k) {
+    std::string d = ax(k);
+    if (doc.empty()) doc = d;
+    else if (d.empty()) doc = "(" + doc + ") * " + std::to_string(dims[k]);
+    else doc = "(" + doc + ") * " + std::to_string(dims[k]) + " + " + d;
+  }
+  return doc;
+}
+
+std::string Emitter::scope_name(int scope_id, int tn) const {
+  return "v" + std::to_string(scope_id) + "_" + P.tn(tn).ident;
+}
+std::string Emitter::node_name(int tn) const { return P.tn(tn).ident; }
+
+std::string Emitter::constant(double c, Prec prec) {
+  char buf[64];
+  if (prec == Prec::Single || lowp(prec)) {
+    std::string lit;
+    if (std::isinf(c)) lit = c > 0 ? "B200_INF" : "(-B200_INF)";
+    else if (std::isnan(c)) lit = "B200_NAN";
+    else {
+      snprintf(buf, sizeof buf, "%a", (double)(float)c);
+      lit = std::string(buf) + "f";
+      if (c < 0) lit = "(" + lit + ")";
+    }
+    if (prec == Prec::Single) return lit;
+    return std::string(down_fn(prec)) + lit + ")";
+  }
+  if (prec == Prec::Double) {
+    if (std::isinf(c)) return c > 0 ? "((double)B200_INF)" : "(-(double)B200_INF)";
+    if (std::isnan(c)) return "((double)B200_NAN)";
+    snprintf(buf, sizeof buf, "%a", c);
+    return c < 0 ? "(" + std::string(buf) + ")" : std::string(buf);
+  }
+  snprintf(buf, sizeof buf, "%a", c);
+  return std::string("(") + ctype(prec) + ")(" + buf + ")";
+}
+
+// Ops.binop_c_syntax / unop_c_syntax / ternop_c_syntax with device literals.
+static std::string binop_plain(Prec prec, const std::string& op, const std::string& a, const std::string& b) {
+  const bool dbl = prec == Prec::Double;
+  const bool integ = is_int_prec(prec);
+  const std::string zero = integ ? "0" : (dbl ? "0.0" : "0.0f");
+  const std::string T = Emitter::ctype(prec);
+  if (op == "add") return "(" + a + " + " + b + ")";
+  if (op == "sub") return "(" + a + " - " + b + ")";
+  if (op == "mul") return "(" + a + " * " + b + ")";
+  if (op == "div") return "(" + a + " / " + b + ")";
+  if (op == "pow") {
+    if (integ) throw Error(-4, "pow is not defined for integer precisions");
+    return (dbl ? "pow(" : "powf(") + a + ", " + b + ")";
+  }
+  if (op == "relu_gate") return "(" + a + " > " + zero + " ? " + b + " : " + zero + ")";
+  if (op == "sat01_gate") {
+    if (integ) return "(abs(" + a + ") > 0 ? 0 : (" + b + "))";
+    return (dbl ? "(fabs(floor(" : "(fabsf(floorf(") + a + ")) > " + zero + " ? " + zero + " : (" + b + "))";
+  }
+  if (op == "max" || op == "min") {
+    if (integ) return "(" + T + ")f" + op + "((double)(" + a + "), (double)(" + b + "))";
+    return std::string("f") + op + (dbl ? "(" : "f(") + a + ", " + b + ")";
+  }
+  if (op == "mod") return "(" + a + " % " + b + ")";
+  const char* sym = op == "lt" ? "<" : op == "eq" ? "==" : op == "ne" ? "!=" : op == "or" ? "||" : op == "and" ? "&&" : nullptr;
+  if (sym) return "((" + T + ")(" + a + " " + sym + " " + b + "))";
+  throw Error(-4, "unsupported binary operation '" + op + "'");
+}
+
+static std::string unop_plain(Prec prec, const std::string& op, const std::string& v) {
+  const bool dbl = prec == Prec::Double;
+  const bool integ = is_int_prec(prec);
+  const std::string zero = integ ? "0" : (dbl ? "0.0" : "0.0f");
+  const std::string one = integ ? "1" : (dbl ? "1.0" : "1.0f");
+  const std::string T = Emitter::ctype(prec);
+  auto fn = [&](const char* name) {
+    if (integ) return "(" + T + ")" + name + "((double)(" + v + "))";
+    return std::string(name) + (dbl ? "(" : "f(") + v + ")";
+  };
+  if (op == "id") return v;
+  if (op == "relu") {
+    if (integ) return "(" + T + ")fmax(0.0, (double)(" + v + "))";
+    return std::string(dbl ? "fmax(" : "fmaxf(") + zero + ", " + v + ")";
+  }
+  if (op == "sat01") {
+    if (integ) return "(" + T + ")fmax(0.0, fmin(1.0, (double)(" + v + ")))";
+    return std::string(dbl ? "fmax(" : "fmaxf(") + zero + ", " + (dbl ? "fmin(" : "fminf(") + one + ", " + v + "))";
+  }
+  if (op == "exp" || op == "log" || op == "exp2" || op == "log2" || op == "sin" || op == "cos" || op == "sqrt")
+    return fn(op.c_str());
+  if (integ && (op == "recip" || op == "recip_sqrt" || op == "tanh"))
+    throw Error(-4, "operation '" + op + "' is not defined for integer precisions");
+  if (op == "recip") return "(" + one + " / (" + v + "))";
+  if (op == "recip_sqrt") return "(" + one + " / " + (dbl ? "sqrt(" : "sqrtf(") + v + "))";
+  if (op == "neg") return "(-(" + v + "))";
+  if (op == "trunc") return dbl ? "trunc(" + v + ")" : "truncf(" + v + ")";
+  if (op == "tanh") return dbl ? "tanh(" + v + ")" : "tanhf(" + v + ")";
+  if (op == "not") return "(" + v + " == " + zero + " ? " + one + " : " + zero + ")";
+  throw Error(-4, "unsupported unary operation '" + op + "'");
+}
+
+static std::string ternop_plain(Prec prec, const std::string& op, const std::string& a, const std::string& b,
+                                const std::string& c) {
+  const bool dbl = prec == Prec::Double;
+  const bool integ = is_int_prec(prec);
+  if (op == "where") return "((" + a + ") != 0 ? (" + b + ") : (" + c + "))";
+  if (op == "fma") {
+    if (integ) return "((" + a + ") * (" + b + ") + (" + c + "))";
+    return std::string(dbl ? "fma(" : "fmaf(") + a + ", " + b + ", " + c + ")";
+  }
+  if (op == "mul3") return "((" + a + ") * (" + b + ") * (" + c + "))";
+  throw Error(-4, "unsupported ternary operation '" + op + "'");
+}
+
+std::string Emitter::binop(Prec prec, const std::string& op, const std::string& a, const std::string& b) {
+  if (lowp(prec))
+    return std::string(down_fn(prec)) + binop_plain(Prec::Single, op, up_fn(prec) + a + ")", up_fn(prec) + b + ")") + ")";
+  return binop_plain(prec, op, a, b);
+}
+std::string Emitter::unop(Prec prec, const std::string& op, const std::string& a) {
+  if (lowp(prec)) return std::string(down_fn(prec)) + unop_plain(Prec::Single, op, up_fn(prec) + a + ")") + ")";
+  return unop_plain(prec, op, a);
+}
+std::string Emitter::ternop(Prec prec, const std::string& op, const std::string& a, const std::string& b,
+                            const std::string& c) {
+  if (lowp(prec)) {
+    // `where` in a low-precision context: the condition was rendered in its own precision
+    // and is converted like the arms (cc_backend.ml:169-186 wraps all three arguments).
+    return std::string(down_fn(prec)) +
+           ternop_plain(Prec::Single, op, up_fn(prec) + a + ")", up_fn(prec) + b + ")", up_fn(prec) + c + ")") + ")";
+  }
+  return ternop_plain(prec, op, a, b, c);
+}
+
+// Low_level.reads_scope_before_set (arrayjit/lib/low_level.ml:1998-2037)
+bool Emitter::reads_scope_before_set(int scope_id, int tn, const Stmt& body) {
+  struct W {
+    int sid, tn;
+    bool sc_reads(const Scalar& e) const {
+      switch (e.kind) {
+        case Scalar::GetLocal: return e.scope_id == sid && e.tn == tn;
+        case Scalar::LocalScope: return st_reads(*e.body);
+        case Scalar::GetDyn: return sc_reads(*e.args[0].s);
+        case Scalar::Tern:
+        case Scalar::Bin:
+        case Scalar::Un:
+          for (auto& a : e.args)
+            if (sc_reads(*a.s)) return true;
+          return false;
+        default: return false;
+      }
+    }
+    bool st_reads(const Stmt& s) const {
+      switch (s.kind) {
+        case Stmt::Seq:
+          for (auto& x : s.items)
+            if (st_reads(*x)) return true;
+          return false;
+        case Stmt::For: return st_reads(*s.body);
+        case Stmt::Set:
+        case Stmt::SetLocal: return sc_reads(*s.value);
+        default: return false;
+      }
+    }
+    // 0 neither, 1 read, 2 written
+    int scan(const Stmt& s) const {
+      switch (s.kind) {
+        case Stmt::Set: return sc_reads(*s.value) ? 1 : 0;
+        case Stmt::SetLocal:
+          if (sc_reads(*s.value)) return 1;
+          return (s.scope_id == sid && s.tn == tn) ? 2 : 0;
+        case Stmt::Seq:
+          for (auto& x : s.items) {
+            int r = scan(*x);
+            if (r) return r;
+          }
+          return 0;
+        case Stmt::For: {
+          int r = scan(*s.body);
+          if (r == 2) return s.from <= s.to ? 2 : 0;
+          return r;
+        }
+        default: return 0;
+      }
+    }
+  } w{scope_id, tn};
+  return w.scan(body) != 2;
+}
+
+Emitter::Res Emitter::scalar(Prec prec, const Scalar& e) {
+  Res r;
+  switch (e.kind) {
+    case Scalar::LocalScope: {
+      Prec sp = P.tn(e.tn).prec;
+      auto cv = convert(sp, prec);
+      auto sub = scope_subst.find(e.scope_id);
+      if (sub != scope_subst.end()) {
+        r.expr = cv.first + sub->second + cv.second;
+        return r;
+      }
+      std::string init;
+      if (reads_scope_before_set(e.scope_id, e.tn, *e.body)) init = " = " + constant(0.0, sp);
+      std::string def = std::string(ctype(sp)) + " " + scope_name(e.scope_id, e.tn) + init + ";\n" + stmt(*e.body, 0);
+      r.defs.push_back({e.scope_id, def});
+      r.expr = cv.first + scope_name(e.scope_id, e.tn) + cv.second;
+      return r;
+    }
+    case Scalar::GetLocal: {
+      auto cv = convert(P.tn(e.tn).prec, prec);
+      auto sub = scope_subst.find(e.scope_id);
+      r.expr = cv.first + (sub != scope_subst.end() ? sub->second : scope_name(e.scope_id, e.tn)) + cv.second;
+      return r;
+    }
+    case Scalar::Get:
+    case Scalar::GetMerge: {
+      const Tnode& t = P.tn(e.tn);
+      auto cv = convert(t.prec, prec);
+      if (e.kind == Scalar::Get) {
+        auto f = forwarded.find(e.tn);
+        if (f != forwarded.end() && same_indices(f->second.first, e.idcs)) {
+          r.expr = cv.first + f->second.second + cv.second;
+          return r;
+        }
+        if (t.mode == Mode::Virtual) throw Error(-3, "b200ir: read of virtual node '" + t.ident + "'");
+        used_nodes.insert(e.tn);
+      } else {
+        uses_merge = true;
+      }
+      std::string name = e.kind == Scalar::GetMerge ? "merge_buffer" : t.ident;
+      r.expr = cv.first + name + "[" + offset(e.idcs, t.dims) + "]" + cv.second;
+      return r;
+    }
+    case Scalar::GetDyn: {
+      const Tnode& t = P.tn(e.tn);
+      auto cv = convert(t.prec, prec);
+      Res d = scalar(e.args[0].prec, *e.args[0].s);
+      used_nodes.insert(e.tn);
+      std::string dyn = std::string("((") + (large_models ? "unsigned long long" : "unsigned int") + ")(" + d.expr + "))";
+      r.defs = d.defs;
+      r.expr = cv.first + t.ident + "[" + offset(e.idcs, t.dims, e.dyn_axis, dyn) + "]" + cv.second;
+      return r;
+    }
+    case Scalar::Const: r.expr = constant(e.cval, prec); return r;
+    case Scalar::ConstBits: {
+      auto cv = convert(Prec::Int64, prec);
+      r.expr = cv.first + std::to_string(e.bits) + "LL" + cv.second;
+      return r;
+    }
+    case Scalar::EmbedIdx: {
+      auto cv = convert(large_models ? Prec::Uint64 : Prec::Uint32, prec);
+      std::string d = index(e.idx);
+      r.expr = cv.first + (d.empty() ? "0" : d) + cv.second;
+      return r;
+    }
+    case Scalar::Bin: {
+      if (e.op == "arg1") return scalar(prec, *e.args[0].s);
+      if (e.op == "arg2") return scalar(prec, *e.args[1].s);
+      Res a = scalar(prec, *e.args[0].s), b = scalar(prec, *e.args[1].s);
+      r.defs = a.defs;
+      r.defs.insert(r.defs.end(), b.defs.begin(), b.defs.end());
+      r.expr = binop(prec, e.op, a.expr, b.expr);
+      return r;
+    }
+    case Scalar::Un: {
+      Res a = scalar(prec, *e.args[0].s);
+      r.defs = a.defs;
+      r.expr = unop(prec, e.op, a.expr);
+      return r;
+    }
+    case Scalar::Tern: {
+      const bool is_where = e.op == "where";
+      Res a = scalar(is_where ? e.args[0].prec : prec, *e.args[0].s);
+      Res b = scalar(prec, *e.args[1].s), c = scalar(prec, *e.args[2].s);
+      r.defs = a.defs;
+      r.defs.insert(r.defs.end(), b.defs.begin(), b.defs.end());
+      r.defs.insert(r.defs.end(), c.defs.begin(), c.defs.end());
+      if (is_where) {
+        // the condition keeps its own precision: compare it there, select in `prec`
+        std::string cond = a.expr;
+        Prec cp = e.args[0].prec;
+        if (cp == Prec::Bfloat16) cond = "b200_bf2f(" + cond + ")";
+        else if (cp == Prec::Half) cond = "b200_h2f(" + cond + ")";
+        r.expr = "((" + cond + ") != 0 ? (" + b.expr + ") : (" + c.expr + "))";
+      } else {
+        r.expr = ternop(prec, e.op, a.expr, b.expr, c.expr);
+      }
+      return r;
+    }
+  }
+  throw Error(-3, "b200ir: unknown scalar");
+}
+
+static std::string emit_defs(std::vector<std::pair<int, std::string>> defs, int indent) {
+  std::stable_sort(defs.begin(), defs.end(), [](auto& a, auto& b) { return a.first < b.first; });
+  std::string out;
+  int last = -1;
+  bool first = true;
+  for (auto& d : defs) {
+    if (!first && d.first == last) continue;
+    first = false;
+    last = d.first;
+    // re-indent the definition text
+    size_t pos = 0;
+    while (pos < d.second.size()) {
+      size_t nl = d.second.find('\n', pos);
+      std::string line = d.second.substr(pos, nl == std::string::npos ? std::string::npos : nl - pos);
+      if (!line.empty()) out += pad(indent) + line + "\n";
+      if (nl == std::string::npos) break;
+      pos = nl + 1;
+    }
+  }
+  return out;
+}
+
+std::string Emitter::stmt(const Stmt& s, int ind) {
+  switch (s.kind) {
+    case Stmt::Noop: return "";
+    case Stmt::Comment: {
+      std::string t = s.text;
+      for (size_t p = 0; (p = t.find("*/", p)) != std::string::npos;) t.replace(p, 2, "* /");
+      return pad(ind) + "/* " + t + " */\n";
+    }
+    case Stmt::Seq: {
+      std::string out;
+      for (auto& x : s.items) out += stmt(*x, ind);
+      return out;
+    }
+    case Stmt::For: {
+      const char* it = large_models ? "unsigned long long" : "unsigned int";
+      std::string lo = std::to_string(s.from), hi = std::to_string(s.to);
+      std::string head;
+      if (!coop_sym.empty() && coop_sym == s.index) {
+        // cooperative reduction: the lanes of a warp stride over this loop
+        head = pad(ind) + "for (" + it + " " + s.index + " = " + lo + " + b200_lane; " + s.index + " <= " + hi + "; " +
+               s.index + " += 32) {\n";
+      } else {
+        head = pad(ind) + "for (" + it + " " + s.index + " = " + lo + "; " + s.index + " <= " + hi + "; ++" + s.index + ") {\n";
+      }
+      return head + stmt(*s.body, ind + 2) + pad(ind) + "}\n";
+    }
+    case Stmt::ZeroOut: {
+      const Tnode& t = P.tn(s.tn);
+      used_nodes.insert(s.tn);
+      std::string n = std::to_string(t.num_elems());
+      std::string v = "b200_z" + std::to_string(tmp_counter++);
+      return pad(ind) + "for (unsigned int " + v + " = 0; " + v + " < " + n + "; ++" + v + ") " + t.ident + "[" + v +
+             "] = " + constant(0.0, t.prec) + ";\n";
+    }
+    case Stmt::Set: {
+      const Tnode& t = P.tn(s.tn);
+      if (t.mode == Mode::Virtual) throw Error(-3, "b200ir: write to virtual node '" + t.ident + "'");
+      Res v = scalar(t.prec, *s.value);
+      used_nodes.insert(s.tn);
+      std::string a = t.ident + "[" + offset(s.idcs, t.dims) + "] = " + v.expr + ";\n";
+      if (v.defs.empty()) return pad(ind) + a;
+      return pad(ind) + "{\n" + emit_defs(v.defs, ind + 2) + pad(ind + 2) + a + pad(ind) + "}\n";
+    }
+    case Stmt::SetLocal: {
+      Prec p = P.tn(s.tn).prec;
+      Res v = scalar(p, *s.value);
+      auto sub = scope_subst.find(s.scope_id);
+      std::string a = (sub != scope_subst.end() ? sub->second : scope_name(s.scope_id, s.tn)) + " = " + v.expr + ";\n";
+      if (v.defs.empty()) return pad(ind) + a;
+      return pad(ind) + "{\n" + emit_defs(v.defs, ind + 2) + pad(ind + 2) + a + pad(ind) + "}\n";
+    }
+    case Stmt::DeclareLocal: {
+      Prec p = P.tn(s.tn).prec;
+      return pad(ind) + ctype(p) + " " + scope_name(s.scope_id, s.tn) + (s.needs_init ? " = " + constant(0.0, p) : "") + ";\n";
+    }
+  }
+  return "";
+}
+
+}  // namespace b200

@@ -1,0 +1,64 @@
+// CUDA C emission of Low_level statements and scalars.
+//
+// The arithmetic contract is the cc backend's (arrayjit/lib/c_syntax.ml:441-855 with the
+// operator tables of arrayjit/lib/ops.ml:579-863 and the compute-in-float rule for
+// bf16/half of arrayjit/lib/cc_backend.ml:169-322): every homogeneous operation converts
+// its arguments to the RESULT precision first, `where` keeps the precision of its
+// condition, constants are doubles converted to the context precision, offsets are
+// row-major.  Differences from the C text, none of which changes a result beyond the last
+// bit: float contexts use float literals (the C text writes `0.0`/`1.0` and lets the
+// compiler fold them), and indices are `unsigned`.
+#pragma once
+#include <map>
+#include <set>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "ir.hpp"
+
+namespace b200 {
+
+struct Emitter {
+  const Program& P;
+  bool large_models = false;
+  // scope ids whose Local_scope is replaced by a ready expression (the accumulator a
+  // contraction kernel hands to its epilogue)
+  std::map<int, std::string> scope_subst;
+  // (node id) -> expression holding the value just stored at the position of the current
+  // parallel iteration; lets a fused consumer read a producer's value from a register
+  std::map<int, std::pair<Indices, std::string>> forwarded;
+  // nodes whose loads may use the read-only data path
+  std::set<int> readonly_nodes;
+  // cooperative reductions: scope id -> lane-strided loop symbol (see compile.cpp)
+  std::string coop_sym;
+  std::set<int> used_nodes;
+  bool uses_statics = false, uses_merge = false;
+  int tmp_counter = 0;
+
+  explicit Emitter(const Program& p) : P(p) {}
+
+  static const char* ctype(Prec p);
+  static std::pair<std::string, std::string> convert(Prec from, Prec to);
+  std::string index(const Index& ix);
+  std::string offset(const Indices& idcs, const std::vector<int64_t>& dims, int dyn_axis = -1,
+                     const std::string& dyn_doc = "");
+  std::string scope_name(int scope_id, int tn) const;
+  std::string node_name(int tn) const;
+
+  struct Res {
+    std::vector<std::pair<int, std::string>> defs;
+    std::string expr;
+  };
+  Res scalar(Prec prec, const Scalar& s);
+  std::string stmt(const Stmt& s, int indent);
+  std::string constant(double c, Prec prec);
+  static bool reads_scope_before_set(int scope_id, int tn, const Stmt& body);
+
+  std::string binop(Prec prec, const std::string& op, const std::string& a, const std::string& b);
+  std::string unop(Prec prec, const std::string& op, const std::string& a);
+  std::string ternop(Prec prec, const std::string& op, const std::string& a, const std::string& b,
+                     const std::string& c);
+};
+
+}  // namespace b200

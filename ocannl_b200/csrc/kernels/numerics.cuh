@@ -1,0 +1,105 @@
+// Device numerics shared by every generated kernel.  Self-contained (no headers) so that
+// NVRTC can compile it as the prelude of a routine's translation unit.
+//
+// Bit-level helpers follow the reference's C helpers so that integer paths agree bit for
+// bit with the cc backend (arrayjit/lib/builtins.c):
+//   bf16 <-> f32        :611-627  (shift / add 0x7FFF + lsb, no NaN special case)
+//   threefry4x32        :156-329  (20-round and 2-round forms)
+//   uniform conversions :345-360, widening to uint4x32 :545-578
+// Half values are stored as their 16 bits; arithmetic on them is done in f32 and rounded
+// once per operation, as arrayjit/lib/cc_backend.ml:169-322 prescribes.
+#ifndef B200_NUMERICS_CUH
+#define B200_NUMERICS_CUH
+
+typedef unsigned int b200_u32;
+typedef unsigned long long b200_u64;
+
+#define B200_INF (__int_as_float(0x7f800000))
+#define B200_NAN (__int_as_float(0x7fffffff))
+
+__device__ __forceinline__ float b200_bf2f(unsigned short h) { return __uint_as_float(((b200_u32)h) << 16); }
+__device__ __forceinline__ unsigned short b200_f2bf(float f) {
+  b200_u32 u = __float_as_uint(f);
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  return (unsigned short)(u >> 16);
+}
+__device__ __forceinline__ float b200_h2f(unsigned short h) {
+  float f;
+  asm("{ .reg .b16 t; mov.b16 t, %1; cvt.f32.f16 %0, t; }" : "=f"(f) : "h"(h));
+  return f;
+}
+__device__ __forceinline__ unsigned short b200_f2h(float f) {
+  unsigned short h;
+  asm("{ .reg .b16 t; cvt.rn.f16.f32 t, %1; mov.b16 %0, t; }" : "=h"(h) : "f"(f));
+  return h;
+}
+
+struct b200_u4x32 {
+  b200_u32 v[4];
+};
+
+__device__ __forceinline__ b200_u32 b200_rotl(b200_u32 x, unsigned n) { return (x << n) | (x >> (32 - n)); }
+__device__ __forceinline__ void b200_mix2(b200_u32* x, unsigned r0, unsigned r1, unsigned r2, unsigned r3) {
+  b200_u32 t;
+  x[0] += x[1]; x[1] = b200_rotl(x[1], r0) ^ x[0];
+  x[2] += x[3]; x[3] = b200_rotl(x[3], r1) ^ x[2];
+  t = x[1]; x[1] = x[3]; x[3] = t;
+  x[0] += x[1]; x[1] = b200_rotl(x[1], r2) ^ x[0];
+  x[2] += x[3]; x[3] = b200_rotl(x[3], r3) ^ x[2];
+  t = x[1]; x[1] = x[3]; x[3] = t;
+}
+template <int INJECTIONS>
+__device__ __forceinline__ b200_u4x32 b200_threefry(b200_u4x32 key, b200_u4x32 ctr) {
+  b200_u32 ks[5], x[4];
+  ks[4] = 0x1BD11BDAu;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { ks[i] = key.v[i]; ks[4] ^= key.v[i]; x[i] = ctr.v[i] + key.v[i]; }
+#pragma unroll
+  for (int s = 1; s <= INJECTIONS; ++s) {
+    b200_mix2(x, 13, 15, 26, 6);
+    b200_mix2(x, 17, 29, 16, 24);
+    if (INJECTIONS > 1) {
+      b200_mix2(x, 13, 15, 26, 6);
+      b200_mix2(x, 17, 29, 16, 24);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) x[i] += ks[(s + i) % 5];
+    x[3] += (b200_u32)s;
+  }
+  b200_u4x32 r;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) r.v[i] = x[i];
+  return r;
+}
+__device__ __forceinline__ b200_u4x32 b200_threefry_crypto(b200_u4x32 k, b200_u4x32 c) { return b200_threefry<5>(k, c); }
+__device__ __forceinline__ b200_u4x32 b200_threefry_light(b200_u4x32 k, b200_u4x32 c) { return b200_threefry<1>(k, c); }
+__device__ __forceinline__ float b200_u32_uniform(b200_u32 x) { return (float)(x >> 8) * (1.0f / 16777216.0f); }
+__device__ __forceinline__ b200_u4x32 b200_u32_widen(b200_u32 x) {
+  b200_u4x32 r;
+  r.v[0] = x; r.v[1] = x ^ 0x9E3779B9u; r.v[2] = x ^ 0x6C078965u; r.v[3] = x ^ ((x << 16) | (x >> 16));
+  return r;
+}
+
+// ---- warp-level combine used by cooperative (one warp per output element) reductions
+__device__ __forceinline__ float b200_warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float b200_warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float b200_warp_min(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ double b200_warp_sum(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+#endif  // B200_NUMERICS_CUH

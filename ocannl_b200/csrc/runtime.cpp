@@ -1,0 +1,217 @@
+// Linking and launching of compiled routines.
+//
+// `link` binds every in-context node of the routine to {pool, offset}
+// (`Lowered_backend.link`, arrayjit/lib/backend_impl.ml:334-367; the cuda backend resolves the
+// same pairs at each launch, arrayjit/lib/cuda_backend.ml:1005-1009) and loads the routine's
+// machine code.  `launch` enqueues the stages on the device stream; static index values
+// travel through a small device table so that a captured CUDA graph stays valid when they
+// change between runs.
+#include "runtime.hpp"
+
+#include <cstring>
+
+using namespace b200;
+
+static const size_t kRing = 512;
+
+CUdeviceptr b200_dev::address(int pool_id, size_t offset, size_t bytes) {
+  std::lock_guard<std::mutex> g(mu);
+  auto it = pools.find(pool_id);
+  if (it == pools.end()) throw Error(B200_E_INVALID, "unknown pool id " + std::to_string(pool_id));
+  if (offset > it->second.bytes || bytes > it->second.bytes - offset)
+    throw Error(B200_E_INVALID, "range [" + std::to_string(offset) + ", +" + std::to_string(bytes) + ") exceeds pool " +
+                                    std::to_string(pool_id) + " of " + std::to_string(it->second.bytes) + " bytes");
+  return it->second.ptr + offset;
+}
+
+void b200_dev::check_status() {
+  if (status_host && status_host[0] != 0) {
+    unsigned int code = status_host[0], where = status_host[1];
+    status_host[0] = 0;
+    status_host[1] = 0;
+    throw Error(B200_E_DEVICE, "a kernel gave up a bounded wait (code " + std::to_string(code) + ", site " +
+                                   std::to_string(where) + ")");
+  }
+}
+
+void b200_routine::link(b200_dev* d, b200_code* c, const b200_binding* b, int n) {
+  dev = d;
+  code = c;
+  const Program& P = c->code.prog;
+  std::map<int, const b200_binding*> bind;
+  for (int i = 0; i < n; ++i) bind[b[i].tn_id] = &b[i];
+
+  // routine-local nodes live in a scratch slab owned by the routine
+  size_t off = 0;
+  std::map<int, size_t> local_off;
+  for (int id : c->code.local_nodes) {
+    const Tnode& t = P.tn(id);
+    local_off[id] = off;
+    if (t.zero_init) scratch_zero.push_back({off, (size_t)t.bytes()});
+    off += ((size_t)t.bytes() + 255) & ~(size_t)255;
+  }
+  scratch_bytes = off;
+  if (scratch_bytes) cu_check(cu().cuMemAlloc_(&scratch, scratch_bytes), "cuMemAlloc(scratch)");
+
+  for (auto& t : P.tnodes) {
+    if (t.mode == Mode::Local) {
+      node_ptr[t.id] = scratch + local_off[t.id];
+    } else if (t.is_param()) {
+      auto it = bind.find(t.id);
+      if (it == bind.end()) continue;  // checked per stage below: only nodes a stage uses are required
+      node_ptr[t.id] = d->address(it->second->pool_id, it->second->offset, (size_t)t.bytes());
+    }
+  }
+
+  if (!P.statics.empty()) {
+    cu_check(cu().cuMemAlloc_(&statics_dev, 256 + 4 * P.statics.size()), "cuMemAlloc(statics)");
+    void* hp = nullptr;
+    cu_check(cu().cuMemHostAlloc_(&hp, kRing * 4 * P.statics.size(), 0), "cuMemHostAlloc(statics)");
+    statics_ring = (unsigned int*)hp;
+  }
+
+  if (c->cubin) cu_check(cu().cuModuleLoadData_(&module, c->cubin->data()), "cuModuleLoadData");
+  const size_t ns = c->code.stages.size();
+  fns.assign(ns, nullptr);
+  arg_values.assign(ns, {});
+  gemm.assign(ns, nullptr);
+  gemm_modules.assign(ns, nullptr);
+  for (size_t i = 0; i < ns; ++i) {
+    const Stage& st = c->code.stages[i];
+    if (st.kind == Stage::Memset) {
+      if (!node_ptr.count(st.memset_tn))
+        throw Error(B200_E_USER, "link: node '" + P.tn(st.memset_tn).ident + "' has no buffer binding");
+      continue;
+    }
+    for (auto& a : st.args) {
+      if (a.kind == KArg::Node) {
+        auto it = node_ptr.find(a.tn);
+        if (it == node_ptr.end()) throw Error(B200_E_USER, "link: node '" + P.tn(a.tn).ident + "' has no buffer binding");
+        arg_values[i].push_back(it->second);
+      } else if (a.kind == KArg::Statics) {
+        arg_values[i].push_back(statics_dev);
+      } else {
+        arg_values[i].push_back(0);  // merge buffer: resolved at launch (pool 0 may be re-allocated)
+      }
+    }
+    if (st.kind == Stage::Generic) {
+      cu_check(cu().cuModuleGetFunction_(&fns[i], module, st.kernel.c_str()), "cuModuleGetFunction");
+    } else {
+      cu_check(cu().cuModuleLoadData_(&gemm_modules[i], c->gemm_cubins[i]->data()), "cuModuleLoadData(gemm)");
+      cu_check(cu().cuModuleGetFunction_(&fns[i], gemm_modules[i], st.kernel.c_str()), "cuModuleGetFunction(gemm)");
+      gemm[i] = gemm_prepare(this, (int)i);
+    }
+  }
+}
+
+void b200_routine::enqueue_stages() {
+  const Program& P = code->code.prog;
+  for (auto& z : scratch_zero)
+    cu_check(cu().cuMemsetD8Async_(scratch + z.first, 0, z.second, dev->stream), "cuMemsetD8Async(scratch)");
+  for (size_t i = 0; i < code->code.stages.size(); ++i) {
+    const Stage& st = code->code.stages[i];
+    if (st.kind == Stage::Memset) {
+      const Tnode& t = P.tn(st.memset_tn);
+      cu_check(cu().cuMemsetD8Async_(node_ptr[st.memset_tn], 0, (size_t)t.bytes(), dev->stream), "cuMemsetD8Async");
+      continue;
+    }
+    if (st.total <= 0 && st.kind == Stage::Generic) continue;
+    if (st.kind == Stage::Gemm) {
+      gemm_enqueue(this, (int)i);
+      dev->n_launches++;
+      continue;
+    }
+    std::vector<CUdeviceptr>& vals = arg_values[i];
+    for (size_t a = 0; a < st.args.size(); ++a)
+      if (st.args[a].kind == KArg::Merge) vals[a] = dev->address(0, 0, (size_t)P.tn(P.merge_node).bytes());
+    std::vector<void*> args(vals.size());
+    for (size_t a = 0; a < vals.size(); ++a) args[a] = &vals[a];
+    long long threads = st.coop ? st.total * st.coop : st.total;
+    long long blocks = (threads + st.block - 1) / st.block;
+    long long cap = (long long)dev->sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    cu_check(cu().cuLaunchKernel_(fns[i], (unsigned)blocks, 1, 1, (unsigned)st.block, 1, 1, 0, dev->stream, args.data(),
+                                  nullptr),
+             "cuLaunchKernel");
+    dev->n_launches++;
+  }
+}
+
+void b200_routine::launch(const int64_t* static_idx, int n_static) {
+  const Program& P = code->code.prog;
+  if (n_static != (int)P.statics.size())
+    throw Error(B200_E_USER, "routine '" + P.name + "' takes " + std::to_string(P.statics.size()) + " static indices, got " +
+                                 std::to_string(n_static));
+  if (n_static > 0) {
+    bool changed = !statics_valid;
+    for (int i = 0; i < n_static; ++i) {
+      long long v = static_idx[i];
+      if (v < 0) throw Error(B200_E_USER, "static index " + P.statics[i].sym + " is negative: " + std::to_string(v));
+      if (P.statics[i].range >= 0 && v >= P.statics[i].range)
+        throw Error(B200_E_USER, "static index " + P.statics[i].sym + " is too big: " + std::to_string(v) + " >= " +
+                                     std::to_string(P.statics[i].range));
+      if (v > 0xffffffffLL) throw Error(B200_E_USER, "static index " + P.statics[i].sym + " does not fit 32 bits");
+      if (!statics_valid || last_statics[i] != v) changed = true;
+    }
+    if (changed) {
+      if (ring_pos == kRing) {  // staging slots may still be in flight: drain before reuse
+        cu_check(cu().cuStreamSynchronize_(dev->stream), "cuStreamSynchronize");
+        ring_pos = 0;
+      }
+      unsigned int* slot = statics_ring + ring_pos * n_static;
+      ++ring_pos;
+      last_statics.assign(static_idx, static_idx + n_static);
+      for (int i = 0; i < n_static; ++i) slot[i] = (unsigned int)static_idx[i];
+      cu_check(cu().cuMemcpyHtoDAsync_(statics_dev, slot, 4 * (size_t)n_static, dev->stream), "cuMemcpyHtoDAsync(statics)");
+      statics_valid = true;
+    }
+  }
+  if (want_graph) {
+    if (!graph) {
+      CUgraph g = nullptr;
+      cu_check(cu().cuStreamBeginCapture_(dev->stream, CU_STREAM_CAPTURE_MODE_THREAD_LOCAL), "cuStreamBeginCapture");
+      try {
+        enqueue_stages();
+      } catch (...) {
+        cu().cuStreamEndCapture_(dev->stream, &g);
+        if (g) cu().cuGraphDestroy_(g);
+        throw;
+      }
+      cu_check(cu().cuStreamEndCapture_(dev->stream, &g), "cuStreamEndCapture");
+      CUresult r = cu().cuGraphInstantiateWithFlags_(&graph, g, 0);
+      cu().cuGraphDestroy_(g);
+      cu_check(r, "cuGraphInstantiate");
+    }
+    cu_check(cu().cuGraphLaunch_(graph, dev->stream), "cuGraphLaunch");
+    dev->n_graph_launches++;
+    for (auto& s : code->code.stages) dev->n_launches += s.kind != Stage::Memset;
+    return;
+  }
+  enqueue_stages();
+}
+
+void b200_routine::set_graph(bool on) {
+  want_graph = on;
+  if (!on && graph) {
+    cu().cuGraphExecDestroy_(graph);
+    graph = nullptr;
+  }
+}
+
+void b200_routine::destroy() {
+  if (dev) cu().cuStreamSynchronize_(dev->stream);
+  if (graph) cu().cuGraphExecDestroy_(graph);
+  for (auto* g : gemm) gemm_release(g);
+  for (auto m : gemm_modules)
+    if (m) cu().cuModuleUnload_(m);
+  if (module) cu().cuModuleUnload_(module);
+  if (scratch) cu().cuMemFree_(scratch);
+  if (statics_dev) cu().cuMemFree_(statics_dev);
+  if (statics_ring) cu().cuMemFreeHost_(statics_ring);
+  graph = nullptr;
+  module = nullptr;
+  scratch = 0;
+  statics_dev = 0;
+  statics_ring = nullptr;
+}

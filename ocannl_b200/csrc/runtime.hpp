@@ -1,0 +1,82 @@
+// Run-time objects behind the C ABI: devices with their pool tables and stream, events,
+// compiled code and linked routines.
+#pragma once
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/b200.h"
+#include "compile.hpp"
+#include "driver.hpp"
+
+struct Pool {
+  CUdeviceptr ptr = 0;
+  size_t bytes = 0;
+};
+
+// One GPU: primary context, one non-blocking stream, the (pool id -> slab) table of
+// `Slab_alloc` (arrayjit/lib/backend_intf.ml:22-37).
+struct b200_dev {
+  int ordinal = 0;
+  CUdevice dev = 0;
+  CUcontext ctx = nullptr;
+  CUstream stream = nullptr;
+  std::string name;
+  int sm_count = 0, cc_major = 0, cc_minor = 0;
+  std::mutex mu;
+  std::map<int, Pool> pools;
+  size_t used = 0;
+  volatile unsigned int* status_host = nullptr;  // written by kernels whose bounded waits expire
+  CUdeviceptr status_dev = 0;
+  long long n_launches = 0, n_graph_launches = 0, n_h2d = 0, n_d2h = 0, n_d2d = 0, n_events = 0;
+
+  void make_current() { b200::cu_check(b200::cu().cuCtxSetCurrent_(ctx), "cuCtxSetCurrent"); }
+  CUdeviceptr address(int pool_id, size_t offset, size_t bytes);
+  void check_status();
+};
+
+struct b200_event {
+  b200_dev* dev = nullptr;
+  CUevent ev = nullptr;
+};
+
+struct b200_code {
+  b200::Code code;
+  const std::string* cubin = nullptr;              // generic kernels of the routine
+  std::vector<const std::string*> gemm_cubins;     // per stage (null for non-contraction stages)
+};
+
+struct GemmLaunch;  // gemm_launch.cpp
+
+struct b200_routine {
+  b200_dev* dev = nullptr;
+  b200_code* code = nullptr;
+  CUmodule module = nullptr;
+  std::vector<CUmodule> gemm_modules;
+  std::vector<CUfunction> fns;                     // per stage
+  std::vector<std::vector<CUdeviceptr>> arg_values;  // per stage, one per KArg
+  std::vector<GemmLaunch*> gemm;                   // per stage
+  std::map<int, CUdeviceptr> node_ptr;
+  CUdeviceptr scratch = 0;                         // routine-local nodes
+  size_t scratch_bytes = 0;
+  std::vector<std::pair<size_t, size_t>> scratch_zero;  // (offset, bytes) cleared every run
+  CUdeviceptr statics_dev = 0;
+  unsigned int* statics_ring = nullptr;            // page-locked staging
+  size_t ring_pos = 0;
+  std::vector<long long> last_statics;
+  bool statics_valid = false;
+  bool want_graph = false;
+  CUgraphExec graph = nullptr;
+
+  void link(b200_dev* d, b200_code* c, const b200_binding* b, int n);
+  void launch(const int64_t* static_idx, int n_static);
+  void enqueue_stages();
+  void set_graph(bool on);
+  void destroy();
+};
+
+// Contraction stages (gemm_launch.cpp)
+GemmLaunch* gemm_prepare(b200_routine* r, int stage_index);
+void gemm_enqueue(b200_routine* r, int stage_index);
+void gemm_release(GemmLaunch* g);

@@ -1,0 +1,319 @@
+"""The benchmark configurations as lowered routines plus their seeded synthetic inputs.
+
+No OCaml frontend runs here, so each routine is assembled by hand in the forms the
+reference's lowering produces (`Assignments.to_low_level`, arrayjit/lib/assignments.ml:311-488,
+followed by inlining and FMA formation, arrayjit/lib/low_level.ml:750-1150,1631-1634):
+
+  * a contraction read once by a pointwise consumer is a virtual accumulator inside the
+    consumer's assignment (`v := 0; for k { v := fma(a, b, v) }`);
+  * anything read more than once per position, every parameter gradient and every routine
+    output is a materialised node updated in place;
+  * loop order is the LHS axes (batch, output, input) followed by the contracted axes, and
+    back-propagation keeps the forward loop order.
+
+Models follow lib/nn_blocks.ml (`mlp` :119-126 — hidden layers `relu(w*x + b)`, linear output
+without bias; `softmax` :137-143) and the training programs test/training/moons_demo.ml:42-59
+and test/training/mlp_names.ml:153-168.  Inputs are seeded numpy (PCG64) draws with the
+shapes and value ranges of the reference's datasets, which are not available offline.
+"""
+from __future__ import annotations
+
+import math
+from typing import Callable, Dict, List, Sequence, Tuple
+
+import numpy as np
+
+from .low_level import (Comment, Const, EmbedIndex, For, Get, GetDynamic, GetLocal, LocalScope, Routine, Scalar, Seq,
+                        Set, SetLocal, Tnode, Unop, ZeroOut, binop, fma, loops, un, where)
+
+NEG_INF = float("-inf")
+
+
+# ------------------------------------------------------------------ bf16 helpers (host side)
+def f32_to_bf16_bits(a: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even on the bit pattern (arrayjit/lib/builtins.c:620-627)."""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    u = u + 0x7FFF + ((u >> 16) & 1)
+    return ((u >> 16) & 0xFFFF).astype(np.uint16)
+
+
+def bf16_bits_to_f32(h: np.ndarray) -> np.ndarray:
+    return (np.ascontiguousarray(h, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def store(prec: str, a: np.ndarray) -> np.ndarray:
+    """Host array in the storage type of `prec`."""
+    if prec == "bfloat16":
+        return f32_to_bf16_bits(a)
+    if prec == "half":
+        return np.asarray(a, np.float16)
+    return np.asarray(a, {"single": np.float32, "double": np.float64}[prec])
+
+
+def load(prec: str, a: np.ndarray) -> np.ndarray:
+    """Host array of storage type `prec` as float32/float64 values."""
+    if prec == "bfloat16":
+        return bf16_bits_to_f32(a)
+    if prec == "half":
+        return np.asarray(a, np.float32)
+    return a
+
+
+# ------------------------------------------------------------------ lowering helpers
+def reduce_scope(r: Routine, name: str, prec: str, red: Sequence[Tuple[str, int]], term: Callable[[], Scalar],
+                 op: str = "fma", orig=()) -> LocalScope:
+    """`v { v := neutral; for k.. { v := op(v, term) } }` — the inlined form of a virtual
+    accumulation (golden: test/einsum/inline_permuted_view-c_fwd.ll.expected)."""
+    vt = r.tn(name, prec, [1], mode="virtual")
+    sid = r.scope(vt)
+    if op == "fma":
+        a, b = term()
+        step = SetLocal(sid, fma(a, b, GetLocal(sid)))
+        init = 0.0
+    elif op == "add":
+        step = SetLocal(sid, binop("add", GetLocal(sid), term()))
+        init = 0.0
+    elif op == "max":
+        step = SetLocal(sid, binop("max", GetLocal(sid), term()))
+        init = NEG_INF
+    else:
+        raise ValueError(op)
+    body = Seq([SetLocal(sid, Const(init, prec)), loops(red, step)])
+    return LocalScope(sid, body, tuple(orig))
+
+
+def gelu_tanh(z: Scalar) -> Scalar:
+    """0.5*z*(1 + tanh(0.7978845608*(z + 0.044715*z^3))) composed from the reference's
+    primitives (`*.`, `+`, `**.`, `tanh`); GELU itself is not a reference op."""
+    z3 = binop("pow", z, 3.0)
+    inner = 0.7978845608 * (z + 0.044715 * z3)
+    return (0.5 * z) * (1.0 + un("tanh", inner))
+
+
+# ------------------------------------------------------------------ config 1: half-moons MLP, train step
+def moons_inputs(n_points=1024, batch=20, seed=1):
+    """Two interleaved unit half-circles with N(0, 0.1) noise per coordinate; labels +1 / -1.
+    The upper one is (cos t, sin t); the lower one is the mirrored half-circle moved to
+    (1 - cos t, 0.5 - sin t), i.e. centred one unit to the right and half a unit below the
+    first one's top.  Angles are uniform on [0, pi]; points are shuffled, then viewed as
+    [n_batches, batch, 2]."""
+    rng = np.random.default_rng(seed)
+    half = n_points // 2
+    t = rng.uniform(0.0, math.pi, n_points)
+    x = np.empty((n_points, 2), np.float32)
+    y = np.empty((n_points, 1), np.float32)
+    x[:half, 0] = np.cos(t[:half]); x[:half, 1] = np.sin(t[:half]); y[:half] = 1.0
+    x[half:, 0] = 1.0 - np.cos(t[half:]); x[half:, 1] = 0.5 - np.sin(t[half:]); y[half:] = -1.0
+    x += rng.normal(0.0, 0.1, x.shape).astype(np.float32)
+    perm = rng.permutation(n_points)
+    x, y = x[perm], y[perm]
+    nb = n_points // batch
+    return (np.ascontiguousarray(x[:nb * batch].reshape(nb, batch, 2)),
+            np.ascontiguousarray(y[:nb * batch].reshape(nb, batch, 1)))
+
+
+def moons_params(seed=2, hid=16):
+    rng = np.random.default_rng(seed)
+    u = lambda *s: rng.uniform(-1.0, 1.0, s).astype(np.float32)
+    return {"w1": u(hid, 2), "b1": u(hid), "w2": u(hid, hid), "b2": u(hid), "w3": u(1, hid)}
+
+
+def moons_train_step(n_batches=51, batch=20, hid=16, steps=4080, weight_decay=1e-4) -> Routine:
+    """One routine = forward + zero grads + backprop + SGD (`Asgns.sequence [update; sgd]`,
+    test/training/moons_demo.ml:63-72; lib/train.ml:61-90) of the 2->16->16->1 ReLU MLP with
+    the hinge loss relu(1 - y*mlp(x)) averaged over the batch."""
+    r = Routine("moons_sgd_step")
+    i_batch = r.static_sym(n_batches)
+    i_step = r.static_sym(None)
+    B, H = batch, hid
+    flat = r.tn("moons_flat", "single", [n_batches, B, 2], read_only=True)
+    cls = r.tn("moons_classes", "single", [n_batches, B, 1], read_only=True)
+    w1, b1 = r.tn("w1", "single", [H, 2]), r.tn("b1", "single", [H])
+    w2, b2 = r.tn("w2", "single", [H, H]), r.tn("b2", "single", [H])
+    w3 = r.tn("w3", "single", [1, H])
+    h1, h2 = r.tn("h1", "single", [B, H]), r.tn("h2", "single", [B, H])
+    margin = r.tn("margin_loss", "single", [B, 1])
+    loss = r.tn("scalar_loss", "single", [1])
+    lr = r.tn("learning_rate", "single", [1])
+    grads = {p.ident: r.tn(p.ident + "_grad", "single", p.dims) for p in (w1, b1, w2, b2, w3)}
+    loc = lambda n, d: r.tn(n, "single", d, mode="local", zero_init=True)
+    g_margin, g_f = loc("margin_loss_grad", [B, 1]), loc("mlp_grad", [B, 1])
+    g_h2, g_z2, g_h1, g_z1 = loc("h2_grad", [B, H]), loc("z2_grad", [B, H]), loc("h1_grad", [B, H]), loc("z1_grad", [B, H])
+    g_loss = loc("scalar_loss_grad", [1])
+    body: List = [Comment("scalar_loss forward and gradient update")]
+    # ---- forward
+    b, o, i = r.syms(3)
+    body.append(loops([(b, B), (o, H)], Set(h1, (b, o), un("relu", b1[o] + reduce_scope(
+        r, "n_w1x", "single", [(i, 2)], lambda: (w1[o, i], flat[i_batch, b, i]), orig=(b, o))))))
+    b, o, i = r.syms(3)
+    body.append(loops([(b, B), (o, H)], Set(h2, (b, o), un("relu", b2[o] + reduce_scope(
+        r, "n_w2h", "single", [(i, H)], lambda: (w2[o, i], h1[b, i]), orig=(b, o))))))
+    b, i = r.syms(2)
+    body.append(loops([(b, B)], Set(margin, (b, 0), un("relu", 1.0 - cls[i_batch, b, 0] * reduce_scope(
+        r, "mlp_out", "single", [(i, H)], lambda: (w3[0, i], h2[b, i]), orig=(b, 0))))))
+    b = r.sym()
+    body.append(Set(loss, (0,), reduce_scope(r, "n_sum", "single", [(b, B)], lambda: margin[b, 0], op="add") / float(B)))
+    # ---- zero grads and backprop
+    body.append(Comment("zero grads and backprop"))
+    for g in list(grads.values()) + [g_margin, g_f, g_h2, g_z2, g_h1, g_z1, g_loss]:
+        body.append(ZeroOut(g))
+    body.append(Set(g_loss, (0,), Const(1.0)))
+    b = r.sym()
+    body.append(loops([(b, B)], Set(g_margin, (b, 0), g_margin[b, 0] + g_loss[0] / float(B))))
+    b = r.sym()
+    body.append(loops([(b, B)], Set(g_f, (b, 0), g_f[b, 0] - cls[i_batch, b, 0] * binop(
+        "relu_gate", margin[b, 0], g_margin[b, 0]))))
+    b, i = r.syms(2)
+    body.append(loops([(b, B), (i, H)], Set(grads["w3"], (0, i), fma(g_f[b, 0], h2[b, i], grads["w3"][0, i]))))
+    b, i = r.syms(2)
+    body.append(loops([(b, B), (i, H)], Set(g_h2, (b, i), fma(w3[0, i], g_f[b, 0], g_h2[b, i]))))
+
+    def layer_backward(g_h, h, g_z, w, gw, gb, x_get, g_x, in_dim):
+        bb, oo = r.syms(2)
+        body.append(loops([(bb, B), (oo, H)], Set(g_z, (bb, oo), g_z[bb, oo] + binop("relu_gate", h[bb, oo], g_h[bb, oo]))))
+        bb, oo = r.syms(2)
+        body.append(loops([(bb, B), (oo, H)], Set(gb, (oo,), gb[oo] + g_z[bb, oo])))
+        bb, oo, ii = r.syms(3)
+        body.append(loops([(bb, B), (oo, H), (ii, in_dim)],
+                          Set(gw, (oo, ii), fma(g_z[bb, oo], x_get(bb, ii), gw[oo, ii]))))
+        if g_x is not None:
+            bb, oo, ii = r.syms(3)
+            body.append(loops([(bb, B), (oo, H), (ii, in_dim)],
+                              Set(g_x, (bb, ii), fma(w[oo, ii], g_z[bb, oo], g_x[bb, ii]))))
+
+    layer_backward(g_h2, h2, g_z2, w2, grads["w2"], grads["b2"], lambda bb, ii: h1[bb, ii], g_h1, H)
+    layer_backward(g_h1, h1, g_z1, w1, grads["w1"], grads["b1"], lambda bb, ii: flat[i_batch, bb, ii], None, 2)
+    # ---- sgd_update with weight decay; the learning rate decays linearly with step_n
+    body.append(Comment("sgd_update"))
+    body.append(Set(lr, (0,), (0.1 * ((2.0 * steps) - Scalar_from_index(i_step))) / float(steps)))
+    for p in (w1, b1, w2, b2, w3):
+        syms = r.syms(len(p.dims))
+        idx = tuple(0 if d == 1 else s for s, d in zip(syms, p.dims))
+        nest = [(s, d) for s, d in zip(syms, p.dims) if d != 1]
+        upd = Get(p, idx) - lr[0] * fma(Const(weight_decay), Get(p, idx), Get(grads[p.ident], idx))
+        body.append(loops(nest, Set(p, idx, upd)))
+    body.append(Comment("end"))
+    r.body = Seq(body)
+    return r
+
+
+def Scalar_from_index(sym: str) -> Scalar:
+    """`!@step_n`: the static index embedded as a number."""
+    return EmbedIndex(sym)
+
+
+def moons_step_numpy(P: Dict[str, np.ndarray], x: np.ndarray, y: np.ndarray, step: int, steps=4080, wd=1e-4):
+    """Float64 numpy statement of the same training step, used as an independent
+    cross-check of the hand-lowered routine (not as the parity oracle)."""
+    P = {k: v.astype(np.float64) for k, v in P.items()}
+    B = x.shape[0]
+    z1 = x @ P["w1"].T + P["b1"]; h1 = np.maximum(z1, 0)
+    z2 = h1 @ P["w2"].T + P["b2"]; h2 = np.maximum(z2, 0)
+    f = h2 @ P["w3"].T
+    m = np.maximum(1 - y * f, 0)
+    loss = m.sum() / B
+    gf = -(y * (m > 0)) / B
+    g = {"w3": gf.T @ h2}
+    gz2 = (gf @ P["w3"]) * (h2 > 0)
+    g["b2"] = gz2.sum(0); g["w2"] = gz2.T @ h1
+    gz1 = (gz2 @ P["w2"]) * (h1 > 0)
+    g["b1"] = gz1.sum(0); g["w1"] = gz1.T @ x
+    lr = 0.1 * (2 * steps - step) / steps
+    new = {k: P[k] - lr * (wd * P[k] + g[k]) for k in P}
+    return new, loss
+
+
+# ------------------------------------------------------------------ config 2: makemore char MLP forward
+def makemore_inputs(batch=4096, block=3, vocab=27, seed=3, target_seed=5):
+    rng = np.random.default_rng(seed)
+    ids = rng.integers(0, vocab, (batch, block)).astype(np.float32)
+    tg = np.random.default_rng(target_seed).integers(0, vocab, batch)
+    onehot = np.zeros((batch, vocab), np.float32)
+    onehot[np.arange(batch), tg] = 1.0
+    return ids, onehot
+
+
+def makemore_params(vocab=27, block=3, embed=10, hid=200, seed=4):
+    rng = np.random.default_rng(seed)
+    n = lambda fan_in, *s: (rng.normal(0.0, 1.0, s) / math.sqrt(fan_in)).astype(np.float32)
+    return {"c": n(vocab, embed, vocab), "w1": n(block * embed, hid, block, embed), "b1": n(block * embed, hid),
+            "w2": n(hid, vocab, hid), "b2": n(hid, vocab)}
+
+
+def makemore_forward(batch=4096, block=3, vocab=27, embed=10, hid=200, wprec="single") -> Routine:
+    """Inference forward of the character MLP of test/training/mlp_names.ml:153-168:
+    embedding gather (the one-hot contraction rewritten by `rewrite_one_hot_reductions`,
+    arrayjit/lib/low_level.ml:2158-2329) -> tanh(sum_{s,e} emb*w1 + b1) -> logits ->
+    max-subtracted log-softmax cross-entropy against one-hot targets, mean over the batch."""
+    r = Routine("makemore_fwd_" + wprec)
+    B = batch
+    ids = r.tn("input_batch", "single", [B, block], read_only=True)
+    tgt = r.tn("target_batch", "single", [B, vocab], read_only=True)
+    c = r.tn("c", wprec, [embed, vocab], read_only=True)
+    w1 = r.tn("w1", wprec, [hid, block, embed], read_only=True)
+    b1 = r.tn("b1", wprec, [hid], read_only=True)
+    w2 = r.tn("w2", wprec, [vocab, hid], read_only=True)
+    b2 = r.tn("b2", wprec, [vocab], read_only=True)
+    emb = r.tn("embed", wprec, [B, block, embed])
+    hidden = r.tn("hidden", wprec, [B, hid])
+    logits = r.tn("logits", "single", [B, vocab])
+    max_l = r.tn("max_l", "single", [B, 1])
+    shifted = r.tn("shifted", "single", [B, vocab])
+    lse = r.tn("lse", "single", [B, 1])
+    nll = r.tn("nll", "single", [1])
+    batch_loss = r.tn("batch_loss", "single", [1])
+    body: List = [Comment("batch_loss fwd")]
+    # gather: where(-1 < id && id < vocab && id == trunc(id), c[e, (uint32)id], 0), guard in double
+    b, s, e = r.syms(3)
+    idv = lambda: Get(ids, (b, s))
+    D = "double"
+    lower = binop("lt", Const(-1.0, D), _as(idv(), D))
+    upper = binop("lt", _as(idv(), D), Const(float(vocab), D))
+    integral = binop("eq", _as(idv(), D), Unop("trunc", _as(idv(), D), D))
+    guard = _force(binop("and", _force(binop("and", _force(lower, D), _force(upper, D)), D), _force(integral, D)), D)
+    gather = GetDynamic(c, (e, 0), 1, idv())
+    body.append(loops([(b, B), (s, block), (e, embed)], Set(emb, (b, s, e), where(guard, gather, Const(0.0, wprec)))))
+    # hidden = tanh(sum_{s,e} emb*w1 + b1); contraction accumulates in single
+    b, h, s, e = r.syms(4)
+    body.append(loops([(b, B), (h, hid)], Set(hidden, (b, h), un("tanh", reduce_scope(
+        r, "n_hid", "single", [(s, block), (e, embed)], lambda: (emb[b, s, e], w1[h, s, e]), orig=(b, h)) + b1[h]))))
+    b, v, h = r.syms(3)
+    body.append(loops([(b, B), (v, vocab)], Set(logits, (b, v), reduce_scope(
+        r, "n_logit", "single", [(h, hid)], lambda: (w2[v, h], hidden[b, h]), orig=(b, v)) + b2[v])))
+    b, v = r.syms(2)
+    body.append(loops([(b, B)], Set(max_l, (b, 0), reduce_scope(
+        r, "n_max", "single", [(v, vocab)], lambda: logits[b, v], op="max"))))
+    b, v = r.syms(2)
+    body.append(loops([(b, B), (v, vocab)], Set(shifted, (b, v), logits[b, v] - max_l[b, 0])))
+    b, v = r.syms(2)
+    body.append(loops([(b, B)], Set(lse, (b, 0), un("log", reduce_scope(
+        r, "n_sumexp", "single", [(v, vocab)], lambda: un("exp", shifted[b, v]), op="add")))))
+    b, v = r.syms(2)
+    body.append(Set(nll, (0,), un("neg", reduce_scope(
+        r, "n_nll", "single", [(b, B), (v, vocab)], lambda: tgt[b, v] * (shifted[b, v] - lse[b, 0]), op="add"))))
+    body.append(Set(batch_loss, (0,), nll[0] / float(B)))
+    body.append(Comment("end"))
+    r.body = Seq(body)
+    return r
+
+
+def _as(s: Scalar, prec: str) -> Scalar:
+    return s
+
+
+def _force(s: Scalar, prec: str) -> Scalar:
+    """Pins the argument precision recorded for a heterogeneous consumer (the guard of
+    `build_guarded_gather` is typed double throughout, low_level.ml:2193-2215)."""
+    s.prec = prec
+    return s
+
+
+def makemore_forward_numpy(P, ids, onehot):
+    P = {k: v.astype(np.float64) for k, v in P.items()}
+    idx = ids.astype(np.int64)
+    emb = np.transpose(P["c"][:, idx], (1, 2, 0))                 # [B, block, embed]
+    hidden = np.tanh(np.einsum("bse,hse->bh", emb, P["w1"]) + P["b1"])
+    logits = hidden @ P["w2"].T + P["b2"]
+    sh = logits - logits.max(1, keepdims=True)
+    lse = np.log(np.exp(sh).sum(1, keepdims=True))
+    return -(onehot * (sh - lse)).sum() / ids.shape[0], logits

@@ -1,0 +1,158 @@
+"""Pins the CPU oracle to the reference: golden generated C, numeric known answers and the
+reference's own builtins.c compiled into oracle/_ref."""
+import ctypes
+import hashlib
+import json
+import os
+
+import numpy as np
+import pytest
+
+from ocannl_b200 import workloads as W
+from oracle.emit_c import Emitter
+from oracle.run_c import OracleRoutine
+from tests.golden.golden_routines import GOLDEN
+from tests.golden.make_cc_golden_digests import routine_text
+from tests.parity import run_oracle
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF_DIR = os.path.join(os.path.dirname(HERE), "oracle", "_ref")
+
+
+@pytest.mark.parametrize("name", sorted(GOLDEN))
+def test_emitter_reproduces_golden_c(name):
+    """The emitted routine text equals the reference's golden generated C once whitespace
+    is removed (digests made by tests/golden/make_cc_golden_digests.py)."""
+    dig = json.load(open(os.path.join(HERE, "golden", "cc_golden_digests.json")))[name]
+    text = routine_text(Emitter(GOLDEN[name]().to_b200ir()).function())
+    assert len(text) == dig["chars"]
+    assert hashlib.sha256(text.encode()).hexdigest() == dig["sha256"]
+
+
+def test_golden_routines_run():
+    # d = bf16((bf16(a) + bf16(b)) * c), one rounding per operation
+    o = OracleRoutine(GOLDEN["top_down_prec"]().to_b200ir())
+    b = o.buffers()
+    b["a"][0], b["b"][0] = 1.5, 2.25
+    b["c"][:] = W.f32_to_bf16_bits(np.float32([3.0]))
+    o.run(b)
+    assert W.bf16_bits_to_f32(b["d"])[0] == 11.25
+    o = OracleRoutine(GOLDEN["zero_out_local_decl"]().to_b200ir())
+    b = o.buffers()
+    b["out"][:] = 7
+    o.run(b)
+    assert np.array_equal(b["out"], np.zeros(4, np.float32))   # sparse[:, 2] is never written
+
+
+def test_bf16_known_answers():
+    """arrayjit/test/test_numerical_types.expected: 3.14159 -> 0x4049 -> 3.140625; 1e-3 -> 0x3a83."""
+    bits = W.f32_to_bf16_bits(np.float32([3.14159, 1e-3, 1.0, -2.5, 0.0]))
+    assert [hex(int(x)) for x in bits[:2]] == ["0x4049", "0x3a83"]
+    assert W.bf16_bits_to_f32(bits)[0] == 3.140625
+    assert list(W.bf16_bits_to_f32(bits)[2:]) == [1.0, -2.5, 0.0]
+
+
+def _ref_lib():
+    p = os.path.join(REF_DIR, "libref_builtins.so")
+    if not os.path.exists(p):
+        pytest.skip("oracle/_ref not built (needs the reference checkout: make -C oracle)")
+    try:
+        return ctypes.CDLL(p)
+    except OSError as e:      # built with -march=native on another host
+        pytest.skip("oracle/_ref does not load here: %s" % e)
+
+
+class U4(ctypes.Structure):
+    _fields_ = [("v", ctypes.c_uint32 * 4)]
+
+
+def _port_lib(tmp_path_factory=None):
+    import subprocess
+    src = os.path.join(os.path.dirname(HERE), "oracle", "_build", "port_exports.c")
+    os.makedirs(os.path.dirname(src), exist_ok=True)
+    so = src[:-2] + ".so"
+    with open(src, "w") as f:
+        f.write('#include "builtins_port.h"\n'
+                'uint16_t p_s2b(float f){return single_to_bfloat16(f);}\n'
+                'float p_b2s(uint16_t h){return bfloat16_to_single(h);}\n'
+                'uint4x32_t p_light(uint4x32_t k, uint4x32_t c){return arrayjit_threefry4x32_light(k,c);}\n'
+                'uint4x32_t p_crypto(uint4x32_t k, uint4x32_t c){return arrayjit_threefry4x32_crypto(k,c);}\n'
+                'float p_uni(uint32_t x){return uint32_to_single_uniform(x);}\n'
+                'uint4x32_t p_widen(uint32_t x){return uint32_to_uint4x32(x);}\n')
+    subprocess.run(["gcc", "-O2", "-shared", "-fPIC", "-I", os.path.dirname(os.path.dirname(src)), src, "-o", so, "-lm"],
+                   check=True)
+    return ctypes.CDLL(so)
+
+
+def test_port_matches_reference_builtins():
+    """The restated helpers agree bit for bit with the reference's builtins.c."""
+    ref, port = _ref_lib(), _port_lib()
+    ref.single_to_bfloat16.restype = ctypes.c_uint16
+    ref.single_to_bfloat16.argtypes = [ctypes.c_float]
+    port.p_s2b.restype = ctypes.c_uint16
+    port.p_s2b.argtypes = [ctypes.c_float]
+    ref.bfloat16_to_single.restype = ctypes.c_float
+    ref.bfloat16_to_single.argtypes = [ctypes.c_uint16]
+    port.p_b2s.restype = ctypes.c_float
+    port.p_b2s.argtypes = [ctypes.c_uint16]
+    rng = np.random.default_rng(0)
+    vals = np.concatenate([rng.normal(0, 1, 2000), rng.normal(0, 1e-30, 200), rng.normal(0, 1e30, 200),
+                           [0.0, -0.0, 1.0, 65504.0, 1e-45, 3.14159, 0.001, np.inf, -np.inf]]).astype(np.float32)
+    for v in vals:
+        assert ref.single_to_bfloat16(float(v)) == port.p_s2b(float(v))
+    assert np.array_equal(W.f32_to_bf16_bits(vals), np.array([port.p_s2b(float(v)) for v in vals], np.uint16))
+    for h in rng.integers(0, 0x7F80, 500):       # finite positive patterns
+        assert ref.bfloat16_to_single(int(h)) == port.p_b2s(int(h))
+    for fn_ref, fn_port in (("arrayjit_threefry4x32_light", "p_light"), ("arrayjit_threefry4x32_crypto", "p_crypto")):
+        fr, fp = getattr(ref, fn_ref), getattr(port, fn_port)
+        fr.restype = fp.restype = U4
+        fr.argtypes = fp.argtypes = [U4, U4]
+        for _ in range(200):
+            k = U4((ctypes.c_uint32 * 4)(*[int(x) for x in rng.integers(0, 2**32, 4)]))
+            c = U4((ctypes.c_uint32 * 4)(*[int(x) for x in rng.integers(0, 2**32, 4)]))
+            assert list(fr(k, c).v) == list(fp(k, c).v)
+    ref.uint32_to_single_uniform.restype = port.p_uni.restype = ctypes.c_float
+    ref.uint32_to_single_uniform.argtypes = port.p_uni.argtypes = [ctypes.c_uint32]
+    ref.uint32_to_uint4x32.restype = port.p_widen.restype = U4
+    ref.uint32_to_uint4x32.argtypes = port.p_widen.argtypes = [ctypes.c_uint32]
+    for x in [0, 1, 255, 256, 2**31, 2**32 - 1] + [int(v) for v in rng.integers(0, 2**32, 100)]:
+        assert ref.uint32_to_single_uniform(x) == port.p_uni(x)
+        assert list(ref.uint32_to_uint4x32(x).v) == list(port.p_widen(x).v)
+
+
+def test_oracle_moons_step_matches_float64_model():
+    """The hand-lowered training routine computes the model it claims to: three steps through
+    the oracle track an independent float64 numpy statement of the same update."""
+    ir = W.moons_train_step()
+    x, y = W.moons_inputs()
+    P = W.moons_params()
+    inputs = dict(P, moons_flat=x, moons_classes=y)
+    statics = [{"i1": 0, "i2": 0}, {"i1": 1, "i2": 1}, {"i1": 50, "i2": 2}]
+    got = run_oracle(ir, inputs, statics)
+    Pn, loss = dict(P), None
+    for st in statics:
+        Pn, loss = W.moons_step_numpy(Pn, x[st["i1"]].astype(np.float64), y[st["i1"]].astype(np.float64), st["i2"])
+    for k in P:
+        np.testing.assert_allclose(got[k], Pn[k], rtol=2e-5, atol=2e-6)
+    np.testing.assert_allclose(got["scalar_loss"][0], loss, rtol=2e-5)
+
+
+@pytest.mark.parametrize("wprec", ["single", "bfloat16"])
+def test_oracle_makemore_forward(wprec):
+    ir = W.makemore_forward(batch=64, wprec=wprec)
+    ids, onehot = W.makemore_inputs(batch=64)
+    P = W.makemore_params()
+    inputs = {k: W.store(wprec, v) for k, v in P.items()}
+    inputs.update(input_batch=ids, target_batch=onehot)
+    got = run_oracle(ir, inputs)
+    Pq = {k: W.load(wprec, W.store(wprec, v)) for k, v in P.items()}
+    loss, logits = W.makemore_forward_numpy(Pq, ids, onehot)
+    tol = 1e-5 if wprec == "single" else 3e-2
+    np.testing.assert_allclose(got["logits"], logits, rtol=tol, atol=tol)
+    np.testing.assert_allclose(got["batch_loss"][0], loss, rtol=tol)
+    # out-of-range and fractional ids gather 0 (test/operations/test_one_hot_embedding_lookup.ml)
+    ids2 = ids.copy()
+    ids2[0, 0], ids2[1, 1], ids2[2, 2] = -1.0, 27.0, 1.5
+    got2 = run_oracle(ir, dict(inputs, input_batch=ids2))
+    emb = W.load(wprec, got2["embed"])
+    assert not emb[0, 0].any() and not emb[1, 1].any() and not emb[2, 2].any() and emb[3].any()
