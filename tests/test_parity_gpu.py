@@ -1,0 +1,79 @@
+"""Device parity: every routine runs through the C ABI on the GPU and on the CPU oracle
+(the restated cc backend) from identical seeded inputs.
+
+Tolerances (the ones the north star states): fp32 pointwise rel 1e-5; bf16 contractions
+rel 2e-2 with fp32 accumulation; index work (the gather) bit-exact."""
+import numpy as np
+import pytest
+
+from ocannl_b200 import workloads as W
+from tests.golden.golden_routines import GOLDEN
+from tests.parity import compare, run_device, run_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def test_golden_routines_on_device(device):
+    for name, mk in GOLDEN.items():
+        ir = mk()
+        rng = np.random.default_rng(1)
+        inputs = {}
+        for t in ir.params():
+            if t.prec == "half":
+                inputs[t.ident] = rng.normal(0, 1, t.dims).astype(np.float16)
+            elif t.prec == "bfloat16":
+                inputs[t.ident] = W.f32_to_bf16_bits(rng.normal(0, 1, t.dims).astype(np.float32))
+            elif t.prec == "byte":
+                inputs[t.ident] = np.ones(t.dims, np.uint8)
+            else:
+                inputs[t.ident] = rng.normal(0, 1, t.dims).astype(np.float32)
+        want = run_oracle(ir, inputs)
+        got, _ = run_device(device, ir, inputs)
+        for t in ir.params():
+            assert np.array_equal(got[t.ident].view(np.uint8), want[t.ident].view(np.uint8)), (name, t.ident)
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_moons_training_steps(device, graph):
+    """Config 1: forward + backprop + SGD, five steps over different batches; parameters,
+    gradients, activations and the loss agree with the cc restatement to rel 1e-5."""
+    ir = W.moons_train_step()
+    x, y = W.moons_inputs()
+    inputs = dict(W.moons_params(), moons_flat=x, moons_classes=y)
+    statics = [{"i1": b, "i2": s} for s, b in enumerate([0, 1, 7, 50, 3])]
+    want = run_oracle(ir, inputs, statics)
+    got, info = run_device(device, ir, inputs, statics, graph=graph)
+    compare(ir, got, want, rtol=1e-5, atol=1e-6)
+    assert abs(float(got["scalar_loss"][0])) > 0
+
+
+def test_moons_static_index_errors(device):
+    from ocannl_b200 import backend as bk
+    ir = W.moons_train_step()
+    code = bk.Code(ir)
+    rt = bk.Context(device).link(code)
+    with pytest.raises(bk.UserError):
+        rt.run(i1=51, i2=0)          # range is 0..50
+    with pytest.raises(bk.UserError):
+        rt.run(i1=-1, i2=0)
+    rt.run(i1=0, i2=0)
+    device.await_()
+    rt.free()
+
+
+@pytest.mark.parametrize("wprec", ["single", "bfloat16"])
+@pytest.mark.parametrize("options", [None, "gemm=0 coop=0"])
+def test_makemore_forward(device, wprec, options):
+    """Config 2 at full size (batch 4096).  The gathered embedding is index work: bit-exact,
+    including ids that are negative, too large or fractional (they gather 0)."""
+    ir = W.makemore_forward(wprec=wprec)
+    ids, onehot = W.makemore_inputs()
+    ids[0, 0], ids[1, 1], ids[2, 2] = -1.0, 27.0, 1.5
+    inputs = {k: W.store(wprec, v) for k, v in W.makemore_params().items()}
+    inputs.update(input_batch=ids, target_batch=onehot)
+    want = run_oracle(ir, inputs)
+    got, info = run_device(device, ir, inputs, options=options)
+    if wprec == "single":
+        compare(ir, got, want, rtol=1e-5, atol=1e-5, exact=["embed"])
+    else:
+        compare(ir, got, want, rtol=2e-2, atol=2e-2, exact=["embed"])
