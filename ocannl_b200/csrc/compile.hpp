@@ -53,6 +53,9 @@ struct Stage {
   int coop = 0;                  // >0: lanes cooperating on one output element (row reductions)
   GemmPlan gemm;
   std::string gemm_source;       // full translation unit of this stage's contraction kernel
+  std::string epi_params, epi_args;  // epilogue plumbing: extra kernel parameters / call arguments
+  int tile_m = 0, tile_n = 0, tile_k = 0;
+  int smem_bytes = 0;            // dynamic shared memory of the contraction kernel
   std::string note;              // human-readable classification, for debug info
 };
 

@@ -1,6 +1,133 @@
-// placeholder until the contraction kernel lands
+// Launch side of the contraction kernel: TMA tensor maps for the two operands (built once at
+// link, when the nodes' addresses are known) and the persistent launch.
+#include <cstring>
+
 #include "runtime.hpp"
-struct GemmLaunch {};
-GemmLaunch* gemm_prepare(b200_routine*, int) { return nullptr; }
-void gemm_enqueue(b200_routine*, int) {}
-void gemm_release(GemmLaunch*) {}
+
+using namespace b200;
+
+// must match b200_gemm_shape in kernels/gemm_sm100.cuh
+struct GemmShape {
+  unsigned int M, N, K, B0, B1, a_b0, a_b1, b_b0, b_b1, tiles_m, tiles_n;
+};
+
+struct GemmLaunch {
+  CUtensorMap map_a, map_b;
+  GemmShape shape;
+  unsigned int grid = 1;
+  CUdeviceptr status = 0;
+};
+
+static void encode_operand(CUtensorMap* map, CUdeviceptr base, Prec prec, bool kmajor, const GemmDim& mn, int64_t mn_stride,
+                           const GemmDim& k, int64_t k_stride, const std::vector<GemmDim>& batch,
+                           const std::vector<int64_t>& batch_stride, int tile_mn, int tile_k) {
+  const int eb = prec_bytes(prec);
+  CUtensorMapDataType dt = prec == Prec::Bfloat16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                           : prec == Prec::Half   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                  : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  const int row_elems = 128 / eb;
+  cuuint64_t dims[4];
+  cuuint64_t strides[3];
+  cuuint32_t box[4] = {(cuuint32_t)row_elems, 1, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  if (kmajor) {
+    dims[0] = (cuuint64_t)k.extent;
+    dims[1] = (cuuint64_t)mn.extent;
+    strides[0] = (cuuint64_t)mn_stride * eb;
+    box[1] = (cuuint32_t)tile_mn;
+  } else {
+    dims[0] = (cuuint64_t)mn.extent;
+    dims[1] = (cuuint64_t)k.extent;
+    strides[0] = (cuuint64_t)k_stride * eb;
+    box[1] = (cuuint32_t)tile_k;
+  }
+  // batch axes: index 2 is the inner one, index 3 the outer one; an operand that does not
+  // vary along an axis sees extent 1 there
+  const cuuint64_t filler = ((dims[0] * eb + 15) / 16) * 16;
+  for (int i = 0; i < 2; ++i) {
+    dims[2 + i] = 1;
+    strides[1 + i] = filler;
+  }
+  const int nb = (int)batch.size();
+  for (int i = 0; i < nb; ++i) {
+    // batch[nb-1] is the innermost
+    const int slot = 2 + (nb - 1 - i);
+    if (batch_stride[i] != 0) {
+      dims[slot] = (cuuint64_t)batch[i].extent;
+      strides[slot - 1] = (cuuint64_t)batch_stride[i] * eb;
+    }
+  }
+  CUresult r = cu().cuTensorMapEncodeTiled_(map, dt, 4, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    throw Error(B200_E_UNSUPPORTED, "the operand layout of a contraction cannot be described to the TMA unit (CUresult " +
+                                        std::to_string((int)r) + "); compile the routine with gemm=0");
+}
+
+GemmLaunch* gemm_prepare(b200_routine* r, int si) {
+  const Stage& st = r->code->code.stages[si];
+  const GemmPlan& g = st.gemm;
+  const Program& P = r->code->code.prog;
+  auto ptr = [&](int tn) {
+    auto it = r->node_ptr.find(tn);
+    if (it == r->node_ptr.end()) throw Error(B200_E_USER, "link: node '" + P.tn(tn).ident + "' has no buffer binding");
+    return it->second;
+  };
+  const int eb = prec_bytes(g.in_prec);
+  CUdeviceptr a = ptr(g.a_tn) + (CUdeviceptr)(g.a_off * eb), b = ptr(g.b_tn) + (CUdeviceptr)(g.b_off * eb);
+  if ((a & 15) || (b & 15))
+    throw Error(B200_E_UNSUPPORTED, "contraction operands must be 16-byte aligned for TMA; compile the routine with gemm=0");
+  auto* L = new GemmLaunch();
+  try {
+    std::vector<int64_t> sa, sb;
+    for (auto& d : g.batch) { sa.push_back(d.sa); sb.push_back(d.sb); }
+    encode_operand(&L->map_a, a, g.in_prec, g.a_kmajor, g.m, g.m.sa, g.k, g.k.sa, g.batch, sa, st.tile_m, st.tile_k);
+    encode_operand(&L->map_b, b, g.in_prec, g.b_kmajor, g.n, g.n.sb, g.k, g.k.sb, g.batch, sb, st.tile_n, st.tile_k);
+  } catch (...) {
+    delete L;
+    throw;
+  }
+  GemmShape& s = L->shape;
+  memset(&s, 0, sizeof s);
+  s.M = (unsigned)g.m.extent;
+  s.N = (unsigned)g.n.extent;
+  s.K = (unsigned)g.k.extent;
+  s.B0 = s.B1 = 1;
+  s.a_b0 = s.a_b1 = s.b_b0 = s.b_b1 = 0;
+  const int nb = (int)g.batch.size();
+  if (nb == 2) {
+    s.B0 = (unsigned)g.batch[0].extent;
+    s.B1 = (unsigned)g.batch[1].extent;
+    s.a_b0 = g.batch[0].sa != 0; s.b_b0 = g.batch[0].sb != 0;
+    s.a_b1 = g.batch[1].sa != 0; s.b_b1 = g.batch[1].sb != 0;
+  } else if (nb == 1) {
+    s.B1 = (unsigned)g.batch[0].extent;
+    s.a_b1 = g.batch[0].sa != 0; s.b_b1 = g.batch[0].sb != 0;
+  }
+  s.tiles_m = (s.M + st.tile_m - 1) / st.tile_m;
+  s.tiles_n = (s.N + st.tile_n - 1) / st.tile_n;
+  unsigned long long tiles = (unsigned long long)s.tiles_m * s.tiles_n * s.B0 * s.B1;
+  L->grid = (unsigned)(tiles < (unsigned long long)r->dev->sm_count ? tiles : (unsigned long long)r->dev->sm_count);
+  L->status = r->dev->status_dev;
+  cu_check(cu().cuFuncSetAttribute_(r->fns[si], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, st.smem_bytes),
+           "cuFuncSetAttribute(max dynamic shared memory)");
+  return L;
+}
+
+void gemm_enqueue(b200_routine* r, int si) {
+  const Stage& st = r->code->code.stages[si];
+  GemmLaunch* L = r->gemm[si];
+  std::vector<void*> args;
+  args.push_back(&L->map_a);
+  args.push_back(&L->map_b);
+  args.push_back(&L->shape);
+  args.push_back(&L->status);
+  std::vector<CUdeviceptr>& vals = r->arg_values[si];
+  for (size_t a = 0; a < vals.size(); ++a) args.push_back(&vals[a]);
+  cu_check(cu().cuLaunchKernel_(r->fns[si], L->grid, 1, 1, (unsigned)st.block, 1, 1, (unsigned)st.smem_bytes, r->dev->stream,
+                                args.data(), nullptr),
+           "cuLaunchKernel(contraction)");
+}
+
+void gemm_release(GemmLaunch* g) { delete g; }

@@ -1,6 +1,435 @@
-// placeholder until the contraction matcher lands
+// Recognition of dense contractions in a loop nest and generation of the translation unit
+// that instantiates the tcgen05 kernel (kernels/gemm_sm100.cuh) with the routine's epilogue.
+//
+// Two shapes are recognised (they are what `Assignments.to_low_level` + inlining produce for
+// `+*`/matmul, arrayjit/lib/assignments.ml:311-488, arrayjit/lib/low_level.ml:750-1150,1631-1634):
+//   A. virtual accumulator inside the consumer:
+//        for f.. { t[f..] := E( v { v := 0; for k.. { v := fma(x[..], y[..], v) } } ) }
+//   B. materialised accumulate:
+//        [zero_out t;] for f.., k.. { t[f..] := fma(x[..], y[..], t[f..]) }
+// A loop symbol is a batch axis when both operands carry it, an M (N) axis when only the
+// first (second) operand carries it, and a K axis when it is reduced.  Anything else —
+// affine or static indices in the operands, mixed operand precisions, an accumulator that
+// is not fp32 (the cc backend would round every step, arrayjit/lib/cc_backend.ml:169-186),
+// strides the tensor maps cannot express — is left to the generic loop-nest kernels.
+#include <algorithm>
+#include <functional>
+#include <set>
+#include <sstream>
+
 #include "compile.hpp"
+#include "emit.hpp"
+
 namespace b200 {
-bool match_gemm(const Program&, const std::vector<LoopDim>&, const Stmt&, bool, const CompileOptions&, Stage*) { return false; }
-std::string gemm_translation_unit(const Program&, Stage&, const std::string&, const CompileOptions&) { return ""; }
+
+namespace {
+
+const int kAccScope = -777;  // pseudo scope id standing for the TMEM accumulator value
+
+struct SymInfo {
+  std::string sym;
+  int64_t extent = 1;
+  int64_t sa = 0, sb = 0, sd = 0;
+  bool in_a = false, in_b = false, in_d = false;
+};
+
+// element stride of `sym` in a row-major tensor indexed by idcs; false on unsupported index forms
+bool strides_of(const Tnode& t, const Indices& idcs, std::map<std::string, int64_t>& stride, int64_t& const_off) {
+  if (idcs.size() != t.dims.size()) return false;
+  int64_t s = 1;
+  const_off = 0;
+  for (size_t a = idcs.size(); a-- > 0;) {
+    const Index& ix = idcs[a];
+    if (ix.kind == Index::Iter) stride[ix.sym] += s;
+    else if (ix.kind == Index::Fixed) const_off += ix.fixed * s;
+    else return false;
+    s *= t.dims[a];
+  }
+  return true;
+}
+
+bool is_get_of(const Scalar& e, int tn, const Indices& idcs) {
+  if (e.kind != Scalar::Get || e.tn != tn || e.idcs.size() != idcs.size()) return false;
+  for (size_t i = 0; i < idcs.size(); ++i) {
+    const Index &a = e.idcs[i], &b = idcs[i];
+    if (a.kind != b.kind || a.fixed != b.fixed || a.sym != b.sym || a.terms != b.terms) return false;
+  }
+  return true;
+}
+
+// the multiply-accumulate step: returns the two factors
+bool mac_step(const Scalar& v, const std::function<bool(const Scalar&)>& is_acc, const Scalar** x, const Scalar** y) {
+  if (v.kind == Scalar::Tern && v.op == "fma" && is_acc(*v.args[2].s)) {
+    *x = v.args[0].s.get();
+    *y = v.args[1].s.get();
+    return true;
+  }
+  if (v.kind == Scalar::Bin && v.op == "add") {
+    for (int side = 0; side < 2; ++side) {
+      const Scalar& acc = *v.args[side].s;
+      const Scalar& prod = *v.args[1 - side].s;
+      if (is_acc(acc) && prod.kind == Scalar::Bin && prod.op == "mul") {
+        *x = prod.args[0].s.get();
+        *y = prod.args[1].s.get();
+        return true;
+      }
+    }
+  }
+  return false;
+}
+
+}  // namespace
+
+bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& set, bool zeroed_before,
+                const CompileOptions& opt, Stage* out) {
+  if (set.kind != Stmt::Set) return false;
+  const Tnode& D = P.tn(set.tn);
+  std::set<std::string> statics;
+  for (auto& s : P.statics) statics.insert(s.sym);
+
+  const Scalar *x = nullptr, *y = nullptr;
+  std::vector<LoopDim> red;  // reduction loops, outer to inner
+  std::vector<LoopDim> free_loops;
+  const Scalar* scope = nullptr;
+  bool form_b = false;
+
+  // ---- form B
+  {
+    const Scalar& v = *set.value;
+    auto is_acc = [&](const Scalar& e) { return is_get_of(e, set.tn, set.idcs); };
+    if (mac_step(v, is_acc, &x, &y)) {
+      form_b = true;
+      for (auto& d : nest) {
+        bool in_lhs = false;
+        for (auto& ix : set.idcs)
+          if (ix.uses(d.sym)) in_lhs = true;
+        (in_lhs ? free_loops : red).push_back(d);
+      }
+      if (D.prec != Prec::Single) return false;  // accumulating in a rounded type: not a tensor-core job
+    }
+  }
+  // ---- form A
+  if (!form_b) {
+    int n_scopes = 0;
+    std::function<void(const Scalar&)> find = [&](const Scalar& e) {
+      if (e.kind == Scalar::LocalScope) {
+        ++n_scopes;
+        scope = &e;
+        return;
+      }
+      for (auto& a : e.args) find(*a.s);
+    };
+    find(*set.value);
+    if (n_scopes != 1) return false;
+    if (P.tn(scope->tn).prec != Prec::Single) return false;
+    const Stmt* b = scope->body.get();
+    if (b->kind == Stmt::Seq) {
+      if (b->items.size() != 2 || b->items[0]->kind != Stmt::SetLocal || b->items[0]->scope_id != scope->scope_id ||
+          b->items[0]->value->kind != Scalar::Const || b->items[0]->value->cval != 0.0)
+        return false;
+      b = b->items[1].get();
+    }
+    while (b->kind == Stmt::For) {
+      red.push_back({b->index, b->from, b->to});
+      b = b->body.get();
+    }
+    if (b->kind != Stmt::SetLocal || b->scope_id != scope->scope_id) return false;
+    auto is_acc = [&](const Scalar& e) { return e.kind == Scalar::GetLocal && e.scope_id == scope->scope_id; };
+    if (!mac_step(*b->value, is_acc, &x, &y)) return false;
+    free_loops = nest;
+    // no other use of the accumulator's local inside the expression
+    int uses = 0;
+    std::function<void(const Scalar&)> cnt = [&](const Scalar& e) {
+      if (e.kind == Scalar::GetLocal && e.scope_id == scope->scope_id) ++uses;
+      if (e.kind == Scalar::LocalScope) return;
+      for (auto& a : e.args) cnt(*a.s);
+    };
+    cnt(*set.value);
+    if (uses) return false;
+  }
+  if (red.empty() || free_loops.empty()) return false;
+  for (auto& d : nest)
+    if (d.from != 0) return false;
+  for (auto& d : red)
+    if (d.from != 0) return false;
+  if (x->kind != Scalar::Get || y->kind != Scalar::Get) return false;
+  const Tnode &X = P.tn(x->tn), &Y = P.tn(y->tn);
+  if (X.prec != Y.prec) return false;
+  if (!(X.prec == Prec::Bfloat16 || X.prec == Prec::Half)) return false;
+  if (X.mode == Mode::Virtual || Y.mode == Mode::Virtual) return false;
+
+  // ---- strides
+  std::map<std::string, int64_t> sx, sy, sd;
+  int64_t offx = 0, offy = 0, offd = 0;
+  if (!strides_of(X, x->idcs, sx, offx) || !strides_of(Y, y->idcs, sy, offy) || !strides_of(D, set.idcs, sd, offd))
+    return false;
+  for (auto& m : {sx, sy})
+    for (auto& kv : m)
+      if (statics.count(kv.first)) return false;
+  // every free symbol indexes the output exactly once; reduction symbols never do
+  std::vector<SymInfo> F, R;
+  std::set<std::string> known;
+  for (auto& d : free_loops) {
+    SymInfo s{d.sym, d.extent(), sx.count(d.sym) ? sx[d.sym] : 0, sy.count(d.sym) ? sy[d.sym] : 0,
+              sd.count(d.sym) ? sd[d.sym] : 0};
+    s.in_a = sx.count(d.sym);
+    s.in_b = sy.count(d.sym);
+    s.in_d = sd.count(d.sym);
+    if (!s.in_d) return false;
+    int occurrences = 0;
+    for (auto& ix : set.idcs)
+      if (ix.kind == Index::Iter && ix.sym == d.sym) ++occurrences;
+    if (occurrences != 1) return false;
+    if (!s.in_a && !s.in_b) return false;
+    if (s.extent <= 0) return false;
+    F.push_back(s);
+    known.insert(d.sym);
+  }
+  for (auto& d : red) {
+    SymInfo s{d.sym, d.extent(), sx.count(d.sym) ? sx[d.sym] : 0, sy.count(d.sym) ? sy[d.sym] : 0, 0};
+    s.in_a = sx.count(d.sym);
+    s.in_b = sy.count(d.sym);
+    if (!s.in_a || !s.in_b || sd.count(d.sym)) return false;
+    R.push_back(s);
+    known.insert(d.sym);
+  }
+  for (auto& m : {sx, sy, sd})
+    for (auto& kv : m)
+      if (!known.count(kv.first) && !statics.count(kv.first)) return false;
+  for (auto& kv : sd)
+    if (statics.count(kv.first)) { /* a static slice of the output moves with each launch: fine, the epilogue indexes it */ }
+
+  // ---- which operand sits on the N side: the output's unit-stride symbol should be N
+  bool swap = false;
+  for (auto& s : F)
+    if (s.sd == 1 && s.extent > 1 && s.in_a && !s.in_b) swap = true;
+  if (swap) {
+    std::swap(x, y);
+    for (auto& s : F) { std::swap(s.sa, s.sb); std::swap(s.in_a, s.in_b); }
+    for (auto& s : R) { std::swap(s.sa, s.sb); std::swap(s.in_a, s.in_b); }
+    std::swap(offx, offy);
+  }
+  const Tnode &A = P.tn(x->tn), &B = P.tn(y->tn);
+
+  // ---- group and merge symbols
+  struct Dim {
+    std::vector<std::pair<std::string, int64_t>> syms;  // (symbol, extent), outer to inner
+    int64_t extent = 1, sa = 0, sb = 0, sd = 0;
+  };
+  auto merge = [](std::vector<Dim>& g) {
+    for (size_t i = 0; i + 1 < g.size();) {
+      Dim &o = g[i], &n = g[i + 1];
+      bool ok = o.sa == n.extent * n.sa && o.sb == n.extent * n.sb && o.sd == n.extent * n.sd;
+      if (ok) {
+        Dim m = n;
+        m.extent = o.extent * n.extent;
+        m.syms.insert(m.syms.begin(), o.syms.begin(), o.syms.end());
+        g[i] = m;
+        g.erase(g.begin() + i + 1);
+      } else {
+        ++i;
+      }
+    }
+  };
+  std::vector<Dim> gm, gn, gk, gb;
+  for (auto& s : F) {
+    if (s.extent == 1) continue;  // degenerate loop: contributes nothing to addressing
+    Dim d{{{s.sym, s.extent}}, s.extent, s.sa, s.sb, s.sd};
+    if (s.in_a && s.in_b) gb.push_back(d);
+    else if (s.in_a) gm.push_back(d);
+    else gn.push_back(d);
+  }
+  for (auto& s : R) {
+    if (s.extent == 1) continue;
+    gk.push_back(Dim{{{s.sym, s.extent}}, s.extent, s.sa, s.sb, 0});
+  }
+  merge(gm); merge(gn); merge(gk); merge(gb);
+  // leftover outer M / N dims become batch axes along which one operand is broadcast
+  while (gm.size() > 1) { gb.push_back(gm.front()); gm.erase(gm.begin()); }
+  while (gn.size() > 1) { gb.push_back(gn.front()); gn.erase(gn.begin()); }
+  if (gm.size() != 1 || gn.size() != 1 || gk.size() != 1 || gb.size() > 2) return false;
+  const Dim &dm = gm[0], &dn = gn[0], &dk = gk[0];
+
+  GemmPlan g;
+  g.a_tn = x->tn;
+  g.b_tn = y->tn;
+  g.d_tn = set.tn;
+  g.m = {dm.extent, dm.sa, 0, dm.sd};
+  g.n = {dn.extent, 0, dn.sb, dn.sd};
+  g.k = {dk.extent, dk.sa, dk.sb, 0};
+  for (auto& d : gb) g.batch.push_back({d.extent, d.sa, d.sb, d.sd});
+  g.a_off = offx;
+  g.b_off = offy;
+  g.in_prec = A.prec;
+  g.accumulate = form_b && !zeroed_before;
+  if (g.k.sa == 1) g.a_kmajor = true;
+  else if (g.m.sa == 1) g.a_kmajor = false;
+  else return false;
+  if (g.k.sb == 1) g.b_kmajor = true;
+  else if (g.n.sb == 1) g.b_kmajor = false;
+  else return false;
+
+  // ---- what the tensor maps can express: 16-byte aligned bases and strides, 32-bit extents
+  const int eb = prec_bytes(A.prec);
+  auto ok16 = [&](int64_t elems) { return (elems * eb) % 16 == 0; };
+  if (!ok16(g.a_off) || !ok16(g.b_off)) return false;
+  if (!ok16(g.a_kmajor ? g.m.sa : g.k.sa) || !ok16(g.b_kmajor ? g.n.sb : g.k.sb)) return false;
+  for (auto& b : g.batch)
+    if ((b.sa && !ok16(b.sa)) || (b.sb && !ok16(b.sb))) return false;
+  if (g.m.extent >= (1ll << 31) || g.n.extent >= (1ll << 31) || g.k.extent >= (1ll << 31)) return false;
+  // ---- worth a tensor-core launch?
+  if (g.m.extent < 32 || g.n.extent < 8 || g.k.extent < 16 || g.flops() < 4.0e6) return false;
+  (void)B;
+  (void)opt;
+
+  // ---- epilogue: recover the loop symbols from (batch, m, n) and run the consumer assignment
+  Emitter em(P);
+  em.large_models = opt.large_models;
+  std::ostringstream ep;
+  auto recover = [&](const Dim& d, const std::string& var) {
+    std::string rem = var;
+    for (size_t i = d.syms.size(); i-- > 0;) {
+      const auto& s = d.syms[i];
+      if (i == 0) ep << "    const unsigned int " << s.first << " = " << rem << ";\n";
+      else {
+        ep << "    const unsigned int " << s.first << " = " << rem << " % " << s.second << "u;\n";
+        std::string nr = "b200_q_" + s.first;
+        ep << "    const unsigned int " << nr << " = " << rem << " / " << s.second << "u;\n";
+        rem = nr;
+      }
+    }
+  };
+  // degenerate (extent 1) free loops and unit reductions still name symbols the epilogue may use
+  std::string unit_syms;
+  for (auto& s : F)
+    if (s.extent == 1) unit_syms += "    const unsigned int " + s.sym + " = 0u;\n";
+
+  em.scope_subst[kAccScope] = "b200_acc";
+  std::string body;
+  if (form_b) {
+    const Tnode& t = D;
+    em.used_nodes.insert(set.tn);
+    std::string off = em.offset(set.idcs, t.dims);
+    if (g.accumulate) body = "      " + t.ident + "[" + off + "] = " + t.ident + "[" + off + "] + b200_acc;\n";
+    else body = "      " + t.ident + "[" + off + "] = b200_acc;\n";
+  } else {
+    em.scope_subst[scope->scope_id] = "b200_acc";
+    body = em.stmt(set, 6);
+  }
+
+  std::ostringstream fn;
+  // parameters of the epilogue: the nodes it touches (+ static table)
+  std::string params, args;
+  std::vector<KArg> kargs;
+  for (auto& t : P.tnodes) {
+    if (!em.used_nodes.count(t.id) || t.mode == Mode::Virtual) continue;
+    const bool written = t.id == set.tn;
+    params += std::string(", ") + (written ? "" : "const ") + Emitter::ctype(t.prec) + "* " + (written ? "" : "__restrict__ ") + t.ident;
+    args += ", " + t.ident;
+    kargs.push_back({KArg::Node, t.id});
+  }
+  std::string statics_prologue;
+  {
+    std::string text = body;
+    for (size_t i = 0; i < P.statics.size(); ++i) {
+      const std::string& s = P.statics[i].sym;
+      size_t p = 0;
+      bool found = false;
+      auto isid = [](char c) { return isalnum((unsigned char)c) || c == '_'; };
+      while ((p = text.find(s, p)) != std::string::npos) {
+        bool l = p == 0 || !isid(text[p - 1]);
+        bool r = p + s.size() >= text.size() || !isid(text[p + s.size()]);
+        if (l && r) { found = true; break; }
+        p += s.size();
+      }
+      if (found) statics_prologue += "  const unsigned int " + s + " = b200_statics[" + std::to_string(i) + "];\n";
+    }
+    if (!statics_prologue.empty()) {
+      params += ", const unsigned int* __restrict__ b200_statics";
+      args += ", b200_statics";
+      kargs.push_back({KArg::Statics, -1});
+    }
+  }
+  if (em.uses_merge) return false;
+
+  fn << "__device__ __forceinline__ void b200_epilogue_row(const unsigned int* b200_r, unsigned int b200_b0, unsigned int b200_b1, "
+        "unsigned int b200_m, unsigned int b200_n0, unsigned int b200_N"
+     << params << ") {\n"
+     << statics_prologue;
+  {
+    // batch axes: gb[0] is the outer one
+    std::ostringstream pre;
+    ep.str("");
+    if (gb.size() == 2) { recover(gb[0], "b200_b0"); recover(gb[1], "b200_b1"); }
+    else if (gb.size() == 1) { recover(gb[0], "b200_b1"); }
+    recover(dm, "b200_m");
+    fn << ep.str();
+    ep.str("");
+  }
+  fn << unit_syms;
+  fn << "#pragma unroll\n  for (int b200_j = 0; b200_j < B200_EPI_CHUNK; ++b200_j) {\n"
+     << "    const unsigned int b200_n = b200_n0 + (unsigned int)b200_j;\n"
+     << "    if (b200_n < b200_N) {\n"
+     << "      const float b200_acc = __uint_as_float(b200_r[b200_j]);\n";
+  recover(dn, "b200_n");
+  fn << ep.str() << body << "    }\n  }\n}\n";
+
+  out->kind = Stage::Gemm;
+  out->gemm = g;
+  out->gemm.epilogue = fn.str();
+  out->args = kargs;
+  out->total = 1;
+  out->epi_params = params;
+  out->epi_args = args;
+  return true;
+}
+
+std::string gemm_translation_unit(const Program& P, Stage& st, const std::string& kernel_name, const CompileOptions&) {
+  GemmPlan& g = st.gemm;
+  const int eb = prec_bytes(g.in_prec);
+  const int row_elems = 128 / eb;
+  int bn;
+  if (g.n.extent >= 256) bn = 256;
+  else bn = (int)((g.n.extent + 15) / 16 * 16);
+  if (!g.b_kmajor) bn = (bn + row_elems - 1) / row_elems * row_elems;
+  if (bn > 256) bn = 256;
+  const int bm = 128, bk = row_elems;
+  const int umma_k = 32 / eb;
+  const int stage_bytes = (bm + bn) * bk * eb;
+  int stages = (200 * 1024) / stage_bytes;
+  if (stages > 8) stages = 8;
+  if (stages < 2) stages = 2;
+  int tmem_cols = 32;
+  while (tmem_cols < 2 * bn) tmem_cols *= 2;
+  const int epi_warps = bn >= 128 ? 8 : 4;
+  // instruction descriptor: fp32 accumulate, operand formats, majors, N >> 3, M >> 4
+  unsigned int fmt = g.in_prec == Prec::Bfloat16 ? 1u : (g.in_prec == Prec::Half ? 0u : 2u);
+  unsigned int idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((g.a_kmajor ? 0u : 1u) << 15) | ((g.b_kmajor ? 0u : 1u) << 16) |
+                       ((unsigned int)(bn >> 3) << 17) | ((unsigned int)(bm >> 4) << 24);
+  const std::string &params = st.epi_params, &args = st.epi_args;
+  std::ostringstream o;
+  o << kNumericsSource << "\n";
+  o << "#define B200_GEMM_NAME " << kernel_name << "\n#define B200_BM " << bm << "\n#define B200_BN " << bn
+    << "\n#define B200_BK " << bk << "\n#define B200_UMMA_K " << umma_k << "\n#define B200_ELEM_BYTES " << eb
+    << "\n#define B200_STAGES " << stages << "\n#define B200_EPI_WARPS " << epi_warps << "\n#define B200_A_KMAJOR "
+    << (g.a_kmajor ? 1 : 0) << "\n#define B200_B_KMAJOR " << (g.b_kmajor ? 1 : 0) << "\n#define B200_IDESC " << idesc
+    << "u\n#define B200_TMEM_COLS " << tmem_cols << "\n#define B200_RASTER 8\n";
+  o << "#if " << bn << " >= 32\n#define B200_EPI_CHUNK 32\n#else\n#define B200_EPI_CHUNK 16\n#endif\n";
+  o << g.epilogue << "\n";
+  o << "#define B200_EPI_PARAMS " << params << "\n";
+  o << "#define B200_EPILOGUE_ROW b200_epilogue_row(b200_r, b200_b0, b200_b1, b200_m, b200_n0, shape.N" << args << ");\n";
+  o << kGemmSource << "\n";
+  std::ostringstream note;
+  note << "tcgen05 " << bm << "x" << bn << "x" << bk << " stages=" << stages << " epi_warps=" << epi_warps
+       << (g.accumulate ? " beta=1" : "");
+  st.note = note.str();
+  // remembered for the launcher
+  st.block = 64 + 32 * epi_warps;
+  st.tile_m = bm;
+  st.tile_n = bn;
+  st.tile_k = bk;
+  st.smem_bytes = stages * stage_bytes + 1024 + 256;
+  return o.str();
+}
+
 }  // namespace b200

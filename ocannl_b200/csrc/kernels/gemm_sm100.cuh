@@ -1,1 +1,366 @@
-// placeholder
+// Dense contraction kernel for sm_100a:  D[b, m, n] = epilogue( sum_k A[b, m, k] * B[b, n, k] )
+//
+// One persistent CTA per SM, warp specialised:
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of A and B tiles (128-byte swizzle)
+//               into a B200_STAGES-deep shared-memory ring, completion on mbarriers
+//   warp 1      owns tensor memory (tcgen05.alloc) and issues tcgen05.mma (kind::f16 or
+//               kind::tf32, fp32 accumulators in TMEM); tcgen05.commit releases ring slots
+//               and publishes finished accumulators
+//   warps 2..   epilogue: tcgen05.ld of the accumulator (one TMEM lane = one output row per
+//               thread), the routine's generated epilogue expression, global stores
+// Two accumulator buffers in TMEM let the epilogue of tile i overlap the main loop of
+// tile i+1.  Every wait is bounded: a wait that does not complete within ~2 s raises the
+// device status word, all roles drain and the CTA frees its tensor memory and returns.
+//
+// The translation unit that includes this text defines:
+//   B200_GEMM_NAME            kernel symbol
+//   B200_BM (128), B200_BN    tile extents (B200_BN multiple of 16, <= 256)
+//   B200_BK                   k elements per ring slot (128 bytes worth)
+//   B200_UMMA_K               k elements per tcgen05.mma (16 for 16-bit inputs, 8 for tf32)
+//   B200_ELEM_BYTES           operand element size
+//   B200_STAGES               ring depth
+//   B200_EPI_WARPS            4 or 8
+//   B200_A_KMAJOR/B_KMAJOR    1: k is the contiguous axis of the operand, 0: m/n is
+//   B200_IDESC                tcgen05 instruction descriptor (formats, majors, M, N)
+//   B200_TMEM_COLS            power of two >= 2*B200_BN (and >= 32)
+//   B200_EPI_PARAMS           extra kernel parameters (node pointers) of the epilogue
+//   B200_EPILOGUE_ROW(...)    statement block evaluated per (row, 32-column chunk), see below
+#ifndef B200_GEMM_SM100_CUH
+#define B200_GEMM_SM100_CUH
+
+struct __align__(64) b200_tmap {
+  unsigned long long opaque[16];
+};
+
+struct b200_gemm_shape {
+  unsigned int M, N, K;
+  unsigned int B0, B1;          // batch extents, outer and inner (1 when absent)
+  unsigned int a_b0, a_b1;      // 1 when the operand varies along that batch axis
+  unsigned int b_b0, b_b1;
+  unsigned int tiles_m, tiles_n;
+};
+
+__device__ __forceinline__ unsigned int b200_smem_addr(const void* p) {
+  return (unsigned int)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void b200_mbar_init(unsigned int bar, unsigned int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void b200_mbar_expect_tx(unsigned int bar, unsigned int bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void b200_mbar_arrive(unsigned int bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ unsigned int b200_mbar_try(unsigned int bar, unsigned int parity) {
+  unsigned int ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ unsigned long long b200_now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#ifndef B200_WAIT_LIMIT_NS
+#define B200_WAIT_LIMIT_NS 2000000000ull
+#endif
+// Bounded wait.  Returns false when the CTA is aborting or the limit passed (then it raises
+// the abort flag and records `site` in the device status word).
+__device__ __forceinline__ bool b200_wait(unsigned int bar, unsigned int parity, volatile unsigned int* abort_flag,
+                                          unsigned int* status, unsigned int site) {
+  if (b200_mbar_try(bar, parity)) return true;
+  const unsigned long long t0 = b200_now_ns();
+  for (unsigned int it = 1;; ++it) {
+    if (b200_mbar_try(bar, parity)) return true;
+    if ((it & 255u) == 0u) {
+      if (*abort_flag) return false;
+      if (b200_now_ns() - t0 > B200_WAIT_LIMIT_NS) {
+        *abort_flag = 1u;
+        if (atomicCAS(status, 0u, 1u) == 0u) status[1] = site;
+        __threadfence_system();
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void b200_tma_load_4d(unsigned int dst, const b200_tmap* map, unsigned int bar, int c0, int c1,
+                                                 int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :
+      : "r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of tcgen05.mma for a 128-byte-swizzled tile.
+//   bits [0,14)  start address >> 4      bits [16,30) leading byte offset >> 4
+//   bits [32,46) stride byte offset >> 4 bits [46,48) descriptor version (1 on sm_100)
+//   bits [61,64) swizzle mode (2 = 128 bytes)
+__device__ __forceinline__ unsigned long long b200_smem_desc(unsigned int addr, unsigned int lbo_bytes,
+                                                             unsigned int sbo_bytes) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);
+  d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (unsigned long long)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+
+__device__ __forceinline__ void b200_umma(unsigned int tmem_d, unsigned long long desc_a, unsigned long long desc_b,
+                                          unsigned int idesc, unsigned int accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+#if B200_ELEM_BYTES == 4
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+#else
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+#endif
+      "}"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void b200_umma_commit(unsigned int bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void b200_tmem_ld32(unsigned int taddr, unsigned int* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void b200_tmem_ld16(unsigned int taddr, unsigned int* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+#define B200_A_TILE_BYTES (B200_BM * B200_BK * B200_ELEM_BYTES)
+#define B200_B_TILE_BYTES (B200_BN * B200_BK * B200_ELEM_BYTES)
+#define B200_STAGE_BYTES (B200_A_TILE_BYTES + B200_B_TILE_BYTES)
+#define B200_THREADS (64 + 32 * B200_EPI_WARPS)
+// elements of the contiguous axis covered by one 128-byte swizzle row
+#define B200_ROW_ELEMS (128 / B200_ELEM_BYTES)
+#ifndef B200_EPI_CHUNK
+#if B200_BN >= 32
+#define B200_EPI_CHUNK 32
+#else
+#define B200_EPI_CHUNK 16
+#endif
+#endif
+#ifndef B200_RASTER
+#define B200_RASTER 8
+#endif
+
+extern "C" __global__ void __launch_bounds__(B200_THREADS, 1)
+B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ b200_tmap map_b,
+               const b200_gemm_shape shape, unsigned int* status B200_EPI_PARAMS) {
+  extern __shared__ unsigned char b200_dyn_smem[];
+  // tiles need 1024-byte alignment for the 128-byte swizzle pattern
+  const unsigned int smem_base = (b200_smem_addr(b200_dyn_smem) + 1023u) & ~1023u;
+  unsigned char* smem_gen = b200_dyn_smem + (smem_base - b200_smem_addr(b200_dyn_smem));
+  const unsigned int tiles_at = smem_base;
+  // barriers and bookkeeping live after the ring
+  unsigned long long* bars = (unsigned long long*)(smem_gen + B200_STAGES * B200_STAGE_BYTES);
+  const unsigned int bar_full = b200_smem_addr(bars);                          // [STAGES]
+  const unsigned int bar_empty = bar_full + 8u * B200_STAGES;                  // [STAGES]
+  const unsigned int bar_acc_full = bar_empty + 8u * B200_STAGES;              // [2]
+  const unsigned int bar_acc_empty = bar_acc_full + 16u;                       // [2]
+  volatile unsigned int* tmem_slot = (volatile unsigned int*)(bars + 2 * B200_STAGES + 4);
+  volatile unsigned int* abort_flag = tmem_slot + 1;
+
+  const unsigned int warp = threadIdx.x >> 5;
+  const unsigned int lane = threadIdx.x & 31u;
+
+  if (threadIdx.x == 0) {
+    for (unsigned int s = 0; s < B200_STAGES; ++s) {
+      b200_mbar_init(bar_full + 8u * s, 1);
+      b200_mbar_init(bar_empty + 8u * s, 1);
+    }
+    for (unsigned int a = 0; a < 2; ++a) {
+      b200_mbar_init(bar_acc_full + 8u * a, 1);
+      b200_mbar_init(bar_acc_empty + 8u * a, B200_EPI_WARPS);
+    }
+    *abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(b200_smem_addr((const void*)tmem_slot)),
+                 "r"((unsigned int)B200_TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned int tmem_base = *tmem_slot;
+
+  const unsigned int tiles_per_batch = shape.tiles_m * shape.tiles_n;
+  const unsigned int total_tiles = tiles_per_batch * shape.B0 * shape.B1;
+  const unsigned int k_blocks = (shape.K + B200_BK - 1) / B200_BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      unsigned int slot = 0, phase = 0;
+      bool live = true;
+      for (unsigned int tile = blockIdx.x; live && tile < total_tiles; tile += gridDim.x) {
+        const unsigned int bidx = tile / tiles_per_batch;
+        const unsigned int t = tile - bidx * tiles_per_batch;
+        // consecutive tiles walk down m first so that a wave of CTAs shares few B tiles
+        const unsigned int group = t / (B200_RASTER * shape.tiles_n);
+        const unsigned int first_m = group * B200_RASTER;
+        const unsigned int rows = min((unsigned int)B200_RASTER, shape.tiles_m - first_m);
+        const unsigned int r = t - group * B200_RASTER * shape.tiles_n;
+        const unsigned int mt = first_m + r % rows;
+        const unsigned int nt = r / rows;
+        const unsigned int b0 = bidx / shape.B1, b1 = bidx - b0 * shape.B1;
+        const int m0 = (int)(mt * B200_BM), n0 = (int)(nt * B200_BN);
+        for (unsigned int kb = 0; kb < k_blocks; ++kb) {
+          if (!b200_wait(bar_empty + 8u * slot, phase ^ 1u, abort_flag, status, 1u)) { live = false; break; }
+          const unsigned int full = bar_full + 8u * slot;
+          b200_mbar_expect_tx(full, B200_STAGE_BYTES);
+          const unsigned int sa = tiles_at + slot * B200_STAGE_BYTES;
+          const unsigned int sb = sa + B200_A_TILE_BYTES;
+          const int k0 = (int)(kb * B200_BK);
+#if B200_A_KMAJOR
+          b200_tma_load_4d(sa, &map_a, full, k0, m0, (int)(b1 * shape.a_b1), (int)(b0 * shape.a_b0));
+#else
+#pragma unroll
+          for (int c = 0; c < B200_BM / B200_ROW_ELEMS; ++c)
+            b200_tma_load_4d(sa + c * (B200_ROW_ELEMS * B200_BK * B200_ELEM_BYTES), &map_a, full, m0 + c * B200_ROW_ELEMS, k0,
+                             (int)(b1 * shape.a_b1), (int)(b0 * shape.a_b0));
+#endif
+#if B200_B_KMAJOR
+          b200_tma_load_4d(sb, &map_b, full, k0, n0, (int)(b1 * shape.b_b1), (int)(b0 * shape.b_b0));
+#else
+#pragma unroll
+          for (int c = 0; c < B200_BN / B200_ROW_ELEMS; ++c)
+            b200_tma_load_4d(sb + c * (B200_ROW_ELEMS * B200_BK * B200_ELEM_BYTES), &map_b, full, n0 + c * B200_ROW_ELEMS, k0,
+                             (int)(b1 * shape.b_b1), (int)(b0 * shape.b_b0));
+#endif
+          if (++slot == B200_STAGES) { slot = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      unsigned int slot = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool live = true;
+      for (unsigned int tile = blockIdx.x; live && tile < total_tiles; tile += gridDim.x) {
+        if (!b200_wait(bar_acc_empty + 8u * acc, acc_phase ^ 1u, abort_flag, status, 2u)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned int d_tmem = tmem_base + acc * B200_BN;
+        for (unsigned int kb = 0; kb < k_blocks; ++kb) {
+          if (!b200_wait(bar_full + 8u * slot, phase, abort_flag, status, 3u)) { live = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const unsigned int sa = tiles_at + slot * B200_STAGE_BYTES;
+          const unsigned int sb = sa + B200_A_TILE_BYTES;
+#pragma unroll
+          for (unsigned int ks = 0; ks < B200_BK / B200_UMMA_K; ++ks) {
+#if B200_A_KMAJOR
+            // k-major: rows of 128 bytes, 8-row groups 1024 bytes apart; a k step moves
+            // UMMA_K elements along the row
+            const unsigned long long da = b200_smem_desc(sa + ks * (B200_UMMA_K * B200_ELEM_BYTES), 16u, 1024u);
+#else
+            // m-major: 64-element (128-byte) chunks of m, k rows 128 bytes apart, 8-row
+            // groups 1024 bytes apart, chunks of m one box apart; a k step moves UMMA_K rows
+            const unsigned long long da =
+                b200_smem_desc(sa + ks * (B200_UMMA_K * 128u), B200_ROW_ELEMS * B200_BK * B200_ELEM_BYTES, 1024u);
+#endif
+#if B200_B_KMAJOR
+            const unsigned long long db = b200_smem_desc(sb + ks * (B200_UMMA_K * B200_ELEM_BYTES), 16u, 1024u);
+#else
+            const unsigned long long db =
+                b200_smem_desc(sb + ks * (B200_UMMA_K * 128u), B200_ROW_ELEMS * B200_BK * B200_ELEM_BYTES, 1024u);
+#endif
+            b200_umma(d_tmem, da, db, (unsigned int)B200_IDESC, (kb | ks) != 0u ? 1u : 0u);
+          }
+          b200_umma_commit(bar_empty + 8u * slot);  // frees the slot once these MMAs retire
+          if (++slot == B200_STAGES) { slot = 0; phase ^= 1u; }
+        }
+        if (live) b200_umma_commit(bar_acc_full + 8u * acc);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const unsigned int ew = warp - 2;                 // 0 .. EPI_WARPS-1
+    const unsigned int quarter = warp & 3u;           // TMEM lanes this warp may read
+    const unsigned int col_half = ew >> 2;            // with 8 warps, two warps share a quarter
+    const unsigned int cols_per_warp = B200_BN / (B200_EPI_WARPS / 4);
+    unsigned int acc = 0, acc_phase = 0;
+    for (unsigned int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const unsigned int bidx = tile / tiles_per_batch;
+      const unsigned int t = tile - bidx * tiles_per_batch;
+      const unsigned int group = t / (B200_RASTER * shape.tiles_n);
+      const unsigned int first_m = group * B200_RASTER;
+      const unsigned int rows = min((unsigned int)B200_RASTER, shape.tiles_m - first_m);
+      const unsigned int r = t - group * B200_RASTER * shape.tiles_n;
+      const unsigned int mt = first_m + r % rows;
+      const unsigned int nt = r / rows;
+      const unsigned int b200_b0 = bidx / shape.B1, b200_b1 = bidx - b200_b0 * shape.B1;
+      if (!b200_wait(bar_acc_full + 8u * acc, acc_phase, abort_flag, status, 4u)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const unsigned int b200_m = mt * B200_BM + quarter * 32u + lane;
+      const unsigned int taddr = tmem_base + acc * B200_BN + ((quarter * 32u) << 16);
+      for (unsigned int c = 0; c < cols_per_warp; c += B200_EPI_CHUNK) {
+        const unsigned int col = col_half * cols_per_warp + c;
+        const unsigned int b200_n0 = nt * B200_BN + col;
+        if (b200_n0 >= shape.N) break;  // warp-uniform
+        unsigned int b200_r[B200_EPI_CHUNK];
+#if B200_EPI_CHUNK == 32
+        b200_tmem_ld32(taddr + col, b200_r);
+#else
+        b200_tmem_ld16(taddr + col, b200_r);
+#endif
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (b200_m < shape.M) {
+          B200_EPILOGUE_ROW
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) b200_mbar_arrive(bar_acc_empty + 8u * acc);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  __syncwarp();
+  if (*abort_flag) {
+    // let copies and MMAs already in flight land before the tensor memory is released
+    const unsigned long long t0 = b200_now_ns();
+    while (b200_now_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned int)B200_TMEM_COLS)
+                 : "memory");
+  }
+}
+
+#endif  // B200_GEMM_SM100_CUH

@@ -115,7 +115,7 @@ void b200_routine::enqueue_stages() {
       cu_check(cu().cuMemsetD8Async_(node_ptr[st.memset_tn], 0, (size_t)t.bytes(), dev->stream), "cuMemsetD8Async");
       continue;
     }
-    if (st.total <= 0 && st.kind == Stage::Generic) continue;
+    if (st.kind == Stage::Generic && st.total <= 0) continue;
     if (st.kind == Stage::Gemm) {
       gemm_enqueue(this, (int)i);
       dev->n_launches++;

@@ -317,3 +317,103 @@ def makemore_forward_numpy(P, ids, onehot):
     sh = logits - logits.max(1, keepdims=True)
     lse = np.log(np.exp(sh).sum(1, keepdims=True))
     return -(onehot * (sh - lse)).sum() / ids.shape[0], logits
+
+
+# ------------------------------------------------------------------ config 3: batched einsum + bias + GELU
+def einsum_gelu(batch=8, M=1024, N=1024, K=1024, in_prec="bfloat16", y_prec="bfloat16") -> Routine:
+    """`b|m,k ; b|k,n => b|m,n` through `+*`, bias add and a composed tanh-GELU.  The
+    contraction result is read once (by the bias add) so it is a virtual fp32 accumulator
+    inside `z`'s assignment; `z` is read three times by the GELU chain and is therefore
+    materialised (fp32), `y` is the routine output."""
+    r = Routine("einsum_gelu_%dx%dx%dx%d" % (batch, M, N, K))
+    a = r.tn("a", in_prec, [batch, M, K], read_only=True)
+    bm = r.tn("b", in_prec, [batch, K, N], read_only=True)
+    bias = r.tn("bias", "single", [N], read_only=True)
+    z = r.tn("z", "single", [batch, M, N])
+    y = r.tn("y", y_prec, [batch, M, N])
+    ib, im, in_, ik = r.syms(4)
+    s1 = loops([(ib, batch), (im, M), (in_, N)], Set(z, (ib, im, in_), reduce_scope(
+        r, "n_ab", "single", [(ik, K)], lambda: (a[ib, im, ik], bm[ib, ik, in_]), orig=(ib, im, in_)) + bias[in_]))
+    jb, jm, jn = r.syms(3)
+    s2 = loops([(jb, batch), (jm, M), (jn, N)], Set(y, (jb, jm, jn), gelu_tanh(z[jb, jm, jn])))
+    r.body = Seq([Comment("y fwd"), s1, s2, Comment("end")])
+    return r
+
+
+def einsum_gelu_inputs(batch, M, N, K, in_prec="bfloat16"):
+    a = np.random.default_rng(6).standard_normal((batch, M, K), np.float32)
+    b = np.random.default_rng(7).standard_normal((batch, K, N), np.float32)
+    bias = np.random.default_rng(8).standard_normal(N).astype(np.float32)
+    return {"a": store(in_prec, a), "b": store(in_prec, b), "bias": bias}
+
+
+# ------------------------------------------------------------------ config 5: data-parallel MLP 784-1024-1024-10
+def mlp_params(dims=(784, 1024, 1024, 10), seed=22, wprec="bfloat16"):
+    """U(-1,1)*sqrt(6/(fan_in+fan_out)) weights, the same on every shard; hidden-layer biases."""
+    rng = np.random.default_rng(seed)
+    P = {}
+    n_layers = len(dims) - 1
+    for l in range(n_layers):
+        fi, fo = dims[l], dims[l + 1]
+        name = "w_out" if l == n_layers - 1 else "w%d" % (l + 1)
+        P[name] = store(wprec, (rng.uniform(-1, 1, (fo, fi)) * math.sqrt(6.0 / (fi + fo))).astype(np.float32))
+        if l < n_layers - 1:
+            P["b%d" % (l + 1)] = store(wprec, (rng.uniform(-1, 1, fo) * math.sqrt(6.0 / (fi + fo))).astype(np.float32))
+    return P
+
+
+def mlp_inputs(rows=8192, in_dim=784, classes=10, seed=20, label_seed=21, xprec="bfloat16"):
+    x = np.random.default_rng(seed).standard_normal((rows, in_dim), np.float32)
+    lab = np.random.default_rng(label_seed).integers(0, classes, rows)
+    onehot = np.zeros((rows, classes), np.float32)
+    onehot[np.arange(rows), lab] = 1.0
+    return store(xprec, x), onehot
+
+
+def mlp_forward(rows=8192, dims=(784, 1024, 1024, 10), wprec="bfloat16", with_loss=True) -> Routine:
+    """Forward of `Nn_blocks.mlp` (lib/nn_blocks.ml:108,119-126: hidden `relu(w*x + b)`, linear
+    output without bias) with bf16 weights/activations and fp32 accumulation, followed by the
+    softmax cross-entropy mean loss of lib/nn_blocks.ml:137-143 against one-hot labels."""
+    r = Routine("mlp_fwd_%d" % rows)
+    x = r.tn("x", wprec, [rows, dims[0]], read_only=True)
+    labels = r.tn("labels", "single", [rows, dims[-1]], read_only=True)
+    n_layers = len(dims) - 1
+    body: List = [Comment("mlp fwd")]
+    h = x
+    for l in range(n_layers):
+        fi, fo = dims[l], dims[l + 1]
+        last = l == n_layers - 1
+        w = r.tn("w_out" if last else "w%d" % (l + 1), wprec, [fo, fi], read_only=True)
+        ib, io, ii = r.syms(3)
+        hin = h
+        acc = lambda: reduce_scope(r, "n_mm%d" % l, "single", [(ii, fi)], lambda: (w[io, ii], hin[ib, ii]), orig=(ib, io))
+        if last:
+            out = r.tn("logits", "single", [rows, fo])
+            body.append(loops([(ib, rows), (io, fo)], Set(out, (ib, io), acc())))
+        else:
+            b = r.tn("b%d" % (l + 1), wprec, [fo], read_only=True)
+            out = r.tn("h%d" % (l + 1), wprec, [rows, fo])
+            body.append(loops([(ib, rows), (io, fo)], Set(out, (ib, io), un("relu", acc() + b[io]))))
+        h = out
+    if with_loss:
+        C = dims[-1]
+        logits = h
+        max_l = r.tn("max_l", "single", [rows, 1])
+        expv = r.tn("exp_vals", "single", [rows, C])
+        ssum = r.tn("sum_exp", "single", [rows, 1])
+        loss = r.tn("loss", "single", [1])
+        ib, ic = r.syms(2)
+        body.append(loops([(ib, rows)], Set(max_l, (ib, 0), reduce_scope(
+            r, "n_max", "single", [(ic, C)], lambda: logits[ib, ic], op="max"))))
+        ib, ic = r.syms(2)
+        body.append(loops([(ib, rows), (ic, C)], Set(expv, (ib, ic), un("exp", logits[ib, ic] - max_l[ib, 0]))))
+        ib, ic = r.syms(2)
+        body.append(loops([(ib, rows)], Set(ssum, (ib, 0), reduce_scope(
+            r, "n_sum", "single", [(ic, C)], lambda: expv[ib, ic], op="add"))))
+        ib, ic = r.syms(2)
+        body.append(Set(loss, (0,), un("neg", reduce_scope(
+            r, "n_ce", "single", [(ib, rows), (ic, C)],
+            lambda: labels[ib, ic] * un("log", expv[ib, ic] / ssum[ib, 0]), op="add")) / float(rows)))
+    body.append(Comment("end"))
+    r.body = Seq(body)
+    return r

@@ -77,3 +77,36 @@ def test_makemore_forward(device, wprec, options):
         compare(ir, got, want, rtol=1e-5, atol=1e-5, exact=["embed"])
     else:
         compare(ir, got, want, rtol=2e-2, atol=2e-2, exact=["embed"])
+
+
+@pytest.mark.parametrize("shape", [(2, 256, 256, 256), (1, 200, 136, 200), (3, 128, 512, 64), (1, 384, 48, 1000)])
+@pytest.mark.parametrize("y_prec", ["bfloat16", "single"])
+def test_einsum_bias_gelu(device, shape, y_prec):
+    """Config 3 shapes (`b|m,k ; b|k,n => b|m,n`, bias, composed GELU) on the tensor-core path,
+    including ragged M/N/K that exercise the zero-filled tile edges.  bf16 operands, fp32
+    accumulation: rel 2e-2 (outputs) as the tolerance for bf16 contractions."""
+    b, m, n, k = shape
+    ir = W.einsum_gelu(b, m, n, k, y_prec=y_prec)
+    inputs = W.einsum_gelu_inputs(b, m, n, k)
+    want = run_oracle(ir, inputs)
+    got, info = run_device(device, ir, inputs)
+    assert info["stages"][0]["kind"] == "gemm", info
+    compare(ir, got, want, rtol=2e-2, atol=2e-3)
+    # same routine on the generic path: the two device paths agree with the oracle alike
+    got2, info2 = run_device(device, ir, inputs, options="gemm=0")
+    assert all(s["kind"] != "gemm" for s in info2["stages"])
+    compare(ir, got2, want, rtol=2e-2, atol=2e-3)
+
+
+@pytest.mark.parametrize("rows", [256, 1000])
+def test_mlp_forward_bf16(device, rows):
+    """Config 5 forward (784-1024-1024-10, bf16 weights and activations, fp32 accumulation
+    and loss) on a shard of `rows` rows."""
+    ir = W.mlp_forward(rows=rows)
+    x, onehot = W.mlp_inputs(rows=rows)
+    inputs = dict(W.mlp_params(), x=x, labels=onehot)
+    want = run_oracle(ir, inputs)
+    got, info = run_device(device, ir, inputs)
+    kinds = [s["kind"] for s in info["stages"]]
+    assert kinds[:2] == ["gemm", "gemm"], info
+    compare(ir, got, want, rtol=2e-2, atol=2e-3)
