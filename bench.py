@@ -1,0 +1,334 @@
+"""Benchmark of the hot path: batch-sharded inference forward of the 784-1024-1024-10 MLP.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One process per GPU (the launcher is torch.distributed.run for N > 1); every rank runs the
+forward routine over its own shard of `--rows` rows (weak scaling, no data-path collective —
+inference forward shards by batch).  A step = one run of the routine over one batch.
+
+Reported on ONE JSON line by rank 0:
+  value      forward samples/s of the whole job, inputs resident in device memory
+  e2e        the same through the host-facing calls: page-locked host batch -> from_host ->
+             run -> to_host of the loss, copies inside the timed region
+  roofline   the dominant kernel (the widest hidden-layer contraction): algorithmic FLOPs /
+             its CUDA-event duration, against the measured bf16 peak
+  cpu_baseline  the restated cc backend (oracle) on one host core, on a bounded row sample
+  contraction_sweep  `b|m,k ; b|k,n => b|m,n` + bias + GELU at 1024/4096/8192, TFLOP/s and
+             fraction of the measured bf16 peak (rank 0, N = 1 only)
+Timing: per-step CUDA events on the library's stream, L2 flushed between steps by clearing a
+256 MiB buffer outside the timed events; the job time is the max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "forward samples/sec"
+DIMS = (784, 1024, 1024, 10)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"bf16": d["bf16_tflops"], "bf16_sustained": d["bf16_tflops_sustained"], "hbm": d["hbm_gbs"],
+                "source": "measured"}
+    return {"bf16": 1590.0, "bf16_sustained": 1400.0, "hbm": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.rows = []
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def cpu_baseline(target_s=12.0):
+    """The oracle (restated cc backend, gcc -O3 -march=native, one thread as `sync_cc` runs)
+    on a row sample of the same forward; returns samples/s."""
+    from ocannl_b200 import workloads as W
+    from oracle.run_c import OracleRoutine
+
+    def run(rows):
+        ir = W.mlp_forward(rows=rows, dims=DIMS)
+        o = OracleRoutine(ir.to_b200ir())
+        bufs = o.buffers()
+        x, onehot = W.mlp_inputs(rows=rows)
+        for k, v in dict(W.mlp_params(dims=DIMS), x=x, labels=onehot).items():
+            bufs[k][...] = np.asarray(v).reshape(bufs[k].shape)
+        o.run(bufs)                       # warm-up
+        ts = [o.run(bufs) for _ in range(3)]
+        return float(np.median(ts))
+
+    t = run(64)
+    rows = int(min(8192, max(64, 64 * target_s / (4 * max(t, 1e-6)))))
+    rows = max(64, rows // 64 * 64)
+    t = run(rows)
+    return {"value": rows / t, "unit": "samples/s", "cores": 1, "kind": "port",
+            "sample": "%d of the shard's rows, same routine, median of 3 runs after 1 warm-up" % rows}
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, args.steps)
+    from ocannl_b200 import workloads as W
+    from oracle.run_c import OracleRoutine
+    rows = args.ref_rows
+    ir = W.mlp_forward(rows=rows, dims=DIMS)
+    o = OracleRoutine(ir.to_b200ir())
+    bufs = o.buffers()
+    x, onehot = W.mlp_inputs(rows=rows)
+    for k, v in dict(W.mlp_params(dims=DIMS), x=x, labels=onehot).items():
+        bufs[k][...] = np.asarray(v).reshape(bufs[k].shape)
+    for _ in range(max(1, min(args.warmup, 2))):
+        o.run(bufs)
+    t = sum(o.run(bufs) for _ in range(steps))
+    v = rows * steps / t
+    sample = "%d rows per step (bounded sample of the %d-row shard), one host thread as the reference's sync_cc" % (
+        rows, args.rows)
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "samples/s", "n_gpus": args.gpus, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * t / steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "config 5 forward: MLP 784-1024-1024-10, bf16 weights, fp32 accumulation, softmax CE",
+                   "rows_per_step": rows},
+        "cpu_baseline": {"value": v, "unit": "samples/s", "cores": 1, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+def contraction_sweep(dev, pk):
+    """Config 3: batch 8, M=N=K in {1024, 4096, 8192}, bf16 in, fp32 z + bf16 y out."""
+    from ocannl_b200 import backend as bk
+    from ocannl_b200 import workloads as W
+    out = []
+    for n in (1024, 4096, 8192):
+        ir = W.einsum_gelu(8, n, n, n)
+        code = bk.Code(ir)
+        rt = bk.Context(dev).link(code)
+        blk_a = W.store("bfloat16", np.random.default_rng(6).standard_normal((n, n), np.float32))
+        blk_b = W.store("bfloat16", np.random.default_rng(7).standard_normal((n, n), np.float32))
+        for name, blk in (("a", blk_a), ("b", blk_b)):
+            pool, off, t = rt.context.arrays[name]
+            for b in range(8):
+                dev.from_host(pool, off + b * blk.nbytes, blk)
+            dev.await_()
+        rt.context.from_host("bias", np.random.default_rng(8).standard_normal(n).astype(np.float32))
+        for _ in range(3):
+            rt.run()
+        dev.await_()
+        rt.profile(True)
+        reps = 5 if n < 8192 else 3
+        for _ in range(reps):
+            rt.run()
+        dev.await_()
+        st = rt.stage_times()
+        info = code.info()["stages"]
+        gemm_ms = st[0][0] / st[0][1]
+        total_ms = sum(t / c for t, c in st if c)
+        flops = 2.0 * 8 * n ** 3
+        out.append({"n": n, "kernel_ms": gemm_ms, "routine_ms": total_ms, "tflops": flops / gemm_ms / 1e9,
+                    "frac_of_bf16_peak": flops / gemm_ms / 1e9 / pk["bf16"], "routine_tflops": flops / total_ms / 1e9,
+                    "stages": [s["kind"] for s in info]})
+        rt.free()
+        code.free()
+        for p in {p for p, _, _ in rt.context.arrays.values()}:
+            dev.free_pool(p)
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--rows", type=int, default=8192, help="rows of the batch each GPU processes per step")
+    ap.add_argument("--ref-rows", type=int, default=512)
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("gloo")
+
+    from ocannl_b200 import backend as bk
+    from ocannl_b200 import workloads as W
+    if not os.path.exists(bk.LIB_PATH):
+        from ocannl_b200 import build
+        build.build_library()
+    pk = peaks()
+    dev = bk.Device(local)
+    rows, K, Wm = args.rows, max(1, args.steps), max(3, args.warmup)
+    ir = W.mlp_forward(rows=rows, dims=DIMS)
+    code = bk.Code(ir)
+    rt = bk.Context(dev).link(code)
+    ctx = rt.context
+    # every rank holds the same parameters and its own shard of rows (seeded by rank)
+    params = W.mlp_params(dims=DIMS)
+    x, onehot = W.mlp_inputs(rows=rows, seed=20 + rank, label_seed=21 + rank)
+    for k, v in params.items():
+        ctx.from_host(k, v)
+    ctx.from_host("x", x)
+    ctx.from_host("labels", onehot)
+    flush_pool = dev.alloc_pool(256 << 20)
+    rt.use_graph(True)
+
+    def barrier():
+        dev.await_()
+        if dist is not None:
+            dist.barrier()
+
+    def timed(step_fn, n):
+        total = 0.0
+        for _ in range(n):
+            dev.memset_zero(flush_pool, 0, 256 << 20)      # L2 flush, outside the events
+            e0 = dev.all_work()
+            step_fn()
+            e1 = dev.all_work()
+            e1.sync()
+            total += e0.elapsed_ms(e1)
+            e0.free()
+            e1.free()
+        return total
+
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        import torch
+        t = torch.tensor([ms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    # ---- device-resident forward
+    for _ in range(Wm):
+        rt.run()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = timed(rt.run, K)
+    barrier()
+    ms = max_over_ranks(ms)
+    value = rows * world * K / (ms / 1e3)
+
+    # ---- end to end: host batch in, loss out, through from_host / run / to_host
+    hx = bk.PinnedBuffer(x.shape, x.dtype)
+    hl = bk.PinnedBuffer(onehot.shape, onehot.dtype)
+    hloss = bk.PinnedBuffer((1,), np.float32)
+    hx.array[...] = x
+    hl.array[...] = onehot
+    px, ox, _ = ctx.arrays["x"]
+    pl, ol, _ = ctx.arrays["labels"]
+    ps, os_, _ = ctx.arrays["loss"]
+
+    def e2e_step():
+        dev.from_host(px, ox, hx.array)
+        dev.from_host(pl, ol, hl.array)
+        rt.run()
+        dev.to_host(ps, os_, hloss.array)
+
+    for _ in range(Wm):
+        e2e_step()
+    barrier()
+    ms_e2e = timed(e2e_step, K)
+    barrier()
+    ms_e2e = max_over_ranks(ms_e2e)
+    clocks = sampler.stop() if rank == 0 else None
+    loss_value = float(hloss.array[0])
+
+    # ---- roofline of the dominant kernel, timed per stage with CUDA events
+    rt.profile(True)
+    for _ in range(K):
+        dev.memset_zero(flush_pool, 0, 256 << 20)
+        rt.run()
+    dev.await_()
+    st = rt.stage_times()
+    stages = code.info()["stages"]
+    shares = [(t / c if c else 0.0) for t, c in st]
+    dom = max((i for i, s in enumerate(stages) if s["kind"] == "gemm"), key=lambda i: shares[i])
+    dom_ms = shares[dom]
+    achieved = stages[dom]["flops"] / dom_ms / 1e9
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": pk["bf16"], "unit": "TFLOP/s",
+                "frac": achieved / pk["bf16"], "traffic": None, "peak_source": pk["source"] + " (burst)",
+                "kernel": stages[dom]["kernel"], "kernel_ms": dom_ms,
+                "shape": {k: stages[dom][k] for k in ("m", "n", "k", "batch")},
+                "stage_ms": [round(s, 5) for s in shares]}
+    rt.profile(False)
+
+    if rank != 0:
+        return
+    line = {
+        "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": K, "warmup": Wm,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": "config 5 forward: MLP 784-1024-1024-10, bf16 weights and activations, fp32 "
+                               "accumulation, softmax cross-entropy; batch-sharded, no collective",
+                   "rows_per_gpu": rows, "global_batch": rows * world, "parallelism": "dp%d" % world,
+                   "l2": "flushed between steps (256 MiB clear outside the per-step CUDA events)",
+                   "launch": "CUDA graph replay of the routine's stages"},
+        "e2e": {"value": rows * world * K / (ms_e2e / 1e3), "unit": "samples/s",
+                "h2d_bytes_per_step": int(x.nbytes + onehot.nbytes), "d2h_bytes_per_step": 4,
+                "ms_per_step": ms_e2e / K},
+        "gpu_launches": int(rt.kernels_per_run()) * K,
+        "clocks": clocks, "roofline": roofline, "loss": loss_value,
+    }
+    if world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline()
+    if world == 1 and not args.no_sweep:
+        line["contraction_sweep"] = contraction_sweep(dev, pk)
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

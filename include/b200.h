@@ -103,6 +103,10 @@ int b200_link(b200_dev* dev, b200_code* code, const b200_binding* bindings, int 
 int b200_launch(b200_routine* r, const int64_t* static_idx, int n_static);
 int b200_routine_use_graph(b200_routine* r, int enable);
 int b200_routine_launch_count(b200_routine* r, int64_t* kernels_per_run);
+/* Per-stage device timing (CUDA events around every stage of the next runs; disables graph
+ * replay while on).  No counterpart in the reference, which has no profiler hooks. */
+int b200_routine_profile(b200_routine* r, int enable);
+int b200_routine_stage_time(b200_routine* r, int stage, float* total_ms, int* runs);
 int b200_routine_free(b200_routine* r);
 
 /* ---- observability: get_used_memory, get_debug_info (arrayjit/lib/cuda_backend.ml:123-126,1114-1118) */

@@ -307,6 +307,18 @@ class Routine:
         check(lib().b200_routine_launch_count(self.h, ctypes.byref(k)))
         return k.value
 
+    def profile(self, on: bool = True):
+        check(lib().b200_routine_profile(self.h, ctypes.c_int(int(on))))
+
+    def stage_times(self):
+        """[(total_ms, runs)] per stage, over the runs made while profiling was on."""
+        out = []
+        for i in range(len(self.code.info()["stages"])):
+            ms, n = ctypes.c_float(0), ctypes.c_int(0)
+            check(lib().b200_routine_stage_time(self.h, ctypes.c_int(i), ctypes.byref(ms), ctypes.byref(n)))
+            out.append((ms.value, n.value))
+        return out
+
     def free(self):
         if self.h:
             lib().b200_routine_free(self.h)

@@ -433,6 +433,21 @@ int b200_routine_launch_count(b200_routine* r, int64_t* kernels_per_run) {
   });
 }
 
+int b200_routine_profile(b200_routine* r, int enable) {
+  return guard([&] {
+    if (!r) throw Error(B200_E_INVALID, "null routine");
+    r->profiling = enable != 0;
+  });
+}
+
+int b200_routine_stage_time(b200_routine* r, int stage, float* total_ms, int* runs) {
+  return guard([&] {
+    if (!r || !total_ms || !runs) throw Error(B200_E_INVALID, "null argument");
+    r->dev->make_current();
+    r->stage_time(stage, total_ms, runs);
+  });
+}
+
 int b200_routine_free(b200_routine* r) {
   return guard([&] {
     if (!r) return;

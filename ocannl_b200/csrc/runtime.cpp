@@ -108,8 +108,26 @@ void b200_routine::enqueue_stages() {
   const Program& P = code->code.prog;
   for (auto& z : scratch_zero)
     cu_check(cu().cuMemsetD8Async_(scratch + z.first, 0, z.second, dev->stream), "cuMemsetD8Async(scratch)");
+  if (profiling && stage_events.size() != code->code.stages.size()) stage_events.assign(code->code.stages.size(), {});
+  struct Timer {
+    b200_routine* r;
+    size_t i;
+    CUevent a = nullptr, b = nullptr;
+    Timer(b200_routine* r_, size_t i_) : r(r_), i(i_) {
+      if (!r->profiling) return;
+      cu_check(cu().cuEventCreate_(&a, CU_EVENT_DEFAULT), "cuEventCreate");
+      cu_check(cu().cuEventCreate_(&b, CU_EVENT_DEFAULT), "cuEventCreate");
+      cu_check(cu().cuEventRecord_(a, r->dev->stream), "cuEventRecord");
+    }
+    ~Timer() {
+      if (!a) return;
+      cu().cuEventRecord_(b, r->dev->stream);
+      r->stage_events[i].push_back({a, b});
+    }
+  };
   for (size_t i = 0; i < code->code.stages.size(); ++i) {
     const Stage& st = code->code.stages[i];
+    Timer timer(this, i);
     if (st.kind == Stage::Memset) {
       const Tnode& t = P.tn(st.memset_tn);
       cu_check(cu().cuMemsetD8Async_(node_ptr[st.memset_tn], 0, (size_t)t.bytes(), dev->stream), "cuMemsetD8Async");
@@ -167,7 +185,7 @@ void b200_routine::launch(const int64_t* static_idx, int n_static) {
       statics_valid = true;
     }
   }
-  if (want_graph) {
+  if (want_graph && !profiling) {
     if (!graph) {
       CUgraph g = nullptr;
       cu_check(cu().cuStreamBeginCapture_(dev->stream, CU_STREAM_CAPTURE_MODE_THREAD_LOCAL), "cuStreamBeginCapture");
@@ -199,8 +217,28 @@ void b200_routine::set_graph(bool on) {
   }
 }
 
+void b200_routine::stage_time(int stage, float* total_ms, int* runs) {
+  if (stage < 0 || stage >= (int)code->code.stages.size()) throw Error(B200_E_INVALID, "stage out of range");
+  *total_ms = 0;
+  *runs = 0;
+  if ((size_t)stage >= stage_events.size()) return;
+  for (auto& e : stage_events[stage]) {
+    cu_check(cu().cuEventSynchronize_(e.second), "cuEventSynchronize");
+    float ms = 0;
+    cu_check(cu().cuEventElapsedTime_(&ms, e.first, e.second), "cuEventElapsedTime");
+    *total_ms += ms;
+    ++*runs;
+  }
+}
+
 void b200_routine::destroy() {
   if (dev) cu().cuStreamSynchronize_(dev->stream);
+  for (auto& v : stage_events)
+    for (auto& e : v) {
+      cu().cuEventDestroy_(e.first);
+      cu().cuEventDestroy_(e.second);
+    }
+  stage_events.clear();
   if (graph) cu().cuGraphExecDestroy_(graph);
   for (auto* g : gemm) gemm_release(g);
   for (auto m : gemm_modules)

@@ -67,12 +67,15 @@ struct b200_routine {
   std::vector<long long> last_statics;
   bool statics_valid = false;
   bool want_graph = false;
+  bool profiling = false;
+  std::vector<std::vector<std::pair<CUevent, CUevent>>> stage_events;  // per stage, per profiled run
   CUgraphExec graph = nullptr;
 
   void link(b200_dev* d, b200_code* c, const b200_binding* b, int n);
   void launch(const int64_t* static_idx, int n_static);
   void enqueue_stages();
   void set_graph(bool on);
+  void stage_time(int stage, float* total_ms, int* runs);
   void destroy();
 };
 
