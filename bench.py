@@ -140,12 +140,12 @@ def reference_arm(args):
         "e2e": {"value": v, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
-def contraction_sweep(dev, pk):
+def contraction_sweep(dev, pk, sizes=(1024, 4096, 8192)):
     """Config 3: batch 8, M=N=K in {1024, 4096, 8192}, bf16 in, fp32 z + bf16 y out."""
     from ocannl_b200 import backend as bk
     from ocannl_b200 import workloads as W
     out = []
-    for n in (1024, 4096, 8192):
+    for n in sizes:
         ir = W.einsum_gelu(8, n, n, n)
         code = bk.Code(ir)
         rt = bk.Context(dev).link(code)
@@ -189,6 +189,8 @@ def main():
     ap.add_argument("--rows", type=int, default=8192, help="rows of the batch each GPU processes per step")
     ap.add_argument("--ref-rows", type=int, default=512)
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--sweep-size", type=int, default=0,
+                    help="run only the batch-8 contraction of this M=N=K (a small case for profilers) and exit")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -209,6 +211,9 @@ def main():
         build.build_library()
     pk = peaks()
     dev = bk.Device(local)
+    if args.sweep_size:
+        print(json.dumps({"contraction_sweep": contraction_sweep(dev, pk, (args.sweep_size,))}))
+        return
     rows, K, Wm = args.rows, max(1, args.steps), max(3, args.warmup)
     ir = W.mlp_forward(rows=rows, dims=DIMS)
     code = bk.Code(ir)

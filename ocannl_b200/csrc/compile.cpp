@@ -18,7 +18,8 @@
 namespace b200 {
 
 bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& body, bool zeroed_before,
-                const CompileOptions& opt, Stage* out);  // gemm_match.cpp
+                const CompileOptions& opt, const std::vector<Follower>& followers, int* n_fused,
+                Stage* out);  // gemm_match.cpp
 std::string gemm_translation_unit(const Program& P, Stage& st, const std::string& kernel_name,
                                   const CompileOptions& opt);
 
@@ -118,6 +119,7 @@ void collect_scopes(const Stmt& s, std::set<std::pair<int, int>>& declared, std:
 // warp per output element pays.  Returns the lane-strided symbol or "".
 struct CoopInfo {
   std::string sym;
+  int width = 32;  // threads cooperating on one output element
   std::vector<std::pair<int, std::string>> scopes;  // (scope id, combine op)
 };
 
@@ -233,13 +235,14 @@ struct Builder {
     return out;
   }
 
-  // Tries to find a lane-strided loop for a warp-per-element reduction.
+  // Cooperative reduction: the stage's assignment holds Local_scope reductions
+  // `v := neutral; for k1 { for k2 .. { v := v (+|max|min) f(k..) } }`.  A group of threads (a
+  // warp, or a whole block when there are few outputs and much to reduce) strides over the
+  // flattened reduction space of one output element and combines its partial results.
   CoopInfo find_coop(const Stmt& body, int64_t par_total) {
     CoopInfo ci;
     if (!opt.enable_coop) return ci;
     if (body.kind != Stmt::Set) return ci;
-    // every Local_scope directly inside the expression must be `init; for k {accum}` over the
-    // same extent; nested scopes inside the accumulated term are not handled
     std::vector<const Scalar*> scopes;
     bool nested = false;
     std::function<void(const Scalar&, int)> rec = [&](const Scalar& e, int depth) {
@@ -264,23 +267,28 @@ struct Builder {
         loop = b.items[1].get();
       } else return CoopInfo{};
       if (init && (init->scope_id != sc->scope_id || init->value->kind != Scalar::Const)) return CoopInfo{};
+      int64_t ext = 1;
+      const Stmt* inner = loop;
+      while (inner->kind == Stmt::For) {
+        ext *= inner->to - inner->from + 1;
+        inner = inner->body.get();
+      }
       std::string op;
-      if (!accum_form(*loop->body, sc->scope_id, sc->tn, &op)) return CoopInfo{};
+      if (!accum_form(*inner, sc->scope_id, sc->tn, &op)) return CoopInfo{};
       Prec p = code.prog.tn(sc->tn).prec;
       if (p != Prec::Single && !(p == Prec::Double && op == "add")) return CoopInfo{};
       // the initial value must be the neutral element of the combine
       double want = op == "add" ? 0.0 : (op == "max" ? -INFINITY : INFINITY);
       if (init && init->value->cval != want) return CoopInfo{};
       if (!init && op != "add") return CoopInfo{};
-      int64_t ext = loop->to - loop->from + 1;
       if (extent < 0) extent = ext;
       else if (ext != extent) return CoopInfo{};
       ci.scopes.push_back({sc->scope_id, op});
     }
-    // worth it when rows are long and a thread per row would leave the GPU idle or uncoalesced
     if (extent < 64) return CoopInfo{};
-    (void)par_total;
-    ci.sym = "*";  // every scope loop is strided (each has its own symbol)
+    ci.sym = "*";
+    // few outputs and a long reduction: a whole block per output element
+    ci.width = (par_total <= 256 && extent >= 4096) ? 1024 : 32;
     return ci;
   }
 
@@ -289,7 +297,6 @@ struct Builder {
     st.kind = Stage::Generic;
     st.kernel = kernel_name();
     // which loops are independent
-    Stmt probe;  // the nest's innermost body is what writes
     std::vector<bool> par(nest.size(), false);
     for (size_t i = 0; i < nest.size(); ++i) par[i] = nest[i].extent() > 0 && parallel_safe(nest[i].sym, *body);
     for (size_t i = 0; i < nest.size(); ++i) (par[i] ? st.par : st.ser).push_back(nest[i]);
@@ -311,7 +318,8 @@ struct Builder {
     std::string inner;
     int ind = 4 + 2 * (int)st.ser.size();
     if (!ci.sym.empty()) {
-      st.coop = 32;
+      st.coop = ci.width;
+      if (ci.width > 32) st.block = ci.width;
       inner = coop_body(em, *body, ci, ind);
     } else {
       inner = em.stmt(*body, ind);
@@ -350,11 +358,15 @@ struct Builder {
     std::string statics = static_prologue(body_text + decomp, em, 2);
 
     std::ostringstream k_src;
-    k_src << "extern \"C\" __global__ void __launch_bounds__(256) " << st.kernel << "(";
+    k_src << "extern \"C\" __global__ void __launch_bounds__(" << st.block << ") " << st.kernel << "(";
     emit_params(k_src, st, em, written);
     k_src << ") {\n" << statics;
-    if (st.coop) {
-      k_src << "  const unsigned int b200_lane = threadIdx.x & 31u;\n";
+    if (st.coop > 32) {
+      k_src << "  __shared__ double b200_red[32];\n";
+      k_src << "  const unsigned int b200_t = threadIdx.x;\n";
+      k_src << "  for (unsigned long long b200_g = blockIdx.x; b200_g < " << st.total << "ull; b200_g += gridDim.x) {\n";
+    } else if (st.coop) {
+      k_src << "  const unsigned int b200_t = threadIdx.x & 31u;\n";
       k_src << "  const unsigned long long b200_warp = ((unsigned long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;\n";
       k_src << "  const unsigned long long b200_nwarps = ((unsigned long long)gridDim.x * blockDim.x) >> 5;\n";
       k_src << "  for (unsigned long long b200_g = b200_warp; b200_g < " << st.total << "ull; b200_g += b200_nwarps) {\n";
@@ -365,18 +377,19 @@ struct Builder {
     k_src << decomp << body_text << "  }\n}\n\n";
     src << k_src.str();
     std::ostringstream note;
-    note << "par=" << st.par.size() << " ser=" << st.ser.size() << (st.coop ? " warp-per-element" : "");
+    note << "par=" << st.par.size() << " ser=" << st.ser.size()
+         << (st.coop > 32 ? " block-per-element" : st.coop ? " warp-per-element" : "");
     st.note = note.str();
     code.stages.push_back(st);
   }
 
-  // One warp per output element: each Local_scope reduction loop is strided over the lanes,
-  // the partial results are combined with shuffles, and lane 0 evaluates and stores the rest.
+  // A group of threads per output element: each Local_scope reduction runs over its flattened
+  // loop space strided by the group width, partial results are combined with shuffles (and
+  // shared memory across warps), and thread 0 of the group evaluates and stores the rest.
   std::string coop_body(Emitter& em, const Stmt& set, const CoopInfo& ci, int ind) {
     std::string out;
     std::string padding((size_t)ind, ' ');
     const Tnode& t = code.prog.tn(set.tn);
-    // 1. emit each scope's reduction with a lane-strided loop
     std::function<void(const Scalar&)> rec = [&](const Scalar& e) {
       if (e.kind == Scalar::LocalScope) {
         std::string op;
@@ -385,13 +398,38 @@ struct Builder {
         Prec p = code.prog.tn(e.tn).prec;
         const Stmt& b = *e.body;
         const Stmt* loop = b.kind == Stmt::For ? &b : b.items[1].get();
+        std::vector<LoopDim> red;
+        const Stmt* inner = loop;
+        while (inner->kind == Stmt::For) {
+          red.push_back({inner->index, inner->from, inner->to});
+          inner = inner->body.get();
+        }
+        int64_t total = 1;
+        for (auto& d : red) total *= d.extent();
         std::string name = em.scope_name(e.scope_id, e.tn);
         double neutral = op == "add" ? 0.0 : (op == "max" ? -INFINITY : INFINITY);
         out += padding + Emitter::ctype(p) + " " + name + " = " + em.constant(neutral, p) + ";\n";
-        em.coop_sym = loop->index;
-        out += em.stmt(*loop, ind);
-        em.coop_sym.clear();
-        out += padding + name + " = b200_warp_" + (op == "add" ? "sum" : op) + "(" + name + ");\n";
+        std::string lv = "b200_l" + std::to_string(e.scope_id);
+        out += padding + "for (unsigned long long " + lv + " = b200_t; " + lv + " < " + std::to_string(total) + "ull; " + lv +
+               " += " + std::to_string(ci.width) + "u) {\n";
+        std::string rem = lv;
+        for (size_t i = red.size(); i-- > 0;) {
+          const LoopDim& d = red[i];
+          std::string ext = std::to_string(d.extent()) + "ull";
+          std::string val = i == 0 ? rem : "(" + rem + " % " + ext + ")";
+          out += padding + "  const unsigned int " + d.sym + " = (unsigned int)" + val +
+                 (d.from ? " + " + std::to_string(d.from) : std::string()) + ";\n";
+          if (i != 0) {
+            std::string nr = "b200_q" + std::to_string(e.scope_id) + "_" + std::to_string(i);
+            out += padding + "  const unsigned long long " + nr + " = " + rem + " / " + ext + ";\n";
+            rem = nr;
+          }
+        }
+        out += em.stmt(*inner, ind + 2);
+        out += padding + "}\n";
+        const std::string fn = op == "add" ? "sum" : op;
+        if (ci.width > 32) out += padding + name + " = b200_block_" + fn + "(" + name + ", b200_red);\n";
+        else out += padding + name + " = b200_warp_" + fn + "(" + name + ");\n";
         em.scope_subst[e.scope_id] = name;
         return;
       }
@@ -400,7 +438,7 @@ struct Builder {
     rec(*set.value);
     Emitter::Res v = em.scalar(t.prec, *set.value);
     em.used_nodes.insert(set.tn);
-    out += padding + "if (b200_lane == 0) " + t.ident + "[" + em.offset(set.idcs, t.dims) + "] = " + v.expr + ";\n";
+    out += padding + "if (b200_t == 0) " + t.ident + "[" + em.offset(set.idcs, t.dims) + "] = " + v.expr + ";\n";
     em.scope_subst.clear();
     return out;
   }
@@ -418,6 +456,23 @@ struct Builder {
       for (auto& x : s->items) top_level(x, flat);
     else if (s->kind != Stmt::Noop && s->kind != Stmt::Comment)
       flat.push_back(s);
+  }
+
+  // the perfect-nest pointwise assignments that directly follow position `from`
+  std::vector<Follower> followers_after(const std::vector<StmtP>& flat, size_t from) {
+    std::vector<Follower> out;
+    for (size_t k = from; k < flat.size() && out.size() < 4; ++k) {
+      Follower f;
+      const Stmt* b = flat[k].get();
+      while (b->kind == Stmt::For) {
+        f.nest.push_back({b->index, b->from, b->to});
+        b = b->body.get();
+      }
+      if (b->kind != Stmt::Set) break;
+      f.set = b;
+      out.push_back(f);
+    }
+    return out;
   }
 
   void run() {
@@ -442,12 +497,14 @@ struct Builder {
             body = body->body;
           }
           Stage g;
-          if (body->kind == Stmt::Set && body->tn == s->tn && match_gemm(code.prog, nest, *body, true, opt, &g)) {
+          int n_fused = 0;
+          if (body->kind == Stmt::Set && body->tn == s->tn &&
+              match_gemm(code.prog, nest, *body, true, opt, followers_after(flat, i + 2), &n_fused, &g)) {
             g.kernel = kernel_name();
             g.gemm_source = gemm_translation_unit(code.prog, g, g.kernel, opt);
             code.stages.push_back(g);
             absorbed = true;
-            ++i;
+            i += 1 + (size_t)n_fused;
           }
         }
         if (!absorbed) memset_stage(s->tn);
@@ -470,10 +527,12 @@ struct Builder {
       }
       if (opt.enable_gemm && body->kind == Stmt::Set) {
         Stage g;
-        if (match_gemm(code.prog, nest, *body, false, opt, &g)) {
+        int n_fused = 0;
+        if (match_gemm(code.prog, nest, *body, false, opt, followers_after(flat, i + 1), &n_fused, &g)) {
           g.kernel = kernel_name();
           g.gemm_source = gemm_translation_unit(code.prog, g, g.kernel, opt);
           code.stages.push_back(g);
+          i += (size_t)n_fused;
           continue;
         }
       }

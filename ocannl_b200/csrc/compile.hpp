@@ -59,6 +59,12 @@ struct Stage {
   std::string note;              // human-readable classification, for debug info
 };
 
+// A loop nest that follows a contraction and may be folded into its epilogue.
+struct Follower {
+  std::vector<LoopDim> nest;
+  const Stmt* set = nullptr;
+};
+
 struct Code {
   Program prog;
   std::vector<Stage> stages;

@@ -221,7 +221,16 @@ std::string Emitter::binop(Prec prec, const std::string& op, const std::string& 
   return binop_plain(prec, op, a, b);
 }
 std::string Emitter::unop(Prec prec, const std::string& op, const std::string& a) {
-  if (lowp(prec)) return std::string(down_fn(prec)) + unop_plain(Prec::Single, op, up_fn(prec) + a + ")") + ")";
+  if (lowp(prec)) {
+    // a 16-bit result keeps 8 (bf16) or 11 (half) significant bits: the hardware
+    // approximations of tanh / exp / log (relative error below 2^-10) round to the same value
+    // as the libm functions except for rare one-unit differences in the last kept bit
+    const std::string x = up_fn(prec) + a + ")";
+    if (op == "tanh") return std::string(down_fn(prec)) + "b200_tanh_fast(" + x + "))";
+    if (op == "exp") return std::string(down_fn(prec)) + "__expf(" + x + "))";
+    if (op == "log") return std::string(down_fn(prec)) + "__logf(" + x + "))";
+    return std::string(down_fn(prec)) + unop_plain(Prec::Single, op, x) + ")";
+  }
   return unop_plain(prec, op, a);
 }
 std::string Emitter::ternop(Prec prec, const std::string& op, const std::string& a, const std::string& b,
@@ -358,6 +367,16 @@ Emitter::Res Emitter::scalar(Prec prec, const Scalar& e) {
     case Scalar::Bin: {
       if (e.op == "arg1") return scalar(prec, *e.args[0].s);
       if (e.op == "arg2") return scalar(prec, *e.args[1].s);
+      if (e.op == "pow" && e.args[1].s->kind == Scalar::Const && !is_int_prec(prec) &&
+          (e.args[1].s->cval == 2.0 || e.args[1].s->cval == 3.0)) {
+        // x ** 2 and x ** 3 by multiplication (within 2 ulp of powf, far cheaper in an epilogue)
+        Res a = scalar(prec, *e.args[0].s);
+        r.defs = a.defs;
+        const std::string fn = e.args[1].s->cval == 2.0 ? "b200_pow2(" : "b200_pow3(";
+        if (lowp(prec)) r.expr = std::string(down_fn(prec)) + fn + up_fn(prec) + a.expr + ")))";
+        else r.expr = fn + a.expr + ")";
+        return r;
+      }
       Res a = scalar(prec, *e.args[0].s), b = scalar(prec, *e.args[1].s);
       r.defs = a.defs;
       r.defs.insert(r.defs.end(), b.defs.begin(), b.defs.end());
@@ -455,6 +474,8 @@ std::string Emitter::stmt(const Stmt& s, int ind) {
       Res v = scalar(t.prec, *s.value);
       used_nodes.insert(s.tn);
       std::string a = t.ident + "[" + offset(s.idcs, t.dims) + "] = " + v.expr + ";\n";
+      auto rd = set_redirect.find(s.tn);
+      if (rd != set_redirect.end() && same_indices(rd->second.first, s.idcs)) a = rd->second.second + " = " + v.expr + ";\n";
       if (v.defs.empty()) return pad(ind) + a;
       return pad(ind) + "{\n" + emit_defs(v.defs, ind + 2) + pad(ind + 2) + a + pad(ind) + "}\n";
     }

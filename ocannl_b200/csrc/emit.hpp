@@ -28,6 +28,9 @@ struct Emitter {
   // (node id) -> expression holding the value just stored at the position of the current
   // parallel iteration; lets a fused consumer read a producer's value from a register
   std::map<int, std::pair<Indices, std::string>> forwarded;
+  // (node id) -> lvalue that receives a Set at exactly these indices instead of memory (the
+  // register tile of a contraction epilogue; the caller stores the tile afterwards)
+  std::map<int, std::pair<Indices, std::string>> set_redirect;
   // nodes whose loads may use the read-only data path
   std::set<int> readonly_nodes;
   // cooperative reductions: scope id -> lane-strided loop symbol (see compile.cpp)

@@ -81,7 +81,8 @@ bool mac_step(const Scalar& v, const std::function<bool(const Scalar&)>& is_acc,
 }  // namespace
 
 bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& set, bool zeroed_before,
-                const CompileOptions& opt, Stage* out) {
+                const CompileOptions& opt, const std::vector<Follower>& followers, int* n_fused, Stage* out) {
+  *n_fused = 0;
   if (set.kind != Stmt::Set) return false;
   const Tnode& D = P.tn(set.tn);
   std::set<std::string> statics;
@@ -304,18 +305,135 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
   for (auto& s : F)
     if (s.extent == 1) unit_syms += "    const unsigned int " + s.sym + " = 0u;\n";
 
+  // Every node the epilogue writes goes through a per-thread register tile (one value per
+  // column of the chunk) so that the tile can be stored with 16-byte vector stores, and so
+  // that fused follow-up assignments read the producer's value from registers.
+  struct Out {
+    int tn;
+    Indices idcs;
+    std::string arr;
+    bool unit_n = false;   // the node's last axis is the n symbol: a chunk is contiguous
+    std::string row_off;   // element offset of column n = 0 of this row
+  };
+  std::vector<Out> outs;
+  const std::string n_sym = dn.syms.size() == 1 ? dn.syms[0].first : std::string();
+  auto add_out = [&](int tn, const Indices& idcs) {
+    Out o;
+    o.tn = tn;
+    o.idcs = idcs;
+    o.arr = "b200_o" + std::to_string(tn);
+    const Tnode& t = P.tn(tn);
+    if (!n_sym.empty() && !idcs.empty() && idcs.back().kind == Index::Iter && idcs.back().sym == n_sym) {
+      bool elsewhere = false;
+      for (size_t a = 0; a + 1 < idcs.size(); ++a)
+        if (idcs[a].uses(n_sym)) elsewhere = true;
+      if (!elsewhere) {
+        Indices row = idcs;
+        row.back().kind = Index::Fixed;
+        row.back().fixed = 0;
+        row.back().sym.clear();
+        o.unit_n = true;
+        o.row_off = em.offset(row, t.dims);
+      }
+    }
+    em.set_redirect[tn] = {idcs, o.arr + "[b200_j]"};
+    em.used_nodes.insert(tn);
+    outs.push_back(o);
+  };
+
   em.scope_subst[kAccScope] = "b200_acc";
   std::string body;
+  add_out(set.tn, set.idcs);
   if (form_b) {
     const Tnode& t = D;
-    em.used_nodes.insert(set.tn);
     std::string off = em.offset(set.idcs, t.dims);
-    if (g.accumulate) body = "      " + t.ident + "[" + off + "] = " + t.ident + "[" + off + "] + b200_acc;\n";
-    else body = "      " + t.ident + "[" + off + "] = b200_acc;\n";
+    if (g.accumulate) body = "      " + outs[0].arr + "[b200_j] = " + t.ident + "[" + off + "] + b200_acc;\n";
+    else body = "      " + outs[0].arr + "[b200_j] = b200_acc;\n";
   } else {
     em.scope_subst[scope->scope_id] = "b200_acc";
     body = em.stmt(set, 6);
   }
+  em.forwarded[set.tn] = {set.idcs, outs[0].arr + "[b200_j]"};
+
+  // ---- fuse following pointwise assignments over the same index space into the epilogue:
+  //      `for f'.. { u[f'..] := E(t[f'..], ...) }` where t is what this stage just produced
+  int fused = 0;
+  std::string aliases;
+  std::set<int> produced = {set.tn};
+  for (const Follower& fo : followers) {
+    if (fo.nest.size() != free_loops.size() || fo.set->kind != Stmt::Set) break;
+    bool ok = true;
+    std::map<std::string, std::string> ren;  // follower symbol -> this stage's symbol
+    for (size_t i = 0; i < fo.nest.size(); ++i) {
+      if (fo.nest[i].from != 0 || fo.nest[i].extent() != free_loops[i].extent()) ok = false;
+      ren[fo.nest[i].sym] = free_loops[i].sym;
+    }
+    if (!ok) break;
+    auto renamed_equal = [&](const Indices& a, const Indices& b) {
+      if (a.size() != b.size()) return false;
+      for (size_t i = 0; i < a.size(); ++i) {
+        if (a[i].kind != b[i].kind) return false;
+        if (a[i].kind == Index::Iter) {
+          auto it = ren.find(a[i].sym);
+          if ((it == ren.end() ? a[i].sym : it->second) != b[i].sym) return false;
+        } else if (a[i].kind == Index::Fixed) {
+          if (a[i].fixed != b[i].fixed) return false;
+        } else return false;
+      }
+      return true;
+    };
+    // the follower may read produced nodes only at the very position being produced, writes a
+    // node not produced or read so far, at a position that is a bijection of the index space
+    bool reads_producer = false;
+    std::function<void(const Scalar&)> chk = [&](const Scalar& e) {
+      if (e.kind == Scalar::LocalScope || e.kind == Scalar::GetLocal || e.kind == Scalar::GetMerge) ok = false;
+      if (e.kind == Scalar::Get || e.kind == Scalar::GetDyn) {
+        if (produced.count(e.tn)) {
+          reads_producer = true;
+          const Out* src = nullptr;
+          for (auto& o : outs)
+            if (o.tn == e.tn) src = &o;
+          if (e.kind != Scalar::Get || !src || !renamed_equal(e.idcs, src->idcs)) ok = false;
+        }
+        if (e.tn == fo.set->tn) ok = false;
+      }
+      for (auto& a : e.args) chk(*a.s);
+    };
+    chk(*fo.set->value);
+    if (!ok || !reads_producer || produced.count(fo.set->tn) || em.used_nodes.count(fo.set->tn)) break;
+    for (size_t i = 0; i < fo.nest.size(); ++i) {
+      int occ = 0;
+      for (auto& ix : fo.set->idcs)
+        if (ix.kind == Index::Iter && ix.sym == fo.nest[i].sym) ++occ;
+      if (occ != 1) ok = false;
+    }
+    for (auto& ix : fo.set->idcs)
+      if (ix.kind != Index::Iter && ix.kind != Index::Fixed) ok = false;
+    if (!ok) break;
+    // aliases make the follower's symbols names for this stage's symbols
+    for (size_t i = 0; i < fo.nest.size(); ++i)
+      if (fo.nest[i].sym != free_loops[i].sym)
+        aliases += "      const unsigned int " + fo.nest[i].sym + " = " + free_loops[i].sym + ";\n";
+    // forwarded reads are matched on the follower's own spelling of the indices
+    for (auto& o : outs) {
+      Indices spelled = o.idcs;
+      for (auto& ix : spelled)
+        if (ix.kind == Index::Iter)
+          for (auto& kv : ren)
+            if (kv.second == ix.sym) ix.sym = kv.first;
+      em.forwarded[o.tn] = {spelled, o.arr + "[b200_j]"};
+    }
+    Indices canon = fo.set->idcs;
+    for (auto& ix : canon)
+      if (ix.kind == Index::Iter) ix.sym = ren[ix.sym];
+    add_out(fo.set->tn, canon);
+    em.set_redirect[fo.set->tn] = {fo.set->idcs, outs.back().arr + "[b200_j]"};
+    body += aliases + em.stmt(*fo.set, 6);
+    aliases.clear();
+    produced.insert(fo.set->tn);
+    ++fused;
+  }
+  *n_fused = fused;
 
   std::ostringstream fn;
   // parameters of the epilogue: the nodes it touches (+ static table)
@@ -323,7 +441,8 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
   std::vector<KArg> kargs;
   for (auto& t : P.tnodes) {
     if (!em.used_nodes.count(t.id) || t.mode == Mode::Virtual) continue;
-    const bool written = t.id == set.tn;
+    bool written = false;
+    for (auto& o : outs) written |= o.tn == t.id;
     params += std::string(", ") + (written ? "" : "const ") + Emitter::ctype(t.prec) + "* " + (written ? "" : "__restrict__ ") + t.ident;
     args += ", " + t.ident;
     kargs.push_back({KArg::Node, t.id});
@@ -367,12 +486,55 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
     ep.str("");
   }
   fn << unit_syms;
+  for (auto& o : outs) fn << "  " << Emitter::ctype(P.tn(o.tn).prec) << " " << o.arr << "[B200_EPI_CHUNK];\n";
   fn << "#pragma unroll\n  for (int b200_j = 0; b200_j < B200_EPI_CHUNK; ++b200_j) {\n"
      << "    const unsigned int b200_n = b200_n0 + (unsigned int)b200_j;\n"
      << "    if (b200_n < b200_N) {\n"
      << "      const float b200_acc = __uint_as_float(b200_r[b200_j]);\n";
   recover(dn, "b200_n");
-  fn << ep.str() << body << "    }\n  }\n}\n";
+  fn << ep.str() << body << "    }\n  }\n";
+  // ---- store the register tiles: 16-byte vector stores when the chunk is whole, contiguous
+  //      and aligned; element stores (guarded) otherwise
+  for (auto& o : outs) {
+    const Tnode& t = P.tn(o.tn);
+    const int ebytes = prec_bytes(t.prec);
+    const bool vec = o.unit_n && (ebytes == 4 || ebytes == 2);
+    if (o.unit_n) {
+      fn << "  {\n    " << Emitter::ctype(t.prec) << "* b200_p = " << t.ident << " + (" << o.row_off << ") + b200_n0;\n";
+      if (vec) {
+        fn << "    if (b200_n0 + B200_EPI_CHUNK <= b200_N && (((unsigned long long)b200_p) & 15ull) == 0ull) {\n";
+        if (ebytes == 4) {
+          fn << "#pragma unroll\n      for (int b200_v = 0; b200_v < B200_EPI_CHUNK / 4; ++b200_v) {\n"
+             << "        uint4 b200_q;\n"
+             << "        b200_q.x = b200_bits32(" << o.arr << "[4 * b200_v]); b200_q.y = b200_bits32(" << o.arr << "[4 * b200_v + 1]);\n"
+             << "        b200_q.z = b200_bits32(" << o.arr << "[4 * b200_v + 2]); b200_q.w = b200_bits32(" << o.arr << "[4 * b200_v + 3]);\n"
+             << "        ((uint4*)b200_p)[b200_v] = b200_q;\n      }\n";
+        } else {
+          fn << "#pragma unroll\n      for (int b200_v = 0; b200_v < B200_EPI_CHUNK / 8; ++b200_v) {\n"
+             << "        uint4 b200_q;\n"
+             << "        b200_q.x = (unsigned int)" << o.arr << "[8 * b200_v] | ((unsigned int)" << o.arr << "[8 * b200_v + 1] << 16);\n"
+             << "        b200_q.y = (unsigned int)" << o.arr << "[8 * b200_v + 2] | ((unsigned int)" << o.arr << "[8 * b200_v + 3] << 16);\n"
+             << "        b200_q.z = (unsigned int)" << o.arr << "[8 * b200_v + 4] | ((unsigned int)" << o.arr << "[8 * b200_v + 5] << 16);\n"
+             << "        b200_q.w = (unsigned int)" << o.arr << "[8 * b200_v + 6] | ((unsigned int)" << o.arr << "[8 * b200_v + 7] << 16);\n"
+             << "        ((uint4*)b200_p)[b200_v] = b200_q;\n      }\n";
+        }
+        fn << "    } else {\n";
+      } else {
+        fn << "    {\n";
+      }
+      fn << "#pragma unroll\n      for (int b200_j = 0; b200_j < B200_EPI_CHUNK; ++b200_j)\n"
+         << "        if (b200_n0 + (unsigned int)b200_j < b200_N) b200_p[b200_j] = " << o.arr << "[b200_j];\n"
+         << "    }\n  }\n";
+    } else {
+      // general position: recompute the offset per column
+      fn << "#pragma unroll\n  for (int b200_j = 0; b200_j < B200_EPI_CHUNK; ++b200_j) {\n"
+         << "    const unsigned int b200_n = b200_n0 + (unsigned int)b200_j;\n    if (b200_n < b200_N) {\n";
+      ep.str("");
+      recover(dn, "b200_n");
+      fn << ep.str() << "      " << t.ident << "[" << em.offset(o.idcs, t.dims) << "] = " << o.arr << "[b200_j];\n    }\n  }\n";
+    }
+  }
+  fn << "}\n";
 
   out->kind = Stage::Gemm;
   out->gemm = g;

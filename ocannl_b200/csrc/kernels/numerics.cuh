@@ -34,6 +34,20 @@ __device__ __forceinline__ unsigned short b200_f2h(float f) {
   return h;
 }
 
+__device__ __forceinline__ float b200_pow2(float x) { return x * x; }
+__device__ __forceinline__ float b200_pow3(float x) { return x * x * x; }
+__device__ __forceinline__ double b200_pow2(double x) { return x * x; }
+__device__ __forceinline__ double b200_pow3(double x) { return x * x * x; }
+__device__ __forceinline__ float b200_tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ b200_u32 b200_bits32(float f) { return __float_as_uint(f); }
+__device__ __forceinline__ b200_u32 b200_bits32(b200_u32 u) { return u; }
+__device__ __forceinline__ b200_u32 b200_bits32(int i) { return (b200_u32)i; }
+
 struct b200_u4x32 {
   b200_u32 v[4];
 };
@@ -101,5 +115,25 @@ __device__ __forceinline__ double b200_warp_sum(double v) {
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
+
+// ---- block-level combine (one block per output element).  `sh` holds one slot per warp;
+//      every thread of the block calls these together and every thread gets the result.
+#define B200_BLOCK_REDUCE(NAME, T, WARP_FN, NEUTRAL)                              \
+  __device__ __forceinline__ T NAME(T v, double* sh_raw) {                        \
+    T* sh = (T*)sh_raw;                                                           \
+    const unsigned int lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;         \
+    const unsigned int nwarps = (blockDim.x + 31u) >> 5;                          \
+    v = WARP_FN(v);                                                               \
+    __syncthreads();                                                              \
+    if (lane == 0) sh[warp] = v;                                                  \
+    __syncthreads();                                                              \
+    T r = lane < nwarps ? sh[lane] : (T)(NEUTRAL);                                \
+    r = WARP_FN(r);                                                               \
+    return r;                                                                     \
+  }
+B200_BLOCK_REDUCE(b200_block_sum, float, b200_warp_sum, 0.0f)
+B200_BLOCK_REDUCE(b200_block_max, float, b200_warp_max, -B200_INF)
+B200_BLOCK_REDUCE(b200_block_min, float, b200_warp_min, B200_INF)
+B200_BLOCK_REDUCE(b200_block_sum, double, b200_warp_sum, 0.0)
 
 #endif  // B200_NUMERICS_CUH
