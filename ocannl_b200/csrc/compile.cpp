@@ -120,6 +120,7 @@ void collect_scopes(const Stmt& s, std::set<std::pair<int, int>>& declared, std:
 struct CoopInfo {
   std::string sym;
   int width = 32;  // threads cooperating on one output element
+  int grid_blocks = 0;  // >0: two-kernel grid-wide reduction with this many blocks in pass 1
   std::vector<std::pair<int, std::string>> scopes;  // (scope id, combine op)
 };
 
@@ -289,7 +290,117 @@ struct Builder {
     ci.sym = "*";
     // few outputs and a long reduction: a whole block per output element
     ci.width = (par_total <= 256 && extent >= 4096) ? 1024 : 32;
+    // a single output fed by a very long reduction: many blocks write partial results to
+    // scratch and a second, single-block kernel combines them
+    if (par_total == 1 && extent >= 32768) {
+      ci.width = 1024;
+      ci.grid_blocks = (int)std::min<int64_t>(296, (extent + 4095) / 4096);
+    }
     return ci;
+  }
+
+  // Grid-wide reduction of a single output element in two kernels.  Pass 1: every block
+  // reduces a strided slice of each Local_scope's flattened loop space and writes one partial
+  // per scope to scratch[scope_index * blocks + block].  Pass 2: one block combines the
+  // partials in block order (a fixed order: the result does not depend on scheduling) and
+  // evaluates the assignment.
+  void grid_reduce_stage(const StmtP& body, const CoopInfo& ci) {
+    const Stmt& set = *body;
+    const Tnode& t = code.prog.tn(set.tn);
+    const int G = ci.grid_blocks;
+    const size_t scratch_off = code.reduce_scratch_bytes;
+    code.reduce_scratch_bytes += (size_t)G * ci.scopes.size() * 8;
+    code.reduce_scratch_bytes = (code.reduce_scratch_bytes + 255) & ~(size_t)255;
+
+    Stage a, b;
+    a.kind = b.kind = Stage::Generic;
+    a.kernel = kernel_name();
+    b.kernel = a.kernel + "_combine";
+    a.total = b.total = 1;
+    a.block = 1024;
+    a.coop = 1024;
+    a.grid_override = G;
+    b.block = 256;
+    b.coop = 256;
+    b.grid_override = 1;
+
+    Emitter ea(code.prog), eb(code.prog);
+    ea.large_models = eb.large_models = opt.large_models;
+    std::string pass1, pass2;
+    int si = 0;
+    std::function<void(const Scalar&)> rec = [&](const Scalar& e) {
+      if (e.kind == Scalar::LocalScope) {
+        std::string op;
+        for (auto& s : ci.scopes)
+          if (s.first == e.scope_id) op = s.second;
+        Prec p = code.prog.tn(e.tn).prec;
+        const Stmt& sb = *e.body;
+        const Stmt* loop = sb.kind == Stmt::For ? &sb : sb.items[1].get();
+        std::vector<LoopDim> red;
+        const Stmt* inner = loop;
+        while (inner->kind == Stmt::For) {
+          red.push_back({inner->index, inner->from, inner->to});
+          inner = inner->body.get();
+        }
+        int64_t total = 1;
+        for (auto& d : red) total *= d.extent();
+        const std::string name = ea.scope_name(e.scope_id, e.tn);
+        const std::string T = Emitter::ctype(p);
+        const double neutral = op == "add" ? 0.0 : (op == "max" ? -INFINITY : INFINITY);
+        const std::string fn = op == "add" ? "sum" : op;
+        const std::string slot = "((" + T + "*)(b200_partials + " + std::to_string((size_t)si * G * 8) + "))";
+        pass1 += "  {\n    " + T + " " + name + " = " + ea.constant(neutral, p) + ";\n";
+        pass1 += "    for (unsigned long long b200_l = (unsigned long long)blockIdx.x * 1024ull + threadIdx.x; b200_l < " +
+                 std::to_string(total) + "ull; b200_l += (unsigned long long)gridDim.x * 1024ull) {\n";
+        std::string rem = "b200_l";
+        for (size_t i = red.size(); i-- > 0;) {
+          const LoopDim& d = red[i];
+          std::string ext = std::to_string(d.extent()) + "ull";
+          std::string val = i == 0 ? rem : "(" + rem + " % " + ext + ")";
+          pass1 += "      const unsigned int " + d.sym + " = (unsigned int)" + val +
+                   (d.from ? " + " + std::to_string(d.from) : std::string()) + ";\n";
+          if (i != 0) {
+            std::string nr = "b200_q" + std::to_string(i);
+            pass1 += "      const unsigned long long " + nr + " = " + rem + " / " + ext + ";\n";
+            rem = nr;
+          }
+        }
+        pass1 += ea.stmt(*inner, 6);
+        pass1 += "    }\n    " + name + " = b200_block_" + fn + "(" + name + ", b200_red);\n";
+        pass1 += "    if (threadIdx.x == 0) " + slot + "[blockIdx.x] = " + name + ";\n  }\n";
+        // pass 2: fixed-order combine of the partials
+        pass2 += "  " + T + " " + name + " = " + eb.constant(neutral, p) + ";\n";
+        pass2 += "  for (unsigned int b200_i = threadIdx.x; b200_i < " + std::to_string(G) + "u; b200_i += blockDim.x) " + name + " = ";
+        if (op == "add") pass2 += name + " + " + slot + "[b200_i];\n";
+        else pass2 += std::string(p == Prec::Double ? "f" : "f") + op + (p == Prec::Double ? "(" : "f(") + name + ", " + slot + "[b200_i]);\n";
+        pass2 += "  " + name + " = b200_block_" + fn + "(" + name + ", b200_red);\n";
+        eb.scope_subst[e.scope_id] = name;
+        ++si;
+        return;
+      }
+      for (auto& x : e.args) rec(*x.s);
+    };
+    rec(*set.value);
+    Emitter::Res v = eb.scalar(t.prec, *set.value);
+    eb.used_nodes.insert(set.tn);
+    pass2 += "  if (threadIdx.x == 0) " + t.ident + "[" + eb.offset(set.idcs, t.dims) + "] = " + v.expr + ";\n";
+
+    std::set<int> none, written = {set.tn};
+    std::ostringstream ka, kb;
+    std::string sa = static_prologue(pass1, ea, 2), sb2 = static_prologue(pass2, eb, 2);
+    ka << "extern \"C\" __global__ void __launch_bounds__(1024) " << a.kernel << "(";
+    emit_params(ka, a, ea, none);
+    ka << (a.args.empty() ? "" : ", ") << "unsigned char* b200_partials) {\n  __shared__ double b200_red[32];\n" << sa << pass1 << "}\n\n";
+    a.args.push_back({KArg::Scratch, (int)scratch_off});
+    kb << "extern \"C\" __global__ void __launch_bounds__(256) " << b.kernel << "(";
+    emit_params(kb, b, eb, written);
+    kb << (b.args.empty() ? "" : ", ") << "const unsigned char* b200_partials) {\n  __shared__ double b200_red[32];\n" << sb2 << pass2 << "}\n\n";
+    b.args.push_back({KArg::Scratch, (int)scratch_off});
+    src << ka.str() << kb.str();
+    a.note = "grid-wide reduction, pass 1 (" + std::to_string(G) + " blocks)";
+    b.note = "grid-wide reduction, pass 2 (combine)";
+    code.stages.push_back(a);
+    code.stages.push_back(b);
   }
 
   void generic_stage(const std::vector<LoopDim>& nest, const StmtP& body) {
@@ -310,6 +421,11 @@ struct Builder {
 
     CoopInfo ci;
     if (st.ser.empty() && st.total > 0) ci = find_coop(*body, st.total);
+    if (ci.grid_blocks > 0) {
+      --next_kernel;  // the name reserved above is re-issued to the first pass
+      grid_reduce_stage(body, ci);
+      return;
+    }
     std::set<int> written;
     walk_stmt(*body, [](const Scalar&) {}, [&](const Stmt& s) {
       if (s.kind == Stmt::Set || s.kind == Stmt::ZeroOut) written.insert(s.tn);

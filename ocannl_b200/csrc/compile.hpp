@@ -19,8 +19,8 @@ struct LoopDim {
 // One kernel argument: a tensor node pointer (in-context node, or a routine-local node that
 // lives in the routine's scratch slab), the static-index table, or the merge buffer.
 struct KArg {
-  enum Kind { Node, Statics, Merge } kind;
-  int tn = -1;
+  enum Kind { Node, Statics, Merge, Scratch } kind;
+  int tn = -1;  // node id; for Scratch: byte offset into the routine's reduction scratch
 };
 
 // A dense contraction recognised in the loop nest, in GEMM terms:
@@ -51,6 +51,7 @@ struct Stage {
   int64_t total = 1;             // parallel iterations
   int block = 256;
   int coop = 0;                  // >0: lanes cooperating on one output element (row reductions)
+  int grid_override = 0;         // >0: launch exactly this many blocks (first pass of a grid-wide reduction)
   GemmPlan gemm;
   std::string gemm_source;       // full translation unit of this stage's contraction kernel
   std::string epi_params, epi_args;  // epilogue plumbing: extra kernel parameters / call arguments
@@ -70,6 +71,7 @@ struct Code {
   std::vector<Stage> stages;
   std::string source;            // one translation unit holding every generic kernel
   std::vector<int> local_nodes;  // routine-local nodes that need scratch
+  size_t reduce_scratch_bytes = 0;  // partial results of grid-wide reductions
   std::string describe() const;  // JSON-ish summary for b200_code_info
 };
 

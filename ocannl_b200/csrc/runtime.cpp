@@ -50,6 +50,8 @@ void b200_routine::link(b200_dev* d, b200_code* c, const b200_binding* b, int n)
     if (t.zero_init) scratch_zero.push_back({off, (size_t)t.bytes()});
     off += ((size_t)t.bytes() + 255) & ~(size_t)255;
   }
+  const size_t reduce_off = off;
+  off += c->code.reduce_scratch_bytes;
   scratch_bytes = off;
   if (scratch_bytes) cu_check(cu().cuMemAlloc_(&scratch, scratch_bytes), "cuMemAlloc(scratch)");
 
@@ -90,6 +92,8 @@ void b200_routine::link(b200_dev* d, b200_code* c, const b200_binding* b, int n)
         arg_values[i].push_back(it->second);
       } else if (a.kind == KArg::Statics) {
         arg_values[i].push_back(statics_dev);
+      } else if (a.kind == KArg::Scratch) {
+        arg_values[i].push_back(scratch + reduce_off + (size_t)a.tn);
       } else {
         arg_values[i].push_back(0);  // merge buffer: resolved at launch (pool 0 may be re-allocated)
       }
@@ -149,6 +153,7 @@ void b200_routine::enqueue_stages() {
     long long cap = (long long)dev->sm_count * 16;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
+    if (st.grid_override > 0) blocks = st.grid_override;
     cu_check(cu().cuLaunchKernel_(fns[i], (unsigned)blocks, 1, 1, (unsigned)st.block, 1, 1, 0, dev->stream, args.data(),
                                   nullptr),
              "cuLaunchKernel");
