@@ -125,6 +125,17 @@ int b200_comm_init_rank(b200_dev* dev, int n_ranks, int rank, const char* id128,
 int b200_allreduce(b200_comm* comm, int pool_id, size_t offset, size_t count, int dtype, int op);
 int b200_comm_free(b200_comm* comm);
 
+/* ---- allocation-free reduction.  No counterpart in the reference: added for callers that may
+ *      not reach the device allocator while they run (inside a stream capture, in a serving
+ *      loop that cannot afford cudaMalloc's implicit synchronisation, or under a memory budget
+ *      that was handed out up front).  Writes sum(in[0..count)) as one float at the output
+ *      location, in stream order on the device's stream, with its scratch in a 4 KiB array that
+ *      is part of the library's device image.  count <= 2^26, else B200_E_NO_SPACE.  The first
+ *      call on a device resolves the array's address: make it before any stream capture.
+ *      Calls that overlap on the GPU race on the shared array; stream-ordered calls do not. */
+int b200_sum_f32_static(b200_dev* dev, int in_pool, size_t in_offset, size_t count, int out_pool,
+                        size_t out_offset);
+
 #ifdef __cplusplus
 }
 #endif

@@ -162,6 +162,14 @@ class Device:
         check(lib().b200_stream_handle(self.h, ctypes.byref(s)))
         return s.value
 
+    def sum_f32_static(self, in_pool: int, in_offset: int, count: int, out_pool: int, out_offset: int):
+        """Sum of `count` floats, written as one float, without any allocation at call time
+        (scratch is a fixed 4 KiB array inside the library's device image; count <= 2**26).
+        For callers that must not touch the device allocator while running; calls that overlap
+        on the GPU share that array and race, stream-ordered calls are safe."""
+        check(lib().b200_sum_f32_static(self.h, ctypes.c_int(in_pool), ctypes.c_size_t(in_offset),
+                                        ctypes.c_size_t(count), ctypes.c_int(out_pool), ctypes.c_size_t(out_offset)))
+
     def get_used_memory(self) -> int:
         n = ctypes.c_size_t(0)
         check(lib().b200_used_memory(self.h, ctypes.byref(n)))

@@ -23,6 +23,7 @@ CUDA = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
 HOST_SOURCES = ["ir.cpp", "emit.cpp", "compile.cpp", "gemm_match.cpp", "driver.cpp", "runtime.cpp",
                 "gemm_launch.cpp", "api.cpp"]
+CUDA_SOURCES = ["sum_static.cu"]
 EMBED = {"kNumericsSource": "kernels/numerics.cuh", "kGemmSource": "kernels/gemm_sm100.cuh"}
 
 
@@ -66,8 +67,20 @@ def build_library(verbose=False) -> str:
                 print(" ".join(cmd))
             subprocess.run(cmd, check=True)
         objs.append(o)
+    # translation units that hold ahead-of-time kernels: nvcc, sm_100a only
+    for s in CUDA_SOURCES:
+        src = os.path.join(CSRC, s)
+        o = os.path.join(OUT, s[:-3] + ".o")
+        if _newer(o, [src] + hdrs):
+            cmd = [os.path.join(CUDA, "bin", "nvcc"), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+                   "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-I", CSRC, "-c", src, "-o", o]
+            if verbose:
+                print(" ".join(cmd))
+            subprocess.run(cmd, check=True)
+        objs.append(o)
     if _newer(LIB, objs):
-        cmd = ["g++", "-shared", "-o", LIB] + objs + ["-ldl", "-lpthread"]
+        cmd = ["g++", "-shared", "-o", LIB] + objs + ["-L", os.path.join(CUDA, "lib64"), "-lcudart_static", "-lrt",
+                                                       "-ldl", "-lpthread"]
         if verbose:
             print(" ".join(cmd))
         subprocess.run(cmd, check=True)

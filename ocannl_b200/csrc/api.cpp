@@ -14,7 +14,9 @@
 
 using namespace b200;
 
-static thread_local std::string g_last_error;
+// thread-local message of the last failure; other translation units of the library set it too
+thread_local std::string b200_error_slot;
+#define g_last_error b200_error_slot
 
 const char* b200_last_error(void) { return g_last_error.c_str(); }
 const char* b200_version(void) { return "b200-arrayjit 0.1 (sm_100a)"; }
