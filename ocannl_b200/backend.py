@@ -246,6 +246,23 @@ class Context:
         self.device = device
         self.arrays: Dict[str, Tuple[int, int, Tnode]] = dict(arrays or {})   # ident -> (pool, offset, tn)
 
+    def allocate(self, tnodes: Sequence[Tnode]) -> "Context":
+        """Child context that also holds `tnodes`, packed back to back in one new zeroed pool
+        (how the data-parallel driver keeps all gradients in one contiguous range)."""
+        new = [t for t in tnodes if t.ident not in self.arrays]
+        arrays = dict(self.arrays)
+        if new:
+            offs, total = [], 0
+            for t in new:
+                total = (total + 255) // 256 * 256
+                offs.append(total)
+                total += t.size_in_bytes
+            pool = self.device.alloc_pool(max(total, 1))
+            self.device.memset_zero(pool, 0, max(total, 1))
+            for t, o in zip(new, offs):
+                arrays[t.ident] = (pool, o, t)
+        return Context(self.device, arrays)
+
     def link(self, code: Code) -> "Routine":
         dev = self.device
         new: List[Tnode] = [t for t in code.ir.params() if t.ident not in self.arrays]

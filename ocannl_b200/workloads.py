@@ -417,3 +417,32 @@ def mlp_forward(rows=8192, dims=(784, 1024, 1024, 10), wprec="bfloat16", with_lo
     body.append(Comment("end"))
     r.body = Seq(body)
     return r
+
+
+# ------------------------------------------------------------------ data-parallel regression step
+def linreg_update(batch: int) -> Routine:
+    """`Train.grad_update` of the sum-over-batch squared error ((w *. x) - y)^2 of
+    test/training/data_parallel.ml:44-51: forward, zero grads, backprop.  `w` has one element."""
+    r = Routine("linreg_update_%d" % batch)
+    x = r.tn("x", "single", [batch, 1], read_only=True)
+    y = r.tn("y", "single", [batch, 1], read_only=True)
+    w = r.tn("w", "single", [1])
+    g = r.tn("w_grad", "single", [1])
+    loss = r.tn("loss", "single", [1])
+    b = r.sym()
+    diff = lambda bb: (w[0] * x[bb, 0]) - y[bb, 0]
+    fwd = Set(loss, (0,), reduce_scope(r, "n_sq", "single", [(b, batch)], lambda: diff(b) * diff(b), op="add"))
+    b2 = r.sym()
+    bwd = loops([(b2, batch)], Set(g, (0,), g[0] + ((diff(b2) * x[b2, 0]) + (diff(b2) * x[b2, 0]))))
+    r.body = Seq([Comment("loss forward and gradient update"), fwd, ZeroOut(g), bwd, Comment("end")])
+    return r
+
+
+def linreg_sgd() -> Routine:
+    """`Train.sgd_update` without momentum or weight decay (lib/train.ml:76-90): w =- lr * w.grad."""
+    r = Routine("linreg_sgd")
+    w = r.tn("w", "single", [1])
+    g = r.tn("w_grad", "single", [1], read_only=True)
+    lr = r.tn("learning_rate", "single", [1], read_only=True)
+    r.body = Seq([Comment("w param sgd step"), Set(w, (0,), w[0] - lr[0] * g[0]), Comment("end")])
+    return r
