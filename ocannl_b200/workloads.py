@@ -446,3 +446,148 @@ def linreg_sgd() -> Routine:
     lr = r.tn("learning_rate", "single", [1], read_only=True)
     r.body = Seq([Comment("w param sgd step"), Set(w, (0,), w[0] - lr[0] * g[0]), Comment("end")])
     return r
+
+
+# ------------------------------------------------------------------ config 4: decoder-only transformer forward
+def transformer_params(layers=6, d_model=512, heads=8, d_head=64, d_ff=2048, vocab=27, seed=10, wprec="bfloat16"):
+    """Xavier-normal weights (sigma = sqrt(2/(fan_in+fan_out))), gamma = 1, beta = 0, zero biases
+    except the FFN bias which is drawn like the weights."""
+    rng = np.random.default_rng(seed)
+
+    def xavier(shape, fan_in, fan_out):
+        return store(wprec, (rng.standard_normal(shape) * math.sqrt(2.0 / (fan_in + fan_out))).astype(np.float32))
+
+    P = {"tok_embed": xavier((d_model, vocab), vocab, d_model), "pos": xavier((d_model,), 1, d_model),
+         "w_head": xavier((vocab, d_model), d_model, vocab)}
+    for l in range(layers):
+        p = "l%d_" % l
+        for n in ("w_q", "w_k", "w_v"):
+            P[p + n] = xavier((heads, d_head, d_model), d_model, heads * d_head)
+        P[p + "w_o"] = xavier((d_model, heads, d_head), heads * d_head, d_model)
+        P[p + "ffn_w"] = xavier((d_ff, d_model), d_model, d_ff)
+        P[p + "ffn_b"] = xavier((d_ff,), d_model, d_ff)
+        P[p + "ffn_w_out"] = xavier((d_model, d_ff), d_ff, d_model)
+        for ln in ("ln1_", "ln2_"):
+            P[p + ln + "gamma"] = np.ones(d_model, np.float32)
+            P[p + ln + "beta"] = np.zeros(d_model, np.float32)
+    return P
+
+
+def transformer_inputs(batch=64, seq=256, vocab=27, seed=9):
+    tok = np.random.default_rng(seed).integers(0, vocab, (batch, seq))
+    onehot = np.zeros((batch, seq, vocab), np.float32)
+    onehot[np.arange(batch)[:, None], np.arange(seq)[None, :], tok] = 1.0
+    mask = (np.arange(seq)[:, None] >= np.arange(seq)[None, :]).astype(np.float32)   # s >= t
+    return {"tokens": store("bfloat16", onehot), "mask": mask}
+
+
+def transformer_forward(batch=64, seq=256, layers=6, d_model=512, heads=8, d_head=64, d_ff=2048, vocab=27,
+                        wprec="bfloat16", act="gelu", eps=1e-5) -> Routine:
+    """Forward of `Nn_blocks.decoder_only` (lib/nn_blocks.ml:274-296): per layer masked
+    multi-head attention (:209-236: q/k/v projections, scores `s | h d ; t | h d => s | t -> h`
+    scaled by 1/sqrt(d), `where mask scores -1e9`, softmax over t as in :137-143, `attn +* v`,
+    `w_o`), residual, layer_norm as written in :251-258 (`(x - sum_d x) / d`, summed squares),
+    FFN (`mlp` with one hidden layer, :119-126), residual, layer_norm; then a linear head.
+    bf16 weights and activations, fp32 accumulators, fp32 softmax and layer-norm statistics."""
+    r = Routine("decoder_fwd_b%d_s%d_l%d" % (batch, seq, layers))
+    B, S, D, H, E, F, V = batch, seq, d_model, heads, d_head, d_ff, vocab
+    P = wprec
+    tokens = r.tn("tokens", P, [B, S, V], read_only=True)
+    mask = r.tn("mask", "single", [S, S], read_only=True)
+    tok_embed = r.tn("tok_embed", P, [D, V], read_only=True)
+    pos = r.tn("pos", P, [D], read_only=True)
+    body: List = [Comment("logits fwd")]
+    x = r.tn("x0", P, [B, S, D])
+    b, s, d, v = r.syms(4)
+    body.append(loops([(b, B), (s, S), (d, D)], Set(x, (b, s, d), reduce_scope(
+        r, "n_emb", "single", [(v, V)], lambda: (tok_embed[d, v], tokens[b, s, v]), orig=(b, s, d)) + pos[d])))
+
+    def layer_norm(pref, src, out):
+        ssum = r.tn(pref + "sum", "single", [B, S, 1])
+        cen = r.tn(pref + "centered", "single", [B, S, D])
+        std = r.tn(pref + "std", "single", [B, S, 1])
+        gamma = r.tn(pref + "gamma", "single", [D], read_only=True)
+        beta = r.tn(pref + "beta", "single", [D], read_only=True)
+        bb, ss, dd = r.syms(3)
+        body.append(loops([(bb, B), (ss, S)], Set(ssum, (bb, ss, 0), reduce_scope(
+            r, pref + "n_sum", "single", [(dd, D)], lambda: src[bb, ss, dd], op="add"))))
+        bb, ss, dd = r.syms(3)
+        body.append(loops([(bb, B), (ss, S), (dd, D)], Set(cen, (bb, ss, dd), (src[bb, ss, dd] - ssum[bb, ss, 0]) / float(D))))
+        bb, ss, dd = r.syms(3)
+        body.append(loops([(bb, B), (ss, S)], Set(std, (bb, ss, 0), un("sqrt", reduce_scope(
+            r, pref + "n_var", "single", [(dd, D)], lambda: cen[bb, ss, dd] * cen[bb, ss, dd], op="add") + eps))))
+        bb, ss, dd = r.syms(3)
+        body.append(loops([(bb, B), (ss, S), (dd, D)], Set(out, (bb, ss, dd),
+                                                            (gamma[dd] * (cen[bb, ss, dd] / std[bb, ss, 0])) + beta[dd])))
+
+    for l in range(layers):
+        p = "l%d_" % l
+        wq, wk, wv = (r.tn(p + n, P, [H, E, D], read_only=True) for n in ("w_q", "w_k", "w_v"))
+        wo = r.tn(p + "w_o", P, [D, H, E], read_only=True)
+        q, k, vv = (r.tn(p + n, P, [B, S, H, E]) for n in ("q", "k", "v"))
+        for w, out in ((wq, q), (wk, k), (wv, vv)):
+            b, s, h, e, i = r.syms(5)
+            xin = x
+            body.append(loops([(b, B), (s, S), (h, H), (e, E)], Set(out, (b, s, h, e), reduce_scope(
+                r, out.ident + "_mm", "single", [(i, D)], lambda: (w[h, e, i], xin[b, s, i]), orig=(b, s, h, e)))))
+        scores = r.tn(p + "scores", "single", [B, S, H, S])
+        b, s, h, t, e = r.syms(5)
+        body.append(loops([(b, B), (s, S), (h, H), (t, S)], Set(scores, (b, s, h, t), where(
+            mask[s, t],
+            reduce_scope(r, p + "qk", "single", [(e, E)], lambda: (q[b, s, h, e], k[b, t, h, e]), orig=(b, s, h, t))
+            / math.sqrt(E), Const(-1e9)))))
+        mx = r.tn(p + "max", "single", [B, S, H, 1])
+        b, s, h, t = r.syms(4)
+        body.append(loops([(b, B), (s, S), (h, H)], Set(mx, (b, s, h, 0), reduce_scope(
+            r, p + "n_max", "single", [(t, S)], lambda: scores[b, s, h, t], op="max"))))
+        ex = r.tn(p + "exp_vals", "single", [B, S, H, S])
+        b, s, h, t = r.syms(4)
+        body.append(loops([(b, B), (s, S), (h, H), (t, S)], Set(ex, (b, s, h, t), un("exp", scores[b, s, h, t] - mx[b, s, h, 0]))))
+        sm = r.tn(p + "sum_exp", "single", [B, S, H, 1])
+        b, s, h, t = r.syms(4)
+        body.append(loops([(b, B), (s, S), (h, H)], Set(sm, (b, s, h, 0), reduce_scope(
+            r, p + "n_sumexp", "single", [(t, S)], lambda: ex[b, s, h, t], op="add"))))
+        attn = r.tn(p + "attn", P, [B, S, H, S])
+        b, s, h, t = r.syms(4)
+        body.append(loops([(b, B), (s, S), (h, H), (t, S)], Set(attn, (b, s, h, t), ex[b, s, h, t] / sm[b, s, h, 0])))
+        av = r.tn(p + "av", P, [B, S, H, E])
+        b, s, h, e, t = r.syms(5)
+        body.append(loops([(b, B), (s, S), (h, H), (e, E)], Set(av, (b, s, h, e), reduce_scope(
+            r, p + "n_av", "single", [(t, S)], lambda: (attn[b, s, h, t], vv[b, t, h, e]), orig=(b, s, h, e)))))
+        r1 = r.tn(p + "res1", P, [B, S, D])
+        b, s, o, h, e = r.syms(5)
+        xin = x
+        body.append(loops([(b, B), (s, S), (o, D)], Set(r1, (b, s, o), xin[b, s, o] + reduce_scope(
+            r, p + "n_wo", "single", [(h, H), (e, E)], lambda: (wo[o, h, e], av[b, s, h, e]), orig=(b, s, o)))))
+        x1 = r.tn(p + "x1", P, [B, S, D])
+        layer_norm(p + "ln1_", r1, x1)
+        fw = r.tn(p + "ffn_w", P, [F, D], read_only=True)
+        fb = r.tn(p + "ffn_b", P, [F], read_only=True)
+        fwo = r.tn(p + "ffn_w_out", P, [D, F], read_only=True)
+        hid = r.tn(p + "ffn_h", P, [B, S, F])
+        b, s, j, i = r.syms(4)
+        pre = lambda: reduce_scope(r, p + "n_ffn", "single", [(i, D)], lambda: (fw[j, i], x1[b, s, i]), orig=(b, s, j)) + fb[j]
+        if act == "relu":
+            body.append(loops([(b, B), (s, S), (j, F)], Set(hid, (b, s, j), un("relu", pre()))))
+        else:
+            # the pre-activation is read three times by the composed GELU: materialised
+            z = r.tn(p + "ffn_z", "single", [B, S, F])
+            body.append(loops([(b, B), (s, S), (j, F)], Set(z, (b, s, j), pre())))
+            b2, s2, j2 = r.syms(3)
+            body.append(loops([(b2, B), (s2, S), (j2, F)], Set(hid, (b2, s2, j2), gelu_tanh(z[b2, s2, j2]))))
+        r2 = r.tn(p + "res2", P, [B, S, D])
+        b, s, o, j = r.syms(4)
+        body.append(loops([(b, B), (s, S), (o, D)], Set(r2, (b, s, o), x1[b, s, o] + reduce_scope(
+            r, p + "n_ffo", "single", [(j, F)], lambda: (fwo[o, j], hid[b, s, j]), orig=(b, s, o)))))
+        x2 = r.tn(p + "x2", P, [B, S, D])
+        layer_norm(p + "ln2_", r2, x2)
+        x = x2
+    w_head = r.tn("w_head", P, [V, D], read_only=True)
+    logits = r.tn("logits", "single", [B, S, V])
+    b, s, v, d = r.syms(4)
+    xin = x
+    body.append(loops([(b, B), (s, S), (v, V)], Set(logits, (b, s, v), reduce_scope(
+        r, "n_head", "single", [(d, D)], lambda: (w_head[v, d], xin[b, s, d]), orig=(b, s, v)))))
+    body.append(Comment("end"))
+    r.body = Seq(body)
+    return r

@@ -110,3 +110,22 @@ def test_mlp_forward_bf16(device, rows):
     kinds = [s["kind"] for s in info["stages"]]
     assert kinds[:2] == ["gemm", "gemm"], info
     compare(ir, got, want, rtol=2e-2, atol=2e-3)
+
+
+@pytest.mark.parametrize("act", ["gelu", "relu"])
+def test_decoder_only_forward(device, act):
+    """Config 4 at reduced width (2 sequences of 128 tokens, 2 layers, 2 heads of 64, d_model 128):
+    every stage of the decoder block — batched strided q.k^T and attn.v contractions on the
+    tensor-core path, masked softmax, layer norm, residual epilogues — against the cc restatement.
+    The reference's own tests pin only shapes for these blocks, so the oracle is the only pin."""
+    cfg = dict(batch=2, seq=128, layers=2, d_model=128, heads=2, d_head=64, d_ff=256)
+    ir = W.transformer_forward(act=act, **cfg)
+    inputs = dict(W.transformer_params(layers=2, d_model=128, heads=2, d_head=64, d_ff=256),
+                  **W.transformer_inputs(batch=2, seq=128))
+    want = run_oracle(ir, inputs)
+    got, info = run_device(device, ir, inputs)
+    kinds = [s["kind"] for s in info["stages"]]
+    assert kinds.count("gemm") >= 2 * 7, kinds      # q, k, v, q.k^T, attn.v, w_o, ffn, ffn_out per layer
+    gemms = [s for s in info["stages"] if s["kind"] == "gemm"]
+    assert any(s["batch"] == 4 and not s["b_kmajor"] for s in gemms)      # attn.v: (b, h) batch, v is n-major
+    compare(ir, got, want, rtol=2e-2, atol=2e-2)
