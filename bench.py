@@ -180,6 +180,96 @@ def contraction_sweep(dev, pk, sizes=(1024, 4096, 8192)):
     return out
 
 
+def _time_routine(dev, rt, code, runs, pk, statics=None, flush_pool=None):
+    """ms per run with CUDA-graph replay, plus a per-stage breakdown from event-timed runs."""
+    statics = statics or [{}]
+    rt.use_graph(True)
+    for i in range(3):
+        rt.run(**statics[i % len(statics)])
+    dev.await_()
+    total = 0.0
+    for i in range(runs):
+        if flush_pool is not None:
+            dev.memset_zero(flush_pool, 0, 256 << 20)
+        e0 = dev.all_work()
+        rt.run(**statics[i % len(statics)])
+        e1 = dev.all_work()
+        e1.sync()
+        total += e0.elapsed_ms(e1)
+        e0.free()
+        e1.free()
+    rt.profile(True)
+    for i in range(runs):
+        if flush_pool is not None:
+            dev.memset_zero(flush_pool, 0, 256 << 20)
+        rt.run(**statics[i % len(statics)])
+    dev.await_()
+    rt.profile(False)
+    stages = code.info()["stages"]
+    out = []
+    for s, (t, c) in zip(stages, rt.stage_times()):
+        ms = t / c if c else 0.0
+        e = {"kernel": s["kernel"] or "memset", "kind": s["kind"], "ms": round(ms, 5), "bytes": s.get("bytes", 0)}
+        if ms > 0:
+            e["gbs"] = round(s.get("bytes", 0) / ms / 1e6, 1)
+            if s["kind"] == "gemm":
+                e["tflops"] = round(s["flops"] / ms / 1e9, 1)
+        out.append(e)
+    return total / runs, out
+
+
+def other_configs(dev, pk):
+    """Configs 1, 2 and 4 of the baseline, each through compile / link / run with graph replay."""
+    from ocannl_b200 import backend as bk
+    from ocannl_b200 import workloads as W
+    res = {}
+    flush_pool = dev.alloc_pool(256 << 20)
+
+    def run(ir, inputs, runs, statics=None, flush=True):
+        code = bk.Code(ir)
+        rt = bk.Context(dev).link(code)
+        for k, v in inputs.items():
+            rt.context.from_host(k, v)
+        ms, stages = _time_routine(dev, rt, code, runs, pk, statics, flush_pool if flush else None)
+        n_kernels = rt.kernels_per_run()
+        rt.free()
+        code.free()
+        for p in {p for p, _, _ in rt.context.arrays.values()}:
+            dev.free_pool(p)
+        return ms, stages, n_kernels
+
+    # config 1: half-moons MLP, one training step per run (batch 20)
+    x, y = W.moons_inputs()
+    ms, st, nk = run(W.moons_train_step(), dict(W.moons_params(), moons_flat=x, moons_classes=y), 50,
+                     [{"i1": i % 51, "i2": i} for i in range(51)], flush=False)
+    res["moons_train_step"] = {"ms_per_step": ms, "samples_per_s": 20 / (ms / 1e3), "kernels": nk,
+                               "bound": "launch latency"}
+    # config 2: makemore forward, fp32 and bf16 weights
+    ids, onehot = W.makemore_inputs()
+    for wp in ("single", "bfloat16"):
+        inp = {k: W.store(wp, v) for k, v in W.makemore_params().items()}
+        inp.update(input_batch=ids, target_batch=onehot)
+        ms, st, nk = run(W.makemore_forward(wprec=wp), inp, 30)
+        res["makemore_forward_" + wp] = {"ms_per_step": ms, "samples_per_s": 4096 / (ms / 1e3), "kernels": nk,
+                                         "stages": st}
+    # config 4: decoder-only transformer forward, batch 64 x 256 tokens
+    ir = W.transformer_forward()
+    inp = dict(W.transformer_params(), **W.transformer_inputs())
+    ms, st, nk = run(ir, inp, 5)
+    flops = sum(s_["flops"] for s_ in bk.Code(ir).info()["stages"] if s_["kind"] == "gemm")
+    top = sorted(st, key=lambda e: -e["ms"])[:8]
+    gen = [e for e in st if e["kind"] == "generic" and e["ms"] > 0]
+    res["decoder_forward"] = {
+        "ms_per_step": ms, "samples_per_s": 64 / (ms / 1e3), "tokens_per_s": 64 * 256 / (ms / 1e3), "kernels": nk,
+        "contraction_tflops_over_whole_step": flops / ms / 1e9, "top_stages": top,
+        "generic_stage_time_ms": round(sum(e["ms"] for e in gen), 4),
+        "contraction_stage_time_ms": round(sum(e["ms"] for e in st if e["kind"] == "gemm"), 4),
+        "generic_gbs_weighted": round(sum(e["bytes"] for e in gen) / max(sum(e["ms"] for e in gen), 1e-9) / 1e6, 1),
+        "hbm_peak_gbs": pk["hbm"]}
+    dev.free_pool(flush_pool)
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -189,6 +279,7 @@ def main():
     ap.add_argument("--rows", type=int, default=8192, help="rows of the batch each GPU processes per step")
     ap.add_argument("--ref-rows", type=int, default=512)
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-configs", action="store_true", help="skip the configs 1, 2 and 4 section")
     ap.add_argument("--sweep-size", type=int, default=0,
                     help="run only the batch-8 contraction of this M=N=K (a small case for profilers) and exit")
     ap.add_argument("--no-cpu", action="store_true")
@@ -332,6 +423,8 @@ def main():
         line["cpu_baseline"] = cpu_baseline()
     if world == 1 and not args.no_sweep:
         line["contraction_sweep"] = contraction_sweep(dev, pk)
+    if world == 1 and not args.no_configs:
+        line["configs"] = other_configs(dev, pk)
     print(json.dumps(line))
 
 

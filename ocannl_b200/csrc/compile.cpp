@@ -171,6 +171,16 @@ std::string Code::describe() const {
       o << ",\"batch\":" << b << ",\"a_kmajor\":" << (s.gemm.a_kmajor ? 1 : 0) << ",\"b_kmajor\":" << (s.gemm.b_kmajor ? 1 : 0)
         << ",\"accumulate\":" << (s.gemm.accumulate ? 1 : 0) << ",\"flops\":" << s.gemm.flops();
     }
+    if (s.kind != Stage::Memset) {
+      // bytes of every node the stage touches, each counted once: the stage's algorithmic traffic
+      long long bytes = 0;
+      for (auto& a : s.args)
+        if (a.kind == KArg::Node) bytes += prog.tn(a.tn).bytes();
+      if (s.kind == Stage::Gemm) bytes += prog.tn(s.gemm.a_tn).bytes() + prog.tn(s.gemm.b_tn).bytes();
+      o << ",\"bytes\":" << bytes;
+    } else {
+      o << ",\"bytes\":" << prog.tn(s.memset_tn).bytes();
+    }
     o << ",\"note\":\"" << s.note << "\"}";
   }
   o << "]}";

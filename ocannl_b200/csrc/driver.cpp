@@ -3,6 +3,7 @@
 
 #include <dlfcn.h>
 
+#include <cstdio>
 #include <cstdlib>
 #include <map>
 #include <mutex>
@@ -120,6 +121,7 @@ const std::string& compile_cubin(const std::string& source, const std::string& n
     n.nvrtcGetProgramLog_(prog, &log[0]);
   }
   if (log_out) *log_out = log;
+  if (!env("B200_NVRTC_LOG").empty() && !log.empty()) fprintf(stderr, "[b200 nvrtc] %s: %s\n", name.c_str(), log.c_str());
   if (r != NVRTC_SUCCESS) {
     n.nvrtcDestroyProgram_(&prog);
     throw Error((int)r, "NVRTC failed to compile routine '" + name + "': " + n.nvrtcGetErrorString_(r) + "\n" + log);

@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstring>
 
 namespace b200 {
 
@@ -129,7 +130,22 @@ std::string Emitter::constant(double c, Prec prec) {
       if (c < 0) lit = "(" + lit + ")";
     }
     if (prec == Prec::Single) return lit;
-    return std::string(down_fn(prec)) + lit + ")";
+    // 16-bit constants are rounded here, once, instead of per element on the device
+    unsigned int bits16;
+    const float f = (float)c;
+    if (prec == Prec::Bfloat16) {
+      unsigned int u;
+      memcpy(&u, &f, 4);
+      u += 0x7FFFu + ((u >> 16) & 1u);  // arrayjit/lib/builtins.c:620-627
+      bits16 = u >> 16;
+    } else {
+      _Float16 h = (_Float16)f;
+      unsigned short hb;
+      memcpy(&hb, &h, 2);
+      bits16 = hb;
+    }
+    snprintf(buf, sizeof buf, "((unsigned short)0x%04xu)", bits16 & 0xFFFFu);
+    return buf;
   }
   if (prec == Prec::Double) {
     if (std::isinf(c)) return c > 0 ? "((double)B200_INF)" : "(-(double)B200_INF)";
@@ -335,6 +351,11 @@ Emitter::Res Emitter::scalar(Prec prec, const Scalar& e) {
         }
         if (t.mode == Mode::Virtual) throw Error(-3, "b200ir: read of virtual node '" + t.ident + "'");
         used_nodes.insert(e.tn);
+        for (auto& lt : load_tiles)
+          if (lt.tn == e.tn && same_indices(lt.idcs, e.idcs)) {
+            r.expr = cv.first + lt.expr + cv.second;
+            return r;
+          }
       } else {
         uses_merge = true;
       }

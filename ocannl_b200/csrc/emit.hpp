@@ -31,6 +31,13 @@ struct Emitter {
   // (node id) -> lvalue that receives a Set at exactly these indices instead of memory (the
   // register tile of a contraction epilogue; the caller stores the tile afterwards)
   std::map<int, std::pair<Indices, std::string>> set_redirect;
+  // reads that were pre-loaded into a register tile: a Get of `tn` at exactly `idcs` becomes `expr`
+  struct LoadTile {
+    int tn;
+    Indices idcs;
+    std::string expr;
+  };
+  std::vector<LoadTile> load_tiles;
   // nodes whose loads may use the read-only data path
   std::set<int> readonly_nodes;
   // cooperative reductions: scope id -> lane-strided loop symbol (see compile.cpp)

@@ -341,6 +341,75 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
     outs.push_back(o);
   };
 
+  // ---- operands of the epilogue that run along n (bias[n], mask[s, n], a residual x[b, s, n]):
+  //      pre-loaded into a register tile with 16-byte loads, so that the per-column code has no
+  //      dependent global load in it
+  std::string load_code;
+  int n_in_tiles = 0;
+  std::set<int> not_loadable = {set.tn};
+  auto collect_loads = [&](const Scalar& root, const std::map<std::string, std::string>* ren) {
+    std::function<void(const Scalar&)> go = [&](const Scalar& e) {
+      if (e.kind == Scalar::LocalScope) return;
+      if (e.kind == Scalar::Get && !not_loadable.count(e.tn) && !n_sym.empty() && !e.idcs.empty()) {
+        const Tnode& t = P.tn(e.tn);
+        Indices canon = e.idcs;
+        bool ok = t.mode != Mode::Virtual && (t.prec == Prec::Single || prec_bytes(t.prec) == 2) && t.prec != Prec::Uint16;
+        for (auto& ix : canon) {
+          if (ix.kind == Index::Iter) {
+            if (ren) {
+              auto it = ren->find(ix.sym);
+              if (it != ren->end()) ix.sym = it->second;
+            }
+          } else if (ix.kind != Index::Fixed) ok = false;
+        }
+        if (ok && canon.back().kind == Index::Iter && canon.back().sym == n_sym) {
+          for (size_t a = 0; a + 1 < canon.size(); ++a)
+            if (canon[a].uses(n_sym)) ok = false;
+          bool dup = false;
+          for (auto& lt : em.load_tiles)
+            if (lt.tn == e.tn && lt.idcs.size() == e.idcs.size()) {
+              bool same = true;
+              for (size_t a = 0; a < e.idcs.size(); ++a)
+                if (lt.idcs[a].kind != e.idcs[a].kind || lt.idcs[a].sym != e.idcs[a].sym || lt.idcs[a].fixed != e.idcs[a].fixed) same = false;
+              if (same) dup = true;
+            }
+          if (ok && !dup && n_in_tiles < 4) {
+            const std::string arr = "b200_i" + std::to_string(n_in_tiles++);
+            Indices row = canon;
+            row.back().kind = Index::Fixed;
+            row.back().fixed = 0;
+            row.back().sym.clear();
+            const std::string T = Emitter::ctype(t.prec);
+            const bool f32 = t.prec == Prec::Single;
+            std::ostringstream lc;
+            lc << "  " << T << " " << arr << "[B200_EPI_CHUNK];\n  if (b200_row_ok) {\n"
+               << "    const " << T << "* b200_p = " << t.ident << " + (" << em.offset(row, t.dims) << ") + b200_n0;\n"
+               << "    if (b200_n0 + B200_EPI_CHUNK <= b200_N && (((unsigned long long)b200_p) & 15ull) == 0ull) {\n"
+               << "#pragma unroll\n      for (int v = 0; v < B200_EPI_CHUNK / " << (f32 ? 4 : 8) << "; ++v) {\n"
+               << "        const uint4 q = ((const uint4*)b200_p)[v];\n";
+            if (f32)
+              lc << "        " << arr << "[4 * v] = __uint_as_float(q.x); " << arr << "[4 * v + 1] = __uint_as_float(q.y);\n"
+                 << "        " << arr << "[4 * v + 2] = __uint_as_float(q.z); " << arr << "[4 * v + 3] = __uint_as_float(q.w);\n";
+            else
+              lc << "        " << arr << "[8 * v] = (unsigned short)q.x; " << arr << "[8 * v + 1] = (unsigned short)(q.x >> 16);\n"
+                 << "        " << arr << "[8 * v + 2] = (unsigned short)q.y; " << arr << "[8 * v + 3] = (unsigned short)(q.y >> 16);\n"
+                 << "        " << arr << "[8 * v + 4] = (unsigned short)q.z; " << arr << "[8 * v + 5] = (unsigned short)(q.z >> 16);\n"
+                 << "        " << arr << "[8 * v + 6] = (unsigned short)q.w; " << arr << "[8 * v + 7] = (unsigned short)(q.w >> 16);\n";
+            lc << "      }\n    } else {\n#pragma unroll\n      for (int j = 0; j < B200_EPI_CHUNK; ++j) " << arr
+               << "[j] = (b200_n0 + (unsigned int)j < b200_N) ? b200_p[j] : (" << T << ")0;\n    }\n  }\n";
+            load_code += lc.str();
+            em.load_tiles.push_back({e.tn, e.idcs, arr + "[b200_j]"});
+            em.used_nodes.insert(e.tn);
+          }
+        }
+      }
+      if (e.kind == Scalar::GetDyn) return;
+      for (auto& a : e.args) go(*a.s);
+    };
+    go(root);
+  };
+  if (!form_b) collect_loads(*set.value, nullptr);
+
   em.scope_subst[kAccScope] = "b200_acc";
   std::string body;
   add_out(set.tn, set.idcs);
@@ -428,6 +497,9 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
       if (ix.kind == Index::Iter) ix.sym = ren[ix.sym];
     add_out(fo.set->tn, canon);
     em.set_redirect[fo.set->tn] = {fo.set->idcs, outs.back().arr + "[b200_j]"};
+    not_loadable.insert(fo.set->tn);
+    for (auto& o : outs) not_loadable.insert(o.tn);
+    collect_loads(*fo.set->value, &ren);
     body += aliases + em.stmt(*fo.set, 6);
     aliases.clear();
     produced.insert(fo.set->tn);
@@ -449,7 +521,7 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
   }
   std::string statics_prologue;
   {
-    std::string text = body;
+    std::string text = body + load_code;
     for (size_t i = 0; i < P.statics.size(); ++i) {
       const std::string& s = P.statics[i].sym;
       size_t p = 0;
@@ -471,13 +543,15 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
   }
   if (em.uses_merge) return false;
 
-  fn << "__device__ __forceinline__ void b200_epilogue_row(const unsigned int* b200_r, unsigned int b200_b0, unsigned int b200_b1, "
-        "unsigned int b200_m, unsigned int b200_n0, unsigned int b200_N"
+  fn << "__device__ __forceinline__ void b200_tmem_ld_chunk(unsigned int taddr, unsigned int* r);\n"
+     << "__device__ __forceinline__ void b200_epilogue_row(unsigned int* b200_r, unsigned int b200_b0, unsigned int b200_b1, "
+        "unsigned int b200_m, bool b200_row_ok, unsigned int b200_n0, unsigned int b200_N, uint4* b200_stage, "
+        "bool b200_has_next, unsigned int b200_next_taddr"
      << params << ") {\n"
      << statics_prologue;
+  fn << "  const unsigned int b200_lane = threadIdx.x & 31u;\n";
   {
     // batch axes: gb[0] is the outer one
-    std::ostringstream pre;
     ep.str("");
     if (gb.size() == 2) { recover(gb[0], "b200_b0"); recover(gb[1], "b200_b1"); }
     else if (gb.size() == 1) { recover(gb[0], "b200_b1"); }
@@ -485,42 +559,54 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
     fn << ep.str();
     ep.str("");
   }
-  fn << unit_syms;
+  fn << unit_syms << load_code;
   for (auto& o : outs) fn << "  " << Emitter::ctype(P.tn(o.tn).prec) << " " << o.arr << "[B200_EPI_CHUNK];\n";
   fn << "#pragma unroll\n  for (int b200_j = 0; b200_j < B200_EPI_CHUNK; ++b200_j) {\n"
      << "    const unsigned int b200_n = b200_n0 + (unsigned int)b200_j;\n"
-     << "    if (b200_n < b200_N) {\n"
+     << "    if (b200_row_ok && b200_n < b200_N) {\n"
      << "      const float b200_acc = __uint_as_float(b200_r[b200_j]);\n";
   recover(dn, "b200_n");
   fn << ep.str() << body << "    }\n  }\n";
-  // ---- store the register tiles: 16-byte vector stores when the chunk is whole, contiguous
-  //      and aligned; element stores (guarded) otherwise
+  // the accumulator chunk is consumed: start fetching the next one while this one is stored
+  fn << "  if (b200_has_next) b200_tmem_ld_chunk(b200_next_taddr, b200_r);\n";
+  // ---- store the register tiles.  A thread owns one row of the chunk, so storing from
+  //      registers would touch 32 different lines per instruction; when the chunk is whole,
+  //      contiguous and every row is 16-byte aligned, the warp transposes the chunk through a
+  //      swizzled shared-memory staging tile and writes whole row segments instead.
   for (auto& o : outs) {
     const Tnode& t = P.tn(o.tn);
     const int ebytes = prec_bytes(t.prec);
     const bool vec = o.unit_n && (ebytes == 4 || ebytes == 2);
+    const std::string T = Emitter::ctype(t.prec);
     if (o.unit_n) {
-      fn << "  {\n    " << Emitter::ctype(t.prec) << "* b200_p = " << t.ident << " + (" << o.row_off << ") + b200_n0;\n";
+      fn << "  {\n    " << T << "* b200_p = b200_row_ok ? (" << t.ident << " + (" << o.row_off << ") + b200_n0) : (" << T << "*)0;\n";
       if (vec) {
-        fn << "    if (b200_n0 + B200_EPI_CHUNK <= b200_N && (((unsigned long long)b200_p) & 15ull) == 0ull) {\n";
+        const std::string V = ebytes == 4 ? "4" : "8";  // elements per 16 bytes
+        fn << "    const bool b200_fast = (b200_n0 + B200_EPI_CHUNK <= b200_N) && __all_sync(0xffffffffu, (((unsigned long long)b200_p) & 15ull) == 0ull);\n"
+           << "    if (b200_fast) {\n"
+           << "      constexpr int G = B200_EPI_CHUNK / " << V << ";   // 16-byte groups per row\n"
+           << "#pragma unroll\n      for (int g = 0; g < G; ++g) {\n        uint4 q;\n";
         if (ebytes == 4) {
-          fn << "#pragma unroll\n      for (int b200_v = 0; b200_v < B200_EPI_CHUNK / 4; ++b200_v) {\n"
-             << "        uint4 b200_q;\n"
-             << "        b200_q.x = b200_bits32(" << o.arr << "[4 * b200_v]); b200_q.y = b200_bits32(" << o.arr << "[4 * b200_v + 1]);\n"
-             << "        b200_q.z = b200_bits32(" << o.arr << "[4 * b200_v + 2]); b200_q.w = b200_bits32(" << o.arr << "[4 * b200_v + 3]);\n"
-             << "        ((uint4*)b200_p)[b200_v] = b200_q;\n      }\n";
+          fn << "        q.x = b200_bits32(" << o.arr << "[4 * g]); q.y = b200_bits32(" << o.arr << "[4 * g + 1]);\n"
+             << "        q.z = b200_bits32(" << o.arr << "[4 * g + 2]); q.w = b200_bits32(" << o.arr << "[4 * g + 3]);\n";
         } else {
-          fn << "#pragma unroll\n      for (int b200_v = 0; b200_v < B200_EPI_CHUNK / 8; ++b200_v) {\n"
-             << "        uint4 b200_q;\n"
-             << "        b200_q.x = (unsigned int)" << o.arr << "[8 * b200_v] | ((unsigned int)" << o.arr << "[8 * b200_v + 1] << 16);\n"
-             << "        b200_q.y = (unsigned int)" << o.arr << "[8 * b200_v + 2] | ((unsigned int)" << o.arr << "[8 * b200_v + 3] << 16);\n"
-             << "        b200_q.z = (unsigned int)" << o.arr << "[8 * b200_v + 4] | ((unsigned int)" << o.arr << "[8 * b200_v + 5] << 16);\n"
-             << "        b200_q.w = (unsigned int)" << o.arr << "[8 * b200_v + 6] | ((unsigned int)" << o.arr << "[8 * b200_v + 7] << 16);\n"
-             << "        ((uint4*)b200_p)[b200_v] = b200_q;\n      }\n";
+          fn << "        q.x = (unsigned int)" << o.arr << "[8 * g] | ((unsigned int)" << o.arr << "[8 * g + 1] << 16);\n"
+             << "        q.y = (unsigned int)" << o.arr << "[8 * g + 2] | ((unsigned int)" << o.arr << "[8 * g + 3] << 16);\n"
+             << "        q.z = (unsigned int)" << o.arr << "[8 * g + 4] | ((unsigned int)" << o.arr << "[8 * g + 5] << 16);\n"
+             << "        q.w = (unsigned int)" << o.arr << "[8 * g + 6] | ((unsigned int)" << o.arr << "[8 * g + 7] << 16);\n";
         }
-        fn << "    } else {\n";
+        fn << "        b200_stage[b200_lane * G + (g ^ (b200_lane % G))] = q;\n      }\n"
+           << "      __syncwarp();\n"
+           << "      const unsigned long long b200_pv = (unsigned long long)b200_p;\n"
+           << "#pragma unroll\n      for (int it = 0; it < G; ++it) {\n"
+           << "        const unsigned int r = it * (32 / G) + b200_lane / G, c = b200_lane % G;\n"
+           << "        const unsigned long long dst = __shfl_sync(0xffffffffu, b200_pv, r);\n"
+           << "        const uint4 q = b200_stage[r * G + (c ^ (r % G))];\n"
+           << "        if (dst) *(uint4*)(dst + 16ull * c) = q;\n      }\n"
+           << "      __syncwarp();\n"
+           << "    } else if (b200_row_ok) {\n";
       } else {
-        fn << "    {\n";
+        fn << "    if (b200_row_ok) {\n";
       }
       fn << "#pragma unroll\n      for (int b200_j = 0; b200_j < B200_EPI_CHUNK; ++b200_j)\n"
          << "        if (b200_n0 + (unsigned int)b200_j < b200_N) b200_p[b200_j] = " << o.arr << "[b200_j];\n"
@@ -528,7 +614,7 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
     } else {
       // general position: recompute the offset per column
       fn << "#pragma unroll\n  for (int b200_j = 0; b200_j < B200_EPI_CHUNK; ++b200_j) {\n"
-         << "    const unsigned int b200_n = b200_n0 + (unsigned int)b200_j;\n    if (b200_n < b200_N) {\n";
+         << "    const unsigned int b200_n = b200_n0 + (unsigned int)b200_j;\n    if (b200_row_ok && b200_n < b200_N) {\n";
       ep.str("");
       recover(dn, "b200_n");
       fn << ep.str() << "      " << t.ident << "[" << em.offset(o.idcs, t.dims) << "] = " << o.arr << "[b200_j];\n    }\n  }\n";
@@ -541,6 +627,7 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
   out->gemm.epilogue = fn.str();
   out->args = kargs;
   out->total = 1;
+  out->epi_tiles = (int)outs.size() + n_in_tiles;
   out->epi_params = params;
   out->epi_args = args;
   return true;
@@ -558,12 +645,13 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   const int bm = 128, bk = row_elems;
   const int umma_k = 32 / eb;
   const int stage_bytes = (bm + bn) * bk * eb;
-  int stages = (200 * 1024) / stage_bytes;
+  const int epi_warps = bn >= 128 ? 8 : 4;
+  // 227 KB per CTA: ring + alignment slack + barriers + one 4 KB staging tile per epilogue warp
+  int stages = (227 * 1024 - 1024 - 256 - epi_warps * 4096) / stage_bytes;
   if (stages > 8) stages = 8;
   if (stages < 2) stages = 2;
   int tmem_cols = 32;
   while (tmem_cols < 2 * bn) tmem_cols *= 2;
-  const int epi_warps = bn >= 128 ? 8 : 4;
   // instruction descriptor: fp32 accumulate, operand formats, majors, N >> 3, M >> 4
   unsigned int fmt = g.in_prec == Prec::Bfloat16 ? 1u : (g.in_prec == Prec::Half ? 0u : 2u);
   unsigned int idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((g.a_kmajor ? 0u : 1u) << 15) | ((g.b_kmajor ? 0u : 1u) << 16) |
@@ -576,10 +664,12 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
     << "\n#define B200_STAGES " << stages << "\n#define B200_EPI_WARPS " << epi_warps << "\n#define B200_A_KMAJOR "
     << (g.a_kmajor ? 1 : 0) << "\n#define B200_B_KMAJOR " << (g.b_kmajor ? 1 : 0) << "\n#define B200_IDESC " << idesc
     << "u\n#define B200_TMEM_COLS " << tmem_cols << "\n#define B200_RASTER 8\n";
-  o << "#if " << bn << " >= 32\n#define B200_EPI_CHUNK 32\n#else\n#define B200_EPI_CHUNK 16\n#endif\n";
+  // columns per epilogue step: 32 when the epilogue keeps few register tiles, else 16 so that
+  // the tiles and the double-buffered accumulator chunk stay in registers
+  o << "#ifndef B200_EPI_CHUNK\n#define B200_EPI_CHUNK " << ((bn >= 32 && st.epi_tiles <= 2) ? 32 : 16) << "\n#endif\n";
   o << g.epilogue << "\n";
   o << "#define B200_EPI_PARAMS " << params << "\n";
-  o << "#define B200_EPILOGUE_ROW b200_epilogue_row(b200_r, b200_b0, b200_b1, b200_m, b200_n0, shape.N" << args << ");\n";
+  o << "#define B200_EPILOGUE_ROW b200_epilogue_row(b200_r, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_n0, shape.N, b200_stage, b200_has_next, b200_next_taddr" << args << ");\n";
   o << kGemmSource << "\n";
   std::ostringstream note;
   note << "tcgen05 " << bm << "x" << bn << "x" << bk << " stages=" << stages << " epi_warps=" << epi_warps
@@ -590,7 +680,7 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   st.tile_m = bm;
   st.tile_n = bn;
   st.tile_k = bk;
-  st.smem_bytes = stages * stage_bytes + 1024 + 256;
+  st.smem_bytes = stages * stage_bytes + 1024 + 256 + epi_warps * 4096;
   return o.str();
 }
 

@@ -155,6 +155,14 @@ __device__ __forceinline__ void b200_tmem_ld16(unsigned int taddr, unsigned int*
       : "memory");
 }
 
+__device__ __forceinline__ void b200_tmem_ld_chunk(unsigned int taddr, unsigned int* r) {
+#if B200_EPI_CHUNK == 32
+  b200_tmem_ld32(taddr, r);
+#else
+  b200_tmem_ld16(taddr, r);
+#endif
+}
+
 #define B200_A_TILE_BYTES (B200_BM * B200_BK * B200_ELEM_BYTES)
 #define B200_B_TILE_BYTES (B200_BN * B200_BK * B200_ELEM_BYTES)
 #define B200_STAGE_BYTES (B200_A_TILE_BYTES + B200_B_TILE_BYTES)
@@ -310,6 +318,8 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
     const unsigned int quarter = warp & 3u;           // TMEM lanes this warp may read
     const unsigned int col_half = ew >> 2;            // with 8 warps, two warps share a quarter
     const unsigned int cols_per_warp = B200_BN / (B200_EPI_WARPS / 4);
+    // this warp's 4 KB staging tile (transposes a chunk so that stores cover whole row segments)
+    uint4* b200_stage = (uint4*)(smem_gen + B200_STAGES * B200_STAGE_BYTES + 256 + ew * 4096u);
     unsigned int acc = 0, acc_phase = 0;
     for (unsigned int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       const unsigned int bidx = tile / tiles_per_batch;
@@ -325,20 +335,22 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const unsigned int b200_m = mt * B200_BM + quarter * 32u + lane;
       const unsigned int taddr = tmem_base + acc * B200_BN + ((quarter * 32u) << 16);
+      // One register buffer: the epilogue issues the TMEM load of the next chunk as soon as it
+      // has consumed the current one, so the load overlaps the epilogue's stores.  (The loop is
+      // deliberately not unrolled: the generated epilogue can be thousands of instructions.)
+      unsigned int b200_r[B200_EPI_CHUNK];
+      const unsigned int col0 = col_half * cols_per_warp;
+      if (nt * B200_BN + col0 < shape.N) b200_tmem_ld_chunk(taddr + col0, b200_r);
+#pragma unroll 1
       for (unsigned int c = 0; c < cols_per_warp; c += B200_EPI_CHUNK) {
-        const unsigned int col = col_half * cols_per_warp + c;
+        const unsigned int col = col0 + c;
         const unsigned int b200_n0 = nt * B200_BN + col;
         if (b200_n0 >= shape.N) break;  // warp-uniform
-        unsigned int b200_r[B200_EPI_CHUNK];
-#if B200_EPI_CHUNK == 32
-        b200_tmem_ld32(taddr + col, b200_r);
-#else
-        b200_tmem_ld16(taddr + col, b200_r);
-#endif
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (b200_m < shape.M) {
-          B200_EPILOGUE_ROW
-        }
+        const bool b200_has_next = (c + B200_EPI_CHUNK < cols_per_warp) && (b200_n0 + B200_EPI_CHUNK < shape.N);
+        const unsigned int b200_next_taddr = taddr + col + B200_EPI_CHUNK;
+        // every lane takes part: rows beyond M compute nothing but help move the chunk
+        B200_EPILOGUE_ROW
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();

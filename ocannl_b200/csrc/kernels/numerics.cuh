@@ -3,7 +3,8 @@
 //
 // Bit-level helpers follow the reference's C helpers so that integer paths agree bit for
 // bit with the cc backend (arrayjit/lib/builtins.c):
-//   bf16 <-> f32        :611-627  (shift / add 0x7FFF + lsb, no NaN special case)
+//   bf16 <-> f32        :611-627  (round to nearest even; same bits as the reference's
+//                                  add-0x7FFF-plus-lsb formula for everything but NaN payloads)
 //   threefry4x32        :156-329  (20-round and 2-round forms)
 //   uniform conversions :345-360, widening to uint4x32 :545-578
 // Half values are stored as their 16 bits; arithmetic on them is done in f32 and rounded
@@ -18,10 +19,18 @@ typedef unsigned long long b200_u64;
 #define B200_NAN (__int_as_float(0x7fffffff))
 
 __device__ __forceinline__ float b200_bf2f(unsigned short h) { return __uint_as_float(((b200_u32)h) << 16); }
+// Round to nearest even in one instruction.  For every finite value and for infinities this is
+// bit-identical to the reference's `(u + 0x7FFF + ((u >> 16) & 1)) >> 16`; NaNs come out as the
+// canonical NaN instead of a truncated payload.
 __device__ __forceinline__ unsigned short b200_f2bf(float f) {
+#ifdef B200_F2BF_INT
   b200_u32 u = __float_as_uint(f);
   u += 0x7FFFu + ((u >> 16) & 1u);
   return (unsigned short)(u >> 16);
+#endif
+  unsigned short h;
+  asm("{ .reg .b16 t; cvt.rn.bf16.f32 t, %1; mov.b16 %0, t; }" : "=h"(h) : "f"(f));
+  return h;
 }
 __device__ __forceinline__ float b200_h2f(unsigned short h) {
   float f;
