@@ -189,11 +189,20 @@ std::string Code::describe() const {
 
 namespace {
 
+// What generic_stage knows about a stage before its kernel text is written.
+struct Piece {
+  bool fusable = false;
+  std::string decomp, body_text;
+  std::set<int> used, written;
+  bool uses_merge = false;
+};
+
 struct Builder {
   Code& code;
   const CompileOptions& opt;
   std::ostringstream src;
   int next_kernel = 0;
+  std::map<size_t, Piece> pieces;  // by index into code.stages
 
   std::string kernel_name() { return code.prog.name + "_s" + std::to_string(next_kernel++); }
 
@@ -481,11 +490,35 @@ struct Builder {
         }
       }
     }
-    std::string statics = static_prologue(body_text + decomp, em, 2);
+    // the kernel text is assembled at the end of the routine (emit_kernels), when it is known
+    // which neighbouring stages are small enough to share one launch
+    Piece pc;
+    pc.decomp = decomp;
+    pc.body_text = body_text;
+    pc.used = em.used_nodes;
+    pc.written = written;
+    pc.uses_merge = em.uses_merge;
+    int64_t ser_work = 1;
+    for (auto& d : st.ser) ser_work *= std::max<int64_t>(1, d.extent());
+    pc.fusable = opt.enable_fuse && st.total > 0 && (st.coop == 0 || st.coop == 32) &&
+                 st.total * std::max(1, st.coop) <= 16384 && ser_work <= 4096;
+    std::ostringstream note;
+    note << "par=" << st.par.size() << " ser=" << st.ser.size()
+         << (st.coop > 32 ? " block-per-element" : st.coop ? " warp-per-element" : "");
+    st.note = note.str();
+    pieces[code.stages.size()] = pc;
+    code.stages.push_back(st);
+  }
 
+  // Text of one stand-alone generic kernel (grid-stride over the stage's parallel iterations).
+  void emit_single(Stage& st, const Piece& pc) {
+    Emitter em(code.prog);
+    em.used_nodes = pc.used;
+    em.uses_merge = pc.uses_merge;
+    std::string statics = static_prologue(pc.body_text + pc.decomp, em, 2);
     std::ostringstream k_src;
     k_src << "extern \"C\" __global__ void __launch_bounds__(" << st.block << ") " << st.kernel << "(";
-    emit_params(k_src, st, em, written);
+    emit_params(k_src, st, em, pc.written);
     k_src << ") {\n" << statics;
     if (st.coop > 32) {
       k_src << "  __shared__ double b200_red[32];\n";
@@ -500,13 +533,92 @@ struct Builder {
       k_src << "  for (unsigned long long b200_g = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; b200_g < "
             << st.total << "ull; b200_g += (unsigned long long)gridDim.x * blockDim.x) {\n";
     }
-    k_src << decomp << body_text << "  }\n}\n\n";
+    k_src << pc.decomp << pc.body_text << "  }\n}\n\n";
     src << k_src.str();
-    std::ostringstream note;
-    note << "par=" << st.par.size() << " ser=" << st.ser.size()
-         << (st.coop > 32 ? " block-per-element" : st.coop ? " warp-per-element" : "");
-    st.note = note.str();
-    code.stages.push_back(st);
+  }
+
+  // Several small consecutive stages (and small zero_outs) as ONE kernel of a single
+  // 1024-thread block: each stage strides its iterations over the block, __syncthreads()
+  // separates the stages.  Launch latency, not work, dominates such routines (the 2-16-16-1
+  // training step is ~30 stages of a few hundred iterations each).
+  Stage emit_fused(const std::vector<size_t>& idx) {
+    Stage f;
+    f.kind = Stage::Generic;
+    f.kernel = code.stages[idx.front()].kernel.empty() ? kernel_name() : code.stages[idx.front()].kernel;
+    f.block = 1024;
+    f.grid_override = 1;
+    f.total = 1;
+    Emitter em(code.prog);
+    std::set<int> written;
+    std::string text;
+    for (size_t i : idx) {
+      const Stage& st = code.stages[i];
+      if (st.kind == Stage::Memset) {
+        const Tnode& t = code.prog.tn(st.memset_tn);
+        em.used_nodes.insert(t.id);
+        written.insert(t.id);
+        text += "  for (unsigned int b200_z = threadIdx.x; b200_z < " + std::to_string(t.num_elems()) +
+                "u; b200_z += blockDim.x) " + t.ident + "[b200_z] = " + em.constant(0.0, t.prec) + ";\n";
+      } else {
+        const Piece& pc = pieces[i];
+        em.used_nodes.insert(pc.used.begin(), pc.used.end());
+        written.insert(pc.written.begin(), pc.written.end());
+        em.uses_merge |= pc.uses_merge;
+        text += "  {\n";
+        if (st.coop) {
+          text += "  const unsigned int b200_t = threadIdx.x & 31u;\n";
+          text += "  for (unsigned long long b200_g = threadIdx.x >> 5; b200_g < " + std::to_string(st.total) +
+                  "ull; b200_g += blockDim.x >> 5) {\n";
+        } else {
+          text += "  for (unsigned long long b200_g = threadIdx.x; b200_g < " + std::to_string(st.total) +
+                  "ull; b200_g += blockDim.x) {\n";
+        }
+        text += pc.decomp + pc.body_text + "  }\n  }\n";
+      }
+      text += "  __syncthreads();\n";
+    }
+    std::string statics = static_prologue(text, em, 2);
+    std::ostringstream k_src;
+    k_src << "extern \"C\" __global__ void __launch_bounds__(1024) " << f.kernel << "(";
+    emit_params(k_src, f, em, written);
+    k_src << ") {\n" << statics << text << "}\n\n";
+    src << k_src.str();
+    f.note = "fused " + std::to_string(idx.size()) + " small stages in one block";
+    return f;
+  }
+
+  // Decides which stages share a launch and writes the kernels' text.
+  void emit_kernels() {
+    std::vector<Stage> out;
+    auto fusable = [&](size_t i) {
+      const Stage& st = code.stages[i];
+      if (st.kind == Stage::Memset) {
+        const Tnode& t = code.prog.tn(st.memset_tn);
+        return opt.enable_fuse && t.bytes() <= 262144 && prec_bytes(t.prec) <= 8 && t.prec != Prec::Uint4x32;
+      }
+      auto it = pieces.find(i);
+      return it != pieces.end() && it->second.fusable;
+    };
+    for (size_t i = 0; i < code.stages.size();) {
+      if (fusable(i)) {
+        std::vector<size_t> run;
+        size_t j = i;
+        while (j < code.stages.size() && fusable(j)) run.push_back(j++);
+        int kernels = 0;
+        for (size_t k : run) kernels += code.stages[k].kind != Stage::Memset;
+        if (run.size() >= 2 && kernels >= 1) {
+          out.push_back(emit_fused(run));
+          i = j;
+          continue;
+        }
+      }
+      Stage st = code.stages[i];
+      auto it = pieces.find(i);
+      if (it != pieces.end()) emit_single(st, it->second);
+      out.push_back(st);
+      ++i;
+    }
+    code.stages = out;
   }
 
   // A group of threads per output element: each Local_scope reduction runs over its flattened
@@ -664,6 +776,7 @@ struct Builder {
       }
       generic_stage(nest, body);
     }
+    emit_kernels();
     code.source = src.str();
     for (auto& t : code.prog.tnodes)
       if (t.mode == Mode::Local) code.local_nodes.push_back(t.id);

@@ -79,6 +79,7 @@ struct Code {
 struct CompileOptions {
   bool enable_gemm = true;
   bool enable_coop = true;
+  bool enable_fuse = true;   // several small stages in one single-block kernel
   bool large_models = false;
 };
 

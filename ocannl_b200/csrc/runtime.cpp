@@ -50,6 +50,17 @@ void b200_routine::link(b200_dev* d, b200_code* c, const b200_binding* b, int n)
     if (t.zero_init) scratch_zero.push_back({off, (size_t)t.bytes()});
     off += ((size_t)t.bytes() + 255) & ~(size_t)255;
   }
+  // neighbouring zero ranges become one memset (the padding between nodes may be cleared too)
+  {
+    std::vector<std::pair<size_t, size_t>> merged;
+    for (auto& z : scratch_zero) {
+      if (!merged.empty() && merged.back().first + merged.back().second + 256 >= z.first)
+        merged.back().second = z.first + z.second - merged.back().first;
+      else
+        merged.push_back(z);
+    }
+    scratch_zero.swap(merged);
+  }
   const size_t reduce_off = off;
   off += c->code.reduce_scratch_bytes;
   scratch_bytes = off;

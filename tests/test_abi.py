@@ -39,7 +39,13 @@ def test_compile_is_device_independent(built_lib):
     """`compile` may not touch a device (docs/anatomy_of_a_backend.md:97-108): the moons
     training routine compiles to sm_100a kernels on a machine without a GPU."""
     _nvrtc_or_skip()
-    code = bk.Code(W.moons_train_step())
+    fused = bk.Code(W.moons_train_step())
+    st = fused.info()["stages"]
+    # ~30 tiny stages share ONE single-block launch
+    assert len(st) == 1 and st[0]["kind"] == "generic" and "fused" in st[0]["note"], st
+    assert fused.source().count("__syncthreads()") >= 30
+    fused.free()
+    code = bk.Code(W.moons_train_step(), options="fuse=0")
     info = code.info()
     kinds = [s["kind"] for s in info["stages"]]
     assert kinds.count("generic") >= 15 and "memset" in kinds

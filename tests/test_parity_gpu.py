@@ -33,8 +33,9 @@ def test_golden_routines_on_device(device):
             assert np.array_equal(got[t.ident].view(np.uint8), want[t.ident].view(np.uint8)), (name, t.ident)
 
 
+@pytest.mark.parametrize("options", [None, "fuse=0"])
 @pytest.mark.parametrize("graph", [False, True])
-def test_moons_training_steps(device, graph):
+def test_moons_training_steps(device, graph, options):
     """Config 1: forward + backprop + SGD, five steps over different batches; parameters,
     gradients, activations and the loss agree with the cc restatement to rel 1e-5."""
     ir = W.moons_train_step()
@@ -42,7 +43,8 @@ def test_moons_training_steps(device, graph):
     inputs = dict(W.moons_params(), moons_flat=x, moons_classes=y)
     statics = [{"i1": b, "i2": s} for s, b in enumerate([0, 1, 7, 50, 3])]
     want = run_oracle(ir, inputs, statics)
-    got, info = run_device(device, ir, inputs, statics, graph=graph)
+    got, info = run_device(device, ir, inputs, statics, options=options, graph=graph)
+    assert (len(info["stages"]) == 1) == (options is None)       # one fused launch by default
     compare(ir, got, want, rtol=1e-5, atol=1e-6)
     assert abs(float(got["scalar_loss"][0])) > 0
 
