@@ -422,6 +422,114 @@ struct Builder {
     code.stages.push_back(b);
   }
 
+  // Accumulation whose reduced loops are OUTSIDE the output loops (back-propagation keeps the
+  // forward loop order: `for b { for o { g[o] := g[o] + dz[b, o] } }`, or the fma form with two
+  // factors).  A 32x32 block owns 32 consecutive outputs (threadIdx.x, coalesced) and splits the
+  // flattened serial loop space over threadIdx.y; partial sums meet in shared memory and the
+  // y == 0 row adds them to the node in a fixed order.
+  bool ser_split_stage(Stage st, const Stmt& set) {
+    if (set.kind != Stmt::Set) return false;
+    const Tnode& t = code.prog.tn(set.tn);
+    if (t.prec != Prec::Single && t.prec != Prec::Double) return false;
+    int64_t ser_total = 1;
+    for (auto& d : st.ser) ser_total *= d.extent();
+    if (ser_total < 256) return false;
+    const Scalar& v = *set.value;
+    auto is_self = [&](const Scalar& e) {
+      if (e.kind != Scalar::Get || e.tn != set.tn || e.idcs.size() != set.idcs.size()) return false;
+      for (size_t i = 0; i < e.idcs.size(); ++i)
+        if (e.idcs[i].kind != set.idcs[i].kind || e.idcs[i].sym != set.idcs[i].sym || e.idcs[i].fixed != set.idcs[i].fixed ||
+            e.idcs[i].terms != set.idcs[i].terms)
+          return false;
+      return true;
+    };
+    auto reads_node = [&](const Scalar& e) {
+      bool m = false;
+      walk_scalar(e, [&](const Scalar& x) {
+        if ((x.kind == Scalar::Get || x.kind == Scalar::GetDyn) && x.tn == set.tn) m = true;
+        if (x.kind == Scalar::LocalScope) m = true;  // keep this path to plain terms
+      }, [](const Stmt&) {});
+      return m;
+    };
+    const Scalar *fa = nullptr, *fb = nullptr, *term = nullptr;
+    if (v.kind == Scalar::Tern && v.op == "fma" && is_self(*v.args[2].s)) {
+      fa = v.args[0].s.get();
+      fb = v.args[1].s.get();
+      if (reads_node(*fa) || reads_node(*fb)) return false;
+    } else if (v.kind == Scalar::Bin && v.op == "add") {
+      if (is_self(*v.args[0].s)) term = v.args[1].s.get();
+      else if (is_self(*v.args[1].s)) term = v.args[0].s.get();
+      if (!term || reads_node(*term)) return false;
+    } else {
+      return false;
+    }
+    Emitter em(code.prog);
+    em.large_models = opt.large_models;
+    const std::string T = Emitter::ctype(t.prec);
+    std::string step;
+    if (term) {
+      Emitter::Res r = em.scalar(t.prec, *term);
+      if (!r.defs.empty()) return false;
+      step = "b200_acc = b200_acc + " + r.expr + ";";
+    } else {
+      Emitter::Res ra = em.scalar(t.prec, *fa), rb = em.scalar(t.prec, *fb);
+      if (!ra.defs.empty() || !rb.defs.empty()) return false;
+      step = std::string("b200_acc = ") + (t.prec == Prec::Double ? "fma(" : "fmaf(") + ra.expr + ", " + rb.expr + ", b200_acc);";
+    }
+    em.used_nodes.insert(set.tn);
+    std::string decomp, sdecomp;
+    {
+      std::string rem = "b200_g";
+      for (size_t i = st.par.size(); i-- > 0;) {
+        const LoopDim& d = st.par[i];
+        std::string ext = std::to_string(d.extent()) + "ull";
+        decomp += "      const unsigned int " + d.sym + " = (unsigned int)" + (i == 0 ? rem : "(" + rem + " % " + ext + ")") + ";\n";
+        if (i != 0) {
+          decomp += "      const unsigned long long b200_r" + std::to_string(i) + " = " + rem + " / " + ext + ";\n";
+          rem = "b200_r" + std::to_string(i);
+        }
+      }
+      rem = "b200_l";
+      for (size_t i = st.ser.size(); i-- > 0;) {
+        const LoopDim& d = st.ser[i];
+        std::string ext = std::to_string(d.extent()) + "ull";
+        sdecomp += "        const unsigned int " + d.sym + " = (unsigned int)" + (i == 0 ? rem : "(" + rem + " % " + ext + ")") + ";\n";
+        if (i != 0) {
+          sdecomp += "        const unsigned long long b200_q" + std::to_string(i) + " = " + rem + " / " + ext + ";\n";
+          rem = "b200_q" + std::to_string(i);
+        }
+      }
+    }
+    for (auto& d : st.par) if (d.from != 0) return false;
+    for (auto& d : st.ser) if (d.from != 0) return false;
+    const std::string off = em.offset(set.idcs, t.dims);
+    std::string text = decomp + sdecomp + step + off;
+    std::string statics = static_prologue(text, em, 2);
+    st.block = 32;
+    st.block_y = 32;
+    st.coop = 32;  // 32 threads per output element
+    std::set<int> written = {set.tn};
+    std::ostringstream k;
+    k << "extern \"C\" __global__ void __launch_bounds__(1024) " << st.kernel << "(";
+    emit_params(k, st, em, written);
+    k << ") {\n" << statics << "  __shared__ " << T << " b200_part[32][33];\n"
+      << "  for (unsigned long long b200_g0 = (unsigned long long)blockIdx.x * 32ull; b200_g0 < " << st.total
+      << "ull; b200_g0 += (unsigned long long)gridDim.x * 32ull) {\n"
+      << "    const unsigned long long b200_g = b200_g0 + threadIdx.x;\n"
+      << "    const bool b200_ok = b200_g < " << st.total << "ull;\n"
+      << "    " << T << " b200_acc = 0;\n    if (b200_ok) {\n"
+      << decomp << "      for (unsigned long long b200_l = threadIdx.y; b200_l < " << ser_total << "ull; b200_l += 32ull) {\n"
+      << sdecomp << "        " << step << "\n      }\n    }\n"
+      << "    b200_part[threadIdx.y][threadIdx.x] = b200_acc;\n    __syncthreads();\n"
+      << "    if (threadIdx.y == 0 && b200_ok) {\n" << decomp << "      " << T << " b200_s = 0;\n"
+      << "      for (int b200_y = 0; b200_y < 32; ++b200_y) b200_s += b200_part[b200_y][threadIdx.x];\n"
+      << "      " << t.ident << "[" << off << "] = " << t.ident << "[" << off << "] + b200_s;\n    }\n    __syncthreads();\n  }\n}\n\n";
+    src << k.str();
+    st.note = "par=" + std::to_string(st.par.size()) + " ser=" + std::to_string(st.ser.size()) + " serial loops split over a 32x32 block";
+    code.stages.push_back(st);
+    return true;
+  }
+
   void generic_stage(const std::vector<LoopDim>& nest, const StmtP& body) {
     Stage st;
     st.kind = Stage::Generic;
@@ -437,6 +545,8 @@ struct Builder {
 
     Emitter em(code.prog);
     em.large_models = opt.large_models;
+
+    if (!st.ser.empty() && st.total > 0 && opt.enable_coop && ser_split_stage(st, *body)) return;
 
     CoopInfo ci;
     if (st.ser.empty() && st.total > 0) ci = find_coop(*body, st.total);
@@ -745,7 +855,10 @@ struct Builder {
             i += 1 + (size_t)n_fused;
           }
         }
-        if (!absorbed) memset_stage(s->tn);
+        if (!absorbed) {
+          memset_stage(s->tn);
+          zeroed.insert(s->tn);  // still all zero until some stage writes it
+        }
         continue;
       }
       // peel the perfect loop nest
@@ -763,10 +876,19 @@ struct Builder {
           if (!declared.count(u))
             throw Error(-4, "function-scope scalar locals (cross-statement hoisting) are not supported by the b200 backend");
       }
+      // a node zeroed earlier and untouched since lets a contraction skip reading it (beta = 0)
+      std::set<int> writes_now;
+      walk_stmt(*body, [](const Scalar&) {}, [&](const Stmt& w) {
+        if (w.kind == Stmt::Set || w.kind == Stmt::ZeroOut) writes_now.insert(w.tn);
+      });
+      const bool was_zero = body->kind == Stmt::Set && zeroed.count(body->tn) > 0;
+      for (int w : writes_now) zeroed.erase(w);
       if (opt.enable_gemm && body->kind == Stmt::Set) {
         Stage g;
         int n_fused = 0;
-        if (match_gemm(code.prog, nest, *body, false, opt, followers_after(flat, i + 1), &n_fused, &g)) {
+        const std::vector<Follower> fol = followers_after(flat, i + 1);
+        if (match_gemm(code.prog, nest, *body, was_zero, opt, fol, &n_fused, &g)) {
+          for (int f = 0; f < n_fused; ++f) zeroed.erase(fol[(size_t)f].set->tn);
           g.kernel = kernel_name();
           g.gemm_source = gemm_translation_unit(code.prog, g, g.kernel, opt);
           code.stages.push_back(g);

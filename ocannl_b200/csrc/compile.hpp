@@ -50,6 +50,7 @@ struct Stage {
   std::vector<LoopDim> par, ser;
   int64_t total = 1;             // parallel iterations
   int block = 256;
+  int block_y = 1;               // >1: two-dimensional block (serial loops split over y)
   int coop = 0;                  // >0: lanes cooperating on one output element (row reductions)
   int grid_override = 0;         // >0: launch exactly this many blocks (first pass of a grid-wide reduction)
   GemmPlan gemm;

@@ -8,6 +8,7 @@
 // change between runs.
 #include "runtime.hpp"
 
+#include <algorithm>
 #include <cstring>
 
 using namespace b200;
@@ -164,8 +165,9 @@ void b200_routine::enqueue_stages() {
     long long cap = (long long)dev->sm_count * 16;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
+    if (st.block_y > 1) blocks = std::min<long long>(cap, (st.total + st.block - 1) / st.block);
     if (st.grid_override > 0) blocks = st.grid_override;
-    cu_check(cu().cuLaunchKernel_(fns[i], (unsigned)blocks, 1, 1, (unsigned)st.block, 1, 1, 0, dev->stream, args.data(),
+    cu_check(cu().cuLaunchKernel_(fns[i], (unsigned)blocks, 1, 1, (unsigned)st.block, (unsigned)st.block_y, 1, 0, dev->stream, args.data(),
                                   nullptr),
              "cuLaunchKernel");
     dev->n_launches++;

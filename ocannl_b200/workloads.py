@@ -591,3 +591,105 @@ def transformer_forward(batch=64, seq=256, layers=6, d_model=512, heads=8, d_hea
     body.append(Comment("end"))
     r.body = Seq(body)
     return r
+
+
+# ------------------------------------------------------------------ config 5 (ii): forward + backward, SGD
+def mlp_train_update(rows=8192, dims=(784, 1024, 1024, 10), wprec="bfloat16") -> Routine:
+    """`Train.grad_update` of the softmax cross-entropy MLP (lib/train.ml:61-73): forward, zero
+    grads, backprop.  bf16 weights, activations and activation gradients; parameter gradients
+    and the gradients that are accumulated over a contracted axis are fp32 (so that the
+    contraction result nodes are fp32, as the tensor-core path requires).  Back-propagation
+    keeps the forward loop order (b, o, i): dW reduces over the outermost loop, dX over the
+    middle one."""
+    r = Routine("mlp_update_%d" % rows)
+    n_layers = len(dims) - 1
+    x = r.tn("x", wprec, [rows, dims[0]], read_only=True)
+    labels = r.tn("labels", "single", [rows, dims[-1]], read_only=True)
+    body: List = [Comment("loss forward and gradient update")]
+    W_, Bv, H = [], [], [x]
+    for l in range(n_layers):
+        fi, fo = dims[l], dims[l + 1]
+        last = l == n_layers - 1
+        w = r.tn("w_out" if last else "w%d" % (l + 1), wprec, [fo, fi], read_only=True)
+        W_.append(w)
+        ib, io, ii = r.syms(3)
+        hin = H[-1]
+        acc = lambda: reduce_scope(r, "n_mm%d" % l, "single", [(ii, fi)], lambda: (w[io, ii], hin[ib, ii]), orig=(ib, io))
+        if last:
+            out = r.tn("logits", "single", [rows, fo])
+            body.append(loops([(ib, rows), (io, fo)], Set(out, (ib, io), acc())))
+            Bv.append(None)
+        else:
+            b = r.tn("b%d" % (l + 1), wprec, [fo], read_only=True)
+            Bv.append(b)
+            out = r.tn("h%d" % (l + 1), wprec, [rows, fo])
+            body.append(loops([(ib, rows), (io, fo)], Set(out, (ib, io), un("relu", acc() + b[io]))))
+        H.append(out)
+    C = dims[-1]
+    logits = H[-1]
+    max_l = r.tn("max_l", "single", [rows, 1])
+    expv = r.tn("exp_vals", "single", [rows, C])
+    ssum = r.tn("sum_exp", "single", [rows, 1])
+    loss = r.tn("loss", "single", [1])
+    ib, ic = r.syms(2)
+    body.append(loops([(ib, rows)], Set(max_l, (ib, 0), reduce_scope(r, "n_max", "single", [(ic, C)], lambda: logits[ib, ic], op="max"))))
+    ib, ic = r.syms(2)
+    body.append(loops([(ib, rows), (ic, C)], Set(expv, (ib, ic), un("exp", logits[ib, ic] - max_l[ib, 0]))))
+    ib, ic = r.syms(2)
+    body.append(loops([(ib, rows)], Set(ssum, (ib, 0), reduce_scope(r, "n_sum", "single", [(ic, C)], lambda: expv[ib, ic], op="add"))))
+    ib, ic = r.syms(2)
+    body.append(Set(loss, (0,), un("neg", reduce_scope(
+        r, "n_ce", "single", [(ib, rows), (ic, C)], lambda: labels[ib, ic] * un("log", expv[ib, ic] / ssum[ib, 0]), op="add")) / float(rows)))
+    # ---- zero grads and backprop
+    body.append(Comment("zero grads and backprop"))
+    gW = [r.tn(w.ident + "_grad", "single", w.dims) for w in W_]
+    gB = [r.tn(b.ident + "_grad", "single", b.dims) if b is not None else None for b in Bv]
+    dH = [None] + [r.tn("h%d_grad" % l, "single", [rows, dims[l]]) for l in range(1, n_layers)]
+    for g in gW + [g for g in gB if g is not None] + [d for d in dH if d is not None]:
+        body.append(ZeroOut(g))
+    dz = r.tn("logits_grad", wprec, [rows, C])
+    ib, ic = r.syms(2)
+    body.append(loops([(ib, rows), (ic, C)], Set(dz, (ib, ic), (expv[ib, ic] / ssum[ib, 0] - labels[ib, ic]) / float(rows))))
+    for l in reversed(range(n_layers)):
+        fi, fo = dims[l], dims[l + 1]
+        w, gw, hin = W_[l], gW[l], H[l]
+        if gB[l] is not None:
+            ib, io = r.syms(2)
+            body.append(loops([(ib, rows), (io, fo)], Set(gB[l], (io,), gB[l][io] + dz[ib, io])))
+        ib, io, ii = r.syms(3)
+        dzz = dz
+        body.append(loops([(ib, rows), (io, fo), (ii, fi)], Set(gw, (io, ii), fma(dzz[ib, io], hin[ib, ii], gw[io, ii]))))
+        if l > 0:
+            ib, io, ii = r.syms(3)
+            body.append(loops([(ib, rows), (io, fo), (ii, fi)], Set(dH[l], (ib, ii), fma(w[io, ii], dzz[ib, io], dH[l][ib, ii]))))
+            ndz = r.tn("z%d_grad" % l, wprec, [rows, fi])
+            ib, ii = r.syms(2)
+            body.append(loops([(ib, rows), (ii, fi)], Set(ndz, (ib, ii), binop("relu_gate", hin[ib, ii], dH[l][ib, ii]))))
+            dz = ndz
+    body.append(Comment("end"))
+    r.body = Seq(body)
+    return r
+
+
+def mlp_sgd(dims=(784, 1024, 1024, 10), wprec="bfloat16") -> Routine:
+    """`Train.sgd_update` without momentum or weight decay: p =- learning_rate * p.grad per parameter."""
+    r = Routine("mlp_sgd")
+    lr = r.tn("learning_rate", "single", [1], read_only=True)
+    n_layers = len(dims) - 1
+    body: List = [Comment("sgd_update")]
+    for l in range(n_layers):
+        fi, fo = dims[l], dims[l + 1]
+        last = l == n_layers - 1
+        names = [("w_out" if last else "w%d" % (l + 1), [fo, fi])] + ([] if last else [("b%d" % (l + 1), [fo])])
+        for name, d in names:
+            p = r.tn(name, wprec, d)
+            g = r.tn(name + "_grad", "single", d, read_only=True)
+            syms = r.syms(len(d))
+            idx = tuple(syms)
+            body.append(loops(list(zip(syms, d)), Set(p, idx, Get(p, idx) - lr[0] * Get(g, idx))))
+    body.append(Comment("end"))
+    r.body = Seq(body)
+    return r
+
+
+MLP_PARAM_NAMES = ("w1", "b1", "w2", "b2", "w_out")
