@@ -77,6 +77,16 @@ class ClockSampler:
                 self.proc.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
+        if not self.rows:
+            # the timed region was shorter than one sampling period: take one reading now
+            try:
+                q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+                     "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q,
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=20).stdout
+                self.rows = [[c.strip() for c in line.split(",")] for line in out.splitlines() if line.strip()]
+            except (OSError, subprocess.SubprocessError):
+                pass
         sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
         mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
@@ -270,6 +280,48 @@ def other_configs(dev, pk):
     return res
 
 
+def train_step(dev, dist, rank, world, rows, K, Wm):
+    """Config 5 (ii): per shard forward + backward, one NCCL allreduce (average) over the
+    contiguous fp32 gradient range, local SGD on every replica.  Max over ranks of the
+    CUDA-event time of K steps."""
+    from ocannl_b200 import parallel as par
+    from ocannl_b200 import workloads as W
+    rep = par.DeviceReplica(dev, W.mlp_train_update(rows=rows, dims=DIMS), W.mlp_sgd(dims=DIMS), W.MLP_PARAM_NAMES)
+    if world > 1:
+        box = [par.NcclExchange.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        ex = par.NcclExchange(dev, world, rank, box[0])
+    else:
+        ex = par.LocalExchange()
+    h = par.DataParallel(rep, ex, "mean", input_ident="x", target_ident="labels")
+    x, onehot = W.mlp_inputs(rows=rows, seed=20 + rank, label_seed=21 + rank)
+    rep.set_values(dict(W.mlp_params(dims=DIMS), x=x, labels=onehot, learning_rate=np.float32([0.01])))
+    for _ in range(Wm):
+        h.step()
+    dev.await_()
+    if dist is not None:
+        dist.barrier()
+    e0 = dev.all_work()
+    for _ in range(K):
+        h.step()
+    e1 = dev.all_work()
+    e1.sync()
+    ms = e0.elapsed_ms(e1)
+    if dist is not None:
+        import torch
+        t = torch.tensor([ms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    loss = h.owner_loss_value()
+    pool, off, count = rep.grad_range
+    kernels = rep.update.kernels_per_run() + rep.sgd.kernels_per_run()
+    if world > 1:
+        ex.free()
+    return {"samples_per_s": rows * world * K / (ms / 1e3), "ms_per_step": ms / K, "allreduce_bytes": int(count) * 4,
+            "exchange": "ncclAllReduce(avg, fp32) over one contiguous gradient range" if world > 1 else "none (1 shard)",
+            "kernels_per_step": int(kernels), "loss_after": loss}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -279,6 +331,7 @@ def main():
     ap.add_argument("--rows", type=int, default=8192, help="rows of the batch each GPU processes per step")
     ap.add_argument("--ref-rows", type=int, default=512)
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-train", action="store_true", help="skip the forward+backward+allreduce+SGD section")
     ap.add_argument("--no-configs", action="store_true", help="skip the configs 1, 2 and 4 section")
     ap.add_argument("--sweep-size", type=int, default=0,
                     help="run only the batch-8 contraction of this M=N=K (a small case for profilers) and exit")
@@ -347,12 +400,12 @@ def main():
         return float(t[0])
 
     # ---- device-resident forward
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()          # runs through warm-up, the timed steps and the end-to-end steps
     for _ in range(Wm):
         rt.run()
     barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     ms = timed(rt.run, K)
     barrier()
     ms = max_over_ranks(ms)
@@ -402,6 +455,8 @@ def main():
                 "stage_ms": [round(s, 5) for s in shares]}
     rt.profile(False)
 
+    train = None if args.no_train else train_step(dev, dist, rank, world, rows, K, Wm)
+
     if rank != 0:
         return
     line = {
@@ -419,13 +474,15 @@ def main():
         "gpu_launches": int(rt.kernels_per_run()) * K,
         "clocks": clocks, "roofline": roofline, "loss": loss_value,
     }
+    if train is not None:
+        line["train_step"] = train
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline()
     if world == 1 and not args.no_sweep:
         line["contraction_sweep"] = contraction_sweep(dev, pk)
     if world == 1 and not args.no_configs:
         line["configs"] = other_configs(dev, pk)
-    print(json.dumps(line))
+    print(json.dumps(line), flush=True)
 
 
 if __name__ == "__main__":
