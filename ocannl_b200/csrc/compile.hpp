@@ -58,6 +58,7 @@ struct Stage {
   std::string epi_params, epi_args;  // epilogue plumbing: extra kernel parameters / call arguments
   int tile_m = 0, tile_n = 0, tile_k = 0;
   int smem_bytes = 0;            // dynamic shared memory of the contraction kernel
+  int epi_out_bytes = 4;         // widest element the epilogue stores through the staging tile (2 or 4)
   int epi_tiles = 0;             // register tiles (inputs + outputs) the epilogue keeps per chunk
   std::string note;              // human-readable classification, for debug info
 };

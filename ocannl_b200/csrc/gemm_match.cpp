@@ -543,7 +543,11 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
   }
   if (em.uses_merge) return false;
 
-  fn << "__device__ __forceinline__ void b200_tmem_ld_chunk(unsigned int taddr, unsigned int* r);\n"
+  fn << "#ifdef B200_TRACE\n__device__ unsigned int* b200_trace_ptr;\n__device__ unsigned long long b200_trace_t0;\n"
+        "__device__ int b200_trace_on;\n__device__ __forceinline__ unsigned long long b200_now_ns();\n"
+        "#define B200_TRE(slot) do { if (blockIdx.x == 0 && threadIdx.x == 64 && b200_trace_on) b200_trace_ptr[slot] = (unsigned int)(b200_now_ns() - b200_trace_t0); } while (0)\n"
+        "#else\n#define B200_TRE(slot) do { } while (0)\n#endif\n"
+     << "__device__ __forceinline__ void b200_tmem_ld_chunk(unsigned int taddr, unsigned int* r);\n"
      << "__device__ __forceinline__ void b200_epilogue_row(unsigned int* b200_r, unsigned int b200_b0, unsigned int b200_b1, "
         "unsigned int b200_m, bool b200_row_ok, unsigned int b200_n0, unsigned int b200_N, uint4* b200_stage, "
         "bool b200_has_next, unsigned int b200_next_taddr"
@@ -568,7 +572,7 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
   recover(dn, "b200_n");
   fn << ep.str() << body << "    }\n  }\n";
   // the accumulator chunk is consumed: start fetching the next one while this one is stored
-  fn << "  if (b200_has_next) b200_tmem_ld_chunk(b200_next_taddr, b200_r);\n";
+  fn << "  B200_TRE(13);\n  if (b200_has_next) b200_tmem_ld_chunk(b200_next_taddr, b200_r);\n";
   // ---- store the register tiles.  A thread owns one row of the chunk, so storing from
   //      registers would touch 32 different lines per instruction; when the chunk is whole,
   //      contiguous and every row is 16-byte aligned, the warp transposes the chunk through a
@@ -596,7 +600,7 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
              << "        q.w = (unsigned int)" << o.arr << "[8 * g + 6] | ((unsigned int)" << o.arr << "[8 * g + 7] << 16);\n";
         }
         fn << "        b200_stage[b200_lane * G + (g ^ (b200_lane % G))] = q;\n      }\n"
-           << "      __syncwarp();\n"
+           << "      __syncwarp();\n      B200_TRE(14);\n"
            << "      const unsigned long long b200_pv = (unsigned long long)b200_p;\n"
            << "#pragma unroll\n      for (int it = 0; it < G; ++it) {\n"
            << "        const unsigned int r = it * (32 / G) + b200_lane / G, c = b200_lane % G;\n"
@@ -620,7 +624,7 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
       fn << ep.str() << "      " << t.ident << "[" << em.offset(o.idcs, t.dims) << "] = " << o.arr << "[b200_j];\n    }\n  }\n";
     }
   }
-  fn << "}\n";
+  fn << "  B200_TRE(15);\n}\n";
 
   out->kind = Stage::Gemm;
   out->gemm = g;
@@ -628,6 +632,8 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
   out->args = kargs;
   out->total = 1;
   out->epi_tiles = (int)outs.size() + n_in_tiles;
+  out->epi_out_bytes = 2;
+  for (auto& o : outs) out->epi_out_bytes = std::max(out->epi_out_bytes, std::min(4, prec_bytes(P.tn(o.tn).prec)));
   out->epi_params = params;
   out->epi_args = args;
   return true;
@@ -645,9 +651,15 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   const int bm = 128, bk = row_elems;
   const int umma_k = 32 / eb;
   const int stage_bytes = (bm + bn) * bk * eb;
-  const int epi_warps = bn >= 128 ? 8 : 4;
-  // 227 KB per CTA: ring + alignment slack + barriers + one 4 KB staging tile per epilogue warp
-  int stages = (227 * 1024 - 1024 - 256 - epi_warps * 4096) / stage_bytes;
+  // Epilogue width: the epilogue is a chain of dependent instructions per warp, so it is bound
+  // by latency, not issue rate; light epilogues (few register tiles) get 16 warps, which fits
+  // the register file at <= 112 registers per thread.
+  const int chunk = (bn >= 32 && st.epi_tiles <= 2) ? 32 : 16;
+  const bool light = st.epi_tiles <= 2 && bn >= 256;
+  const int epi_warps = light ? 16 : (bn >= 128 ? 8 : 4);
+  const int staging = 32 * chunk * st.epi_out_bytes;   // per warp
+  // 227 KB per CTA: ring + alignment slack + barriers + one staging tile per epilogue warp
+  int stages = (227 * 1024 - 1024 - 256 - epi_warps * staging) / stage_bytes;
   if (stages > 8) stages = 8;
   if (stages < 2) stages = 2;
   int tmem_cols = 32;
@@ -666,7 +678,7 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
     << "u\n#define B200_TMEM_COLS " << tmem_cols << "\n#define B200_RASTER 8\n";
   // columns per epilogue step: 32 when the epilogue keeps few register tiles, else 16 so that
   // the tiles and the double-buffered accumulator chunk stay in registers
-  o << "#ifndef B200_EPI_CHUNK\n#define B200_EPI_CHUNK " << ((bn >= 32 && st.epi_tiles <= 2) ? 32 : 16) << "\n#endif\n";
+  o << "#define B200_EPI_CHUNK " << chunk << "\n#define B200_STAGING_BYTES " << staging << "\n";
   o << g.epilogue << "\n";
   o << "#define B200_EPI_PARAMS " << params << "\n";
   o << "#define B200_EPILOGUE_ROW b200_epilogue_row(b200_r, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_n0, shape.N, b200_stage, b200_has_next, b200_next_taddr" << args << ");\n";
@@ -680,7 +692,7 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   st.tile_m = bm;
   st.tile_n = bn;
   st.tile_k = bk;
-  st.smem_bytes = stages * stage_bytes + 1024 + 256 + epi_warps * 4096;
+  st.smem_bytes = stages * stage_bytes + 1024 + 256 + epi_warps * staging;
   return o.str();
 }
 

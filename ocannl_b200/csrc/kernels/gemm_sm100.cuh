@@ -19,7 +19,8 @@
 //   B200_UMMA_K               k elements per tcgen05.mma (16 for 16-bit inputs, 8 for tf32)
 //   B200_ELEM_BYTES           operand element size
 //   B200_STAGES               ring depth
-//   B200_EPI_WARPS            4 or 8
+//   B200_EPI_WARPS            4, 8 or 16 (a multiple of 4: one warp per TMEM lane quarter and column part)
+//   B200_STAGING_BYTES        bytes of the per-warp staging tile (32 rows x chunk columns of the widest output)
 //   B200_A_KMAJOR/B_KMAJOR    1: k is the contiguous axis of the operand, 0: m/n is
 //   B200_IDESC                tcgen05 instruction descriptor (formats, majors, M, N)
 //   B200_TMEM_COLS            power of two >= 2*B200_BN (and >= 32)
@@ -163,6 +164,14 @@ __device__ __forceinline__ void b200_tmem_ld_chunk(unsigned int taddr, unsigned 
 #endif
 }
 
+// Developer aid: with -DB200_TRACE, CTA 0 records nanoseconds since its start at a few points
+// into words 2..15 of the device status buffer (printed by the host when B200_TRACE is set).
+#ifdef B200_TRACE
+#define B200_TR(slot) do { if (blockIdx.x == 0) status[slot] = (unsigned int)(b200_now_ns() - b200_t0); } while (0)
+#else
+#define B200_TR(slot) do { } while (0)
+#endif
+
 #define B200_A_TILE_BYTES (B200_BM * B200_BK * B200_ELEM_BYTES)
 #define B200_B_TILE_BYTES (B200_BN * B200_BK * B200_ELEM_BYTES)
 #define B200_STAGE_BYTES (B200_A_TILE_BYTES + B200_B_TILE_BYTES)
@@ -199,6 +208,10 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
 
   const unsigned int warp = threadIdx.x >> 5;
   const unsigned int lane = threadIdx.x & 31u;
+#ifdef B200_TRACE
+  const unsigned long long b200_t0 = b200_now_ns();
+  if (blockIdx.x == 0 && threadIdx.x == 64) { b200_trace_ptr = status; b200_trace_t0 = b200_t0; b200_trace_on = 0; }
+#endif
 
   if (threadIdx.x == 0) {
     for (unsigned int s = 0; s < B200_STAGES; ++s) {
@@ -222,6 +235,7 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned int tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) B200_TR(2);   // set-up done
 
   const unsigned int tiles_per_batch = shape.tiles_m * shape.tiles_n;
   const unsigned int total_tiles = tiles_per_batch * shape.B0 * shape.B1;
@@ -267,9 +281,11 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
             b200_tma_load_4d(sb + c * (B200_ROW_ELEMS * B200_BK * B200_ELEM_BYTES), &map_b, full, n0 + c * B200_ROW_ELEMS, k0,
                              (int)(b1 * shape.b_b1), (int)(b0 * shape.b_b0));
 #endif
+          if (tile == blockIdx.x && kb == 0) B200_TR(3);   // first loads issued
           if (++slot == B200_STAGES) { slot = 0; phase ^= 1u; }
         }
       }
+      B200_TR(4);   // producer done
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
@@ -283,6 +299,7 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
         for (unsigned int kb = 0; kb < k_blocks; ++kb) {
           if (!b200_wait(bar_full + 8u * slot, phase, abort_flag, status, 3u)) { live = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          if (tile == blockIdx.x && kb == 0) B200_TR(5);   // first operands landed
           const unsigned int sa = tiles_at + slot * B200_STAGE_BYTES;
           const unsigned int sb = sa + B200_A_TILE_BYTES;
 #pragma unroll
@@ -309,6 +326,8 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
           if (++slot == B200_STAGES) { slot = 0; phase ^= 1u; }
         }
         if (live) b200_umma_commit(bar_acc_full + 8u * acc);
+        if (tile == blockIdx.x) B200_TR(6);                  // tile 0 MMAs issued
+        else if (tile == blockIdx.x + gridDim.x) B200_TR(7); // tile 1 MMAs issued
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
     }
@@ -316,10 +335,10 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
     // ------------------------------------------------------------------ epilogue
     const unsigned int ew = warp - 2;                 // 0 .. EPI_WARPS-1
     const unsigned int quarter = warp & 3u;           // TMEM lanes this warp may read
-    const unsigned int col_half = ew >> 2;            // with 8 warps, two warps share a quarter
+    const unsigned int col_half = ew >> 2;            // which part of the tile's columns this warp owns
     const unsigned int cols_per_warp = B200_BN / (B200_EPI_WARPS / 4);
     // this warp's 4 KB staging tile (transposes a chunk so that stores cover whole row segments)
-    uint4* b200_stage = (uint4*)(smem_gen + B200_STAGES * B200_STAGE_BYTES + 256 + ew * 4096u);
+    uint4* b200_stage = (uint4*)(smem_gen + B200_STAGES * B200_STAGE_BYTES + 256 + ew * (unsigned int)B200_STAGING_BYTES);
     unsigned int acc = 0, acc_phase = 0;
     for (unsigned int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       const unsigned int bidx = tile / tiles_per_batch;
@@ -333,6 +352,7 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
       const unsigned int b200_b0 = bidx / shape.B1, b200_b1 = bidx - b200_b0 * shape.B1;
       if (!b200_wait(bar_acc_full + 8u * acc, acc_phase, abort_flag, status, 4u)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (warp == 2 && lane == 0) { if (tile == blockIdx.x) B200_TR(8); else if (tile == blockIdx.x + gridDim.x) B200_TR(10); }
       const unsigned int b200_m = mt * B200_BM + quarter * 32u + lane;
       const unsigned int taddr = tmem_base + acc * B200_BN + ((quarter * 32u) << 16);
       // One register buffer: the epilogue issues the TMEM load of the next chunk as soon as it
@@ -347,6 +367,10 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
         const unsigned int b200_n0 = nt * B200_BN + col;
         if (b200_n0 >= shape.N) break;  // warp-uniform
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#ifdef B200_TRACE
+        if (blockIdx.x == 0 && threadIdx.x == 64) { b200_trace_on = (tile == blockIdx.x && c == B200_EPI_CHUNK) ? 1 : 0; }
+        B200_TRE(4);
+#endif
         const bool b200_has_next = (c + B200_EPI_CHUNK < cols_per_warp) && (b200_n0 + B200_EPI_CHUNK < shape.N);
         const unsigned int b200_next_taddr = taddr + col + B200_EPI_CHUNK;
         // every lane takes part: rows beyond M compute nothing but help move the chunk
@@ -355,6 +379,7 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) b200_mbar_arrive(bar_acc_empty + 8u * acc);
+      if (warp == 2 && lane == 0) { if (tile == blockIdx.x) B200_TR(9); else if (tile == blockIdx.x + gridDim.x) B200_TR(11); }
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
   }
@@ -368,6 +393,7 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (threadIdx.x == 0) B200_TR(12);  // all roles done
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned int)B200_TMEM_COLS)

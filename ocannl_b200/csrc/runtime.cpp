@@ -9,6 +9,8 @@
 #include "runtime.hpp"
 
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 using namespace b200;
@@ -26,6 +28,12 @@ CUdeviceptr b200_dev::address(int pool_id, size_t offset, size_t bytes) {
 }
 
 void b200_dev::check_status() {
+  if (status_host && getenv("B200_TRACE")) {
+    fprintf(stderr, "[b200 trace] ns since CTA 0 start: setup %u, first loads issued %u, producer done %u, first operands %u, "
+                    "tile0 mma issued %u, tile1 mma issued %u, epi0 begin %u end %u, epi1 begin %u end %u, all done %u | chunk1: tmem ready %u, computed %u, staged %u, stored %u\n",
+            status_host[2], status_host[3], status_host[4], status_host[5], status_host[6], status_host[7], status_host[8],
+            status_host[9], status_host[10], status_host[11], status_host[12], status_host[4], status_host[13], status_host[14], status_host[15]);
+  }
   if (status_host && status_host[0] != 0) {
     unsigned int code = status_host[0], where = status_host[1];
     status_host[0] = 0;
