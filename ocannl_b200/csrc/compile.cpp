@@ -402,7 +402,7 @@ struct Builder {
     rec(*set.value);
     Emitter::Res v = eb.scalar(t.prec, *set.value);
     eb.used_nodes.insert(set.tn);
-    pass2 += "  if (threadIdx.x == 0) " + t.ident + "[" + eb.offset(set.idcs, t.dims) + "] = " + v.expr + ";\n";
+    pass2 += "  if (threadIdx.x == 0) " + t.ident + "[" + eb.offset(set.idcs, t.dims) + "] = " + Emitter::store_wrap(t.prec, v.expr) + ";\n";
 
     std::set<int> none, written = {set.tn};
     std::ostringstream ka, kb;
@@ -668,7 +668,7 @@ struct Builder {
         em.used_nodes.insert(t.id);
         written.insert(t.id);
         text += "  for (unsigned int b200_z = threadIdx.x; b200_z < " + std::to_string(t.num_elems()) +
-                "u; b200_z += blockDim.x) " + t.ident + "[b200_z] = " + em.constant(0.0, t.prec) + ";\n";
+                "u; b200_z += blockDim.x) " + t.ident + "[b200_z] = " + em.storage_zero(t.prec) + ";\n";
       } else {
         const Piece& pc = pieces[i];
         em.used_nodes.insert(pc.used.begin(), pc.used.end());
@@ -786,7 +786,7 @@ struct Builder {
     rec(*set.value);
     Emitter::Res v = em.scalar(t.prec, *set.value);
     em.used_nodes.insert(set.tn);
-    out += padding + "if (b200_t == 0) " + t.ident + "[" + em.offset(set.idcs, t.dims) + "] = " + v.expr + ";\n";
+    out += padding + "if (b200_t == 0) " + t.ident + "[" + em.offset(set.idcs, t.dims) + "] = " + Emitter::store_wrap(t.prec, v.expr) + ";\n";
     em.scope_subst.clear();
     return out;
   }

@@ -20,9 +20,27 @@ bool same_indices(const Indices& a, const Indices& b) {
 }
 std::string pad(int n) { return std::string((size_t)n, ' '); }
 bool lowp(Prec p) { return p == Prec::Bfloat16 || p == Prec::Half; }
-const char* up_fn(Prec p) { return p == Prec::Bfloat16 ? "b200_bf2f(" : "b200_h2f("; }
-const char* down_fn(Prec p) { return p == Prec::Bfloat16 ? "b200_f2bf(" : "b200_f2h("; }
+// Inside expressions a bf16 / half value is a FLOAT that holds a value representable in that
+// format ("rounded float"): one rounding step per operation, no unpack / repack between
+// operations.  Storage stays 16 bits; loads widen, stores take the (already exact) 16 bits.
+const char* round_fn(Prec p) { return p == Prec::Bfloat16 ? "b200_rbf(" : "b200_rhf("; }
 }  // namespace
+
+const char* Emitter::rtype(Prec p) { return lowp(p) ? "float" : ctype(p); }
+std::string Emitter::load_wrap(Prec p, const std::string& e) {
+  if (p == Prec::Bfloat16) return "b200_bf2f(" + e + ")";
+  if (p == Prec::Half) return "b200_h2f(" + e + ")";
+  return e;
+}
+std::string Emitter::store_wrap(Prec p, const std::string& e) {
+  if (p == Prec::Bfloat16) return "b200_bfbits(" + e + ")";
+  if (p == Prec::Half) return "b200_f2h(" + e + ")";
+  return e;
+}
+std::string Emitter::storage_zero(Prec p) {
+  if (lowp(p)) return "((unsigned short)0)";
+  return constant(0.0, p);
+}
 
 const char* Emitter::ctype(Prec p) {
   switch (p) {
@@ -54,25 +72,15 @@ std::pair<std::string, std::string> Emitter::convert(Prec from, Prec to) {
     return p == Prec::Byte || p == Prec::Uint16 || p == Prec::Int32 || p == Prec::Uint32 || p == Prec::Int64 ||
            p == Prec::Uint64;
   };
-  if (from == Prec::Bfloat16) {
-    if (to == Prec::Single) return {"b200_bf2f(", ")"};
-    if (to == Prec::Double) return {"(double)b200_bf2f(", ")"};
-    if (to == Prec::Half) return {"b200_f2h(b200_bf2f(", "))"};
-    return {std::string("(") + ctype(to) + ")b200_bf2f(", ")"};
+  if (lowp(from)) {
+    if (to == Prec::Single) return {"", ""};                       // already a float
+    if (to == Prec::Double) return {"(double)(", ")"};
+    if (lowp(to)) return {round_fn(to), ")"};                      // bf16 <-> half
+    return {std::string("(") + ctype(to) + ")(", ")"};
   }
-  if (to == Prec::Bfloat16) {
-    if (from == Prec::Single) return {"b200_f2bf(", ")"};
-    if (from == Prec::Half) return {"b200_f2bf(b200_h2f(", "))"};
-    return {"b200_f2bf((float)", ")"};  // double and the integer types
-  }
-  if (from == Prec::Half) {
-    if (to == Prec::Single) return {"b200_h2f(", ")"};
-    if (to == Prec::Double) return {"(double)b200_h2f(", ")"};
-    return {std::string("(") + ctype(to) + ")b200_h2f(", ")"};
-  }
-  if (to == Prec::Half) {
-    if (from == Prec::Single) return {"b200_f2h(", ")"};
-    return {"b200_f2h((float)", ")"};
+  if (lowp(to)) {
+    if (from == Prec::Single) return {round_fn(to), ")"};
+    return {std::string(round_fn(to)) + "(float)(", "))"};        // double and the integer types
   }
   (void)is_plain_int;
   return {std::string("(") + ctype(to) + ")(", ")"};
@@ -131,21 +139,23 @@ std::string Emitter::constant(double c, Prec prec) {
     }
     if (prec == Prec::Single) return lit;
     // 16-bit constants are rounded here, once, instead of per element on the device
-    unsigned int bits16;
+    float rounded;
     const float f = (float)c;
     if (prec == Prec::Bfloat16) {
       unsigned int u;
       memcpy(&u, &f, 4);
       u += 0x7FFFu + ((u >> 16) & 1u);  // arrayjit/lib/builtins.c:620-627
-      bits16 = u >> 16;
+      u &= 0xFFFF0000u;
+      memcpy(&rounded, &u, 4);
     } else {
-      _Float16 h = (_Float16)f;
-      unsigned short hb;
-      memcpy(&hb, &h, 2);
-      bits16 = hb;
+      rounded = (float)(_Float16)f;
     }
-    snprintf(buf, sizeof buf, "((unsigned short)0x%04xu)", bits16 & 0xFFFFu);
-    return buf;
+    if (std::isinf(rounded)) return rounded > 0 ? "B200_INF" : "(-B200_INF)";
+    if (std::isnan(rounded)) return "B200_NAN";
+    snprintf(buf, sizeof buf, "%a", (double)rounded);
+    lit = std::string(buf) + "f";
+    if (rounded < 0) lit = "(" + lit + ")";
+    return lit;
   }
   if (prec == Prec::Double) {
     if (std::isinf(c)) return c > 0 ? "((double)B200_INF)" : "(-(double)B200_INF)";
@@ -231,9 +241,17 @@ static std::string ternop_plain(Prec prec, const std::string& op, const std::str
   throw Error(-4, "unsupported ternary operation '" + op + "'");
 }
 
+// Operations whose result, for arguments that are already values of a 16-bit format, is again
+// such a value (one of the arguments, its sign flip or truncation, or 0 / 1): no rounding step.
+static bool selects_exactly(const std::string& op) {
+  static const std::set<std::string> k = {"relu_gate", "sat01_gate", "max", "min", "lt", "eq", "ne", "or", "and",
+                                          "relu", "sat01", "neg", "trunc", "not", "where"};
+  return k.count(op) != 0;
+}
+
 std::string Emitter::binop(Prec prec, const std::string& op, const std::string& a, const std::string& b) {
-  if (lowp(prec))
-    return std::string(down_fn(prec)) + binop_plain(Prec::Single, op, up_fn(prec) + a + ")", up_fn(prec) + b + ")") + ")";
+  if (lowp(prec) && selects_exactly(op)) return binop_plain(Prec::Single, op, a, b);
+  if (lowp(prec)) return std::string(round_fn(prec)) + binop_plain(Prec::Single, op, a, b) + ")";
   return binop_plain(prec, op, a, b);
 }
 std::string Emitter::unop(Prec prec, const std::string& op, const std::string& a) {
@@ -241,22 +259,19 @@ std::string Emitter::unop(Prec prec, const std::string& op, const std::string& a
     // a 16-bit result keeps 8 (bf16) or 11 (half) significant bits: the hardware
     // approximations of tanh / exp / log (relative error below 2^-10) round to the same value
     // as the libm functions except for rare one-unit differences in the last kept bit
-    const std::string x = up_fn(prec) + a + ")";
-    if (op == "tanh") return std::string(down_fn(prec)) + "b200_tanh_fast(" + x + "))";
-    if (op == "exp") return std::string(down_fn(prec)) + "__expf(" + x + "))";
-    if (op == "log") return std::string(down_fn(prec)) + "__logf(" + x + "))";
-    return std::string(down_fn(prec)) + unop_plain(Prec::Single, op, x) + ")";
+    if (op == "id") return a;
+    if (selects_exactly(op)) return unop_plain(Prec::Single, op, a);
+    if (op == "tanh") return std::string(round_fn(prec)) + "b200_tanh_fast(" + a + "))";
+    if (op == "exp") return std::string(round_fn(prec)) + "__expf(" + a + "))";
+    if (op == "log") return std::string(round_fn(prec)) + "__logf(" + a + "))";
+    return std::string(round_fn(prec)) + unop_plain(Prec::Single, op, a) + ")";
   }
   return unop_plain(prec, op, a);
 }
 std::string Emitter::ternop(Prec prec, const std::string& op, const std::string& a, const std::string& b,
                             const std::string& c) {
-  if (lowp(prec)) {
-    // `where` in a low-precision context: the condition was rendered in its own precision
-    // and is converted like the arms (cc_backend.ml:169-186 wraps all three arguments).
-    return std::string(down_fn(prec)) +
-           ternop_plain(Prec::Single, op, up_fn(prec) + a + ")", up_fn(prec) + b + ")", up_fn(prec) + c + ")") + ")";
-  }
+  if (lowp(prec) && selects_exactly(op)) return ternop_plain(Prec::Single, op, a, b, c);
+  if (lowp(prec)) return std::string(round_fn(prec)) + ternop_plain(Prec::Single, op, a, b, c) + ")";
   return ternop_plain(prec, op, a, b, c);
 }
 
@@ -328,7 +343,7 @@ Emitter::Res Emitter::scalar(Prec prec, const Scalar& e) {
       }
       std::string init;
       if (reads_scope_before_set(e.scope_id, e.tn, *e.body)) init = " = " + constant(0.0, sp);
-      std::string def = std::string(ctype(sp)) + " " + scope_name(e.scope_id, e.tn) + init + ";\n" + stmt(*e.body, 0);
+      std::string def = std::string(rtype(sp)) + " " + scope_name(e.scope_id, e.tn) + init + ";\n" + stmt(*e.body, 0);
       r.defs.push_back({e.scope_id, def});
       r.expr = cv.first + scope_name(e.scope_id, e.tn) + cv.second;
       return r;
@@ -353,14 +368,14 @@ Emitter::Res Emitter::scalar(Prec prec, const Scalar& e) {
         used_nodes.insert(e.tn);
         for (auto& lt : load_tiles)
           if (lt.tn == e.tn && same_indices(lt.idcs, e.idcs)) {
-            r.expr = cv.first + lt.expr + cv.second;
+            r.expr = cv.first + load_wrap(t.prec, lt.expr) + cv.second;   // tiles hold storage bits
             return r;
           }
       } else {
         uses_merge = true;
       }
       std::string name = e.kind == Scalar::GetMerge ? "merge_buffer" : t.ident;
-      r.expr = cv.first + name + "[" + offset(e.idcs, t.dims) + "]" + cv.second;
+      r.expr = cv.first + load_wrap(t.prec, name + "[" + offset(e.idcs, t.dims) + "]") + cv.second;
       return r;
     }
     case Scalar::GetDyn: {
@@ -370,7 +385,7 @@ Emitter::Res Emitter::scalar(Prec prec, const Scalar& e) {
       used_nodes.insert(e.tn);
       std::string dyn = std::string("((") + (large_models ? "unsigned long long" : "unsigned int") + ")(" + d.expr + "))";
       r.defs = d.defs;
-      r.expr = cv.first + t.ident + "[" + offset(e.idcs, t.dims, e.dyn_axis, dyn) + "]" + cv.second;
+      r.expr = cv.first + load_wrap(t.prec, t.ident + "[" + offset(e.idcs, t.dims, e.dyn_axis, dyn) + "]") + cv.second;
       return r;
     }
     case Scalar::Const: r.expr = constant(e.cval, prec); return r;
@@ -394,7 +409,7 @@ Emitter::Res Emitter::scalar(Prec prec, const Scalar& e) {
         Res a = scalar(prec, *e.args[0].s);
         r.defs = a.defs;
         const std::string fn = e.args[1].s->cval == 2.0 ? "b200_pow2(" : "b200_pow3(";
-        if (lowp(prec)) r.expr = std::string(down_fn(prec)) + fn + up_fn(prec) + a.expr + ")))";
+        if (lowp(prec)) r.expr = std::string(round_fn(prec)) + fn + a.expr + "))";
         else r.expr = fn + a.expr + ")";
         return r;
       }
@@ -420,9 +435,6 @@ Emitter::Res Emitter::scalar(Prec prec, const Scalar& e) {
       if (is_where) {
         // the condition keeps its own precision: compare it there, select in `prec`
         std::string cond = a.expr;
-        Prec cp = e.args[0].prec;
-        if (cp == Prec::Bfloat16) cond = "b200_bf2f(" + cond + ")";
-        else if (cp == Prec::Half) cond = "b200_h2f(" + cond + ")";
         r.expr = "((" + cond + ") != 0 ? (" + b.expr + ") : (" + c.expr + "))";
       } else {
         r.expr = ternop(prec, e.op, a.expr, b.expr, c.expr);
@@ -487,14 +499,14 @@ std::string Emitter::stmt(const Stmt& s, int ind) {
       std::string n = std::to_string(t.num_elems());
       std::string v = "b200_z" + std::to_string(tmp_counter++);
       return pad(ind) + "for (unsigned int " + v + " = 0; " + v + " < " + n + "; ++" + v + ") " + t.ident + "[" + v +
-             "] = " + constant(0.0, t.prec) + ";\n";
+             "] = " + storage_zero(t.prec) + ";\n";
     }
     case Stmt::Set: {
       const Tnode& t = P.tn(s.tn);
       if (t.mode == Mode::Virtual) throw Error(-3, "b200ir: write to virtual node '" + t.ident + "'");
       Res v = scalar(t.prec, *s.value);
       used_nodes.insert(s.tn);
-      std::string a = t.ident + "[" + offset(s.idcs, t.dims) + "] = " + v.expr + ";\n";
+      std::string a = t.ident + "[" + offset(s.idcs, t.dims) + "] = " + store_wrap(t.prec, v.expr) + ";\n";
       auto rd = set_redirect.find(s.tn);
       if (rd != set_redirect.end() && same_indices(rd->second.first, s.idcs)) a = rd->second.second + " = " + v.expr + ";\n";
       if (v.defs.empty()) return pad(ind) + a;
@@ -510,7 +522,7 @@ std::string Emitter::stmt(const Stmt& s, int ind) {
     }
     case Stmt::DeclareLocal: {
       Prec p = P.tn(s.tn).prec;
-      return pad(ind) + ctype(p) + " " + scope_name(s.scope_id, s.tn) + (s.needs_init ? " = " + constant(0.0, p) : "") + ";\n";
+      return pad(ind) + rtype(p) + " " + scope_name(s.scope_id, s.tn) + (s.needs_init ? " = " + constant(0.0, p) : "") + ";\n";
     }
   }
   return "";

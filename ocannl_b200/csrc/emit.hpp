@@ -48,7 +48,11 @@ struct Emitter {
 
   explicit Emitter(const Program& p) : P(p) {}
 
-  static const char* ctype(Prec p);
+  static const char* ctype(Prec p);   // storage type of a node
+  static const char* rtype(Prec p);   // type of a value of that precision inside an expression
+  static std::string load_wrap(Prec p, const std::string& storage_expr);
+  static std::string store_wrap(Prec p, const std::string& value_expr);
+  std::string storage_zero(Prec p);
   static std::pair<std::string, std::string> convert(Prec from, Prec to);
   std::string index(const Index& ix);
   std::string offset(const Indices& idcs, const std::vector<int64_t>& dims, int dyn_axis = -1,

@@ -13,6 +13,7 @@
 // is not fp32 (the cc backend would round every step, arrayjit/lib/cc_backend.ml:169-186),
 // strides the tensor maps cannot express — is left to the generic loop-nest kernels.
 #include <algorithm>
+#include <cstdlib>
 #include <functional>
 #include <set>
 #include <sstream>
@@ -344,7 +345,7 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
   // ---- operands of the epilogue that run along n (bias[n], mask[s, n], a residual x[b, s, n]):
   //      pre-loaded into a register tile with 16-byte loads, so that the per-column code has no
   //      dependent global load in it
-  std::string load_code;
+  std::string load_code, prefetch_code;
   int n_in_tiles = 0;
   std::set<int> not_loadable = {set.tn};
   auto collect_loads = [&](const Scalar& root, const std::map<std::string, std::string>* ren) {
@@ -398,6 +399,12 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
             lc << "      }\n    } else {\n#pragma unroll\n      for (int j = 0; j < B200_EPI_CHUNK; ++j) " << arr
                << "[j] = (b200_n0 + (unsigned int)j < b200_N) ? b200_p[j] : (" << T << ")0;\n    }\n  }\n";
             load_code += lc.str();
+            // the same lines, requested early (before the accumulator is ready) so that the
+            // loads above hit in L1 instead of paying an L2 round trip per chunk
+            prefetch_code += "    { const char* b200_q = (const char*)(" + t.ident + " + (" + em.offset(row, t.dims) +
+                             ") + b200_n0);\n      asm volatile(\"prefetch.global.L1 [%0];\" ::\"l\"(b200_q));\n"
+                             "      asm volatile(\"prefetch.global.L1 [%0];\" ::\"l\"(b200_q + B200_EPI_CHUNK * " +
+                             std::to_string(prec_bytes(t.prec)) + " - 1));\n    }\n";
             em.load_tiles.push_back({e.tn, e.idcs, arr + "[b200_j]"});
             em.used_nodes.insert(e.tn);
           }
@@ -543,6 +550,22 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
   }
   if (em.uses_merge) return false;
 
+  {
+    // parameters mirror the epilogue's so that the kernel can use one argument list
+    fn << "__device__ __forceinline__ void b200_epilogue_prefetch(unsigned int b200_b0, unsigned int b200_b1, "
+          "unsigned int b200_m, bool b200_row_ok, unsigned int b200_n0, unsigned int b200_N"
+       << params << ") {\n";
+    if (!prefetch_code.empty()) {
+      fn << statics_prologue;
+      ep.str("");
+      if (gb.size() == 2) { recover(gb[0], "b200_b0"); recover(gb[1], "b200_b1"); }
+      else if (gb.size() == 1) { recover(gb[0], "b200_b1"); }
+      recover(dm, "b200_m");
+      fn << ep.str() << unit_syms << "  if (b200_row_ok && b200_n0 < b200_N) {\n" << prefetch_code << "  }\n";
+      ep.str("");
+    }
+    fn << "}\n";
+  }
   fn << "#ifdef B200_TRACE\n__device__ unsigned int* b200_trace_ptr;\n__device__ unsigned long long b200_trace_t0;\n"
         "__device__ int b200_trace_on;\n__device__ __forceinline__ unsigned long long b200_now_ns();\n"
         "#define B200_TRE(slot) do { if (blockIdx.x == 0 && threadIdx.x == 64 && b200_trace_on) b200_trace_ptr[slot] = (unsigned int)(b200_now_ns() - b200_trace_t0); } while (0)\n"
@@ -564,7 +587,8 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
     ep.str("");
   }
   fn << unit_syms << load_code;
-  for (auto& o : outs) fn << "  " << Emitter::ctype(P.tn(o.tn).prec) << " " << o.arr << "[B200_EPI_CHUNK];\n";
+  // output tiles hold expression values (16-bit precisions as rounded floats); they are packed at the store
+  for (auto& o : outs) fn << "  " << Emitter::rtype(P.tn(o.tn).prec) << " " << o.arr << "[B200_EPI_CHUNK];\n";
   fn << "#pragma unroll\n  for (int b200_j = 0; b200_j < B200_EPI_CHUNK; ++b200_j) {\n"
      << "    const unsigned int b200_n = b200_n0 + (unsigned int)b200_j;\n"
      << "    if (b200_row_ok && b200_n < b200_N) {\n"
@@ -594,10 +618,11 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
           fn << "        q.x = b200_bits32(" << o.arr << "[4 * g]); q.y = b200_bits32(" << o.arr << "[4 * g + 1]);\n"
              << "        q.z = b200_bits32(" << o.arr << "[4 * g + 2]); q.w = b200_bits32(" << o.arr << "[4 * g + 3]);\n";
         } else {
-          fn << "        q.x = (unsigned int)" << o.arr << "[8 * g] | ((unsigned int)" << o.arr << "[8 * g + 1] << 16);\n"
-             << "        q.y = (unsigned int)" << o.arr << "[8 * g + 2] | ((unsigned int)" << o.arr << "[8 * g + 3] << 16);\n"
-             << "        q.z = (unsigned int)" << o.arr << "[8 * g + 4] | ((unsigned int)" << o.arr << "[8 * g + 5] << 16);\n"
-             << "        q.w = (unsigned int)" << o.arr << "[8 * g + 6] | ((unsigned int)" << o.arr << "[8 * g + 7] << 16);\n";
+          const std::string pk = t.prec == Prec::Bfloat16 ? "b200_pack_bf(" : "b200_pack_hf(";
+          fn << "        q.x = " << pk << o.arr << "[8 * g], " << o.arr << "[8 * g + 1]);\n"
+             << "        q.y = " << pk << o.arr << "[8 * g + 2], " << o.arr << "[8 * g + 3]);\n"
+             << "        q.z = " << pk << o.arr << "[8 * g + 4], " << o.arr << "[8 * g + 5]);\n"
+             << "        q.w = " << pk << o.arr << "[8 * g + 6], " << o.arr << "[8 * g + 7]);\n";
         }
         fn << "        b200_stage[b200_lane * G + (g ^ (b200_lane % G))] = q;\n      }\n"
            << "      __syncwarp();\n      B200_TRE(14);\n"
@@ -613,7 +638,7 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
         fn << "    if (b200_row_ok) {\n";
       }
       fn << "#pragma unroll\n      for (int b200_j = 0; b200_j < B200_EPI_CHUNK; ++b200_j)\n"
-         << "        if (b200_n0 + (unsigned int)b200_j < b200_N) b200_p[b200_j] = " << o.arr << "[b200_j];\n"
+         << "        if (b200_n0 + (unsigned int)b200_j < b200_N) b200_p[b200_j] = " << Emitter::store_wrap(t.prec, o.arr + "[b200_j]") << ";\n"
          << "    }\n  }\n";
     } else {
       // general position: recompute the offset per column
@@ -621,7 +646,7 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
          << "    const unsigned int b200_n = b200_n0 + (unsigned int)b200_j;\n    if (b200_row_ok && b200_n < b200_N) {\n";
       ep.str("");
       recover(dn, "b200_n");
-      fn << ep.str() << "      " << t.ident << "[" << em.offset(o.idcs, t.dims) << "] = " << o.arr << "[b200_j];\n    }\n  }\n";
+      fn << ep.str() << "      " << t.ident << "[" << em.offset(o.idcs, t.dims) << "] = " << Emitter::store_wrap(t.prec, o.arr + "[b200_j]") << ";\n    }\n  }\n";
     }
   }
   fn << "  B200_TRE(15);\n}\n";
@@ -654,8 +679,11 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   // Epilogue width: the epilogue is a chain of dependent instructions per warp, so it is bound
   // by latency, not issue rate; light epilogues (few register tiles) get 16 warps, which fits
   // the register file at <= 112 registers per thread.
-  const int chunk = (bn >= 32 && st.epi_tiles <= 2) ? 32 : 16;
-  const bool light = st.epi_tiles <= 2 && bn >= 256;
+  // columns per epilogue step: more columns = more independent work per thread (the epilogue
+  // is latency-bound) but more registers
+  int chunk = (bn >= 32 && st.epi_tiles <= 2) ? 32 : 16;
+  if (const char* ov = getenv("B200_EPI_CHUNK")) chunk = atoi(ov);
+  const bool light = false;  // 16 warps measured slower: the register cap (96) makes the epilogue spill
   const int epi_warps = light ? 16 : (bn >= 128 ? 8 : 4);
   const int staging = 32 * chunk * st.epi_out_bytes;   // per warp
   // 227 KB per CTA: ring + alignment slack + barriers + one staging tile per epilogue warp
@@ -681,6 +709,7 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   o << "#define B200_EPI_CHUNK " << chunk << "\n#define B200_STAGING_BYTES " << staging << "\n";
   o << g.epilogue << "\n";
   o << "#define B200_EPI_PARAMS " << params << "\n";
+  o << "#define B200_EPILOGUE_PREFETCH b200_epilogue_prefetch(b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_pn0, shape.N" << args << ");\n";
   o << "#define B200_EPILOGUE_ROW b200_epilogue_row(b200_r, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_n0, shape.N, b200_stage, b200_has_next, b200_next_taddr" << args << ");\n";
   o << kGemmSource << "\n";
   std::ostringstream note;

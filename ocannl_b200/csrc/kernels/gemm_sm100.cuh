@@ -157,7 +157,10 @@ __device__ __forceinline__ void b200_tmem_ld16(unsigned int taddr, unsigned int*
 }
 
 __device__ __forceinline__ void b200_tmem_ld_chunk(unsigned int taddr, unsigned int* r) {
-#if B200_EPI_CHUNK == 32
+#if B200_EPI_CHUNK == 64
+  b200_tmem_ld32(taddr, r);
+  b200_tmem_ld32(taddr + 32u, r + 32);
+#elif B200_EPI_CHUNK == 32
   b200_tmem_ld32(taddr, r);
 #else
   b200_tmem_ld16(taddr, r);
@@ -350,10 +353,17 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
       const unsigned int mt = first_m + r % rows;
       const unsigned int nt = r / rows;
       const unsigned int b200_b0 = bidx / shape.B1, b200_b1 = bidx - b200_b0 * shape.B1;
+      const unsigned int b200_m = mt * B200_BM + quarter * 32u + lane;
+      // while the tensor cores are still busy with this tile, pull the epilogue's operands
+      // (bias, mask, residual rows ...) of every chunk this warp owns towards L1
+#pragma unroll 1
+      for (unsigned int c = 0; c < cols_per_warp; c += B200_EPI_CHUNK) {
+        const unsigned int b200_pn0 = nt * B200_BN + col_half * cols_per_warp + c;
+        B200_EPILOGUE_PREFETCH
+      }
       if (!b200_wait(bar_acc_full + 8u * acc, acc_phase, abort_flag, status, 4u)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (warp == 2 && lane == 0) { if (tile == blockIdx.x) B200_TR(8); else if (tile == blockIdx.x + gridDim.x) B200_TR(10); }
-      const unsigned int b200_m = mt * B200_BM + quarter * 32u + lane;
       const unsigned int taddr = tmem_base + acc * B200_BN + ((quarter * 32u) << 16);
       // One register buffer: the epilogue issues the TMEM load of the next chunk as soon as it
       // has consumed the current one, so the load overlaps the epilogue's stores.  (The loop is

@@ -43,6 +43,23 @@ __device__ __forceinline__ unsigned short b200_f2h(float f) {
   return h;
 }
 
+// "Rounded floats": the value of a bf16 / half number kept in a float register.
+__device__ __forceinline__ float b200_rbf(float f) {
+  b200_u32 u;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %1;" : "=r"(u) : "f"(f));   // both halves hold bf16(f)
+  return __uint_as_float(u & 0xFFFF0000u);
+}
+__device__ __forceinline__ float b200_rhf(float f) { return b200_h2f(b200_f2h(f)); }
+// the 16 bits of a float that already holds a bf16 value
+__device__ __forceinline__ unsigned short b200_bfbits(float f) { return (unsigned short)(__float_as_uint(f) >> 16); }
+// two such floats as one 32-bit word (element 0 in the low half)
+__device__ __forceinline__ b200_u32 b200_pack_bf(float lo, float hi) {
+  return (__float_as_uint(lo) >> 16) | (__float_as_uint(hi) & 0xFFFF0000u);
+}
+__device__ __forceinline__ b200_u32 b200_pack_hf(float lo, float hi) {
+  return (b200_u32)b200_f2h(lo) | ((b200_u32)b200_f2h(hi) << 16);
+}
+
 __device__ __forceinline__ float b200_pow2(float x) { return x * x; }
 __device__ __forceinline__ float b200_pow3(float x) { return x * x * x; }
 __device__ __forceinline__ double b200_pow2(double x) { return x * x; }
