@@ -82,6 +82,7 @@ struct CompileOptions {
   bool enable_gemm = true;
   bool enable_coop = true;
   bool enable_fuse = true;   // several small stages in one single-block kernel
+  bool enable_pairs = true;  // contraction epilogues over pairs of columns with packed 16-bit arithmetic
   bool large_models = false;
 };
 

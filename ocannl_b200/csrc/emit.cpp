@@ -89,13 +89,14 @@ std::pair<std::string, std::string> Emitter::convert(Prec from, Prec to) {
 std::string Emitter::index(const Index& ix) {
   switch (ix.kind) {
     case Index::Fixed: return std::to_string(ix.fixed);
-    case Index::Iter: return ix.sym;
+    case Index::Iter: return (pair_hi && ix.sym == pair_sym) ? "(" + ix.sym + "+1u)" : ix.sym;
     case Index::SubAxis: return "";
     case Index::Affine: {
       std::string r;
       for (auto& t : ix.terms) {
         if (!r.empty()) r += "+";
-        r += t.first == 1 ? t.second : std::to_string(t.first) + "*" + t.second;
+        const std::string sym = (pair_hi && t.second == pair_sym) ? "(" + t.second + "+1u)" : t.second;
+        r += t.first == 1 ? sym : std::to_string(t.first) + "*" + sym;
       }
       if (ix.fixed > 0) r += (r.empty() ? "" : "+") + std::to_string(ix.fixed);
       else if (ix.fixed < 0) r += (r.empty() ? "" : "+") + std::string("-") + std::to_string(-ix.fixed);
@@ -126,6 +127,35 @@ std::string Emitter::scope_name(int scope_id, int tn) const {
 }
 std::string Emitter::node_name(int tn) const { return P.tn(tn).ident; }
 
+// the value of `c` rounded to a 16-bit format, as a float
+static float round_lowp(double c, Prec prec) {
+  const float f = (float)c;
+  if (prec == Prec::Bfloat16) {
+    unsigned int u;
+    float rounded;
+    memcpy(&u, &f, 4);
+    if (std::isnan(f)) return f;
+    u += 0x7FFFu + ((u >> 16) & 1u);  // arrayjit/lib/builtins.c:620-627
+    u &= 0xFFFF0000u;
+    memcpy(&rounded, &u, 4);
+    return rounded;
+  }
+  return (float)(_Float16)f;
+}
+// ... and its 16 storage bits
+static unsigned int lowp_bits(double c, Prec prec) {
+  const float r = round_lowp(c, prec);
+  if (prec == Prec::Bfloat16) {
+    unsigned int u;
+    memcpy(&u, &r, 4);
+    return std::isnan(r) ? 0x7FFFu : (u >> 16);
+  }
+  const _Float16 h = (_Float16)r;
+  unsigned short b;
+  memcpy(&b, &h, 2);
+  return b;
+}
+
 std::string Emitter::constant(double c, Prec prec) {
   char buf[64];
   if (prec == Prec::Single || lowp(prec)) {
@@ -139,17 +169,7 @@ std::string Emitter::constant(double c, Prec prec) {
     }
     if (prec == Prec::Single) return lit;
     // 16-bit constants are rounded here, once, instead of per element on the device
-    float rounded;
-    const float f = (float)c;
-    if (prec == Prec::Bfloat16) {
-      unsigned int u;
-      memcpy(&u, &f, 4);
-      u += 0x7FFFu + ((u >> 16) & 1u);  // arrayjit/lib/builtins.c:620-627
-      u &= 0xFFFF0000u;
-      memcpy(&rounded, &u, 4);
-    } else {
-      rounded = (float)(_Float16)f;
-    }
+    const float rounded = round_lowp(c, prec);
     if (std::isinf(rounded)) return rounded > 0 ? "B200_INF" : "(-B200_INF)";
     if (std::isnan(rounded)) return "B200_NAN";
     snprintf(buf, sizeof buf, "%a", (double)rounded);
@@ -504,6 +524,15 @@ std::string Emitter::stmt(const Stmt& s, int ind) {
     case Stmt::Set: {
       const Tnode& t = P.tn(s.tn);
       if (t.mode == Mode::Virtual) throw Error(-3, "b200ir: write to virtual node '" + t.ident + "'");
+      if (pair) {
+        auto prd = set_redirect.find(s.tn);
+        if (prd == set_redirect.end() || !same_indices(prd->second.first, s.idcs))
+          throw Error(-4, "pair emission of a store to memory");
+        std::string code;
+        const std::string v = pair_scalar(t.prec, *s.value, code);
+        used_nodes.insert(s.tn);
+        return code + pad(ind) + prd->second.second + " = " + v + ";\n";
+      }
       Res v = scalar(t.prec, *s.value);
       used_nodes.insert(s.tn);
       std::string a = t.ident + "[" + offset(s.idcs, t.dims) + "] = " + store_wrap(t.prec, v.expr) + ";\n";
@@ -526,6 +555,153 @@ std::string Emitter::stmt(const Stmt& s, int ind) {
     }
   }
   return "";
+}
+
+// ------------------------------------------------------------------------- pair mode
+
+namespace {
+std::string pair_lo(Prec p, const std::string& v) {
+  if (p == Prec::Single) return v + ".x";
+  return (p == Prec::Bfloat16 ? "b200_bf2_lo(" : "b200_hf2_lo(") + v + ")";
+}
+std::string pair_hi_of(Prec p, const std::string& v) {
+  if (p == Prec::Single) return v + ".y";
+  return (p == Prec::Bfloat16 ? "b200_bf2_hi(" : "b200_hf2_hi(") + v + ")";
+}
+// a pair of precision p from two float expressions (rounds when p is a 16-bit format)
+std::string pair_make(Prec p, const std::string& lo, const std::string& hi) {
+  if (p == Prec::Single) return "b200_f2{" + lo + ", " + hi + "}";
+  return (p == Prec::Bfloat16 ? "b200_bf2_pack(" : "b200_hf2_pack(") + lo + ", " + hi + ")";
+}
+const char* pair_suffix(Prec p) { return p == Prec::Bfloat16 ? "bf2" : "hf2"; }
+}  // namespace
+
+bool Emitter::pair_supported(const Scalar& e) const {
+  switch (e.kind) {
+    case Scalar::Const: return true;
+    case Scalar::Get: if (!pair_prec(P.tn(e.tn).prec)) return false; break;
+    case Scalar::LocalScope:
+    case Scalar::GetLocal:
+      return scope_subst.count(e.scope_id) != 0 && pair_prec(P.tn(e.tn).prec);
+    case Scalar::Bin:
+    case Scalar::Un:
+    case Scalar::Tern: break;
+    default: return false;
+  }
+  for (auto& a : e.args) {
+    if (!pair_prec(a.prec)) return false;
+    if (!pair_supported(*a.s)) return false;
+  }
+  return true;
+}
+
+std::string Emitter::pair_tmp(Prec p, const std::string& init, std::string& code) {
+  const std::string n = "b200_t" + std::to_string(tmp_counter++);
+  code += std::string("      const ") + pair_type(p) + " " + n + " = " + init + ";\n";
+  return n;
+}
+
+std::string Emitter::pair_convert(Prec from, Prec to, const std::string& v, std::string& code) {
+  if (from == to) return v;
+  return pair_tmp(to, pair_make(to, pair_lo(from, v), pair_hi_of(from, v)), code);
+}
+
+std::string Emitter::pair_scalar(Prec prec, const Scalar& e, std::string& code) {
+  if (!pair_prec(prec)) throw Error(-4, "pair emission of an unsupported precision");
+  switch (e.kind) {
+    case Scalar::LocalScope:
+    case Scalar::GetLocal: {
+      auto sub = scope_subst.find(e.scope_id);
+      if (sub == scope_subst.end()) throw Error(-4, "pair emission of a local scope");
+      return pair_convert(P.tn(e.tn).prec, prec, sub->second, code);
+    }
+    case Scalar::Const: {
+      if (prec == Prec::Single) {
+        const std::string c = constant(e.cval, prec);
+        return "b200_f2{" + c + ", " + c + "}";
+      }
+      char buf[32];
+      const unsigned int b = lowp_bits(e.cval, prec);
+      snprintf(buf, sizeof buf, "0x%08xu", b | (b << 16));
+      return buf;
+    }
+    case Scalar::Get: {
+      const Tnode& t = P.tn(e.tn);
+      auto f = forwarded.find(e.tn);
+      if (f != forwarded.end() && same_indices(f->second.first, e.idcs)) return pair_convert(t.prec, prec, f->second.second, code);
+      if (t.mode == Mode::Virtual) throw Error(-3, "b200ir: read of virtual node '" + t.ident + "'");
+      used_nodes.insert(e.tn);
+      for (auto& lt : load_tiles)
+        if (lt.tn == e.tn && same_indices(lt.idcs, e.idcs)) return pair_convert(t.prec, prec, lt.expr, code);
+      const std::string off0 = offset(e.idcs, t.dims);
+      pair_hi = true;
+      const std::string off1 = offset(e.idcs, t.dims);
+      pair_hi = false;
+      const std::string a = t.ident + "[" + off0 + "]", b = t.ident + "[" + off1 + "]";
+      std::string v;
+      if (t.prec == Prec::Single) v = pair_tmp(t.prec, "b200_f2{" + a + ", " + (off0 == off1 ? a : b) + "}", code);
+      else if (off0 == off1) v = pair_tmp(t.prec, "b200_dup16(" + a + ")", code);
+      else v = pair_tmp(t.prec, "((unsigned int)" + a + " | ((unsigned int)" + b + " << 16))", code);
+      return pair_convert(t.prec, prec, v, code);
+    }
+    case Scalar::Bin: {
+      if (e.op == "arg1") return pair_scalar(prec, *e.args[0].s, code);
+      if (e.op == "arg2") return pair_scalar(prec, *e.args[1].s, code);
+      if (e.op == "pow" && e.args[1].s->kind == Scalar::Const && (e.args[1].s->cval == 2.0 || e.args[1].s->cval == 3.0)) {
+        const std::string a = pair_scalar(prec, *e.args[0].s, code);
+        const bool cube = e.args[1].s->cval == 3.0;
+        if (lowp(prec)) {
+          // one rounding of the float power, as the scalar form does
+          const std::string fn = cube ? "b200_pow3(" : "b200_pow2(";
+          return pair_tmp(prec, pair_make(prec, fn + pair_lo(prec, a) + ")", fn + pair_hi_of(prec, a) + ")"), code);
+        }
+        const std::string fn = cube ? "b200_pow3(" : "b200_pow2(";
+        return pair_tmp(prec, "b200_f2{" + fn + a + ".x), " + fn + a + ".y)}", code);
+      }
+      const std::string a = pair_scalar(prec, *e.args[0].s, code), b = pair_scalar(prec, *e.args[1].s, code);
+      if (lowp(prec) && (e.op == "add" || e.op == "sub" || e.op == "mul" || e.op == "max" || e.op == "min"))
+        return pair_tmp(prec, std::string("b200_") + pair_suffix(prec) + "_" + e.op + "(" + a + ", " + b + ")", code);
+      return pair_tmp(prec,
+                      pair_make(prec, binop_plain(Prec::Single, e.op, pair_lo(prec, a), pair_lo(prec, b)),
+                                binop_plain(Prec::Single, e.op, pair_hi_of(prec, a), pair_hi_of(prec, b))),
+                      code);
+    }
+    case Scalar::Un: {
+      const std::string a = pair_scalar(prec, *e.args[0].s, code);
+      if (e.op == "id") return a;
+      if (lowp(prec)) {
+        if (e.op == "neg") return pair_tmp(prec, "(" + a + " ^ 0x80008000u)", code);
+        if (e.op == "relu") return pair_tmp(prec, std::string("b200_") + pair_suffix(prec) + "_max(" + a + ", 0u)", code);
+        auto one = [&](const std::string& x) {
+          if (e.op == "tanh") return "b200_tanh_fast(" + x + ")";
+          if (e.op == "exp") return "__expf(" + x + ")";
+          if (e.op == "log") return "__logf(" + x + ")";
+          return unop_plain(Prec::Single, e.op, x);
+        };
+        return pair_tmp(prec, pair_make(prec, one(pair_lo(prec, a)), one(pair_hi_of(prec, a))), code);
+      }
+      return pair_tmp(prec, "b200_f2{" + unop_plain(prec, e.op, a + ".x") + ", " + unop_plain(prec, e.op, a + ".y") + "}", code);
+    }
+    case Scalar::Tern: {
+      if (e.op == "where") {
+        const Prec cp = e.args[0].prec;
+        const std::string c = pair_scalar(cp, *e.args[0].s, code);
+        const std::string a = pair_scalar(prec, *e.args[1].s, code), b = pair_scalar(prec, *e.args[2].s, code);
+        const std::string c0 = "(" + pair_lo(cp, c) + " != 0)", c1 = "(" + pair_hi_of(cp, c) + " != 0)";
+        if (prec == Prec::Single)
+          return pair_tmp(prec, "b200_f2{" + c0 + " ? " + a + ".x : " + b + ".x, " + c1 + " ? " + a + ".y : " + b + ".y}", code);
+        return pair_tmp(prec, "b200_sel16x2(" + c0 + ", " + c1 + ", " + a + ", " + b + ")", code);
+      }
+      const std::string a = pair_scalar(prec, *e.args[0].s, code), b = pair_scalar(prec, *e.args[1].s, code),
+                        c = pair_scalar(prec, *e.args[2].s, code);
+      return pair_tmp(prec,
+                      pair_make(prec, ternop_plain(Prec::Single, e.op, pair_lo(prec, a), pair_lo(prec, b), pair_lo(prec, c)),
+                                ternop_plain(Prec::Single, e.op, pair_hi_of(prec, a), pair_hi_of(prec, b), pair_hi_of(prec, c))),
+                      code);
+    }
+    default: break;
+  }
+  throw Error(-4, "pair emission of an unsupported scalar");
 }
 
 }  // namespace b200

@@ -69,6 +69,26 @@ struct Emitter {
   std::string constant(double c, Prec prec);
   static bool reads_scope_before_set(int scope_id, int tn, const Stmt& body);
 
+  // ---- pair mode: every value is TWO neighbouring elements along `pair_sym` (sym and sym + 1).
+  // Single values are a `b200_f2`, bf16 / half values one 32-bit word holding both (element
+  // `sym` in the low half), so that add / sub / mul / min / max / neg / fma run as one packed
+  // instruction and a float pair is rounded by one packed conversion.  For two operands that are
+  // values of the 16-bit format, the packed add / sub / mul round the exact result once; the
+  // float operation followed by a rounding gives the same bits, because whenever the exact
+  // result does not fit a float the smaller operand is far below half a unit in the last place
+  // of the larger one and both roundings return the larger operand.
+  bool pair = false;
+  std::string pair_sym;
+  bool pair_hi = false;   // while true, index() spells pair_sym as (pair_sym + 1u)
+  static bool pair_prec(Prec p) { return p == Prec::Single || p == Prec::Bfloat16 || p == Prec::Half; }
+  static const char* pair_type(Prec p) { return p == Prec::Single ? "b200_f2" : "unsigned int"; }
+  // whether `s` can be emitted in pair mode (given the scopes that are substituted)
+  bool pair_supported(const Scalar& s) const;
+  // emits definitions of temporaries into `code` and returns the name / expression of the value
+  std::string pair_scalar(Prec prec, const Scalar& s, std::string& code);
+  std::string pair_convert(Prec from, Prec to, const std::string& v, std::string& code);
+  std::string pair_tmp(Prec p, const std::string& init, std::string& code);
+
   std::string binop(Prec prec, const std::string& op, const std::string& a, const std::string& b);
   std::string unop(Prec prec, const std::string& op, const std::string& a);
   std::string ternop(Prec prec, const std::string& op, const std::string& a, const std::string& b,

@@ -81,8 +81,30 @@ bool mac_step(const Scalar& v, const std::function<bool(const Scalar&)>& is_acc,
 
 }  // namespace
 
+static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, const Stmt& set, bool zeroed_before,
+                            const CompileOptions& opt, const std::vector<Follower>& followers, int* n_fused, Stage* out,
+                            bool pair);
+
+// The epilogue is first tried over pairs of columns (packed 16-bit arithmetic); anything that form
+// cannot express falls back to one column at a time.
 bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& set, bool zeroed_before,
                 const CompileOptions& opt, const std::vector<Follower>& followers, int* n_fused, Stage* out) {
+  if (opt.enable_pairs) {
+    Stage trial = *out;
+    try {
+      if (match_gemm_mode(P, nest, set, zeroed_before, opt, followers, n_fused, &trial, true)) {
+        *out = trial;
+        return true;
+      }
+    } catch (const Error&) {
+    }
+  }
+  return match_gemm_mode(P, nest, set, zeroed_before, opt, followers, n_fused, out, false);
+}
+
+static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, const Stmt& set, bool zeroed_before,
+                            const CompileOptions& opt, const std::vector<Follower>& followers, int* n_fused, Stage* out,
+                            const bool pair) {
   *n_fused = 0;
   if (set.kind != Stmt::Set) return false;
   const Tnode& D = P.tn(set.tn);
@@ -318,6 +340,11 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
   };
   std::vector<Out> outs;
   const std::string n_sym = dn.syms.size() == 1 ? dn.syms[0].first : std::string();
+  // pair mode: b200_j counts PAIRS of columns; tiles hold one pair per entry
+  if (pair && (form_b || n_sym.empty() || g.n.extent % 2 != 0)) return false;
+  em.pair = pair;
+  em.pair_sym = n_sym;
+  bool pair_fail = false;
   auto add_out = [&](int tn, const Indices& idcs) {
     Out o;
     o.tn = tn;
@@ -337,6 +364,7 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
         o.row_off = em.offset(row, t.dims);
       }
     }
+    if (pair && (!o.unit_n || !Emitter::pair_prec(t.prec))) pair_fail = true;
     em.set_redirect[tn] = {idcs, o.arr + "[b200_j]"};
     em.used_nodes.insert(tn);
     outs.push_back(o);
@@ -383,6 +411,7 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
             const std::string T = Emitter::ctype(t.prec);
             const bool f32 = t.prec == Prec::Single;
             std::ostringstream lc;
+            if (!pair) {
             lc << "  " << T << " " << arr << "[B200_EPI_CHUNK];\n  if (b200_row_ok) {\n"
                << "    const " << T << "* b200_p = " << t.ident << " + (" << em.offset(row, t.dims) << ") + b200_n0;\n"
                << "    if (b200_n0 + B200_EPI_CHUNK <= b200_N && (((unsigned long long)b200_p) & 15ull) == 0ull) {\n"
@@ -398,6 +427,26 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
                  << "        " << arr << "[8 * v + 6] = (unsigned short)q.w; " << arr << "[8 * v + 7] = (unsigned short)(q.w >> 16);\n";
             lc << "      }\n    } else {\n#pragma unroll\n      for (int j = 0; j < B200_EPI_CHUNK; ++j) " << arr
                << "[j] = (b200_n0 + (unsigned int)j < b200_N) ? b200_p[j] : (" << T << ")0;\n    }\n  }\n";
+            } else {
+            // one pair per entry: packed words are taken as they lie in memory
+            lc << "  " << Emitter::pair_type(t.prec) << " " << arr << "[B200_EPI_CHUNK / 2];\n  if (b200_row_ok) {\n"
+               << "    const " << T << "* b200_p = " << t.ident << " + (" << em.offset(row, t.dims) << ") + b200_n0;\n"
+               << "    if (b200_n0 + B200_EPI_CHUNK <= b200_N && (((unsigned long long)b200_p) & 15ull) == 0ull) {\n"
+               << "#pragma unroll\n      for (int v = 0; v < B200_EPI_CHUNK / " << (f32 ? 4 : 8) << "; ++v) {\n"
+               << "        const uint4 q = ((const uint4*)b200_p)[v];\n";
+            if (f32)
+              lc << "        " << arr << "[2 * v] = b200_f2{__uint_as_float(q.x), __uint_as_float(q.y)};\n"
+                 << "        " << arr << "[2 * v + 1] = b200_f2{__uint_as_float(q.z), __uint_as_float(q.w)};\n";
+            else
+              lc << "        " << arr << "[4 * v] = q.x; " << arr << "[4 * v + 1] = q.y; " << arr << "[4 * v + 2] = q.z; " << arr
+                 << "[4 * v + 3] = q.w;\n";
+            lc << "      }\n    } else {\n#pragma unroll\n      for (int j = 0; j < B200_EPI_CHUNK / 2; ++j) {\n"
+               << "        const " << T << " b200_e0 = (b200_n0 + 2u * (unsigned int)j < b200_N) ? b200_p[2 * j] : (" << T << ")0;\n"
+               << "        const " << T << " b200_e1 = (b200_n0 + 2u * (unsigned int)j + 1u < b200_N) ? b200_p[2 * j + 1] : (" << T << ")0;\n";
+            if (f32) lc << "        " << arr << "[j] = b200_f2{b200_e0, b200_e1};\n";
+            else lc << "        " << arr << "[j] = (unsigned int)b200_e0 | ((unsigned int)b200_e1 << 16);\n";
+            lc << "      }\n    }\n  }\n";
+            }
             load_code += lc.str();
             // the same lines, requested early (before the accumulator is ready) so that the
             // loads above hit in L1 instead of paying an L2 round trip per chunk
@@ -418,6 +467,10 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
   if (!form_b) collect_loads(*set.value, nullptr);
 
   em.scope_subst[kAccScope] = "b200_acc";
+  if (pair) {
+    em.scope_subst[scope->scope_id] = "b200_acc";
+    if (!em.pair_supported(*set.value)) return false;
+  }
   std::string body;
   add_out(set.tn, set.idcs);
   if (form_b) {
@@ -477,6 +530,7 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
     };
     chk(*fo.set->value);
     if (!ok || !reads_producer || produced.count(fo.set->tn) || em.used_nodes.count(fo.set->tn)) break;
+    if (pair && !em.pair_supported(*fo.set->value)) return false;   // the one-column form can still fuse it
     for (size_t i = 0; i < fo.nest.size(); ++i) {
       int occ = 0;
       for (auto& ix : fo.set->idcs)
@@ -513,6 +567,7 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
     ++fused;
   }
   *n_fused = fused;
+  if (pair_fail) return false;
 
   std::ostringstream fn;
   // parameters of the epilogue: the nodes it touches (+ static table)
@@ -588,11 +643,19 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
   }
   fn << unit_syms << load_code;
   // output tiles hold expression values (16-bit precisions as rounded floats); they are packed at the store
+  if (pair) {
+    for (auto& o : outs) fn << "  " << Emitter::pair_type(P.tn(o.tn).prec) << " " << o.arr << "[B200_EPI_CHUNK / 2];\n";
+    fn << "#pragma unroll\n  for (int b200_j = 0; b200_j < B200_EPI_CHUNK / 2; ++b200_j) {\n"
+       << "    const unsigned int b200_n = b200_n0 + 2u * (unsigned int)b200_j;\n"
+       << "    if (b200_row_ok && b200_n < b200_N) {\n"
+       << "      const b200_f2 b200_acc = {__uint_as_float(b200_r[2 * b200_j]), __uint_as_float(b200_r[2 * b200_j + 1])};\n";
+  } else {
   for (auto& o : outs) fn << "  " << Emitter::rtype(P.tn(o.tn).prec) << " " << o.arr << "[B200_EPI_CHUNK];\n";
   fn << "#pragma unroll\n  for (int b200_j = 0; b200_j < B200_EPI_CHUNK; ++b200_j) {\n"
      << "    const unsigned int b200_n = b200_n0 + (unsigned int)b200_j;\n"
      << "    if (b200_row_ok && b200_n < b200_N) {\n"
      << "      const float b200_acc = __uint_as_float(b200_r[b200_j]);\n";
+  }
   recover(dn, "b200_n");
   fn << ep.str() << body << "    }\n  }\n";
   // the accumulator chunk is consumed: start fetching the next one while this one is stored
@@ -614,7 +677,13 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
            << "    if (b200_fast) {\n"
            << "      constexpr int G = B200_EPI_CHUNK / " << V << ";   // 16-byte groups per row\n"
            << "#pragma unroll\n      for (int g = 0; g < G; ++g) {\n        uint4 q;\n";
-        if (ebytes == 4) {
+        if (pair && ebytes == 4) {
+          fn << "        q.x = __float_as_uint(" << o.arr << "[2 * g].x); q.y = __float_as_uint(" << o.arr << "[2 * g].y);\n"
+             << "        q.z = __float_as_uint(" << o.arr << "[2 * g + 1].x); q.w = __float_as_uint(" << o.arr << "[2 * g + 1].y);\n";
+        } else if (pair) {
+          fn << "        q.x = " << o.arr << "[4 * g]; q.y = " << o.arr << "[4 * g + 1]; q.z = " << o.arr << "[4 * g + 2]; q.w = "
+             << o.arr << "[4 * g + 3];\n";
+        } else if (ebytes == 4) {
           fn << "        q.x = b200_bits32(" << o.arr << "[4 * g]); q.y = b200_bits32(" << o.arr << "[4 * g + 1]);\n"
              << "        q.z = b200_bits32(" << o.arr << "[4 * g + 2]); q.w = b200_bits32(" << o.arr << "[4 * g + 3]);\n";
         } else {
@@ -638,7 +707,11 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
         fn << "    if (b200_row_ok) {\n";
       }
       fn << "#pragma unroll\n      for (int b200_j = 0; b200_j < B200_EPI_CHUNK; ++b200_j)\n"
-         << "        if (b200_n0 + (unsigned int)b200_j < b200_N) b200_p[b200_j] = " << Emitter::store_wrap(t.prec, o.arr + "[b200_j]") << ";\n"
+         << "        if (b200_n0 + (unsigned int)b200_j < b200_N) b200_p[b200_j] = "
+         << (!pair ? Emitter::store_wrap(t.prec, o.arr + "[b200_j]")
+                   : ebytes == 4 ? "((b200_j & 1) ? " + o.arr + "[b200_j >> 1].y : " + o.arr + "[b200_j >> 1].x)"
+                                 : "(unsigned short)(" + o.arr + "[b200_j >> 1] >> (16 * (b200_j & 1)))")
+         << ";\n"
          << "    }\n  }\n";
     } else {
       // general position: recompute the offset per column

@@ -60,6 +60,47 @@ __device__ __forceinline__ b200_u32 b200_pack_hf(float lo, float hi) {
   return (b200_u32)b200_f2h(lo) | ((b200_u32)b200_f2h(hi) << 16);
 }
 
+// ---- pairs of neighbouring elements: two floats, or two 16-bit values in one word (the first
+//      element in the low half).  The packed add / sub / mul round the exact result once, which
+//      for operands of the 16-bit format equals the float operation followed by a rounding.
+struct b200_f2 {
+  float x, y;
+};
+__device__ __forceinline__ float b200_bf2_lo(b200_u32 v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float b200_bf2_hi(b200_u32 v) { return __uint_as_float(v & 0xFFFF0000u); }
+__device__ __forceinline__ float b200_hf2_lo(b200_u32 v) { return b200_h2f((unsigned short)(v & 0xFFFFu)); }
+__device__ __forceinline__ float b200_hf2_hi(b200_u32 v) { return b200_h2f((unsigned short)(v >> 16)); }
+__device__ __forceinline__ b200_u32 b200_bf2_pack(float lo, float hi) {
+  b200_u32 u;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(u) : "f"(hi), "f"(lo));
+  return u;
+}
+__device__ __forceinline__ b200_u32 b200_hf2_pack(float lo, float hi) {
+  b200_u32 u;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(u) : "f"(hi), "f"(lo));
+  return u;
+}
+__device__ __forceinline__ b200_u32 b200_dup16(unsigned short h) { return (b200_u32)h | ((b200_u32)h << 16); }
+__device__ __forceinline__ b200_u32 b200_sel16x2(bool c0, bool c1, b200_u32 a, b200_u32 b) {
+  return ((c0 ? a : b) & 0xFFFFu) | ((c1 ? a : b) & 0xFFFF0000u);
+}
+#define B200_PACKED_OP(NAME, PTX)                                                   \
+  __device__ __forceinline__ b200_u32 NAME(b200_u32 a, b200_u32 b) {               \
+    b200_u32 d;                                                                     \
+    asm(PTX " %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));                             \
+    return d;                                                                       \
+  }
+B200_PACKED_OP(b200_bf2_add, "add.rn.bf16x2")
+B200_PACKED_OP(b200_bf2_sub, "sub.rn.bf16x2")
+B200_PACKED_OP(b200_bf2_mul, "mul.rn.bf16x2")
+B200_PACKED_OP(b200_bf2_max, "max.bf16x2")
+B200_PACKED_OP(b200_bf2_min, "min.bf16x2")
+B200_PACKED_OP(b200_hf2_add, "add.rn.f16x2")
+B200_PACKED_OP(b200_hf2_sub, "sub.rn.f16x2")
+B200_PACKED_OP(b200_hf2_mul, "mul.rn.f16x2")
+B200_PACKED_OP(b200_hf2_max, "max.f16x2")
+B200_PACKED_OP(b200_hf2_min, "min.f16x2")
+
 __device__ __forceinline__ float b200_pow2(float x) { return x * x; }
 __device__ __forceinline__ float b200_pow3(float x) { return x * x * x; }
 __device__ __forceinline__ double b200_pow2(double x) { return x * x; }
