@@ -27,7 +27,9 @@ LIB_PATH = os.path.join(_HERE, "libb200.so")
 
 NP_DTYPE = {"byte": np.uint8, "uint16": np.uint16, "int32": np.int32, "uint32": np.uint32,
             "int64": np.int64, "uint64": np.uint64, "half": np.float16, "bfloat16": np.uint16,
-            "single": np.float32, "double": np.float64}
+            "single": np.float32, "double": np.float64,
+            # four 32-bit words per element: arrays of this precision get a trailing axis of 4
+            "uint4x32": np.dtype((np.uint32, (4,)))}
 
 
 class B200Error(RuntimeError):
@@ -295,8 +297,9 @@ class Context:
     # ---- host access (Context.set_values / get_values, arrayjit/lib/context.ml:322-395)
     def from_host(self, ident: str, arr: np.ndarray):
         pool, off, t = self.arrays[ident]
-        a = np.ascontiguousarray(arr, dtype=NP_DTYPE[t.prec]).reshape(-1)
-        if a.size != t.num_elems:
+        words = 4 if t.prec == "uint4x32" else 1
+        a = np.ascontiguousarray(arr, dtype=np.uint32 if words == 4 else NP_DTYPE[t.prec]).reshape(-1)
+        if a.size != t.num_elems * words:
             raise UserError(-5, "from_host: '%s' has %d elements, got %d" % (ident, t.num_elems, a.size))
         self.device.from_host(pool, off, a)
         self.device.await_()     # the staging array may be a temporary

@@ -65,6 +65,16 @@ bool parallel_safe(const std::string& s, const Stmt& body) {
         if (st.kind == Stmt::ZeroOut) ok = false;
         if (st.kind == Stmt::Set) {
           int a = axis_with(st.idcs);
+          if (a < 0 && st.vec_len > 0 && !st.idcs.empty()) {
+            // a vector store whose last index is c * s (+ fixed) with c >= the vector length
+            // writes disjoint runs for distinct s
+            const Index& last = st.idcs.back();
+            if (last.kind == Index::Affine && last.terms.size() == 1 && last.terms[0].second == s &&
+                last.terms[0].first >= st.vec_len)
+              a = (int)st.idcs.size() - 1;
+          } else if (a >= 0 && st.vec_len > 1 && a == (int)st.idcs.size() - 1) {
+            a = -1;  // runs of neighbouring elements would overlap
+          }
           if (a < 0) { ok = false; return; }
           // the symbol must not appear on any other axis of the write
           for (size_t k = 0; k < st.idcs.size(); ++k)

@@ -65,7 +65,16 @@ std::pair<std::string, std::string> Emitter::convert(Prec from, Prec to) {
   if (from == to) return {"", ""};
   if (from == Prec::Fp8 || to == Prec::Fp8) throw Error(-4, "precision fp8 is not supported by the b200 backend");
   if (from == Prec::Uint4x32 || to == Prec::Uint4x32) {
-    if (to == Prec::Uint4x32 && (from == Prec::Uint32 || from == Prec::Int32)) return {"b200_u32_widen((b200_u32)(", "))"};
+    // arrayjit/lib/builtins.c:531-606
+    if (to == Prec::Uint4x32) {
+      if (from == Prec::Uint32 || from == Prec::Int32) return {"b200_u32_widen((b200_u32)(", "))"};
+      if (from == Prec::Uint64 || from == Prec::Int64) return {"b200_u64_to_u4x32((b200_u64)(", "))"};
+      if (from == Prec::Double) return {"b200_f64_to_u4x32(", ")"};
+      if (from == Prec::Single) return {"b200_f32_to_u4x32(", ")"};
+      if (from == Prec::Byte || from == Prec::Uint16) return {"b200_word_to_u4x32((b200_u32)(", "))"};
+      if (from == Prec::Bfloat16) return {"b200_word_to_u4x32((b200_u32)b200_bfbits(", "))"};
+      if (from == Prec::Half) return {"b200_word_to_u4x32((b200_u32)b200_f2h(", "))"};
+    }
     throw Error(-4, "unsupported uint4x32 conversion");
   }
   auto is_plain_int = [](Prec p) {
@@ -158,6 +167,10 @@ static unsigned int lowp_bits(double c, Prec prec) {
 
 std::string Emitter::constant(double c, Prec prec) {
   char buf[64];
+  if (prec == Prec::Uint4x32) {
+    snprintf(buf, sizeof buf, "%a", c);
+    return std::string("b200_f64_to_u4x32(") + buf + ")";
+  }
   if (prec == Prec::Single || lowp(prec)) {
     std::string lit;
     if (std::isinf(c)) lit = c > 0 ? "B200_INF" : "(-B200_INF)";
@@ -270,6 +283,10 @@ static bool selects_exactly(const std::string& op) {
 }
 
 std::string Emitter::binop(Prec prec, const std::string& op, const std::string& a, const std::string& b) {
+  if (op == "threefry4x32_crypto" || op == "threefry4x32_light") {
+    if (prec != Prec::Uint4x32) throw Error(-4, "threefry4x32 outside a uint4x32 context");
+    return (op == "threefry4x32_crypto" ? "b200_threefry_crypto(" : "b200_threefry_light(") + a + ", " + b + ")";
+  }
   if (lowp(prec) && selects_exactly(op)) return binop_plain(Prec::Single, op, a, b);
   if (lowp(prec)) return std::string(round_fn(prec)) + binop_plain(Prec::Single, op, a, b) + ")";
   return binop_plain(prec, op, a, b);
@@ -440,6 +457,24 @@ Emitter::Res Emitter::scalar(Prec prec, const Scalar& e) {
       return r;
     }
     case Scalar::Un: {
+      if (e.op == "uint4x32_to_prec_uniform1") {
+        // not homogeneous: the argument keeps its own (uint4x32) precision
+        Res a = scalar(e.args[0].prec, *e.args[0].s);
+        r.defs = a.defs;
+        if (e.args[0].prec != Prec::Uint4x32) throw Error(-4, "uint4x32_to_prec_uniform1 of a non-uint4x32 argument");
+        switch (prec) {
+          case Prec::Single: r.expr = "b200_uniform_single(" + a.expr + ", 0)"; break;
+          case Prec::Double: r.expr = "b200_uniform_double(" + a.expr + ", 0)"; break;
+          case Prec::Int32: r.expr = "b200_uniform_int32(" + a.expr + ", 0)"; break;
+          case Prec::Uint32: r.expr = "(b200_u32)b200_uniform_int32(" + a.expr + ", 0)"; break;
+          case Prec::Int64: r.expr = "b200_uniform_int64(" + a.expr + ", 0)"; break;
+          case Prec::Uint64: r.expr = "(b200_u64)b200_uniform_int64(" + a.expr + ", 0)"; break;
+          case Prec::Bfloat16: r.expr = load_wrap(prec, "b200_uniform1_bfloat16(" + a.expr + ")"); break;
+          case Prec::Half: r.expr = load_wrap(prec, "b200_uniform_half(" + a.expr + ", 0)"); break;
+          default: throw Error(-4, "uint4x32_to_prec_uniform1 into an unsupported precision");
+        }
+        return r;
+      }
       Res a = scalar(prec, *e.args[0].s);
       r.defs = a.defs;
       r.expr = unop(prec, e.op, a.expr);
@@ -524,6 +559,40 @@ std::string Emitter::stmt(const Stmt& s, int ind) {
     case Stmt::Set: {
       const Tnode& t = P.tn(s.tn);
       if (t.mode == Mode::Virtual) throw Error(-3, "b200ir: write to virtual node '" + t.ident + "'");
+      if (s.vec_len > 0) {
+        // C_syntax (arrayjit/lib/c_syntax.ml:548-592): one evaluation of the argument, then one
+        // store per element; a Fixed last index advances, any other gets "+ i" on the offset
+        if (pair) throw Error(-4, "pair emission of a vector store");
+        const char* fn = nullptr;
+        int want = 0;
+        switch (t.prec) {
+          case Prec::Single: fn = "b200_uniform_single("; want = 4; break;
+          case Prec::Double: fn = "b200_uniform_double("; want = 2; break;
+          case Prec::Int32: fn = "b200_uniform_int32("; want = 4; break;
+          case Prec::Int64: fn = "b200_uniform_int64("; want = 2; break;
+          case Prec::Bfloat16: fn = "b200_uniform_bfloat16("; want = 8; break;
+          case Prec::Half: fn = "b200_uniform_half("; want = 8; break;
+          default: throw Error(-4, "uint4x32_to_prec_uniform into an unsupported precision");
+        }
+        if (s.vec_len != want && s.vec_len != 1) throw Error(-3, "b200ir: vector length does not match the precision");
+        if (s.arg_prec != Prec::Uint4x32) throw Error(-4, "uint4x32_to_prec_uniform of a non-uint4x32 argument");
+        Res v = scalar(s.arg_prec, *s.value);
+        used_nodes.insert(s.tn);
+        const std::string tmp = "b200_vec" + std::to_string(tmp_counter++);
+        std::string out = pad(ind) + "{\n" + emit_defs(v.defs, ind + 2) + pad(ind + 2) + "const b200_u4x32 " + tmp + " = " + v.expr + ";\n";
+        for (int i = 0; i < s.vec_len; ++i) {
+          std::string off;
+          if (!s.idcs.empty() && s.idcs.back().kind == Index::Fixed) {
+            Indices el = s.idcs;
+            el.back().fixed += i;
+            off = offset(el, t.dims);
+          } else {
+            off = offset(s.idcs, t.dims) + " + " + std::to_string(i);
+          }
+          out += pad(ind + 2) + t.ident + "[" + off + "] = " + fn + tmp + ", " + std::to_string(i) + ");\n";
+        }
+        return out + pad(ind) + "}\n";
+      }
       if (pair) {
         auto prd = set_redirect.find(s.tn);
         if (prd == set_redirect.end() || !same_indices(prd->second.first, s.idcs))

@@ -106,7 +106,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
                             const CompileOptions& opt, const std::vector<Follower>& followers, int* n_fused, Stage* out,
                             const bool pair) {
   *n_fused = 0;
-  if (set.kind != Stmt::Set) return false;
+  if (set.kind != Stmt::Set || set.vec_len > 0) return false;
   const Tnode& D = P.tn(set.tn);
   std::set<std::string> statics;
   for (auto& s : P.statics) statics.insert(s.sym);
@@ -490,7 +490,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   std::string aliases;
   std::set<int> produced = {set.tn};
   for (const Follower& fo : followers) {
-    if (fo.nest.size() != free_loops.size() || fo.set->kind != Stmt::Set) break;
+    if (fo.nest.size() != free_loops.size() || fo.set->kind != Stmt::Set || fo.set->vec_len > 0) break;
     bool ok = true;
     std::map<std::string, std::string> ren;  // follower symbol -> this stage's symbol
     for (size_t i = 0; i < fo.nest.size(); ++i) {

@@ -221,6 +221,17 @@ StmtP parse_stmt(const Sx& s) {
     r->tn = (int)to_int(s.at(1));
     r->idcs = parse_indices(s.at(2));
     r->value = parse_scalar(s.at(3));
+  } else if (h == "set_from_vec") {
+    r->kind = Stmt::Set;
+    r->tn = (int)to_int(s.at(1));
+    r->idcs = parse_indices(s.at(2));
+    r->vec_len = (int)to_int(s.at(3));
+    r->vec_op = s.at(4).a;
+    if (r->vec_op != "uint4x32_to_prec_uniform" || r->vec_len < 1 || r->vec_len > 16)
+      throw Error(-3, "b200ir: unsupported vector operation '" + r->vec_op + "'");
+    Arg a = parse_arg(s.at(5));
+    r->value = a.s;
+    r->arg_prec = a.prec;
   } else if (h == "set_local") {
     r->kind = Stmt::SetLocal;
     r->scope_id = (int)to_int(s.at(1));

@@ -102,6 +102,11 @@ struct Stmt {
   ScalarP value;
   int scope_id = 0;
   bool needs_init = false;
+  // Set_from_vec is a Set whose value is a vector operation: `vec_len` results go to `vec_len`
+  // consecutive elements starting at idcs; `value` is the operation's argument at `arg_prec`
+  int vec_len = 0;
+  std::string vec_op;
+  Prec arg_prec = Prec::Single;
 };
 
 struct StaticSym {

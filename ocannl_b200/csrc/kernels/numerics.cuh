@@ -161,6 +161,44 @@ __device__ __forceinline__ b200_u4x32 b200_u32_widen(b200_u32 x) {
   return r;
 }
 
+// widening of the other sources (arrayjit/lib/builtins.c:531-606)
+__device__ __forceinline__ b200_u4x32 b200_u64_to_u4x32(b200_u64 x) {
+  b200_u4x32 r;
+  r.v[0] = (b200_u32)(x & 0xFFFFFFFFull); r.v[1] = (b200_u32)(x >> 32); r.v[2] = 0u; r.v[3] = 0u;
+  return r;
+}
+__device__ __forceinline__ b200_u4x32 b200_f64_to_u4x32(double d) { return b200_u64_to_u4x32((b200_u64)__double_as_longlong(d)); }
+__device__ __forceinline__ b200_u4x32 b200_word_to_u4x32(b200_u32 x) {
+  b200_u4x32 r;
+  r.v[0] = x; r.v[1] = 0u; r.v[2] = 0u; r.v[3] = 0u;
+  return r;
+}
+__device__ __forceinline__ b200_u4x32 b200_f32_to_u4x32(float f) { return b200_word_to_u4x32(__float_as_uint(f)); }
+
+// uniform values from random bits: element i of the vector forms (builtins.c:428-528) and the
+// scalar forms (builtins.c:351-414).  16-bit results are returned as storage bits.
+__device__ __forceinline__ unsigned short b200_bf16_bits_rne(float f) {
+  const b200_u32 bits = __float_as_uint(f);
+  unsigned short bf = (unsigned short)(bits >> 16);
+  if ((bits & 0x8000u) && ((bits & 0x7FFFu) || (bf & 1u))) bf++;
+  return bf;
+}
+__device__ __forceinline__ float b200_uniform_single(b200_u4x32 x, int i) { return b200_u32_uniform(x.v[i]); }
+__device__ __forceinline__ double b200_uniform_double(b200_u4x32 x, int i) {
+  const b200_u64 c = ((b200_u64)x.v[2 * i + 1] << 32) | x.v[2 * i];
+  return (double)c * (1.0 / 18446744073709551616.0);
+}
+__device__ __forceinline__ int b200_uniform_int32(b200_u4x32 x, int i) { return (int)x.v[i]; }
+__device__ __forceinline__ long long b200_uniform_int64(b200_u4x32 x, int i) {
+  return (long long)(((b200_u64)x.v[2 * i + 1] << 32) | x.v[2 * i]);
+}
+__device__ __forceinline__ float b200_uniform_16(b200_u4x32 x, int i) {
+  return (float)((x.v[i >> 1] >> (16 * (i & 1))) & 0xFFFFu) * (1.0f / 65536.0f);
+}
+__device__ __forceinline__ unsigned short b200_uniform_bfloat16(b200_u4x32 x, int i) { return b200_bf16_bits_rne(b200_uniform_16(x, i)); }
+__device__ __forceinline__ unsigned short b200_uniform_half(b200_u4x32 x, int i) { return b200_f2h(b200_uniform_16(x, i)); }
+__device__ __forceinline__ unsigned short b200_uniform1_bfloat16(b200_u4x32 x) { return b200_bf16_bits_rne(b200_u32_uniform(x.v[0])); }
+
 // ---- warp-level combine used by cooperative (one warp per output element) reductions
 __device__ __forceinline__ float b200_warp_sum(float v) {
 #pragma unroll

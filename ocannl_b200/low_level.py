@@ -40,9 +40,13 @@ PREC_BYTES = {"byte": 1, "uint16": 2, "int32": 4, "uint32": 4, "int64": 8, "uint
               "uint4x32": 16, "half": 2, "bfloat16": 2, "fp8": 1, "single": 4, "double": 8}
 
 BINOPS = ("arg1", "arg2", "add", "sub", "mul", "div", "pow", "relu_gate", "sat01_gate",
-          "lt", "eq", "ne", "or", "and", "mod", "max", "min")
+          "lt", "eq", "ne", "or", "and", "mod", "max", "min",
+          "threefry4x32_crypto", "threefry4x32_light")
 UNOPS = ("id", "relu", "sat01", "exp", "log", "exp2", "log2", "sin", "cos", "sqrt", "recip",
-         "recip_sqrt", "neg", "trunc", "tanh", "not")
+         "recip_sqrt", "neg", "trunc", "tanh", "not", "uint4x32_to_prec_uniform1")
+# elements one uint4x32 yields per result precision (Ops.c_vec_typ_of_prec, arrayjit/lib/ops.ml:339-351)
+VEC_LENGTH = {"single": 4, "double": 2, "int32": 4, "int64": 2, "byte": 16, "fp8": 16,
+              "uint16": 8, "bfloat16": 8, "half": 8}
 TERNOPS = ("where", "fma", "mul3")
 
 
@@ -374,6 +378,23 @@ class Set(Stmt):
 
     def sexp(self):
         return "(set %d %s %s)" % (self.tn.id, _idcs_sexp(self.idcs), self.llsc.sexp())
+
+
+@dataclass(eq=False)
+class SetFromVec(Stmt):
+    """`Set_from_vec {tn; idcs; length; vec_unop; arg}` (arrayjit/lib/low_level.mli:35-42): the
+    vector operation's `length` results go to `length` consecutive elements starting at `idcs`.
+    The only vector operation is `uint4x32_to_prec_uniform`, whose argument keeps its own
+    (uint4x32) precision."""
+    tn: Tnode
+    idcs: Tuple[Index, ...]
+    length: int
+    arg: Scalar
+    vec_unop: str = "uint4x32_to_prec_uniform"
+
+    def sexp(self):
+        return "(set_from_vec %d %s %d %s %s)" % (self.tn.id, _idcs_sexp(self.idcs), self.length,
+                                                   self.vec_unop, _arg(self.arg))
 
 
 @dataclass(eq=False)

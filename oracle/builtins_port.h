@@ -11,7 +11,8 @@
  *     (Threefry-4x32 of Salmon et al., "Parallel random numbers: as easy as
  *     1, 2, 3", with the rotation pairs 13/15/26/6 and 17/29/16/24 applied as
  *     two mixes per call and a word swap after each);
- *   - uniform conversions: builtins.c:345-360.
+ *   - uniform conversions, scalar and vector forms: builtins.c:345-528;
+ *   - widening to uint4x32: builtins.c:531-606.
  * Checked bit for bit against the reference's builtins.c compiled into
  * oracle/_ref (tests/test_oracle_golden.py).
  */
@@ -50,6 +51,11 @@ static inline uint16_t single_to_bfloat16(float f) {
 
 typedef struct { uint32_t v[4]; } uint4x32_t;
 typedef struct { float v[4]; } float4_t;
+typedef struct { double v[2]; } double2_t;
+typedef struct { int32_t v[4]; } int32x4_t;
+typedef struct { int64_t v[2]; } int64x2_t;
+typedef struct { uint16_t v[8]; } uint16x8_t;
+typedef struct { HALF_T v[8]; } half8_t;
 
 static inline uint32_t b200o_rotl(uint32_t x, unsigned n) { return (x << n) | (x >> (32 - n)); }
 
@@ -113,6 +119,88 @@ static inline uint4x32_t int32_to_uint4x32(int32_t x) { return uint32_to_uint4x3
 static inline uint4x32_t single_to_uint4x32(float f) {
   uint4x32_t r = {{0, 0, 0, 0}};
   memcpy(&r.v[0], &f, 4);
+  return r;
+}
+/* 64-bit sources fill the two low words (builtins.c:538-543,559-563,579-582) */
+static inline uint4x32_t uint64_to_uint4x32(uint64_t x) {
+  uint4x32_t r = {{(uint32_t)(x & 0xFFFFFFFFu), (uint32_t)(x >> 32), 0, 0}};
+  return r;
+}
+static inline uint4x32_t int64_to_uint4x32(int64_t x) { return uint64_to_uint4x32((uint64_t)x); }
+static inline uint4x32_t double_to_uint4x32(double d) {
+  uint64_t bits;
+  memcpy(&bits, &d, 8);
+  return uint64_to_uint4x32(bits);
+}
+/* 16-bit sources go to word 0 as they are (builtins.c:589-602) */
+static inline uint4x32_t uint16_to_uint4x32(uint16_t x) {
+  uint4x32_t r = {{(uint32_t)x, 0, 0, 0}};
+  return r;
+}
+static inline uint4x32_t bfloat16_to_uint4x32(uint16_t x) { return uint16_to_uint4x32(x); }
+
+/* ---- scalar uniform forms (builtins.c:351-414) */
+static inline double uint4x32_to_double_uniform(uint4x32_t x) {
+  uint64_t c = ((uint64_t)x.v[1] << 32) | x.v[0];
+  return c * (1.0 / 18446744073709551616.0);
+}
+static inline int32_t uint4x32_to_int32_uniform(uint4x32_t x) { return (int32_t)x.v[0]; }
+static inline uint32_t uint4x32_to_uint32_uniform(uint4x32_t x) { return x.v[0]; }
+static inline int64_t uint4x32_to_int64_uniform(uint4x32_t x) {
+  return (int64_t)(((uint64_t)x.v[1] << 32) | x.v[0]);
+}
+static inline uint16_t b200o_round_bits_bf16(float f) {
+  /* round to nearest even written with guard / sticky tests (builtins.c:399-405) */
+  uint32_t bits;
+  memcpy(&bits, &f, 4);
+  uint16_t bf = (uint16_t)(bits >> 16);
+  if ((bits & 0x8000u) && ((bits & 0x7FFFu) || (bf & 1u))) bf++;
+  return bf;
+}
+static inline uint16_t uint4x32_to_bfloat16_uniform(uint4x32_t x) {
+  return b200o_round_bits_bf16(uint32_to_single_uniform(x.v[0]));
+}
+/* The reference declares this one `uint16_t` while returning FLOAT_TO_HALF(f); with a native
+ * _Float16 that converts the VALUE (always 0).  The port returns the half itself, as the
+ * vector form does (builtins.c:407-412 against :501-513). */
+static inline HALF_T uint4x32_to_half_uniform(uint4x32_t x) {
+  float f = (float)(x.v[0] & 0xFFFFu) * (1.0f / 65536.0f);
+  return FLOAT_TO_HALF(f);
+}
+
+/* ---- vector uniform forms: all 128 bits are used (builtins.c:428-528) */
+static inline double2_t uint4x32_to_double_uniform_vec(uint4x32_t x) {
+  double2_t r;
+  for (int i = 0; i < 2; ++i) {
+    uint64_t c = ((uint64_t)x.v[2 * i + 1] << 32) | x.v[2 * i];
+    r.v[i] = c * (1.0 / 18446744073709551616.0);
+  }
+  return r;
+}
+static inline int32x4_t uint4x32_to_int32_uniform_vec(uint4x32_t x) {
+  int32x4_t r;
+  for (int i = 0; i < 4; ++i) r.v[i] = (int32_t)x.v[i];
+  return r;
+}
+static inline int64x2_t uint4x32_to_int64_uniform_vec(uint4x32_t x) {
+  int64x2_t r;
+  for (int i = 0; i < 2; ++i) r.v[i] = (int64_t)(((uint64_t)x.v[2 * i + 1] << 32) | x.v[2 * i]);
+  return r;
+}
+static inline uint16x8_t uint4x32_to_bfloat16_uniform_vec(uint4x32_t x) {
+  uint16x8_t r;
+  for (int i = 0; i < 8; ++i) {
+    uint32_t h = (x.v[i / 2] >> (16 * (i & 1))) & 0xFFFFu;
+    r.v[i] = b200o_round_bits_bf16((float)h * (1.0f / 65536.0f));
+  }
+  return r;
+}
+static inline half8_t uint4x32_to_half_uniform_vec(uint4x32_t x) {
+  half8_t r;
+  for (int i = 0; i < 8; ++i) {
+    uint32_t h = (x.v[i / 2] >> (16 * (i & 1))) & 0xFFFFu;
+    r.v[i] = FLOAT_TO_HALF((float)h * (1.0f / 65536.0f));
+  }
   return r;
 }
 

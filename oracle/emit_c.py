@@ -131,6 +131,8 @@ def binop_syntax(prec: str, op: str):
         return ("fmax(", ",", ")") if prec in DOUBLEISH else ("fmaxf(", ",", ")")
     if op == "min":
         return ("fmin(", ",", ")") if prec in DOUBLEISH else ("fminf(", ",", ")")
+    if op in ("threefry4x32_crypto", "threefry4x32_light"):
+        return "arrayjit_" + op + "(", ",", ")"      # ops.ml:627-630
     simple = {"mod": " %", "lt": " <", "eq": " ==", "ne": " !=", "or": " ||", "and": " &&"}
     return "(", simple[op], ")"
 
@@ -163,6 +165,8 @@ def unop_syntax(prec: str, op: str):
         return "tanhf(", ")"
     if op == "not":
         return "(", " == 0.0 ? 1.0 : 0.0)"
+    if op == "uint4x32_to_prec_uniform1":
+        return "uint4x32_to_" + prec + "_uniform(", ")"   # ops.ml:771-773
     raise ValueError(op)
 
 
@@ -176,6 +180,11 @@ def ternop_syntax(prec: str, op: str):
         return ("fma(", ",", ",", ")") if prec in DOUBLEISH else ("fmaf(", ",", ",", ")")
     return "((", ") * (", ") * (", "))"
 
+
+# Ops.c_vec_typ_of_prec (ops.ml:339-351)
+VEC_TYPE = {("single", 4): "float4_t", ("double", 2): "double2_t", ("int32", 4): "int32x4_t",
+            ("int64", 2): "int64x2_t", ("uint16", 8): "uint16x8_t", ("bfloat16", 8): "uint16x8_t",
+            ("half", 8): "half8_t"}
 
 # cc_backend.ml:169-322 — low-precision results are computed in float.
 _LOWP = {"bfloat16": ("bfloat16_to_single(", "single_to_bfloat16("),
@@ -375,6 +384,10 @@ class Emitter:
             d2, v2 = self.scalar(prec, e[3][0])
             return d1 + d2, self._binop(prec, op, v1, v2)
         if k == "un":
+            if e[1] == "uint4x32_to_prec_uniform1":   # not homogeneous: ops.ml:955-958
+                d, v = self.scalar(e[2][1], e[2][0])
+                p, q = unop_syntax(prec, e[1])
+                return d, p + v + q
             d, v = self.scalar(prec, e[2][0])
             return d, self._unop(prec, e[1], v)
         if k == "tern":
@@ -442,6 +455,26 @@ class Emitter:
             defs, val = self.scalar(t["prec"], s[3])
             a = "%s[%s] = %s;" % (t["ident"], self.offset(s[2], t["dims"]), val)
             return self._block(self._defs(defs), a)
+        if k == "set_from_vec":
+            # c_syntax.ml:548-592: one call, then `length` element stores; a Fixed_idx last
+            # index is advanced per element, any other gets "+ i" on the computed offset
+            t = self.tn[int(s[1])]
+            length, op, (arg, arg_prec) = int(s[3]), s[4], s[5]
+            assert op == "uint4x32_to_prec_uniform"
+            defs, val = self.scalar(arg_prec, arg)
+            vec_t = VEC_TYPE[(t["prec"], length)] if length > 1 else C_TYPE[t["prec"]]
+            fn = "uint4x32_to_%s_uniform_vec(" % t["prec"]
+            lines = ["%s vec_result = %s%s);" % (vec_t, fn, val)]
+            idcs = list(s[2])
+            for i in range(length):
+                last = idcs[-1]
+                if isinstance(last, str) and (last.isdigit() or (last[:1] == "-" and last[1:].isdigit())):
+                    off = self.offset(idcs[:-1] + [str(int(last) + i)], t["dims"])
+                else:
+                    off = "%s + %d" % (self.offset(idcs, t["dims"]), i)
+                lines.append("%s[%s] = %s;" % (t["ident"], off,
+                                               "vec_result" if length == 1 else "vec_result.v[%d]" % i))
+            return "{\n" + (self._defs(defs) + "\n" if defs else "") + "\n".join(lines) + "\n}"
         if k == "set_local":
             prec = self.tn[int(s[2])]["prec"]
             defs, val = self.scalar(prec, s[3])

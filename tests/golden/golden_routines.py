@@ -5,8 +5,14 @@ the `Low_level` routine the cc backend printed:
   d_fwd      test/operations/top_down_prec.ml      -> top_down_prec.c.expected
   out_fwd    test/operations/zero_out_local_decl.ml -> zero_out_local_decl.c.expected
   where_fwd  test/operations/test_where_precision.ml -> test_where_precision.c.expected
+and, for the random-number path, the routine of the IR golden
+  n3_fwd     test/operations/n3_fwd_with_prec-unoptimized.ll.expected
+(seed 0x2A as constant bits, a counter from the loop index, 2-round threefry, vector uniform
+conversion), whose single-precision results the reference prints in
+test/operations/test_threefry4x32.ml:37-45.
 """
-from ocannl_b200.low_level import (Comment, EmbedIndex, For, Routine, Seq, Set, ZeroOut, where)
+from ocannl_b200.low_level import (VEC_LENGTH, Affine, Binop, Comment, ConstBits, EmbedIndex, For, Routine, Seq,
+                                   Set, SetFromVec, Unop, ZeroOut, where)
 
 
 def d_fwd() -> Routine:
@@ -43,6 +49,33 @@ def where_fwd() -> Routine:
     b = r.tn("b_else_val", "bfloat16", [1])
     w = r.tn("where", "single", [1])
     r.body = Seq([Comment("where fwd"), Set(w, (0,), where(cond[0], a[0], b[0])), Comment("end")])
+    return r
+
+
+def n3_fwd(prec: str = "half", count: int = 5, variant: str = "light", scalar_too: bool = False) -> Routine:
+    """random_seed := 0x2A; n1 := index; bits := seed ^^ n1; n3[len*i ..] := uniform(bits[i])."""
+    r = Routine("n3_fwd_" + prec + "_" + variant)
+    r._next_sym = 5
+    seed = r.tn("random_seed", "uint4x32", [count])
+    n1 = r.tn("n1", "uint4x32", [count])
+    bits = r.tn("threefry4x32_" + variant, "uint4x32", [count])
+    length = VEC_LENGTH[prec]
+    n3 = r.tn("n3", prec, [length * count])
+    i5, i6, i7, i8 = r.syms(4)
+    body = [
+        Comment("n3 fwd"),
+        For(i5, 0, count - 1, Set(seed, (i5,), ConstBits(0x2A))),
+        For(i6, 0, count - 1, Set(n1, (i6,), EmbedIndex(i6))),
+        For(i7, 0, count - 1, Set(bits, (i7,), Binop("threefry4x32_" + variant, seed[i7], n1[i7]))),
+        For(i8, 0, count - 1, SetFromVec(n3, (Affine(((length, i8),)),), length, bits[i8])),
+    ]
+    if scalar_too:
+        # the one-value form of the conversion (Ops.Uint4x32_to_prec_uniform1)
+        first = r.tn("first", prec, [count])
+        i9 = r.sym()
+        body.append(For(i9, 0, count - 1, Set(first, (i9,), Unop("uint4x32_to_prec_uniform1", bits[i9], prec=prec))))
+    body.append(Comment("end"))
+    r.body = Seq(body)
     return r
 
 

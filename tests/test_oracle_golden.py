@@ -11,7 +11,7 @@ import pytest
 from ocannl_b200 import workloads as W
 from oracle.emit_c import Emitter
 from oracle.run_c import OracleRoutine
-from tests.golden.golden_routines import GOLDEN
+from tests.golden.golden_routines import GOLDEN, n3_fwd
 from tests.golden.make_cc_golden_digests import routine_text
 from tests.parity import run_oracle
 
@@ -78,7 +78,15 @@ def _port_lib(tmp_path_factory=None):
                 'uint4x32_t p_light(uint4x32_t k, uint4x32_t c){return arrayjit_threefry4x32_light(k,c);}\n'
                 'uint4x32_t p_crypto(uint4x32_t k, uint4x32_t c){return arrayjit_threefry4x32_crypto(k,c);}\n'
                 'float p_uni(uint32_t x){return uint32_to_single_uniform(x);}\n'
-                'uint4x32_t p_widen(uint32_t x){return uint32_to_uint4x32(x);}\n')
+                'uint4x32_t p_widen(uint32_t x){return uint32_to_uint4x32(x);}\n'
+                'uint4x32_t p_widen64(uint64_t x){return uint64_to_uint4x32(x);}\n'
+                'uint4x32_t p_widen_d(double x){return double_to_uint4x32(x);}\n'
+                'double2_t p_uni_d(uint4x32_t x){return uint4x32_to_double_uniform_vec(x);}\n'
+                'uint16x8_t p_uni_bf(uint4x32_t x){return uint4x32_to_bfloat16_uniform_vec(x);}\n'
+                'void p_uni_hf(uint4x32_t x, void* out){half8_t r = uint4x32_to_half_uniform_vec(x); memcpy(out, &r, 16);}\n'
+                'int32x4_t p_uni_i(uint4x32_t x){return uint4x32_to_int32_uniform_vec(x);}\n'
+                'uint16_t p_uni1_bf(uint4x32_t x){return uint4x32_to_bfloat16_uniform(x);}\n'
+                'double p_uni1_d(uint4x32_t x){return uint4x32_to_double_uniform(x);}\n')
     subprocess.run(["gcc", "-O2", "-shared", "-fPIC", "-I", os.path.dirname(os.path.dirname(src)), src, "-o", so, "-lm"],
                    check=True)
     return ctypes.CDLL(so)
@@ -118,6 +126,80 @@ def test_port_matches_reference_builtins():
     for x in [0, 1, 255, 256, 2**31, 2**32 - 1] + [int(v) for v in rng.integers(0, 2**32, 100)]:
         assert ref.uint32_to_single_uniform(x) == port.p_uni(x)
         assert list(ref.uint32_to_uint4x32(x).v) == list(port.p_widen(x).v)
+
+
+def test_port_uniform_forms_match_reference_builtins():
+    """Vector and scalar uniform conversions and the 64-bit widenings (builtins.c:345-606)."""
+    ref, port = _ref_lib(), _port_lib()
+
+    class D2(ctypes.Structure):
+        _fields_ = [("v", ctypes.c_double * 2)]
+
+    class H8(ctypes.Structure):
+        _fields_ = [("v", ctypes.c_uint16 * 8)]
+
+    class I4(ctypes.Structure):
+        _fields_ = [("v", ctypes.c_int32 * 4)]
+
+    pairs = [("uint4x32_to_double_uniform_vec", "p_uni_d", D2), ("uint4x32_to_bfloat16_uniform_vec", "p_uni_bf", H8),
+             ("uint4x32_to_int32_uniform_vec", "p_uni_i", I4),
+             ("uint4x32_to_bfloat16_uniform", "p_uni1_bf", ctypes.c_uint16),
+             ("uint4x32_to_double_uniform", "p_uni1_d", ctypes.c_double)]
+    rng = np.random.default_rng(1)
+    cases = [[0, 0, 0, 0], [2**32 - 1] * 4, [0xFFFF, 0x10000, 0x8000, 0x7FFF8000]] + \
+        [[int(x) for x in rng.integers(0, 2**32, 4)] for _ in range(300)]
+    for nr, npn, rt in pairs:
+        fr, fp = getattr(ref, nr), getattr(port, npn)
+        fr.restype = fp.restype = rt
+        fr.argtypes = fp.argtypes = [U4]
+        for w in cases:
+            a, b = fr(U4((ctypes.c_uint32 * 4)(*w))), fp(U4((ctypes.c_uint32 * 4)(*w)))
+            if hasattr(a, "v"):
+                assert bytes(a) == bytes(b), (nr, w)     # bit patterns, whatever the element type
+            else:
+                assert a == b, (nr, w)
+    # eight _Float16 come back in a vector register, which ctypes cannot describe: a shim compiled
+    # against the reference library stores them through a pointer
+    import subprocess
+    shim_c = os.path.join(os.path.dirname(HERE), "oracle", "_build", "ref_half_shim.c")
+    with open(shim_c, "w") as f:
+        f.write('#include <stdint.h>\n#include <string.h>\ntypedef struct { uint32_t v[4]; } uint4x32_t;\n'
+                'typedef struct { _Float16 v[8]; } half8_t;\nextern half8_t uint4x32_to_half_uniform_vec(uint4x32_t);\n'
+                'void r_uni_hf(uint4x32_t x, void* out){half8_t r = uint4x32_to_half_uniform_vec(x); memcpy(out, &r, 16);}\n')
+    shim_so = shim_c[:-2] + ".so"
+    subprocess.run(["gcc", "-O2", "-shared", "-fPIC", shim_c, "-o", shim_so, "-L", REF_DIR, "-lref_builtins",
+                    "-Wl,-rpath," + REF_DIR], check=True)
+    shim = ctypes.CDLL(shim_so)
+    shim.r_uni_hf.argtypes = port.p_uni_hf.argtypes = [U4, ctypes.c_void_p]
+    shim.r_uni_hf.restype = port.p_uni_hf.restype = None
+    for w in cases:
+        a, b = np.zeros(8, np.uint16), np.zeros(8, np.uint16)
+        shim.r_uni_hf(U4((ctypes.c_uint32 * 4)(*w)), a.ctypes.data)
+        port.p_uni_hf(U4((ctypes.c_uint32 * 4)(*w)), b.ctypes.data)
+        assert np.array_equal(a, b), w
+    ref.uint64_to_uint4x32.restype = port.p_widen64.restype = U4
+    ref.uint64_to_uint4x32.argtypes = port.p_widen64.argtypes = [ctypes.c_uint64]
+    ref.double_to_uint4x32.restype = port.p_widen_d.restype = U4
+    ref.double_to_uint4x32.argtypes = port.p_widen_d.argtypes = [ctypes.c_double]
+    for x in [0, 1, 42, 2**32, 2**64 - 1] + [int(v) for v in rng.integers(0, 2**63, 50)]:
+        assert list(ref.uint64_to_uint4x32(x).v) == list(port.p_widen64(x).v)
+    for d in [0.0, 42.0, -1.5, 1e300, 3.14159]:
+        assert list(ref.double_to_uint4x32(d).v) == list(port.p_widen_d(d).v)
+
+
+def test_threefry_uniform_known_answers():
+    """test/operations/test_threefry4x32.ml:37-45 prints the first five uniform values of the
+    default seed against the counters 0, 1, ...: the routine of the IR golden
+    n3_fwd_with_prec-unoptimized.ll.expected, run by the oracle, gives the same digits."""
+    out = run_oracle(n3_fwd("single", 10, "light", scalar_too=True), {})
+    assert ["%.4g" % v for v in out["n3"][:5]] == ["0.4638", "0.7325", "0.5608", "0.5066", "0.5019"]
+    assert np.all((out["n3"] >= 0.0) & (out["n3"] < 1.0))
+    assert np.array_equal(out["first"], out["n3"][::4])      # the one-value form takes word 0
+    # the half golden writes 8 values per counter; every precision stays inside [0, 1)
+    for prec in ("half", "bfloat16", "double"):
+        o = run_oracle(n3_fwd(prec, 5, "light"), {})["n3"]
+        v = W.bf16_bits_to_f32(o) if prec == "bfloat16" else o.astype(np.float64)
+        assert v.shape == (5 * (2 if prec == "double" else 8),) and np.all((v >= 0.0) & (v <= 1.0))
 
 
 def test_oracle_moons_step_matches_float64_model():

@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 from ocannl_b200 import workloads as W
-from tests.golden.golden_routines import GOLDEN
+from tests.golden.golden_routines import GOLDEN, n3_fwd
 from tests.parity import compare, run_device, run_oracle
 
 pytestmark = pytest.mark.gpu
@@ -31,6 +31,21 @@ def test_golden_routines_on_device(device):
         got, _ = run_device(device, ir, inputs)
         for t in ir.params():
             assert np.array_equal(got[t.ident].view(np.uint8), want[t.ident].view(np.uint8)), (name, t.ident)
+
+
+@pytest.mark.parametrize("prec", ["single", "double", "bfloat16", "half", "int32"])
+@pytest.mark.parametrize("variant,count,options", [("light", 5, None), ("crypto", 1000, "fuse=0"), ("light", 70001, None)])
+def test_threefry_uniform_bits(device, prec, variant, count, options):
+    """Random numbers are integer work: seed and counter widening, threefry4x32 (2-round and
+    20-round), the vector and the one-value uniform conversions agree bit for bit."""
+    ir = n3_fwd(prec, count, variant, scalar_too=prec != "int32")
+    want = run_oracle(ir, {})
+    got, _ = run_device(device, ir, {}, options=options)
+    for t in ir.params():
+        assert np.array_equal(np.ascontiguousarray(got[t.ident]).view(np.uint8),
+                              np.ascontiguousarray(want[t.ident]).view(np.uint8)), t.ident
+    if prec == "single" and variant == "light":     # test/operations/test_threefry4x32.ml:37-45
+        assert ["%.4g" % v for v in got["n3"][:5]] == ["0.4638", "0.7325", "0.5608", "0.5066", "0.5019"]
 
 
 @pytest.mark.parametrize("options", [None, "fuse=0"])
