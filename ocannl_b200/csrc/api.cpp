@@ -101,9 +101,9 @@ int b200_device_open(int ordinal, b200_dev** out) {
     cu().cuDeviceGetAttribute_(&d->cc_minor, CU_DEVICE_ATTRIBUTE_COMPUTE_CAPABILITY_MINOR, d->dev);
     // device-side status word, written by kernels whose bounded waits expire
     void* hp = nullptr;
-    cu_check(cu().cuMemHostAlloc_(&hp, 64, CU_MEMHOSTALLOC_DEVICEMAP | CU_MEMHOSTALLOC_PORTABLE), "cuMemHostAlloc");
-    d->status_host = (volatile unsigned int*)hp;
-    memset(hp, 0, 64);
+    cu_check(cu().cuMemHostAlloc_(&hp, 256, CU_MEMHOSTALLOC_DEVICEMAP | CU_MEMHOSTALLOC_PORTABLE), "cuMemHostAlloc");
+    d->status_host = (volatile unsigned int*)hp;   // words 0-1: status, 2-31: developer trace
+    memset(hp, 0, 256);
     cu_check(cu().cuMemHostGetDevicePointer_(&d->status_dev, hp, 0), "cuMemHostGetDevicePointer");
     *out = d.get();
     g_devs[ordinal] = std::move(d);

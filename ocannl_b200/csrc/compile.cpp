@@ -205,6 +205,10 @@ struct Piece {
   std::string decomp, body_text;
   std::set<int> used, written;
   bool uses_merge = false;
+  // row fusion: the outermost parallel loop ("row") and the work of one of its iterations
+  StmtP body;
+  std::string row_sym;
+  int64_t rows = 0, per_row = 0;
 };
 
 struct Builder {
@@ -328,30 +332,27 @@ struct Builder {
     return ci;
   }
 
-  // Grid-wide reduction of a single output element in two kernels.  Pass 1: every block
-  // reduces a strided slice of each Local_scope's flattened loop space and writes one partial
-  // per scope to scratch[scope_index * blocks + block].  Pass 2: one block combines the
-  // partials in block order (a fixed order: the result does not depend on scheduling) and
-  // evaluates the assignment.
+  // Grid-wide reduction of a single output element in one launch.  Every block reduces a strided
+  // slice of each Local_scope's flattened loop space and writes one partial per scope to
+  // scratch[scope_index * blocks + block]; the block that takes the last ticket of a counter in
+  // scratch (zero at link time, reset here) then combines the partials in block order -- a fixed
+  // order, so the result does not depend on scheduling -- and evaluates the assignment.
   void grid_reduce_stage(const StmtP& body, const CoopInfo& ci) {
     const Stmt& set = *body;
     const Tnode& t = code.prog.tn(set.tn);
     const int G = ci.grid_blocks;
     const size_t scratch_off = code.reduce_scratch_bytes;
-    code.reduce_scratch_bytes += (size_t)G * ci.scopes.size() * 8;
+    const size_t counter_off = (size_t)G * ci.scopes.size() * 8;
+    code.reduce_scratch_bytes += counter_off + 8;
     code.reduce_scratch_bytes = (code.reduce_scratch_bytes + 255) & ~(size_t)255;
 
-    Stage a, b;
-    a.kind = b.kind = Stage::Generic;
+    Stage a;
+    a.kind = Stage::Generic;
     a.kernel = kernel_name();
-    b.kernel = a.kernel + "_combine";
-    a.total = b.total = 1;
+    a.total = 1;
     a.block = 1024;
     a.coop = 1024;
     a.grid_override = G;
-    b.block = 256;
-    b.coop = 256;
-    b.grid_override = 1;
 
     Emitter ea(code.prog), eb(code.prog);
     ea.large_models = eb.large_models = opt.large_models;
@@ -377,7 +378,8 @@ struct Builder {
         const std::string T = Emitter::ctype(p);
         const double neutral = op == "add" ? 0.0 : (op == "max" ? -INFINITY : INFINITY);
         const std::string fn = op == "add" ? "sum" : op;
-        const std::string slot = "((" + T + "*)(b200_partials + " + std::to_string((size_t)si * G * 8) + "))";
+        const std::string at = "(b200_partials + " + std::to_string((size_t)si * G * 8) + "))";
+        const std::string slot = "((" + T + "*)" + at, vslot = "((volatile " + T + "*)" + at;
         pass1 += "  {\n    " + T + " " + name + " = " + ea.constant(neutral, p) + ";\n";
         pass1 += "    for (unsigned long long b200_l = (unsigned long long)blockIdx.x * 1024ull + threadIdx.x; b200_l < " +
                  std::to_string(total) + "ull; b200_l += (unsigned long long)gridDim.x * 1024ull) {\n";
@@ -397,11 +399,11 @@ struct Builder {
         pass1 += ea.stmt(*inner, 6);
         pass1 += "    }\n    " + name + " = b200_block_" + fn + "(" + name + ", b200_red);\n";
         pass1 += "    if (threadIdx.x == 0) " + slot + "[blockIdx.x] = " + name + ";\n  }\n";
-        // pass 2: fixed-order combine of the partials
+        // combine: the partials in block order
         pass2 += "  " + T + " " + name + " = " + eb.constant(neutral, p) + ";\n";
         pass2 += "  for (unsigned int b200_i = threadIdx.x; b200_i < " + std::to_string(G) + "u; b200_i += blockDim.x) " + name + " = ";
-        if (op == "add") pass2 += name + " + " + slot + "[b200_i];\n";
-        else pass2 += std::string(p == Prec::Double ? "f" : "f") + op + (p == Prec::Double ? "(" : "f(") + name + ", " + slot + "[b200_i]);\n";
+        if (op == "add") pass2 += name + " + " + vslot + "[b200_i];\n";
+        else pass2 += std::string("f") + op + (p == Prec::Double ? "(" : "f(") + name + ", " + vslot + "[b200_i]);\n";
         pass2 += "  " + name + " = b200_block_" + fn + "(" + name + ", b200_red);\n";
         eb.scope_subst[e.scope_id] = name;
         ++si;
@@ -412,24 +414,29 @@ struct Builder {
     rec(*set.value);
     Emitter::Res v = eb.scalar(t.prec, *set.value);
     eb.used_nodes.insert(set.tn);
-    pass2 += "  if (threadIdx.x == 0) " + t.ident + "[" + eb.offset(set.idcs, t.dims) + "] = " + Emitter::store_wrap(t.prec, v.expr) + ";\n";
+    pass2 += "  if (threadIdx.x == 0) {\n    " + t.ident + "[" + eb.offset(set.idcs, t.dims) + "] = " + Emitter::store_wrap(t.prec, v.expr) +
+             ";\n    *b200_ticket = 0u;\n  }\n";
 
-    std::set<int> none, written = {set.tn};
-    std::ostringstream ka, kb;
-    std::string sa = static_prologue(pass1, ea, 2), sb2 = static_prologue(pass2, eb, 2);
+    std::set<int> written = {set.tn};
+    Emitter eu(code.prog);
+    eu.used_nodes = ea.used_nodes;
+    eu.used_nodes.insert(eb.used_nodes.begin(), eb.used_nodes.end());
+    eu.uses_merge = ea.uses_merge || eb.uses_merge;
+    std::ostringstream ka;
+    std::string statics = static_prologue(pass1 + pass2, eu, 2);
     ka << "extern \"C\" __global__ void __launch_bounds__(1024) " << a.kernel << "(";
-    emit_params(ka, a, ea, none);
-    ka << (a.args.empty() ? "" : ", ") << "unsigned char* b200_partials) {\n  __shared__ double b200_red[32];\n" << sa << pass1 << "}\n\n";
+    emit_params(ka, a, eu, written);
+    ka << (a.args.empty() ? "" : ", ") << "unsigned char* b200_partials) {\n  __shared__ double b200_red[32];\n"
+       << "  __shared__ unsigned int b200_last;\n  unsigned int* b200_ticket = (unsigned int*)(b200_partials + " << counter_off << ");\n"
+       << statics << pass1
+       << "  __threadfence();\n  __syncthreads();\n"
+       << "  if (threadIdx.x == 0) b200_last = atomicAdd(b200_ticket, 1u) == gridDim.x - 1u ? 1u : 0u;\n"
+       << "  __syncthreads();\n  if (!b200_last) return;\n  __threadfence();\n"
+       << pass2 << "}\n\n";
     a.args.push_back({KArg::Scratch, (int)scratch_off});
-    kb << "extern \"C\" __global__ void __launch_bounds__(256) " << b.kernel << "(";
-    emit_params(kb, b, eb, written);
-    kb << (b.args.empty() ? "" : ", ") << "const unsigned char* b200_partials) {\n  __shared__ double b200_red[32];\n" << sb2 << pass2 << "}\n\n";
-    b.args.push_back({KArg::Scratch, (int)scratch_off});
-    src << ka.str() << kb.str();
-    a.note = "grid-wide reduction, pass 1 (" + std::to_string(G) + " blocks)";
-    b.note = "grid-wide reduction, pass 2 (combine)";
+    src << ka.str();
+    a.note = "grid-wide reduction (" + std::to_string(G) + " blocks, the last one combines)";
     code.stages.push_back(a);
-    code.stages.push_back(b);
   }
 
   // Accumulation whose reduced loops are OUTSIDE the output loops (back-propagation keeps the
@@ -622,6 +629,12 @@ struct Builder {
     for (auto& d : st.ser) ser_work *= std::max<int64_t>(1, d.extent());
     pc.fusable = opt.enable_fuse && st.total > 0 && (st.coop == 0 || st.coop == 32) &&
                  st.total * std::max(1, st.coop) <= 16384 && ser_work <= 4096;
+    if (opt.enable_fuse && st.coop == 0 && st.total > 0 && !st.par.empty() && st.par[0].from == 0) {
+      pc.body = body;
+      pc.row_sym = st.par[0].sym;
+      pc.rows = st.par[0].extent();
+      pc.per_row = st.total / pc.rows * ser_work;
+    }
     std::ostringstream note;
     note << "par=" << st.par.size() << " ser=" << st.ser.size()
          << (st.coop > 32 ? " block-per-element" : st.coop ? " warp-per-element" : "");
@@ -707,6 +720,84 @@ struct Builder {
     return f;
   }
 
+  // Row fusion.  Consecutive stages whose outermost parallel loop has the same extent, and which
+  // hand data to one another only within one iteration of that loop (every node written by one
+  // of them and touched by another is indexed by the row symbol on one fixed axis, nowhere else),
+  // run as ONE kernel: a thread takes a row and executes the stages one after the other for it,
+  // the inner parallel loops of each stage becoming short serial loops.  A softmax over ten
+  // logits (row max, exponentials, row sum) is one launch and one pass instead of three.
+  bool rows_independent(const std::vector<size_t>& run) {
+    std::map<int, int> writers, users;  // node -> number of stages writing / touching it
+    for (size_t i : run) {
+      const Piece& pc = pieces[i];
+      for (int n : pc.written) writers[n]++;
+      for (int n : pc.used) users[n]++;
+    }
+    std::map<int, int> axis;  // shared node -> axis that carries the row symbol
+    bool ok = true;
+    for (size_t i : run) {
+      const Piece& pc = pieces[i];
+      auto check = [&](int tn, const Indices& idcs) {
+        if (!writers.count(tn) || users[tn] < 2) return;   // private to one stage, or only read
+        int a = -1;
+        for (size_t k = 0; k < idcs.size(); ++k) {
+          if (idcs[k].kind == Index::Iter && idcs[k].sym == pc.row_sym && a < 0) a = (int)k;
+          else if (idcs[k].uses(pc.row_sym)) ok = false;
+        }
+        if (a < 0) { ok = false; return; }
+        auto it = axis.find(tn);
+        if (it == axis.end()) axis[tn] = a;
+        else if (it->second != a) ok = false;
+      };
+      walk_stmt(
+          *pc.body,
+          [&](const Scalar& e) {
+            if (e.kind == Scalar::Get) check(e.tn, e.idcs);
+            if (e.kind == Scalar::GetDyn && writers.count(e.tn) && users[e.tn] >= 2) ok = false;
+          },
+          [&](const Stmt& st) {
+            if (st.kind == Stmt::Set) {
+              if (st.vec_len > 0 && writers.count(st.tn) && users[st.tn] >= 2) ok = false;
+              check(st.tn, st.idcs);
+            }
+            if (st.kind == Stmt::ZeroOut) ok = false;
+          });
+    }
+    return ok;
+  }
+
+  Stage emit_rows(const std::vector<size_t>& run) {
+    Stage f;
+    f.kind = Stage::Generic;
+    f.kernel = code.stages[run.front()].kernel;
+    f.block = 128;
+    f.total = pieces[run.front()].rows;
+    Emitter em(code.prog);
+    std::set<int> written;
+    std::string text;
+    for (size_t i : run) {
+      const Stage& st = code.stages[i];
+      const Piece& pc = pieces[i];
+      em.used_nodes.insert(pc.used.begin(), pc.used.end());
+      written.insert(pc.written.begin(), pc.written.end());
+      em.uses_merge |= pc.uses_merge;
+      const std::string inner = std::to_string(st.total / pc.rows) + "ull";
+      text += "    for (unsigned long long b200_g = b200_row * " + inner + "; b200_g < (b200_row + 1ull) * " + inner +
+              "; ++b200_g) {\n" + pc.decomp + pc.body_text + "    }\n";
+    }
+    std::string statics = static_prologue(text, em, 2);
+    std::ostringstream k_src;
+    k_src << "extern \"C\" __global__ void __launch_bounds__(" << f.block << ") " << f.kernel << "(";
+    emit_params(k_src, f, em, written);
+    k_src << ") {\n" << statics
+          << "  for (unsigned long long b200_row = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; b200_row < "
+          << f.total << "ull; b200_row += (unsigned long long)gridDim.x * blockDim.x) {\n"
+          << text << "  }\n}\n\n";
+    src << k_src.str();
+    f.note = "row-fused " + std::to_string(run.size()) + " stages, one thread per row";
+    return f;
+  }
+
   // Decides which stages share a launch and writes the kernels' text.
   void emit_kernels() {
     std::vector<Stage> out;
@@ -719,7 +810,29 @@ struct Builder {
       auto it = pieces.find(i);
       return it != pieces.end() && it->second.fusable;
     };
+    auto row_candidate = [&](size_t i) {
+      auto it = pieces.find(i);
+      return it != pieces.end() && it->second.body && it->second.rows >= 256 && it->second.per_row <= 64;
+    };
     for (size_t i = 0; i < code.stages.size();) {
+      if (row_candidate(i)) {
+        // the longest run that stays row-independent; runs made only of small stages are left to
+        // the single-block fusion below, which also takes stages of unrelated shapes
+        std::vector<size_t> run = {i};
+        size_t j = i + 1;
+        bool all_small = fusable(i);
+        while (j < code.stages.size() && row_candidate(j) && pieces[j].rows == pieces[i].rows && run.size() < 16) {
+          run.push_back(j);
+          if (!rows_independent(run)) { run.pop_back(); break; }
+          all_small = all_small && fusable(j);
+          ++j;
+        }
+        if (run.size() >= 2 && !all_small) {
+          out.push_back(emit_rows(run));
+          i = run.back() + 1;
+          continue;
+        }
+      }
       if (fusable(i)) {
         std::vector<size_t> run;
         size_t j = i;

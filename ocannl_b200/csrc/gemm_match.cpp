@@ -621,9 +621,21 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
     }
     fn << "}\n";
   }
-  fn << "#ifdef B200_TRACE\n__device__ unsigned int* b200_trace_ptr;\n__device__ unsigned long long b200_trace_t0;\n"
-        "__device__ int b200_trace_on;\n__device__ __forceinline__ unsigned long long b200_now_ns();\n"
-        "#define B200_TRE(slot) do { if (blockIdx.x == 0 && threadIdx.x == 64 && b200_trace_on) b200_trace_ptr[slot] = (unsigned int)(b200_now_ns() - b200_trace_t0); } while (0)\n"
+  // Staging swizzle.  A row of the staging tile holds G 16-byte groups, so 8 / G rows share one
+  // 128-byte line of banks; the group index is xor-ed with a key that changes every 8 / G rows,
+  // which makes the 8 lanes of a quarter warp (one row group each when writing, 8 / G rows of G
+  // groups when reading) hit 8 different bank groups.
+  fn << "#define B200_STAGE_KEY(row, G) ((G) >= 8 ? ((row) & 7u) : (((row) / (8u / ((G) >= 8 ? 8u : (G)))) % (G)))\n";
+  // developer trace: the first epilogue thread of CTA 0 adds up the clock cycles it spends in
+  // each phase of the epilogue (slot = phase that just ended)
+  fn << "#ifdef B200_TRACE\n__device__ __forceinline__ void b200_tre(int slot, bool dump, unsigned int* out) {\n"
+        "  __shared__ unsigned int acc[16];\n  __shared__ long long last;\n"
+        "  if (blockIdx.x != 0 || threadIdx.x != 64) return;\n"
+        "  if (dump) { for (int i = 0; i < 16; ++i) { out[16 + i] = acc[i]; } return; }\n"
+        "  const long long now = clock64();\n"
+        "  if (slot < 0) { for (int i = 0; i < 16; ++i) acc[i] = 0; } else { acc[slot] += (unsigned int)(now - last); }\n"
+        "  last = clock64();\n}\n"
+        "#define B200_TRE(slot) b200_tre(slot, false, nullptr)\n"
         "#else\n#define B200_TRE(slot) do { } while (0)\n#endif\n"
      << "__device__ __forceinline__ void b200_tmem_ld_chunk(unsigned int taddr, unsigned int* r);\n"
      << "__device__ __forceinline__ void b200_epilogue_row(unsigned int* b200_r, unsigned int b200_b0, unsigned int b200_b1, "
@@ -664,6 +676,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   //      registers would touch 32 different lines per instruction; when the chunk is whole,
   //      contiguous and every row is 16-byte aligned, the warp transposes the chunk through a
   //      swizzled shared-memory staging tile and writes whole row segments instead.
+  fn << "#ifndef B200_DEBUG_NO_STORE\n";   // developer experiment: the epilogue without its stores
   for (auto& o : outs) {
     const Tnode& t = P.tn(o.tn);
     const int ebytes = prec_bytes(t.prec);
@@ -693,13 +706,13 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
              << "        q.z = " << pk << o.arr << "[8 * g + 4], " << o.arr << "[8 * g + 5]);\n"
              << "        q.w = " << pk << o.arr << "[8 * g + 6], " << o.arr << "[8 * g + 7]);\n";
         }
-        fn << "        b200_stage[b200_lane * G + (g ^ (b200_lane % G))] = q;\n      }\n"
+        fn << "        b200_stage[b200_lane * G + (g ^ B200_STAGE_KEY(b200_lane, G))] = q;\n      }\n"
            << "      __syncwarp();\n      B200_TRE(14);\n"
            << "      const unsigned long long b200_pv = (unsigned long long)b200_p;\n"
            << "#pragma unroll\n      for (int it = 0; it < G; ++it) {\n"
            << "        const unsigned int r = it * (32 / G) + b200_lane / G, c = b200_lane % G;\n"
            << "        const unsigned long long dst = __shfl_sync(0xffffffffu, b200_pv, r);\n"
-           << "        const uint4 q = b200_stage[r * G + (c ^ (r % G))];\n"
+           << "        const uint4 q = b200_stage[r * G + (c ^ B200_STAGE_KEY(r, G))];\n"
            << "        if (dst) *(uint4*)(dst + 16ull * c) = q;\n      }\n"
            << "      __syncwarp();\n"
            << "    } else if (b200_row_ok) {\n";
@@ -722,7 +735,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
       fn << ep.str() << "      " << t.ident << "[" << em.offset(o.idcs, t.dims) << "] = " << Emitter::store_wrap(t.prec, o.arr + "[b200_j]") << ";\n    }\n  }\n";
     }
   }
-  fn << "  B200_TRE(15);\n}\n";
+  fn << "#endif\n  B200_TRE(15);\n}\n";
 
   out->kind = Stage::Gemm;
   out->gemm = g;
@@ -746,6 +759,10 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   else bn = (int)((g.n.extent + 15) / 16 * 16);
   if (!g.b_kmajor) bn = (bn + row_elems - 1) / row_elems * row_elems;
   if (bn > 256) bn = 256;
+  if (const char* ov = getenv("B200_GEMM_BN")) {   // developer override for tile-shape experiments
+    const int want = atoi(ov);
+    if (want >= 16 && want <= 256 && want % 16 == 0 && want <= bn && (g.b_kmajor || want % row_elems == 0)) bn = want;
+  }
   const int bm = 128, bk = row_elems;
   const int umma_k = 32 / eb;
   const int stage_bytes = (bm + bn) * bk * eb;
@@ -757,7 +774,11 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   int chunk = (bn >= 32 && st.epi_tiles <= 2) ? 32 : 16;
   if (const char* ov = getenv("B200_EPI_CHUNK")) chunk = atoi(ov);
   const bool light = false;  // 16 warps measured slower: the register cap (96) makes the epilogue spill
-  const int epi_warps = light ? 16 : (bn >= 128 ? 8 : 4);
+  int epi_warps = light ? 16 : (bn >= 128 ? 8 : 4);
+  if (const char* ov = getenv("B200_GEMM_EPI_WARPS")) {
+    const int want = atoi(ov);
+    if ((want == 4 || want == 8 || want == 16) && bn % (want / 4 * chunk) == 0) epi_warps = want;
+  }
   const int staging = 32 * chunk * st.epi_out_bytes;   // per warp
   // 227 KB per CTA: ring + alignment slack + barriers + one staging tile per epilogue warp
   int stages = (227 * 1024 - 1024 - 256 - epi_warps * staging) / stage_bytes;

@@ -213,9 +213,14 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
   const unsigned int lane = threadIdx.x & 31u;
 #ifdef B200_TRACE
   const unsigned long long b200_t0 = b200_now_ns();
-  if (blockIdx.x == 0 && threadIdx.x == 64) { b200_trace_ptr = status; b200_trace_t0 = b200_t0; b200_trace_on = 0; }
+  B200_TRE(-1);
 #endif
 
+  if (threadIdx.x == 32) {
+    // the descriptors are fetched while the barriers and the tensor memory are being set up
+    asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_b) : "memory");
+  }
   if (threadIdx.x == 0) {
     for (unsigned int s = 0; s < B200_STAGES; ++s) {
       b200_mbar_init(bar_full + 8u * s, 1);
@@ -364,6 +369,9 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
       if (!b200_wait(bar_acc_full + 8u * acc, acc_phase, abort_flag, status, 4u)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (warp == 2 && lane == 0) { if (tile == blockIdx.x) B200_TR(8); else if (tile == blockIdx.x + gridDim.x) B200_TR(10); }
+#ifdef B200_TRACE
+      B200_TRE(3);   // waiting for the accumulator (and the operand prefetch before it)
+#endif
       const unsigned int taddr = tmem_base + acc * B200_BN + ((quarter * 32u) << 16);
       // One register buffer: the epilogue issues the TMEM load of the next chunk as soon as it
       // has consumed the current one, so the load overlaps the epilogue's stores.  (The loop is
@@ -378,20 +386,27 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
         if (b200_n0 >= shape.N) break;  // warp-uniform
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #ifdef B200_TRACE
-        if (blockIdx.x == 0 && threadIdx.x == 64) { b200_trace_on = (tile == blockIdx.x && c == B200_EPI_CHUNK) ? 1 : 0; }
         B200_TRE(4);
 #endif
         const bool b200_has_next = (c + B200_EPI_CHUNK < cols_per_warp) && (b200_n0 + B200_EPI_CHUNK < shape.N);
         const unsigned int b200_next_taddr = taddr + col + B200_EPI_CHUNK;
         // every lane takes part: rows beyond M compute nothing but help move the chunk
+#ifndef B200_DEBUG_NO_EPILOGUE   // developer experiment: how fast is the main loop left alone?
         B200_EPILOGUE_ROW
+#endif
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) b200_mbar_arrive(bar_acc_empty + 8u * acc);
       if (warp == 2 && lane == 0) { if (tile == blockIdx.x) B200_TR(9); else if (tile == blockIdx.x + gridDim.x) B200_TR(11); }
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+#ifdef B200_TRACE
+      B200_TRE(5);   // release of the accumulator buffer
+#endif
     }
+#ifdef B200_TRACE
+    b200_tre(0, true, status);
+#endif
   }
 
   // ---------------------------------------------------------------------- teardown

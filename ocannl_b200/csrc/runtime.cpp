@@ -30,9 +30,12 @@ CUdeviceptr b200_dev::address(int pool_id, size_t offset, size_t bytes) {
 void b200_dev::check_status() {
   if (status_host && getenv("B200_TRACE")) {
     fprintf(stderr, "[b200 trace] ns since CTA 0 start: setup %u, first loads issued %u, producer done %u, first operands %u, "
-                    "tile0 mma issued %u, tile1 mma issued %u, epi0 begin %u end %u, epi1 begin %u end %u, all done %u | chunk1: tmem ready %u, computed %u, staged %u, stored %u\n",
+                    "tile0 mma issued %u, tile1 mma issued %u, epi0 begin %u end %u, epi1 begin %u end %u, all done %u\n"
+                    "[b200 trace] epilogue cycles of warp 2 by phase: accumulator wait %u, tmem load wait %u, operand loads + "
+                    "compute %u, staging %u, stores %u, release %u\n",
             status_host[2], status_host[3], status_host[4], status_host[5], status_host[6], status_host[7], status_host[8],
-            status_host[9], status_host[10], status_host[11], status_host[12], status_host[4], status_host[13], status_host[14], status_host[15]);
+            status_host[9], status_host[10], status_host[11], status_host[12], status_host[16 + 3], status_host[16 + 4],
+            status_host[16 + 13], status_host[16 + 14], status_host[16 + 15], status_host[16 + 5]);
   }
   if (status_host && status_host[0] != 0) {
     unsigned int code = status_host[0], where = status_host[1];
@@ -73,7 +76,12 @@ void b200_routine::link(b200_dev* d, b200_code* c, const b200_binding* b, int n)
   const size_t reduce_off = off;
   off += c->code.reduce_scratch_bytes;
   scratch_bytes = off;
-  if (scratch_bytes) cu_check(cu().cuMemAlloc_(&scratch, scratch_bytes), "cuMemAlloc(scratch)");
+  if (scratch_bytes) {
+    cu_check(cu().cuMemAlloc_(&scratch, scratch_bytes), "cuMemAlloc(scratch)");
+    // the tickets of grid-wide reductions start at zero (each kernel resets its own afterwards)
+    if (c->code.reduce_scratch_bytes)
+      cu_check(cu().cuMemsetD8Async_(scratch + reduce_off, 0, c->code.reduce_scratch_bytes, d->stream), "cuMemsetD8Async(reduce scratch)");
+  }
 
   for (auto& t : P.tnodes) {
     if (t.mode == Mode::Local) {
