@@ -453,6 +453,12 @@ def main():
                 "kernel": stages[dom]["kernel"], "kernel_ms": dom_ms,
                 "shape": {k: stages[dom][k] for k in ("m", "n", "k", "batch")},
                 "stage_ms": [round(s, 5) for s in shares]}
+    # DRAM bytes of one launch from the ncu capture summarised in
+    # profiles/contraction_mlp_layer_8192x1024x784.md (dram__bytes_read.sum + dram__bytes_write.sum)
+    if stages[dom]["kernel"] == "mlp_fwd_8192_s0":
+        roofline["traffic"] = 14477312
+        roofline["traffic_unit"] = "bytes per launch (ncu; outputs stay in L2)"
+        roofline["algorithmic_bytes"] = stages[dom]["bytes"]
     rt.profile(False)
 
     train = None if args.no_train else train_step(dev, dist, rank, world, rows, K, Wm)
