@@ -200,6 +200,11 @@ std::string Code::describe() const {
 namespace {
 
 // What generic_stage knows about a stage before its kernel text is written.
+// First statements of every generated kernel: let the next kernel in the stream be placed, then
+// wait until the grids before this one have completed and their writes are visible.
+static const char* kGridEntry =
+    "  asm volatile(\"griddepcontrol.launch_dependents;\");\n  asm volatile(\"griddepcontrol.wait;\" ::: \"memory\");\n";
+
 struct Piece {
   bool fusable = false;
   std::string decomp, body_text;
@@ -327,7 +332,7 @@ struct Builder {
     // scratch and a second, single-block kernel combines them
     if (par_total == 1 && extent >= 32768) {
       ci.width = 1024;
-      ci.grid_blocks = (int)std::min<int64_t>(296, (extent + 4095) / 4096);
+      ci.grid_blocks = (int)std::min<int64_t>(296, (extent + 1023) / 1024);
     }
     return ci;
   }
@@ -426,7 +431,7 @@ struct Builder {
     std::string statics = static_prologue(pass1 + pass2, eu, 2);
     ka << "extern \"C\" __global__ void __launch_bounds__(1024) " << a.kernel << "(";
     emit_params(ka, a, eu, written);
-    ka << (a.args.empty() ? "" : ", ") << "unsigned char* b200_partials) {\n  __shared__ double b200_red[32];\n"
+    ka << (a.args.empty() ? "" : ", ") << "unsigned char* b200_partials) {\n" << kGridEntry << "  __shared__ double b200_red[32];\n"
        << "  __shared__ unsigned int b200_last;\n  unsigned int* b200_ticket = (unsigned int*)(b200_partials + " << counter_off << ");\n"
        << statics << pass1
        << "  __threadfence();\n  __syncthreads();\n"
@@ -529,7 +534,7 @@ struct Builder {
     std::ostringstream k;
     k << "extern \"C\" __global__ void __launch_bounds__(1024) " << st.kernel << "(";
     emit_params(k, st, em, written);
-    k << ") {\n" << statics << "  __shared__ " << T << " b200_part[32][33];\n"
+    k << ") {\n" << kGridEntry << statics << "  __shared__ " << T << " b200_part[32][33];\n"
       << "  for (unsigned long long b200_g0 = (unsigned long long)blockIdx.x * 32ull; b200_g0 < " << st.total
       << "ull; b200_g0 += (unsigned long long)gridDim.x * 32ull) {\n"
       << "    const unsigned long long b200_g = b200_g0 + threadIdx.x;\n"
@@ -652,7 +657,7 @@ struct Builder {
     std::ostringstream k_src;
     k_src << "extern \"C\" __global__ void __launch_bounds__(" << st.block << ") " << st.kernel << "(";
     emit_params(k_src, st, em, pc.written);
-    k_src << ") {\n" << statics;
+    k_src << ") {\n" << kGridEntry << statics;
     if (st.coop > 32) {
       k_src << "  __shared__ double b200_red[32];\n";
       k_src << "  const unsigned int b200_t = threadIdx.x;\n";
@@ -714,7 +719,7 @@ struct Builder {
     std::ostringstream k_src;
     k_src << "extern \"C\" __global__ void __launch_bounds__(1024) " << f.kernel << "(";
     emit_params(k_src, f, em, written);
-    k_src << ") {\n" << statics << text << "}\n\n";
+    k_src << ") {\n" << kGridEntry << statics << text << "}\n\n";
     src << k_src.str();
     f.note = "fused " + std::to_string(idx.size()) + " small stages in one block";
     return f;
@@ -789,7 +794,7 @@ struct Builder {
     std::ostringstream k_src;
     k_src << "extern \"C\" __global__ void __launch_bounds__(" << f.block << ") " << f.kernel << "(";
     emit_params(k_src, f, em, written);
-    k_src << ") {\n" << statics
+    k_src << ") {\n" << kGridEntry << statics
           << "  for (unsigned long long b200_row = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; b200_row < "
           << f.total << "ull; b200_row += (unsigned long long)gridDim.x * blockDim.x) {\n"
           << text << "  }\n}\n\n";

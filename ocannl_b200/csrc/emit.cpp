@@ -412,6 +412,7 @@ Emitter::Res Emitter::scalar(Prec prec, const Scalar& e) {
         uses_merge = true;
       }
       std::string name = e.kind == Scalar::GetMerge ? "merge_buffer" : t.ident;
+      ++direct_reads;
       r.expr = cv.first + load_wrap(t.prec, name + "[" + offset(e.idcs, t.dims) + "]") + cv.second;
       return r;
     }
@@ -420,6 +421,7 @@ Emitter::Res Emitter::scalar(Prec prec, const Scalar& e) {
       auto cv = convert(t.prec, prec);
       Res d = scalar(e.args[0].prec, *e.args[0].s);
       used_nodes.insert(e.tn);
+      ++direct_reads;
       std::string dyn = std::string("((") + (large_models ? "unsigned long long" : "unsigned int") + ")(" + d.expr + "))";
       r.defs = d.defs;
       r.expr = cv.first + load_wrap(t.prec, t.ident + "[" + offset(e.idcs, t.dims, e.dyn_axis, dyn) + "]") + cv.second;
@@ -702,6 +704,7 @@ std::string Emitter::pair_scalar(Prec prec, const Scalar& e, std::string& code) 
       used_nodes.insert(e.tn);
       for (auto& lt : load_tiles)
         if (lt.tn == e.tn && same_indices(lt.idcs, e.idcs)) return pair_convert(t.prec, prec, lt.expr, code);
+      ++direct_reads;
       const std::string off0 = offset(e.idcs, t.dims);
       pair_hi = true;
       const std::string off1 = offset(e.idcs, t.dims);

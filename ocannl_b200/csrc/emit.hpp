@@ -45,6 +45,7 @@ struct Emitter {
   std::set<int> used_nodes;
   bool uses_statics = false, uses_merge = false;
   int tmp_counter = 0;
+  int direct_reads = 0;   // reads emitted as plain memory accesses (not served by a register tile)
 
   explicit Emitter(const Program& p) : P(p) {}
 

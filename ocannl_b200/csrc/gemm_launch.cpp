@@ -125,9 +125,7 @@ void gemm_enqueue(b200_routine* r, int si) {
   args.push_back(&L->status);
   std::vector<CUdeviceptr>& vals = r->arg_values[si];
   for (size_t a = 0; a < vals.size(); ++a) args.push_back(&vals[a]);
-  cu_check(cu().cuLaunchKernel_(r->fns[si], L->grid, 1, 1, (unsigned)st.block, 1, 1, (unsigned)st.smem_bytes, r->dev->stream,
-                                args.data(), nullptr),
-           "cuLaunchKernel(contraction)");
+  launch_kernel(r->dev, r->fns[si], L->grid, (unsigned)st.block, 1, (unsigned)st.smem_bytes, args.data(), "cuLaunchKernelEx(contraction)");
 }
 
 void gemm_release(GemmLaunch* g) { delete g; }

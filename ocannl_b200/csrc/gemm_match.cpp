@@ -373,7 +373,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   // ---- operands of the epilogue that run along n (bias[n], mask[s, n], a residual x[b, s, n]):
   //      pre-loaded into a register tile with 16-byte loads, so that the per-column code has no
   //      dependent global load in it
-  std::string load_code, prefetch_code;
+  std::string load_code, tile_decls;
   int n_in_tiles = 0;
   std::set<int> not_loadable = {set.tn};
   auto collect_loads = [&](const Scalar& root, const std::map<std::string, std::string>* ren) {
@@ -403,7 +403,8 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
               if (same) dup = true;
             }
           if (ok && !dup && n_in_tiles < 4) {
-            const std::string arr = "b200_i" + std::to_string(n_in_tiles++);
+            const std::string member = "i" + std::to_string(n_in_tiles++);
+            const std::string arr = "b200_t." + member;
             Indices row = canon;
             row.back().kind = Index::Fixed;
             row.back().fixed = 0;
@@ -412,7 +413,8 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
             const bool f32 = t.prec == Prec::Single;
             std::ostringstream lc;
             if (!pair) {
-            lc << "  " << T << " " << arr << "[B200_EPI_CHUNK];\n  if (b200_row_ok) {\n"
+            tile_decls += std::string("  ") + T + " " + member + "[B200_EPI_CHUNK];\n";
+            lc << "  if (b200_row_ok) {\n"
                << "    const " << T << "* b200_p = " << t.ident << " + (" << em.offset(row, t.dims) << ") + b200_n0;\n"
                << "    if (b200_n0 + B200_EPI_CHUNK <= b200_N && (((unsigned long long)b200_p) & 15ull) == 0ull) {\n"
                << "#pragma unroll\n      for (int v = 0; v < B200_EPI_CHUNK / " << (f32 ? 4 : 8) << "; ++v) {\n"
@@ -429,7 +431,8 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
                << "[j] = (b200_n0 + (unsigned int)j < b200_N) ? b200_p[j] : (" << T << ")0;\n    }\n  }\n";
             } else {
             // one pair per entry: packed words are taken as they lie in memory
-            lc << "  " << Emitter::pair_type(t.prec) << " " << arr << "[B200_EPI_CHUNK / 2];\n  if (b200_row_ok) {\n"
+            tile_decls += std::string("  ") + Emitter::pair_type(t.prec) + " " + member + "[B200_EPI_CHUNK / 2];\n";
+            lc << "  if (b200_row_ok) {\n"
                << "    const " << T << "* b200_p = " << t.ident << " + (" << em.offset(row, t.dims) << ") + b200_n0;\n"
                << "    if (b200_n0 + B200_EPI_CHUNK <= b200_N && (((unsigned long long)b200_p) & 15ull) == 0ull) {\n"
                << "#pragma unroll\n      for (int v = 0; v < B200_EPI_CHUNK / " << (f32 ? 4 : 8) << "; ++v) {\n"
@@ -448,12 +451,6 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
             lc << "      }\n    }\n  }\n";
             }
             load_code += lc.str();
-            // the same lines, requested early (before the accumulator is ready) so that the
-            // loads above hit in L1 instead of paying an L2 round trip per chunk
-            prefetch_code += "    { const char* b200_q = (const char*)(" + t.ident + " + (" + em.offset(row, t.dims) +
-                             ") + b200_n0);\n      asm volatile(\"prefetch.global.L1 [%0];\" ::\"l\"(b200_q));\n"
-                             "      asm volatile(\"prefetch.global.L1 [%0];\" ::\"l\"(b200_q + B200_EPI_CHUNK * " +
-                             std::to_string(prec_bytes(t.prec)) + " - 1));\n    }\n";
             em.load_tiles.push_back({e.tn, e.idcs, arr + "[b200_j]"});
             em.used_nodes.insert(e.tn);
           }
@@ -605,18 +602,49 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   }
   if (em.uses_merge) return false;
 
+  std::string row_code;
+  for (auto& o : outs) {
+    const Tnode& t = P.tn(o.tn);
+    const int ebytes = prec_bytes(t.prec);
+    if (!(o.unit_n && (ebytes == 4 || ebytes == 2))) continue;
+    const std::string G = std::string("(B200_EPI_CHUNK / ") + (ebytes == 4 ? "4" : "8") + ")";
+    const std::string member = "r" + std::to_string(o.tn);
+    tile_decls += "  unsigned long long " + member + "[" + G + "];\n";
+    row_code += "  {\n#ifdef B200_DEBUG_NO_GLOBAL_STORE\n    const unsigned long long b200_pv = 0ull;\n#else\n"
+                "    const unsigned long long b200_pv = b200_row_ok ? (unsigned long long)(" + t.ident + " + (" + o.row_off +
+                ")) : 0ull;\n#endif\n#pragma unroll\n    for (int it = 0; it < " + G + "; ++it) b200_t." + member +
+                "[it] = __shfl_sync(0xffffffffu, b200_pv, it * (32 / " + G + ") + b200_lane / " + G + ");\n  }\n";
+  }
   {
-    // parameters mirror the epilogue's so that the kernel can use one argument list
-    fn << "__device__ __forceinline__ void b200_epilogue_prefetch(unsigned int b200_b0, unsigned int b200_b1, "
+    // Operand tiles of one chunk.  They do not depend on the accumulator, so the kernel fills them
+    // for a tile's first chunk while the tensor cores still work on it, and the epilogue refills
+    // them for the next chunk as soon as it has consumed the current one (the loads then overlap
+    // the stores).  Parameters mirror the epilogue's so that one argument list serves both.
+    fn << "struct b200_in_tiles {\n" << tile_decls << (tile_decls.empty() ? "  int none;\n" : "") << "};\n"
+       << "__device__ __forceinline__ void b200_epilogue_load(b200_in_tiles& b200_t, unsigned int b200_b0, unsigned int b200_b1, "
           "unsigned int b200_m, bool b200_row_ok, unsigned int b200_n0, unsigned int b200_N"
        << params << ") {\n";
-    if (!prefetch_code.empty()) {
+    if (!load_code.empty()) {
       fn << statics_prologue;
       ep.str("");
       if (gb.size() == 2) { recover(gb[0], "b200_b0"); recover(gb[1], "b200_b1"); }
       else if (gb.size() == 1) { recover(gb[0], "b200_b1"); }
       recover(dm, "b200_m");
-      fn << ep.str() << unit_syms << "  if (b200_row_ok && b200_n0 < b200_N) {\n" << prefetch_code << "  }\n";
+      fn << ep.str() << unit_syms << load_code;
+      ep.str("");
+    }
+    fn << "}\n";
+    // Row pointers of the transposed store, once per tile: entry `it` is the address of column 0
+    // of the row this lane writes in store step `it` (0 for rows beyond M).
+    fn << "__device__ __forceinline__ void b200_epilogue_rows(b200_in_tiles& b200_t, unsigned int b200_b0, unsigned int b200_b1, "
+          "unsigned int b200_m, bool b200_row_ok" << params << ") {\n";
+    if (!row_code.empty()) {
+      fn << statics_prologue << "  const unsigned int b200_lane = threadIdx.x & 31u;\n";
+      ep.str("");
+      if (gb.size() == 2) { recover(gb[0], "b200_b0"); recover(gb[1], "b200_b1"); }
+      else if (gb.size() == 1) { recover(gb[0], "b200_b1"); }
+      recover(dm, "b200_m");
+      fn << ep.str() << unit_syms << row_code;
       ep.str("");
     }
     fn << "}\n";
@@ -640,7 +668,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
      << "__device__ __forceinline__ void b200_tmem_ld_chunk(unsigned int taddr, unsigned int* r);\n"
      << "__device__ __forceinline__ void b200_epilogue_row(unsigned int* b200_r, unsigned int b200_b0, unsigned int b200_b1, "
         "unsigned int b200_m, bool b200_row_ok, unsigned int b200_n0, unsigned int b200_N, uint4* b200_stage, "
-        "bool b200_has_next, unsigned int b200_next_taddr"
+        "bool b200_has_next, unsigned int b200_next_taddr, b200_in_tiles& b200_t"
      << params << ") {\n"
      << statics_prologue;
   fn << "  const unsigned int b200_lane = threadIdx.x & 31u;\n";
@@ -653,29 +681,35 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
     fn << ep.str();
     ep.str("");
   }
-  fn << unit_syms << load_code;
+  fn << unit_syms;
   // output tiles hold expression values (16-bit precisions as rounded floats); they are packed at the store
+  // The arithmetic of rows beyond M and columns beyond N is skipped only when it reads memory
+  // itself; when every operand comes from a register tile it runs on whatever the registers hold
+  // (nothing of it is stored), which saves a possibly divergent branch per column.
+  const std::string guard = (em.direct_reads > 0 || form_b) ? "b200_row_ok && b200_n < b200_N" : "true";
   if (pair) {
     for (auto& o : outs) fn << "  " << Emitter::pair_type(P.tn(o.tn).prec) << " " << o.arr << "[B200_EPI_CHUNK / 2];\n";
     fn << "#pragma unroll\n  for (int b200_j = 0; b200_j < B200_EPI_CHUNK / 2; ++b200_j) {\n"
        << "    const unsigned int b200_n = b200_n0 + 2u * (unsigned int)b200_j;\n"
-       << "    if (b200_row_ok && b200_n < b200_N) {\n"
+       << "    if (" << guard << ") {\n"
        << "      const b200_f2 b200_acc = {__uint_as_float(b200_r[2 * b200_j]), __uint_as_float(b200_r[2 * b200_j + 1])};\n";
   } else {
   for (auto& o : outs) fn << "  " << Emitter::rtype(P.tn(o.tn).prec) << " " << o.arr << "[B200_EPI_CHUNK];\n";
   fn << "#pragma unroll\n  for (int b200_j = 0; b200_j < B200_EPI_CHUNK; ++b200_j) {\n"
      << "    const unsigned int b200_n = b200_n0 + (unsigned int)b200_j;\n"
-     << "    if (b200_row_ok && b200_n < b200_N) {\n"
+     << "    if (" << guard << ") {\n"
      << "      const float b200_acc = __uint_as_float(b200_r[b200_j]);\n";
   }
   recover(dn, "b200_n");
   fn << ep.str() << body << "    }\n  }\n";
   // the accumulator chunk is consumed: start fetching the next one while this one is stored
-  fn << "  B200_TRE(13);\n  if (b200_has_next) b200_tmem_ld_chunk(b200_next_taddr, b200_r);\n";
+  fn << "  B200_TRE(13);\n  if (b200_has_next) {\n    b200_tmem_ld_chunk(b200_next_taddr, b200_r);\n"
+     << "    b200_epilogue_load(b200_t, b200_b0, b200_b1, b200_m, b200_row_ok, b200_n0 + B200_EPI_CHUNK, b200_N" << args << ");\n  }\n";
   // ---- store the register tiles.  A thread owns one row of the chunk, so storing from
   //      registers would touch 32 different lines per instruction; when the chunk is whole,
   //      contiguous and every row is 16-byte aligned, the warp transposes the chunk through a
   //      swizzled shared-memory staging tile and writes whole row segments instead.
+  fn << "#ifdef B200_DEBUG_ONLY_TMEM\n  return;\n#endif\n";   // developer experiment: TMEM traffic alone
   fn << "#ifndef B200_DEBUG_NO_STORE\n";   // developer experiment: the epilogue without its stores
   for (auto& o : outs) {
     const Tnode& t = P.tn(o.tn);
@@ -708,12 +742,11 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
         }
         fn << "        b200_stage[b200_lane * G + (g ^ B200_STAGE_KEY(b200_lane, G))] = q;\n      }\n"
            << "      __syncwarp();\n      B200_TRE(14);\n"
-           << "      const unsigned long long b200_pv = (unsigned long long)b200_p;\n"
            << "#pragma unroll\n      for (int it = 0; it < G; ++it) {\n"
            << "        const unsigned int r = it * (32 / G) + b200_lane / G, c = b200_lane % G;\n"
-           << "        const unsigned long long dst = __shfl_sync(0xffffffffu, b200_pv, r);\n"
+           << "        const unsigned long long dst = b200_t.r" << o.tn << "[it];\n"
            << "        const uint4 q = b200_stage[r * G + (c ^ B200_STAGE_KEY(r, G))];\n"
-           << "        if (dst) *(uint4*)(dst + 16ull * c) = q;\n      }\n"
+           << "        if (dst) *(uint4*)(dst + (unsigned long long)b200_n0 * " << ebytes << "ull + 16ull * c) = q;\n      }\n"
            << "      __syncwarp();\n"
            << "    } else if (b200_row_ok) {\n";
       } else {
@@ -803,8 +836,9 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   o << "#define B200_EPI_CHUNK " << chunk << "\n#define B200_STAGING_BYTES " << staging << "\n";
   o << g.epilogue << "\n";
   o << "#define B200_EPI_PARAMS " << params << "\n";
-  o << "#define B200_EPILOGUE_PREFETCH b200_epilogue_prefetch(b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_pn0, shape.N" << args << ");\n";
-  o << "#define B200_EPILOGUE_ROW b200_epilogue_row(b200_r, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_n0, shape.N, b200_stage, b200_has_next, b200_next_taddr" << args << ");\n";
+  o << "#define B200_EPILOGUE_ROWS b200_epilogue_rows(b200_tiles, b200_b0, b200_b1, b200_m, b200_m < shape.M" << args << ");\n";
+  o << "#define B200_EPILOGUE_LOAD b200_epilogue_load(b200_tiles, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_pn0, shape.N" << args << ");\n";
+  o << "#define B200_EPILOGUE_ROW b200_epilogue_row(b200_r, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_n0, shape.N, b200_stage, b200_has_next, b200_next_taddr, b200_tiles" << args << ");\n";
   o << kGemmSource << "\n";
   std::ostringstream note;
   note << "tcgen05 " << bm << "x" << bn << "x" << bk << " stages=" << stages << " epi_warps=" << epi_warps

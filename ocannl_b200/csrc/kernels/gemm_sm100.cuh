@@ -157,6 +157,11 @@ __device__ __forceinline__ void b200_tmem_ld16(unsigned int taddr, unsigned int*
 }
 
 __device__ __forceinline__ void b200_tmem_ld_chunk(unsigned int taddr, unsigned int* r) {
+#ifdef B200_DEBUG_NO_TMEM   // developer experiment: the epilogue without its TMEM loads (garbage results)
+#pragma unroll
+  for (int i = 0; i < B200_EPI_CHUNK; ++i) r[i] = taddr + i;
+  return;
+#endif
 #if B200_EPI_CHUNK == 64
   b200_tmem_ld32(taddr, r);
   b200_tmem_ld32(taddr + 32u, r + 32);
@@ -209,6 +214,8 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
   volatile unsigned int* tmem_slot = (volatile unsigned int*)(bars + 2 * B200_STAGES + 4);
   volatile unsigned int* abort_flag = tmem_slot + 1;
 
+  // the next kernel in the stream may be placed as soon as every CTA of this one is running
+  asm volatile("griddepcontrol.launch_dependents;");
   const unsigned int warp = threadIdx.x >> 5;
   const unsigned int lane = threadIdx.x & 31u;
 #ifdef B200_TRACE
@@ -239,6 +246,8 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  // set-up above touched no global memory; from here on the grids before this one must be complete
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -359,12 +368,13 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
       const unsigned int nt = r / rows;
       const unsigned int b200_b0 = bidx / shape.B1, b200_b1 = bidx - b200_b0 * shape.B1;
       const unsigned int b200_m = mt * B200_BM + quarter * 32u + lane;
-      // while the tensor cores are still busy with this tile, pull the epilogue's operands
-      // (bias, mask, residual rows ...) of every chunk this warp owns towards L1
-#pragma unroll 1
-      for (unsigned int c = 0; c < cols_per_warp; c += B200_EPI_CHUNK) {
-        const unsigned int b200_pn0 = nt * B200_BN + col_half * cols_per_warp + c;
-        B200_EPILOGUE_PREFETCH
+      // while the tensor cores are still busy with this tile, load the epilogue's operands (bias,
+      // mask, residual rows ...) of the first chunk this warp owns
+      b200_in_tiles b200_tiles;
+      B200_EPILOGUE_ROWS
+      {
+        const unsigned int b200_pn0 = nt * B200_BN + col_half * cols_per_warp;
+        if (b200_pn0 < shape.N) { B200_EPILOGUE_LOAD }
       }
       if (!b200_wait(bar_acc_full + 8u * acc, acc_phase, abort_flag, status, 4u)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

@@ -136,6 +136,31 @@ void b200_routine::link(b200_dev* d, b200_code* c, const b200_binding* b, int n)
   }
 }
 
+// One kernel launch.  Every kernel of this library releases its dependents at entry and waits for
+// the grids before it (griddepcontrol) ahead of its first access to memory, so a launch may be
+// marked for programmatic stream serialisation: the next kernel's blocks are placed, and run their
+// set-up, while the tail of the previous kernel drains.  B200_PDL=0 turns the marking off.
+void launch_kernel(b200_dev* dev, CUfunction fn, unsigned grid, unsigned bx, unsigned by, unsigned smem, void** args,
+                   const char* what) {
+  static const bool pdl = [] {
+    const char* e = getenv("B200_PDL");
+    return !(e && e[0] == '0');
+  }();
+  CUlaunchConfig cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDimX = grid; cfg.gridDimY = 1; cfg.gridDimZ = 1;
+  cfg.blockDimX = bx; cfg.blockDimY = by; cfg.blockDimZ = 1;
+  cfg.sharedMemBytes = smem;
+  cfg.hStream = dev->stream;
+  CUlaunchAttribute attr;
+  memset(&attr, 0, sizeof attr);
+  attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+  attr.value.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  cu_check(cu().cuLaunchKernelEx_(&cfg, fn, args, nullptr), what);
+}
+
 void b200_routine::enqueue_stages() {
   const Program& P = code->code.prog;
   for (auto& z : scratch_zero)
@@ -183,9 +208,7 @@ void b200_routine::enqueue_stages() {
     if (blocks < 1) blocks = 1;
     if (st.block_y > 1) blocks = std::min<long long>(cap, (st.total + st.block - 1) / st.block);
     if (st.grid_override > 0) blocks = st.grid_override;
-    cu_check(cu().cuLaunchKernel_(fns[i], (unsigned)blocks, 1, 1, (unsigned)st.block, (unsigned)st.block_y, 1, 0, dev->stream, args.data(),
-                                  nullptr),
-             "cuLaunchKernel");
+    launch_kernel(dev, fns[i], (unsigned)blocks, (unsigned)st.block, (unsigned)st.block_y, 0, args.data(), "cuLaunchKernelEx");
     dev->n_launches++;
   }
 }

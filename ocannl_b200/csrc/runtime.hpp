@@ -83,3 +83,8 @@ struct b200_routine {
 GemmLaunch* gemm_prepare(b200_routine* r, int stage_index);
 void gemm_enqueue(b200_routine* r, int stage_index);
 void gemm_release(GemmLaunch* g);
+
+// One kernel launch on the device's stream, marked for programmatic stream serialisation
+// (runtime.cpp).
+void launch_kernel(b200_dev* dev, CUfunction fn, unsigned grid, unsigned bx, unsigned by, unsigned smem, void** args,
+                   const char* what);
