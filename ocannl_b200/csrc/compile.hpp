@@ -57,6 +57,8 @@ struct Stage {
   std::string gemm_source;       // full translation unit of this stage's contraction kernel
   std::string epi_params, epi_args;  // epilogue plumbing: extra kernel parameters / call arguments
   int tile_m = 0, tile_n = 0, tile_k = 0;
+  int cta_pair = 0;              // 1: two CTAs of a cluster share one tile_m x tile_n tile (cta_group::2)
+  int box_m = 0, box_n = 0;      // rows of A / B one CTA stages per k block (the TMA boxes)
   int smem_bytes = 0;            // dynamic shared memory of the contraction kernel
   int epi_out_bytes = 4;         // widest element the epilogue stores through the staging tile (2 or 4)
   int epi_tiles = 0;             // register tiles (inputs + outputs) the epilogue keeps per chunk

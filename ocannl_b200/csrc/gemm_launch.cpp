@@ -82,8 +82,8 @@ GemmLaunch* gemm_prepare(b200_routine* r, int si) {
   try {
     std::vector<int64_t> sa, sb;
     for (auto& d : g.batch) { sa.push_back(d.sa); sb.push_back(d.sb); }
-    encode_operand(&L->map_a, a, g.in_prec, g.a_kmajor, g.m, g.m.sa, g.k, g.k.sa, g.batch, sa, st.tile_m, st.tile_k);
-    encode_operand(&L->map_b, b, g.in_prec, g.b_kmajor, g.n, g.n.sb, g.k, g.k.sb, g.batch, sb, st.tile_n, st.tile_k);
+    encode_operand(&L->map_a, a, g.in_prec, g.a_kmajor, g.m, g.m.sa, g.k, g.k.sa, g.batch, sa, st.box_m, st.tile_k);
+    encode_operand(&L->map_b, b, g.in_prec, g.b_kmajor, g.n, g.n.sb, g.k, g.k.sb, g.batch, sb, st.box_n, st.tile_k);
   } catch (...) {
     delete L;
     throw;
@@ -108,10 +108,29 @@ GemmLaunch* gemm_prepare(b200_routine* r, int si) {
   s.tiles_m = (s.M + st.tile_m - 1) / st.tile_m;
   s.tiles_n = (s.N + st.tile_n - 1) / st.tile_n;
   unsigned long long tiles = (unsigned long long)s.tiles_m * s.tiles_n * s.B0 * s.B1;
-  L->grid = (unsigned)(tiles < (unsigned long long)r->dev->sm_count ? tiles : (unsigned long long)r->dev->sm_count);
-  L->status = r->dev->status_dev;
   cu_check(cu().cuFuncSetAttribute_(r->fns[si], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, st.smem_bytes),
            "cuFuncSetAttribute(max dynamic shared memory)");
+  if (st.cta_pair) {
+    // persistent pairs: as many 2-CTA clusters as the device keeps resident at once
+    int clusters = r->dev->sm_count / 2;
+    CUlaunchConfig cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDimX = (unsigned)(r->dev->sm_count / 2 * 2); cfg.gridDimY = 1; cfg.gridDimZ = 1;
+    cfg.blockDimX = (unsigned)st.block; cfg.blockDimY = 1; cfg.blockDimZ = 1;
+    cfg.sharedMemBytes = (unsigned)st.smem_bytes;
+    CUlaunchAttribute attr;
+    memset(&attr, 0, sizeof attr);
+    attr.id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+    attr.value.clusterDim.x = 2; attr.value.clusterDim.y = 1; attr.value.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int active = 0;
+    if (cu().cuOccupancyMaxActiveClusters_(&active, r->fns[si], &cfg) == CUDA_SUCCESS && active > 0 && active < clusters) clusters = active;
+    L->grid = 2u * (unsigned)(tiles < (unsigned long long)clusters ? tiles : (unsigned long long)clusters);
+  } else {
+    L->grid = (unsigned)(tiles < (unsigned long long)r->dev->sm_count ? tiles : (unsigned long long)r->dev->sm_count);
+  }
+  L->status = r->dev->status_dev;
   return L;
 }
 
@@ -125,7 +144,8 @@ void gemm_enqueue(b200_routine* r, int si) {
   args.push_back(&L->status);
   std::vector<CUdeviceptr>& vals = r->arg_values[si];
   for (size_t a = 0; a < vals.size(); ++a) args.push_back(&vals[a]);
-  launch_kernel(r->dev, r->fns[si], L->grid, (unsigned)st.block, 1, (unsigned)st.smem_bytes, args.data(), "cuLaunchKernelEx(contraction)");
+  launch_kernel(r->dev, r->fns[si], L->grid, (unsigned)st.block, 1, (unsigned)st.smem_bytes, args.data(), "cuLaunchKernelEx(contraction)",
+                st.cta_pair ? 2u : 1u);
 }
 
 void gemm_release(GemmLaunch* g) { delete g; }

@@ -796,9 +796,13 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
     const int want = atoi(ov);
     if (want >= 16 && want <= 256 && want % 16 == 0 && want <= bn && (g.b_kmajor || want % row_elems == 0)) bn = want;
   }
-  const int bm = 128, bk = row_elems;
+  // Two CTAs per 256 x bn tile when the problem has at least one full pair tile of rows: each CTA
+  // then stages half of B, and the tensor cores of both SMs work from one instruction stream.
+  bool pair = g.m.extent >= 256 && bn >= 64 && bn % 32 == 0 && (g.b_kmajor || (bn / 2) % row_elems == 0);
+  if (const char* ov = getenv("B200_GEMM_PAIR")) pair = pair && ov[0] != '0';
+  const int bm = pair ? 256 : 128, bk = row_elems;
   const int umma_k = 32 / eb;
-  const int stage_bytes = (bm + bn) * bk * eb;
+  const int stage_bytes = (128 + (pair ? bn / 2 : bn)) * bk * eb;   // per CTA
   // Epilogue width: the epilogue is a chain of dependent instructions per warp, so it is bound
   // by latency, not issue rate; light epilogues (few register tiles) get 16 warps, which fits
   // the register file at <= 112 registers per thread.
@@ -830,7 +834,8 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
     << "\n#define B200_BK " << bk << "\n#define B200_UMMA_K " << umma_k << "\n#define B200_ELEM_BYTES " << eb
     << "\n#define B200_STAGES " << stages << "\n#define B200_EPI_WARPS " << epi_warps << "\n#define B200_A_KMAJOR "
     << (g.a_kmajor ? 1 : 0) << "\n#define B200_B_KMAJOR " << (g.b_kmajor ? 1 : 0) << "\n#define B200_IDESC " << idesc
-    << "u\n#define B200_TMEM_COLS " << tmem_cols << "\n#define B200_RASTER 8\n";
+    << "u\n#define B200_TMEM_COLS " << tmem_cols << "\n#define B200_RASTER " << (pair ? 4 : 8) << "\n#define B200_CTA_PAIR "
+    << (pair ? 1 : 0) << "\n";
   // columns per epilogue step: 32 when the epilogue keeps few register tiles, else 16 so that
   // the tiles and the double-buffered accumulator chunk stay in registers
   o << "#define B200_EPI_CHUNK " << chunk << "\n#define B200_STAGING_BYTES " << staging << "\n";
@@ -841,14 +846,17 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   o << "#define B200_EPILOGUE_ROW b200_epilogue_row(b200_r, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_n0, shape.N, b200_stage, b200_has_next, b200_next_taddr, b200_tiles" << args << ");\n";
   o << kGemmSource << "\n";
   std::ostringstream note;
-  note << "tcgen05 " << bm << "x" << bn << "x" << bk << " stages=" << stages << " epi_warps=" << epi_warps
-       << (g.accumulate ? " beta=1" : "");
+  note << "tcgen05 " << bm << "x" << bn << "x" << bk << (pair ? " (CTA pair, cta_group::2)" : "") << " stages=" << stages
+       << " epi_warps=" << epi_warps << (g.accumulate ? " beta=1" : "");
   st.note = note.str();
   // remembered for the launcher
   st.block = 64 + 32 * epi_warps;
   st.tile_m = bm;
   st.tile_n = bn;
   st.tile_k = bk;
+  st.cta_pair = pair ? 1 : 0;
+  st.box_m = 128;
+  st.box_n = pair ? bn / 2 : bn;
   st.smem_bytes = stages * stage_bytes + 1024 + 256 + epi_warps * staging;
   return o.str();
 }

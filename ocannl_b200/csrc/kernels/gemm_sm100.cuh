@@ -92,10 +92,57 @@ __device__ __forceinline__ bool b200_wait(unsigned int bar, unsigned int parity,
   }
 }
 
+// B200_CTA_PAIR: two CTAs of a cluster (one TPC) work on one 256 x BN tile.  Each stages its own
+// 128 rows of A and half of the BN columns of B; the even CTA (the leader) issues the
+// cta_group::2 MMAs, which read both CTAs' shared memory and write each CTA's 128 accumulator rows
+// into that CTA's tensor memory.  Per CTA the operand traffic into shared memory drops by a third.
+#ifndef B200_CTA_PAIR
+#define B200_CTA_PAIR 0
+#endif
+#if B200_CTA_PAIR
+#define B200_CG "cta_group::2"
+#else
+#define B200_CG "cta_group::1"
+#endif
+
+__device__ __forceinline__ unsigned int b200_cta_rank() {
+#if B200_CTA_PAIR
+  unsigned int r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+#else
+  return 0u;
+#endif
+}
+// the shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ unsigned int b200_map_to_cta(unsigned int addr, unsigned int rank) {
+#if B200_CTA_PAIR
+  unsigned int r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+#else
+  return addr;
+#endif
+}
+__device__ __forceinline__ void b200_mbar_arrive_cluster(unsigned int cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void b200_cluster_sync() {
+#if B200_CTA_PAIR
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+#endif
+}
+
 __device__ __forceinline__ void b200_tma_load_4d(unsigned int dst, const b200_tmap* map, unsigned int bar, int c0, int c1,
                                                  int c2, int c3) {
   asm volatile(
+#if B200_CTA_PAIR
+      // the completion may be signalled on the peer CTA's barrier (no multicast: each CTA loads its own data)
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+#else
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+#endif
       :
       : "r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
@@ -122,17 +169,25 @@ __device__ __forceinline__ void b200_umma(unsigned int tmem_d, unsigned long lon
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
 #if B200_ELEM_BYTES == 4
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+      "tcgen05.mma." B200_CG ".kind::tf32 [%0], %1, %2, %3, p;\n\t"
 #else
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "tcgen05.mma." B200_CG ".kind::f16 [%0], %1, %2, %3, p;\n\t"
 #endif
       "}"
       :
       : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Arrives on `bar` once the MMAs issued so far have retired; in pair mode on the barrier at the
+// same offset in both CTAs.
 __device__ __forceinline__ void b200_umma_commit(unsigned int bar) {
+#if B200_CTA_PAIR
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"((unsigned short)3)
+               : "memory");
+#else
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+#endif
 }
 __device__ __forceinline__ void b200_tmem_ld32(unsigned int taddr, unsigned int* r) {
   asm volatile(
@@ -180,8 +235,11 @@ __device__ __forceinline__ void b200_tmem_ld_chunk(unsigned int taddr, unsigned 
 #define B200_TR(slot) do { } while (0)
 #endif
 
-#define B200_A_TILE_BYTES (B200_BM * B200_BK * B200_ELEM_BYTES)
-#define B200_B_TILE_BYTES (B200_BN * B200_BK * B200_ELEM_BYTES)
+// per CTA: 128 rows of A; all of the tile's B columns, or half of them in pair mode
+#define B200_CTA_M 128
+#define B200_CTA_N (B200_BN / (1 + B200_CTA_PAIR))
+#define B200_A_TILE_BYTES (B200_CTA_M * B200_BK * B200_ELEM_BYTES)
+#define B200_B_TILE_BYTES (B200_CTA_N * B200_BK * B200_ELEM_BYTES)
 #define B200_STAGE_BYTES (B200_A_TILE_BYTES + B200_B_TILE_BYTES)
 #define B200_THREADS (64 + 32 * B200_EPI_WARPS)
 // elements of the contiguous axis covered by one 128-byte swizzle row
@@ -235,23 +293,28 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
     }
     for (unsigned int a = 0; a < 2; ++a) {
       b200_mbar_init(bar_acc_full + 8u * a, 1);
-      b200_mbar_init(bar_acc_empty + 8u * a, B200_EPI_WARPS);
+      // the leader's accumulator buffer is free again when the epilogue warps of both CTAs are done with it
+      b200_mbar_init(bar_acc_empty + 8u * a, B200_EPI_WARPS * (1 + B200_CTA_PAIR));
     }
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(b200_smem_addr((const void*)tmem_slot)),
+    asm volatile("tcgen05.alloc." B200_CG ".sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(b200_smem_addr((const void*)tmem_slot)),
                  "r"((unsigned int)B200_TMEM_COLS)
                  : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit." B200_CG ".sync.aligned;" ::: "memory");
   }
   // set-up above touched no global memory; from here on the grids before this one must be complete
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  b200_cluster_sync();   // the peer's barriers are initialised before anything is signalled on them
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned int tmem_base = *tmem_slot;
+  const unsigned int cta_rank = b200_cta_rank();
+  // tiles are taken by CTA pairs in pair mode, by single CTAs otherwise
+  const unsigned int worker = blockIdx.x / (1 + B200_CTA_PAIR), n_workers = gridDim.x / (1 + B200_CTA_PAIR);
   if (threadIdx.x == 0) B200_TR(2);   // set-up done
 
   const unsigned int tiles_per_batch = shape.tiles_m * shape.tiles_n;
@@ -263,7 +326,7 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
     if (lane == 0) {
       unsigned int slot = 0, phase = 0;
       bool live = true;
-      for (unsigned int tile = blockIdx.x; live && tile < total_tiles; tile += gridDim.x) {
+      for (unsigned int tile = worker; live && tile < total_tiles; tile += n_workers) {
         const unsigned int bidx = tile / tiles_per_batch;
         const unsigned int t = tile - bidx * tiles_per_batch;
         // consecutive tiles walk down m first so that a wave of CTAs shares few B tiles
@@ -274,11 +337,13 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
         const unsigned int mt = first_m + r % rows;
         const unsigned int nt = r / rows;
         const unsigned int b0 = bidx / shape.B1, b1 = bidx - b0 * shape.B1;
-        const int m0 = (int)(mt * B200_BM), n0 = (int)(nt * B200_BN);
+        // this CTA's rows of A and its share of the tile's B columns
+        const int m0 = (int)(mt * B200_BM + cta_rank * B200_CTA_M), n0 = (int)(nt * B200_BN + cta_rank * B200_CTA_N);
         for (unsigned int kb = 0; kb < k_blocks; ++kb) {
           if (!b200_wait(bar_empty + 8u * slot, phase ^ 1u, abort_flag, status, 1u)) { live = false; break; }
-          const unsigned int full = bar_full + 8u * slot;
-          b200_mbar_expect_tx(full, B200_STAGE_BYTES);
+          // both CTAs' copies complete on the leader's barrier; the leader announces the bytes of both
+          const unsigned int full = b200_map_to_cta(bar_full + 8u * slot, 0u);   // (the barrier itself when not paired)
+          if (cta_rank == 0u) b200_mbar_expect_tx(bar_full + 8u * slot, B200_STAGE_BYTES * (1 + B200_CTA_PAIR));
           const unsigned int sa = tiles_at + slot * B200_STAGE_BYTES;
           const unsigned int sb = sa + B200_A_TILE_BYTES;
           const int k0 = (int)(kb * B200_BK);
@@ -286,7 +351,7 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
           b200_tma_load_4d(sa, &map_a, full, k0, m0, (int)(b1 * shape.a_b1), (int)(b0 * shape.a_b0));
 #else
 #pragma unroll
-          for (int c = 0; c < B200_BM / B200_ROW_ELEMS; ++c)
+          for (int c = 0; c < B200_CTA_M / B200_ROW_ELEMS; ++c)
             b200_tma_load_4d(sa + c * (B200_ROW_ELEMS * B200_BK * B200_ELEM_BYTES), &map_a, full, m0 + c * B200_ROW_ELEMS, k0,
                              (int)(b1 * shape.a_b1), (int)(b0 * shape.a_b0));
 #endif
@@ -294,29 +359,29 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
           b200_tma_load_4d(sb, &map_b, full, k0, n0, (int)(b1 * shape.b_b1), (int)(b0 * shape.b_b0));
 #else
 #pragma unroll
-          for (int c = 0; c < B200_BN / B200_ROW_ELEMS; ++c)
+          for (int c = 0; c < B200_CTA_N / B200_ROW_ELEMS; ++c)
             b200_tma_load_4d(sb + c * (B200_ROW_ELEMS * B200_BK * B200_ELEM_BYTES), &map_b, full, n0 + c * B200_ROW_ELEMS, k0,
                              (int)(b1 * shape.b_b1), (int)(b0 * shape.b_b0));
 #endif
-          if (tile == blockIdx.x && kb == 0) B200_TR(3);   // first loads issued
+          if (tile == worker && kb == 0) B200_TR(3);   // first loads issued
           if (++slot == B200_STAGES) { slot = 0; phase ^= 1u; }
         }
       }
       B200_TR(4);   // producer done
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer (the leader CTA of a pair)
+    if (lane == 0 && cta_rank == 0u) {
       unsigned int slot = 0, phase = 0, acc = 0, acc_phase = 0;
       bool live = true;
-      for (unsigned int tile = blockIdx.x; live && tile < total_tiles; tile += gridDim.x) {
+      for (unsigned int tile = worker; live && tile < total_tiles; tile += n_workers) {
         if (!b200_wait(bar_acc_empty + 8u * acc, acc_phase ^ 1u, abort_flag, status, 2u)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned int d_tmem = tmem_base + acc * B200_BN;
         for (unsigned int kb = 0; kb < k_blocks; ++kb) {
           if (!b200_wait(bar_full + 8u * slot, phase, abort_flag, status, 3u)) { live = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          if (tile == blockIdx.x && kb == 0) B200_TR(5);   // first operands landed
+          if (tile == worker && kb == 0) B200_TR(5);   // first operands landed
           const unsigned int sa = tiles_at + slot * B200_STAGE_BYTES;
           const unsigned int sb = sa + B200_A_TILE_BYTES;
 #pragma unroll
@@ -343,8 +408,8 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
           if (++slot == B200_STAGES) { slot = 0; phase ^= 1u; }
         }
         if (live) b200_umma_commit(bar_acc_full + 8u * acc);
-        if (tile == blockIdx.x) B200_TR(6);                  // tile 0 MMAs issued
-        else if (tile == blockIdx.x + gridDim.x) B200_TR(7); // tile 1 MMAs issued
+        if (tile == worker) B200_TR(6);                  // tile 0 MMAs issued
+        else if (tile == worker + n_workers) B200_TR(7); // tile 1 MMAs issued
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
     }
@@ -357,7 +422,7 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
     // this warp's 4 KB staging tile (transposes a chunk so that stores cover whole row segments)
     uint4* b200_stage = (uint4*)(smem_gen + B200_STAGES * B200_STAGE_BYTES + 256 + ew * (unsigned int)B200_STAGING_BYTES);
     unsigned int acc = 0, acc_phase = 0;
-    for (unsigned int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    for (unsigned int tile = worker; tile < total_tiles; tile += n_workers) {
       const unsigned int bidx = tile / tiles_per_batch;
       const unsigned int t = tile - bidx * tiles_per_batch;
       const unsigned int group = t / (B200_RASTER * shape.tiles_n);
@@ -367,7 +432,7 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
       const unsigned int mt = first_m + r % rows;
       const unsigned int nt = r / rows;
       const unsigned int b200_b0 = bidx / shape.B1, b200_b1 = bidx - b200_b0 * shape.B1;
-      const unsigned int b200_m = mt * B200_BM + quarter * 32u + lane;
+      const unsigned int b200_m = mt * B200_BM + cta_rank * B200_CTA_M + quarter * 32u + lane;
       // while the tensor cores are still busy with this tile, load the epilogue's operands (bias,
       // mask, residual rows ...) of the first chunk this warp owns
       b200_in_tiles b200_tiles;
@@ -378,7 +443,7 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
       }
       if (!b200_wait(bar_acc_full + 8u * acc, acc_phase, abort_flag, status, 4u)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (warp == 2 && lane == 0) { if (tile == blockIdx.x) B200_TR(8); else if (tile == blockIdx.x + gridDim.x) B200_TR(10); }
+      if (warp == 2 && lane == 0) { if (tile == worker) B200_TR(8); else if (tile == worker + n_workers) B200_TR(10); }
 #ifdef B200_TRACE
       B200_TRE(3);   // waiting for the accumulator (and the operand prefetch before it)
 #endif
@@ -407,8 +472,12 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
+#if B200_CTA_PAIR
+      if (lane == 0) b200_mbar_arrive_cluster(b200_map_to_cta(bar_acc_empty + 8u * acc, 0u));
+#else
       if (lane == 0) b200_mbar_arrive(bar_acc_empty + 8u * acc);
-      if (warp == 2 && lane == 0) { if (tile == blockIdx.x) B200_TR(9); else if (tile == blockIdx.x + gridDim.x) B200_TR(11); }
+#endif
+      if (warp == 2 && lane == 0) { if (tile == worker) B200_TR(9); else if (tile == worker + n_workers) B200_TR(11); }
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
 #ifdef B200_TRACE
       B200_TRE(5);   // release of the accumulator buffer
@@ -428,10 +497,11 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  b200_cluster_sync();   // neither CTA of a pair leaves while the other may still read its memory or signal its barriers
   if (threadIdx.x == 0) B200_TR(12);  // all roles done
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned int)B200_TMEM_COLS)
+    asm volatile("tcgen05.dealloc." B200_CG ".sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned int)B200_TMEM_COLS)
                  : "memory");
   }
 }

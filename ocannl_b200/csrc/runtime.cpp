@@ -141,7 +141,7 @@ void b200_routine::link(b200_dev* d, b200_code* c, const b200_binding* b, int n)
 // marked for programmatic stream serialisation: the next kernel's blocks are placed, and run their
 // set-up, while the tail of the previous kernel drains.  B200_PDL=0 turns the marking off.
 void launch_kernel(b200_dev* dev, CUfunction fn, unsigned grid, unsigned bx, unsigned by, unsigned smem, void** args,
-                   const char* what) {
+                   const char* what, unsigned cluster) {
   static const bool pdl = [] {
     const char* e = getenv("B200_PDL");
     return !(e && e[0] == '0');
@@ -152,12 +152,21 @@ void launch_kernel(b200_dev* dev, CUfunction fn, unsigned grid, unsigned bx, uns
   cfg.blockDimX = bx; cfg.blockDimY = by; cfg.blockDimZ = 1;
   cfg.sharedMemBytes = smem;
   cfg.hStream = dev->stream;
-  CUlaunchAttribute attr;
-  memset(&attr, 0, sizeof attr);
-  attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
-  attr.value.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  CUlaunchAttribute attr[2];
+  memset(attr, 0, sizeof attr);
+  unsigned n = 0;
+  if (cluster > 1) {
+    attr[n].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+    attr[n].value.clusterDim.x = cluster; attr[n].value.clusterDim.y = 1; attr[n].value.clusterDim.z = 1;
+    ++n;
+  }
+  if (pdl) {
+    attr[n].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+    attr[n].value.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
   cu_check(cu().cuLaunchKernelEx_(&cfg, fn, args, nullptr), what);
 }
 

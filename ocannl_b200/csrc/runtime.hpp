@@ -87,4 +87,4 @@ void gemm_release(GemmLaunch* g);
 // One kernel launch on the device's stream, marked for programmatic stream serialisation
 // (runtime.cpp).
 void launch_kernel(b200_dev* dev, CUfunction fn, unsigned grid, unsigned bx, unsigned by, unsigned smem, void** args,
-                   const char* what);
+                   const char* what, unsigned cluster = 1);
