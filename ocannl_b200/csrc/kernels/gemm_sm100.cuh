@@ -374,6 +374,19 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
     if (lane == 0 && cta_rank == 0u) {
       unsigned int slot = 0, phase = 0, acc = 0, acc_phase = 0;
       bool live = true;
+      // operand descriptors of ring slot 0.  k-major: rows of 128 bytes, 8-row groups 1024 bytes
+      // apart.  m/n-major: 64-element (128-byte) chunks of m/n, k rows 128 bytes apart, 8-row groups
+      // 1024 bytes apart, chunks one box apart.
+#if B200_A_KMAJOR
+      const unsigned long long desc_a0 = b200_smem_desc(tiles_at, 16u, 1024u);
+#else
+      const unsigned long long desc_a0 = b200_smem_desc(tiles_at, B200_ROW_ELEMS * B200_BK * B200_ELEM_BYTES, 1024u);
+#endif
+#if B200_B_KMAJOR
+      const unsigned long long desc_b0 = b200_smem_desc(tiles_at + B200_A_TILE_BYTES, 16u, 1024u);
+#else
+      const unsigned long long desc_b0 = b200_smem_desc(tiles_at + B200_A_TILE_BYTES, B200_ROW_ELEMS * B200_BK * B200_ELEM_BYTES, 1024u);
+#endif
       for (unsigned int tile = worker; live && tile < total_tiles; tile += n_workers) {
         if (!b200_wait(bar_acc_empty + 8u * acc, acc_phase ^ 1u, abort_flag, status, 2u)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -382,26 +395,14 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
           if (!b200_wait(bar_full + 8u * slot, phase, abort_flag, status, 3u)) { live = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           if (tile == worker && kb == 0) B200_TR(5);   // first operands landed
-          const unsigned int sa = tiles_at + slot * B200_STAGE_BYTES;
-          const unsigned int sb = sa + B200_A_TILE_BYTES;
+          // descriptors of this slot: the start-address field (bits 0-13, address >> 4) moves, the rest is fixed
+          const unsigned long long da0 = desc_a0 + (unsigned long long)((slot * B200_STAGE_BYTES) >> 4);
+          const unsigned long long db0 = desc_b0 + (unsigned long long)((slot * B200_STAGE_BYTES) >> 4);
 #pragma unroll
           for (unsigned int ks = 0; ks < B200_BK / B200_UMMA_K; ++ks) {
-#if B200_A_KMAJOR
-            // k-major: rows of 128 bytes, 8-row groups 1024 bytes apart; a k step moves
-            // UMMA_K elements along the row
-            const unsigned long long da = b200_smem_desc(sa + ks * (B200_UMMA_K * B200_ELEM_BYTES), 16u, 1024u);
-#else
-            // m-major: 64-element (128-byte) chunks of m, k rows 128 bytes apart, 8-row
-            // groups 1024 bytes apart, chunks of m one box apart; a k step moves UMMA_K rows
-            const unsigned long long da =
-                b200_smem_desc(sa + ks * (B200_UMMA_K * 128u), B200_ROW_ELEMS * B200_BK * B200_ELEM_BYTES, 1024u);
-#endif
-#if B200_B_KMAJOR
-            const unsigned long long db = b200_smem_desc(sb + ks * (B200_UMMA_K * B200_ELEM_BYTES), 16u, 1024u);
-#else
-            const unsigned long long db =
-                b200_smem_desc(sb + ks * (B200_UMMA_K * 128u), B200_ROW_ELEMS * B200_BK * B200_ELEM_BYTES, 1024u);
-#endif
+            // a k step moves UMMA_K elements along a k-major row, or UMMA_K rows of 128 bytes in the m/n-major form
+            const unsigned long long da = da0 + (unsigned long long)((ks * (B200_A_KMAJOR ? B200_UMMA_K * B200_ELEM_BYTES : B200_UMMA_K * 128u)) >> 4);
+            const unsigned long long db = db0 + (unsigned long long)((ks * (B200_B_KMAJOR ? B200_UMMA_K * B200_ELEM_BYTES : B200_UMMA_K * 128u)) >> 4);
             b200_umma(d_tmem, da, db, (unsigned int)B200_IDESC, (kb | ks) != 0u ? 1u : 0u);
           }
           b200_umma_commit(bar_empty + 8u * slot);  // frees the slot once these MMAs retire
