@@ -138,7 +138,7 @@ __device__ __forceinline__ void b200_tma_load_4d(unsigned int dst, const b200_tm
                                                  int c2, int c3) {
   asm volatile(
 #if B200_CTA_PAIR
-      // the completion may be signalled on the peer CTA's barrier (no multicast: each CTA loads its own data)
+      // the completion may be signalled on the peer CTA's barrier; each CTA loads only its own data
       "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
 #else
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
