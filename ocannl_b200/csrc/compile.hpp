@@ -38,6 +38,7 @@ struct GemmPlan {
   bool a_kmajor = true, b_kmajor = true;
   bool accumulate = false;           // beta = 1: add to the existing output (form B without zero_out)
   Prec in_prec = Prec::Bfloat16;     // operand precision (bf16 / half; single runs as tf32)
+  int split_k = 1;                   // >1: that many work units per tile, each over a slice of K, added with vector reds
   std::string epilogue;              // generated device code, see codegen
   double flops() const;
 };
@@ -84,6 +85,7 @@ struct CompileOptions {
   bool enable_gemm = true;
   bool enable_coop = true;
   bool enable_fuse = true;   // several small stages in one single-block kernel
+  bool enable_splitk = true; // few-tile accumulations split K over the idle SMs (fp32 atomic adds: order not fixed)
   bool enable_pairs = true;  // contraction epilogues over pairs of columns with packed 16-bit arithmetic
   bool large_models = false;
 };

@@ -107,7 +107,7 @@ GemmLaunch* gemm_prepare(b200_routine* r, int si) {
   }
   s.tiles_m = (s.M + st.tile_m - 1) / st.tile_m;
   s.tiles_n = (s.N + st.tile_n - 1) / st.tile_n;
-  unsigned long long tiles = (unsigned long long)s.tiles_m * s.tiles_n * s.B0 * s.B1;
+  unsigned long long tiles = (unsigned long long)s.tiles_m * s.tiles_n * s.B0 * s.B1 * (unsigned long long)(g.split_k > 0 ? g.split_k : 1);
   cu_check(cu().cuFuncSetAttribute_(r->fns[si], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, st.smem_bytes),
            "cuFuncSetAttribute(max dynamic shared memory)");
   if (st.cta_pair) {

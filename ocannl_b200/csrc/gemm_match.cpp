@@ -84,6 +84,7 @@ bool mac_step(const Scalar& v, const std::function<bool(const Scalar&)>& is_acc,
 static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, const Stmt& set, bool zeroed_before,
                             const CompileOptions& opt, const std::vector<Follower>& followers, int* n_fused, Stage* out,
                             bool pair);
+static int gemm_split_k(const GemmPlan& g);
 
 // The epilogue is first tried over pairs of columns (packed 16-bit arithmetic); anything that form
 // cannot express falls back to one column at a time.
@@ -470,10 +471,13 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   }
   std::string body;
   add_out(set.tn, set.idcs);
+  if (form_b && opt.enable_splitk && outs[0].unit_n) g.split_k = gemm_split_k(g);
+  const bool reds = g.split_k > 1;   // partial tiles are added to the output instead of stored
   if (form_b) {
     const Tnode& t = D;
     std::string off = em.offset(set.idcs, t.dims);
-    if (g.accumulate) body = "      " + outs[0].arr + "[b200_j] = " + t.ident + "[" + off + "] + b200_acc;\n";
+    if (reds) body = "      " + outs[0].arr + "[b200_j] = b200_acc;\n";
+    else if (g.accumulate) body = "      " + outs[0].arr + "[b200_j] = " + t.ident + "[" + off + "] + b200_acc;\n";
     else body = "      " + outs[0].arr + "[b200_j] = b200_acc;\n";
   } else {
     em.scope_subst[scope->scope_id] = "b200_acc";
@@ -487,6 +491,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   std::string aliases;
   std::set<int> produced = {set.tn};
   for (const Follower& fo : followers) {
+    if (reds) break;   // partial tiles cannot feed a follow-up assignment
     if (fo.nest.size() != free_loops.size() || fo.set->kind != Stmt::Set || fo.set->vec_len > 0) break;
     bool ok = true;
     std::map<std::string, std::string> ren;  // follower symbol -> this stage's symbol
@@ -653,6 +658,9 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   // 128-byte line of banks; the group index is xor-ed with a key that changes every 8 / G rows,
   // which makes the 8 lanes of a quarter warp (one row group each when writing, 8 / G rows of G
   // groups when reading) hit 8 different bank groups.
+  fn << "__device__ __forceinline__ void b200_red_add_v4(unsigned long long addr, uint4 q) {\n"
+        "  asm volatile(\"red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\" ::\"l\"(addr), \"f\"(__uint_as_float(q.x)), \"f\"(__uint_as_float(q.y)),\n"
+        "               \"f\"(__uint_as_float(q.z)), \"f\"(__uint_as_float(q.w)) : \"memory\");\n}\n";
   fn << "#define B200_STAGE_KEY(row, G) ((G) >= 8 ? ((row) & 7u) : (((row) / (8u / ((G) >= 8 ? 8u : (G)))) % (G)))\n";
   // developer trace: the first epilogue thread of CTA 0 adds up the clock cycles it spends in
   // each phase of the epilogue (slot = phase that just ended)
@@ -746,19 +754,24 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
            << "        const unsigned int r = it * (32 / G) + b200_lane / G, c = b200_lane % G;\n"
            << "        const unsigned long long dst = b200_t.r" << o.tn << "[it];\n"
            << "        const uint4 q = b200_stage[r * G + (c ^ B200_STAGE_KEY(r, G))];\n"
-           << "        if (dst) *(uint4*)(dst + (unsigned long long)b200_n0 * " << ebytes << "ull + 16ull * c) = q;\n      }\n"
+           << (reds ? "        if (dst) b200_red_add_v4(dst + (unsigned long long)b200_n0 * "
+                    : "        if (dst) *(uint4*)(dst + (unsigned long long)b200_n0 * ")
+           << ebytes << (reds ? "ull + 16ull * c, q);\n      }\n" : "ull + 16ull * c) = q;\n      }\n")
            << "      __syncwarp();\n"
            << "    } else if (b200_row_ok) {\n";
       } else {
         fn << "    if (b200_row_ok) {\n";
       }
-      fn << "#pragma unroll\n      for (int b200_j = 0; b200_j < B200_EPI_CHUNK; ++b200_j)\n"
-         << "        if (b200_n0 + (unsigned int)b200_j < b200_N) b200_p[b200_j] = "
-         << (!pair ? Emitter::store_wrap(t.prec, o.arr + "[b200_j]")
-                   : ebytes == 4 ? "((b200_j & 1) ? " + o.arr + "[b200_j >> 1].y : " + o.arr + "[b200_j >> 1].x)"
-                                 : "(unsigned short)(" + o.arr + "[b200_j >> 1] >> (16 * (b200_j & 1)))")
-         << ";\n"
-         << "    }\n  }\n";
+      fn << "#pragma unroll\n      for (int b200_j = 0; b200_j < B200_EPI_CHUNK; ++b200_j)\n";
+      if (reds)
+        fn << "        if (b200_n0 + (unsigned int)b200_j < b200_N) atomicAdd(&b200_p[b200_j], " << o.arr << "[b200_j]);\n";
+      else
+        fn << "        if (b200_n0 + (unsigned int)b200_j < b200_N) b200_p[b200_j] = "
+           << (!pair ? Emitter::store_wrap(t.prec, o.arr + "[b200_j]")
+                     : ebytes == 4 ? "((b200_j & 1) ? " + o.arr + "[b200_j >> 1].y : " + o.arr + "[b200_j >> 1].x)"
+                                   : "(unsigned short)(" + o.arr + "[b200_j >> 1] >> (16 * (b200_j & 1)))")
+           << ";\n";
+      fn << "    }\n  }\n";
     } else {
       // general position: recompute the offset per column
       fn << "#pragma unroll\n  for (int b200_j = 0; b200_j < B200_EPI_CHUNK; ++b200_j) {\n"
@@ -783,8 +796,8 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   return true;
 }
 
-std::string gemm_translation_unit(const Program& P, Stage& st, const std::string& kernel_name, const CompileOptions&) {
-  GemmPlan& g = st.gemm;
+// Tile shape of a contraction: columns per tile, and whether two CTAs share a 256-row tile.
+static void gemm_tile_shape(const GemmPlan& g, int* bn_out, bool* pair_out) {
   const int eb = prec_bytes(g.in_prec);
   const int row_elems = 128 / eb;
   int bn;
@@ -800,6 +813,36 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   // then stages half of B, and the tensor cores of both SMs work from one instruction stream.
   bool pair = g.m.extent >= 256 && bn >= 64 && bn % 32 == 0 && (g.b_kmajor || (bn / 2) % row_elems == 0);
   if (const char* ov = getenv("B200_GEMM_PAIR")) pair = pair && ov[0] != '0';
+  *bn_out = bn;
+  *pair_out = pair;
+}
+
+// Work units per tile.  An accumulation into an fp32 node with few output tiles and a long K (the
+// weight gradients: 1024 x 1024 outputs over 8192 rows are 16 pair tiles for 74 pairs) gives
+// every tile to several workers, each over a slice of K; their partial tiles meet in the output
+// through vector reductions in global memory.  148 SMs are assumed (the compile step knows no device).
+static int gemm_split_k(const GemmPlan& g) {
+  int bn;
+  bool pair;
+  gemm_tile_shape(g, &bn, &pair);
+  const int bm = pair ? 256 : 128;
+  long long tiles = ((g.m.extent + bm - 1) / bm) * ((g.n.extent + bn - 1) / bn);
+  for (auto& b : g.batch) tiles *= b.extent;
+  const long long workers = pair ? 74 : 148;
+  const long long k_blocks = (g.k.extent + (128 / prec_bytes(g.in_prec)) - 1) / (128 / prec_bytes(g.in_prec));
+  if (tiles * 2 > workers) return 1;
+  long long s = std::min<long long>(workers / tiles, k_blocks / 8);
+  if (const char* ov = getenv("B200_GEMM_SPLITK")) s = std::min<long long>(atoi(ov), k_blocks);
+  return (int)std::max<long long>(1, std::min<long long>(s, 32));
+}
+
+std::string gemm_translation_unit(const Program& P, Stage& st, const std::string& kernel_name, const CompileOptions&) {
+  GemmPlan& g = st.gemm;
+  const int eb = prec_bytes(g.in_prec);
+  const int row_elems = 128 / eb;
+  int bn;
+  bool pair;
+  gemm_tile_shape(g, &bn, &pair);
   const int bm = pair ? 256 : 128, bk = row_elems;
   const int umma_k = 32 / eb;
   const int stage_bytes = (128 + (pair ? bn / 2 : bn)) * bk * eb;   // per CTA
@@ -835,7 +878,7 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
     << "\n#define B200_STAGES " << stages << "\n#define B200_EPI_WARPS " << epi_warps << "\n#define B200_A_KMAJOR "
     << (g.a_kmajor ? 1 : 0) << "\n#define B200_B_KMAJOR " << (g.b_kmajor ? 1 : 0) << "\n#define B200_IDESC " << idesc
     << "u\n#define B200_TMEM_COLS " << tmem_cols << "\n#define B200_RASTER " << (pair ? 4 : 8) << "\n#define B200_CTA_PAIR "
-    << (pair ? 1 : 0) << "\n";
+    << (pair ? 1 : 0) << "\n#define B200_SPLITK " << g.split_k << "\n";
   // columns per epilogue step: 32 when the epilogue keeps few register tiles, else 16 so that
   // the tiles and the double-buffered accumulator chunk stay in registers
   o << "#define B200_EPI_CHUNK " << chunk << "\n#define B200_STAGING_BYTES " << staging << "\n";
@@ -847,7 +890,8 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   o << kGemmSource << "\n";
   std::ostringstream note;
   note << "tcgen05 " << bm << "x" << bn << "x" << bk << (pair ? " (CTA pair, cta_group::2)" : "") << " stages=" << stages
-       << " epi_warps=" << epi_warps << (g.accumulate ? " beta=1" : "");
+       << " epi_warps=" << epi_warps << (g.split_k > 1 ? " split_k=" + std::to_string(g.split_k) : std::string())
+       << (g.accumulate ? " beta=1" : "");
   st.note = note.str();
   // remembered for the launcher
   st.block = 64 + 32 * epi_warps;

@@ -254,6 +254,11 @@ __device__ __forceinline__ void b200_tmem_ld_chunk(unsigned int taddr, unsigned 
 #ifndef B200_RASTER
 #define B200_RASTER 8
 #endif
+// B200_SPLITK work units per tile, each over its own slice of the k blocks (the epilogue then adds
+// its partial tile to the output with reductions in global memory)
+#ifndef B200_SPLITK
+#define B200_SPLITK 1
+#endif
 
 extern "C" __global__ void __launch_bounds__(B200_THREADS, 1)
 B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ b200_tmap map_b,
@@ -320,13 +325,16 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
   const unsigned int tiles_per_batch = shape.tiles_m * shape.tiles_n;
   const unsigned int total_tiles = tiles_per_batch * shape.B0 * shape.B1;
   const unsigned int k_blocks = (shape.K + B200_BK - 1) / B200_BK;
+  const unsigned int total_units = total_tiles * B200_SPLITK;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       unsigned int slot = 0, phase = 0;
       bool live = true;
-      for (unsigned int tile = worker; live && tile < total_tiles; tile += n_workers) {
+      for (unsigned int unit = worker; live && unit < total_units; unit += n_workers) {
+        const unsigned int tile = unit % total_tiles, split = unit / total_tiles;
+        const unsigned int kb0 = split * k_blocks / B200_SPLITK, kb1 = (split + 1u) * k_blocks / B200_SPLITK;
         const unsigned int bidx = tile / tiles_per_batch;
         const unsigned int t = tile - bidx * tiles_per_batch;
         // consecutive tiles walk down m first so that a wave of CTAs shares few B tiles
@@ -339,7 +347,7 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
         const unsigned int b0 = bidx / shape.B1, b1 = bidx - b0 * shape.B1;
         // this CTA's rows of A and its share of the tile's B columns
         const int m0 = (int)(mt * B200_BM + cta_rank * B200_CTA_M), n0 = (int)(nt * B200_BN + cta_rank * B200_CTA_N);
-        for (unsigned int kb = 0; kb < k_blocks; ++kb) {
+        for (unsigned int kb = kb0; kb < kb1; ++kb) {
           if (!b200_wait(bar_empty + 8u * slot, phase ^ 1u, abort_flag, status, 1u)) { live = false; break; }
           // both CTAs' copies complete on the leader's barrier; the leader announces the bytes of both
           const unsigned int full = b200_map_to_cta(bar_full + 8u * slot, 0u);   // (the barrier itself when not paired)
@@ -363,7 +371,7 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
             b200_tma_load_4d(sb + c * (B200_ROW_ELEMS * B200_BK * B200_ELEM_BYTES), &map_b, full, n0 + c * B200_ROW_ELEMS, k0,
                              (int)(b1 * shape.b_b1), (int)(b0 * shape.b_b0));
 #endif
-          if (tile == worker && kb == 0) B200_TR(3);   // first loads issued
+          if (unit == worker && kb == kb0) B200_TR(3);   // first loads issued
           if (++slot == B200_STAGES) { slot = 0; phase ^= 1u; }
         }
       }
@@ -387,14 +395,16 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
 #else
       const unsigned long long desc_b0 = b200_smem_desc(tiles_at + B200_A_TILE_BYTES, B200_ROW_ELEMS * B200_BK * B200_ELEM_BYTES, 1024u);
 #endif
-      for (unsigned int tile = worker; live && tile < total_tiles; tile += n_workers) {
+      for (unsigned int unit = worker; live && unit < total_units; unit += n_workers) {
+        const unsigned int split = unit / total_tiles;
+        const unsigned int kb0 = split * k_blocks / B200_SPLITK, kb1 = (split + 1u) * k_blocks / B200_SPLITK;
         if (!b200_wait(bar_acc_empty + 8u * acc, acc_phase ^ 1u, abort_flag, status, 2u)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned int d_tmem = tmem_base + acc * B200_BN;
-        for (unsigned int kb = 0; kb < k_blocks; ++kb) {
+        for (unsigned int kb = kb0; kb < kb1; ++kb) {
           if (!b200_wait(bar_full + 8u * slot, phase, abort_flag, status, 3u)) { live = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          if (tile == worker && kb == 0) B200_TR(5);   // first operands landed
+          if (unit == worker && kb == kb0) B200_TR(5);   // first operands landed
           // descriptors of this slot: the start-address field (bits 0-13, address >> 4) moves, the rest is fixed
           const unsigned long long da0 = desc_a0 + (unsigned long long)((slot * B200_STAGE_BYTES) >> 4);
           const unsigned long long db0 = desc_b0 + (unsigned long long)((slot * B200_STAGE_BYTES) >> 4);
@@ -403,14 +413,14 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
             // a k step moves UMMA_K elements along a k-major row, or UMMA_K rows of 128 bytes in the m/n-major form
             const unsigned long long da = da0 + (unsigned long long)((ks * (B200_A_KMAJOR ? B200_UMMA_K * B200_ELEM_BYTES : B200_UMMA_K * 128u)) >> 4);
             const unsigned long long db = db0 + (unsigned long long)((ks * (B200_B_KMAJOR ? B200_UMMA_K * B200_ELEM_BYTES : B200_UMMA_K * 128u)) >> 4);
-            b200_umma(d_tmem, da, db, (unsigned int)B200_IDESC, (kb | ks) != 0u ? 1u : 0u);
+            b200_umma(d_tmem, da, db, (unsigned int)B200_IDESC, (kb != kb0 || ks != 0u) ? 1u : 0u);
           }
           b200_umma_commit(bar_empty + 8u * slot);  // frees the slot once these MMAs retire
           if (++slot == B200_STAGES) { slot = 0; phase ^= 1u; }
         }
         if (live) b200_umma_commit(bar_acc_full + 8u * acc);
-        if (tile == worker) B200_TR(6);                  // tile 0 MMAs issued
-        else if (tile == worker + n_workers) B200_TR(7); // tile 1 MMAs issued
+        if (unit == worker) B200_TR(6);                  // tile 0 MMAs issued
+        else if (unit == worker + n_workers) B200_TR(7); // tile 1 MMAs issued
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
     }
@@ -423,7 +433,8 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
     // this warp's 4 KB staging tile (transposes a chunk so that stores cover whole row segments)
     uint4* b200_stage = (uint4*)(smem_gen + B200_STAGES * B200_STAGE_BYTES + 256 + ew * (unsigned int)B200_STAGING_BYTES);
     unsigned int acc = 0, acc_phase = 0;
-    for (unsigned int tile = worker; tile < total_tiles; tile += n_workers) {
+    for (unsigned int unit = worker; unit < total_units; unit += n_workers) {
+      const unsigned int tile = unit % total_tiles;
       const unsigned int bidx = tile / tiles_per_batch;
       const unsigned int t = tile - bidx * tiles_per_batch;
       const unsigned int group = t / (B200_RASTER * shape.tiles_n);
@@ -444,7 +455,7 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
       }
       if (!b200_wait(bar_acc_full + 8u * acc, acc_phase, abort_flag, status, 4u)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (warp == 2 && lane == 0) { if (tile == worker) B200_TR(8); else if (tile == worker + n_workers) B200_TR(10); }
+      if (warp == 2 && lane == 0) { if (unit == worker) B200_TR(8); else if (unit == worker + n_workers) B200_TR(10); }
 #ifdef B200_TRACE
       B200_TRE(3);   // waiting for the accumulator (and the operand prefetch before it)
 #endif
@@ -478,7 +489,7 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
 #else
       if (lane == 0) b200_mbar_arrive(bar_acc_empty + 8u * acc);
 #endif
-      if (warp == 2 && lane == 0) { if (tile == worker) B200_TR(9); else if (tile == worker + n_workers) B200_TR(11); }
+      if (warp == 2 && lane == 0) { if (unit == worker) B200_TR(9); else if (unit == worker + n_workers) B200_TR(11); }
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
 #ifdef B200_TRACE
       B200_TRE(5);   // release of the accumulator buffer
