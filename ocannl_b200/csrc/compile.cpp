@@ -499,14 +499,22 @@ struct Builder {
       step = std::string("b200_acc = ") + (t.prec == Prec::Double ? "fma(" : "fmaf(") + ra.expr + ", " + rb.expr + ", b200_acc);";
     }
     em.used_nodes.insert(set.tn);
+    for (auto& d : st.par) if (d.from != 0) return false;
+    for (auto& d : st.ser) if (d.from != 0) return false;
+    // Register tiling: a short outermost output loop (the 10 classes of `dW[o, i] += dz[b, o] * h[b, i]`)
+    // stays inside the thread, which then reads the other factor once for all of its values.
+    const bool tiled = !term && st.par.size() >= 2 && st.par[0].extent() <= 16;
+    const int64_t e0 = tiled ? st.par[0].extent() : 1;
+    const size_t first_par = tiled ? 1 : 0;
+    const int64_t outputs = st.total / e0;          // output elements spread over threadIdx.x
     std::string decomp, sdecomp;
     {
       std::string rem = "b200_g";
-      for (size_t i = st.par.size(); i-- > 0;) {
+      for (size_t i = st.par.size(); i-- > first_par;) {
         const LoopDim& d = st.par[i];
         std::string ext = std::to_string(d.extent()) + "ull";
-        decomp += "      const unsigned int " + d.sym + " = (unsigned int)" + (i == 0 ? rem : "(" + rem + " % " + ext + ")") + ";\n";
-        if (i != 0) {
+        decomp += "      const unsigned int " + d.sym + " = (unsigned int)" + (i == first_par ? rem : "(" + rem + " % " + ext + ")") + ";\n";
+        if (i != first_par) {
           decomp += "      const unsigned long long b200_r" + std::to_string(i) + " = " + rem + " / " + ext + ";\n";
           rem = "b200_r" + std::to_string(i);
         }
@@ -522,37 +530,85 @@ struct Builder {
         }
       }
     }
-    for (auto& d : st.par) if (d.from != 0) return false;
-    for (auto& d : st.ser) if (d.from != 0) return false;
     const std::string off = em.offset(set.idcs, t.dims);
     std::string text = decomp + sdecomp + step + off;
     std::string statics = static_prologue(text, em, 2);
+    // Few output groups leave most SMs idle: the serial loop space is then also cut into Z slices,
+    // one block per (group, slice), and the slices meet in the output through atomic adds (their
+    // order is not fixed; the node is fp32 or fp64 and already holds the value being added to).
+    const int64_t groups = (outputs + 31) / 32;
+    int64_t Z = 1;
+    if (groups < 2 * 148) Z = std::max<int64_t>(1, std::min<int64_t>((4 * 148 + groups - 1) / groups, ser_total / 256));
     st.block = 32;
     st.block_y = 32;
     st.coop = 32;  // 32 threads per output element
+    st.grid_override = (int)std::min<int64_t>(groups * Z, 148 * 8);
     std::set<int> written = {set.tn};
+    const std::string o_sym = tiled ? st.par[0].sym : std::string();
+    const std::string E0 = std::to_string(e0);
     std::ostringstream k;
     k << "extern \"C\" __global__ void __launch_bounds__(1024) " << st.kernel << "(";
     emit_params(k, st, em, written);
     k << ") {\n" << kGridEntry << statics << "  __shared__ " << T << " b200_part[32][33];\n"
-      << "  for (unsigned long long b200_g0 = (unsigned long long)blockIdx.x * 32ull; b200_g0 < " << st.total
-      << "ull; b200_g0 += (unsigned long long)gridDim.x * 32ull) {\n"
-      << "    const unsigned long long b200_g = b200_g0 + threadIdx.x;\n"
-      << "    const bool b200_ok = b200_g < " << st.total << "ull;\n"
-      << "    " << T << " b200_acc = 0;\n    if (b200_ok) {\n"
-      << decomp << "      for (unsigned long long b200_l = threadIdx.y; b200_l < " << ser_total << "ull; b200_l += 32ull) {\n"
-      << sdecomp << "        " << step << "\n      }\n    }\n"
-      << "    b200_part[threadIdx.y][threadIdx.x] = b200_acc;\n    __syncthreads();\n"
-      << "    if (threadIdx.y == 0 && b200_ok) {\n" << decomp << "      " << T << " b200_s = 0;\n"
-      << "      for (int b200_y = 0; b200_y < 32; ++b200_y) b200_s += b200_part[b200_y][threadIdx.x];\n"
-      << "      " << t.ident << "[" << off << "] = " << t.ident << "[" << off << "] + b200_s;\n    }\n    __syncthreads();\n  }\n}\n\n";
+      << "  for (unsigned long long b200_u = blockIdx.x; b200_u < " << groups * Z << "ull; b200_u += gridDim.x) {\n"
+      << "    const unsigned long long b200_g = (b200_u % " << groups << "ull) * 32ull + threadIdx.x, b200_z = b200_u / " << groups << "ull;\n"
+      << "    const unsigned long long b200_l0 = b200_z * " << ser_total << "ull / " << Z << "ull, b200_l1 = (b200_z + 1ull) * "
+      << ser_total << "ull / " << Z << "ull;\n"
+      << "    const bool b200_ok = b200_g < " << outputs << "ull;\n";
+    if (tiled) k << "    " << T << " b200_accs[" << E0 << "];\n#pragma unroll\n    for (int b200_o = 0; b200_o < " << E0 << "; ++b200_o) b200_accs[b200_o] = 0;\n";
+    else k << "    " << T << " b200_acc = 0;\n";
+    k << "    if (b200_ok) {\n" << decomp
+      << "#pragma unroll 4\n      for (unsigned long long b200_l = b200_l0 + threadIdx.y; b200_l < b200_l1; b200_l += 32ull) {\n" << sdecomp;
+    if (tiled)
+      k << "#pragma unroll\n        for (unsigned int " << o_sym << " = 0; " << o_sym << " < " << E0 << "u; ++" << o_sym << ") {\n"
+        << "          " << T << " b200_acc = b200_accs[" << o_sym << "];\n          " << step << "\n          b200_accs[" << o_sym
+        << "] = b200_acc;\n        }\n";
+    else
+      k << "        " << step << "\n";
+    k << "      }\n    }\n";
+    // combine the 32 slices of threadIdx.y, one output value (of the tiled loop) at a time
+    if (tiled) k << "#pragma unroll\n    for (unsigned int " << o_sym << " = 0; " << o_sym << " < " << E0 << "u; ++" << o_sym << ") {\n      const "
+                 << T << " b200_acc = b200_accs[" << o_sym << "];\n";
+    else k << "    {\n";
+    k << "      b200_part[threadIdx.y][threadIdx.x] = b200_acc;\n      __syncthreads();\n"
+      << "      if (threadIdx.y == 0 && b200_ok) {\n" << decomp << "        " << T << " b200_s = 0;\n"
+      << "        for (int b200_y = 0; b200_y < 32; ++b200_y) b200_s += b200_part[b200_y][threadIdx.x];\n";
+    if (Z > 1) k << "        atomicAdd(&" << t.ident << "[" << off << "], b200_s);\n";
+    else k << "        " << t.ident << "[" << off << "] = " << t.ident << "[" << off << "] + b200_s;\n";
+    k << "      }\n      __syncthreads();\n    }\n  }\n}\n\n";
     src << k.str();
-    st.note = "par=" + std::to_string(st.par.size()) + " ser=" + std::to_string(st.ser.size()) + " serial loops split over a 32x32 block";
+    st.note = "par=" + std::to_string(st.par.size()) + " ser=" + std::to_string(st.ser.size()) + " serial loops split over a 32x32 block" +
+              (Z > 1 ? ", " + std::to_string(Z) + " slices per output group (atomic adds)" : std::string()) +
+              (tiled ? ", outer loop of " + E0 + " kept in registers" : std::string());
     code.stages.push_back(st);
     return true;
   }
 
-  void generic_stage(const std::vector<LoopDim>& nest, const StmtP& body) {
+  // Does `set` write every element of its node exactly once over `loops` (each axis a distinct
+  // loop symbol running over the whole axis, or a fixed 0 on an axis of extent 1)?
+  bool covers_node(const Stmt& set, const std::vector<LoopDim>& loops) {
+    const Tnode& t = code.prog.tn(set.tn);
+    if (set.kind != Stmt::Set || set.vec_len > 0 || set.idcs.size() != t.dims.size()) return false;
+    std::set<std::string> seen;
+    for (size_t a = 0; a < set.idcs.size(); ++a) {
+      const Index& ix = set.idcs[a];
+      if (ix.kind == Index::Fixed) {
+        if (ix.fixed != 0 || t.dims[a] != 1) return false;
+        continue;
+      }
+      if (ix.kind != Index::Iter || !seen.insert(ix.sym).second) return false;
+      bool found = false;
+      for (auto& d : loops)
+        if (d.sym == ix.sym && d.from == 0 && d.extent() == t.dims[a]) found = true;
+      if (!found) return false;
+    }
+    return true;
+  }
+
+  // `lhs_zero`: the node the body assigns is known to be all zero when the stage starts.
+  // Returns true when the stage made an earlier zero_out of that node unnecessary.
+  bool generic_stage(const std::vector<LoopDim>& nest, const StmtP& body, bool lhs_zero = false) {
+    bool zero_out_dead = false;
     Stage st;
     st.kind = Stage::Generic;
     st.kernel = kernel_name();
@@ -568,20 +624,55 @@ struct Builder {
     Emitter em(code.prog);
     em.large_models = opt.large_models;
 
-    if (!st.ser.empty() && st.total > 0 && opt.enable_coop && ser_split_stage(st, *body)) return;
+    if (!st.ser.empty() && st.total > 0 && opt.enable_coop && ser_split_stage(st, *body)) return false;
 
     CoopInfo ci;
     if (st.ser.empty() && st.total > 0) ci = find_coop(*body, st.total);
     if (ci.grid_blocks > 0) {
       --next_kernel;  // the name reserved above is re-issued to the first pass
       grid_reduce_stage(body, ci);
-      return;
+      return false;
     }
     std::set<int> written;
     walk_stmt(*body, [](const Scalar&) {}, [&](const Stmt& s) {
       if (s.kind == Stmt::Set || s.kind == Stmt::ZeroOut) written.insert(s.tn);
     });
 
+    // Accumulator promotion: `t[p] := f(t[p], ...)` under serial loops that do not move p keeps
+    // t[p] in a register across those loops (one load, or none when the node is known to be zero,
+    // and one store) instead of a read-modify-write of memory per iteration.
+    std::string before, after;
+    if (ci.sym.empty() && !st.ser.empty() && body->kind == Stmt::Set && body->vec_len == 0) {
+      const Stmt& set = *body;
+      const Tnode& t = code.prog.tn(set.tn);
+      bool ok = t.mode != Mode::Virtual && t.prec != Prec::Uint4x32;
+      for (auto& ix : set.idcs)
+        for (auto& d : st.ser)
+          if (ix.uses(d.sym)) ok = false;
+      int self_reads = 0;
+      walk_scalar(*set.value, [&](const Scalar& e) {
+        if (e.kind == Scalar::LocalScope) ok = false;
+        if ((e.kind == Scalar::Get || e.kind == Scalar::GetDyn) && e.tn == set.tn) {
+          bool same = e.kind == Scalar::Get && e.idcs.size() == set.idcs.size();
+          for (size_t i = 0; same && i < e.idcs.size(); ++i)
+            if (e.idcs[i].kind != set.idcs[i].kind || e.idcs[i].sym != set.idcs[i].sym || e.idcs[i].fixed != set.idcs[i].fixed ||
+                e.idcs[i].terms != set.idcs[i].terms)
+              same = false;
+          if (same) ++self_reads; else ok = false;
+        }
+      }, [](const Stmt&) {});
+      if (ok && self_reads > 0) {
+        const std::string off = em.offset(set.idcs, t.dims);
+        const std::string lv = t.ident + "[" + off + "]";
+        em.used_nodes.insert(set.tn);
+        before = std::string("    ") + Emitter::rtype(t.prec) + " b200_self = " +
+                 (lhs_zero ? em.constant(0.0, t.prec) : Emitter::load_wrap(t.prec, lv)) + ";\n";
+        after = "    " + lv + " = " + Emitter::store_wrap(t.prec, "b200_self") + ";\n";
+        em.forwarded[set.tn] = {set.idcs, "b200_self"};
+        em.set_redirect[set.tn] = {set.idcs, "b200_self"};
+        zero_out_dead = lhs_zero && covers_node(set, st.par);
+      }
+    }
     std::string inner;
     int ind = 4 + 2 * (int)st.ser.size();
     if (!ci.sym.empty()) {
@@ -603,7 +694,7 @@ struct Builder {
       k -= 2;
       close += std::string((size_t)k, ' ') + "}\n";
     }
-    std::string body_text = open + inner + close;
+    std::string body_text = before + open + inner + close + after;
 
     // index decomposition: the innermost parallel loop varies fastest across threads
     std::string decomp;
@@ -646,6 +737,7 @@ struct Builder {
     st.note = note.str();
     pieces[code.stages.size()] = pc;
     code.stages.push_back(st);
+    return zero_out_dead;
   }
 
   // Text of one stand-alone generic kernel (grid-stride over the stage's parallel iterations).
@@ -805,6 +897,19 @@ struct Builder {
 
   // Decides which stages share a launch and writes the kernels' text.
   void emit_kernels() {
+    {
+      // zero_outs that later stages made unnecessary leave the list (pieces are keyed by stage index)
+      std::vector<Stage> kept;
+      std::map<size_t, Piece> moved;
+      for (size_t i = 0; i < code.stages.size(); ++i) {
+        if (code.stages[i].kind == Stage::Memset && code.stages[i].memset_tn < 0) continue;
+        auto it = pieces.find(i);
+        if (it != pieces.end()) moved[kept.size()] = it->second;
+        kept.push_back(code.stages[i]);
+      }
+      code.stages.swap(kept);
+      pieces.swap(moved);
+    }
     std::vector<Stage> out;
     auto fusable = [&](size_t i) {
       const Stage& st = code.stages[i];
@@ -956,6 +1061,15 @@ struct Builder {
     top_level(code.prog.body, flat);
     src << kNumericsSource << "\n";
     std::set<int> zeroed;  // nodes zeroed by the previous stage (for beta = 0 contractions)
+    std::map<int, size_t> zero_stage;  // ... and the index of the stage that zeroes them
+    std::set<int> zero_read;           // zeroed nodes some later stage has read as zeros
+    auto drop_zero_out = [&](int tn) {
+      // the node is about to be overwritten completely by a stage that does not read it
+      auto it = zero_stage.find(tn);
+      if (it == zero_stage.end() || zero_read.count(tn)) return;
+      code.stages[it->second].memset_tn = -1;   // filtered out in emit_kernels
+      zero_stage.erase(it);
+    };
     for (size_t i = 0; i < flat.size(); ++i) {
       const StmtP& s = flat[i];
       if (s->kind == Stmt::DeclareLocal || s->kind == Stmt::SetLocal)
@@ -976,6 +1090,7 @@ struct Builder {
           int n_fused = 0;
           if (body->kind == Stmt::Set && body->tn == s->tn &&
               match_gemm(code.prog, nest, *body, true, opt, followers_after(flat, i + 2), &n_fused, &g)) {
+            if (g.gemm.split_k > 1) memset_stage(s->tn);   // partial tiles are added to the zeroed node
             g.kernel = kernel_name();
             g.gemm_source = gemm_translation_unit(code.prog, g, g.kernel, opt);
             code.stages.push_back(g);
@@ -984,6 +1099,8 @@ struct Builder {
           }
         }
         if (!absorbed) {
+          zero_stage[s->tn] = code.stages.size();
+          zero_read.erase(s->tn);
           memset_stage(s->tn);
           zeroed.insert(s->tn);  // still all zero until some stage writes it
         }
@@ -1010,6 +1127,10 @@ struct Builder {
         if (w.kind == Stmt::Set || w.kind == Stmt::ZeroOut) writes_now.insert(w.tn);
       });
       const bool was_zero = body->kind == Stmt::Set && zeroed.count(body->tn) > 0;
+      walk_stmt(*body, [&](const Scalar& e) {
+        if ((e.kind == Scalar::Get || e.kind == Scalar::GetDyn) && zeroed.count(e.tn) && !(body->kind == Stmt::Set && e.tn == body->tn))
+          zero_read.insert(e.tn);
+      }, [](const Stmt&) {});
       for (int w : writes_now) zeroed.erase(w);
       if (opt.enable_gemm && body->kind == Stmt::Set) {
         Stage g;
@@ -1017,6 +1138,8 @@ struct Builder {
         const std::vector<Follower> fol = followers_after(flat, i + 1);
         if (match_gemm(code.prog, nest, *body, was_zero, opt, fol, &n_fused, &g)) {
           for (int f = 0; f < n_fused; ++f) zeroed.erase(fol[(size_t)f].set->tn);
+          // beta = 0 over the whole node: the zero_out before it has no reader left
+          if (was_zero && !g.gemm.accumulate && g.gemm.split_k == 1 && covers_node(*body, nest)) drop_zero_out(body->tn);
           g.kernel = kernel_name();
           g.gemm_source = gemm_translation_unit(code.prog, g, g.kernel, opt);
           code.stages.push_back(g);
@@ -1024,7 +1147,7 @@ struct Builder {
           continue;
         }
       }
-      generic_stage(nest, body);
+      if (generic_stage(nest, body, was_zero)) drop_zero_out(body->tn);
     }
     emit_kernels();
     code.source = src.str();
