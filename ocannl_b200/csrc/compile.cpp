@@ -638,6 +638,29 @@ struct Builder {
       if (s.kind == Stmt::Set || s.kind == Stmt::ZeroOut) written.insert(s.tn);
     });
 
+    // Pairs.  When the stage is one assignment whose innermost parallel loop runs along the last
+    // axis of the written node, and everything in it is fp32, bf16 or half, a thread takes TWO
+    // neighbouring iterations of that loop: 4- and 8-byte accesses, packed 16-bit arithmetic.
+    bool pairs = false;
+    if (opt.enable_pairs && ci.sym.empty() && body->kind == Stmt::Set && body->vec_len == 0 && !st.par.empty() && st.total > 0) {
+      const Stmt& set = *body;
+      const Tnode& t = code.prog.tn(set.tn);
+      const LoopDim& p = st.par.back();
+      bool ok = p.from == 0 && p.extent() % 2 == 0 && Emitter::pair_prec(t.prec) && t.mode != Mode::Virtual && !set.idcs.empty() &&
+                set.idcs.back().kind == Index::Iter && set.idcs.back().sym == p.sym && t.dims.back() % 2 == 0;
+      for (size_t a = 0; ok && a + 1 < set.idcs.size(); ++a)
+        if (set.idcs[a].uses(p.sym)) ok = false;
+      // reads of the written node only at the written position (they become the promoted register)
+      walk_scalar(*set.value, [&](const Scalar& e) {
+        if ((e.kind == Scalar::Get || e.kind == Scalar::GetDyn) && e.tn == set.tn && st.ser.empty()) ok = false;
+      }, [](const Stmt&) {});
+      if (ok && em.pair_supported(*set.value)) {
+        pairs = true;
+        em.pair = true;
+        em.pair_sym = p.sym;
+        em.pair_vector_loads = true;
+      }
+    }
     // Accumulator promotion: `t[p] := f(t[p], ...)` under serial loops that do not move p keeps
     // t[p] in a register across those loops (one load, or none when the node is known to be zero,
     // and one store) instead of a read-modify-write of memory per iteration.
@@ -665,14 +688,35 @@ struct Builder {
         const std::string off = em.offset(set.idcs, t.dims);
         const std::string lv = t.ident + "[" + off + "]";
         em.used_nodes.insert(set.tn);
-        before = std::string("    ") + Emitter::rtype(t.prec) + " b200_self = " +
-                 (lhs_zero ? em.constant(0.0, t.prec) : Emitter::load_wrap(t.prec, lv)) + ";\n";
-        after = "    " + lv + " = " + Emitter::store_wrap(t.prec, "b200_self") + ";\n";
+        if (pairs) {
+          const std::string PT = Emitter::pair_type(t.prec);
+          const std::string at = "(" + t.ident + " + " + off + ")";
+          before = "    " + PT + " b200_self = " +
+                   (lhs_zero ? (t.prec == Prec::Single ? std::string("b200_f2{0.0f, 0.0f}") : std::string("0u")) : "*(const " + PT + "*)" + at) + ";\n";
+          after = "    *(" + PT + "*)" + at + " = b200_self;\n";
+        } else {
+          before = std::string("    ") + Emitter::rtype(t.prec) + " b200_self = " +
+                   (lhs_zero ? em.constant(0.0, t.prec) : Emitter::load_wrap(t.prec, lv)) + ";\n";
+          after = "    " + lv + " = " + Emitter::store_wrap(t.prec, "b200_self") + ";\n";
+        }
         em.forwarded[set.tn] = {set.idcs, "b200_self"};
         em.set_redirect[set.tn] = {set.idcs, "b200_self"};
         zero_out_dead = lhs_zero && covers_node(set, st.par);
       }
     }
+    if (pairs && before.empty()) {
+      // without promotion a read of the written node would be a plain (unpaired) memory access
+      bool self = false;
+      walk_scalar(*body->value, [&](const Scalar& e) {
+        if ((e.kind == Scalar::Get || e.kind == Scalar::GetDyn) && e.tn == body->tn) self = true;
+      }, [](const Stmt&) {});
+      if (self) {
+        pairs = false;
+        em.pair = false;
+        em.pair_vector_loads = false;
+      }
+    }
+    if (pairs) st.total /= 2;   // one thread per pair
     std::string inner;
     int ind = 4 + 2 * (int)st.ser.size();
     if (!ci.sym.empty()) {
@@ -702,9 +746,10 @@ struct Builder {
       std::string rem = "b200_g";
       for (size_t i = st.par.size(); i-- > 0;) {
         const LoopDim& d = st.par[i];
-        std::string ext = std::to_string(d.extent()) + "ull";
+        const bool pair_dim = pairs && i + 1 == st.par.size();   // iterations of this loop are taken two at a time
+        std::string ext = std::to_string(pair_dim ? d.extent() / 2 : d.extent()) + "ull";
         std::string val = i == 0 ? rem : "(" + rem + " % " + ext + ")";
-        decomp += "    const unsigned int " + d.sym + " = (unsigned int)" + val +
+        decomp += "    const unsigned int " + d.sym + " = " + (pair_dim ? "2u * " : "") + "(unsigned int)" + val +
                   (d.from ? " + " + std::to_string(d.from) : std::string()) + ";\n";
         if (i != 0) {
           std::string nr = "b200_r" + std::to_string(i);
@@ -725,7 +770,7 @@ struct Builder {
     for (auto& d : st.ser) ser_work *= std::max<int64_t>(1, d.extent());
     pc.fusable = opt.enable_fuse && st.total > 0 && (st.coop == 0 || st.coop == 32) &&
                  st.total * std::max(1, st.coop) <= 16384 && ser_work <= 4096;
-    if (opt.enable_fuse && st.coop == 0 && st.total > 0 && !st.par.empty() && st.par[0].from == 0) {
+    if (opt.enable_fuse && st.coop == 0 && st.total > 0 && !st.par.empty() && st.par[0].from == 0 && !(pairs && st.par.size() == 1)) {
       pc.body = body;
       pc.row_sym = st.par[0].sym;
       pc.rows = st.par[0].extent();
@@ -733,7 +778,7 @@ struct Builder {
     }
     std::ostringstream note;
     note << "par=" << st.par.size() << " ser=" << st.ser.size()
-         << (st.coop > 32 ? " block-per-element" : st.coop ? " warp-per-element" : "");
+         << (st.coop > 32 ? " block-per-element" : st.coop ? " warp-per-element" : "") << (pairs ? " pairs" : "");
     st.note = note.str();
     pieces[code.stages.size()] = pc;
     code.stages.push_back(st);

@@ -597,12 +597,20 @@ std::string Emitter::stmt(const Stmt& s, int ind) {
       }
       if (pair) {
         auto prd = set_redirect.find(s.tn);
-        if (prd == set_redirect.end() || !same_indices(prd->second.first, s.idcs))
-          throw Error(-4, "pair emission of a store to memory");
+        const bool redirected = prd != set_redirect.end() && same_indices(prd->second.first, s.idcs);
+        if (!redirected) {
+          // a store to memory: only of a pair that lies side by side (checked by the caller)
+          bool contiguous = pair_vector_loads && !s.idcs.empty() && s.idcs.back().kind == Index::Iter &&
+                            s.idcs.back().sym == pair_sym && t.dims.back() % 2 == 0;
+          for (size_t a = 0; contiguous && a + 1 < s.idcs.size(); ++a)
+            if (s.idcs[a].uses(pair_sym)) contiguous = false;
+          if (!contiguous) throw Error(-4, "pair emission of a store to memory");
+        }
         std::string code;
         const std::string v = pair_scalar(t.prec, *s.value, code);
         used_nodes.insert(s.tn);
-        return code + pad(ind) + prd->second.second + " = " + v + ";\n";
+        if (redirected) return code + pad(ind) + prd->second.second + " = " + v + ";\n";
+        return code + pad(ind) + "*(" + pair_type(t.prec) + "*)(" + t.ident + " + " + offset(s.idcs, t.dims) + ") = " + v + ";\n";
       }
       Res v = scalar(t.prec, *s.value);
       used_nodes.insert(s.tn);
@@ -706,6 +714,18 @@ std::string Emitter::pair_scalar(Prec prec, const Scalar& e, std::string& code) 
         if (lt.tn == e.tn && same_indices(lt.idcs, e.idcs)) return pair_convert(t.prec, prec, lt.expr, code);
       ++direct_reads;
       const std::string off0 = offset(e.idcs, t.dims);
+      {
+        // the pair lies side by side in memory when the pair symbol is the last index and nothing else;
+        // it is then one 4- or 8-byte load (pair symbols are even and rows of even length keep it aligned)
+        bool contiguous = pair_vector_loads && !e.idcs.empty() && e.idcs.back().kind == Index::Iter &&
+                          e.idcs.back().sym == pair_sym && t.dims.back() % 2 == 0;
+        for (size_t a = 0; contiguous && a + 1 < e.idcs.size(); ++a)
+          if (e.idcs[a].uses(pair_sym)) contiguous = false;
+        if (contiguous) {
+          const std::string v = pair_tmp(t.prec, std::string("*(const ") + pair_type(t.prec) + "*)(" + t.ident + " + " + off0 + ")", code);
+          return pair_convert(t.prec, prec, v, code);
+        }
+      }
       pair_hi = true;
       const std::string off1 = offset(e.idcs, t.dims);
       pair_hi = false;

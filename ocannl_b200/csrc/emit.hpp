@@ -81,6 +81,7 @@ struct Emitter {
   bool pair = false;
   std::string pair_sym;
   bool pair_hi = false;   // while true, index() spells pair_sym as (pair_sym + 1u)
+  bool pair_vector_loads = false;  // the pair symbol takes even values only: side-by-side pairs are one access
   static bool pair_prec(Prec p) { return p == Prec::Single || p == Prec::Bfloat16 || p == Prec::Half; }
   static const char* pair_type(Prec p) { return p == Prec::Single ? "b200_f2" : "unsigned int"; }
   // whether `s` can be emitted in pair mode (given the scopes that are substituted)

@@ -63,7 +63,7 @@ __device__ __forceinline__ b200_u32 b200_pack_hf(float lo, float hi) {
 // ---- pairs of neighbouring elements: two floats, or two 16-bit values in one word (the first
 //      element in the low half).  The packed add / sub / mul round the exact result once, which
 //      for operands of the 16-bit format equals the float operation followed by a rounding.
-struct b200_f2 {
+struct __align__(8) b200_f2 {
   float x, y;
 };
 __device__ __forceinline__ float b200_bf2_lo(b200_u32 v) { return __uint_as_float(v << 16); }
