@@ -340,9 +340,35 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
     std::string row_off;   // element offset of column n = 0 of this row
   };
   std::vector<Out> outs;
-  const std::string n_sym = dn.syms.size() == 1 ? dn.syms[0].first : std::string();
-  // pair mode: b200_j counts PAIRS of columns; tiles hold one pair per entry
-  if (pair && (form_b || n_sym.empty() || g.n.extent % 2 != 0)) return false;
+  // The n axis may be several merged loop symbols (the (head, d) of an attention projection).  A
+  // node runs "along n" when its trailing axes are exactly those symbols, in order, over axes as
+  // long as the symbols' loops (the outermost may be longer): column n of a row then lies n
+  // elements after column 0.  `along_n` returns the indices of column 0, or nothing.
+  const size_t n_syms = dn.syms.size();
+  const std::string n_sym = n_syms >= 1 ? dn.syms.back().first : std::string();   // innermost: neighbours differ in it
+  auto along_n = [&](const Indices& idcs, const std::vector<int64_t>& dims, Indices* row) {
+    if (n_syms == 0 || idcs.size() < n_syms || idcs.size() != dims.size()) return false;
+    const size_t first = idcs.size() - n_syms;
+    for (size_t q = 0; q < n_syms; ++q) {
+      const Index& ix = idcs[first + q];
+      if (ix.kind != Index::Iter || ix.sym != dn.syms[q].first) return false;
+      if (q > 0 && dims[first + q] != dn.syms[q].second) return false;
+    }
+    for (size_t a = 0; a < first; ++a)
+      for (auto& sy : dn.syms)
+        if (idcs[a].uses(sy.first)) return false;
+    *row = idcs;
+    for (size_t q = 0; q < n_syms; ++q) {
+      Index& ix = (*row)[first + q];
+      ix.kind = Index::Fixed;
+      ix.fixed = 0;
+      ix.sym.clear();
+    }
+    return true;
+  };
+  // pair mode: b200_j counts PAIRS of columns; tiles hold one pair per entry.  Neighbouring columns
+  // differ only in the innermost n symbol as long as its loop has an even length.
+  if (pair && (form_b || n_sym.empty() || g.n.extent % 2 != 0 || dn.syms.back().second % 2 != 0)) return false;
   em.pair = pair;
   em.pair_sym = n_sym;
   bool pair_fail = false;
@@ -352,15 +378,9 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
     o.idcs = idcs;
     o.arr = "b200_o" + std::to_string(tn);
     const Tnode& t = P.tn(tn);
-    if (!n_sym.empty() && !idcs.empty() && idcs.back().kind == Index::Iter && idcs.back().sym == n_sym) {
-      bool elsewhere = false;
-      for (size_t a = 0; a + 1 < idcs.size(); ++a)
-        if (idcs[a].uses(n_sym)) elsewhere = true;
-      if (!elsewhere) {
-        Indices row = idcs;
-        row.back().kind = Index::Fixed;
-        row.back().fixed = 0;
-        row.back().sym.clear();
+    {
+      Indices row;
+      if (along_n(idcs, t.dims, &row)) {
         o.unit_n = true;
         o.row_off = em.offset(row, t.dims);
       }
@@ -392,9 +412,8 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
             }
           } else if (ix.kind != Index::Fixed) ok = false;
         }
-        if (ok && canon.back().kind == Index::Iter && canon.back().sym == n_sym) {
-          for (size_t a = 0; a + 1 < canon.size(); ++a)
-            if (canon[a].uses(n_sym)) ok = false;
+        Indices row;
+        if (ok && along_n(canon, t.dims, &row)) {
           bool dup = false;
           for (auto& lt : em.load_tiles)
             if (lt.tn == e.tn && lt.idcs.size() == e.idcs.size()) {
@@ -406,10 +425,6 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
           if (ok && !dup && n_in_tiles < 4) {
             const std::string member = "i" + std::to_string(n_in_tiles++);
             const std::string arr = "b200_t." + member;
-            Indices row = canon;
-            row.back().kind = Index::Fixed;
-            row.back().fixed = 0;
-            row.back().sym.clear();
             const std::string T = Emitter::ctype(t.prec);
             const bool f32 = t.prec == Prec::Single;
             std::ostringstream lc;
