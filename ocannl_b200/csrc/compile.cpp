@@ -214,6 +214,13 @@ struct Piece {
   StmtP body;
   std::string row_sym;
   int64_t rows = 0, per_row = 0;
+  // warp-per-row fusion: the stage's parallel loops, whether a warp cooperates on each output
+  // element (its reductions are warp-wide), whether a thread takes pairs of the innermost loop
+  StmtP any_body;
+  std::vector<LoopDim> par;
+  int coop = 0;
+  bool pairs = false;
+  int64_t ser_work = 1;
 };
 
 struct Builder {
@@ -776,6 +783,11 @@ struct Builder {
       pc.rows = st.par[0].extent();
       pc.per_row = st.total / pc.rows * ser_work;
     }
+    pc.any_body = body;
+    pc.par = st.par;
+    pc.coop = st.coop;
+    pc.pairs = pairs;
+    pc.ser_work = ser_work;
     std::ostringstream note;
     note << "par=" << st.par.size() << " ser=" << st.ser.size()
          << (st.coop > 32 ? " block-per-element" : st.coop ? " warp-per-element" : "") << (pairs ? " pairs" : "");
@@ -859,6 +871,113 @@ struct Builder {
     k_src << ") {\n" << kGridEntry << statics << text << "}\n\n";
     src << k_src.str();
     f.note = "fused " + std::to_string(idx.size()) + " small stages in one block";
+    return f;
+  }
+
+  // Warp-per-row fusion.  A run of stages that share their L outermost parallel loops ("the
+  // row": (batch, position, head) of an attention softmax), some of which reduce over the rest of
+  // the row with a warp per output element while others are pointwise along it, and which hand
+  // data to one another only within a row, runs as ONE kernel: a warp takes a row and executes
+  // the stages one after the other, its lanes striding over the row.  Row max, exponentials, row
+  // sum and the division of a softmax are one launch; the row stays in L1 / L2 between them.
+  bool rows_independent_prefix(const std::vector<size_t>& run, size_t L) {
+    std::map<int, int> writers, users;
+    for (size_t i : run) {
+      const Piece& pc = pieces[i];
+      for (int n : pc.written) writers[n]++;
+      for (int n : pc.used) users[n]++;
+    }
+    std::map<std::pair<int, size_t>, int> axis;  // (shared node, prefix position) -> axis carrying that loop's symbol
+    bool ok = true;
+    for (size_t i : run) {
+      const Piece& pc = pieces[i];
+      auto check = [&](int tn, const Indices& idcs) {
+        if (!writers.count(tn) || users[tn] < 2) return;
+        for (size_t q = 0; q < L; ++q) {
+          if (pc.par[q].extent() == 1) continue;   // a loop of one iteration separates nothing
+          const std::string& sym = pc.par[q].sym;
+          int a = -1;
+          for (size_t k = 0; k < idcs.size(); ++k) {
+            if (idcs[k].kind == Index::Iter && idcs[k].sym == sym && a < 0) a = (int)k;
+            else if (idcs[k].uses(sym)) ok = false;
+          }
+          if (a < 0) { ok = false; return; }
+          auto it = axis.find({tn, q});
+          if (it == axis.end()) axis[{tn, q}] = a;
+          else if (it->second != a) ok = false;
+        }
+      };
+      walk_stmt(
+          *pc.any_body,
+          [&](const Scalar& e) {
+            if (e.kind == Scalar::Get) check(e.tn, e.idcs);
+            if (e.kind == Scalar::GetDyn && writers.count(e.tn) && users[e.tn] >= 2) ok = false;
+          },
+          [&](const Stmt& st) {
+            if (st.kind == Stmt::Set) {
+              if (st.vec_len > 0 && writers.count(st.tn) && users[st.tn] >= 2) ok = false;
+              check(st.tn, st.idcs);
+            }
+            if (st.kind == Stmt::ZeroOut) ok = false;
+          });
+    }
+    return ok;
+  }
+
+  // can stage i join a warp-per-row group whose rows are the first L parallel loops of `like`?
+  bool warp_row_member(size_t i, size_t L, const Piece* like) {
+    auto it = pieces.find(i);
+    if (it == pieces.end() || !it->second.any_body) return false;
+    const Piece& pc = it->second;
+    if (pc.coop != 0 && pc.coop != 32) return false;
+    if (pc.par.size() < L || (pc.coop == 32 && pc.par.size() != L)) return false;
+    if (pc.pairs && pc.par.size() == L) return false;   // the pair loop must lie inside the row
+    for (size_t q = 0; q < L; ++q) {
+      if (pc.par[q].from != 0) return false;
+      if (like && pc.par[q].extent() != like->par[q].extent()) return false;
+    }
+    return true;
+  }
+
+  Stage emit_warp_rows(const std::vector<size_t>& run, size_t L) {
+    Stage f;
+    f.kind = Stage::Generic;
+    f.kernel = code.stages[run.front()].kernel;
+    f.block = 256;
+    int64_t rows = 1;
+    for (size_t q = 0; q < L; ++q) rows *= pieces[run.front()].par[q].extent();
+    f.total = rows;
+    f.coop = 32;   // launch arithmetic: 32 threads per row
+    Emitter em(code.prog);
+    std::set<int> written;
+    std::string text;
+    for (size_t i : run) {
+      const Stage& st = code.stages[i];
+      const Piece& pc = pieces[i];
+      em.used_nodes.insert(pc.used.begin(), pc.used.end());
+      written.insert(pc.written.begin(), pc.written.end());
+      em.uses_merge |= pc.uses_merge;
+      if (pc.coop == 32) {
+        text += "    {\n    const unsigned long long b200_g = b200_row;\n" + pc.decomp + pc.body_text + "    }\n";
+      } else {
+        const std::string inner = std::to_string(st.total / rows) + "ull";
+        text += "    for (unsigned long long b200_g = b200_row * " + inner + " + b200_t; b200_g < (b200_row + 1ull) * " + inner +
+                "; b200_g += 32ull) {\n" + pc.decomp + pc.body_text + "    }\n";
+      }
+      text += "    __syncwarp();\n";   // orders the row's stores before the next stage's loads
+    }
+    std::string statics = static_prologue(text, em, 2);
+    std::ostringstream k_src;
+    k_src << "extern \"C\" __global__ void __launch_bounds__(" << f.block << ") " << f.kernel << "(";
+    emit_params(k_src, f, em, written);
+    k_src << ") {\n" << kGridEntry << statics
+          << "  const unsigned int b200_t = threadIdx.x & 31u;\n"
+          << "  const unsigned long long b200_warp = ((unsigned long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;\n"
+          << "  const unsigned long long b200_nwarps = ((unsigned long long)gridDim.x * blockDim.x) >> 5;\n"
+          << "  for (unsigned long long b200_row = b200_warp; b200_row < " << rows << "ull; b200_row += b200_nwarps) {\n"
+          << text << "  }\n}\n\n";
+    src << k_src.str();
+    f.note = "row-fused " + std::to_string(run.size()) + " stages, one warp per row";
     return f;
   }
 
@@ -970,6 +1089,36 @@ struct Builder {
       return it != pieces.end() && it->second.body && it->second.rows >= 256 && it->second.per_row <= 64;
     };
     for (size_t i = 0; i < code.stages.size();) {
+      if (opt.enable_fuse && pieces.count(i) && pieces[i].any_body && (pieces[i].coop == 0 || pieces[i].coop == 32)) {
+        // the row is given by the first warp-cooperative stage of the run
+        size_t L = 0;
+        for (size_t j = i; j < code.stages.size() && j < i + 16; ++j) {
+          auto it = pieces.find(j);
+          if (it == pieces.end()) break;
+          if (it->second.coop == 32) { L = it->second.par.size(); break; }
+          if (it->second.coop != 0) break;
+        }
+        if (L > 0 && warp_row_member(i, L, nullptr)) {
+          const Piece& first = pieces[i];
+          int64_t rows = 1;
+          for (size_t q = 0; q < L; ++q) rows *= first.par[q].extent();
+          std::vector<size_t> run = {i};
+          bool has_coop = first.coop == 32;
+          size_t j = i + 1;
+          while (j < code.stages.size() && run.size() < 16 && warp_row_member(j, L, &first)) {
+            run.push_back(j);
+            if (!rows_independent_prefix(run, L)) { run.pop_back(); break; }
+            has_coop = has_coop || pieces[j].coop == 32;
+            ++j;
+          }
+          // a trailing pointwise stage gains nothing from the warp form unless it follows a reduction
+          if (run.size() >= 2 && has_coop && rows >= 1024) {
+            out.push_back(emit_warp_rows(run, L));
+            i = run.back() + 1;
+            continue;
+          }
+        }
+      }
       if (row_candidate(i)) {
         // the longest run that stays row-independent; runs made only of small stages are left to
         // the single-block fusion below, which also takes stages of unrelated shapes
