@@ -1112,7 +1112,7 @@ struct Builder {
             ++j;
           }
           // a trailing pointwise stage gains nothing from the warp form unless it follows a reduction
-          if (run.size() >= 2 && has_coop && rows >= 1024) {
+          if (run.size() >= 2 && has_coop && rows >= 128) {
             out.push_back(emit_warp_rows(run, L));
             i = run.back() + 1;
             continue;

@@ -129,8 +129,8 @@ def test_mlp_forward_bf16(device, rows):
     compare(ir, got, want, rtol=2e-2, atol=2e-3)
 
 
-@pytest.mark.parametrize("act", ["gelu", "relu"])
-def test_decoder_only_forward(device, act):
+@pytest.mark.parametrize("act,options", [("gelu", None), ("relu", None), ("gelu", "fuse=0 pairs=0")])
+def test_decoder_only_forward(device, act, options):
     """Config 4 at reduced width (2 sequences of 128 tokens, 2 layers, 2 heads of 64, d_model 128):
     every stage of the decoder block — batched strided q.k^T and attn.v contractions on the
     tensor-core path, masked softmax, layer norm, residual epilogues — against the cc restatement.
@@ -140,8 +140,13 @@ def test_decoder_only_forward(device, act):
     inputs = dict(W.transformer_params(layers=2, d_model=128, heads=2, d_head=64, d_ff=256),
                   **W.transformer_inputs(batch=2, seq=128))
     want = run_oracle(ir, inputs)
-    got, info = run_device(device, ir, inputs)
+    got, info = run_device(device, ir, inputs, options=options)
     kinds = [s["kind"] for s in info["stages"]]
+    notes = [s["note"] or "" for s in info["stages"]]
+    if options is None:       # softmax and layer norm chains run as one warp-per-row kernel each
+        assert sum("one warp per row" in n for n in notes) >= 2 * 3, notes
+    else:
+        assert not any("row-fused" in n or "pairs" in n for n in notes), notes
     assert kinds.count("gemm") >= 2 * 7, kinds      # q, k, v, q.k^T, attn.v, w_o, ffn, ffn_out per layer
     gemms = [s for s in info["stages"] if s["kind"] == "gemm"]
     assert any(s["batch"] == 4 and not s["b_kmajor"] for s in gemms)      # attn.v: (b, h) batch, v is n-major
@@ -162,18 +167,22 @@ def test_moons_large_batch_split_reductions(device):
     compare(ir, got, want, rtol=1e-4, atol=1e-6)
 
 
-def test_mlp_train_update_and_sgd(device):
+@pytest.mark.parametrize("rows,options", [(512, None), (512, "splitk=0 pairs=0"), (1024, None)])
+def test_mlp_train_update_and_sgd(device, rows, options):
     """Config 5 (ii) on a 512-row shard: forward, backprop (dW with both operands m/n-major and
     the batch axis contracted, dX with an n-major weight operand, beta = 0 into zeroed
     gradients) and the SGD routine, against the cc restatement."""
     from ocannl_b200 import backend as bk
-    rows = 512
     ir = W.mlp_train_update(rows=rows)
     x, onehot = W.mlp_inputs(rows=rows)
     inputs = dict(W.mlp_params(), x=x, labels=onehot)
     want = run_oracle(ir, inputs)
-    got, info = run_device(device, ir, inputs)
+    got, info = run_device(device, ir, inputs, options=options)
     gemms = [s for s in info["stages"] if s["kind"] == "gemm"]
+    if options is None:       # the weight gradients are few tiles over a long K: split, added with reductions
+        assert any("split_k" in s["note"] for s in gemms), [s["note"] for s in gemms]
+    else:
+        assert not any("split_k" in s["note"] for s in gemms)
     assert len(gemms) >= 6 and any(not s["a_kmajor"] and not s["b_kmajor"] for s in gemms), info
     # Gradients are sums over 512 rows of products of bf16 values.  Upstream activation
     # gradients are themselves ROUNDED to bf16 after an fp32 accumulation whose order differs
