@@ -1,0 +1,59 @@
+"""Host logic of the stage planner, checked without a GPU: `b200_compile` is device independent,
+so the plan (which stages exist, what each one is) can be read back from `b200_code_info`."""
+from ocannl_b200 import backend as bk
+from ocannl_b200 import workloads as W
+
+
+def _plan(ir, options=None):
+    code = bk.Code(ir, options)
+    try:
+        return code.info()["stages"]
+    finally:
+        code.free()
+
+
+def test_mlp_forward_plan():
+    st = _plan(W.mlp_forward(rows=8192))
+    notes = [s["note"] or "" for s in st]
+    assert [s["kind"] for s in st] == ["gemm", "gemm", "gemm", "generic", "generic"], notes
+    # 8192 x 1024 layers: CTA pairs on 256 x 256 tiles; the 10-wide logits: one CTA per 128 x 16 tile
+    assert "CTA pair" in notes[0] and "256x256x64" in notes[0] and "CTA pair" in notes[1]
+    assert "128x16x64" in notes[2] and "CTA pair" not in notes[2]
+    assert "row-fused 3 stages, one thread per row" in notes[3]          # row max, exp, row sum
+    assert "grid-wide reduction" in notes[4] and "last one combines" in notes[4]
+
+
+def test_training_plan_split_k_and_dropped_zero_outs():
+    st = _plan(W.mlp_train_update(rows=8192))
+    notes = [s["note"] or "" for s in st]
+    # seven gradient nodes are zeroed by the routine; the two activation gradients are then
+    # overwritten completely (beta = 0 contraction, promoted accumulation): their zero_outs go
+    assert sum(s["kind"] == "memset" for s in st) == 5, notes
+    split = [n for n in notes if "split_k" in n]
+    assert len(split) == 2 and all("split_k=4" in n for n in split), notes     # dW1, dW2: 16 pair tiles each
+    assert any("outer loop of 10 kept in registers" in n for n in notes), notes  # dW_out
+    assert any("slices per output group (atomic adds)" in n for n in notes), notes
+    assert any(n.endswith("pairs") for n in notes), notes
+    off = [s["note"] or "" for s in _plan(W.mlp_train_update(rows=8192), "splitk=0 pairs=0")]
+    assert not any("split_k" in n or n.endswith("pairs") for n in off), off
+
+
+def test_decoder_plan_fuses_softmax_and_layer_norm():
+    st = _plan(W.transformer_forward(batch=2, seq=128, layers=2, d_model=128, heads=2, d_head=64, d_ff=256))
+    notes = [s["note"] or "" for s in st]
+    assert sum("row-fused 4 stages, one warp per row" in n for n in notes) == 2 * 3, notes   # softmax + 2 layer norms per layer
+    unfused = _plan(W.transformer_forward(batch=2, seq=128, layers=2, d_model=128, heads=2, d_head=64, d_ff=256), "fuse=0")
+    assert len(unfused) == len(st) + 2 * 3 * 3
+    # the (head, d) columns of the q / k / v projections are one contiguous n axis: stored through the staging tile
+    code = bk.Code(W.transformer_forward(batch=2, seq=128, layers=2, d_model=128, heads=2, d_head=64, d_ff=256))
+    try:
+        first_gemm = [i for i, s in enumerate(st) if s["kind"] == "gemm"][0]
+        assert "b200_stage[" in code.source(first_gemm)
+    finally:
+        code.free()
+
+
+def test_random_number_routine_plan():
+    from tests.golden.golden_routines import n3_fwd
+    st = _plan(n3_fwd("single", 100000, "light"), "fuse=0")
+    assert all(s["kind"] == "generic" and s["total"] == 100000 for s in st), st     # every loop parallel, the vector store too
