@@ -79,6 +79,12 @@ int b200_stream_wait(b200_dev* dev, b200_event* ev);
 int b200_await(b200_dev* dev);
 int b200_is_idle(b200_dev* dev, int* idle);
 int b200_stream_handle(b200_dev* dev, uint64_t* custream);
+/* Extension (the reference has one stream per device, arrayjit/lib/cuda_backend.ml:215-238): with
+ * `on`, b200_h2d copies run on a second stream.  A copy still waits for everything queued before
+ * it, and everything queued after it waits for the copy; what changes is that work queued AFTER
+ * a copy runs beside it (the copy does not wait for it): uploading the next batch into a second
+ * buffer before launching the current step overlaps the two. */
+int b200_set_async_uploads(b200_dev* dev, int on);
 
 /* ---- routines: Lowered_backend.{compile, link} (arrayjit/lib/backend_impl.ml:334-367;
  *      cuda: arrayjit/lib/cuda_backend.ml:898-928 compile, :983-1066 link and launch).

@@ -159,6 +159,10 @@ class Device:
         check(lib().b200_is_idle(self.h, ctypes.byref(d)))
         return bool(d.value)
 
+    def set_async_uploads(self, on: bool = True):
+        """from_host copies on a second stream (see b200_set_async_uploads in include/b200.h)."""
+        check(lib().b200_set_async_uploads(self.h, ctypes.c_int(1 if on else 0)))
+
     def stream_handle(self) -> int:
         s = ctypes.c_uint64(0)
         check(lib().b200_stream_handle(self.h, ctypes.byref(s)))

@@ -182,9 +182,17 @@ int b200_pool_address(b200_dev* dev, int pool_id, uint64_t* device_ptr, size_t* 
 int b200_h2d(b200_dev* dev, int pool_id, size_t offset, const void* src, size_t bytes) {
   return guard([&] {
     if (!dev || (!src && bytes)) throw Error(B200_E_INVALID, "null argument");
-    dev->make_current();
+    dev->make_current(/*join=*/dev->upload_stream == nullptr);
     CUdeviceptr p = dev->address(pool_id, offset, bytes);
-    if (bytes) cu_check(cu().cuMemcpyHtoDAsync_(p, src, bytes, dev->stream), "cuMemcpyHtoDAsync");
+    if (bytes && dev->upload_stream) {
+      cu_check(cu().cuEventRecord_(dev->ev_compute, dev->stream), "cuEventRecord");
+      cu_check(cu().cuStreamWaitEvent_(dev->upload_stream, dev->ev_compute, 0), "cuStreamWaitEvent");
+      cu_check(cu().cuMemcpyHtoDAsync_(p, src, bytes, dev->upload_stream), "cuMemcpyHtoDAsync");
+      cu_check(cu().cuEventRecord_(dev->ev_upload, dev->upload_stream), "cuEventRecord");
+      dev->uploads_pending = true;
+    } else if (bytes) {
+      cu_check(cu().cuMemcpyHtoDAsync_(p, src, bytes, dev->stream), "cuMemcpyHtoDAsync");
+    }
     dev->n_h2d++;
   });
 }
@@ -334,6 +342,26 @@ int b200_is_idle(b200_dev* dev, int* idle) {
     if (r == CUDA_SUCCESS) *idle = 1;
     else if (r == CUDA_ERROR_NOT_READY) *idle = 0;
     else cu_check(r, "cuStreamQuery");
+  });
+}
+
+int b200_set_async_uploads(b200_dev* dev, int on) {
+  return guard([&] {
+    if (!dev) throw Error(B200_E_INVALID, "null argument");
+    dev->make_current();
+    if (on && !dev->upload_stream) {
+      cu_check(cu().cuStreamCreate_(&dev->upload_stream, CU_STREAM_NON_BLOCKING), "cuStreamCreate");
+      cu_check(cu().cuEventCreate_(&dev->ev_compute, CU_EVENT_DISABLE_TIMING), "cuEventCreate");
+      cu_check(cu().cuEventCreate_(&dev->ev_upload, CU_EVENT_DISABLE_TIMING), "cuEventCreate");
+    } else if (!on && dev->upload_stream) {
+      cu_check(cu().cuStreamSynchronize_(dev->upload_stream), "cuStreamSynchronize");
+      cu().cuStreamDestroy_(dev->upload_stream);
+      cu().cuEventDestroy_(dev->ev_compute);
+      cu().cuEventDestroy_(dev->ev_upload);
+      dev->upload_stream = nullptr;
+      dev->ev_compute = dev->ev_upload = nullptr;
+      dev->uploads_pending = false;
+    }
   });
 }
 

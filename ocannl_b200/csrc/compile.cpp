@@ -723,7 +723,10 @@ struct Builder {
         em.pair_vector_loads = false;
       }
     }
-    if (pairs) st.total /= 2;   // one thread per pair
+    if (pairs) {
+      st.total /= 2;      // one thread per pair
+      st.min_align = 8;   // pairs are read and written as 4- and 8-byte words
+    }
     std::string inner;
     int ind = 4 + 2 * (int)st.ser.size();
     if (!ci.sym.empty()) {
@@ -848,6 +851,7 @@ struct Builder {
                 "u; b200_z += blockDim.x) " + t.ident + "[b200_z] = " + em.storage_zero(t.prec) + ";\n";
       } else {
         const Piece& pc = pieces[i];
+        f.min_align = std::max(f.min_align, st.min_align);
         em.used_nodes.insert(pc.used.begin(), pc.used.end());
         written.insert(pc.written.begin(), pc.written.end());
         em.uses_merge |= pc.uses_merge;
@@ -954,6 +958,7 @@ struct Builder {
     for (size_t i : run) {
       const Stage& st = code.stages[i];
       const Piece& pc = pieces[i];
+      f.min_align = std::max(f.min_align, st.min_align);
       em.used_nodes.insert(pc.used.begin(), pc.used.end());
       written.insert(pc.written.begin(), pc.written.end());
       em.uses_merge |= pc.uses_merge;
@@ -1039,6 +1044,7 @@ struct Builder {
     for (size_t i : run) {
       const Stage& st = code.stages[i];
       const Piece& pc = pieces[i];
+      f.min_align = std::max(f.min_align, st.min_align);
       em.used_nodes.insert(pc.used.begin(), pc.used.end());
       written.insert(pc.written.begin(), pc.written.end());
       em.uses_merge |= pc.uses_merge;

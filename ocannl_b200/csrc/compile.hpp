@@ -58,6 +58,7 @@ struct Stage {
   std::string gemm_source;       // full translation unit of this stage's contraction kernel
   std::string epi_params, epi_args;  // epilogue plumbing: extra kernel parameters / call arguments
   int tile_m = 0, tile_n = 0, tile_k = 0;
+  int min_align = 0;             // >0: every node the stage touches must be bound at a multiple of this many bytes
   int cta_pair = 0;              // 1: two CTAs of a cluster share one tile_m x tile_n tile (cta_group::2)
   int box_m = 0, box_n = 0;      // rows of A / B one CTA stages per k block (the TMA boxes)
   int smem_bytes = 0;            // dynamic shared memory of the contraction kernel

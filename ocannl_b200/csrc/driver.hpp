@@ -21,7 +21,7 @@ namespace b200 {
   X(cuEventElapsedTime) X(cuModuleLoadData) X(cuModuleUnload) X(cuModuleGetFunction) X(cuLaunchKernel)                 \
   X(cuFuncSetAttribute) X(cuFuncGetAttribute) X(cuGetErrorString) X(cuTensorMapEncodeTiled) X(cuStreamBeginCapture)    \
   X(cuStreamEndCapture) X(cuGraphInstantiateWithFlags) X(cuGraphLaunch) X(cuGraphExecDestroy) X(cuGraphDestroy)        \
-  X(cuDeviceCanAccessPeer) X(cuCtxEnablePeerAccess) X(cuModuleGetGlobal) X(cuLaunchKernelEx) X(cuOccupancyMaxActiveClusters)
+  X(cuDeviceCanAccessPeer) X(cuCtxEnablePeerAccess) X(cuModuleGetGlobal) X(cuLaunchKernelEx) X(cuOccupancyMaxActiveClusters) X(cuStreamDestroy)
 
 #define B200_NVRTC_FUNCS(X)                                                                                  \
   X(nvrtcCreateProgram) X(nvrtcCompileProgram) X(nvrtcDestroyProgram) X(nvrtcGetCUBINSize) X(nvrtcGetCUBIN)  \

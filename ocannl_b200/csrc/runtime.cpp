@@ -117,6 +117,10 @@ void b200_routine::link(b200_dev* d, b200_code* c, const b200_binding* b, int n)
       if (a.kind == KArg::Node) {
         auto it = node_ptr.find(a.tn);
         if (it == node_ptr.end()) throw Error(B200_E_USER, "link: node '" + P.tn(a.tn).ident + "' has no buffer binding");
+        if (st.min_align > 1 && (it->second % (CUdeviceptr)st.min_align) != 0)
+          throw Error(B200_E_UNSUPPORTED, "link: node '" + P.tn(a.tn).ident + "' is bound at an address that is not a multiple of " +
+                                              std::to_string(st.min_align) + " bytes, which the pair form of stage '" + st.kernel +
+                                              "' needs; bind nodes at 16-byte multiples or compile the routine with pairs=0");
         arg_values[i].push_back(it->second);
       } else if (a.kind == KArg::Statics) {
         arg_values[i].push_back(statics_dev);

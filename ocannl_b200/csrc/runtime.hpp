@@ -31,7 +31,24 @@ struct b200_dev {
   CUdeviceptr status_dev = 0;
   long long n_launches = 0, n_graph_launches = 0, n_h2d = 0, n_d2h = 0, n_d2d = 0, n_events = 0;
 
-  void make_current() { b200::cu_check(b200::cu().cuCtxSetCurrent_(ctx), "cuCtxSetCurrent"); }
+  // Optional second stream for host-to-device copies (b200_set_async_uploads).  A copy waits for
+  // the work queued on `stream` before it and everything queued on `stream` after it waits for the
+  // copy, so every hazard the single stream would have ordered stays ordered -- but a copy no
+  // longer waits for the kernels launched AFTER it was queued, nor they for it: a caller that
+  // uploads batch i + 1 into a second buffer before launching step i overlaps the two.
+  CUstream upload_stream = nullptr;
+  CUevent ev_compute = nullptr, ev_upload = nullptr;
+  bool uploads_pending = false;
+
+  // `join` = false only for the upload itself: queueing a copy must not make the stream wait for
+  // the copies before it (they are ordered among themselves on their own stream)
+  void make_current(bool join = true) {
+    b200::cu_check(b200::cu().cuCtxSetCurrent_(ctx), "cuCtxSetCurrent");
+    if (join && uploads_pending) {
+      uploads_pending = false;
+      b200::cu_check(b200::cu().cuStreamWaitEvent_(stream, ev_upload, 0), "cuStreamWaitEvent(upload)");
+    }
+  }
   CUdeviceptr address(int pool_id, size_t offset, size_t bytes);
   void check_status();
 };

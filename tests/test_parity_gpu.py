@@ -33,6 +33,69 @@ def test_golden_routines_on_device(device):
             assert np.array_equal(got[t.ident].view(np.uint8), want[t.ident].view(np.uint8)), (name, t.ident)
 
 
+def test_pair_form_wants_aligned_bindings(device):
+    """A pair-form stage reads 16-bit elements two at a time: a node bound at an odd element offset
+    is refused at link (with pairs=0 the same binding is accepted and gives the right values)."""
+    from ocannl_b200 import backend as bk
+    from ocannl_b200.low_level import Routine, Seq, Set, loops
+    r = Routine("scale2")
+    x = r.tn("x", "bfloat16", [64, 32], read_only=True)
+    y = r.tn("y", "bfloat16", [64, 32])
+    i, j = r.syms(2)
+    r.body = Seq([loops([(i, 64), (j, 32)], Set(y, (i, j), x[i, j] + x[i, j]))])
+    pool = device.alloc_pool(1 << 16)
+    arrays = {"x": (pool, 2, x), "y": (pool, 8192, y)}          # x starts one element into the pool
+    code = bk.Code(r)
+    assert any((s["note"] or "").endswith("pairs") for s in code.info()["stages"])
+    with pytest.raises(bk.B200Error, match="multiple of 8 bytes"):
+        bk.Context(device, dict(arrays)).link(code)
+    plain = bk.Code(r, "pairs=0")
+    rt = bk.Context(device, dict(arrays)).link(plain)
+    xs = W.f32_to_bf16_bits(np.random.default_rng(3).normal(0, 1, (64, 32)).astype(np.float32))
+    rt.context.from_host("x", xs)
+    rt.run()
+    got = W.bf16_bits_to_f32(rt.context.to_host("y"))
+    assert np.array_equal(got, W.bf16_bits_to_f32(W.f32_to_bf16_bits(2 * W.bf16_bits_to_f32(xs))))
+    device.free_pool(pool)
+
+
+def test_uploads_on_second_stream_keep_order(device):
+    """With b200_set_async_uploads the copies run on their own stream; launches queued after a copy
+    still see its data, and a copy queued after a launch does not overwrite what the launch reads."""
+    ir = W.mlp_forward(rows=256)
+    x, onehot = W.mlp_inputs(rows=256)
+    x2, onehot2 = W.mlp_inputs(rows=256, seed=77, label_seed=78)
+    params = W.mlp_params()
+    want = [run_oracle(ir, dict(params, x=a, labels=b))["loss"] for a, b in ((x, onehot), (x2, onehot2))]
+    from ocannl_b200 import backend as bk
+    code = bk.Code(ir)
+    rt = bk.Context(device).link(code)
+    device.set_async_uploads(True)
+    try:
+        for k, v in params.items():
+            rt.context.from_host(k, v)
+        px, ox, _ = rt.context.arrays["x"]
+        pl, ol, _ = rt.context.arrays["labels"]
+        ps, os_, _ = rt.context.arrays["loss"]
+        h = [(bk.PinnedBuffer(a.shape, a.dtype), bk.PinnedBuffer(b.shape, b.dtype)) for a, b in ((x, onehot), (x2, onehot2))]
+        for (ha, hb), (a, b) in zip(h, ((x, onehot), (x2, onehot2))):
+            ha.array[...] = a
+            hb.array[...] = b
+        out = [bk.PinnedBuffer((1,), np.float32) for _ in range(6)]
+        for i in range(6):       # alternate the two batches through ONE input buffer, no host sync in between
+            ha, hb = h[i % 2]
+            device.from_host(px, ox, ha.array)
+            device.from_host(pl, ol, hb.array)
+            rt.run()
+            device.to_host(ps, os_, out[i].array)
+        device.await_()
+        for i in range(6):
+            np.testing.assert_allclose(out[i].array[0], want[i % 2][0], rtol=2e-2)
+        assert abs(float(want[0][0]) - float(want[1][0])) > 1e-4     # the two batches are told apart
+    finally:
+        device.set_async_uploads(False)
+
+
 @pytest.mark.parametrize("prec", ["single", "double", "bfloat16", "half", "int32"])
 @pytest.mark.parametrize("variant,count,options", [("light", 5, None), ("crypto", 1000, "fuse=0"), ("light", 70001, None)])
 def test_threefry_uniform_bits(device, prec, variant, count, options):
