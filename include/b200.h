@@ -80,10 +80,11 @@ int b200_await(b200_dev* dev);
 int b200_is_idle(b200_dev* dev, int* idle);
 int b200_stream_handle(b200_dev* dev, uint64_t* custream);
 /* Extension (the reference has one stream per device, arrayjit/lib/cuda_backend.ml:215-238): with
- * `on`, b200_h2d copies run on a second stream.  A copy still waits for everything queued before
- * it, and everything queued after it waits for the copy; what changes is that work queued AFTER
- * a copy runs beside it (the copy does not wait for it): uploading the next batch into a second
- * buffer before launching the current step overlaps the two. */
+ * `on`, b200_h2d copies run on a second stream.  A copy waits for everything queued before it.
+ * Work queued after it waits for the copy when it may touch the copied pool: b200_launch waits for
+ * the copies into the pools its routine binds (and pool 0), b200_d2h / b200_pool_memset0 for the
+ * copies into their pool, every other call for all copies.  Uploading the next batch into a second
+ * pool before launching the current step therefore overlaps the two. */
 int b200_set_async_uploads(b200_dev* dev, int on);
 
 /* ---- routines: Lowered_backend.{compile, link} (arrayjit/lib/backend_impl.ml:334-367;

@@ -133,6 +133,7 @@ int b200_pool_alloc(b200_dev* dev, int pool_id, size_t bytes, size_t alignment) 
     if (it != dev->pools.end()) {
       cu_check(cu().cuStreamSynchronize_(dev->stream), "cuStreamSynchronize");
       cu_check(cu().cuMemFree_(it->second.ptr), "cuMemFree");
+      if (it->second.upload_ev) cu().cuEventDestroy_(it->second.upload_ev);
       dev->used -= it->second.bytes;
       dev->pools.erase(it);
     }
@@ -153,6 +154,7 @@ int b200_pool_free(b200_dev* dev, int pool_id) {
     if (it == dev->pools.end()) throw Error(B200_E_INVALID, "free_pool: unknown pool id " + std::to_string(pool_id));
     cu_check(cu().cuStreamSynchronize_(dev->stream), "cuStreamSynchronize");
     cu_check(cu().cuMemFree_(it->second.ptr), "cuMemFree");
+    if (it->second.upload_ev) cu().cuEventDestroy_(it->second.upload_ev);
     dev->used -= it->second.bytes;
     dev->pools.erase(it);
   });
@@ -161,7 +163,8 @@ int b200_pool_free(b200_dev* dev, int pool_id) {
 int b200_pool_memset0(b200_dev* dev, int pool_id, size_t offset, size_t bytes) {
   return guard([&] {
     if (!dev) throw Error(B200_E_INVALID, "null device");
-    dev->make_current();
+    dev->make_current(/*join=*/false);
+    dev->join_pool_id(pool_id);   // only uploads into this pool matter to the clear
     CUdeviceptr p = dev->address(pool_id, offset, bytes);
     if (bytes) cu_check(cu().cuMemsetD8Async_(p, 0, bytes, dev->stream), "cuMemsetD8Async");
   });
@@ -185,10 +188,13 @@ int b200_h2d(b200_dev* dev, int pool_id, size_t offset, const void* src, size_t 
     dev->make_current(/*join=*/dev->upload_stream == nullptr);
     CUdeviceptr p = dev->address(pool_id, offset, bytes);
     if (bytes && dev->upload_stream) {
+      Pool& pool = dev->pools.at(pool_id);
+      if (!pool.upload_ev) cu_check(cu().cuEventCreate_(&pool.upload_ev, CU_EVENT_DISABLE_TIMING), "cuEventCreate");
       cu_check(cu().cuEventRecord_(dev->ev_compute, dev->stream), "cuEventRecord");
       cu_check(cu().cuStreamWaitEvent_(dev->upload_stream, dev->ev_compute, 0), "cuStreamWaitEvent");
       cu_check(cu().cuMemcpyHtoDAsync_(p, src, bytes, dev->upload_stream), "cuMemcpyHtoDAsync");
-      cu_check(cu().cuEventRecord_(dev->ev_upload, dev->upload_stream), "cuEventRecord");
+      cu_check(cu().cuEventRecord_(pool.upload_ev, dev->upload_stream), "cuEventRecord");
+      pool.upload_pending = true;
       dev->uploads_pending = true;
     } else if (bytes) {
       cu_check(cu().cuMemcpyHtoDAsync_(p, src, bytes, dev->stream), "cuMemcpyHtoDAsync");
@@ -200,7 +206,8 @@ int b200_h2d(b200_dev* dev, int pool_id, size_t offset, const void* src, size_t 
 int b200_d2h(b200_dev* dev, int pool_id, size_t offset, void* dst, size_t bytes) {
   return guard([&] {
     if (!dev || (!dst && bytes)) throw Error(B200_E_INVALID, "null argument");
-    dev->make_current();
+    dev->make_current(/*join=*/false);
+    dev->join_pool_id(pool_id);
     CUdeviceptr p = dev->address(pool_id, offset, bytes);
     if (bytes) cu_check(cu().cuMemcpyDtoHAsync_(dst, p, bytes, dev->stream), "cuMemcpyDtoHAsync");
     dev->n_d2h++;
@@ -352,14 +359,17 @@ int b200_set_async_uploads(b200_dev* dev, int on) {
     if (on && !dev->upload_stream) {
       cu_check(cu().cuStreamCreate_(&dev->upload_stream, CU_STREAM_NON_BLOCKING), "cuStreamCreate");
       cu_check(cu().cuEventCreate_(&dev->ev_compute, CU_EVENT_DISABLE_TIMING), "cuEventCreate");
-      cu_check(cu().cuEventCreate_(&dev->ev_upload, CU_EVENT_DISABLE_TIMING), "cuEventCreate");
     } else if (!on && dev->upload_stream) {
       cu_check(cu().cuStreamSynchronize_(dev->upload_stream), "cuStreamSynchronize");
       cu().cuStreamDestroy_(dev->upload_stream);
       cu().cuEventDestroy_(dev->ev_compute);
-      cu().cuEventDestroy_(dev->ev_upload);
+      for (auto& kv : dev->pools) {
+        if (kv.second.upload_ev) cu().cuEventDestroy_(kv.second.upload_ev);
+        kv.second.upload_ev = nullptr;
+        kv.second.upload_pending = false;
+      }
       dev->upload_stream = nullptr;
-      dev->ev_compute = dev->ev_upload = nullptr;
+      dev->ev_compute = nullptr;
       dev->uploads_pending = false;
     }
   });
@@ -445,7 +455,11 @@ int b200_link(b200_dev* dev, b200_code* code, const b200_binding* bindings, int 
 int b200_launch(b200_routine* r, const int64_t* static_idx, int n_static) {
   return guard([&] {
     if (!r) throw Error(B200_E_INVALID, "null routine");
-    r->dev->make_current();
+    r->dev->make_current(/*join=*/false);
+    if (r->dev->uploads_pending) {
+      r->dev->join_pool_id(0);   // the merge buffer
+      for (int id : r->pools_used) r->dev->join_pool_id(id);
+    }
     r->launch(static_idx, n_static);
   });
 }

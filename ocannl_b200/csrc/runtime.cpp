@@ -51,7 +51,10 @@ void b200_routine::link(b200_dev* d, b200_code* c, const b200_binding* b, int n)
   code = c;
   const Program& P = c->code.prog;
   std::map<int, const b200_binding*> bind;
-  for (int i = 0; i < n; ++i) bind[b[i].tn_id] = &b[i];
+  for (int i = 0; i < n; ++i) {
+    bind[b[i].tn_id] = &b[i];
+    pools_used.insert(b[i].pool_id);
+  }
 
   // routine-local nodes live in a scratch slab owned by the routine
   size_t off = 0;

@@ -2,6 +2,7 @@
 // compiled code and linked routines.
 #pragma once
 #include <map>
+#include <set>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -13,6 +14,9 @@
 struct Pool {
   CUdeviceptr ptr = 0;
   size_t bytes = 0;
+  // last upload into this pool on the upload stream, and whether `stream` still has to wait for it
+  CUevent upload_ev = nullptr;
+  bool upload_pending = false;
 };
 
 // One GPU: primary context, one non-blocking stream, the (pool id -> slab) table of
@@ -32,22 +36,32 @@ struct b200_dev {
   long long n_launches = 0, n_graph_launches = 0, n_h2d = 0, n_d2h = 0, n_d2d = 0, n_events = 0;
 
   // Optional second stream for host-to-device copies (b200_set_async_uploads).  A copy waits for
-  // the work queued on `stream` before it and everything queued on `stream` after it waits for the
-  // copy, so every hazard the single stream would have ordered stays ordered -- but a copy no
-  // longer waits for the kernels launched AFTER it was queued, nor they for it: a caller that
-  // uploads batch i + 1 into a second buffer before launching step i overlaps the two.
+  // the work queued on `stream` before it.  Work queued on `stream` after it waits for the copy if
+  // it may touch the copied pool: a routine launch waits for the copies into the pools it binds,
+  // every other call for all copies.  A caller that uploads batch i + 1 into a second pool before
+  // launching step i therefore overlaps the two, and no hazard the single stream ordered is lost.
   CUstream upload_stream = nullptr;
-  CUevent ev_compute = nullptr, ev_upload = nullptr;
+  CUevent ev_compute = nullptr;
   bool uploads_pending = false;
 
-  // `join` = false only for the upload itself: queueing a copy must not make the stream wait for
-  // the copies before it (they are ordered among themselves on their own stream)
+  void join_pool(Pool& p) {
+    if (!p.upload_pending) return;
+    p.upload_pending = false;
+    b200::cu_check(b200::cu().cuStreamWaitEvent_(stream, p.upload_ev, 0), "cuStreamWaitEvent(upload)");
+  }
+  void join_pool_id(int pool_id) {
+    auto it = pools.find(pool_id);
+    if (it != pools.end()) join_pool(it->second);
+  }
+  void join_all() {
+    if (!uploads_pending) return;
+    uploads_pending = false;
+    for (auto& kv : pools) join_pool(kv.second);
+  }
+  // `join` = false for the upload itself and for routine launches (which join their own pools)
   void make_current(bool join = true) {
     b200::cu_check(b200::cu().cuCtxSetCurrent_(ctx), "cuCtxSetCurrent");
-    if (join && uploads_pending) {
-      uploads_pending = false;
-      b200::cu_check(b200::cu().cuStreamWaitEvent_(stream, ev_upload, 0), "cuStreamWaitEvent(upload)");
-    }
+    if (join) join_all();
   }
   CUdeviceptr address(int pool_id, size_t offset, size_t bytes);
   void check_status();
@@ -88,6 +102,7 @@ struct b200_routine {
   std::vector<std::vector<std::pair<CUevent, CUevent>>> stage_events;  // per stage, per profiled run
   CUgraphExec graph = nullptr;
 
+  std::set<int> pools_used;   // pools of the bound nodes (what a launch has to wait for, uploads-wise)
   void link(b200_dev* d, b200_code* c, const b200_binding* b, int n);
   void launch(const int64_t* static_idx, int n_static);
   void enqueue_stages();
