@@ -33,6 +33,69 @@ def test_golden_routines_on_device(device):
             assert np.array_equal(got[t.ident].view(np.uint8), want[t.ident].view(np.uint8)), (name, t.ident)
 
 
+@pytest.mark.parametrize("prec", ["bfloat16", "half", "single"])
+@pytest.mark.parametrize("options", ["fuse=0", "fuse=0 pairs=0", None])
+def test_pointwise_arithmetic_bits(device, prec, options):
+    """Every exactly-rounded operation of the pointwise tables, in the pair form (packed 16-bit add,
+    sub, mul, min, max, one packed rounding per float pair) and in the one-element form, gives the
+    bits the cc restatement gives: the packed instructions round the exact result once, the
+    reference rounds a float result, and for operands of the format these coincide.  Half is
+    compared with a tolerance: the reference's C text writes half arithmetic on native `_Float16`
+    values (its conversion macros are the identity then), so how often a chain of half operations
+    is rounded is the host compiler's choice (gcc keeps float intermediates unless the CPU has
+    half arithmetic), while the device rounds after every operation as the cc backend's rule says."""
+    from ocannl_b200.low_level import Routine, Seq, Set, loops, binop, un, where, fma
+    r = Routine("pointwise_" + prec)
+    a = r.tn("a", prec, [96, 64], read_only=True)
+    b = r.tn("b", prec, [96, 64], read_only=True)
+    c = r.tn("c", "single", [96, 64], read_only=True)
+    outs = {}
+    body = []
+    exprs = {
+        "add": lambda x, y, z: x + y, "sub": lambda x, y, z: x - y, "mul": lambda x, y, z: x * y,
+        "div": lambda x, y, z: x / y, "max": lambda x, y, z: binop("max", x, y), "min": lambda x, y, z: binop("min", x, y),
+        "neg_relu": lambda x, y, z: un("relu", -x) + un("relu", y), "gate": lambda x, y, z: binop("relu_gate", x, y),
+        "where": lambda x, y, z: where(binop("lt", x, y), x, y), "fma": lambda x, y, z: fma(x, y, x),
+        "mixed": lambda x, y, z: (x * z + y) * 0.5 - z, "cube": lambda x, y, z: x ** 3.0 + y ** 2.0,
+        "sqrt_recip": lambda x, y, z: un("sqrt", x * x) + un("recip", y),
+    }
+    for name, f in exprs.items():
+        t = r.tn("o_" + name, prec, [96, 64])
+        outs[name] = t
+        i, j = r.syms(2)
+        body.append(loops([(i, 96), (j, 64)], Set(t, (i, j), f(a[i, j], b[i, j], c[i, j]))))
+    r.body = Seq(body)
+    rng = np.random.default_rng(11)
+    va = rng.normal(0, 1, (96, 64)).astype(np.float32)
+    vb = rng.normal(0, 3, (96, 64)).astype(np.float32)
+    vb[np.abs(vb) < 1e-3] = 1.0
+    va[0, :8] = [0.0, -0.0, 1.0, -1.0, 65504.0, 1e-7, 3.0e38, -3.0e38]        # zeros, format edges
+    vb[0, :8] = [0.0, 1.0, -1.0, 2.0 ** -14, 65504.0, 1e-7, 3.0e38, 1.0]
+    vc = rng.normal(0, 1, (96, 64)).astype(np.float32)
+    inputs = {"a": W.store(prec, va), "b": W.store(prec, vb), "c": vc}
+    want = run_oracle(r, inputs)
+    got, info = run_device(device, r, inputs, options=options)
+    if options == "fuse=0":
+        assert all("pairs" in (s["note"] or "") for s in info["stages"]), info
+    elif options is None:      # thirteen small stages: one single-block kernel
+        assert len(info["stages"]) == 1, info
+    for name, t in outs.items():
+        g = np.ascontiguousarray(got[t.ident]).view(np.uint16 if prec != "single" else np.uint32)
+        w_ = np.ascontiguousarray(want[t.ident]).view(np.uint16 if prec != "single" else np.uint32)
+        if name in ("div", "sqrt_recip", "cube") or prec == "half":
+            # libm / division / multiplication chains: last-bit tolerance; half: see the docstring
+            gv = W.load(prec, got[t.ident]).astype(np.float64)
+            wv = W.load(prec, want[t.ident]).astype(np.float64)
+            rtol = {"single": 1e-5, "half": 4e-3}.get(prec, 8e-3)       # fp32: the pointwise tolerance; 16-bit: 1-2 units
+            fin = np.isfinite(wv)
+            scale = float(np.abs(wv[fin & (np.abs(wv) < 1e30)]).max())  # sums of terms of either sign: absolute part
+            ok = np.isclose(gv, wv, rtol=rtol, atol=rtol * scale * (1e-2 if prec == "single" else 1.0), equal_nan=True) | (gv == wv)
+            assert ok.all(), (name, np.argwhere(~ok)[:4])
+        else:
+            same = (g == w_) | (np.isnan(W.load(prec, got[t.ident])) & np.isnan(W.load(prec, want[t.ident])))
+            assert same.all(), (name, np.argwhere(~same)[:4], g[~same][:4], w_[~same][:4])
+
+
 def test_pair_form_wants_aligned_bindings(device):
     """A pair-form stage reads 16-bit elements two at a time: a node bound at an odd element offset
     is refused at link (with pairs=0 the same binding is accepted and gives the right values)."""
