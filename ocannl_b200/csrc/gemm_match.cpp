@@ -368,7 +368,8 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   };
   // pair mode: b200_j counts PAIRS of columns; tiles hold one pair per entry.  Neighbouring columns
   // differ only in the innermost n symbol as long as its loop has an even length.
-  if (pair && (form_b || n_sym.empty() || g.n.extent % 2 != 0 || dn.syms.back().second % 2 != 0)) return false;
+  // (a materialised accumulate that reads its output back stays in the one-column form)
+  if (pair && ((form_b && g.accumulate) || n_sym.empty() || g.n.extent % 2 != 0 || dn.syms.back().second % 2 != 0)) return false;
   em.pair = pair;
   em.pair_sym = n_sym;
   bool pair_fail = false;
@@ -480,7 +481,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   if (!form_b) collect_loads(*set.value, nullptr);
 
   em.scope_subst[kAccScope] = "b200_acc";
-  if (pair) {
+  if (pair && !form_b) {
     em.scope_subst[scope->scope_id] = "b200_acc";
     if (!em.pair_supported(*set.value)) return false;
   }
@@ -709,7 +710,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   // The arithmetic of rows beyond M and columns beyond N is skipped only when it reads memory
   // itself; when every operand comes from a register tile it runs on whatever the registers hold
   // (nothing of it is stored), which saves a possibly divergent branch per column.
-  const std::string guard = (em.direct_reads > 0 || form_b) ? "b200_row_ok && b200_n < b200_N" : "true";
+  const std::string guard = (em.direct_reads > 0 || (form_b && g.accumulate && g.split_k == 1)) ? "b200_row_ok && b200_n < b200_N" : "true";
   if (pair) {
     for (auto& o : outs) fn << "  " << Emitter::pair_type(P.tn(o.tn).prec) << " " << o.arr << "[B200_EPI_CHUNK / 2];\n";
     fn << "#pragma unroll\n  for (int b200_j = 0; b200_j < B200_EPI_CHUNK / 2; ++b200_j) {\n"
@@ -779,7 +780,8 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
       }
       fn << "#pragma unroll\n      for (int b200_j = 0; b200_j < B200_EPI_CHUNK; ++b200_j)\n";
       if (reds)
-        fn << "        if (b200_n0 + (unsigned int)b200_j < b200_N) atomicAdd(&b200_p[b200_j], " << o.arr << "[b200_j]);\n";
+        fn << "        if (b200_n0 + (unsigned int)b200_j < b200_N) atomicAdd(&b200_p[b200_j], "
+           << (pair ? "((b200_j & 1) ? " + o.arr + "[b200_j >> 1].y : " + o.arr + "[b200_j >> 1].x)" : o.arr + "[b200_j]") << ");\n";
       else
         fn << "        if (b200_n0 + (unsigned int)b200_j < b200_N) b200_p[b200_j] = "
            << (!pair ? Emitter::store_wrap(t.prec, o.arr + "[b200_j]")
