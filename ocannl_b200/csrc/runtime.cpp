@@ -202,8 +202,20 @@ void b200_routine::enqueue_stages() {
     const Stage& st = code->code.stages[i];
     Timer timer(this, i);
     if (st.kind == Stage::Memset) {
-      const Tnode& t = P.tn(st.memset_tn);
-      cu_check(cu().cuMemsetD8Async_(node_ptr[st.memset_tn], 0, (size_t)t.bytes(), dev->stream), "cuMemsetD8Async");
+      // zero_outs of nodes that lie back to back in memory (parameter gradients allocated as one
+      // range) become one clear; nothing between two nodes is touched unless they are adjacent
+      CUdeviceptr at = node_ptr[st.memset_tn];
+      size_t bytes = (size_t)P.tn(st.memset_tn).bytes();
+      while (!profiling && i + 1 < code->code.stages.size() && code->code.stages[i + 1].kind == Stage::Memset) {
+        const int next_tn = code->code.stages[i + 1].memset_tn;
+        const CUdeviceptr next_at = node_ptr[next_tn];
+        const size_t next_bytes = (size_t)P.tn(next_tn).bytes();
+        if (next_at == at + bytes) bytes += next_bytes;
+        else if (next_at + next_bytes == at) { at = next_at; bytes += next_bytes; }
+        else break;
+        ++i;
+      }
+      cu_check(cu().cuMemsetD8Async_(at, 0, bytes, dev->stream), "cuMemsetD8Async");
       continue;
     }
     if (st.kind == Stage::Generic && st.total <= 0) continue;
