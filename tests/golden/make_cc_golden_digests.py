@@ -5,7 +5,7 @@ For each golden generated-C file of the reference, takes the text of the routine
 records the SHA-256 and length.  The parity test recomputes the same digest from
 the oracle emitter's output, so the golden text itself never enters this repository.
 
-    python tests/golden/make_cc_golden_digests.py /root/reference
+    python tests/golden/make_cc_golden_digests.py <reference checkout>
 """
 import hashlib
 import json
