@@ -222,7 +222,10 @@ def test_makemore_forward(device, wprec, options):
         compare(ir, got, want, rtol=2e-2, atol=2e-2, exact=["embed"])
 
 
-@pytest.mark.parametrize("shape", [(2, 256, 256, 256), (1, 200, 136, 200), (3, 128, 512, 64), (1, 384, 48, 1000)])
+@pytest.mark.parametrize("shape", [(2, 256, 256, 256), (1, 200, 136, 200), (3, 128, 512, 64), (1, 384, 48, 1000),
+                                   # ragged CTA-pair tiles: the second CTA of the last pair is partly / wholly beyond M,
+                                   # a last column tile of 8, a single partial k block
+                                   (2, 300, 200, 72), (1, 520, 264, 40)])
 @pytest.mark.parametrize("y_prec", ["bfloat16", "single"])
 def test_einsum_bias_gelu(device, shape, y_prec):
     """Config 3 shapes (`b|m,k ; b|k,n => b|m,n`, bias, composed GELU) on the tensor-core path,
