@@ -887,6 +887,12 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   unsigned int fmt = g.in_prec == Prec::Bfloat16 ? 1u : (g.in_prec == Prec::Half ? 0u : 2u);
   unsigned int idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((g.a_kmajor ? 0u : 1u) << 15) | ((g.b_kmajor ? 0u : 1u) << 16) |
                        ((unsigned int)(bn >> 3) << 17) | ((unsigned int)(bm >> 4) << 24);
+  // consecutive tiles walk down this many row tiles before moving to the next column tile
+  int raster = 8;
+  if (const char* ov = getenv("B200_GEMM_RASTER")) {
+    const int want = atoi(ov);
+    if (want >= 1 && want <= 64) raster = want;
+  }
   const std::string &params = st.epi_params, &args = st.epi_args;
   std::ostringstream o;
   o << kNumericsSource << "\n";
@@ -894,7 +900,7 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
     << "\n#define B200_BK " << bk << "\n#define B200_UMMA_K " << umma_k << "\n#define B200_ELEM_BYTES " << eb
     << "\n#define B200_STAGES " << stages << "\n#define B200_EPI_WARPS " << epi_warps << "\n#define B200_A_KMAJOR "
     << (g.a_kmajor ? 1 : 0) << "\n#define B200_B_KMAJOR " << (g.b_kmajor ? 1 : 0) << "\n#define B200_IDESC " << idesc
-    << "u\n#define B200_TMEM_COLS " << tmem_cols << "\n#define B200_RASTER " << (pair ? 4 : 8) << "\n#define B200_CTA_PAIR "
+    << "u\n#define B200_TMEM_COLS " << tmem_cols << "\n#define B200_RASTER " << raster << "\n#define B200_CTA_PAIR "
     << (pair ? 1 : 0) << "\n#define B200_SPLITK " << g.split_k << "\n";
   // columns per epilogue step: 32 when the epilogue keeps few register tiles, else 16 so that
   // the tiles and the double-buffered accumulator chunk stay in registers
