@@ -494,9 +494,37 @@ struct Builder {
     }
     Emitter em(code.prog);
     em.large_models = opt.large_models;
-    const std::string T = Emitter::ctype(t.prec);
+    // Pairs: a thread owns two neighbouring outputs along the innermost output loop when that loop
+    // runs along the last axis of the fp32 node; the factors are then read as 4- and 8-byte words.
+    bool pairs = false;
+    if (opt.enable_pairs && t.prec == Prec::Single && !st.par.empty() && !set.idcs.empty()) {
+      const LoopDim& p = st.par.back();
+      bool ok = p.from == 0 && p.extent() % 2 == 0 && set.idcs.back().kind == Index::Iter && set.idcs.back().sym == p.sym &&
+                t.dims.back() % 2 == 0;
+      for (size_t a = 0; ok && a + 1 < set.idcs.size(); ++a)
+        if (set.idcs[a].uses(p.sym)) ok = false;
+      if (ok && (term ? em.pair_supported(*term) : em.pair_supported(*fa) && em.pair_supported(*fb))) {
+        pairs = true;
+        em.pair = true;
+        em.pair_sym = p.sym;
+        em.pair_vector_loads = true;
+      }
+    }
+    const std::string T = pairs ? "b200_f2" : Emitter::ctype(t.prec);
+    const std::string zero = pairs ? "b200_f2{0.0f, 0.0f}" : "0";
     std::string step;
-    if (term) {
+    if (pairs) {
+      std::string pre;
+      if (term) {
+        const std::string v = em.pair_scalar(t.prec, *term, pre);
+        step = "{\n" + pre + "          b200_acc = b200_f2{b200_acc.x + " + v + ".x, b200_acc.y + " + v + ".y};\n          }";
+      } else {
+        const std::string a = em.pair_scalar(t.prec, *fa, pre), b = em.pair_scalar(t.prec, *fb, pre);
+        step = "{\n" + pre + "          b200_acc = b200_f2{fmaf(" + a + ".x, " + b + ".x, b200_acc.x), fmaf(" + a + ".y, " + b +
+               ".y, b200_acc.y)};\n          }";
+      }
+      st.min_align = 8;
+    } else if (term) {
       Emitter::Res r = em.scalar(t.prec, *term);
       if (!r.defs.empty()) return false;
       step = "b200_acc = b200_acc + " + r.expr + ";";
@@ -513,14 +541,16 @@ struct Builder {
     const bool tiled = !term && st.par.size() >= 2 && st.par[0].extent() <= 16;
     const int64_t e0 = tiled ? st.par[0].extent() : 1;
     const size_t first_par = tiled ? 1 : 0;
-    const int64_t outputs = st.total / e0;          // output elements spread over threadIdx.x
+    const int64_t outputs = st.total / e0 / (pairs ? 2 : 1);   // output elements (or pairs) spread over threadIdx.x
     std::string decomp, sdecomp;
     {
       std::string rem = "b200_g";
       for (size_t i = st.par.size(); i-- > first_par;) {
         const LoopDim& d = st.par[i];
-        std::string ext = std::to_string(d.extent()) + "ull";
-        decomp += "      const unsigned int " + d.sym + " = (unsigned int)" + (i == first_par ? rem : "(" + rem + " % " + ext + ")") + ";\n";
+        const bool pair_dim = pairs && i + 1 == st.par.size();
+        std::string ext = std::to_string(pair_dim ? d.extent() / 2 : d.extent()) + "ull";
+        decomp += "      const unsigned int " + d.sym + " = " + (pair_dim ? "2u * " : "") + "(unsigned int)" +
+                  (i == first_par ? rem : "(" + rem + " % " + ext + ")") + ";\n";
         if (i != first_par) {
           decomp += "      const unsigned long long b200_r" + std::to_string(i) + " = " + rem + " / " + ext + ";\n";
           rem = "b200_r" + std::to_string(i);
@@ -562,8 +592,8 @@ struct Builder {
       << "    const unsigned long long b200_l0 = b200_z * " << ser_total << "ull / " << Z << "ull, b200_l1 = (b200_z + 1ull) * "
       << ser_total << "ull / " << Z << "ull;\n"
       << "    const bool b200_ok = b200_g < " << outputs << "ull;\n";
-    if (tiled) k << "    " << T << " b200_accs[" << E0 << "];\n#pragma unroll\n    for (int b200_o = 0; b200_o < " << E0 << "; ++b200_o) b200_accs[b200_o] = 0;\n";
-    else k << "    " << T << " b200_acc = 0;\n";
+    if (tiled) k << "    " << T << " b200_accs[" << E0 << "];\n#pragma unroll\n    for (int b200_o = 0; b200_o < " << E0 << "; ++b200_o) b200_accs[b200_o] = " << zero << ";\n";
+    else k << "    " << T << " b200_acc = " << zero << ";\n";
     k << "    if (b200_ok) {\n" << decomp
       << "#pragma unroll 4\n      for (unsigned long long b200_l = b200_l0 + threadIdx.y; b200_l < b200_l1; b200_l += 32ull) {\n" << sdecomp;
     if (tiled)
@@ -578,15 +608,22 @@ struct Builder {
                  << T << " b200_acc = b200_accs[" << o_sym << "];\n";
     else k << "    {\n";
     k << "      b200_part[threadIdx.y][threadIdx.x] = b200_acc;\n      __syncthreads();\n"
-      << "      if (threadIdx.y == 0 && b200_ok) {\n" << decomp << "        " << T << " b200_s = 0;\n"
-      << "        for (int b200_y = 0; b200_y < 32; ++b200_y) b200_s += b200_part[b200_y][threadIdx.x];\n";
-    if (Z > 1) k << "        atomicAdd(&" << t.ident << "[" << off << "], b200_s);\n";
-    else k << "        " << t.ident << "[" << off << "] = " << t.ident << "[" << off << "] + b200_s;\n";
+      << "      if (threadIdx.y == 0 && b200_ok) {\n" << decomp << "        " << T << " b200_s = " << zero << ";\n";
+    if (pairs) {
+      k << "        for (int b200_y = 0; b200_y < 32; ++b200_y) { b200_s.x += b200_part[b200_y][threadIdx.x].x; b200_s.y += b200_part[b200_y][threadIdx.x].y; }\n";
+      if (Z > 1) k << "        atomicAdd(&" << t.ident << "[" << off << "], b200_s.x);\n        atomicAdd(&" << t.ident << "[(" << off << ") + 1], b200_s.y);\n";
+      else k << "        " << t.ident << "[" << off << "] = " << t.ident << "[" << off << "] + b200_s.x;\n        " << t.ident << "[(" << off
+             << ") + 1] = " << t.ident << "[(" << off << ") + 1] + b200_s.y;\n";
+    } else {
+      k << "        for (int b200_y = 0; b200_y < 32; ++b200_y) b200_s += b200_part[b200_y][threadIdx.x];\n";
+      if (Z > 1) k << "        atomicAdd(&" << t.ident << "[" << off << "], b200_s);\n";
+      else k << "        " << t.ident << "[" << off << "] = " << t.ident << "[" << off << "] + b200_s;\n";
+    }
     k << "      }\n      __syncthreads();\n    }\n  }\n}\n\n";
     src << k.str();
     st.note = "par=" + std::to_string(st.par.size()) + " ser=" + std::to_string(st.ser.size()) + " serial loops split over a 32x32 block" +
               (Z > 1 ? ", " + std::to_string(Z) + " slices per output group (atomic adds)" : std::string()) +
-              (tiled ? ", outer loop of " + E0 + " kept in registers" : std::string());
+              (tiled ? ", outer loop of " + E0 + " kept in registers" : std::string()) + (pairs ? ", pairs" : std::string());
     code.stages.push_back(st);
     return true;
   }
