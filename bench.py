@@ -371,6 +371,18 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("gloo")
 
+    # run this rank on the host cores next to its GPU, so that its page-locked batches are
+    # allocated in that socket's memory (a property of this process, not of the GPU)
+    numa = None
+    if world > 1:
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            pynvml.nvmlDeviceSetCpuAffinity(pynvml.nvmlDeviceGetHandleByIndex(local))
+            numa = "cpu affinity of the rank set to its GPU's cores (NVML)"
+        except Exception as e:      # not fatal: the copies then may cross sockets
+            numa = "cpu affinity not set: %s" % (e,)
+
     from ocannl_b200 import backend as bk
     from ocannl_b200 import workloads as W
     if not os.path.exists(bk.LIB_PATH):
@@ -521,7 +533,7 @@ def main():
                                "accumulation, softmax cross-entropy; batch-sharded, no collective",
                    "rows_per_gpu": rows, "global_batch": rows * world, "parallelism": "dp%d" % world,
                    "l2": "flushed between steps (256 MiB clear outside the per-step CUDA events)",
-                   "launch": "CUDA graph replay of the routine's stages"},
+                   "launch": "CUDA graph replay of the routine's stages", "host_placement": numa},
         "e2e": {"value": rows * world * K / (ms_e2e / 1e3), "unit": "samples/s",
                 "h2d_bytes_per_step": int(x.nbytes + onehot.nbytes), "d2h_bytes_per_step": 4,
                 "ms_per_step": ms_e2e / K,
