@@ -37,6 +37,8 @@ let c_pool_free = foreign ~from:lib "b200_pool_free" (vp @-> int @-> returning i
 let c_pool_memset0 = foreign ~from:lib "b200_pool_memset0" (vp @-> int @-> size_t @-> size_t @-> returning int)
 let c_h2d = foreign ~from:lib "b200_h2d" (vp @-> int @-> size_t @-> vp @-> size_t @-> returning int)
 let c_d2h = foreign ~from:lib "b200_d2h" (vp @-> int @-> size_t @-> vp @-> size_t @-> returning int)
+(* extension: from_host copies on a second stream, ordered per pool (include/b200.h) *)
+let c_set_async_uploads = foreign ~from:lib "b200_set_async_uploads" (vp @-> int @-> returning int)
 
 let c_d2d =
   foreign ~from:lib "b200_d2d" (vp @-> int @-> size_t @-> vp @-> int @-> size_t @-> size_t @-> returning int)
