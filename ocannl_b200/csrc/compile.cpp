@@ -788,19 +788,27 @@ struct Builder {
     std::string body_text = before + open + inner + close + after;
 
     // index decomposition: the innermost parallel loop varies fastest across threads
+    // (in 32-bit arithmetic when the flattened count fits: 64-bit divisions by constants cost
+    // several times as many instructions, and pointwise kernels are made of little else)
     std::string decomp;
     {
+      const bool narrow = st.total < (1ll << 31);
+      const std::string IT = narrow ? "unsigned int" : "unsigned long long", SUF = narrow ? "u" : "ull";
       std::string rem = "b200_g";
+      if (narrow && st.par.size() > 1) {
+        decomp += "    const unsigned int b200_g32 = (unsigned int)b200_g;\n";
+        rem = "b200_g32";
+      }
       for (size_t i = st.par.size(); i-- > 0;) {
         const LoopDim& d = st.par[i];
         const bool pair_dim = pairs && i + 1 == st.par.size();   // iterations of this loop are taken two at a time
-        std::string ext = std::to_string(pair_dim ? d.extent() / 2 : d.extent()) + "ull";
+        std::string ext = std::to_string(pair_dim ? d.extent() / 2 : d.extent()) + SUF;
         std::string val = i == 0 ? rem : "(" + rem + " % " + ext + ")";
         decomp += "    const unsigned int " + d.sym + " = " + (pair_dim ? "2u * " : "") + "(unsigned int)" + val +
                   (d.from ? " + " + std::to_string(d.from) : std::string()) + ";\n";
         if (i != 0) {
           std::string nr = "b200_r" + std::to_string(i);
-          decomp += "    const unsigned long long " + nr + " = " + rem + " / " + ext + ";\n";
+          decomp += "    const " + IT + " " + nr + " = " + rem + " / " + ext + ";\n";
           rem = nr;
         }
       }
@@ -1228,18 +1236,20 @@ struct Builder {
         double neutral = op == "add" ? 0.0 : (op == "max" ? -INFINITY : INFINITY);
         out += padding + Emitter::ctype(p) + " " + name + " = " + em.constant(neutral, p) + ";\n";
         std::string lv = "b200_l" + std::to_string(e.scope_id);
-        out += padding + "for (unsigned long long " + lv + " = b200_t; " + lv + " < " + std::to_string(total) + "ull; " + lv +
+        const bool narrow = total < (1ll << 31);
+        const std::string IT = narrow ? "unsigned int" : "unsigned long long", SUF = narrow ? "u" : "ull";
+        out += padding + "for (" + IT + " " + lv + " = b200_t; " + lv + " < " + std::to_string(total) + SUF + "; " + lv +
                " += " + std::to_string(ci.width) + "u) {\n";
         std::string rem = lv;
         for (size_t i = red.size(); i-- > 0;) {
           const LoopDim& d = red[i];
-          std::string ext = std::to_string(d.extent()) + "ull";
+          std::string ext = std::to_string(d.extent()) + SUF;
           std::string val = i == 0 ? rem : "(" + rem + " % " + ext + ")";
           out += padding + "  const unsigned int " + d.sym + " = (unsigned int)" + val +
                  (d.from ? " + " + std::to_string(d.from) : std::string()) + ";\n";
           if (i != 0) {
             std::string nr = "b200_q" + std::to_string(e.scope_id) + "_" + std::to_string(i);
-            out += padding + "  const unsigned long long " + nr + " = " + rem + " / " + ext + ";\n";
+            out += padding + "  const " + IT + " " + nr + " = " + rem + " / " + ext + ";\n";
             rem = nr;
           }
         }
