@@ -53,10 +53,20 @@ void walk_scalar(const Scalar& e, const std::function<void(const Scalar&)>& fs,
 // distinct values of `s` touch disjoint slices of everything that is written.
 bool parallel_safe(const std::string& s, const Stmt& body) {
   std::map<int, int> axis_of;  // written node -> axis that carries s
+  std::map<int, Index> index_of;  // written node -> the index on that axis
   bool ok = true;
+  // an index is one-to-one in s when it is s itself or c * s + fixed with c != 0 (a padded
+  // node addressed past its margin)
+  auto one_to_one = [&](const Index& ix) {
+    return (ix.kind == Index::Iter && ix.sym == s) ||
+           (ix.kind == Index::Affine && ix.terms.size() == 1 && ix.terms[0].second == s && ix.terms[0].first != 0);
+  };
+  auto same_index = [](const Index& a, const Index& b) {
+    return a.kind == b.kind && a.sym == b.sym && a.fixed == b.fixed && a.terms == b.terms;
+  };
   auto axis_with = [&](const Indices& idcs) {
     for (size_t a = 0; a < idcs.size(); ++a)
-      if (idcs[a].kind == Index::Iter && idcs[a].sym == s) return (int)a;
+      if (one_to_one(idcs[a])) return (int)a;
     return -1;
   };
   walk_stmt(
@@ -65,6 +75,7 @@ bool parallel_safe(const std::string& s, const Stmt& body) {
         if (st.kind == Stmt::ZeroOut) ok = false;
         if (st.kind == Stmt::Set) {
           int a = axis_with(st.idcs);
+          if (st.vec_len > 0 && a >= 0 && st.idcs[a].kind == Index::Affine) a = -1;  // judged by the rule below
           if (a < 0 && st.vec_len > 0 && !st.idcs.empty()) {
             // a vector store whose last index is c * s (+ fixed) with c >= the vector length
             // writes disjoint runs for distinct s
@@ -80,8 +91,8 @@ bool parallel_safe(const std::string& s, const Stmt& body) {
           for (size_t k = 0; k < st.idcs.size(); ++k)
             if ((int)k != a && st.idcs[k].uses(s)) ok = false;
           auto it = axis_of.find(st.tn);
-          if (it == axis_of.end()) axis_of[st.tn] = a;
-          else if (it->second != a) ok = false;
+          if (it == axis_of.end()) { axis_of[st.tn] = a; index_of[st.tn] = st.idcs[a]; }
+          else if (it->second != a || !same_index(index_of[st.tn], st.idcs[a])) ok = false;
         }
       });
   if (!ok) return false;
@@ -93,13 +104,41 @@ bool parallel_safe(const std::string& s, const Stmt& body) {
           if (it == axis_of.end()) return;
           if (e.kind == Scalar::GetDyn) { ok = false; return; }
           int a = it->second;
-          if (a >= (int)e.idcs.size() || e.idcs[a].kind != Index::Iter || e.idcs[a].sym != s) ok = false;
+          if (a >= (int)e.idcs.size() || !same_index(e.idcs[a], index_of[e.tn])) ok = false;
           for (size_t k = 0; k < e.idcs.size(); ++k)
             if ((int)k != a && e.idcs[k].uses(s)) ok = false;
         }
       },
       [](const Stmt&) {});
   return ok;
+}
+
+// `t[p] := fma(a, b, t[p])` or `t[p] := t[p] + term` (either order) where neither a, b nor the
+// term read t or hold a local scope.
+bool accumulates_into_self(const Stmt& set) {
+  if (set.kind != Stmt::Set || !set.value) return false;
+  const Scalar& v = *set.value;
+  auto is_self = [&](const Scalar& e) {
+    if (e.kind != Scalar::Get || e.tn != set.tn || e.idcs.size() != set.idcs.size()) return false;
+    for (size_t i = 0; i < e.idcs.size(); ++i)
+      if (e.idcs[i].kind != set.idcs[i].kind || e.idcs[i].sym != set.idcs[i].sym || e.idcs[i].fixed != set.idcs[i].fixed ||
+          e.idcs[i].terms != set.idcs[i].terms)
+        return false;
+    return true;
+  };
+  auto plain = [&](const Scalar& e) {
+    bool ok = true;
+    walk_scalar(e, [&](const Scalar& x) {
+      if ((x.kind == Scalar::Get || x.kind == Scalar::GetDyn) && x.tn == set.tn) ok = false;
+      if (x.kind == Scalar::LocalScope) ok = false;
+    }, [](const Stmt&) {});
+    return ok;
+  };
+  if (v.kind == Scalar::Tern && v.op == "fma")
+    return is_self(*v.args[2].s) && plain(*v.args[0].s) && plain(*v.args[1].s);
+  if (v.kind == Scalar::Bin && v.op == "add")
+    return (is_self(*v.args[0].s) && plain(*v.args[1].s)) || (is_self(*v.args[1].s) && plain(*v.args[0].s));
+  return false;
 }
 
 bool body_has_set(const Stmt& s) {
@@ -463,6 +502,11 @@ struct Builder {
     int64_t ser_total = 1;
     for (auto& d : st.ser) ser_total *= d.extent();
     if (ser_total < 256) return false;
+    // the written position must not move with a serial loop (an affine output position
+    // `stride * o + k` of a convolution's input gradient does): then this is no reduction
+    for (auto& d : st.ser)
+      for (auto& ix : set.idcs)
+        if (ix.uses(d.sym)) return false;
     const Scalar& v = *set.value;
     auto is_self = [&](const Scalar& e) {
       if (e.kind != Scalar::Get || e.tn != set.tn || e.idcs.size() != set.idcs.size()) return false;
@@ -668,7 +712,33 @@ struct Builder {
     Emitter em(code.prog);
     em.large_models = opt.large_models;
 
-    if (!st.ser.empty() && st.total > 0 && opt.enable_coop && ser_split_stage(st, *body)) return false;
+    // Scatter accumulation: `t[.., c * o + k, ..] := t[same] + term` where the written position
+    // moves with loops that therefore cannot run in parallel (the input gradient of a
+    // convolution).  Those loops are spread over threads all the same: a thread sums over the
+    // loops that do not move the position and adds its partial sum with one atomic add.
+    bool scatter = false;
+    if (opt.enable_coop && !st.ser.empty() && st.total > 0 && body->kind == Stmt::Set && body->vec_len == 0 &&
+        accumulates_into_self(*body)) {
+      const Tnode& t = code.prog.tn(body->tn);
+      std::vector<LoopDim> spread, kept;
+      for (auto& d : nest) {
+        bool in_par = false, moves = false;
+        for (auto& q : st.par) in_par = in_par || q.sym == d.sym;
+        for (auto& ix : body->idcs) moves = moves || ix.uses(d.sym);
+        (in_par || moves ? spread : kept).push_back(d);
+      }
+      int64_t total = 1;
+      for (auto& d : spread) total *= d.extent();
+      if ((t.prec == Prec::Single || t.prec == Prec::Double) && t.mode != Mode::Virtual && spread.size() > st.par.size() &&
+          total >= 4096) {
+        scatter = true;
+        st.par = spread;
+        st.ser = kept;
+        st.total = total;
+      }
+    }
+
+    if (!scatter && !st.ser.empty() && st.total > 0 && opt.enable_coop && ser_split_stage(st, *body)) return false;
 
     CoopInfo ci;
     if (st.ser.empty() && st.total > 0) ci = find_coop(*body, st.total);
@@ -686,7 +756,7 @@ struct Builder {
     // axis of the written node, and everything in it is fp32, bf16 or half, a thread takes TWO
     // neighbouring iterations of that loop: 4- and 8-byte accesses, packed 16-bit arithmetic.
     bool pairs = false;
-    if (opt.enable_pairs && ci.sym.empty() && body->kind == Stmt::Set && body->vec_len == 0 && !st.par.empty() && st.total > 0) {
+    if (opt.enable_pairs && !scatter && ci.sym.empty() && body->kind == Stmt::Set && body->vec_len == 0 && !st.par.empty() && st.total > 0) {
       const Stmt& set = *body;
       const Tnode& t = code.prog.tn(set.tn);
       const LoopDim& p = st.par.back();
@@ -709,7 +779,15 @@ struct Builder {
     // t[p] in a register across those loops (one load, or none when the node is known to be zero,
     // and one store) instead of a read-modify-write of memory per iteration.
     std::string before, after;
-    if (ci.sym.empty() && !st.ser.empty() && body->kind == Stmt::Set && body->vec_len == 0) {
+    if (scatter) {
+      const Stmt& set = *body;
+      const Tnode& t = code.prog.tn(set.tn);
+      em.used_nodes.insert(set.tn);
+      before = std::string("    ") + Emitter::ctype(t.prec) + " b200_self = 0;\n";
+      after = "    atomicAdd(&" + t.ident + "[" + em.offset(set.idcs, t.dims) + "], b200_self);\n";
+      em.forwarded[set.tn] = {set.idcs, "b200_self"};
+      em.set_redirect[set.tn] = {set.idcs, "b200_self"};
+    } else if (ci.sym.empty() && !st.ser.empty() && body->kind == Stmt::Set && body->vec_len == 0) {
       const Stmt& set = *body;
       const Tnode& t = code.prog.tn(set.tn);
       bool ok = t.mode != Mode::Virtual && t.prec != Prec::Uint4x32;
@@ -825,20 +903,22 @@ struct Builder {
     for (auto& d : st.ser) ser_work *= std::max<int64_t>(1, d.extent());
     pc.fusable = opt.enable_fuse && st.total > 0 && (st.coop == 0 || st.coop == 32) &&
                  st.total * std::max(1, st.coop) <= 16384 && ser_work <= 4096;
-    if (opt.enable_fuse && st.coop == 0 && st.total > 0 && !st.par.empty() && st.par[0].from == 0 && !(pairs && st.par.size() == 1)) {
+    if (scatter) pc.fusable = false;
+    if (opt.enable_fuse && !scatter && st.coop == 0 && st.total > 0 && !st.par.empty() && st.par[0].from == 0 && !(pairs && st.par.size() == 1)) {
       pc.body = body;
       pc.row_sym = st.par[0].sym;
       pc.rows = st.par[0].extent();
       pc.per_row = st.total / pc.rows * ser_work;
     }
-    pc.any_body = body;
+    if (!scatter) pc.any_body = body;
     pc.par = st.par;
     pc.coop = st.coop;
     pc.pairs = pairs;
     pc.ser_work = ser_work;
     std::ostringstream note;
     note << "par=" << st.par.size() << " ser=" << st.ser.size()
-         << (st.coop > 32 ? " block-per-element" : st.coop ? " warp-per-element" : "") << (pairs ? " pairs" : "");
+         << (st.coop > 32 ? " block-per-element" : st.coop ? " warp-per-element" : "") << (pairs ? " pairs" : "")
+         << (scatter ? " scatter accumulation (atomic adds)" : "");
     st.note = note.str();
     pieces[code.stages.size()] = pc;
     code.stages.push_back(st);

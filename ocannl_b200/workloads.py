@@ -23,7 +23,7 @@ from typing import Callable, Dict, List, Sequence, Tuple
 
 import numpy as np
 
-from .low_level import (Comment, Const, EmbedIndex, For, Get, GetDynamic, GetLocal, LocalScope, Routine, Scalar, Seq,
+from .low_level import (Affine, Comment, Const, EmbedIndex, For, Get, GetDynamic, GetLocal, LocalScope, Routine, Scalar, Seq,
                         Set, SetLocal, Tnode, Unop, ZeroOut, binop, fma, loops, un, where)
 
 NEG_INF = float("-inf")
@@ -693,3 +693,79 @@ def mlp_sgd(dims=(784, 1024, 1024, 10), wprec="bfloat16") -> Routine:
 
 
 MLP_PARAM_NAMES = ("w1", "b1", "w2", "b2", "w_out")
+
+
+# ------------------------------------------------------------------ convolution as a contraction with affine indices
+def conv2d_update(batch=4, size=16, cin=8, cout=16, kernel=3, stride=1, prec="single") -> Routine:
+    """A `same`-padded (stride 1) or `valid` strided 2-d convolution layer with bias and relu,
+    its squared-error loss and the gradients of kernel, bias and input, in the forms the
+    reference lowers `conv2d` to (lib/nn_blocks.ml:418-428): the input position of an output
+    position is the affine index `stride * oh + kh`, a
+    padded node carries its margins in its dimensions, accesses to it are shifted by the left
+    margin (`apply_padding_offset`, arrayjit/lib/assignments.ml:202-219) and the margins are reset by loops of constant assignments before the node is filled
+    (`reset_padding_regions`, assignments.ml:281-297)."""
+    pad = (kernel - 1) // 2 if stride == 1 else 0
+    out = size if stride == 1 else (size - kernel) // stride + 1
+    padded = size + 2 * pad
+    r = Routine("conv2d_update_b%d_s%d_c%d_%d_k%d_st%d_%s" % (batch, size, cin, cout, kernel, stride, prec))
+    x = r.tn("x", prec, [batch, size, size, cin], read_only=True)
+    xp = r.tn("x_padded", prec, [batch, padded, padded, cin])
+    kw_ = r.tn("kernel", prec, [cout, kernel, kernel, cin], read_only=True)
+    bias = r.tn("bias", prec, [cout], read_only=True)
+    y = r.tn("y", prec, [batch, out, out, cout])
+    target = r.tn("target", prec, [batch, out, out, cout], read_only=True)
+    loss = r.tn("loss", "single", [1])
+    body: List = [Comment("conv fwd")]
+    if pad:
+        body.append(Comment("reset padding margins of x_padded to 0"))
+        ib, ih, iw, ic = r.syms(4)
+        for lo, hi in ((0, pad - 1), (padded - pad, padded - 1)):
+            body.append(For(ib, 0, batch - 1, For(ih, lo, hi, For(iw, 0, padded - 1, For(ic, 0, cin - 1,
+                        Set(xp, (ib, ih, iw, ic), Const(0.0, prec)))))))
+            ib, ih, iw, ic = r.syms(4)
+            body.append(For(ib, 0, batch - 1, For(ih, pad, padded - pad - 1, For(iw, lo, hi, For(ic, 0, cin - 1,
+                        Set(xp, (ib, ih, iw, ic), Const(0.0, prec)))))))
+            ib, ih, iw, ic = r.syms(4)
+    ib, ih, iw, ic = r.syms(4)
+    body.append(loops([(ib, batch), (ih, size), (iw, size), (ic, cin)],
+                      Set(xp, (ib, Affine(((1, ih),), pad), Affine(((1, iw),), pad), ic), x[ib, ih, iw, ic])))
+    ib, oh, ow, co, kh, kw, ci = r.syms(7)
+    src = lambda: xp[ib, Affine(((stride, oh), (1, kh))), Affine(((stride, ow), (1, kw))), ci]
+    body.append(loops([(ib, batch), (oh, out), (ow, out), (co, cout)], Set(y, (ib, oh, ow, co), un("relu", bias[co] + reduce_scope(
+        r, "n_conv", "single", [(kh, kernel), (kw, kernel), (ci, cin)], lambda: (kw_[co, kh, kw, ci], src()),
+        orig=(ib, oh, ow, co))))))
+    ib, oh, ow, co = r.syms(4)
+    diff = lambda: y[ib, oh, ow, co] - target[ib, oh, ow, co]
+    body.append(Set(loss, (0,), reduce_scope(r, "n_sq", "single", [(ib, batch), (oh, out), (ow, out), (co, cout)],
+                                            lambda: (diff(), diff())) / float(batch)))
+    body.append(Comment("zero grads and backprop"))
+    gk = r.tn("kernel_grad", "single", kw_.dims)
+    gb = r.tn("bias_grad", "single", bias.dims)
+    gx = r.tn("x_padded_grad", "single", xp.dims)
+    dz = r.tn("z_grad", prec, y.dims)
+    for g in (gk, gb, gx):
+        body.append(ZeroOut(g))
+    ib, oh, ow, co = r.syms(4)
+    body.append(loops([(ib, batch), (oh, out), (ow, out), (co, cout)], Set(dz, (ib, oh, ow, co), binop(
+        "relu_gate", y[ib, oh, ow, co], (y[ib, oh, ow, co] - target[ib, oh, ow, co]) * (2.0 / batch)))))
+    ib, oh, ow, co = r.syms(4)
+    body.append(loops([(ib, batch), (oh, out), (ow, out), (co, cout)], Set(gb, (co,), gb[co] + dz[ib, oh, ow, co])))
+    ib, oh, ow, co, kh, kw, ci = r.syms(7)
+    nest = [(ib, batch), (oh, out), (ow, out), (co, cout), (kh, kernel), (kw, kernel), (ci, cin)]
+    body.append(loops(nest, Set(gk, (co, kh, kw, ci), fma(dz[ib, oh, ow, co], src(), gk[co, kh, kw, ci]))))
+    ib, oh, ow, co, kh, kw, ci = r.syms(7)
+    nest = [(ib, batch), (oh, out), (ow, out), (co, cout), (kh, kernel), (kw, kernel), (ci, cin)]
+    at = (ib, Affine(((stride, oh), (1, kh))), Affine(((stride, ow), (1, kw))), ci)
+    body.append(loops(nest, Set(gx, at, fma(kw_[co, kh, kw, ci], dz[ib, oh, ow, co], Get(gx, at)))))
+    body.append(Comment("end"))
+    r.body = Seq(body)
+    return r
+
+
+def conv2d_inputs(batch=4, size=16, cin=8, cout=16, kernel=3, stride=1, prec="single"):
+    out = size if stride == 1 else (size - kernel) // stride + 1
+    g = np.random.default_rng(31)
+    return {"x": store(prec, g.standard_normal((batch, size, size, cin), np.float32)),
+            "kernel": store(prec, (g.standard_normal((cout, kernel, kernel, cin), np.float32) / math.sqrt(kernel * kernel * cin)).astype(np.float32)),
+            "bias": store(prec, 0.1 * g.standard_normal(cout).astype(np.float32)),
+            "target": store(prec, g.standard_normal((batch, out, out, cout), np.float32))}

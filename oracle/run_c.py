@@ -8,6 +8,15 @@ calls the routine with numpy buffers in the sorted-parameter order of
 `Cc_backend.link_compiled` builds its call (cc_backend.ml:378-443).
 Runs on one host thread, as the reference's `sync_cc` does
 (arrayjit/lib/schedulers.ml:284).
+
+One flag is added to that command line: `-fno-tree-loop-if-convert`.  gcc 13.3 with
+`-O3 -march=native` on an AVX-512 host (preferred vector width 256) miscompiles the
+vectorised form of `(y[i] > 0.0 ? (y[i] - t[i]) * (float)(0.5) : 0.0)` — the C spelling of a
+relu gate over single-precision nodes, a float value selected in a double comparison — and
+reads zeros or stale lanes in place of `t` for the upper half of each 16-element row; the
+same text gives the right values at -O0, -O2, -O3 without -march, and with if-conversion or
+loop vectorisation off.  A checker must not depend on that, so if-conversion is off here;
+the contraction loops, which carry the run time, are not affected by it.
 """
 from __future__ import annotations
 
@@ -37,15 +46,15 @@ class OracleRoutine:
         self.em = Emitter(ir_text)
         self.src = self.em.source()
         os.makedirs(_BUILD, exist_ok=True)
-        tag = hashlib.sha256(self.src.encode()).hexdigest()[:20]
+        tag = hashlib.sha256((self.src + "|no-if-convert").encode()).hexdigest()[:20]
         self.c_path = os.path.join(_BUILD, "%s_%s.c" % (self.em.name, tag))
         self.so_path = self.c_path[:-2] + ".so"
         if not os.path.exists(self.so_path):
             with open(self.c_path, "w") as f:
                 f.write(self.src)
             tmp = self.so_path + ".tmp%d" % os.getpid()
-            subprocess.run([cc, self.c_path, "-O3", "-march=native", "-o", tmp, "-shared",
-                            "-fPIC", "-I", _HERE, "-lm"], check=True)
+            subprocess.run([cc, self.c_path, "-O3", "-march=native", "-fno-tree-loop-if-convert", "-o", tmp,
+                            "-shared", "-fPIC", "-I", _HERE, "-lm"], check=True)
             os.replace(tmp, self.so_path)
         self.lib = ctypes.CDLL(self.so_path)
         self.fn = getattr(self.lib, self.em.name)

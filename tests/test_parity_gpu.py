@@ -329,3 +329,31 @@ def test_mlp_train_update_and_sgd(device, rows, options):
     want2 = run_oracle(sgd, sin)
     got2, _ = run_device(device, sgd, sin)
     compare(sgd, got2, want2, rtol=1e-2, atol=1e-6)
+
+
+@pytest.mark.parametrize("stride,prec", [(1, "single"), (2, "single"), (1, "bfloat16")])
+@pytest.mark.parametrize("options", [None, "coop=0 fuse=0"])
+def test_convolution_layer_with_gradients(device, stride, prec, options):
+    """Convolution as a contraction over affine positions (`stride * oh + kh`), with a padded
+    input node (margins reset by constant loops, the copy shifted by the margin), bias, relu,
+    a squared-error loss and the kernel / bias / input gradients.  The input gradient is an
+    accumulation whose written position moves with the output and kernel loops: with the
+    default options it is spread over threads with atomic adds, with `coop=0` only the batch
+    and channel loops are parallel.  fp32 throughout (bf16 nodes: products and sums in float,
+    results rounded): accumulation order differs, rel 1e-4 against each node's scale."""
+    ir = W.conv2d_update(stride=stride, prec=prec)
+    inputs = W.conv2d_inputs(stride=stride, prec=prec)
+    want = run_oracle(ir, inputs)
+    got, info = run_device(device, ir, inputs, options=options)
+    notes = [s["note"] or "" for s in info["stages"]]
+    assert any("scatter accumulation" in n for n in notes) == (options is None), notes
+    lowp = prec != "single"
+    for name in ("x_padded", "y", "loss", "z_grad", "bias_grad", "kernel_grad", "x_padded_grad"):
+        w = W.load(prec, want[name]) if want[name].dtype == np.uint16 else want[name]
+        g = W.load(prec, got[name]) if got[name].dtype == np.uint16 else got[name]
+        scale = float(np.abs(w).max())
+        np.testing.assert_allclose(g, w, rtol=2e-2 if lowp else 1e-4, atol=(2e-2 if lowp else 1e-5) * scale, err_msg=name)
+    if stride == 1:     # the margins of the padded node hold zeros, the inside the input
+        xp = got["x_padded"]
+        assert not xp[:, 0].any() and not xp[:, -1].any() and not xp[:, :, 0].any() and not xp[:, :, -1].any()
+        assert np.array_equal(xp[:, 1:-1, 1:-1], inputs["x"])

@@ -57,3 +57,21 @@ def test_random_number_routine_plan():
     from tests.golden.golden_routines import n3_fwd
     st = _plan(n3_fwd("single", 100000, "light"), "fuse=0")
     assert all(s["kind"] == "generic" and s["total"] == 100000 for s in st), st     # every loop parallel, the vector store too
+
+
+def test_convolution_plan_affine_positions():
+    """A convolution layer with its gradients (affine positions `stride * o + k`, a padded node
+    written past its margin): no stage is taken for a tensor-core contraction (affine operands
+    are not strided tiles), the shifted copy into the padded node runs in parallel, and the
+    input gradient, whose written position moves with four serial loops, is spread over threads
+    with atomic adds instead of running as 32 threads."""
+    st = _plan(W.conv2d_update(stride=1), "fuse=0")
+    notes = [s["note"] or "" for s in st]
+    assert all(s["kind"] != "gemm" for s in st), notes
+    copy = [s for s in st if s["kind"] == "generic" and s["total"] in (4 * 16 * 16 * 8, 4 * 16 * 16 * 4)]
+    assert copy, st
+    scatter = [s for s in st if "scatter accumulation" in (s["note"] or "")]
+    assert len(scatter) == 1 and scatter[0]["total"] == 4 * 16 * 16 * 3 * 3 * 8, notes
+    assert any("slices per output group" in n for n in notes), notes      # kernel and bias gradients
+    off = [s["note"] or "" for s in _plan(W.conv2d_update(stride=1), "coop=0")]
+    assert not any("scatter" in n for n in off), off
