@@ -766,7 +766,7 @@ struct Builder {
         if (set.idcs[a].uses(p.sym)) ok = false;
       // reads of the written node only at the written position (they become the promoted register)
       walk_scalar(*set.value, [&](const Scalar& e) {
-        if ((e.kind == Scalar::Get || e.kind == Scalar::GetDyn) && e.tn == set.tn && st.ser.empty()) ok = false;
+        if (e.kind == Scalar::GetDyn && e.tn == set.tn) ok = false;
       }, [](const Stmt&) {});
       if (ok && em.pair_supported(*set.value)) {
         pairs = true;
@@ -787,7 +787,7 @@ struct Builder {
       after = "    atomicAdd(&" + t.ident + "[" + em.offset(set.idcs, t.dims) + "], b200_self);\n";
       em.forwarded[set.tn] = {set.idcs, "b200_self"};
       em.set_redirect[set.tn] = {set.idcs, "b200_self"};
-    } else if (ci.sym.empty() && !st.ser.empty() && body->kind == Stmt::Set && body->vec_len == 0) {
+    } else if (ci.sym.empty() && (pairs || !st.ser.empty()) && body->kind == Stmt::Set && body->vec_len == 0) {
       const Stmt& set = *body;
       const Tnode& t = code.prog.tn(set.tn);
       bool ok = t.mode != Mode::Virtual && t.prec != Prec::Uint4x32;
@@ -1190,6 +1190,53 @@ struct Builder {
     return f;
   }
 
+  // Pointwise chain.  Consecutive stages over the SAME parallel loops (no serial loops, no
+  // cooperative reductions) that hand data to one another only at one position of those loops
+  // run as one kernel: a thread executes the stages one after the other for its element (or
+  // pair).  What one stage stores the next reads back from L1 / L2 instead of DRAM, and a
+  // momentum SGD step (delta, momentum, Nesterov correction, parameter) is one launch per
+  // parameter instead of four.
+  bool pointwise_member(size_t i, const Piece* like) {
+    auto it = pieces.find(i);
+    if (it == pieces.end() || !it->second.any_body) return false;
+    const Piece& pc = it->second;
+    if (pc.coop != 0 || pc.ser_work != 1 || pc.par.empty() || code.stages[i].total <= 0) return false;
+    for (auto& d : pc.par)
+      if (d.from != 0) return false;
+    if (like) {
+      if (pc.par.size() != like->par.size() || pc.pairs != like->pairs) return false;
+      for (size_t q = 0; q < pc.par.size(); ++q)
+        if (pc.par[q].extent() != like->par[q].extent()) return false;
+    }
+    return true;
+  }
+
+  Stage emit_pointwise_chain(const std::vector<size_t>& run) {
+    Stage f = code.stages[run.front()];
+    Emitter em(code.prog);
+    std::set<int> written;
+    std::string text;
+    for (size_t i : run) {
+      const Piece& pc = pieces[i];
+      f.min_align = std::max(f.min_align, code.stages[i].min_align);
+      em.used_nodes.insert(pc.used.begin(), pc.used.end());
+      written.insert(pc.written.begin(), pc.written.end());
+      em.uses_merge |= pc.uses_merge;
+      text += "    {\n" + pc.decomp + pc.body_text + "    }\n";
+    }
+    std::string statics = static_prologue(text, em, 2);
+    std::ostringstream k_src;
+    k_src << "extern \"C\" __global__ void __launch_bounds__(" << f.block << ") " << f.kernel << "(";
+    emit_params(k_src, f, em, written);
+    k_src << ") {\n" << kGridEntry << statics
+          << "  for (unsigned long long b200_g = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; b200_g < "
+          << f.total << "ull; b200_g += (unsigned long long)gridDim.x * blockDim.x) {\n"
+          << text << "  }\n}\n\n";
+    src << k_src.str();
+    f.note = "pointwise chain of " + std::to_string(run.size()) + " stages" + (pieces[run.front()].pairs ? ", pairs" : "");
+    return f;
+  }
+
   // Decides which stages share a launch and writes the kernels' text.
   void emit_kernels() {
     {
@@ -1264,6 +1311,21 @@ struct Builder {
         }
         if (run.size() >= 2 && !all_small) {
           out.push_back(emit_rows(run));
+          i = run.back() + 1;
+          continue;
+        }
+      }
+      if (opt.enable_fuse && !fusable(i) && pointwise_member(i, nullptr)) {
+        const Piece& first = pieces[i];
+        std::vector<size_t> run = {i};
+        size_t j = i + 1;
+        while (j < code.stages.size() && run.size() < 8 && pointwise_member(j, &first)) {
+          run.push_back(j);
+          if (!rows_independent_prefix(run, first.par.size())) { run.pop_back(); break; }
+          ++j;
+        }
+        if (run.size() >= 2) {
+          out.push_back(emit_pointwise_chain(run));
           i = run.back() + 1;
           continue;
         }

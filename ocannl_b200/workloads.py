@@ -671,9 +671,15 @@ def mlp_train_update(rows=8192, dims=(784, 1024, 1024, 10), wprec="bfloat16") ->
     return r
 
 
-def mlp_sgd(dims=(784, 1024, 1024, 10), wprec="bfloat16") -> Routine:
-    """`Train.sgd_update` without momentum or weight decay: p =- learning_rate * p.grad per parameter."""
-    r = Routine("mlp_sgd")
+def mlp_sgd(dims=(784, 1024, 1024, 10), wprec="bfloat16", momentum=0.0, weight_decay=0.0, nesterov=False) -> Routine:
+    """`Train.sgd_update` (lib/train.ml:76-91) per parameter: `sgd_delta =: p.grad + weight_decay * p`;
+    with momentum `sgd_momentum =: momentum * sgd_momentum + sgd_delta` and then
+    `sgd_delta =+ momentum * sgd_momentum` (Nesterov) or `sgd_delta =: sgd_momentum`; last
+    `p =- learning_rate * sgd_delta`.  Without momentum `sgd_delta` is read once and is inlined
+    into the parameter's assignment; with momentum it and `sgd_momentum` are fp32 nodes and the
+    three or four assignments are separate loop nests over the parameter's axes."""
+    tag = "" if momentum == 0.0 and weight_decay == 0.0 else "_m%g_wd%g%s" % (momentum, weight_decay, "_nesterov" if nesterov else "")
+    r = Routine("mlp_sgd" + tag.replace(".", "p").replace("-", "n"))
     lr = r.tn("learning_rate", "single", [1], read_only=True)
     n_layers = len(dims) - 1
     body: List = [Comment("sgd_update")]
@@ -684,9 +690,25 @@ def mlp_sgd(dims=(784, 1024, 1024, 10), wprec="bfloat16") -> Routine:
         for name, d in names:
             p = r.tn(name, wprec, d)
             g = r.tn(name + "_grad", "single", d, read_only=True)
-            syms = r.syms(len(d))
-            idx = tuple(syms)
-            body.append(loops(list(zip(syms, d)), Set(p, idx, Get(p, idx) - lr[0] * Get(g, idx))))
+            nest = lambda: (lambda syms: (list(zip(syms, d)), tuple(syms)))(r.syms(len(d)))
+            delta = lambda idx: (Get(g, idx) + float(weight_decay) * Get(p, idx)) if weight_decay != 0.0 else Get(g, idx)
+            if momentum > 0.0:
+                sd = r.tn(name + "_sgd_delta", "single", d)
+                sm = r.tn(name + "_sgd_momentum", "single", d)
+                lp, idx = nest()
+                body.append(loops(lp, Set(sd, idx, delta(idx))))
+                lp, idx = nest()
+                body.append(loops(lp, Set(sm, idx, float(momentum) * Get(sm, idx) + Get(sd, idx))))
+                lp, idx = nest()
+                if nesterov:
+                    body.append(loops(lp, Set(sd, idx, Get(sd, idx) + float(momentum) * Get(sm, idx))))
+                else:
+                    body.append(loops(lp, Set(sd, idx, Get(sm, idx))))
+                lp, idx = nest()
+                body.append(loops(lp, Set(p, idx, Get(p, idx) - lr[0] * Get(sd, idx))))
+            else:
+                lp, idx = nest()
+                body.append(loops(lp, Set(p, idx, Get(p, idx) - lr[0] * delta(idx))))
     body.append(Comment("end"))
     r.body = Seq(body)
     return r

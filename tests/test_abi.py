@@ -41,9 +41,10 @@ def test_compile_is_device_independent(built_lib):
     _nvrtc_or_skip()
     fused = bk.Code(W.moons_train_step())
     st = fused.info()["stages"]
-    # ~30 tiny stages share ONE single-block launch
+    # ~30 tiny stages share ONE single-block launch (a few zero_outs are gone: the first
+    # accumulation into a node known to be zero starts from the constant instead)
     assert len(st) == 1 and st[0]["kind"] == "generic" and "fused" in st[0]["note"], st
-    assert fused.source().count("__syncthreads()") >= 30
+    assert fused.source().count("__syncthreads()") >= 25
     fused.free()
     code = bk.Code(W.moons_train_step(), options="fuse=0")
     info = code.info()

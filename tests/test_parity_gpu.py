@@ -357,3 +357,34 @@ def test_convolution_layer_with_gradients(device, stride, prec, options):
         xp = got["x_padded"]
         assert not xp[:, 0].any() and not xp[:, -1].any() and not xp[:, :, 0].any() and not xp[:, :, -1].any()
         assert np.array_equal(xp[:, 1:-1, 1:-1], inputs["x"])
+
+
+@pytest.mark.parametrize("kwargs", [dict(momentum=0.9, weight_decay=1e-4, nesterov=True), dict(momentum=0.9),
+                                    dict(weight_decay=1e-2)])
+@pytest.mark.parametrize("options", [None, "fuse=0 pairs=0"])
+def test_sgd_with_momentum_and_weight_decay(device, kwargs, options):
+    """`Train.sgd_one` (lib/train.ml:76-88) with momentum, Nesterov correction and weight decay on
+    the MLP's parameters (bf16) with fp32 gradients, two steps so that the momentum node
+    carries state.  Pointwise fp32 / bf16 arithmetic in the reference's order: the fp32 state
+    nodes agree to rel 1e-6, the bf16 parameters bit for bit up to one unit in the last place
+    where the rounded product lr * delta straddles a rounding boundary."""
+    dims = (64, 48, 32, 10)
+    ir = W.mlp_sgd(dims=dims, **kwargs)
+    g = np.random.default_rng(41)
+    inputs = {"learning_rate": np.float32([0.05])}
+    for t in ir.params():
+        if t.ident.endswith("_grad"):
+            inputs[t.ident] = g.standard_normal(t.dims).astype(np.float32)
+        elif t.ident.endswith(("_sgd_delta", "_sgd_momentum")):
+            inputs[t.ident] = np.zeros(t.dims, np.float32)
+        elif t.ident != "learning_rate":
+            inputs[t.ident] = W.store("bfloat16", g.standard_normal(t.dims).astype(np.float32))
+    want = run_oracle(ir, inputs, statics=({}, {}))
+    got, info = run_device(device, ir, inputs, statics=({}, {}), options=options)
+    for t in ir.params():
+        w, d = want[t.ident], got[t.ident]
+        if t.prec == "bfloat16":
+            assert np.abs(w.astype(np.int32) - d.astype(np.int32)).max() <= 1, t.ident
+            assert (w != d).mean() < 0.01, t.ident
+        else:
+            np.testing.assert_allclose(d, w, rtol=1e-6, atol=1e-7, err_msg=t.ident)

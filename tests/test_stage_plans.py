@@ -75,3 +75,13 @@ def test_convolution_plan_affine_positions():
     assert any("slices per output group" in n for n in notes), notes      # kernel and bias gradients
     off = [s["note"] or "" for s in _plan(W.conv2d_update(stride=1), "coop=0")]
     assert not any("scatter" in n for n in off), off
+
+
+def test_momentum_sgd_is_one_launch_per_parameter():
+    """delta, momentum, Nesterov correction and the parameter update of one parameter share their
+    loops and meet only at one position: a pointwise chain (one kernel, pair form)."""
+    st = _plan(W.mlp_sgd(momentum=0.9, weight_decay=1e-4, nesterov=True))
+    notes = [s["note"] or "" for s in st]
+    assert sum("pointwise chain of 4 stages, pairs" in n for n in notes) == 2, notes   # w1, w2; the small ones share a block
+    assert len(st) == 4, notes
+    assert len(_plan(W.mlp_sgd(momentum=0.9, weight_decay=1e-4, nesterov=True), "fuse=0")) == 5 * 4
