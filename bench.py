@@ -34,6 +34,17 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+# stdout carries the one JSON line and nothing else: when the environment asks NCCL for
+# diagnostics (NCCL_DEBUG), they go to stderr instead of NCCL's default, stdout
+if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+    # this level prints one line, "NCCL version ...", on stdout at the first communicator
+    del os.environ["NCCL_DEBUG"]
+    _NCCL_VERSION_WANTED = True
+else:
+    _NCCL_VERSION_WANTED = False
+    if os.environ.get("NCCL_DEBUG") and not os.environ.get("NCCL_DEBUG_FILE"):
+        os.environ["NCCL_DEBUG_FILE"] = "/dev/stderr"
+
 METRIC = "forward samples/sec"
 DIMS = (784, 1024, 1024, 10)
 
@@ -370,6 +381,9 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("gloo")
+        if _NCCL_VERSION_WANTED and rank == 0:
+            import torch
+            print("NCCL version %s" % (".".join(str(v) for v in torch.cuda.nccl.version()),), file=sys.stderr)
 
     # run this rank on the host cores next to its GPU, so that its page-locked batches are
     # allocated in that socket's memory (a property of this process, not of the GPU)
