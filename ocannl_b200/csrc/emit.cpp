@@ -538,6 +538,9 @@ std::string Emitter::stmt(const Stmt& s, int ind) {
       return out;
     }
     case Stmt::For: {
+      // a loop of no iterations: the counter is unsigned, so `i <= -1` would never be false
+      if (s.to < s.from) return pad(ind) + "/* empty loop " + s.index + " */\n";
+      if (s.from < 0) throw Error(-4, "b200ir: loop '" + s.index + "' starts below zero");
       const char* it = large_models ? "unsigned long long" : "unsigned int";
       std::string lo = std::to_string(s.from), hi = std::to_string(s.to);
       std::string head;

@@ -388,3 +388,57 @@ def test_sgd_with_momentum_and_weight_decay(device, kwargs, options):
             assert (w != d).mean() < 0.01, t.ident
         else:
             np.testing.assert_allclose(d, w, rtol=1e-6, atol=1e-7, err_msg=t.ident)
+
+
+@pytest.mark.parametrize("options", [None, "fuse=0 pairs=0 coop=0"])
+def test_edge_shapes_empty_loops_and_single_elements(device, options):
+    """Edge cases of the loop forms: extents of one with fixed indices, odd extents (no pair
+    form, ragged last block), a loop that starts past zero, an assignment outside any loop and a
+    reduction over a single element.  Integer and fp32 nodes bit for bit, bf16 bit for bit (one
+    operation per element)."""
+    from ocannl_b200.low_level import Comment, Const, For, Get, Routine, Seq, Set, binop, loops
+    r = Routine("edge_shapes")
+    a = r.tn("a", "single", [7, 13], read_only=True)
+    h = r.tn("h", "bfloat16", [7, 13], read_only=True)
+    out = r.tn("out", "single", [7, 13])
+    outh = r.tn("outh", "bfloat16", [7, 13])
+    untouched = r.tn("untouched", "single", [5])
+    one = r.tn("one", "single", [1, 1])
+    tail = r.tn("tail", "int32", [9])
+    rowsum = r.tn("rowsum", "single", [7])
+    i, j, k, l, m, n, p, q = r.syms(8)
+    body = [Comment("edge fwd"),
+            loops([(j, 7), (k, 13)], Set(out, (j, k), a[j, k] * 2.0 + a[j, 12 - 12])),       # odd extents, a fixed index
+            loops([(l, 7), (m, 13)], Set(outh, (l, m), h[l, m] + h[l, 0])),
+            Set(one, (0, 0), a[6, 12] - 1.0),                                                 # no loop at all
+            For(n, 4, 8, Set(tail, (n,), Const(7.0, "int32"))),                               # starts past zero
+            loops([(p, 7)], Set(rowsum, (p,), W.reduce_scope(r, "n_rs", "single", [(q, 1)], lambda: a[p, q], op="add", orig=(p,)))),
+            Comment("end")]
+    r.body = Seq(body)
+    g = np.random.default_rng(51)
+    inputs = {"a": g.standard_normal((7, 13)).astype(np.float32),
+              "h": W.store("bfloat16", g.standard_normal((7, 13)).astype(np.float32)),
+              "untouched": np.full(5, -1.0, np.float32), "tail": np.arange(9, dtype=np.int32)}
+    want = run_oracle(r, inputs)
+    got, info = run_device(device, r, inputs, options=options)
+    for name in ("out", "outh", "untouched", "one", "tail", "rowsum"):
+        assert np.array_equal(got[name], want[name]), (name, got[name], want[name])
+    assert np.array_equal(got["untouched"], inputs["untouched"]) and got["tail"].tolist() == [0, 1, 2, 3, 7, 7, 7, 7, 7]
+
+
+def test_routine_without_statements(device):
+    """A routine whose body holds only comments compiles to no stages and runs as a no-op; so
+    does a loop with `to_ < from_` (device only: the reference's C text compares an unsigned
+    counter with the bound, so it has no zero-iteration loops and never emits one)."""
+    from ocannl_b200.low_level import Comment, Const, For, Routine, Seq, Set
+    r = Routine("nothing_to_do")
+    keep = r.tn("keep", "single", [4])
+    r.body = Seq([Comment("nothing fwd"), Comment("end")])
+    got, info = run_device(device, r, {"keep": np.float32([1, 2, 3, 4])})
+    assert info["stages"] == [] and got["keep"].tolist() == [1, 2, 3, 4]
+    r = Routine("empty_loop")
+    keep = r.tn("keep", "single", [4])
+    (i,) = r.syms(1)
+    r.body = Seq([Comment("empty fwd"), For(i, 0, -1, Set(keep, (i,), Const(9.0, "single"))), Comment("end")])
+    got, info = run_device(device, r, {"keep": np.float32([1, 2, 3, 4])})
+    assert got["keep"].tolist() == [1, 2, 3, 4], (got, info)
