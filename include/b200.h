@@ -105,8 +105,14 @@ typedef struct {
   uint64_t offset;
 } b200_binding;
 
+/* Bindings need only be aligned to the node's element size, which is all the reference's
+ * allocator promises (plan_pool_segments, arrayjit/lib/backends.ml:22-51; an offset that is not a
+ * multiple of the element size is B200_E_INVALID).  Stages whose compiled form wants more (8-byte
+ * pairs, 16-byte TMA operand bases) are re-planned for the addresses at hand; b200_routine_info
+ * reports the plan that runs. */
 int b200_link(b200_dev* dev, b200_code* code, const b200_binding* bindings, int n_bindings,
               b200_routine** out);
+int b200_routine_info(b200_routine* r, char* json, size_t cap);   /* like b200_code_info, for the linked plan */
 /* Runs the routine once on the device stream.  static_idx has one value per static symbol
  * of the routine, in declaration order; a negative or out-of-range value is B200_E_USER
  * (cuda: arrayjit/lib/cuda_backend.ml:1015-1030). */
@@ -140,7 +146,9 @@ int b200_comm_free(b200_comm* comm);
  *      loop that cannot afford cudaMalloc's implicit synchronisation, or under a memory budget
  *      that was handed out up front).  Writes sum(in[0..count)) as one float at the output
  *      location, in stream order on the device's stream, with its scratch in a 4 KiB array that
- *      is part of the library's device image.  count <= 2^26, else B200_E_NO_SPACE.  The first
+ *      is part of the library's device image.  count <= 2^26, else B200_E_NO_SPACE; count 0
+ *      writes 0.0f.  Both offsets must be multiples of 4, else B200_E_INVALID (checked on the
+ *      host: nothing is launched).  A positive return value here is a cudaError_t.  The first
  *      call on a device resolves the array's address: make it before any stream capture.
  *      Calls that overlap on the GPU race on the shared array; stream-ordered calls do not. */
 int b200_sum_f32_static(b200_dev* dev, int in_pool, size_t in_offset, size_t count, int out_pool,

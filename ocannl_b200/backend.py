@@ -143,6 +143,17 @@ class Device:
         check(lib().b200_d2h(self.h, ctypes.c_int(pool_id), ctypes.c_size_t(offset), _vp(arr.ctypes.data),
                              ctypes.c_size_t(arr.nbytes)))
 
+    def device_to_device(self, dst_pool: int, dst_offset: int, src: "Device", src_pool: int, src_offset: int, nbytes: int):
+        """Copy between pools of one device or of two (`device_to_device ~into_merge_buffer:No`,
+        arrayjit/lib/cuda_backend.ml:289-314), ordered after the work queued on the source."""
+        check(lib().b200_d2d(self.h, ctypes.c_int(dst_pool), ctypes.c_size_t(dst_offset), src.h, ctypes.c_int(src_pool),
+                             ctypes.c_size_t(src_offset), ctypes.c_size_t(nbytes)))
+
+    def merge_copy(self, src: "Device", src_pool: int, src_offset: int, nbytes: int):
+        """`device_to_device ~into_merge_buffer:Copy`: the source node lands in this device's merge
+        buffer (pool 0, grown as needed), where a routine's `Get_merge_buffer` reads it."""
+        check(lib().b200_merge_copy(self.h, src.h, ctypes.c_int(src_pool), ctypes.c_size_t(src_offset), ctypes.c_size_t(nbytes)))
+
     def all_work(self) -> Event:
         e = ctypes.c_void_p()
         check(lib().b200_event_record(self.h, ctypes.byref(e)))
@@ -244,13 +255,53 @@ def compile(ir: IrRoutine, options: Optional[str] = None) -> Code:  # noqa: A001
     return Code(ir, options)
 
 
+POOL_CAP = 0x1_0000_0000   # bytes per pool while offsets are 32-bit (arrayjit/lib/backends.ml:536)
+
+
+def plan_pool_segments(items: Sequence[Tuple[int, int]], cap: int = POOL_CAP, what: str = "allocate_delta",
+                       names: Optional[Sequence[str]] = None) -> Tuple[List[Tuple[int, int]], List[int]]:
+    """`Backend_utils.plan_pool_segments` (arrayjit/lib/backends.ml:22-51): lays `(size, alignment)`
+    items out in order; an item that would carry a pool past `cap` bytes opens a new pool at
+    offset 0.  Returns `[(segment, offset)]` per item and the byte size of every segment; an item
+    larger than the cap is a user error."""
+    seg, bump, closed, out = 0, 0, [], []
+    for i, (size, align) in enumerate(items):
+        if size > cap:
+            raise UserError(-5, "%s: tensor node %s needs %d bytes, over the %d-byte per-pool cap; set large_models" % (
+                what, names[i] if names else i, size, cap))
+        off = bump if align <= 1 else (bump + align - 1) // align * align
+        if off + size > cap:
+            closed.append(bump)
+            seg += 1
+            bump = size
+            out.append((seg, 0))
+        else:
+            bump = off + size
+            out.append((seg, off))
+    return out, (closed + [bump]) if items else []
+
+
 class Context:
     """`Backend_intf.context`: a device plus the {node -> (pool, offset)} map of the nodes it
-    holds.  Contexts are persistent: `link` returns a routine whose `.context` is the child."""
+    holds.  Contexts are persistent: `link` returns a routine whose `.context` is the child.
 
-    def __init__(self, device: Device, arrays: Optional[Dict[str, Tuple[int, int, Tnode]]] = None):
+    `packing` chooses how `link` lays out the nodes the parent does not hold yet:
+      "reference"  as `Raise_backend.allocate_delta` does (arrayjit/lib/backends.ml:529-614): working
+                   nodes and read-only nodes go to separate pools, every node aligned to its ELEMENT
+                   size only, pools cut at 4 GiB unless `large_models`, read-only nodes shared per
+                   device by identifier;
+      "aligned"    one pool, every node at a multiple of 256 bytes (the default of this mirror:
+                   every stage then keeps its fastest form)."""
+
+    def __init__(self, device: Device, arrays: Optional[Dict[str, Tuple[int, int, Tnode]]] = None,
+                 packing: str = "aligned", large_models: bool = False):
         self.device = device
         self.arrays: Dict[str, Tuple[int, int, Tnode]] = dict(arrays or {})   # ident -> (pool, offset, tn)
+        self.packing = packing
+        self.large_models = large_models
+
+    def _child(self, arrays) -> "Context":
+        return Context(self.device, arrays, self.packing, self.large_models)
 
     def allocate(self, tnodes: Sequence[Tnode]) -> "Context":
         """Child context that also holds `tnodes`, packed back to back in one new zeroed pool
@@ -267,14 +318,44 @@ class Context:
             self.device.memset_zero(pool, 0, max(total, 1))
             for t, o in zip(new, offs):
                 arrays[t.ident] = (pool, o, t)
-        return Context(self.device, arrays)
+        return self._child(arrays)
+
+    def _pack_reference(self, group: List[Tnode], arrays, zero: bool = True):
+        if not group:
+            return
+        cap = (1 << 62) if self.large_models else POOL_CAP
+        items = [(t.size_in_bytes, PREC_BYTES[t.prec]) for t in group]
+        where, sizes = plan_pool_segments(items, cap, "allocate_delta", [t.ident for t in group])
+        pools = []
+        for seg, size in enumerate(sizes):
+            align = max(PREC_BYTES[t.prec] for t, (s, _) in zip(group, where) if s == seg)
+            pools.append(self.device.alloc_pool(max(size, 1), alignment=align))
+        for t, (seg, off) in zip(group, where):
+            if zero and not t.zero_init:
+                self.device.memset_zero(pools[seg], off, t.size_in_bytes)
+            arrays[t.ident] = (pools[seg], off, t)
 
     def link(self, code: Code) -> "Routine":
         dev = self.device
         new: List[Tnode] = [t for t in code.ir.params() if t.ident not in self.arrays]
         arrays = dict(self.arrays)
-        if new:
-            # bump-pack the delta into one pool (allocate_delta, backends.ml:529-614)
+        if new and self.packing == "reference":
+            cache = dev.__dict__.setdefault("constant_buffer_cache", {})
+            working = [t for t in new if not t.read_only]
+            constants = [t for t in new if t.read_only]
+            self._pack_reference(working, arrays)
+            fresh = []
+            for t in constants:
+                hit = cache.get(t.ident)
+                if hit is not None and hit[2].prec == t.prec and tuple(hit[2].dims) == tuple(t.dims):
+                    arrays[t.ident] = hit
+                else:
+                    fresh.append(t)
+            self._pack_reference(fresh, arrays)
+            for t in fresh:
+                cache[t.ident] = arrays[t.ident]
+        elif new:
+            # bump-pack the delta into one pool at 256-byte multiples
             offs, total = [], 0
             for t in new:
                 align = 256
@@ -296,7 +377,7 @@ class Context:
             binds[i] = Binding(t.id, pool, off)
         h = ctypes.c_void_p()
         check(lib().b200_link(dev.h, code.h, binds, ctypes.c_int(len(params)), ctypes.byref(h)))
-        return Routine(Context(dev, arrays), code, h)
+        return Routine(self._child(arrays), code, h)
 
     # ---- host access (Context.set_values / get_values, arrayjit/lib/context.ml:322-395)
     def from_host(self, ident: str, arr: np.ndarray):
@@ -331,6 +412,13 @@ class Routine:
         vals = (ctypes.c_int64 * max(n, 1))(*[int(static[s]) for s in self.static_syms])
         check(lib().b200_launch(self.h, vals, ctypes.c_int(n)))
 
+    def info(self) -> dict:
+        """The plan that runs: the code's, or a re-planned variant of it when the bound addresses
+        ruled out a stage's aligned form (b200_routine_info)."""
+        buf = ctypes.create_string_buffer(1 << 16)
+        check(lib().b200_routine_info(self.h, buf, ctypes.c_size_t(1 << 16)))
+        return json.loads(buf.value.decode())
+
     def use_graph(self, on: bool = True):
         check(lib().b200_routine_use_graph(self.h, ctypes.c_int(int(on))))
 
@@ -345,7 +433,7 @@ class Routine:
     def stage_times(self):
         """[(total_ms, runs)] per stage, over the runs made while profiling was on."""
         out = []
-        for i in range(len(self.code.info()["stages"])):
+        for i in range(len(self.info()["stages"])):
             ms, n = ctypes.c_float(0), ctypes.c_int(0)
             check(lib().b200_routine_stage_time(self.h, ctypes.c_int(i), ctypes.byref(ms), ctypes.byref(n)))
             out.append((ms.value, n.value))

@@ -139,6 +139,7 @@ int b200_pool_alloc(b200_dev* dev, int pool_id, size_t bytes, size_t alignment) 
     }
     Pool p;
     p.bytes = bytes;
+    if (pool_id == 0) dev->merge_epoch++;
     cu_check(cu().cuMemAlloc_(&p.ptr, bytes ? bytes : 1), "cuMemAlloc");
     dev->used += bytes;
     dev->pools[pool_id] = p;
@@ -152,6 +153,7 @@ int b200_pool_free(b200_dev* dev, int pool_id) {
     std::lock_guard<std::mutex> g(dev->mu);
     auto it = dev->pools.find(pool_id);
     if (it == dev->pools.end()) throw Error(B200_E_INVALID, "free_pool: unknown pool id " + std::to_string(pool_id));
+    if (pool_id == 0) dev->merge_epoch++;
     cu_check(cu().cuStreamSynchronize_(dev->stream), "cuStreamSynchronize");
     cu_check(cu().cuMemFree_(it->second.ptr), "cuMemFree");
     if (it->second.upload_ev) cu().cuEventDestroy_(it->second.upload_ev);
@@ -403,18 +405,46 @@ int b200_compile(const char* name, const char* ir, size_t len, const char* optio
         else throw Error(B200_E_INVALID, "unknown compile option '" + k + "'");
       }
     }
-    Program p = parse_program(ir, len);
-    if (name && *name) p.name = name;
-    auto code = std::make_unique<b200_code>();
-    code->code = compile_program(std::move(p), opt);
-    // machine code for sm_100a is produced here, device independent
-    bool any_generic = false;
-    for (auto& s : code->code.stages) any_generic |= s.kind == Stage::Generic;
-    if (any_generic) code->cubin = &compile_cubin(code->code.source, code->code.prog.name);
-    for (auto& s : code->code.stages)
-      if (s.kind == Stage::Gemm) code->gemm_cubins.push_back(&compile_cubin(s.gemm_source, s.kernel));
-      else code->gemm_cubins.push_back(nullptr);
-    *out = code.release();
+    *out = build_code(name ? name : "", std::string(ir, len), opt).release();
+  });
+}
+
+std::unique_ptr<b200_code> build_code(const std::string& name, const std::string& ir_text, const CompileOptions& opt) {
+  Program p = parse_program(ir_text.data(), ir_text.size());
+  if (!name.empty()) p.name = name;
+  auto code = std::make_unique<b200_code>();
+  code->name = name;
+  code->ir_text = ir_text;
+  code->opt = opt;
+  code->code = compile_program(std::move(p), opt);
+  // machine code for sm_100a is produced here, device independent
+  bool any_generic = false;
+  for (auto& s : code->code.stages) any_generic |= s.kind == Stage::Generic;
+  if (any_generic) code->cubin = &compile_cubin(code->code.source, code->code.prog.name);
+  for (auto& s : code->code.stages)
+    if (s.kind == Stage::Gemm) code->gemm_cubins.push_back(&compile_cubin(s.gemm_source, s.kernel));
+    else code->gemm_cubins.push_back(nullptr);
+  return code;
+}
+
+b200_code* b200_code::variant(const std::set<int>& no_pairs_at, const std::set<int>& no_gemm_at) {
+  std::lock_guard<std::mutex> g(mu);
+  auto key = std::make_pair(no_pairs_at, no_gemm_at);
+  auto it = variants.find(key);
+  if (it != variants.end()) return it->second.get();
+  CompileOptions o = opt;
+  o.no_pairs_at = no_pairs_at;
+  o.no_gemm_at = no_gemm_at;
+  auto v = build_code(name, ir_text, o);
+  b200_code* raw = v.get();
+  variants[key] = std::move(v);
+  return raw;
+}
+
+int b200_routine_info(b200_routine* r, char* json, size_t cap) {
+  return guard([&] {
+    if (!r) throw Error(B200_E_INVALID, "null routine");
+    copy_out(r->code->code.describe(), json, cap);
   });
 }
 

@@ -267,7 +267,10 @@ struct Builder {
   const CompileOptions& opt;
   std::ostringstream src;
   int next_kernel = 0;
+  int cur_origin = -1;             // index of the top-level statement being planned
   std::map<size_t, Piece> pieces;  // by index into code.stages
+  bool pairs_here() const { return opt.enable_pairs && !opt.no_pairs_at.count(cur_origin); }
+  bool gemm_at(size_t i) const { return opt.enable_gemm && !opt.no_gemm_at.count((int)i); }
 
   std::string kernel_name() { return code.prog.name + "_s" + std::to_string(next_kernel++); }
 
@@ -541,7 +544,7 @@ struct Builder {
     // Pairs: a thread owns two neighbouring outputs along the innermost output loop when that loop
     // runs along the last axis of the fp32 node; the factors are then read as 4- and 8-byte words.
     bool pairs = false;
-    if (opt.enable_pairs && t.prec == Prec::Single && !st.par.empty() && !set.idcs.empty()) {
+    if (pairs_here() && t.prec == Prec::Single && !st.par.empty() && !set.idcs.empty()) {
       const LoopDim& p = st.par.back();
       bool ok = p.from == 0 && p.extent() % 2 == 0 && set.idcs.back().kind == Index::Iter && set.idcs.back().sym == p.sym &&
                 t.dims.back() % 2 == 0;
@@ -756,7 +759,7 @@ struct Builder {
     // axis of the written node, and everything in it is fp32, bf16 or half, a thread takes TWO
     // neighbouring iterations of that loop: 4- and 8-byte accesses, packed 16-bit arithmetic.
     bool pairs = false;
-    if (opt.enable_pairs && !scatter && ci.sym.empty() && body->kind == Stmt::Set && body->vec_len == 0 && !st.par.empty() && st.total > 0) {
+    if (pairs_here() && !scatter && ci.sym.empty() && body->kind == Stmt::Set && body->vec_len == 0 && !st.par.empty() && st.total > 0) {
       const Stmt& set = *body;
       const Tnode& t = code.prog.tn(set.tn);
       const LoopDim& p = st.par.back();
@@ -956,8 +959,15 @@ struct Builder {
   // 1024-thread block: each stage strides its iterations over the block, __syncthreads()
   // separates the stages.  Launch latency, not work, dominates such routines (the 2-16-16-1
   // training step is ~30 stages of a few hundred iterations each).
+  void merge_origins(Stage& f, const std::vector<size_t>& idx) {
+    std::set<int> all;
+    for (size_t i : idx) all.insert(code.stages[i].origins.begin(), code.stages[i].origins.end());
+    f.origins.assign(all.begin(), all.end());
+  }
+
   Stage emit_fused(const std::vector<size_t>& idx) {
     Stage f;
+    merge_origins(f, idx);
     f.kind = Stage::Generic;
     f.kernel = code.stages[idx.front()].kernel.empty() ? kernel_name() : code.stages[idx.front()].kernel;
     f.block = 1024;
@@ -1070,6 +1080,7 @@ struct Builder {
 
   Stage emit_warp_rows(const std::vector<size_t>& run, size_t L) {
     Stage f;
+    merge_origins(f, run);
     f.kind = Stage::Generic;
     f.kernel = code.stages[run.front()].kernel;
     f.block = 256;
@@ -1159,6 +1170,7 @@ struct Builder {
 
   Stage emit_rows(const std::vector<size_t>& run) {
     Stage f;
+    merge_origins(f, run);
     f.kind = Stage::Generic;
     f.kernel = code.stages[run.front()].kernel;
     f.block = 128;
@@ -1213,6 +1225,7 @@ struct Builder {
 
   Stage emit_pointwise_chain(const std::vector<size_t>& run) {
     Stage f = code.stages[run.front()];
+    merge_origins(f, run);
     Emitter em(code.prog);
     std::set<int> written;
     std::string text;
@@ -1445,9 +1458,94 @@ struct Builder {
     return out;
   }
 
+  // Function-scope scalar locals.  `hoist_cross_statement_cse` (arrayjit/lib/low_level.ml:2039-2135)
+  // turns a Local_scope shared by sibling assignments into `Declare_local id; <the scope's body>`
+  // before the first user, the users reading `Get_local id`; the cc backend prints a function-scope
+  // variable (arrayjit/lib/c_syntax.ml:695-704,730-734).  Siblings inside one loop body stay inside
+  // one kernel and need nothing.  At the top level of the routine the users become different
+  // kernels, so the local becomes a one-element routine-local node: declaration and body turn back
+  // into `t[0] := scope { body }` (which the reduction paths recognise) and every later
+  // `Get_local id` into `t[0]`.  The value makes one round trip through memory in its own precision.
+  void unhoist_function_locals(std::vector<StmtP>& flat) {
+    std::map<int, int> hoisted;   // scope id -> synthetic node id
+    auto writes_scope = [](const Stmt& s, int sid) {
+      bool w = false;
+      walk_stmt(s, [](const Scalar&) {}, [&](const Stmt& x) { if (x.kind == Stmt::SetLocal && x.scope_id == sid) w = true; });
+      return w;
+    };
+    int next_id = 0;
+    for (auto& t : code.prog.tnodes) next_id = std::max(next_id, t.id + 1);
+    std::vector<StmtP> out;
+    for (size_t i = 0; i < flat.size(); ++i) {
+      const StmtP& s = flat[i];
+      if (s->kind != Stmt::DeclareLocal) { out.push_back(s); continue; }
+      const Tnode& st = code.prog.tn(s->tn);
+      Tnode syn;
+      syn.id = next_id++;
+      syn.ident = "b200_local" + std::to_string(s->scope_id) + "_" + st.ident;
+      syn.prec = st.prec;
+      syn.dims = {1};
+      syn.mode = Mode::Local;
+      syn.zero_init = s->needs_init;
+      auto body = std::make_shared<Stmt>();
+      body->kind = Stmt::Seq;
+      size_t j = i + 1;
+      while (j < flat.size() && writes_scope(*flat[j], s->scope_id)) body->items.push_back(flat[j++]);
+      hoisted[s->scope_id] = syn.id;
+      code.prog.tn_index[syn.id] = code.prog.tnodes.size();
+      code.prog.tnodes.push_back(syn);
+      if (!body->items.empty()) {
+        auto scope = std::make_shared<Scalar>();
+        scope->kind = Scalar::LocalScope;
+        scope->scope_id = s->scope_id;
+        scope->tn = s->tn;
+        scope->body = body;
+        auto set = std::make_shared<Stmt>();
+        set->kind = Stmt::Set;
+        set->tn = syn.id;
+        Index zero;
+        set->idcs = {zero};
+        set->value = scope;
+        out.push_back(set);
+      }
+      i = j - 1;
+    }
+    if (hoisted.empty()) return;
+    // every remaining mention of a hoisted scope reads the node
+    std::function<ScalarP(const ScalarP&, int)> fix_scalar;
+    std::function<StmtP(const StmtP&, int)> fix_stmt = [&](const StmtP& s, int inside) -> StmtP {
+      auto c = std::make_shared<Stmt>(*s);
+      for (auto& x : c->items) x = fix_stmt(x, inside);
+      if (c->body) c->body = fix_stmt(c->body, inside);
+      if (c->value) c->value = fix_scalar(c->value, inside);
+      if (c->kind == Stmt::SetLocal && c->scope_id != inside && hoisted.count(c->scope_id))
+        throw Error(-4, "a function-scope local is assigned after its defining statements");
+      return c;
+    };
+    fix_scalar = [&](const ScalarP& e, int inside) -> ScalarP {
+      if (e->kind == Scalar::GetLocal && e->scope_id != inside && hoisted.count(e->scope_id)) {
+        auto g = std::make_shared<Scalar>();
+        g->kind = Scalar::Get;
+        g->tn = hoisted[e->scope_id];
+        Index zero;
+        g->idcs = {zero};
+        return g;
+      }
+      auto c = std::make_shared<Scalar>(*e);
+      // inside the re-wrapped body the scope's own id keeps meaning the local variable
+      const int in = (c->kind == Scalar::LocalScope && hoisted.count(c->scope_id)) ? c->scope_id : inside;
+      if (c->body) c->body = fix_stmt(c->body, in);
+      for (auto& a : c->args) a.s = fix_scalar(a.s, in);
+      return c;
+    };
+    for (auto& s : out) s = fix_stmt(s, -1);
+    flat.swap(out);
+  }
+
   void run() {
     std::vector<StmtP> flat;
     top_level(code.prog.body, flat);
+    unhoist_function_locals(flat);
     src << kNumericsSource << "\n";
     std::set<int> zeroed;  // nodes zeroed by the previous stage (for beta = 0 contractions)
     std::map<int, size_t> zero_stage;  // ... and the index of the stage that zeroes them
@@ -1459,16 +1557,17 @@ struct Builder {
       code.stages[it->second].memset_tn = -1;   // filtered out in emit_kernels
       zero_stage.erase(it);
     };
-    for (size_t i = 0; i < flat.size(); ++i) {
+    // plans the statement at flat[i]; advances i past the statements it absorbed
+    auto plan_one = [&](size_t& i) {
       const StmtP& s = flat[i];
       if (s->kind == Stmt::DeclareLocal || s->kind == Stmt::SetLocal)
-        throw Error(-4, "function-scope scalar locals (cross-statement hoisting) are not supported by the b200 backend");
+        throw Error(-4, "a function-scope scalar local is assigned away from its declaration");
       if (s->kind == Stmt::ZeroOut) {
         const Tnode& t = code.prog.tn(s->tn);
-        if (t.mode == Mode::Virtual) continue;
+        if (t.mode == Mode::Virtual) return;
         // a zero_out that a following contraction absorbs (beta = 0) is dropped below
         bool absorbed = false;
-        if (opt.enable_gemm && i + 1 < flat.size() && flat[i + 1]->kind == Stmt::For) {
+        if (gemm_at(i + 1) && i + 1 < flat.size() && flat[i + 1]->kind == Stmt::For) {
           std::vector<LoopDim> nest;
           StmtP body = flat[i + 1];
           while (body->kind == Stmt::For) {
@@ -1493,7 +1592,7 @@ struct Builder {
           memset_stage(s->tn);
           zeroed.insert(s->tn);  // still all zero until some stage writes it
         }
-        continue;
+        return;
       }
       // peel the perfect loop nest
       std::vector<LoopDim> nest;
@@ -1502,13 +1601,13 @@ struct Builder {
         nest.push_back({body->index, body->from, body->to});
         body = body->body;
       }
-      if (!body_has_set(*body)) continue;
+      if (!body_has_set(*body)) return;
       {
         std::set<std::pair<int, int>> declared, used;
         collect_scopes(*body, declared, used);
         for (auto& u : used)
           if (!declared.count(u))
-            throw Error(-4, "function-scope scalar locals (cross-statement hoisting) are not supported by the b200 backend");
+            throw Error(-4, "a scalar local is read outside the statement that defines it");
       }
       // a node zeroed earlier and untouched since lets a contraction skip reading it (beta = 0)
       std::set<int> writes_now;
@@ -1521,7 +1620,7 @@ struct Builder {
           zero_read.insert(e.tn);
       }, [](const Stmt&) {});
       for (int w : writes_now) zeroed.erase(w);
-      if (opt.enable_gemm && body->kind == Stmt::Set) {
+      if (gemm_at(i) && body->kind == Stmt::Set) {
         Stage g;
         int n_fused = 0;
         const std::vector<Follower> fol = followers_after(flat, i + 1);
@@ -1533,10 +1632,17 @@ struct Builder {
           g.gemm_source = gemm_translation_unit(code.prog, g, g.kernel, opt);
           code.stages.push_back(g);
           i += (size_t)n_fused;
-          continue;
+          return;
         }
       }
       if (generic_stage(nest, body, was_zero)) drop_zero_out(body->tn);
+    };
+    for (size_t i = 0; i < flat.size(); ++i) {
+      const size_t before = code.stages.size(), first = i;
+      cur_origin = (int)i;
+      plan_one(i);
+      for (size_t k = before; k < code.stages.size(); ++k)
+        for (size_t o = first; o <= i; ++o) code.stages[k].origins.push_back((int)o);
     }
     emit_kernels();
     code.source = src.str();

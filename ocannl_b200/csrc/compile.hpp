@@ -3,6 +3,7 @@
 // generated for it.  Mirrors the role of `Lowered_backend.compile`
 // (arrayjit/lib/backend_impl.ml:334-367): no device or context is touched here.
 #pragma once
+#include <set>
 #include <string>
 #include <vector>
 
@@ -65,6 +66,7 @@ struct Stage {
   int epi_out_bytes = 4;         // widest element the epilogue stores through the staging tile (2 or 4)
   int epi_tiles = 0;             // register tiles (inputs + outputs) the epilogue keeps per chunk
   std::string note;              // human-readable classification, for debug info
+  std::vector<int> origins;      // indices of the routine's top-level statements this stage runs
 };
 
 // A loop nest that follows a contraction and may be folded into its epilogue.
@@ -89,6 +91,11 @@ struct CompileOptions {
   bool enable_splitk = true; // few-tile accumulations split K over the idle SMs (fp32 atomic adds: order not fixed)
   bool enable_pairs = true;  // contraction epilogues over pairs of columns with packed 16-bit arithmetic
   bool large_models = false;
+  // Top-level statements (by index) that must not use the forms with alignment demands: the pair
+  // form of generic stages (8-byte accesses) / the TMA-fed contraction kernel (16-byte operand
+  // bases).  Filled when a routine is linked to buffers at element-size-aligned offsets, as
+  // `Raise_backend.allocate_delta` hands them out (arrayjit/lib/backends.ml:529-614).
+  std::set<int> no_pairs_at, no_gemm_at;
 };
 
 Code compile_program(Program prog, const CompileOptions& opt);

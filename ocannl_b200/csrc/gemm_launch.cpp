@@ -77,7 +77,7 @@ GemmLaunch* gemm_prepare(b200_routine* r, int si) {
   const int eb = prec_bytes(g.in_prec);
   CUdeviceptr a = ptr(g.a_tn) + (CUdeviceptr)(g.a_off * eb), b = ptr(g.b_tn) + (CUdeviceptr)(g.b_off * eb);
   if ((a & 15) || (b & 15))
-    throw Error(B200_E_UNSUPPORTED, "contraction operands must be 16-byte aligned for TMA; compile the routine with gemm=0");
+    throw Error(B200_E_INVALID, "link: internal error: a contraction stage was kept for operands that are not 16-byte aligned");
   auto* L = new GemmLaunch();
   try {
     std::vector<int64_t> sa, sb;

@@ -46,15 +46,64 @@ void b200_dev::check_status() {
   }
 }
 
+// Which stages of `c` cannot run in the compiled form at these addresses?  Pair-form generic
+// stages read and write 8-byte words; the contraction kernel's tensor maps want 16-byte operand
+// bases.  The reference's allocator aligns a node to its element size only
+// (`plan_pool_segments`, arrayjit/lib/backends.ml:22-51), so such bindings are legitimate: the
+// statements behind those stages are re-planned without the demanding form.
+static bool misaligned_stages(const b200_code* c, const std::map<int, CUdeviceptr>& param_ptr, std::set<int>* no_pairs_at,
+                              std::set<int>* no_gemm_at) {
+  bool any = false;
+  const Program& P = c->code.prog;
+  auto at = [&](int tn) -> CUdeviceptr {
+    auto it = param_ptr.find(tn);
+    return it == param_ptr.end() ? 0 : it->second;   // routine-local nodes sit at 256-byte multiples
+  };
+  for (auto& st : c->code.stages) {
+    if (st.kind == Stage::Generic && st.min_align > 1) {
+      bool bad = false;
+      for (auto& a : st.args)
+        if (a.kind == KArg::Node && (at(a.tn) % (CUdeviceptr)st.min_align) != 0) bad = true;
+      if (bad)
+        for (int o : st.origins) any |= no_pairs_at->insert(o).second;
+    } else if (st.kind == Stage::Gemm) {
+      const int eb = prec_bytes(st.gemm.in_prec);
+      const CUdeviceptr a = at(st.gemm.a_tn) + (CUdeviceptr)(st.gemm.a_off * eb), b = at(st.gemm.b_tn) + (CUdeviceptr)(st.gemm.b_off * eb);
+      (void)P;
+      if ((a & 15) || (b & 15))
+        for (int o : st.origins) any |= no_gemm_at->insert(o).second;
+    }
+  }
+  return any;
+}
+
 void b200_routine::link(b200_dev* d, b200_code* c, const b200_binding* b, int n) {
   dev = d;
-  code = c;
-  const Program& P = c->code.prog;
+  requested = c;
   std::map<int, const b200_binding*> bind;
   for (int i = 0; i < n; ++i) {
     bind[b[i].tn_id] = &b[i];
     pools_used.insert(b[i].pool_id);
   }
+  std::map<int, CUdeviceptr> param_ptr;
+  for (auto& t : c->code.prog.tnodes) {
+    if (!t.is_param()) continue;
+    auto it = bind.find(t.id);
+    if (it == bind.end()) continue;  // checked per stage below: only nodes a stage uses are required
+    if (it->second->offset % (uint64_t)prec_bytes(t.prec) != 0)
+      throw Error(B200_E_INVALID, "link: node '" + t.ident + "' is bound at offset " + std::to_string(it->second->offset) +
+                                      ", not a multiple of its element size");
+    param_ptr[t.id] = d->address(it->second->pool_id, it->second->offset, (size_t)t.bytes());
+  }
+  {
+    std::set<int> no_pairs_at = c->opt.no_pairs_at, no_gemm_at = c->opt.no_gemm_at;
+    b200_code* use = c;
+    for (int round = 0; round < 4 && misaligned_stages(use, param_ptr, &no_pairs_at, &no_gemm_at); ++round)
+      use = c->variant(no_pairs_at, no_gemm_at);
+    c = use;
+  }
+  code = c;
+  const Program& P = c->code.prog;
 
   // routine-local nodes live in a scratch slab owned by the routine
   size_t off = 0;
@@ -87,13 +136,8 @@ void b200_routine::link(b200_dev* d, b200_code* c, const b200_binding* b, int n)
   }
 
   for (auto& t : P.tnodes) {
-    if (t.mode == Mode::Local) {
-      node_ptr[t.id] = scratch + local_off[t.id];
-    } else if (t.is_param()) {
-      auto it = bind.find(t.id);
-      if (it == bind.end()) continue;  // checked per stage below: only nodes a stage uses are required
-      node_ptr[t.id] = d->address(it->second->pool_id, it->second->offset, (size_t)t.bytes());
-    }
+    if (t.mode == Mode::Local) node_ptr[t.id] = scratch + local_off[t.id];
+    else if (param_ptr.count(t.id)) node_ptr[t.id] = param_ptr[t.id];
   }
 
   if (!P.statics.empty()) {
@@ -121,9 +165,8 @@ void b200_routine::link(b200_dev* d, b200_code* c, const b200_binding* b, int n)
         auto it = node_ptr.find(a.tn);
         if (it == node_ptr.end()) throw Error(B200_E_USER, "link: node '" + P.tn(a.tn).ident + "' has no buffer binding");
         if (st.min_align > 1 && (it->second % (CUdeviceptr)st.min_align) != 0)
-          throw Error(B200_E_UNSUPPORTED, "link: node '" + P.tn(a.tn).ident + "' is bound at an address that is not a multiple of " +
-                                              std::to_string(st.min_align) + " bytes, which the pair form of stage '" + st.kernel +
-                                              "' needs; bind nodes at 16-byte multiples or compile the routine with pairs=0");
+          throw Error(B200_E_INVALID, "link: internal error: stage '" + st.kernel + "' kept a form that needs " +
+                                          std::to_string(st.min_align) + "-byte alignment for node '" + P.tn(a.tn).ident + "'");
         arg_values[i].push_back(it->second);
       } else if (a.kind == KArg::Statics) {
         arg_values[i].push_back(statics_dev);
@@ -131,6 +174,7 @@ void b200_routine::link(b200_dev* d, b200_code* c, const b200_binding* b, int n)
         arg_values[i].push_back(scratch + reduce_off + (size_t)a.tn);
       } else {
         arg_values[i].push_back(0);  // merge buffer: resolved at launch (pool 0 may be re-allocated)
+        reads_merge = true;
       }
     }
     if (st.kind == Stage::Generic) {
@@ -271,7 +315,14 @@ void b200_routine::launch(const int64_t* static_idx, int n_static) {
     }
   }
   if (want_graph && !profiling) {
+    if (graph && reads_merge && graph_merge_epoch != dev->merge_epoch) {
+      // the merge buffer moved since the capture (`b200_merge_copy` grew pool 0): the graph holds
+      // the old address
+      cu().cuGraphExecDestroy_(graph);
+      graph = nullptr;
+    }
     if (!graph) {
+      graph_merge_epoch = dev->merge_epoch;
       CUgraph g = nullptr;
       cu_check(cu().cuStreamBeginCapture_(dev->stream, CU_STREAM_CAPTURE_MODE_THREAD_LOCAL), "cuStreamBeginCapture");
       try {

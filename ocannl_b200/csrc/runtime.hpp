@@ -2,6 +2,7 @@
 // compiled code and linked routines.
 #pragma once
 #include <map>
+#include <memory>
 #include <set>
 #include <mutex>
 #include <string>
@@ -33,6 +34,9 @@ struct b200_dev {
   size_t used = 0;
   volatile unsigned int* status_host = nullptr;  // written by kernels whose bounded waits expire
   CUdeviceptr status_dev = 0;
+  // bumped whenever pool 0 (the merge buffer) gets a new slab: a captured graph that reads the
+  // merge buffer holds its address and must be captured again
+  unsigned long long merge_epoch = 0;
   long long n_launches = 0, n_graph_launches = 0, n_h2d = 0, n_d2h = 0, n_d2d = 0, n_events = 0;
 
   // Optional second stream for host-to-device copies (b200_set_async_uploads).  A copy waits for
@@ -76,7 +80,17 @@ struct b200_code {
   b200::Code code;
   const std::string* cubin = nullptr;              // generic kernels of the routine
   std::vector<const std::string*> gemm_cubins;     // per stage (null for non-contraction stages)
+  // what the code was compiled from, and re-compilations of it in which some top-level statements
+  // avoid the forms with alignment demands (made at link when the bound addresses call for it)
+  std::string name, ir_text;
+  b200::CompileOptions opt;
+  std::mutex mu;
+  std::map<std::pair<std::set<int>, std::set<int>>, std::unique_ptr<b200_code>> variants;
+  b200_code* variant(const std::set<int>& no_pairs_at, const std::set<int>& no_gemm_at);
 };
+
+// Parses, plans and compiles a routine to sm_100a machine code (api.cpp).
+std::unique_ptr<b200_code> build_code(const std::string& name, const std::string& ir_text, const b200::CompileOptions& opt);
 
 struct GemmLaunch;  // gemm_launch.cpp
 
@@ -101,8 +115,11 @@ struct b200_routine {
   bool profiling = false;
   std::vector<std::vector<std::pair<CUevent, CUevent>>> stage_events;  // per stage, per profiled run
   CUgraphExec graph = nullptr;
+  bool reads_merge = false;               // some stage takes the merge buffer as an argument
+  unsigned long long graph_merge_epoch = 0;  // the device's merge_epoch when `graph` was captured
 
   std::set<int> pools_used;   // pools of the bound nodes (what a launch has to wait for, uploads-wise)
+  b200_code* requested = nullptr;  // the code `link` was given; `code` may be a variant of it
   void link(b200_dev* d, b200_code* c, const b200_binding* b, int n);
   void launch(const int64_t* static_idx, int n_static);
   void enqueue_stages();

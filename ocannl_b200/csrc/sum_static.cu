@@ -13,7 +13,9 @@
 //   * the array holds B200_STATIC_MAX_BLOCKS (1024) partials = 4 KiB per GPU that loads the
 //     library, held until the process exits;
 //   * at most B200_STATIC_MAX_COUNT (2^26) elements per call; larger counts are refused with
-//     B200_E_NO_SPACE before anything is launched;
+//     B200_E_NO_SPACE before anything is launched; an empty range (count 0) writes 0.0f;
+//   * both offsets must be multiples of 4 bytes (B200_E_INVALID otherwise, nothing is launched);
+//   * a positive return value is the cudaError_t of the runtime call that failed;
 //   * the first call on a device resolves the array's device address (cudaGetSymbolAddress,
 //     with that device current).  Make that first call before starting any stream capture;
 //   * every call on a device uses the same array.  Calls queued on the device's stream run one
@@ -81,7 +83,10 @@ extern "C" int b200_sum_f32_static(b200_dev* dev, int in_pool, size_t in_offset,
   try {
     if (!dev) throw b200::Error(B200_E_INVALID, "null device");
     if (dev->ordinal < 0 || dev->ordinal >= 64) throw b200::Error(B200_E_INVALID, "device ordinal out of range");
-    if (count == 0) throw b200::Error(B200_E_INVALID, "b200_sum_f32_static: empty range");
+    // float accesses at an address that is not a multiple of 4 would fault on the device, and a
+    // fault is sticky for the whole context: refuse on the host, before anything is launched
+    if (in_offset % sizeof(float) != 0 || out_offset % sizeof(float) != 0)
+      throw b200::Error(B200_E_INVALID, "b200_sum_f32_static: offsets must be multiples of 4 bytes");
     if ((unsigned long long)count > B200_STATIC_MAX_COUNT)
       throw b200::Error(B200_E_NO_SPACE, "b200_sum_f32_static: " + std::to_string(count) +
                                              " elements exceed the fixed capacity of " +
@@ -117,5 +122,8 @@ extern "C" int b200_sum_f32_static(b200_dev* dev, int in_pool, size_t in_offset,
   } catch (const b200::Error& e) {
     b200_error_slot = e.what();
     return e.code;
+  } catch (const std::exception& e) {   // nothing may cross the C boundary
+    b200_error_slot = e.what();
+    return B200_E_INVALID;
   }
 }

@@ -5,14 +5,18 @@ the `Low_level` routine the cc backend printed:
   d_fwd      test/operations/top_down_prec.ml      -> top_down_prec.c.expected
   out_fwd    test/operations/zero_out_local_decl.ml -> zero_out_local_decl.c.expected
   where_fwd  test/operations/test_where_precision.ml -> test_where_precision.c.expected
+  slides_gd_update  the three statements the C listing of
+             docs/slides-basics_backprop_training_codegen.md:838-866 prints in full (a
+             materialised-accumulate contraction as an `fmaf` nest, `fmaxf(0.0, ...)`, the
+             SGD line with its `(float)(0.0001)` constant)
 and, for the random-number path, the routine of the IR golden
   n3_fwd     test/operations/n3_fwd_with_prec-unoptimized.ll.expected
 (seed 0x2A as constant bits, a counter from the loop index, 2-round threefry, vector uniform
 conversion), whose single-precision results the reference prints in
 test/operations/test_threefry4x32.ml:37-45.
 """
-from ocannl_b200.low_level import (VEC_LENGTH, Affine, Binop, Comment, ConstBits, EmbedIndex, For, Routine, Seq,
-                                   Set, SetFromVec, Unop, ZeroOut, where)
+from ocannl_b200.low_level import (VEC_LENGTH, Affine, Binop, Comment, Const, ConstBits, EmbedIndex, For, Routine, Seq,
+                                   Set, SetFromVec, Unop, ZeroOut, fma, un, where)
 
 
 def d_fwd() -> Routine:
@@ -76,6 +80,34 @@ def n3_fwd(prec: str = "half", count: int = 5, variant: str = "light", scalar_to
         body.append(For(i9, 0, count - 1, Set(first, (i9,), Unop("uint4x32_to_prec_uniform1", bits[i9], prec=prec))))
     body.append(Comment("end"))
     r.body = Seq(body)
+    return r
+
+
+def slides_gd_update() -> Routine:
+    r = Routine("scalar_loss_forward_and_gradient_then_gd_update")
+    i1 = r.static_sym(80)
+    r.static_sym(None)
+    b1 = r.tn("b1", "single", [16])
+    lr = r.tn("learning_rate", "single", [1])
+    flat = r.tn("moons_flat", "single", [80, 10, 2])
+    w1 = r.tn("w1", "single", [16, 2])
+    w3 = r.tn("w3", "single", [1, 16])
+    w3g = r.tn("w3_grad", "single", [1, 16], mode="local", zero_init=True)
+    n35 = r.tn("n35", "single", [10, 16], mode="local", zero_init=True)
+    relu = r.tn("relu", "single", [10, 16], mode="local")
+    r._next_sym = 52
+    i52, i53, i54 = r.syms(3)
+    r._next_sym = 61
+    i61, i62 = r.syms(2)
+    r._next_sym = 160
+    i160 = r.sym()
+    r.body = Seq([
+        Comment("scalar_loss forward and gradient update"),
+        For(i52, 0, 9, For(i53, 0, 15, For(i54, 0, 1, Set(n35, (i52, i53), fma(w1[i53, i54], flat[i1, i52, i54], n35[i52, i53]))))),
+        For(i61, 0, 9, For(i62, 0, 15, Set(relu, (i61, i62), un("relu", b1[i62] + n35[i61, i62])))),
+        Comment("w3 param sgd step"),
+        For(i160, 0, 15, Set(w3, (0, i160), w3[0, i160] - lr[0] * fma(Const(0.0001), w3[0, i160], w3g[0, i160]))),
+        Comment("end"), Comment("end")])
     return r
 
 

@@ -1,0 +1,223 @@
+"""The drop-in boundary on a GPU: bindings as the reference's allocator hands them out, the
+merge-buffer path, copies and stream ordering between devices, function-scope locals."""
+import numpy as np
+import pytest
+
+from ocannl_b200 import backend as bk
+from ocannl_b200 import workloads as W
+from tests import routines as R
+from tests.parity import compare, run_device, run_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _link_reference_packed(device, ir, inputs, options=None, large_models=False):
+    code = bk.Code(ir, options)
+    rt = bk.Context(device, packing="reference", large_models=large_models).link(code)
+    for k, v in inputs.items():
+        rt.context.from_host(k, v)
+    return code, rt
+
+
+def _free(device, rt, code):
+    pools = {p for p, _, _ in rt.context.arrays.values()}
+    rt.free()
+    code.free()
+    for p in pools:
+        device.free_pool(p)
+    device.__dict__.pop("constant_buffer_cache", None)
+
+
+def _outputs(rt, ir):
+    return {t.ident: rt.context.to_host(t.ident) for t in ir.params()}
+
+
+# ------------------------------------------------------------------ allocation as the reference does it
+def test_mlp_links_at_element_aligned_offsets(device):
+    """Config 5's training routine behind the reference's allocator: a [10]-element bf16 bias of 20
+    bytes in front of the weights leaves the following nodes at 4-byte (not 8- or 16-byte)
+    multiples.  Every stage still runs -- those that cannot keep their aligned form are re-planned
+    -- and the results match the oracle like the 256-byte packing's do."""
+    rows = 512
+    dims = (784, 1024, 1024, 10)
+    ir = W.mlp_train_update(rows=rows, dims=dims)
+    # an odd-sized read-only node first in declaration order shifts everything after it
+    odd = ir.tn("odd_bias", "bfloat16", [10], read_only=True)
+    ir.tnodes.remove(odd)
+    ir.tnodes.insert(0, odd)
+    odd2 = ir.tn("odd_scalar", "single", [1])
+    ir.tnodes.remove(odd2)
+    ir.tnodes.insert(1, odd2)
+    from ocannl_b200.low_level import Seq, Set
+    ir.body = Seq([ir.body, Set(odd2, (0,), odd[3] + 1.0)])
+    x, onehot = W.mlp_inputs(rows=rows, in_dim=dims[0], classes=dims[-1])
+    inputs = dict(W.mlp_params(dims=dims), x=x, labels=onehot, odd_bias=W.store("bfloat16", np.arange(10, dtype=np.float32)))
+    want = run_oracle(ir, inputs)
+    code, rt = _link_reference_packed(device, ir, inputs)
+    offs = {k: v[1] for k, v in rt.context.arrays.items()}
+    assert any(o % 16 for o in offs.values()), offs            # the packing really is unaligned somewhere
+    plan = [s["note"] or "" for s in rt.info()["stages"]]
+    default_plan = [s["note"] or "" for s in code.info()["stages"]]
+    assert plan != default_plan                               # some stage had to change its form
+    rt.run()
+    device.await_()
+    got = _outputs(rt, ir)
+    grads = [t.ident for t in ir.params() if t.ident.endswith("_grad")]
+    rest = [t.ident for t in ir.params() if not t.ident.endswith("_grad")]
+    compare(ir, got, want, rtol=2e-2, atol=2e-3, only=rest)
+    for g in grads:
+        scale = float(np.abs(W.load(next(t.prec for t in ir.params() if t.ident == g), want[g])).max())
+        compare(ir, got, want, rtol=2e-2, atol=5e-2 * max(scale, 1e-30), only=[g])
+    _free(device, rt, code)
+
+
+@pytest.mark.parametrize("name", ["moons", "makemore", "einsum", "decoder", "mlp_fwd"])
+def test_configs_behind_reference_packing(device, name):
+    """The five configurations linked through the mirror of `Raise_backend.allocate_delta`
+    (read-only nodes in their own pools, element-size alignment): same parity as elsewhere."""
+    statics = [{}]
+    rtol, atol = 2e-2, 2e-3
+    if name == "moons":
+        ir = W.moons_train_step()
+        x, y = W.moons_inputs()
+        inputs = dict(W.moons_params(), moons_flat=x, moons_classes=y)
+        statics = [{"i1": 0, "i2": 0}, {"i1": 1, "i2": 1}]
+        rtol, atol = 1e-5, 1e-6
+    elif name == "makemore":
+        ir = W.makemore_forward(batch=512)
+        ids, onehot = W.makemore_inputs(batch=512)
+        inputs = dict(W.makemore_params(), input_batch=ids, target_batch=onehot)
+        rtol, atol = 1e-4, 1e-5
+    elif name == "einsum":
+        ir = W.einsum_gelu(2, 256, 256, 256)
+        inputs = W.einsum_gelu_inputs(2, 256, 256, 256)
+    elif name == "decoder":
+        kw = dict(layers=1, d_model=128, heads=2, d_head=64, d_ff=256)
+        ir = W.transformer_forward(batch=2, seq=128, **kw)
+        inputs = dict(W.transformer_params(**kw), **W.transformer_inputs(batch=2, seq=128))
+        atol = 2e-2
+    else:
+        ir = W.mlp_forward(rows=256)
+        x, onehot = W.mlp_inputs(rows=256)
+        inputs = dict(W.mlp_params(), x=x, labels=onehot)
+    want = run_oracle(ir, inputs, statics)
+    code, rt = _link_reference_packed(device, ir, inputs)
+    pools = {v[0] for v in rt.context.arrays.values()}
+    ro = {rt.context.arrays[t.ident][0] for t in ir.params() if t.read_only}
+    rw = {rt.context.arrays[t.ident][0] for t in ir.params() if not t.read_only}
+    assert not (ro & rw) and pools == ro | rw                 # constants and working nodes never share a pool
+    for st in statics:
+        rt.run(**st)
+    device.await_()
+    compare(ir, _outputs(rt, ir), want, rtol=rtol, atol=atol)
+    _free(device, rt, code)
+
+
+# ------------------------------------------------------------------ function-scope locals
+@pytest.mark.parametrize("n", [1000, 100000])
+@pytest.mark.parametrize("options", [None, "fuse=0 coop=0"])
+def test_function_scope_local_shared_by_top_level_statements(device, n, options):
+    ir = R.hoisted_top_level(n)
+    x = np.random.default_rng(5).normal(0, 1, n).astype(np.float32)
+    want = run_oracle(ir, {"x": x})
+    got, _ = run_device(device, ir, {"x": x}, options=options)
+    compare(ir, got, want, rtol=2e-5, atol=1e-6)     # the sum's order differs (cooperative reduction)
+
+
+def test_local_shared_inside_a_loop_body(device):
+    ir = R.hoisted_in_loop(300, 50)
+    m = np.random.default_rng(6).normal(0, 1, (300, 50)).astype(np.float32)
+    want = run_oracle(ir, {"m": m})
+    got, _ = run_device(device, ir, {"m": m})
+    compare(ir, got, want, rtol=0, atol=0, exact=["p", "q"])     # serial sum per row: same order, same bits
+
+
+# ------------------------------------------------------------------ merge buffer, copies, stream order
+def _linked_merge_add(device, n, graph):
+    ir = R.merge_add(n)
+    code = bk.Code(ir)
+    rt = bk.Context(device).link(code)
+    if graph:
+        rt.use_graph(True)
+    return ir, code, rt
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_merge_buffer_known_answer(device, graph):
+    """test/operations/shard_transfer.ml: the owner holds [1 2], the other shard [3 4]; the copy into
+    the merge buffer followed by `g =+ g.merge` leaves [4 6] on the owner."""
+    ir, code, rt = _linked_merge_add(device, 2, graph)
+    pool, off, _ = rt.context.arrays["a"]
+    other = device.alloc_pool(256)
+    device.from_host(other, 0, np.float32([3, 4]))
+    rt.context.from_host("a", np.float32([1, 2]))
+    device.merge_copy(device, other, 0, 8)
+    rt.run()
+    assert list(rt.context.to_host("a")) == [4.0, 6.0]
+    device.free_pool(other)
+    _free(device, rt, code)
+
+
+def test_graph_replay_follows_a_merge_buffer_that_grew(device):
+    """A captured graph holds the merge buffer's address; when a larger copy makes the buffer grow
+    (a new slab), the next run must read the new one."""
+    small_ir, small_code, small = _linked_merge_add(device, 2, True)
+    big_ir, big_code, big = _linked_merge_add(device, 1 << 16, True)
+    src = device.alloc_pool(4 << 16)
+    device.from_host(src, 0, np.float32([3, 4]))
+    small.context.from_host("a", np.float32([1, 2]))
+    device.merge_copy(device, src, 0, 8)
+    small.run()                                   # captures with the small merge slab
+    assert list(small.context.to_host("a")) == [4.0, 6.0]
+    before = device.pool_address(0)
+    ones = np.ones(1 << 16, np.float32)
+    device.from_host(src, 0, ones * 5)
+    big.context.from_host("a", ones)
+    device.merge_copy(device, src, 0, 4 << 16)    # grows pool 0: new slab
+    big.run()
+    assert np.array_equal(big.context.to_host("a"), ones * 6)
+    assert device.pool_address(0) != before
+    device.merge_copy(device, src, 0, 8)          # [5 5] into the grown buffer
+    small.run()                                   # replay: must not read the freed slab
+    assert list(small.context.to_host("a")) == [9.0, 11.0]
+    device.free_pool(src)
+    _free(device, small, small_code)
+    _free(device, big, big_code)
+
+
+def test_device_to_device_and_stream_wait(device):
+    """`device_to_device ~into_merge_buffer:No` between two pools, and `will_wait_for` on an event
+    recorded after the producer."""
+    a = device.alloc_pool(1 << 20)
+    b = device.alloc_pool(1 << 20)
+    x = np.random.default_rng(1).integers(0, 255, 1 << 20, dtype=np.uint8)
+    device.from_host(a, 0, x)
+    ev = device.all_work()
+    device.will_wait_for(ev)
+    device.device_to_device(b, 4096, device, a, 0, (1 << 20) - 4096)
+    out = np.zeros((1 << 20) - 4096, np.uint8)
+    device.to_host(b, 4096, out)
+    device.await_()
+    assert ev.is_done()
+    assert np.array_equal(out, x[:(1 << 20) - 4096])
+    with pytest.raises(bk.B200Error):
+        device.device_to_device(b, 0, device, a, 4096, 1 << 20)      # source range past the pool
+    ev.free()
+    device.free_pool(a)
+    device.free_pool(b)
+
+
+def test_peer_copy_into_merge_buffer(device):
+    """The same known answer with the two shards on two GPUs (skipped on a one-GPU box)."""
+    if bk.num_devices() < 2:
+        pytest.skip("needs two GPUs")
+    dev1 = bk.Device(1)
+    ir, code, rt = _linked_merge_add(device, 2, False)
+    other = dev1.alloc_pool(256)
+    dev1.from_host(other, 0, np.float32([3, 4]))
+    rt.context.from_host("a", np.float32([1, 2]))
+    device.merge_copy(dev1, other, 0, 8)
+    rt.run()
+    assert list(rt.context.to_host("a")) == [4.0, 6.0]
+    dev1.free_pool(other)
+    _free(device, rt, code)

@@ -11,8 +11,9 @@ import pytest
 from ocannl_b200 import workloads as W
 from oracle.emit_c import Emitter
 from oracle.run_c import OracleRoutine
-from tests.golden.golden_routines import GOLDEN, n3_fwd
-from tests.golden.make_cc_golden_digests import routine_text
+from tests import routines as R
+from tests.golden.golden_routines import GOLDEN, n3_fwd, slides_gd_update
+from tests.golden.make_cc_golden_digests import main_logic_text, routine_text
 from tests.parity import run_oracle
 
 HERE = os.path.dirname(os.path.abspath(__file__))
@@ -27,6 +28,65 @@ def test_emitter_reproduces_golden_c(name):
     text = routine_text(Emitter(GOLDEN[name]().to_b200ir()).function())
     assert len(text) == dig["chars"]
     assert hashlib.sha256(text.encode()).hexdigest() == dig["sha256"]
+
+
+def test_emitter_reproduces_slides_listing():
+    """The C listing of docs/slides-basics_backprop_training_codegen.md: a materialised
+    accumulate printed as an `fmaf` loop nest, `fmaxf(0.0, ...)` for relu and the SGD assignment
+    with its `(float)(0.0001)` constant -- the statements between `/* Main logic. */` and the end
+    of the function (the listing's `...` lines dropped), whitespace removed."""
+    dig = json.load(open(os.path.join(HERE, "golden", "cc_golden_digests.json")))["slides_gd_update"]
+    text = main_logic_text(Emitter(slides_gd_update().to_b200ir()).function())
+    assert len(text) == dig["chars"]
+    assert hashlib.sha256(text.encode()).hexdigest() == dig["sha256"]
+
+
+def einsum_trivia_expected(which):
+    """The cells the reference printed for one of the four contractions, as an array of strings in
+    the result's memory layout (fixture made by tests/golden/make_einsum_kat.py)."""
+    cells = json.load(open(os.path.join(HERE, "golden", "einsum_trivia_kat.json")))[which]["cells"]
+    if which == "c":       # 0:2|2:3->1:5 -> [b, o, i]; one block, a column-cell per b
+        return np.array([[[cells[0][o][b][i] for i in range(3)] for o in range(5)] for b in range(2)])
+    if which == "d":       # 0:2,1:2|3:3->2:5 -> [a, b, o, i]; a block per a, a column-cell per b
+        return np.array([[[[cells[a][o][b][i] for i in range(3)] for o in range(5)] for b in range(2)] for a in range(2)])
+    return np.array([[cells[0][o][0][i] for i in range(3)] for o in range(5)])   # 1:3->0:5 -> [o, i]
+
+
+@pytest.mark.parametrize("which", ["c", "d", "e", "f"])
+def test_oracle_reproduces_printed_contractions(which):
+    """test/einsum/einsum_trivia_exec.ml:67-84: batched, outer-batch and batch-reduced matrix
+    products of two `range_of_shape` tensors; the oracle's results print as the reference's did."""
+    out = run_oracle(R.einsum_trivia(which), {"a": R.range_of_shape([2, 4, 3]), "b": R.range_of_shape([2, 5, 4])})[which]
+    assert np.array_equal(np.vectorize(R.printed)(out), einsum_trivia_expected(which))
+
+
+def test_oracle_embedding_lookup_known_answers():
+    """test/operations/test_one_hot_embedding_lookup.ml: C[o, i] = 4 o + i; ids (1, 3, 0) gather
+    rows; an id equal to the vocabulary size and a fractional id give zero rows."""
+    C = np.arange(12, dtype=np.float32).reshape(3, 4)
+    for ids, rows in (([1, 3, 0], [[1, 5, 9], [3, 7, 11], [0, 4, 8]]), ([1, 4], [[1, 5, 9], [0, 0, 0]]),
+                      ([2, 1.5], [[2, 6, 10], [0, 0, 0]]), ([-1, 3], [[0, 0, 0], [3, 7, 11]])):
+        out = run_oracle(R.embedding_lookup(len(ids)), {"ids": np.float32(ids), "C": C})["embedded"]
+        assert np.array_equal(out, np.float32(rows)), (ids, out)
+
+
+def test_oracle_function_scope_locals():
+    """`Declare_local` + body + `Get_local` users (arrayjit/lib/low_level.ml:2039-2135), at the top
+    level of the routine and inside a loop body, against numpy."""
+    x = np.random.default_rng(5).normal(0, 1, 1000).astype(np.float32)
+    out = run_oracle(R.hoisted_top_level(1000), {"x": x})
+    ss = float(np.sum(x.astype(np.float64) ** 2))
+    assert abs(out["a"][0] - ss / 1000) < 1e-4 and abs(out["b"][0] - np.sqrt(ss + 1)) < 1e-3
+    assert np.allclose(out["c"], ss * np.arange(4), rtol=1e-5)
+    m = np.random.default_rng(6).normal(0, 1, (30, 50)).astype(np.float32)
+    out = run_oracle(R.hoisted_in_loop(30, 50), {"m": m})
+    assert np.allclose(out["p"], 2 * m.sum(1), atol=1e-4) and np.allclose(out["q"], m.sum(1) - 1, atol=1e-4)
+
+
+def test_oracle_argmax():
+    x = np.random.default_rng(8).normal(0, 1, (64, 10)).astype(np.float32)
+    out = run_oracle(R.argmax_rows(64, 10), {"scores": x})
+    assert np.array_equal(out["argmax"].reshape(-1), x.argmax(1).astype(np.float32))
 
 
 def test_golden_routines_run():

@@ -2,6 +2,7 @@
 so the plan (which stages exist, what each one is) can be read back from `b200_code_info`."""
 from ocannl_b200 import backend as bk
 from ocannl_b200 import workloads as W
+import pytest
 
 
 def _plan(ir, options=None):
@@ -85,3 +86,15 @@ def test_momentum_sgd_is_one_launch_per_parameter():
     assert sum("pointwise chain of 4 stages, pairs" in n for n in notes) == 2, notes   # w1, w2; the small ones share a block
     assert len(st) == 4, notes
     assert len(_plan(W.mlp_sgd(momentum=0.9, weight_decay=1e-4, nesterov=True), "fuse=0")) == 5 * 4
+
+
+def test_plan_pool_segments_layout():
+    """Element-size alignment, in order, a new pool when the cap would be passed
+    (arrayjit/lib/backends.ml:22-51)."""
+    where, sizes = bk.plan_pool_segments([(20, 2), (8, 4), (6, 2), (100, 4)], cap=64 + 40)
+    assert where == [(0, 0), (0, 20), (0, 28), (1, 0)] and sizes == [34, 100]
+    where, sizes = bk.plan_pool_segments([(3, 1), (8, 8), (2, 2)])
+    assert where == [(0, 0), (0, 8), (0, 16)] and sizes == [18]
+    with pytest.raises(bk.UserError, match="per-pool cap"):
+        bk.plan_pool_segments([(200, 4)], cap=100)
+    assert bk.plan_pool_segments([]) == ([], [])

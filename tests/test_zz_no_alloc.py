@@ -74,4 +74,17 @@ def test_static_sum_refuses_what_does_not_fit(device):
     assert e.value.code == -7 and "capacity" in str(e.value)
     with pytest.raises(bk.B200Error):
         device.sum_f32_static(pool, 0, 1024, pool, 0)          # 4096 bytes do not fit a 1024-byte pool
+    # offsets that are not multiples of 4 would be misaligned float accesses on the device:
+    # refused on the host, nothing is launched
+    for in_off, out_off in ((2, 0), (0, 6), (1, 3)):
+        with pytest.raises(bk.B200Error) as e:
+            device.sum_f32_static(pool, in_off, 8, pool, out_off)
+        assert e.value.code == -1 and "multiples of 4" in str(e.value)
+    # an empty range is a sum of nothing
+    device.from_host(pool, 0, np.float32([7.0]))
+    device.sum_f32_static(pool, 16, 0, pool, 0)
+    got = np.empty(1, np.float32)
+    device.to_host(pool, 0, got)
+    device.await_()
+    assert got[0] == 0.0
     device.free_pool(pool)
