@@ -1426,6 +1426,16 @@ struct Builder {
     return out;
   }
 
+  // an epilogue that ends in a grid-wide sum keeps its per-warp partials and its ticket in the
+  // routine's reduction scratch (zeroed at link; the kernel resets its ticket itself)
+  void assign_epilogue_scratch(Stage& g) {
+    if (!g.epi_scratch_bytes) return;
+    for (auto& a : g.args)
+      if (a.kind == KArg::Scratch) a.tn = (int)code.reduce_scratch_bytes;
+    code.reduce_scratch_bytes += g.epi_scratch_bytes;
+    code.reduce_scratch_bytes = (code.reduce_scratch_bytes + 255) & ~(size_t)255;
+  }
+
   void memset_stage(int tn) {
     Stage st;
     st.kind = Stage::Memset;
@@ -1444,7 +1454,7 @@ struct Builder {
   // the perfect-nest pointwise assignments that directly follow position `from`
   std::vector<Follower> followers_after(const std::vector<StmtP>& flat, size_t from) {
     std::vector<Follower> out;
-    for (size_t k = from; k < flat.size() && out.size() < 4; ++k) {
+    for (size_t k = from; k < flat.size() && out.size() < 8; ++k) {
       Follower f;
       const Stmt* b = flat[k].get();
       while (b->kind == Stmt::For) {
@@ -1579,6 +1589,7 @@ struct Builder {
           if (body->kind == Stmt::Set && body->tn == s->tn &&
               match_gemm(code.prog, nest, *body, true, opt, followers_after(flat, i + 2), &n_fused, &g)) {
             if (g.gemm.split_k > 1) memset_stage(s->tn);   // partial tiles are added to the zeroed node
+            assign_epilogue_scratch(g);
             g.kernel = kernel_name();
             g.gemm_source = gemm_translation_unit(code.prog, g, g.kernel, opt);
             code.stages.push_back(g);
@@ -1628,6 +1639,7 @@ struct Builder {
           for (int f = 0; f < n_fused; ++f) zeroed.erase(fol[(size_t)f].set->tn);
           // beta = 0 over the whole node: the zero_out before it has no reader left
           if (was_zero && !g.gemm.accumulate && g.gemm.split_k == 1 && covers_node(*body, nest)) drop_zero_out(body->tn);
+          assign_epilogue_scratch(g);
           g.kernel = kernel_name();
           g.gemm_source = gemm_translation_unit(code.prog, g, g.kernel, opt);
           code.stages.push_back(g);

@@ -65,6 +65,8 @@ struct Stage {
   int smem_bytes = 0;            // dynamic shared memory of the contraction kernel
   int epi_out_bytes = 4;         // widest element the epilogue stores through the staging tile (2 or 4)
   int epi_tiles = 0;             // register tiles (inputs + outputs) the epilogue keeps per chunk
+  int row_followers = 0;         // assignments over whole output rows evaluated in the epilogue (the tile is one chunk wide)
+  size_t epi_scratch_bytes = 0;  // >0: the epilogue ends in a grid-wide sum; per-warp partials + ticket live in scratch
   std::string note;              // human-readable classification, for debug info
   std::vector<int> origins;      // indices of the routine's top-level statements this stage runs
 };

@@ -256,7 +256,9 @@ static std::string unop_plain(Prec prec, const std::string& op, const std::strin
   if (op == "recip_sqrt") return "(" + one + " / " + (dbl ? "sqrt(" : "sqrtf(") + v + "))";
   if (op == "neg") return "(-(" + v + "))";
   if (op == "trunc") return dbl ? "trunc(" + v + ")" : "truncf(" + v + ")";
-  if (op == "tanh") return dbl ? "tanh(" + v + ")" : "tanhf(" + v + ")";
+  // the reference spells tanh `tanhf(` for every floating precision, double included
+  // (arrayjit/lib/ops.ml:765-769): a double argument is narrowed, the float result widened
+  if (op == "tanh") return dbl ? "(double)tanhf((float)(" + v + "))" : "tanhf(" + v + ")";
   if (op == "not") return "(" + v + " == " + zero + " ? " + one + " : " + zero + ")";
   throw Error(-4, "unsupported unary operation '" + op + "'");
 }
@@ -400,6 +402,29 @@ Emitter::Res Emitter::scalar(Prec prec, const Scalar& e) {
         if (f != forwarded.end() && same_indices(f->second.first, e.idcs)) {
           r.expr = cv.first + f->second.second + cv.second;
           return r;
+        }
+        for (auto& rf : row_forwards) {
+          if (rf.tn != e.tn || rf.idcs.size() != e.idcs.size()) continue;
+          bool ok = true;
+          std::string sub;
+          for (size_t a = 0; ok && a < e.idcs.size(); ++a) {
+            Index x = e.idcs[a];
+            if ((int)a == rf.n_axis) {
+              if (x.kind == Index::Iter) sub = "[" + x.sym + "]";
+              else if (x.kind == Index::Fixed) sub = "[" + std::to_string(x.fixed) + "]";
+              else ok = false;
+            } else {
+              if (x.kind == Index::Iter) {
+                auto it = row_ren.find(x.sym);
+                if (it != row_ren.end()) x.sym = it->second;
+              }
+              ok = same_index(x, rf.idcs[a]);
+            }
+          }
+          if (ok) {
+            r.expr = cv.first + rf.name + sub + cv.second;
+            return r;
+          }
         }
         if (t.mode == Mode::Virtual) throw Error(-3, "b200ir: read of virtual node '" + t.ident + "'");
         used_nodes.insert(e.tn);
@@ -549,7 +574,8 @@ std::string Emitter::stmt(const Stmt& s, int ind) {
         head = pad(ind) + "for (" + it + " " + s.index + " = " + lo + " + b200_lane; " + s.index + " <= " + hi + "; " +
                s.index + " += 32) {\n";
       } else {
-        head = pad(ind) + "for (" + it + " " + s.index + " = " + lo + "; " + s.index + " <= " + hi + "; ++" + s.index + ") {\n";
+        head = (unroll_loops ? "#pragma unroll\n" : std::string()) + pad(ind) + "for (" + it + " " + s.index + " = " + lo + "; " +
+               s.index + " <= " + hi + "; ++" + s.index + ") {\n";
       }
       return head + stmt(*s.body, ind + 2) + pad(ind) + "}\n";
     }

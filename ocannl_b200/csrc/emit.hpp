@@ -38,6 +38,19 @@ struct Emitter {
     std::string expr;
   };
   std::vector<LoadTile> load_tiles;
+  // Row forwarding (the row followers of a contraction epilogue): a thread holds one whole output
+  // row of `tn` in registers -- `name[0 .. N)` when `n_axis` >= 0, the scalar `name` otherwise.  A
+  // Get of `tn` whose other indices equal `idcs` (after renaming its symbols through `row_ren`)
+  // and whose index on `n_axis` is a loop symbol or a fixed position reads `name[that index]`.
+  struct RowForward {
+    int tn;
+    Indices idcs;
+    int n_axis;
+    std::string name;
+  };
+  std::vector<RowForward> row_forwards;
+  std::map<std::string, std::string> row_ren;
+  bool unroll_loops = false;   // `#pragma unroll` before every emitted loop (register arrays stay registers)
   // nodes whose loads may use the read-only data path
   std::set<int> readonly_nodes;
   // cooperative reductions: scope id -> lane-strided loop symbol (see compile.cpp)

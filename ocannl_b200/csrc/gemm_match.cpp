@@ -79,8 +79,21 @@ bool mac_step(const Scalar& v, const std::function<bool(const Scalar&)>& is_acc,
   return false;
 }
 
+void walk_stmt_simple(const Stmt& s, const std::function<void(const Scalar&)>& f);
+void walk_scalar_simple(const Scalar& e, const std::function<void(const Scalar&)>& f) {
+  f(e);
+  if (e.kind == Scalar::LocalScope) walk_stmt_simple(*e.body, f);
+  for (auto& a : e.args) walk_scalar_simple(*a.s, f);
+}
+void walk_stmt_simple(const Stmt& s, const std::function<void(const Scalar&)>& f) {
+  for (auto& x : s.items) walk_stmt_simple(*x, f);
+  if (s.body) walk_stmt_simple(*s.body, f);
+  if (s.value) walk_scalar_simple(*s.value, f);
+}
+
 }  // namespace
 
+static void gemm_tile_shape(const GemmPlan& g, int* bn_out, bool* pair_out);
 static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, const Stmt& set, bool zeroed_before,
                             const CompileOptions& opt, const std::vector<Follower>& followers, int* n_fused, Stage* out,
                             bool pair);
@@ -92,12 +105,29 @@ bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& 
                 const CompileOptions& opt, const std::vector<Follower>& followers, int* n_fused, Stage* out) {
   if (opt.enable_pairs) {
     Stage trial = *out;
+    int fused_pair = 0;
+    bool ok = false;
     try {
-      if (match_gemm_mode(P, nest, set, zeroed_before, opt, followers, n_fused, &trial, true)) {
-        *out = trial;
-        return true;
-      }
+      ok = match_gemm_mode(P, nest, set, zeroed_before, opt, followers, &fused_pair, &trial, true);
     } catch (const Error&) {
+    }
+    if (ok) {
+      // the one-column form is preferred when it can take whole-row assignments into the epilogue
+      Stage plain = *out;
+      int fused_plain = 0;
+      bool ok_plain = false;
+      try {
+        ok_plain = match_gemm_mode(P, nest, set, zeroed_before, opt, followers, &fused_plain, &plain, false);
+      } catch (const Error&) {
+      }
+      if (ok_plain && plain.row_followers > 0 && fused_plain > fused_pair) {
+        *out = plain;
+        *n_fused = fused_plain;
+      } else {
+        *out = trial;
+        *n_fused = fused_pair;
+      }
+      return true;
     }
   }
   return match_gemm_mode(P, nest, set, zeroed_before, opt, followers, n_fused, out, false);
@@ -584,6 +614,254 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
     produced.insert(fo.set->tn);
     ++fused;
   }
+  // ---- row followers.  When the whole output row fits one epilogue chunk (N <= 32: the logits of
+  //      a classifier), the thread that owns accumulator row m holds that row of every produced
+  //      node in registers, so assignments over whole rows can run right there: a row maximum,
+  //      `exp(x - max)`, a row sum (the softmax pieces of lib/nn_blocks.ml:137-143), each a loop
+  //      nest over the row loops with an optional trailing loop over the N columns, reading the
+  //      produced rows and anything else from memory.  A last assignment may sum over ALL rows and
+  //      columns (the mean cross-entropy): every epilogue warp leaves the partial sum of its 32
+  //      rows in scratch, the warp that takes the last ticket adds the partials in slot order -- a
+  //      fixed order, so the value does not depend on scheduling -- and evaluates the assignment.
+  struct RowNode {
+    int tn;
+    Indices canon;      // indices in this stage's symbols
+    int n_axis;         // axis carrying the n symbol, -1 for one value per row
+    std::string name;   // register array / scalar
+    bool from_main;     // the main output's tile (already stored by the column loop's store path)
+  };
+  std::vector<RowNode> rownodes;
+  std::string row_code, row_decls, row_stores, final_code;
+  std::set<int> row_written;   // nodes the row followers write
+  int row_fused = 0;
+  size_t scratch_bytes = 0;
+  const int64_t N = g.n.extent;
+  {
+    std::vector<LoopDim> row_loops;
+    for (auto& d : free_loops) {
+      bool is_n = false;
+      for (auto& sy : dn.syms) is_n = is_n || sy.first == d.sym;
+      if (!is_n) row_loops.push_back(d);
+    }
+    int bn_t;
+    bool pair_t;
+    gemm_tile_shape(g, &bn_t, &pair_t);
+    bool can = !pair && !reds && !(form_b && g.accumulate) && n_syms == 1 && N <= 32 && bn_t <= 32 && !pair_t && outs[0].unit_n;
+    if (can) {
+      int na = -1;
+      for (size_t a = 0; a < set.idcs.size(); ++a)
+        if (set.idcs[a].kind == Index::Iter && set.idcs[a].sym == n_sym) na = (int)a;
+      rownodes.push_back({set.tn, set.idcs, na, outs[0].arr, true});
+      can = na >= 0;
+    }
+    std::set<int> row_produced;
+    for (auto& o : outs) row_produced.insert(o.tn);
+    for (size_t fi = (size_t)fused; can && fi < followers.size(); ++fi) {
+      if (outs.size() != 1) break;   // only directly after the contraction's own assignment
+      const Follower& fo = followers[fi];
+      if (!fo.set || fo.set->kind != Stmt::Set || fo.set->vec_len > 0) break;
+      const bool global = fo.nest.empty();
+      std::map<std::string, std::string> ren;     // follower symbol -> this stage's symbol
+      std::set<std::string> col_syms;             // follower symbols that run over the N columns
+      std::string col_loop;                       // the follower's own trailing column loop, if any
+      bool ok = true;
+      if (!global) {
+        if (fo.nest.size() != row_loops.size() && fo.nest.size() != row_loops.size() + 1) break;
+        for (size_t i = 0; i < row_loops.size(); ++i) {
+          if (fo.nest[i].from != 0 || fo.nest[i].extent() != row_loops[i].extent()) ok = false;
+          ren[fo.nest[i].sym] = row_loops[i].sym;
+        }
+        if (fo.nest.size() == row_loops.size() + 1) {
+          const LoopDim& c = fo.nest.back();
+          if (c.from != 0 || c.extent() != N) ok = false;
+          col_loop = c.sym;
+          col_syms.insert(c.sym);
+        }
+      }
+      if (!ok) break;
+      // local scopes: `[v := neutral;] for c' < N { v := v op term }`; the global form sums over
+      // (row loops, c')
+      const Scalar* gscope = nullptr;
+      std::vector<const Scalar*> scopes;
+      std::function<void(const Scalar&)> find_scopes = [&](const Scalar& e) {
+        if (e.kind == Scalar::LocalScope) { scopes.push_back(&e); return; }
+        for (auto& a : e.args) find_scopes(*a.s);
+      };
+      find_scopes(*fo.set->value);
+      if (global && scopes.size() != 1) break;
+      std::vector<LoopDim> gloops;
+      const Stmt* gstep = nullptr;
+      for (auto* sc : scopes) {
+        const Stmt* b = sc->body.get();
+        if (b->kind == Stmt::Seq) {
+          if (b->items.size() != 2 || b->items[0]->kind != Stmt::SetLocal || b->items[0]->value->kind != Scalar::Const) { ok = false; break; }
+          b = b->items[1].get();
+        }
+        std::vector<LoopDim> red;
+        while (b->kind == Stmt::For) { red.push_back({b->index, b->from, b->to}); b = b->body.get(); }
+        if (b->kind != Stmt::SetLocal || b->scope_id != sc->scope_id) { ok = false; break; }
+        bool nested = false;
+        walk_scalar_simple(*b->value, [&](const Scalar& x) { if (x.kind == Scalar::LocalScope) nested = true; });
+        if (nested) { ok = false; break; }
+        if (global) {
+          if (red.size() != row_loops.size() + 1) { ok = false; break; }
+          for (size_t i = 0; i < row_loops.size(); ++i) {
+            if (red[i].from != 0 || red[i].extent() != row_loops[i].extent()) ok = false;
+            ren[red[i].sym] = row_loops[i].sym;
+          }
+          if (red.back().from != 0 || red.back().extent() != N) ok = false;
+          col_syms.insert(red.back().sym);
+          // the step must be a plain sum: v := v + term / term + v / fma(a, b, v), from zero
+          const Scalar& v = *b->value;
+          auto is_self = [&](const Scalar& e) { return e.kind == Scalar::GetLocal && e.scope_id == sc->scope_id; };
+          bool sum = (v.kind == Scalar::Bin && v.op == "add" && (is_self(*v.args[0].s) != is_self(*v.args[1].s))) ||
+                     (v.kind == Scalar::Tern && v.op == "fma" && is_self(*v.args[2].s));
+          const Stmt* sb = sc->body.get();
+          if (sb->kind == Stmt::Seq && sb->items[0]->value->cval != 0.0) sum = false;
+          if (!sum || P.tn(sc->tn).prec != Prec::Single) ok = false;
+          gscope = sc;
+          gloops = red;
+          gstep = b;
+        } else {
+          if (red.size() != 1 || red[0].from != 0 || red[0].extent() != N) { ok = false; break; }
+          col_syms.insert(red[0].sym);
+        }
+      }
+      if (!ok) break;
+      // reads: produced nodes only row-locally; no merge buffer; a read of the written node is out
+      auto chk = [&](const Scalar& e) {
+        if (e.kind == Scalar::GetMerge) ok = false;
+        if (e.kind == Scalar::Get || e.kind == Scalar::GetDyn) {
+          if (e.tn == fo.set->tn) ok = false;
+          if (row_produced.count(e.tn)) {
+            const RowNode* rn = nullptr;
+            for (auto& r : rownodes) if (r.tn == e.tn) rn = &r;
+            if (e.kind != Scalar::Get || !rn || e.idcs.size() != rn->canon.size()) { ok = false; return; }
+            for (size_t a = 0; a < e.idcs.size(); ++a) {
+              Index x = e.idcs[a];
+              if ((int)a == rn->n_axis) {
+                if (!(x.kind == Index::Fixed && x.fixed >= 0 && x.fixed < N) && !(x.kind == Index::Iter && col_syms.count(x.sym))) ok = false;
+              } else {
+                if (x.kind == Index::Iter && ren.count(x.sym)) x.sym = ren[x.sym];
+                const Index& y = rn->canon[a];
+                if (x.kind != y.kind || x.sym != y.sym || x.fixed != y.fixed || x.terms != y.terms) ok = false;
+              }
+            }
+          }
+        }
+      };
+      walk_scalar_simple(*fo.set->value, chk);
+      if (!ok || row_produced.count(fo.set->tn) || em.used_nodes.count(fo.set->tn)) break;
+      const Tnode& T = P.tn(fo.set->tn);
+      if (T.mode == Mode::Virtual || T.prec == Prec::Uint4x32) break;
+      if (global) {
+        // written position: fixed indices only
+        for (auto& ix : fo.set->idcs) if (ix.kind != Index::Fixed) ok = false;
+        if (!ok) break;
+        em.row_ren = ren;
+        em.row_forwards.clear();
+        for (auto& r : rownodes) em.row_forwards.push_back({r.tn, r.canon, r.n_axis, r.name});
+        em.unroll_loops = true;
+        std::string code = "  {\n    float b200_part = 0.0f;\n    if (b200_row_ok) {\n";
+        for (size_t i = 0; i < row_loops.size(); ++i)
+          if (gloops[i].sym != row_loops[i].sym)
+            code += "      const unsigned int " + gloops[i].sym + " = " + row_loops[i].sym + ";\n";
+        em.scope_subst[gscope->scope_id] = "b200_part";
+        code += "#pragma unroll\n      for (unsigned int " + gloops.back().sym + " = 0; " + gloops.back().sym + " < " + std::to_string(N) + "u; ++" +
+                gloops.back().sym + ") {\n" + em.stmt(*gstep, 8) + "      }\n    }\n";
+        // per-warp partial, ticket, ordered combine by the last warp
+        code += "    b200_part = b200_warp_sum(b200_part);\n"
+                "    float* b200_slots = (float*)b200_partials;\n"
+                "    unsigned int* b200_ticket = (unsigned int*)(b200_partials + 4ull * b200_nslots);\n"
+                "    unsigned int b200_last = 0u;\n"
+                "    if (b200_lane == 0u) {\n      b200_slots[b200_slot] = b200_part;\n      __threadfence();\n"
+                "      b200_last = atomicAdd(b200_ticket, 1u) == b200_nslots - 1u ? 1u : 0u;\n    }\n"
+                "    b200_last = __shfl_sync(0xffffffffu, b200_last, 0);\n"
+                "    if (b200_last) {\n      __threadfence();\n      float b200_total = 0.0f;\n"
+                "      for (unsigned int b200_i = b200_lane; b200_i < b200_nslots; b200_i += 32u) b200_total += ((volatile float*)b200_slots)[b200_i];\n"
+                "      b200_total = b200_warp_sum(b200_total);\n      if (b200_lane == 0u) {\n";
+        em.scope_subst[gscope->scope_id] = "b200_total";
+        Emitter::Res v = em.scalar(T.prec, *fo.set->value);
+        if (!v.defs.empty()) { em.scope_subst.erase(gscope->scope_id); break; }
+        em.used_nodes.insert(fo.set->tn);
+        row_written.insert(fo.set->tn);
+        code += "        " + T.ident + "[" + em.offset(fo.set->idcs, T.dims) + "] = " + Emitter::store_wrap(T.prec, v.expr) + ";\n"
+                "        *b200_ticket = 0u;\n      }\n    }\n  }\n";
+        em.scope_subst.erase(gscope->scope_id);
+        em.unroll_loops = false;
+        final_code = code;
+        // slots: one per epilogue warp of every tile (4 warps per 128-row tile)
+        long long tiles = (g.m.extent + 127) / 128;
+        for (auto& b : g.batch) tiles *= b.extent;
+        scratch_bytes = (size_t)tiles * 4 * 4 + 16;
+        ++row_fused;
+        break;   // the global sum ends the epilogue
+      }
+      // written position: every row symbol once, the column loop at most once, fixed otherwise
+      Indices canon = fo.set->idcs;
+      int na = -1;
+      {
+        std::map<std::string, int> seen;
+        for (size_t a = 0; a < canon.size(); ++a) {
+          Index& ix = canon[a];
+          if (ix.kind == Index::Fixed) continue;
+          if (ix.kind != Index::Iter) { ok = false; break; }
+          if (!col_loop.empty() && ix.sym == col_loop) { if (na >= 0) ok = false; na = (int)a; ix.sym = n_sym; continue; }
+          auto it = ren.find(ix.sym);
+          if (it == ren.end()) { ok = false; break; }
+          ix.sym = it->second;
+          if (++seen[ix.sym] > 1) ok = false;
+        }
+        for (auto& d : row_loops) if (d.extent() > 1 && !seen.count(d.sym)) ok = false;
+        if (!col_loop.empty() && na < 0) ok = false;
+      }
+      if (!ok) break;
+      const std::string name = "b200_f" + std::to_string(fo.set->tn);
+      em.row_ren = ren;
+      em.row_forwards.clear();
+      for (auto& r : rownodes) em.row_forwards.push_back({r.tn, r.canon, r.n_axis, r.name});
+      em.unroll_loops = true;
+      const auto saved_redirect = em.set_redirect;
+      em.set_redirect[fo.set->tn] = {fo.set->idcs, na >= 0 ? name + "[" + col_loop + "]" : name};
+      std::string code = "    {\n";
+      for (size_t i = 0; i < row_loops.size(); ++i)
+        if (fo.nest[i].sym != row_loops[i].sym)
+          code += "      const unsigned int " + fo.nest[i].sym + " = " + row_loops[i].sym + ";\n";
+      std::string st_text = em.stmt(*fo.set, 8);
+      if (na >= 0)
+        code += "#pragma unroll\n      for (unsigned int " + col_loop + " = 0; " + col_loop + " < " + std::to_string(N) + "u; ++" + col_loop +
+                ") {\n" + st_text + "      }\n";
+      else
+        code += st_text;
+      code += "    }\n";
+      em.set_redirect = saved_redirect;
+      em.unroll_loops = false;
+      em.used_nodes.insert(fo.set->tn);
+      row_decls += std::string("  ") + Emitter::rtype(T.prec) + " " + name + (na >= 0 ? "[" + std::to_string(N) + "]" : std::string()) + ";\n";
+      row_code += code;
+      // the node's store: a thread writes its own row
+      {
+        Indices at = canon;
+        if (na >= 0) { at[(size_t)na].kind = Index::Fixed; at[(size_t)na].fixed = 0; at[(size_t)na].sym.clear(); }
+        const std::string off = em.offset(at, T.dims);
+        if (na >= 0) {
+          int64_t stride = 1;
+          for (size_t a = (size_t)na + 1; a < T.dims.size(); ++a) stride *= T.dims[a];
+          row_stores += "#pragma unroll\n    for (unsigned int b200_c = 0; b200_c < " + std::to_string(N) + "u; ++b200_c) " + T.ident + "[(" + off +
+                        ") + b200_c * " + std::to_string(stride) + "u] = " + Emitter::store_wrap(T.prec, name + "[b200_c]") + ";\n";
+        } else {
+          row_stores += "    " + T.ident + "[" + off + "] = " + Emitter::store_wrap(T.prec, name) + ";\n";
+        }
+      }
+      rownodes.push_back({fo.set->tn, canon, na, name, false});
+      row_produced.insert(fo.set->tn);
+      row_written.insert(fo.set->tn);
+      ++row_fused;
+    }
+    em.row_forwards.clear();
+    em.row_ren.clear();
+  }
+  fused += row_fused;
   *n_fused = fused;
   if (pair_fail) return false;
 
@@ -595,13 +873,14 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
     if (!em.used_nodes.count(t.id) || t.mode == Mode::Virtual) continue;
     bool written = false;
     for (auto& o : outs) written |= o.tn == t.id;
+    written |= row_written.count(t.id) > 0;
     params += std::string(", ") + (written ? "" : "const ") + Emitter::ctype(t.prec) + "* " + (written ? "" : "__restrict__ ") + t.ident;
     args += ", " + t.ident;
     kargs.push_back({KArg::Node, t.id});
   }
   std::string statics_prologue;
   {
-    std::string text = body + load_code;
+    std::string text = body + load_code + row_code + final_code;
     for (size_t i = 0; i < P.statics.size(); ++i) {
       const std::string& s = P.statics[i].sym;
       size_t p = 0;
@@ -621,9 +900,14 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
       kargs.push_back({KArg::Statics, -1});
     }
   }
+  if (scratch_bytes) {
+    params += ", unsigned char* b200_partials";
+    args += ", b200_partials";
+    kargs.push_back({KArg::Scratch, 0});   // the planner assigns the offset into the routine's reduction scratch
+  }
   if (em.uses_merge) return false;
 
-  std::string row_code;
+  std::string ptr_code;
   for (auto& o : outs) {
     const Tnode& t = P.tn(o.tn);
     const int ebytes = prec_bytes(t.prec);
@@ -631,7 +915,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
     const std::string G = std::string("(B200_EPI_CHUNK / ") + (ebytes == 4 ? "4" : "8") + ")";
     const std::string member = "r" + std::to_string(o.tn);
     tile_decls += "  unsigned long long " + member + "[" + G + "];\n";
-    row_code += "  {\n#ifdef B200_DEBUG_NO_GLOBAL_STORE\n    const unsigned long long b200_pv = 0ull;\n#else\n"
+    ptr_code += "  {\n#ifdef B200_DEBUG_NO_GLOBAL_STORE\n    const unsigned long long b200_pv = 0ull;\n#else\n"
                 "    const unsigned long long b200_pv = b200_row_ok ? (unsigned long long)(" + t.ident + " + (" + o.row_off +
                 ")) : 0ull;\n#endif\n#pragma unroll\n    for (int it = 0; it < " + G + "; ++it) b200_t." + member +
                 "[it] = __shfl_sync(0xffffffffu, b200_pv, it * (32 / " + G + ") + b200_lane / " + G + ");\n  }\n";
@@ -659,13 +943,13 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
     // of the row this lane writes in store step `it` (0 for rows beyond M).
     fn << "__device__ __forceinline__ void b200_epilogue_rows(b200_in_tiles& b200_t, unsigned int b200_b0, unsigned int b200_b1, "
           "unsigned int b200_m, bool b200_row_ok" << params << ") {\n";
-    if (!row_code.empty()) {
+    if (!ptr_code.empty()) {
       fn << statics_prologue << "  const unsigned int b200_lane = threadIdx.x & 31u;\n";
       ep.str("");
       if (gb.size() == 2) { recover(gb[0], "b200_b0"); recover(gb[1], "b200_b1"); }
       else if (gb.size() == 1) { recover(gb[0], "b200_b1"); }
       recover(dm, "b200_m");
-      fn << ep.str() << unit_syms << row_code;
+      fn << ep.str() << unit_syms << ptr_code;
       ep.str("");
     }
     fn << "}\n";
@@ -692,7 +976,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
      << "__device__ __forceinline__ void b200_tmem_ld_chunk(unsigned int taddr, unsigned int* r);\n"
      << "__device__ __forceinline__ void b200_epilogue_row(unsigned int* b200_r, unsigned int b200_b0, unsigned int b200_b1, "
         "unsigned int b200_m, bool b200_row_ok, unsigned int b200_n0, unsigned int b200_N, uint4* b200_stage, "
-        "bool b200_has_next, unsigned int b200_next_taddr, b200_in_tiles& b200_t"
+        "bool b200_has_next, unsigned int b200_next_taddr, b200_in_tiles& b200_t, unsigned int b200_slot, unsigned int b200_nslots"
      << params << ") {\n"
      << statics_prologue;
   fn << "  const unsigned int b200_lane = threadIdx.x & 31u;\n";
@@ -798,7 +1082,12 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
       fn << ep.str() << "      " << t.ident << "[" << em.offset(o.idcs, t.dims) << "] = " << Emitter::store_wrap(t.prec, o.arr + "[b200_j]") << ";\n    }\n  }\n";
     }
   }
-  fn << "#endif\n  B200_TRE(15);\n}\n";
+  fn << "#endif\n";
+  // row followers: assignments over whole rows, from the register tiles; then the rows' stores
+  fn << row_decls;
+  if (!row_code.empty()) fn << "  if (b200_row_ok) {\n" << row_code << row_stores << "  }\n";
+  fn << final_code;
+  fn << "  B200_TRE(15);\n}\n";
 
   out->kind = Stage::Gemm;
   out->gemm = g;
@@ -810,6 +1099,8 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   for (auto& o : outs) out->epi_out_bytes = std::max(out->epi_out_bytes, std::min(4, prec_bytes(P.tn(o.tn).prec)));
   out->epi_params = params;
   out->epi_args = args;
+  out->row_followers = row_fused;
+  out->epi_scratch_bytes = scratch_bytes;
   return true;
 }
 
@@ -870,6 +1161,7 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   // is latency-bound) but more registers
   int chunk = (bn >= 32 && st.epi_tiles <= 2) ? 32 : 16;
   if (const char* ov = getenv("B200_EPI_CHUNK")) chunk = atoi(ov);
+  if (st.row_followers > 0) chunk = bn;   // the whole row in one chunk
   const bool light = false;  // 16 warps measured slower: the register cap (96) makes the epilogue spill
   int epi_warps = light ? 16 : (bn >= 128 ? 8 : 4);
   if (const char* ov = getenv("B200_GEMM_EPI_WARPS")) {
@@ -909,12 +1201,15 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   o << "#define B200_EPI_PARAMS " << params << "\n";
   o << "#define B200_EPILOGUE_ROWS b200_epilogue_rows(b200_tiles, b200_b0, b200_b1, b200_m, b200_m < shape.M" << args << ");\n";
   o << "#define B200_EPILOGUE_LOAD b200_epilogue_load(b200_tiles, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_pn0, shape.N" << args << ");\n";
-  o << "#define B200_EPILOGUE_ROW b200_epilogue_row(b200_r, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_n0, shape.N, b200_stage, b200_has_next, b200_next_taddr, b200_tiles" << args << ");\n";
+  o << "#define B200_EPILOGUE_ROW b200_epilogue_row(b200_r, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_n0, shape.N, b200_stage, b200_has_next, b200_next_taddr, b200_tiles, b200_slot, b200_nslots" << args << ");\n";
   o << kGemmSource << "\n";
   std::ostringstream note;
   note << "tcgen05 " << bm << "x" << bn << "x" << bk << (pair ? " (CTA pair, cta_group::2)" : "") << " stages=" << stages
        << " epi_warps=" << epi_warps << (g.split_k > 1 ? " split_k=" + std::to_string(g.split_k) : std::string())
-       << (g.accumulate ? " beta=1" : "");
+       << (g.accumulate ? " beta=1" : "")
+       << (st.row_followers ? " + " + std::to_string(st.row_followers) + " whole-row assignments in the epilogue" +
+                                  (st.epi_scratch_bytes ? " (the last one a grid-wide sum)" : "")
+                            : std::string());
   st.note = note.str();
   // remembered for the launcher
   st.block = 64 + 32 * epi_warps;

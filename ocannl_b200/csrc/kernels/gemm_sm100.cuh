@@ -445,6 +445,9 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
       const unsigned int nt = r / rows;
       const unsigned int b200_b0 = bidx / shape.B1, b200_b1 = bidx - b200_b0 * shape.B1;
       const unsigned int b200_m = mt * B200_BM + cta_rank * B200_CTA_M + quarter * 32u + lane;
+      // one scratch slot per (tile, CTA, epilogue warp) for epilogues that end in a grid-wide sum
+      const unsigned int b200_slot = (tile * (1u + B200_CTA_PAIR) + cta_rank) * B200_EPI_WARPS + ew;
+      const unsigned int b200_nslots = total_tiles * (1u + B200_CTA_PAIR) * B200_EPI_WARPS;
       // while the tensor cores are still busy with this tile, load the epilogue's operands (bias,
       // mask, residual rows ...) of the first chunk this warp owns
       b200_in_tiles b200_tiles;

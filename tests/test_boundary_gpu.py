@@ -62,12 +62,19 @@ def test_mlp_links_at_element_aligned_offsets(device):
     rt.run()
     device.await_()
     got = _outputs(rt, ir)
+    prec_of = {t.ident: t.prec for t in ir.params()}
     grads = [t.ident for t in ir.params() if t.ident.endswith("_grad")]
     rest = [t.ident for t in ir.params() if not t.ident.endswith("_grad")]
     compare(ir, got, want, rtol=2e-2, atol=2e-3, only=rest)
     for g in grads:
-        scale = float(np.abs(W.load(next(t.prec for t in ir.params() if t.ident == g), want[g])).max())
-        compare(ir, got, want, rtol=2e-2, atol=5e-2 * max(scale, 1e-30), only=[g])
+        w_ = W.load(prec_of[g], want[g]).astype(np.float64).reshape(-1)
+        g_ = W.load(prec_of[g], got[g]).astype(np.float64).reshape(-1)
+        scale = float(np.abs(w_).max())
+        bad = np.abs(g_ - w_) > 2e-2 * np.abs(w_) + 5e-2 * max(scale, 1e-30)
+        # a relu gate whose activation rounds to zero on one side only switches a whole element of a
+        # bf16 activation gradient on or off: tolerated for one element in ten thousand
+        allowed = 1e-4 * w_.size if prec_of[g] == "bfloat16" else 0
+        assert bad.sum() <= allowed, (g, int(bad.sum()), w_.size)
     _free(device, rt, code)
 
 

