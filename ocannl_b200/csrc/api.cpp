@@ -401,6 +401,7 @@ int b200_compile(const char* name, const char* ir, size_t len, const char* optio
         else if (k == "fuse") opt.enable_fuse = on;
         else if (k == "pairs") opt.enable_pairs = on;
         else if (k == "splitk") opt.enable_splitk = on;
+        else if (k == "tf32") opt.enable_tf32 = on;
         else if (k == "large_models") opt.large_models = on;
         else throw Error(B200_E_INVALID, "unknown compile option '" + k + "'");
       }

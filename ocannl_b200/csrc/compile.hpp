@@ -39,6 +39,7 @@ struct GemmPlan {
   bool a_kmajor = true, b_kmajor = true;
   bool accumulate = false;           // beta = 1: add to the existing output (form B without zero_out)
   Prec in_prec = Prec::Bfloat16;     // operand precision (bf16 / half; single runs as tf32)
+  bool may_split = false;            // an fp32 accumulation whose K may be cut into work units (see split_k)
   int split_k = 1;                   // >1: that many work units per tile, each over a slice of K, added with vector reds
   std::string epilogue;              // generated device code, see codegen
   double flops() const;
@@ -92,6 +93,7 @@ struct CompileOptions {
   bool enable_fuse = true;   // several small stages in one single-block kernel
   bool enable_splitk = true; // few-tile accumulations split K over the idle SMs (fp32 atomic adds: order not fixed)
   bool enable_pairs = true;  // contraction epilogues over pairs of columns with packed 16-bit arithmetic
+  bool enable_tf32 = true;   // single-precision operands of a contraction go through the tensor cores as tf32
   bool large_models = false;
   // Top-level statements (by index) that must not use the forms with alignment demands: the pair
   // form of generic stages (8-byte accesses) / the TMA-fed contraction kernel (16-byte operand

@@ -57,8 +57,11 @@ static void encode_operand(CUtensorMap* map, CUdeviceptr base, Prec prec, bool k
       strides[slot - 1] = (cuuint64_t)batch_stride[i] * eb;
     }
   }
+  // an m/n-major operand of 32-bit elements must lie in shared memory with 32-byte swizzle atoms
+  // (see the descriptor notes in kernels/gemm_sm100.cuh); everything else with 16-byte atoms
+  const CUtensorMapSwizzle swz = (!kmajor && eb == 4) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
   CUresult r = cu().cuTensorMapEncodeTiled_(map, dt, 4, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                            swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     throw Error(B200_E_UNSUPPORTED, "the operand layout of a contraction cannot be described to the TMA unit (CUresult " +

@@ -8,7 +8,9 @@
 //   B. materialised accumulate:
 //        [zero_out t;] for f.., k.. { t[f..] := fma(x[..], y[..], t[f..]) }
 // A loop symbol is a batch axis when both operands carry it, an M (N) axis when only the
-// first (second) operand carries it, and a K axis when it is reduced.  Anything else —
+// first (second) operand carries it, and a K axis when it is reduced.  Operands are bf16 or
+// half pairs, or single-precision pairs that the tensor cores read as tf32 (`tf32=0` keeps those
+// on the exact generic path).  Anything else —
 // affine or static indices in the operands, mixed operand precisions, an accumulator that
 // is not fp32 (the cc backend would round every step, arrayjit/lib/cc_backend.ml:169-186),
 // strides the tensor maps cannot express — is left to the generic loop-nest kernels.
@@ -210,7 +212,9 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   if (x->kind != Scalar::Get || y->kind != Scalar::Get) return false;
   const Tnode &X = P.tn(x->tn), &Y = P.tn(y->tn);
   if (X.prec != Y.prec) return false;
-  if (!(X.prec == Prec::Bfloat16 || X.prec == Prec::Half)) return false;
+  // bf16 / half operands (kind::f16) or, unless switched off, single-precision operands read as tf32
+  // (kind::tf32: the tensor cores use the upper 19 bits of each operand, products are summed in fp32)
+  if (!(X.prec == Prec::Bfloat16 || X.prec == Prec::Half || (X.prec == Prec::Single && opt.enable_tf32))) return false;
   if (X.mode == Mode::Virtual || Y.mode == Mode::Virtual) return false;
 
   // ---- strides
@@ -517,7 +521,10 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   }
   std::string body;
   add_out(set.tn, set.idcs);
-  if (form_b && opt.enable_splitk && outs[0].unit_n) g.split_k = gemm_split_k(g);
+  if (form_b && opt.enable_splitk && outs[0].unit_n) {
+    g.may_split = true;
+    g.split_k = gemm_split_k(g);
+  }
   const bool reds = g.split_k > 1;   // partial tiles are added to the output instead of stored
   if (form_b) {
     const Tnode& t = D;
@@ -1105,24 +1112,67 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
 }
 
 // Tile shape of a contraction: columns per tile, and whether two CTAs share a 256-row tile.
+//
+// One tcgen05.mma of K = 16 takes about 128 cycles whether the tile is 16 or 256 columns wide (the
+// A operand's 128 rows come out of shared memory at 32 bytes per clock), so a k block costs the
+// same ~0.26 us for every shape and wide tiles do more work in it: large problems want the widest
+// tile.  A problem of few tiles is different: its time is one tile's main loop plus one tile's
+// epilogue, and the epilogue shrinks with the tile (about 3.7 us for 128 rows x 256 columns).  The
+// choice minimises  waves x k blocks x 0.26 us + 3.7 us x columns / 256  over the shapes the
+// operands allow; 148 SMs are assumed (compilation knows no device).
 static void gemm_tile_shape(const GemmPlan& g, int* bn_out, bool* pair_out) {
   const int eb = prec_bytes(g.in_prec);
   const int row_elems = 128 / eb;
-  int bn;
-  if (g.n.extent >= 256) bn = 256;
-  else bn = (int)((g.n.extent + 15) / 16 * 16);
-  if (!g.b_kmajor) bn = (bn + row_elems - 1) / row_elems * row_elems;
-  if (bn > 256) bn = 256;
+  int bn0;
+  if (g.n.extent >= 256) bn0 = 256;
+  else bn0 = (int)((g.n.extent + 15) / 16 * 16);
+  if (!g.b_kmajor) bn0 = (bn0 + row_elems - 1) / row_elems * row_elems;
+  if (bn0 > 256) bn0 = 256;
   if (const char* ov = getenv("B200_GEMM_BN")) {   // developer override for tile-shape experiments
     const int want = atoi(ov);
-    if (want >= 16 && want <= 256 && want % 16 == 0 && want <= bn && (g.b_kmajor || want % row_elems == 0)) bn = want;
+    if (want >= 16 && want <= 256 && want % 16 == 0 && want <= bn0 && (g.b_kmajor || want % row_elems == 0)) {
+      bool pair = g.m.extent >= 256 && want >= 64 && want % 32 == 0 && (g.b_kmajor || (want / 2) % row_elems == 0);
+      if (const char* pv = getenv("B200_GEMM_PAIR")) pair = pair && pv[0] != '0';
+      *bn_out = want;
+      *pair_out = pair;
+      return;
+    }
   }
-  // Two CTAs per 256 x bn tile when the problem has at least one full pair tile of rows: each CTA
-  // then stages half of B, and the tensor cores of both SMs work from one instruction stream.
-  bool pair = g.m.extent >= 256 && bn >= 64 && bn % 32 == 0 && (g.b_kmajor || (bn / 2) % row_elems == 0);
-  if (const char* ov = getenv("B200_GEMM_PAIR")) pair = pair && ov[0] != '0';
-  *bn_out = bn;
-  *pair_out = pair;
+  long long batch = 1;
+  for (auto& b : g.batch) batch *= b.extent;
+  const double k_blocks = (double)((g.k.extent + row_elems - 1) / row_elems);
+  double best = 1e300;
+  int best_bn = bn0;
+  bool best_pair = false;
+  for (int pair = 1; pair >= 0; --pair) {
+    for (int bn = bn0; bn >= 16; bn = (bn > 64 ? bn / 2 : 0)) {
+      if (bn != bn0 && (bn % 64 != 0 || (!g.b_kmajor && bn % row_elems != 0))) continue;
+      // two CTAs per 256 x bn tile need a full pair tile of rows; each CTA stages half of B
+      if (pair && !(g.m.extent >= 256 && bn >= 64 && bn % 32 == 0 && (g.b_kmajor || (bn / 2) % row_elems == 0))) continue;
+      const long long bm = pair ? 256 : 128, workers = pair ? 74 : 148;
+      const long long tiles = batch * ((g.m.extent + bm - 1) / bm) * ((g.n.extent + bn - 1) / bn);
+      // few tiles over a long K: several work units per tile, each over a slice of K (gemm_split_k)
+      long long split = 1;
+      if (g.may_split && tiles * 2 <= workers) split = std::max<long long>(1, std::min<long long>({workers / tiles, (long long)k_blocks / 8, 32ll}));
+      const double waves = (double)((tiles * split + workers - 1) / workers);
+      // per k block: the MMA floor, or the delivery of the CTA's operand bytes into shared memory
+      // (sustained about 64 bytes per clock per SM: single CTAs on 128 x 256 tiles reach 54 % of the
+      // tensor peak, CTA pairs, which stage half of B each, 88 %); a CTA pair pays ~0.4 us more
+      // set-up (cluster barrier, paired tensor-memory allocation)
+      const double kb_us = std::max(0.26, (128.0 + (pair ? bn / 2 : bn)) * 128.0 / 64.0 / 1900.0);
+      const double t = waves * (k_blocks / (double)split) * kb_us + 3.7 * bn / 256.0 + (pair ? 0.4 : 0.0);
+      if (t < best - 1e-9) {
+        best = t;
+        best_bn = bn;
+        best_pair = pair != 0;
+      }
+    }
+  }
+  if (const char* ov = getenv("B200_GEMM_PAIR")) {
+    if (ov[0] == '0' && best_pair) best_pair = false;
+  }
+  *bn_out = best_bn;
+  *pair_out = best_pair;
 }
 
 // Work units per tile.  An accumulation into an fp32 node with few output tiles and a long K (the
@@ -1204,7 +1254,7 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   o << "#define B200_EPILOGUE_ROW b200_epilogue_row(b200_r, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_n0, shape.N, b200_stage, b200_has_next, b200_next_taddr, b200_tiles, b200_slot, b200_nslots" << args << ");\n";
   o << kGemmSource << "\n";
   std::ostringstream note;
-  note << "tcgen05 " << bm << "x" << bn << "x" << bk << (pair ? " (CTA pair, cta_group::2)" : "") << " stages=" << stages
+  note << "tcgen05 " << (g.in_prec == Prec::Single ? "tf32 " : "") << bm << "x" << bn << "x" << bk << (pair ? " (CTA pair, cta_group::2)" : "") << " stages=" << stages
        << " epi_warps=" << epi_warps << (g.split_k > 1 ? " split_k=" + std::to_string(g.split_k) : std::string())
        << (g.accumulate ? " beta=1" : "")
        << (st.row_followers ? " + " + std::to_string(st.row_followers) + " whole-row assignments in the epilogue" +

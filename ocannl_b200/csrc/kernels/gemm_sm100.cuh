@@ -151,17 +151,28 @@ __device__ __forceinline__ void b200_tma_load_4d(unsigned int dst, const b200_tm
 // Shared-memory matrix descriptor of tcgen05.mma for a 128-byte-swizzled tile.
 //   bits [0,14)  start address >> 4      bits [16,30) leading byte offset >> 4
 //   bits [32,46) stride byte offset >> 4 bits [46,48) descriptor version (1 on sm_100)
-//   bits [61,64) swizzle mode (2 = 128 bytes)
+//   bits [61,64) swizzle mode: 2 = 16-byte chunks swizzled within 128 bytes over 8 rows;
+//                1 = 32-byte chunks swizzled within 128 bytes over 4 rows, the only form the
+//                tensor cores read an m/n-major operand of 32-bit elements in
 __device__ __forceinline__ unsigned long long b200_smem_desc(unsigned int addr, unsigned int lbo_bytes,
-                                                             unsigned int sbo_bytes) {
+                                                             unsigned int sbo_bytes, unsigned int swizzle_mode = 2u) {
   unsigned long long d = 0;
   d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);
   d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= (unsigned long long)((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= 1ull << 46;
-  d |= 2ull << 61;
+  d |= (unsigned long long)swizzle_mode << 61;
   return d;
 }
+// m/n-major operands: 128-byte chunks of m/n, k rows 128 bytes apart in groups of 8 rows (1024
+// bytes; 4 rows, 512 bytes, for 32-bit elements), chunks one TMA box apart
+#if B200_ELEM_BYTES == 4
+#define B200_MN_GROUP_BYTES 512u
+#define B200_MN_SWIZZLE 1u
+#else
+#define B200_MN_GROUP_BYTES 1024u
+#define B200_MN_SWIZZLE 2u
+#endif
 
 __device__ __forceinline__ void b200_umma(unsigned int tmem_d, unsigned long long desc_a, unsigned long long desc_b,
                                           unsigned int idesc, unsigned int accumulate) {
@@ -388,12 +399,13 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
 #if B200_A_KMAJOR
       const unsigned long long desc_a0 = b200_smem_desc(tiles_at, 16u, 1024u);
 #else
-      const unsigned long long desc_a0 = b200_smem_desc(tiles_at, B200_ROW_ELEMS * B200_BK * B200_ELEM_BYTES, 1024u);
+      const unsigned long long desc_a0 = b200_smem_desc(tiles_at, B200_ROW_ELEMS * B200_BK * B200_ELEM_BYTES, B200_MN_GROUP_BYTES, B200_MN_SWIZZLE);
 #endif
 #if B200_B_KMAJOR
       const unsigned long long desc_b0 = b200_smem_desc(tiles_at + B200_A_TILE_BYTES, 16u, 1024u);
 #else
-      const unsigned long long desc_b0 = b200_smem_desc(tiles_at + B200_A_TILE_BYTES, B200_ROW_ELEMS * B200_BK * B200_ELEM_BYTES, 1024u);
+      const unsigned long long desc_b0 =
+          b200_smem_desc(tiles_at + B200_A_TILE_BYTES, B200_ROW_ELEMS * B200_BK * B200_ELEM_BYTES, B200_MN_GROUP_BYTES, B200_MN_SWIZZLE);
 #endif
       for (unsigned int unit = worker; live && unit < total_units; unit += n_workers) {
         const unsigned int split = unit / total_tiles;
