@@ -141,6 +141,19 @@ int b200_comm_init_rank(b200_dev* dev, int n_ranks, int rank, const char* id128,
 #define B200_F32 0
 #define B200_BF16 1
 int b200_allreduce(b200_comm* comm, int pool_id, size_t offset, size_t count, int dtype, int op);
+/* Overlap of the exchange with the backward pass.  The ranges (at most a few buckets, e.g. the
+ * gradients of the last layers and those of the first) are reduced on the communicator's own
+ * stream, each as soon as the routine's last stage that writes into it has been queued, while the
+ * remaining stages run; the compute stream waits for all of them at the end of the routine, so the
+ * optimizer step that follows sees reduced gradients.  Replaces the gradient-by-gradient
+ * owner-reduce that follows the whole backward pass in lib/parallel.ml:292-304.  n = 0 detaches. */
+int b200_routine_overlap_allreduce(b200_routine* r, b200_comm* comm, int n, const int* pool_ids,
+                                   const size_t* offsets, const size_t* counts, int dtype, int op);
+/* With a timeout (> 0 ms) b200_await polls instead of blocking: an asynchronous NCCL error
+ * (ncclCommGetAsyncError), or a stream still busy after the timeout (a rank that never arrived),
+ * aborts the communicator (ncclCommAbort) and is returned as an error; the device stays usable,
+ * the communicator does not.  No counterpart in the reference, whose shards share one process. */
+int b200_comm_set_timeout(b200_comm* comm, long long timeout_ms);
 int b200_comm_free(b200_comm* comm);
 
 /* ---- allocation-free reduction.  No counterpart in the reference: added for callers that may

@@ -1,8 +1,11 @@
 // C ABI of the backend (include/b200.h): devices, pools, copies, events, routines.
 #include "../../include/b200.h"
 
+#include <algorithm>
+#include <chrono>
 #include <cstring>
 #include <map>
+#include <thread>
 #include <memory>
 #include <mutex>
 #include <sstream>
@@ -335,11 +338,52 @@ int b200_stream_wait(b200_dev* dev, b200_event* ev) {
   });
 }
 
+// Waits for the device's stream.  When a communicator of the device carries a timeout, the wait
+// is a poll: NCCL reports a failed peer or a broken link asynchronously
+// (ncclCommGetAsyncError), and a collective whose peer never arrives would otherwise keep the
+// stream, and this call, busy for ever.  On an asynchronous error, or when the timeout passes
+// with the stream still busy, the communicator is aborted (ncclCommAbort ends its kernels) and
+// the error is returned; the device stays usable.
+static void await_polling(b200_dev* dev) {
+  long long limit = 0;
+  for (auto* c : dev->comms)
+    if (c->timeout_ms > 0 && !c->aborted) limit = limit ? std::min(limit, c->timeout_ms) : c->timeout_ms;
+  if (!limit) {
+    cu_check(cu().cuStreamSynchronize_(dev->stream), "cuStreamSynchronize");
+    return;
+  }
+  const auto t0 = std::chrono::steady_clock::now();
+  for (;;) {
+    CUresult q = cu().cuStreamQuery_(dev->stream);
+    if (q == CUDA_SUCCESS) return;
+    if (q != CUDA_ERROR_NOT_READY) cu_check(q, "cuStreamQuery");
+    const long long waited = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+    for (auto* c : dev->comms) {
+      if (c->aborted || c->timeout_ms <= 0) continue;
+      ncclResult_t async = ncclSuccess;
+      ncclResult_t r = nccl().ncclCommGetAsyncError_(c->comm, &async);
+      const bool failed = r != ncclSuccess || (async != ncclSuccess && async != ncclInProgress);
+      if (failed || waited > c->timeout_ms) {
+        nccl().ncclCommAbort_(c->comm);
+        c->aborted = true;
+        cu().cuStreamSynchronize_(dev->stream);   // the aborted collective's kernels end
+        if (failed)
+          throw Error(r != ncclSuccess ? (int)r : (int)async, std::string("NCCL reported an asynchronous error: ") +
+                                                                    nccl().ncclGetErrorString_(r != ncclSuccess ? r : async) +
+                                                                    "; the communicator was aborted");
+        throw Error(B200_E_DEVICE, "a collective did not finish within " + std::to_string(c->timeout_ms) +
+                                       " ms (is a rank missing?); the communicator was aborted");
+      }
+    }
+    std::this_thread::sleep_for(std::chrono::microseconds(200));
+  }
+}
+
 int b200_await(b200_dev* dev) {
   return guard([&] {
     if (!dev) throw Error(B200_E_INVALID, "null device");
     dev->make_current();
-    cu_check(cu().cuStreamSynchronize_(dev->stream), "cuStreamSynchronize");
+    await_polling(dev);
     dev->check_status();
   });
 }
@@ -555,12 +599,6 @@ int b200_debug_info(b200_dev* dev, char* json, size_t cap) {
 }
 
 // ------------------------------------------------------------- data parallel
-struct b200_comm {
-  b200_dev* dev = nullptr;
-  ncclComm_t comm = nullptr;
-  int n_ranks = 0, rank = 0;
-};
-
 static void nccl_check(ncclResult_t r, const char* what) {
   if (r == ncclSuccess) return;
   throw Error((int)r, std::string(what) + ": " + nccl().ncclGetErrorString_(r));
@@ -590,6 +628,8 @@ int b200_comm_init_rank(b200_dev* dev, int n_ranks, int rank, const char* id128,
     c->n_ranks = n_ranks;
     c->rank = rank;
     nccl_check(nccl().ncclCommInitRank_(&c->comm, n_ranks, id, rank), "ncclCommInitRank");
+    cu_check(cu().cuStreamCreate_(&c->stream, CU_STREAM_NON_BLOCKING), "cuStreamCreate(communicator)");
+    dev->comms.push_back(c.get());
     *out = c.release();
   });
 }
@@ -599,6 +639,7 @@ int b200_allreduce(b200_comm* comm, int pool_id, size_t offset, size_t count, in
     if (!comm) throw Error(B200_E_INVALID, "null communicator");
     if (dtype != B200_F32 && dtype != B200_BF16) throw Error(B200_E_INVALID, "bad dtype");
     if (op != B200_SUM && op != B200_AVG) throw Error(B200_E_INVALID, "bad reduction");
+    if (comm->aborted) throw Error(B200_E_INVALID, "the communicator was aborted");
     b200_dev* dev = comm->dev;
     dev->make_current();
     size_t esz = dtype == B200_F32 ? 4 : 2;
@@ -609,10 +650,65 @@ int b200_allreduce(b200_comm* comm, int pool_id, size_t offset, size_t count, in
   });
 }
 
+int b200_comm_set_timeout(b200_comm* comm, long long timeout_ms) {
+  return guard([&] {
+    if (!comm) throw Error(B200_E_INVALID, "null communicator");
+    comm->timeout_ms = timeout_ms > 0 ? timeout_ms : 0;
+  });
+}
+
+int b200_routine_overlap_allreduce(b200_routine* r, b200_comm* comm, int n, const int* pool_ids, const size_t* offsets,
+                                   const size_t* counts, int dtype, int op) {
+  return guard([&] {
+    if (!r || (n > 0 && (!comm || !pool_ids || !offsets || !counts))) throw Error(B200_E_INVALID, "null argument");
+    if (dtype != B200_F32 && dtype != B200_BF16) throw Error(B200_E_INVALID, "bad dtype");
+    if (op != B200_SUM && op != B200_AVG) throw Error(B200_E_INVALID, "bad reduction");
+    if (n > 0 && comm->dev != r->dev) throw Error(B200_E_INVALID, "the communicator belongs to another device");
+    if (n > 0 && comm->aborted) throw Error(B200_E_INVALID, "the communicator was aborted");
+    r->dev->make_current();
+    r->set_graph(false);   // a captured graph would not hold the new collectives
+    for (auto& b : r->buckets) {
+      if (b.ready) cu().cuEventDestroy_(b.ready);
+      if (b.done) cu().cuEventDestroy_(b.done);
+    }
+    r->buckets.clear();
+    r->overlap_comm = n > 0 ? comm : nullptr;
+    const Program& P = r->code->code.prog;
+    const size_t esz = dtype == B200_F32 ? 4 : 2;
+    for (int k = 0; k < n; ++k) {
+      OverlapBucket b;
+      b.pool_id = pool_ids[k];
+      b.offset = offsets[k];
+      b.count = counts[k];
+      b.dtype = dtype;
+      b.op = op;
+      const CUdeviceptr lo = r->dev->address(b.pool_id, b.offset, b.count * esz), hi = lo + b.count * esz;
+      // the last stage that writes a node overlapping the range
+      for (size_t i = 0; i < r->code->code.stages.size(); ++i)
+        for (int tn : r->code->code.stages[i].writes) {
+          auto it = r->node_ptr.find(tn);
+          if (it == r->node_ptr.end()) continue;
+          const CUdeviceptr a = it->second, e = a + (CUdeviceptr)P.tn(tn).bytes();
+          if (a < hi && lo < e) b.after_stage = (int)i;
+        }
+      cu_check(cu().cuEventCreate_(&b.ready, CU_EVENT_DISABLE_TIMING), "cuEventCreate");
+      cu_check(cu().cuEventCreate_(&b.done, CU_EVENT_DISABLE_TIMING), "cuEventCreate");
+      r->buckets.push_back(b);
+    }
+  });
+}
+
 int b200_comm_free(b200_comm* comm) {
   return guard([&] {
     if (!comm) return;
-    if (comm->comm) nccl().ncclCommDestroy_(comm->comm);
+    b200_dev* dev = comm->dev;
+    if (dev) {
+      dev->make_current();
+      for (size_t i = 0; i < dev->comms.size(); ++i)
+        if (dev->comms[i] == comm) { dev->comms.erase(dev->comms.begin() + (long)i); break; }
+    }
+    if (comm->comm && !comm->aborted) nccl().ncclCommDestroy_(comm->comm);
+    if (comm->stream) cu().cuStreamDestroy_(comm->stream);
     delete comm;
   });
 }

@@ -490,6 +490,7 @@ struct Builder {
     a.args.push_back({KArg::Scratch, (int)scratch_off});
     src << ka.str();
     a.note = "grid-wide reduction (" + std::to_string(G) + " blocks, the last one combines)";
+    a.writes = {set.tn};
     code.stages.push_back(a);
   }
 
@@ -671,6 +672,7 @@ struct Builder {
     st.note = "par=" + std::to_string(st.par.size()) + " ser=" + std::to_string(st.ser.size()) + " serial loops split over a 32x32 block" +
               (Z > 1 ? ", " + std::to_string(Z) + " slices per output group (atomic adds)" : std::string()) +
               (tiled ? ", outer loop of " + E0 + " kept in registers" : std::string()) + (pairs ? ", pairs" : std::string());
+    st.writes = {set.tn};
     code.stages.push_back(st);
     return true;
   }
@@ -924,6 +926,7 @@ struct Builder {
          << (scatter ? " scatter accumulation (atomic adds)" : "");
     st.note = note.str();
     pieces[code.stages.size()] = pc;
+    st.writes.assign(written.begin(), written.end());
     code.stages.push_back(st);
     return zero_out_dead;
   }
@@ -961,8 +964,13 @@ struct Builder {
   // training step is ~30 stages of a few hundred iterations each).
   void merge_origins(Stage& f, const std::vector<size_t>& idx) {
     std::set<int> all;
-    for (size_t i : idx) all.insert(code.stages[i].origins.begin(), code.stages[i].origins.end());
+    std::set<int> w;
+    for (size_t i : idx) {
+      all.insert(code.stages[i].origins.begin(), code.stages[i].origins.end());
+      w.insert(code.stages[i].writes.begin(), code.stages[i].writes.end());
+    }
     f.origins.assign(all.begin(), all.end());
+    f.writes.assign(w.begin(), w.end());
   }
 
   Stage emit_fused(const std::vector<size_t>& idx) {
@@ -1441,6 +1449,7 @@ struct Builder {
     st.kind = Stage::Memset;
     st.memset_tn = tn;
     st.note = "zero_out";
+    st.writes = {tn};
     code.stages.push_back(st);
   }
 

@@ -70,6 +70,7 @@ struct Stage {
   size_t epi_scratch_bytes = 0;  // >0: the epilogue ends in a grid-wide sum; per-warp partials + ticket live in scratch
   std::string note;              // human-readable classification, for debug info
   std::vector<int> origins;      // indices of the routine's top-level statements this stage runs
+  std::vector<int> writes;       // nodes the stage writes
 };
 
 // A loop nest that follows a contraction and may be folded into its epilogue.

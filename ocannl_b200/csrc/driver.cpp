@@ -93,9 +93,11 @@ void cu_check(CUresult r, const char* what) {
 const std::string& compile_cubin(const std::string& source, const std::string& name, std::string* log_out) {
   static std::mutex mu;
   static std::map<std::string, std::string> cache;
+  // the extra flags are part of what is compiled
+  const std::string key = source + "\n// flags: " + env("B200_NVRTC_FLAGS");
   {
     std::lock_guard<std::mutex> g(mu);
-    auto it = cache.find(source);
+    auto it = cache.find(key);
     if (it != cache.end()) return it->second;
   }
   NvrtcApi& n = nvrtc();
@@ -132,7 +134,7 @@ const std::string& compile_cubin(const std::string& source, const std::string& n
   n.nvrtcGetCUBIN_(prog, &cubin[0]);
   n.nvrtcDestroyProgram_(&prog);
   std::lock_guard<std::mutex> g(mu);
-  return cache.emplace(source, std::move(cubin)).first->second;
+  return cache.emplace(key, std::move(cubin)).first->second;
 }
 
 }  // namespace b200

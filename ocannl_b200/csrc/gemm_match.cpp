@@ -1100,6 +1100,9 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   out->gemm = g;
   out->gemm.epilogue = fn.str();
   out->args = kargs;
+  out->writes.clear();
+  for (auto& o : outs) out->writes.push_back(o.tn);
+  out->writes.insert(out->writes.end(), row_written.begin(), row_written.end());
   out->total = 1;
   out->epi_tiles = (int)outs.size() + n_in_tiles;
   out->epi_out_bytes = 2;

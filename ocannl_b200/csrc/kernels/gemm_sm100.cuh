@@ -359,6 +359,11 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
         // this CTA's rows of A and its share of the tile's B columns
         const int m0 = (int)(mt * B200_BM + cta_rank * B200_CTA_M), n0 = (int)(nt * B200_BN + cta_rank * B200_CTA_N);
         for (unsigned int kb = kb0; kb < kb1; ++kb) {
+#ifdef B200_INJECT_NO_LOADS
+          // failure-detection test only: the producer loads nothing, so the waits for operands can
+          // never be satisfied and must run out (no copy or MMA is ever in flight in this build)
+          continue;
+#endif
           if (!b200_wait(bar_empty + 8u * slot, phase ^ 1u, abort_flag, status, 1u)) { live = false; break; }
           // both CTAs' copies complete on the leader's barrier; the leader announces the bytes of both
           const unsigned int full = b200_map_to_cta(bar_full + 8u * slot, 0u);   // (the barrier itself when not paired)

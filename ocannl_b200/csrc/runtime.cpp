@@ -221,6 +221,25 @@ void launch_kernel(b200_dev* dev, CUfunction fn, unsigned grid, unsigned bx, uns
   cu_check(cu().cuLaunchKernelEx_(&cfg, fn, args, nullptr), what);
 }
 
+static void nccl_ok(ncclResult_t r, const char* what) {
+  if (r != ncclSuccess) throw Error((int)r, std::string(what) + ": " + nccl().ncclGetErrorString_(r));
+}
+
+// The bucket's allreduce on the communicator's stream, ordered after everything queued on the
+// compute stream so far; `done` marks its end for the join at the end of the routine.  Inside a
+// stream capture the same calls fork the communicator's stream into the graph.
+void b200_routine::enqueue_bucket(OverlapBucket& b) {
+  b200_comm* c = overlap_comm;
+  const size_t esz = b.dtype == B200_F32 ? 4 : 2;
+  CUdeviceptr p = dev->address(b.pool_id, b.offset, b.count * esz);
+  cu_check(cu().cuEventRecord_(b.ready, dev->stream), "cuEventRecord(bucket ready)");
+  cu_check(cu().cuStreamWaitEvent_(c->stream, b.ready, 0), "cuStreamWaitEvent(bucket ready)");
+  nccl_ok(nccl().ncclAllReduce_((const void*)p, (void*)p, b.count, b.dtype == B200_F32 ? ncclFloat32 : ncclBfloat16,
+                                b.op == B200_SUM ? ncclSum : ncclAvg, c->comm, (cudaStream_t)c->stream),
+          "ncclAllReduce(bucket)");
+  cu_check(cu().cuEventRecord_(b.done, c->stream), "cuEventRecord(bucket done)");
+}
+
 void b200_routine::enqueue_stages() {
   const Program& P = code->code.prog;
   for (auto& z : scratch_zero)
@@ -242,7 +261,11 @@ void b200_routine::enqueue_stages() {
       r->stage_events[i].push_back({a, b});
     }
   };
-  for (size_t i = 0; i < code->code.stages.size(); ++i) {
+  // buckets no stage writes into are reduced first; the others as soon as their last writer is queued
+  for (auto& b : buckets)
+    if (b.after_stage < 0) enqueue_bucket(b);
+  // queues stage i (a clear may take the clears that follow along, advancing i)
+  auto queue_stage = [&](size_t& i) {
     const Stage& st = code->code.stages[i];
     Timer timer(this, i);
     if (st.kind == Stage::Memset) {
@@ -250,7 +273,12 @@ void b200_routine::enqueue_stages() {
       // range) become one clear; nothing between two nodes is touched unless they are adjacent
       CUdeviceptr at = node_ptr[st.memset_tn];
       size_t bytes = (size_t)P.tn(st.memset_tn).bytes();
-      while (!profiling && i + 1 < code->code.stages.size() && code->code.stages[i + 1].kind == Stage::Memset) {
+      auto fires_after = [&](size_t k) {
+        for (auto& b : buckets)
+          if (b.after_stage == (int)k) return true;
+        return false;
+      };
+      while (!profiling && !fires_after(i) && i + 1 < code->code.stages.size() && code->code.stages[i + 1].kind == Stage::Memset) {
         const int next_tn = code->code.stages[i + 1].memset_tn;
         const CUdeviceptr next_at = node_ptr[next_tn];
         const size_t next_bytes = (size_t)P.tn(next_tn).bytes();
@@ -260,13 +288,13 @@ void b200_routine::enqueue_stages() {
         ++i;
       }
       cu_check(cu().cuMemsetD8Async_(at, 0, bytes, dev->stream), "cuMemsetD8Async");
-      continue;
+      return;
     }
-    if (st.kind == Stage::Generic && st.total <= 0) continue;
+    if (st.kind == Stage::Generic && st.total <= 0) return;
     if (st.kind == Stage::Gemm) {
       gemm_enqueue(this, (int)i);
       dev->n_launches++;
-      continue;
+      return;
     }
     std::vector<CUdeviceptr>& vals = arg_values[i];
     for (size_t a = 0; a < st.args.size(); ++a)
@@ -282,7 +310,14 @@ void b200_routine::enqueue_stages() {
     if (st.grid_override > 0) blocks = st.grid_override;
     launch_kernel(dev, fns[i], (unsigned)blocks, (unsigned)st.block, (unsigned)st.block_y, 0, args.data(), "cuLaunchKernelEx");
     dev->n_launches++;
+  };
+  for (size_t i = 0; i < code->code.stages.size(); ++i) {
+    queue_stage(i);
+    for (auto& b : buckets)
+      if (b.after_stage == (int)i) enqueue_bucket(b);
   }
+  // whatever follows the routine on the compute stream (the optimizer step) sees the reduced ranges
+  for (auto& b : buckets) cu_check(cu().cuStreamWaitEvent_(dev->stream, b.done, 0), "cuStreamWaitEvent(bucket done)");
 }
 
 void b200_routine::launch(const int64_t* static_idx, int n_static) {
@@ -376,6 +411,11 @@ void b200_routine::destroy() {
     }
   stage_events.clear();
   if (graph) cu().cuGraphExecDestroy_(graph);
+  for (auto& b : buckets) {
+    if (b.ready) cu().cuEventDestroy_(b.ready);
+    if (b.done) cu().cuEventDestroy_(b.done);
+  }
+  buckets.clear();
   for (auto* g : gemm) gemm_release(g);
   for (auto m : gemm_modules)
     if (m) cu().cuModuleUnload_(m);

@@ -37,6 +37,7 @@ struct b200_dev {
   // bumped whenever pool 0 (the merge buffer) gets a new slab: a captured graph that reads the
   // merge buffer holds its address and must be captured again
   unsigned long long merge_epoch = 0;
+  std::vector<b200_comm*> comms;   // communicators of this device (polled by b200_await when they carry a timeout)
   long long n_launches = 0, n_graph_launches = 0, n_h2d = 0, n_d2h = 0, n_d2d = 0, n_events = 0;
 
   // Optional second stream for host-to-device copies (b200_set_async_uploads).  A copy waits for
@@ -69,6 +70,27 @@ struct b200_dev {
   }
   CUdeviceptr address(int pool_id, size_t offset, size_t bytes);
   void check_status();
+};
+
+// One NCCL communicator rank (one per process and device) with the stream its collectives run on
+// when they overlap a routine.
+struct b200_comm {
+  b200_dev* dev = nullptr;
+  ncclComm_t comm = nullptr;
+  int n_ranks = 0, rank = 0;
+  CUstream stream = nullptr;     // collectives attached to a routine run here, beside the compute stream
+  long long timeout_ms = 0;      // >0: b200_await polls for asynchronous NCCL errors and gives up after this long
+  bool aborted = false;
+};
+
+// A range of gradients reduced across the ranks as soon as the routine's last stage that writes
+// into it has been queued (b200_routine_overlap_allreduce).
+struct OverlapBucket {
+  int pool_id = 0;
+  size_t offset = 0, count = 0;
+  int dtype = 0, op = 0;
+  int after_stage = -1;          // index of the last stage writing into the range
+  CUevent ready = nullptr, done = nullptr;
 };
 
 struct b200_event {
@@ -118,6 +140,9 @@ struct b200_routine {
   bool reads_merge = false;               // some stage takes the merge buffer as an argument
   unsigned long long graph_merge_epoch = 0;  // the device's merge_epoch when `graph` was captured
 
+  b200_comm* overlap_comm = nullptr;
+  std::vector<OverlapBucket> buckets;
+  void enqueue_bucket(OverlapBucket& b);
   std::set<int> pools_used;   // pools of the bound nodes (what a launch has to wait for, uploads-wise)
   b200_code* requested = nullptr;  // the code `link` was given; `code` may be a variant of it
   void link(b200_dev* d, b200_code* c, const b200_binding* b, int n);

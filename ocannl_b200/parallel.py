@@ -74,9 +74,36 @@ class NcclExchange:
         return buf.raw
 
     def allreduce(self, replica: "DeviceReplica", mean: bool):
+        if self.overlapped:
+            return       # the update routine carries the exchange (attach_overlap)
         pool, offset, count = replica.grad_range
         bk.check(bk.lib().b200_allreduce(self.h, ctypes.c_int(pool), ctypes.c_size_t(offset), ctypes.c_size_t(count),
                                          ctypes.c_int(0), ctypes.c_int(1 if mean else 0)))
+
+    overlapped = False
+
+    def attach_overlap(self, replica: "DeviceReplica", mean: bool, max_buckets: int = 3):
+        """Makes the exchange part of the update routine: the gradient range is cut into at most
+        `max_buckets` buckets of similar size in the order back-propagation completes them (last
+        layers first); each bucket's allreduce starts on the communicator's stream as soon as the
+        last kernel writing into it is queued and runs beside the rest of the backward pass
+        (b200_routine_overlap_allreduce).  `grad_sync` then has nothing left to do."""
+        buckets = replica.gradient_buckets(max_buckets)
+        n = len(buckets)
+        pools = (ctypes.c_int * n)(*[b[0] for b in buckets])
+        offs = (ctypes.c_size_t * n)(*[b[1] for b in buckets])
+        counts = (ctypes.c_size_t * n)(*[b[2] for b in buckets])
+        bk.check(bk.lib().b200_routine_overlap_allreduce(replica.update.h, self.h, ctypes.c_int(n), pools, offs, counts,
+                                                         ctypes.c_int(0), ctypes.c_int(1 if mean else 0)))
+        if replica.graph:
+            replica.update.use_graph(True)
+        self.overlapped = True
+        return buckets
+
+    def set_timeout(self, milliseconds: int):
+        """`await` polls for asynchronous NCCL errors and aborts the communicator when one shows up
+        or the stream stays busy this long (a rank that left)."""
+        bk.check(bk.lib().b200_comm_set_timeout(self.h, ctypes.c_longlong(milliseconds)))
 
     def free(self):
         if self.h:
@@ -115,6 +142,9 @@ class DeviceReplica:
         first = min(ctx.arrays[g.ident][1] for g in grads)
         last = max(ctx.arrays[g.ident][1] + g.size_in_bytes for g in grads)
         self.grad_range = (pool, first, (last - first) // 4)
+        # gradients in memory order with their byte ranges (parameters are declared first layer first)
+        self.grad_layout = sorted(((ctx.arrays[g.ident][1], g.size_in_bytes, g.ident) for g in grads))
+        self.graph = graph
         self.update_code, self.sgd_code = bk.Code(update), bk.Code(sgd)
         self.update = ctx.link(self.update_code)
         self.sgd = self.update.context.link(self.sgd_code)
@@ -122,6 +152,25 @@ class DeviceReplica:
         if graph:
             self.update.use_graph(True)
             self.sgd.use_graph(True)
+
+    def gradient_buckets(self, max_buckets: int = 3):
+        """Contiguous (pool, byte offset, element count) ranges covering all gradients, at most
+        `max_buckets` of them, listed in the order back-propagation completes them: the gradients
+        of the last layers lie last in memory and are finished first.  Cuts are made where the
+        bytes gathered from the end pass the next multiple of total / max_buckets."""
+        pool = self.grad_range[0]
+        total = sum(size for _, size, _ in self.grad_layout)
+        out, hi, acc, k = [], None, 0, 1
+        for off, size, _ in reversed(self.grad_layout):
+            if hi is None:
+                hi = off + size
+            acc += size
+            if acc >= k * total / max_buckets or off == self.grad_layout[0][0]:
+                out.append((pool, off, (hi - off) // 4))
+                hi = None
+                while acc >= k * total / max_buckets:
+                    k += 1
+        return out
 
     def set_values(self, values: Dict[str, np.ndarray]):
         for k, v in values.items():

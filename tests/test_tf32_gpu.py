@@ -57,7 +57,12 @@ def test_mlp_training_fp32(device):
     for t in ir.params():
         w_ = want[t.ident].astype(np.float64).reshape(-1)
         g_ = got[t.ident].astype(np.float64).reshape(-1)
-        scale = float(np.abs(w_).max())
-        bad = np.abs(g_ - w_) > 2e-2 * np.abs(w_) + 2e-2 * max(scale, 1e-30)
-        # a relu gate at an activation of +-1e-4 may switch with tf32's rounding: one element in ten thousand
-        assert bad.sum() <= 1e-4 * w_.size, (t.ident, int(bad.sum()), w_.size, scale)
+        if t.ident.endswith("_grad"):
+            # An activation within tf32's rounding of zero passes its relu gate on one side only; each
+            # such gate adds or drops one whole term of every gradient behind it.  A gradient is
+            # therefore compared as a tensor: relative error in the 2-norm.
+            assert np.linalg.norm(g_ - w_) <= 2e-2 * np.linalg.norm(w_), (t.ident, np.linalg.norm(g_ - w_), np.linalg.norm(w_))
+        else:
+            scale = float(np.abs(w_).max())
+            bad = np.abs(g_ - w_) > 2e-2 * np.abs(w_) + 2e-2 * max(scale, 1e-30)
+            assert not bad.any(), (t.ident, int(bad.sum()), w_.size, scale)
