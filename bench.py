@@ -336,6 +336,8 @@ def train_step(dev, dist, rank, world, rows, total_rows, K, Wm):
         box = [par.NcclExchange.unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         ex = par.NcclExchange(dev, world, rank, box[0])
+        ex.set_timeout(120000)       # a rank that never arrives ends the wait instead of hanging it
+        buckets = ex.attach_overlap(rep, mean=True)
     else:
         ex = par.LocalExchange()
     h = par.DataParallel(rep, ex, "mean", input_ident="x", target_ident="labels")
@@ -363,7 +365,8 @@ def train_step(dev, dist, rank, world, rows, total_rows, K, Wm):
     if world > 1:
         ex.free()
     return {"samples_per_s": rows * world * K / (ms / 1e3), "ms_per_step": ms / K, "allreduce_bytes": int(count) * 4,
-            "exchange": "ncclAllReduce(avg, fp32) over one contiguous gradient range" if world > 1 else "none (1 shard)",
+            "exchange": ("ncclAllReduce(avg, fp32) in %d buckets on the communicator's stream, each started when its last "
+                         "gradient kernel is queued, beside the rest of the backward pass" % len(buckets)) if world > 1 else "none (1 shard)",
             "kernels_per_step": int(kernels), "loss_after": loss}
 
 

@@ -101,8 +101,8 @@ WAIT_CHILD = """
     from ocannl_b200 import backend as bk, workloads as W
     from tests.parity import run_device, run_oracle
     dev = bk.Device(0)
-    ir = W.einsum_gelu(1, 128, 64, 64)              # one tile, one k block
-    inputs = W.einsum_gelu_inputs(1, 128, 64, 64)
+    ir = W.einsum_gelu(1, 128, 128, 256)            # one tile, four k blocks
+    inputs = W.einsum_gelu_inputs(1, 128, 128, 256)
     out = {}
     os.environ["B200_NVRTC_FLAGS"] = "-DB200_WAIT_LIMIT_NS=20000000ull -DB200_INJECT_NO_LOADS"
     try:

@@ -124,17 +124,63 @@ def test_two_gloo_ranks_match_single_shard():
 
 
 def _nccl_rank(rank, world, uid, q):
+    """One rank of the two-GPU tests.  Whatever goes wrong is reported through the queue, and the
+    communicator carries a timeout, so that a rank whose peer failed gives up instead of spinning
+    inside a collective."""
     sys.path.insert(0, ROOT)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
-    from ocannl_b200 import backend as bk
-    dev = bk.Device(rank)
-    rep = par.DeviceReplica(dev, W.linreg_update(4 // world), W.linreg_sgd(), ["w"])
-    ex = par.NcclExchange(dev, world, rank, uid)
-    h = par.DataParallel(rep, ex, "sum")
-    loss, w = _one_step(h, 0.05)
-    h.sync_params_to_host()
-    q.put((rank, loss, w))
-    ex.free()
+    try:
+        from ocannl_b200 import backend as bk
+        dev = bk.Device(rank)
+        rep = par.DeviceReplica(dev, W.linreg_update(4 // world), W.linreg_sgd(), ["w"])
+        ex = par.NcclExchange(dev, world, rank, uid)
+        ex.set_timeout(60000)
+        h = par.DataParallel(rep, ex, "sum")
+        loss, w = _one_step(h, 0.05)
+        h.sync_params_to_host()
+        # the MLP update with the exchange carried by the routine, in buckets, beside the backward pass
+        rows = 512
+        mlp = par.DeviceReplica(dev, W.mlp_train_update(rows=rows // world), W.mlp_sgd(), W.MLP_PARAM_NAMES)
+        buckets = ex.attach_overlap(mlp, mean=True)
+        hm = par.DataParallel(mlp, ex, "mean", input_ident="x", target_ident="labels")
+        x, onehot = W.mlp_inputs(rows=rows)
+        mlp.set_values(dict(W.mlp_params(), learning_rate=np.float32([0.1])))
+        hm.set_batch(x, onehot)
+        for _ in range(3):               # the third run replays the captured graph
+            hm.step()
+        hm.sync_params_to_host()
+        params = {k: W.load("bfloat16", hm.read_values(k)).astype(np.float32) for k in W.MLP_PARAM_NAMES}
+        grads = {k: hm.read_values(k + "_grad") for k in W.MLP_PARAM_NAMES}
+        q.put((rank, loss, w, len(buckets), params, grads))
+        ex.free()
+    except Exception as e:      # noqa: BLE001 - the parent must learn of any failure
+        import traceback
+        q.put((rank, "error", traceback.format_exc()))
+
+
+def _run_ranks(target, args_of, n):
+    """Starts n ranks, collects one message from each and never leaves a rank behind."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=target, args=args_of(r) + (q,)) for r in range(n)]
+    for p in procs:
+        p.start()
+    try:
+        out = sorted((q.get(timeout=300) for _ in procs), key=lambda m: m[0])
+        for m in out:
+            assert m[1] != "error", m[2]
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+        return out
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(timeout=10)
+                if p.is_alive():
+                    p.kill()
 
 
 @pytest.mark.gpu
@@ -144,18 +190,32 @@ def test_two_gpus_nccl_match_single_shard(device):
     h = par.DataParallel(rep, par.LocalExchange(), "sum")
     loss, w = _one_step(h, 0.05)
     assert abs(loss - 67.5) < 1e-4 and abs(w - 5.0) < 1e-5
+    # the MLP on one shard: what two shards with an averaged exchange must reproduce
+    rows = 512
+    mlp = par.DeviceReplica(device, W.mlp_train_update(rows=rows), W.mlp_sgd(), W.MLP_PARAM_NAMES)
+    hm = par.DataParallel(mlp, par.LocalExchange(), "mean", input_ident="x", target_ident="labels")
+    x, onehot = W.mlp_inputs(rows=rows)
+    mlp.set_values(dict(W.mlp_params(), learning_rate=np.float32([0.1])))
+    hm.set_batch(x, onehot)
+    for _ in range(3):
+        hm.step()
+    hm.sync_params_to_host()
+    one = {k: W.load("bfloat16", hm.read_values(k)).astype(np.float32) for k in W.MLP_PARAM_NAMES}
+    one_g = {k: hm.read_values(k + "_grad") for k in W.MLP_PARAM_NAMES}
+    assert mlp.gradient_buckets(3) and len(mlp.gradient_buckets(3)) == 2      # (w2, b2, w_out) then (w1, b1)
     if bk.num_devices() < 2:
         pytest.skip("needs two GPUs")
-    import torch.multiprocessing as mp
     uid = par.NcclExchange.unique_id()
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    procs = [ctx.Process(target=_nccl_rank, args=(r, 2, uid, q)) for r in range(2)]
-    for p in procs:
-        p.start()
-    out = sorted(q.get(timeout=180) for _ in procs)
-    for p in procs:
-        p.join(timeout=60)
-        assert p.exitcode == 0
+    out = _run_ranks(_nccl_rank, lambda r: (r, 2, uid), 2)
     assert abs(out[0][1] - 11.25) < 1e-4
     assert abs(out[0][2] - 5.0) < 1e-5 and out[0][2] == out[1][2]
+    assert out[0][3] == 2
+    for k in W.MLP_PARAM_NAMES:
+        # both replicas hold the same parameters, bit for bit, and the same reduced gradients
+        assert np.array_equal(out[0][4][k], out[1][4][k]), k
+        assert np.array_equal(out[0][5][k], out[1][5][k]), k
+        # and they are those of the one-shard run up to the rounding of bf16 activations: a mean
+        # over two half batches adds in another order
+        g1, g2 = one_g[k].astype(np.float64), out[0][5][k].astype(np.float64)
+        assert np.linalg.norm(g1 - g2) <= 5e-2 * np.linalg.norm(g1), k
+        assert np.abs(one[k] - out[0][4][k]).max() <= 2.0 ** -7 * np.abs(one[k]).max() + 1e-6, k
