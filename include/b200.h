@@ -136,6 +136,12 @@ int b200_debug_info(b200_dev* dev, char* json, size_t cap);
  *      per contiguous gradient range.  One communicator rank per process and device. */
 int b200_comm_unique_id(char* id128);                                      /* 128 bytes */
 int b200_comm_init_rank(b200_dev* dev, int n_ranks, int rank, const char* id128, b200_comm** out);
+/* One process that holds every shard, as the reference's data_parallel does
+ * (lib/parallel.ml:166-208): all communicators at once, and one range per device reduced as one
+ * NCCL group (a thread that drives several devices must group its calls). */
+int b200_comm_init_all(int n_devices, b200_dev* const* devs, b200_comm** out);
+int b200_allreduce_all(int n, b200_comm* const* comms, const int* pool_ids, const size_t* offsets, size_t count,
+                       int dtype, int op);
 #define B200_SUM 0
 #define B200_AVG 1
 #define B200_F32 0

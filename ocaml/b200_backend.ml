@@ -63,7 +63,27 @@ let b_pool = field binding "pool_id" int32_t
 let b_off = field binding "offset" uint64_t
 let () = seal binding
 
+(* bindings need only be aligned to the element size, as Raise_backend.allocate_delta hands them out
+   (arrayjit/lib/backends.ml:529-614): the library re-plans stages that wanted more *)
 let c_link = foreign ~from:lib "b200_link" (vp @-> vp @-> ptr binding @-> int @-> ptr vp @-> returning int)
+let c_routine_info = foreign ~from:lib "b200_routine_info" (vp @-> ptr char @-> size_t @-> returning int)
+
+(* data-parallel exchange (used by parallel_b200.ml) *)
+let c_comm_unique_id = foreign ~from:lib "b200_comm_unique_id" (ptr char @-> returning int)
+let c_comm_init_rank = foreign ~from:lib "b200_comm_init_rank" (vp @-> int @-> int @-> ptr char @-> ptr vp @-> returning int)
+let c_allreduce = foreign ~from:lib "b200_allreduce" (vp @-> int @-> size_t @-> size_t @-> int @-> int @-> returning int)
+
+let c_overlap_allreduce =
+  foreign ~from:lib "b200_routine_overlap_allreduce"
+    (vp @-> vp @-> int @-> ptr int @-> ptr size_t @-> ptr size_t @-> int @-> int @-> returning int)
+
+let c_comm_init_all = foreign ~from:lib "b200_comm_init_all" (int @-> ptr vp @-> ptr vp @-> returning int)
+
+let c_allreduce_all =
+  foreign ~from:lib "b200_allreduce_all" (int @-> ptr vp @-> ptr int @-> ptr size_t @-> size_t @-> int @-> int @-> returning int)
+
+let c_comm_set_timeout = foreign ~from:lib "b200_comm_set_timeout" (vp @-> llong @-> returning int)
+let c_comm_free = foreign ~from:lib "b200_comm_free" (vp @-> returning int)
 let c_launch = foreign ~from:lib "b200_launch" (vp @-> ptr int64_t @-> int @-> returning int)
 let c_use_graph = foreign ~from:lib "b200_routine_use_graph" (vp @-> int @-> returning int)
 
@@ -100,13 +120,13 @@ module Ser = struct
     | Ops.Arg1 -> "arg1" | Arg2 -> "arg2" | Add -> "add" | Sub -> "sub" | Mul -> "mul" | Div -> "div"
     | ToPowOf -> "pow" | Relu_gate -> "relu_gate" | Satur01_gate -> "sat01_gate" | Cmplt -> "lt"
     | Cmpeq -> "eq" | Cmpne -> "ne" | Or -> "or" | And -> "and" | Mod -> "mod" | Max -> "max" | Min -> "min"
-    | Threefry4x32_crypto | Threefry4x32_light -> invalid_arg "b200: threefry is not serialised yet"
+    | Threefry4x32_crypto -> "threefry4x32_crypto" | Threefry4x32_light -> "threefry4x32_light"
 
   let unop = function
     | Ops.Identity -> "id" | Relu -> "relu" | Satur01 -> "sat01" | Exp -> "exp" | Log -> "log" | Exp2 -> "exp2"
     | Log2 -> "log2" | Sin -> "sin" | Cos -> "cos" | Sqrt -> "sqrt" | Recip -> "recip"
     | Recip_sqrt -> "recip_sqrt" | Neg -> "neg" | Trunc -> "trunc" | Tanh_approx -> "tanh" | Not -> "not"
-    | Uint4x32_to_prec_uniform1 -> invalid_arg "b200: uniform conversion is not serialised yet"
+    | Uint4x32_to_prec_uniform1 -> "uint4x32_to_prec_uniform1"
 
   let ternop = function Ops.Where -> "where" | FMA -> "fma" | Mul3 -> "mul3"
 
@@ -121,13 +141,18 @@ module Ser = struct
     | Zero_out tn -> buf_add b (Printf.sprintf "(zero_out %d)" tn.Tn.id)
     | Set { tn; idcs = i; llsc; _ } ->
         buf_add b (Printf.sprintf "(set %d %s " tn.Tn.id (idcs i)); scalar b llsc; buf_add b ")"
-    | Set_from_vec _ -> invalid_arg "b200: Set_from_vec is not serialised yet"
+    | Set_from_vec { tn; idcs = i; length; vec_unop = Ops.Uint4x32_to_prec_uniform; arg; _ } ->
+        (* the only vector operation (arrayjit/lib/ops.ml:452): `length` results of the uniform
+           conversion of one uint4x32 value go to consecutive elements starting at idcs *)
+        buf_add b (Printf.sprintf "(set_from_vec %d %s %d uint4x32_to_prec_uniform " tn.Tn.id (idcs i) length);
+        arg_ b arg; buf_add b ")"
     | Set_local ({ scope_id; tn }, v) ->
         buf_add b (Printf.sprintf "(set_local %d %d " scope_id tn.Tn.id); scalar b v; buf_add b ")"
     | Declare_local { id = { scope_id; tn }; needs_init } ->
         buf_add b (Printf.sprintf "(declare_local %d %d %d)" scope_id tn.Tn.id (Bool.to_int needs_init))
 
   and arg b (s, p) = buf_add b "("; scalar b s; buf_add b (" " ^ prec p ^ ")")
+  and arg_ b a = arg b a
 
   and scalar b = function
     | Local_scope { id = { scope_id; tn }; body; orig_indices } ->

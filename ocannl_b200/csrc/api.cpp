@@ -634,6 +634,63 @@ int b200_comm_init_rank(b200_dev* dev, int n_ranks, int rank, const char* id128,
   });
 }
 
+// One process driving all shards (the reference's arrangement: lib/parallel.ml:166-208 keeps every
+// shard's context in one process): the communicators of n devices at once, and an allreduce over
+// one range per device issued as one NCCL group -- a single thread that manages several devices
+// must group its calls, or the first one would wait for ranks that the same thread has yet to call.
+int b200_comm_init_all(int n, b200_dev* const* devs, b200_comm** out) {
+  return guard([&] {
+    if (n < 1 || !devs || !out) throw Error(B200_E_INVALID, "bad arguments");
+    if (!nccl().loaded) throw Error(B200_E_NO_DEVICE, "NCCL is not available: " + nccl().why);
+    std::vector<int> ordinals;
+    std::vector<ncclComm_t> comms((size_t)n, nullptr);
+    for (int i = 0; i < n; ++i) {
+      if (!devs[i]) throw Error(B200_E_INVALID, "null device");
+      ordinals.push_back(devs[i]->ordinal);
+    }
+    nccl_check(nccl().ncclCommInitAll_(comms.data(), n, ordinals.data()), "ncclCommInitAll");
+    for (int i = 0; i < n; ++i) {
+      auto c = std::make_unique<b200_comm>();
+      c->dev = devs[i];
+      c->n_ranks = n;
+      c->rank = i;
+      c->comm = comms[(size_t)i];
+      devs[i]->make_current();
+      cu_check(cu().cuStreamCreate_(&c->stream, CU_STREAM_NON_BLOCKING), "cuStreamCreate(communicator)");
+      devs[i]->comms.push_back(c.get());
+      out[i] = c.release();
+    }
+  });
+}
+
+int b200_allreduce_all(int n, b200_comm* const* comms, const int* pool_ids, const size_t* offsets, size_t count, int dtype,
+                       int op) {
+  return guard([&] {
+    if (n < 1 || !comms || !pool_ids || !offsets) throw Error(B200_E_INVALID, "bad arguments");
+    if (dtype != B200_F32 && dtype != B200_BF16) throw Error(B200_E_INVALID, "bad dtype");
+    if (op != B200_SUM && op != B200_AVG) throw Error(B200_E_INVALID, "bad reduction");
+    const size_t esz = dtype == B200_F32 ? 4 : 2;
+    std::vector<CUdeviceptr> ptrs;
+    for (int i = 0; i < n; ++i) {
+      if (!comms[i] || comms[i]->aborted) throw Error(B200_E_INVALID, "null or aborted communicator");
+      ptrs.push_back(comms[i]->dev->address(pool_ids[i], offsets[i], count * esz));
+    }
+    nccl_check(nccl().ncclGroupStart_(), "ncclGroupStart");
+    ncclResult_t first = ncclSuccess;
+    for (int i = 0; i < n; ++i) {
+      b200_dev* dev = comms[i]->dev;
+      dev->make_current();
+      ncclResult_t r = nccl().ncclAllReduce_((const void*)ptrs[(size_t)i], (void*)ptrs[(size_t)i], count,
+                                             dtype == B200_F32 ? ncclFloat32 : ncclBfloat16, op == B200_SUM ? ncclSum : ncclAvg,
+                                             comms[i]->comm, (cudaStream_t)dev->stream);
+      if (r != ncclSuccess && first == ncclSuccess) first = r;
+    }
+    ncclResult_t e = nccl().ncclGroupEnd_();
+    nccl_check(first, "ncclAllReduce(group)");
+    nccl_check(e, "ncclGroupEnd");
+  });
+}
+
 int b200_allreduce(b200_comm* comm, int pool_id, size_t offset, size_t count, int dtype, int op) {
   return guard([&] {
     if (!comm) throw Error(B200_E_INVALID, "null communicator");
@@ -672,6 +729,7 @@ int b200_routine_overlap_allreduce(b200_routine* r, b200_comm* comm, int n, cons
       if (b.done) cu().cuEventDestroy_(b.done);
     }
     r->buckets.clear();
+    r->overlap_warm = false;
     r->overlap_comm = n > 0 ? comm : nullptr;
     const Program& P = r->code->code.prog;
     const size_t esz = dtype == B200_F32 ? 4 : 2;

@@ -14,10 +14,13 @@ namespace b200 {
 #define B200_STR2(x) #x
 #define B200_STR(x) B200_STR2(x)
 
+// The libraries are opened with RTLD_LOCAL: their symbols must not enter the global namespace, where
+// they would shadow those of another copy loaded later (a Python process that imports a framework
+// bundling its own, newer NCCL after this library opened the system's would fail to resolve).
 static void* open_first(const std::vector<std::string>& names, std::string* why) {
   for (auto& n : names) {
     if (n.empty()) continue;
-    void* h = dlopen(n.c_str(), RTLD_NOW | RTLD_GLOBAL);
+    void* h = dlopen(n.c_str(), RTLD_NOW | RTLD_LOCAL);
     if (h) return h;
     *why += n + ": " + dlerror() + "; ";
   }

@@ -29,7 +29,7 @@ namespace b200 {
 
 #define B200_NCCL_FUNCS(X)                                                                              \
   X(ncclGetUniqueId) X(ncclCommInitRank) X(ncclCommDestroy) X(ncclAllReduce) X(ncclGetErrorString)      \
-  X(ncclCommAbort) X(ncclCommGetAsyncError)
+  X(ncclCommAbort) X(ncclCommGetAsyncError) X(ncclCommInitAll) X(ncclGroupStart) X(ncclGroupEnd)
 
 struct CuApi {
 #define X(name) decltype(&::name) name##_ = nullptr;

@@ -922,9 +922,9 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
     const std::string G = std::string("(B200_EPI_CHUNK / ") + (ebytes == 4 ? "4" : "8") + ")";
     const std::string member = "r" + std::to_string(o.tn);
     tile_decls += "  unsigned long long " + member + "[" + G + "];\n";
-    ptr_code += "  {\n#ifdef B200_DEBUG_NO_GLOBAL_STORE\n    const unsigned long long b200_pv = 0ull;\n#else\n"
+    ptr_code += "  {\n"
                 "    const unsigned long long b200_pv = b200_row_ok ? (unsigned long long)(" + t.ident + " + (" + o.row_off +
-                ")) : 0ull;\n#endif\n#pragma unroll\n    for (int it = 0; it < " + G + "; ++it) b200_t." + member +
+                ")) : 0ull;\n#pragma unroll\n    for (int it = 0; it < " + G + "; ++it) b200_t." + member +
                 "[it] = __shfl_sync(0xffffffffu, b200_pv, it * (32 / " + G + ") + b200_lane / " + G + ");\n  }\n";
   }
   {
@@ -1024,8 +1024,6 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   //      registers would touch 32 different lines per instruction; when the chunk is whole,
   //      contiguous and every row is 16-byte aligned, the warp transposes the chunk through a
   //      swizzled shared-memory staging tile and writes whole row segments instead.
-  fn << "#ifdef B200_DEBUG_ONLY_TMEM\n  return;\n#endif\n";   // developer experiment: TMEM traffic alone
-  fn << "#ifndef B200_DEBUG_NO_STORE\n";   // developer experiment: the epilogue without its stores
   for (auto& o : outs) {
     const Tnode& t = P.tn(o.tn);
     const int ebytes = prec_bytes(t.prec);
@@ -1089,7 +1087,6 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
       fn << ep.str() << "      " << t.ident << "[" << em.offset(o.idcs, t.dims) << "] = " << Emitter::store_wrap(t.prec, o.arr + "[b200_j]") << ";\n    }\n  }\n";
     }
   }
-  fn << "#endif\n";
   // row followers: assignments over whole rows, from the register tiles; then the rows' stores
   fn << row_decls;
   if (!row_code.empty()) fn << "  if (b200_row_ok) {\n" << row_code << row_stores << "  }\n";
@@ -1131,16 +1128,6 @@ static void gemm_tile_shape(const GemmPlan& g, int* bn_out, bool* pair_out) {
   else bn0 = (int)((g.n.extent + 15) / 16 * 16);
   if (!g.b_kmajor) bn0 = (bn0 + row_elems - 1) / row_elems * row_elems;
   if (bn0 > 256) bn0 = 256;
-  if (const char* ov = getenv("B200_GEMM_BN")) {   // developer override for tile-shape experiments
-    const int want = atoi(ov);
-    if (want >= 16 && want <= 256 && want % 16 == 0 && want <= bn0 && (g.b_kmajor || want % row_elems == 0)) {
-      bool pair = g.m.extent >= 256 && want >= 64 && want % 32 == 0 && (g.b_kmajor || (want / 2) % row_elems == 0);
-      if (const char* pv = getenv("B200_GEMM_PAIR")) pair = pair && pv[0] != '0';
-      *bn_out = want;
-      *pair_out = pair;
-      return;
-    }
-  }
   long long batch = 1;
   for (auto& b : g.batch) batch *= b.extent;
   const double k_blocks = (double)((g.k.extent + row_elems - 1) / row_elems);
@@ -1171,9 +1158,6 @@ static void gemm_tile_shape(const GemmPlan& g, int* bn_out, bool* pair_out) {
       }
     }
   }
-  if (const char* ov = getenv("B200_GEMM_PAIR")) {
-    if (ov[0] == '0' && best_pair) best_pair = false;
-  }
   *bn_out = best_bn;
   *pair_out = best_pair;
 }
@@ -1193,7 +1177,6 @@ static int gemm_split_k(const GemmPlan& g) {
   const long long k_blocks = (g.k.extent + (128 / prec_bytes(g.in_prec)) - 1) / (128 / prec_bytes(g.in_prec));
   if (tiles * 2 > workers) return 1;
   long long s = std::min<long long>(workers / tiles, k_blocks / 8);
-  if (const char* ov = getenv("B200_GEMM_SPLITK")) s = std::min<long long>(atoi(ov), k_blocks);
   return (int)std::max<long long>(1, std::min<long long>(s, 32));
 }
 
@@ -1213,14 +1196,9 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   // columns per epilogue step: more columns = more independent work per thread (the epilogue
   // is latency-bound) but more registers
   int chunk = (bn >= 32 && st.epi_tiles <= 2) ? 32 : 16;
-  if (const char* ov = getenv("B200_EPI_CHUNK")) chunk = atoi(ov);
   if (st.row_followers > 0) chunk = bn;   // the whole row in one chunk
   const bool light = false;  // 16 warps measured slower: the register cap (96) makes the epilogue spill
   int epi_warps = light ? 16 : (bn >= 128 ? 8 : 4);
-  if (const char* ov = getenv("B200_GEMM_EPI_WARPS")) {
-    const int want = atoi(ov);
-    if ((want == 4 || want == 8 || want == 16) && bn % (want / 4 * chunk) == 0) epi_warps = want;
-  }
   const int staging = 32 * chunk * st.epi_out_bytes;   // per warp
   // 227 KB per CTA: ring + alignment slack + barriers + one staging tile per epilogue warp
   int stages = (227 * 1024 - 1024 - 256 - epi_warps * staging) / stage_bytes;
@@ -1233,11 +1211,7 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   unsigned int idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((g.a_kmajor ? 0u : 1u) << 15) | ((g.b_kmajor ? 0u : 1u) << 16) |
                        ((unsigned int)(bn >> 3) << 17) | ((unsigned int)(bm >> 4) << 24);
   // consecutive tiles walk down this many row tiles before moving to the next column tile
-  int raster = 8;
-  if (const char* ov = getenv("B200_GEMM_RASTER")) {
-    const int want = atoi(ov);
-    if (want >= 1 && want <= 64) raster = want;
-  }
+  const int raster = 8;
   const std::string &params = st.epi_params, &args = st.epi_args;
   std::ostringstream o;
   o << kNumericsSource << "\n";

@@ -223,11 +223,6 @@ __device__ __forceinline__ void b200_tmem_ld16(unsigned int taddr, unsigned int*
 }
 
 __device__ __forceinline__ void b200_tmem_ld_chunk(unsigned int taddr, unsigned int* r) {
-#ifdef B200_DEBUG_NO_TMEM   // developer experiment: the epilogue without its TMEM loads (garbage results)
-#pragma unroll
-  for (int i = 0; i < B200_EPI_CHUNK; ++i) r[i] = taddr + i;
-  return;
-#endif
 #if B200_EPI_CHUNK == 64
   b200_tmem_ld32(taddr, r);
   b200_tmem_ld32(taddr + 32u, r + 32);
@@ -498,9 +493,7 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
         const bool b200_has_next = (c + B200_EPI_CHUNK < cols_per_warp) && (b200_n0 + B200_EPI_CHUNK < shape.N);
         const unsigned int b200_next_taddr = taddr + col + B200_EPI_CHUNK;
         // every lane takes part: rows beyond M compute nothing but help move the chunk
-#ifndef B200_DEBUG_NO_EPILOGUE   // developer experiment: how fast is the main loop left alone?
         B200_EPILOGUE_ROW
-#endif
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();

@@ -349,7 +349,12 @@ void b200_routine::launch(const int64_t* static_idx, int n_static) {
       statics_valid = true;
     }
   }
-  if (want_graph && !profiling) {
+  // The first run with collectives attached is queued directly: NCCL sets up the connections a
+  // collective needs the first time it runs (allocations, exchanges with the peers), which must
+  // not happen inside a stream capture.  Later runs capture and replay.
+  const bool capture_ok = buckets.empty() || overlap_warm;
+  if (!buckets.empty()) overlap_warm = true;
+  if (want_graph && !profiling && capture_ok) {
     if (graph && reads_merge && graph_merge_epoch != dev->merge_epoch) {
       // the merge buffer moved since the capture (`b200_merge_copy` grew pool 0): the graph holds
       // the old address

@@ -142,6 +142,7 @@ struct b200_routine {
 
   b200_comm* overlap_comm = nullptr;
   std::vector<OverlapBucket> buckets;
+  bool overlap_warm = false;      // the attached collectives have run once outside a capture
   void enqueue_bucket(OverlapBucket& b);
   std::set<int> pools_used;   // pools of the bound nodes (what a launch has to wait for, uploads-wise)
   b200_code* requested = nullptr;  // the code `link` was given; `code` may be a variant of it

@@ -228,3 +228,83 @@ class DataParallel:
 
     def read_values(self, ident: str) -> np.ndarray:
         return self.replica.read(ident)
+
+
+# ------------------------------------------------------------------ all shards in one process
+class Handle:
+    """`Parallel.handle` (lib/parallel.ml:112-141) with every shard held by this process, the
+    reference's own arrangement: `n_shards`, `step`, `grad_sync`, `set_batch`, `owner_loss_value`,
+    `sync_params_to_host`, `read_values`, `owner_params`, `shard_seeds`.  The owner is shard 0.
+    The reference moves each gradient to the owner through merge-buffer copies, updates there
+    and broadcasts the parameters (:247-304); here `grad_sync` is one grouped NCCL allreduce over
+    the shards' contiguous gradient ranges and every shard applies the optimizer routine itself."""
+
+    def __init__(self, replicas: Sequence[DeviceReplica], reduction: str, base_seed: int, input_ident: str, target_ident: str):
+        if reduction not in ("sum", "mean"):
+            raise ValueError("Parallel.data_parallel: reduction must be 'sum' or 'mean'")
+        self.replicas = list(replicas)
+        self.n_shards = len(self.replicas)
+        self.mean = reduction == "mean"
+        self.shard_seeds = [base_seed + i for i in range(self.n_shards)]
+        self.input_ident, self.target_ident = input_ident, target_ident
+        self.owner_params = list(self.replicas[0].params)
+        self.comms = None
+        if self.n_shards > 1:
+            n = self.n_shards
+            devs = (ctypes.c_void_p * n)(*[r.device.h for r in self.replicas])
+            out = (ctypes.c_void_p * n)()
+            bk.check(bk.lib().b200_comm_init_all(ctypes.c_int(n), devs, out))
+            self.comms = out
+
+    def set_batch(self, inputs: np.ndarray, targets: np.ndarray):
+        xs, ys = shard_along(inputs, self.n_shards), shard_along(targets, self.n_shards)
+        for r, x, y in zip(self.replicas, xs, ys):
+            r.set_values({self.input_ident: x, self.target_ident: y})
+
+    def grad_sync(self):
+        if self.comms is None:
+            return
+        n = self.n_shards
+        count = self.replicas[0].grad_range[2]
+        pools = (ctypes.c_int * n)(*[r.grad_range[0] for r in self.replicas])
+        offs = (ctypes.c_size_t * n)(*[r.grad_range[1] for r in self.replicas])
+        bk.check(bk.lib().b200_allreduce_all(ctypes.c_int(n), self.comms, pools, offs, ctypes.c_size_t(count), ctypes.c_int(0),
+                                             ctypes.c_int(1 if self.mean else 0)))
+
+    def step(self, **static):
+        for r in self.replicas:          # launch every shard before waiting for any
+            r.forward_backward(**static)
+        self.grad_sync()
+        for r in self.replicas:
+            r.optimizer_step(**static)
+
+    def owner_loss_value(self) -> float:
+        return float(self.replicas[0].read(self.replicas[0].loss_ident).reshape(-1)[0])
+
+    def sync_params_to_host(self):
+        for r in self.replicas:
+            r.await_()
+
+    def read_values(self, ident: str, shard: int = 0) -> np.ndarray:
+        return self.replicas[shard].read(ident)
+
+    def free(self):
+        if self.comms is not None:
+            for c in self.comms:
+                bk.lib().b200_comm_free(ctypes.c_void_p(c))
+            self.comms = None
+
+
+def data_parallel(devices: Sequence[bk.Device], update_of_rows: Callable[[int], IrRoutine], sgd: IrRoutine, params: Sequence[str],
+                  batch_rows: int, reduction: str = "sum", base_seed: int = 0, input_ident: str = "x",
+                  target_ident: str = "y", loss: str = "loss") -> Handle:
+    """`Parallel.data_parallel` (lib/parallel.ml:166-383): one replica per device in this process,
+    each over `batch_rows / n` rows (the batch must divide evenly, :51-66), seeds `base_seed + i`.
+    `update_of_rows(rows)` builds the forward+backward routine of a shard of that many rows."""
+    n = len(devices)
+    if n <= 0:
+        raise ValueError("Parallel.data_parallel: needs at least one device")
+    if batch_rows % n != 0:
+        raise ValueError("Parallel.shard_along: batch size %d not divisible by n_shards %d" % (batch_rows, n))
+    reps = [DeviceReplica(d, update_of_rows(batch_rows // n), sgd, params, loss=loss) for d in devices]
+    return Handle(reps, reduction, base_seed, input_ident, target_ident)

@@ -28,6 +28,18 @@ ncclResult_t ncclCommInitRank(ncclComm_t* comm, int n, ncclUniqueId id, int rank
   note("init");
   return 0;
 }
+ncclResult_t ncclCommInitAll(ncclComm_t* comms, int n, const int* devs) {
+  (void)devs;
+  for (int i = 0; i < n; ++i) {
+    comms[i] = (ncclComm_t)calloc(1, sizeof **comms);
+    comms[i]->rank = i;
+    comms[i]->n = n;
+  }
+  note("init_all");
+  return 0;
+}
+ncclResult_t ncclGroupStart(void) { return 0; }
+ncclResult_t ncclGroupEnd(void) { return 0; }
 ncclResult_t ncclCommDestroy(ncclComm_t comm) { note("destroy"); free(comm); return 0; }
 ncclResult_t ncclCommAbort(ncclComm_t comm) { note("abort"); free(comm); return 0; }
 ncclResult_t ncclAllReduce(const void* s, void* r, size_t count, int dtype, int op, ncclComm_t comm, void* stream) {

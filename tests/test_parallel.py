@@ -183,6 +183,57 @@ def _run_ranks(target, args_of, n):
                     p.kill()
 
 
+def _mlp_steps(device, exchange, overlap, graph=True, rows=256, steps=3):
+    mlp = par.DeviceReplica(device, W.mlp_train_update(rows=rows), W.mlp_sgd(), W.MLP_PARAM_NAMES, graph=graph)
+    if overlap:
+        exchange.attach_overlap(mlp, mean=True)
+    hm = par.DataParallel(mlp, exchange, "mean", input_ident="x", target_ident="labels")
+    x, onehot = W.mlp_inputs(rows=rows)
+    mlp.set_values(dict(W.mlp_params(), learning_rate=np.float32([0.1])))
+    hm.set_batch(x, onehot)
+    for _ in range(steps):
+        hm.step()
+    hm.sync_params_to_host()
+    return {k: hm.read_values(k) for k in list(W.MLP_PARAM_NAMES) + [p + "_grad" for p in W.MLP_PARAM_NAMES]}
+
+
+def _single_rank_overlap(q):
+    sys.path.insert(0, ROOT)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    try:
+        from ocannl_b200 import backend as bk
+        dev = bk.Device(0)
+        plain = _mlp_steps(dev, par.LocalExchange(), False)
+        out = {}
+        for graph in (False, True):
+            ex = par.NcclExchange(dev, 1, 0, par.NcclExchange.unique_id())
+            ex.set_timeout(30000)
+            got = _mlp_steps(dev, ex, True, graph=graph)
+            # worst difference relative to the node's largest magnitude (bf16 parameters as bits -> values)
+            worst = 0.0
+            for k in plain:
+                a = (W.load("bfloat16", plain[k]) if plain[k].dtype == np.uint16 else plain[k]).astype(np.float64)
+                b = (W.load("bfloat16", got[k]) if got[k].dtype == np.uint16 else got[k]).astype(np.float64)
+                worst = max(worst, float(np.abs(a - b).max() / max(np.abs(a).max(), 1e-30)))
+            out[graph] = worst
+            ex.free()
+        q.put((0, out))
+    except Exception:      # noqa: BLE001
+        import traceback
+        q.put((0, "error", traceback.format_exc()))
+
+
+@pytest.mark.gpu
+def test_overlapped_exchange_with_one_rank(device):
+    """The exchange attached to the update routine (bucket allreduces on the communicator's stream,
+    forked from and joined to the compute stream, also inside the captured graph), with a
+    communicator of one rank: an average over one rank changes nothing, so parameters and gradients
+    after three steps equal those of the run without an exchange, up to the last bits of the weight
+    gradients that split-K adds in no fixed order."""
+    out = _run_ranks(_single_rank_overlap, lambda r: (), 1)
+    assert out[0][1][False] < 1e-3 and out[0][1][True] < 1e-3, out
+
+
 @pytest.mark.gpu
 def test_two_gpus_nccl_match_single_shard(device):
     from ocannl_b200 import backend as bk
@@ -219,3 +270,32 @@ def test_two_gpus_nccl_match_single_shard(device):
         g1, g2 = one_g[k].astype(np.float64), out[0][5][k].astype(np.float64)
         assert np.linalg.norm(g1 - g2) <= 5e-2 * np.linalg.norm(g1), k
         assert np.abs(one[k] - out[0][4][k]).max() <= 2.0 ** -7 * np.abs(one[k]).max() + 1e-6, k
+
+
+@pytest.mark.gpu
+def test_all_shards_in_one_process(device):
+    """The reference's arrangement: one process holds every shard (lib/parallel.ml:166-208).  The
+    known answers of test/training/data_parallel.expected with one and -- where two GPUs are
+    visible -- two shards: owner losses 67.5 / 11.25, w = 5.0 on every replica."""
+    from ocannl_b200 import backend as bk
+
+    def run(devs):
+        h = par.data_parallel(devs, lambda rows: W.linreg_update(rows), W.linreg_sgd(), ["w"], 4, "sum", base_seed=7)
+        for r in h.replicas:
+            r.set_values({"w": np.float32([0.5]), "learning_rate": np.float32([0.05])})
+        h.set_batch(X, Y)
+        h.step()
+        h.sync_params_to_host()
+        out = h.owner_loss_value(), [float(h.read_values("w", i)[0]) for i in range(h.n_shards)], h.shard_seeds
+        h.free()
+        return out
+
+    loss, ws, seeds = run([device])
+    assert abs(loss - 67.5) < 1e-4 and abs(ws[0] - 5.0) < 1e-5 and seeds == [7]
+    with pytest.raises(ValueError):
+        par.data_parallel([device, device, device], lambda rows: W.linreg_update(rows), W.linreg_sgd(), ["w"], 4)
+    if bk.num_devices() < 2:
+        pytest.skip("needs two GPUs")
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    loss, ws, seeds = run([device, bk.Device(1)])
+    assert abs(loss - 11.25) < 1e-4 and all(abs(w - 5.0) < 1e-5 for w in ws) and ws[0] == ws[1] and seeds == [7, 8]
