@@ -55,6 +55,14 @@ WORKLOAD = ("config 5 forward: MLP 784-1024-1024-10, bf16 weights and activation
 DIMS = (784, 1024, 1024, 10)
 
 
+_T0 = time.time()
+
+
+def progress(msg):
+    """One line per phase on stderr (stdout carries the JSON line only)."""
+    print("[bench %6.1fs rank %s] %s" % (time.time() - _T0, os.environ.get("RANK", "0"), msg), file=sys.stderr, flush=True)
+
+
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -340,19 +348,25 @@ def train_step(dev, dist, rank, world, rows, total_rows, K, Wm):
         buckets = ex.attach_overlap(rep, mean=True)
     else:
         ex = par.LocalExchange()
+    progress("training step: replica linked, exchange ready")
     h = par.DataParallel(rep, ex, "mean", input_ident="x", target_ident="labels")
     x, onehot = shard_inputs(rows, rank, total_rows)
     rep.set_values(dict(W.mlp_params(dims=DIMS), x=x, labels=onehot, learning_rate=np.float32([0.01])))
-    for _ in range(Wm):
+    for i in range(Wm):
         h.step()
+        if i == 0:
+            dev.await_()
+            progress("training step: first step done")
     dev.await_()
+    progress("training step: warm-up done")
     if dist is not None:
         dist.barrier()
     e0 = dev.all_work()
     for _ in range(K):
         h.step()
     e1 = dev.all_work()
-    e1.sync()
+    dev.await_()              # with a communicator timeout this wait polls for NCCL errors instead of blocking
+    progress("training step: timed steps done")
     ms = e0.elapsed_ms(e1)
     if dist is not None:
         import torch
@@ -458,6 +472,7 @@ def measure_forward(dev, dist, rank, world, rows, total_rows, K, Wm, pk, e2e=Tru
     ms = timed(rt.run, K)
     barrier()
     res["ms"] = max_over_ranks(ms)
+    progress("  resident forward timed")
 
     if e2e:
         # host batch in, loss out, through from_host / run / to_host.  The batch of step i + 1 is
@@ -502,6 +517,7 @@ def measure_forward(dev, dist, rank, world, rows, total_rows, K, Wm, pk, e2e=Tru
         e1.free()
         barrier()
         res["ms_e2e"] = max_over_ranks(ms_e2e)
+        progress("  end-to-end forward timed")
         dev.set_async_uploads(False)
         res["loss"] = float(hloss[(K - 1) % 2].array[0])
         res["h2d_bytes"] = int(x.nbytes + onehot.nbytes)
@@ -584,11 +600,13 @@ def main():
     rows = total_rows // world
 
     # ---- the stated workload: one batch split over the ranks
+    progress("forward, %d rows per GPU" % rows)
     fwd = measure_forward(dev, dist, rank, world, rows, total_rows, K, Wm, pk, clock_index=local if rank == 0 else None)
     value = total_rows * K / (fwd["ms"] / 1e3)
     # ---- weak scaling beside it: every GPU keeps all the rows (N = 1: the same measurement)
     weak = None
     if world > 1:
+        progress("forward, weak scaling: %d rows per GPU" % total_rows)
         w = measure_forward(dev, dist, rank, world, total_rows, total_rows, K, Wm, pk, e2e=False, stages=False)
         weak = {"rows_per_gpu": total_rows, "value": total_rows * world * K / (w["ms"] / 1e3), "unit": "samples/s",
                 "ms_per_step": w["ms"] / K}
@@ -614,8 +632,10 @@ def main():
 
     train = None
     if not args.no_train:
+        progress("training step")
         train = train_step(dev, dist, rank, world, rows, total_rows, K, Wm)
 
+    progress("measurements done")
     if rank != 0:
         return
     line = {

@@ -730,7 +730,9 @@ int b200_routine_overlap_allreduce(b200_routine* r, b200_comm* comm, int n, cons
     }
     r->buckets.clear();
     r->overlap_warm = false;
+    if (r->overlap_comm) r->overlap_comm->routines.erase(r);
     r->overlap_comm = n > 0 ? comm : nullptr;
+    if (n > 0) comm->routines.insert(r);
     const Program& P = r->code->code.prog;
     const size_t esz = dtype == B200_F32 ? 4 : 2;
     for (int k = 0; k < n; ++k) {
@@ -760,6 +762,20 @@ int b200_comm_free(b200_comm* comm) {
   return guard([&] {
     if (!comm) return;
     b200_dev* dev = comm->dev;
+    // A captured graph that holds collectives of this communicator keeps the communicator in use:
+    // NCCL waits for such graphs to be destroyed before it lets the communicator go.  Routines that
+    // carry its collectives lose them (and their graphs) here.
+    for (b200_routine* r : comm->routines) {
+      r->dev->make_current();
+      r->set_graph(false);
+      for (auto& b : r->buckets) {
+        if (b.ready) cu().cuEventDestroy_(b.ready);
+        if (b.done) cu().cuEventDestroy_(b.done);
+      }
+      r->buckets.clear();
+      r->overlap_comm = nullptr;
+    }
+    comm->routines.clear();
     if (dev) {
       dev->make_current();
       for (size_t i = 0; i < dev->comms.size(); ++i)

@@ -409,6 +409,8 @@ void b200_routine::stage_time(int stage, float* total_ms, int* runs) {
 
 void b200_routine::destroy() {
   if (dev) cu().cuStreamSynchronize_(dev->stream);
+  if (overlap_comm) overlap_comm->routines.erase(this);
+  overlap_comm = nullptr;
   for (auto& v : stage_events)
     for (auto& e : v) {
       cu().cuEventDestroy_(e.first);

@@ -79,6 +79,7 @@ struct b200_comm {
   ncclComm_t comm = nullptr;
   int n_ranks = 0, rank = 0;
   CUstream stream = nullptr;     // collectives attached to a routine run here, beside the compute stream
+  std::set<struct b200_routine*> routines;   // routines whose runs carry collectives of this communicator
   long long timeout_ms = 0;      // >0: b200_await polls for asynchronous NCCL errors and gives up after this long
   bool aborted = false;
 };

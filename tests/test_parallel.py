@@ -6,6 +6,8 @@ import sys
 
 import numpy as np
 import pytest
+import torch  # noqa: F401  (before anything opens libnccl: the loader reuses an already loaded libnccl.so.2 for
+              # torch's own dependency, and the system's copy may be older than the one torch was built against)
 
 from ocannl_b200 import parallel as par
 from ocannl_b200 import workloads as W
