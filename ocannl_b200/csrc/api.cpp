@@ -284,6 +284,7 @@ int b200_host_free(void* p) {
 }
 
 // ------------------------------------------------------------------- events
+static void await_polling(b200_dev* dev, CUevent until);
 int b200_event_record(b200_dev* dev, b200_event** out) {
   return guard([&] {
     if (!dev || !out) throw Error(B200_E_INVALID, "null argument");
@@ -310,7 +311,8 @@ int b200_event_query(b200_event* ev, int* done) {
 int b200_event_sync(b200_event* ev) {
   return guard([&] {
     if (!ev) throw Error(B200_E_INVALID, "null argument");
-    cu_check(cu().cuEventSynchronize_(ev->ev), "cuEventSynchronize");
+    ev->dev->make_current();
+    await_polling(ev->dev, ev->ev);    // polls like b200_await when a communicator carries a timeout
     ev->dev->check_status();
   });
 }
@@ -344,17 +346,21 @@ int b200_stream_wait(b200_dev* dev, b200_event* ev) {
 // stream, and this call, busy for ever.  On an asynchronous error, or when the timeout passes
 // with the stream still busy, the communicator is aborted (ncclCommAbort ends its kernels) and
 // the error is returned; the device stays usable.
-static void await_polling(b200_dev* dev) {
+static void await_polling(b200_dev* dev, CUevent until) {
+  auto block = [&] {
+    if (until) cu_check(cu().cuEventSynchronize_(until), "cuEventSynchronize");
+    else cu_check(cu().cuStreamSynchronize_(dev->stream), "cuStreamSynchronize");
+  };
   long long limit = 0;
   for (auto* c : dev->comms)
     if (c->timeout_ms > 0 && !c->aborted) limit = limit ? std::min(limit, c->timeout_ms) : c->timeout_ms;
   if (!limit) {
-    cu_check(cu().cuStreamSynchronize_(dev->stream), "cuStreamSynchronize");
+    block();
     return;
   }
   const auto t0 = std::chrono::steady_clock::now();
   for (;;) {
-    CUresult q = cu().cuStreamQuery_(dev->stream);
+    CUresult q = until ? cu().cuEventQuery_(until) : cu().cuStreamQuery_(dev->stream);
     if (q == CUDA_SUCCESS) return;
     if (q != CUDA_ERROR_NOT_READY) cu_check(q, "cuStreamQuery");
     const long long waited = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
@@ -383,7 +389,7 @@ int b200_await(b200_dev* dev) {
   return guard([&] {
     if (!dev) throw Error(B200_E_INVALID, "null device");
     dev->make_current();
-    await_polling(dev);
+    await_polling(dev, nullptr);
     dev->check_status();
   });
 }
