@@ -27,7 +27,7 @@ LIB_PATH = os.path.join(_HERE, "libb200.so")
 
 NP_DTYPE = {"byte": np.uint8, "uint16": np.uint16, "int32": np.int32, "uint32": np.uint32,
             "int64": np.int64, "uint64": np.uint64, "half": np.float16, "bfloat16": np.uint16,
-            "single": np.float32, "double": np.float64,
+            "fp8": np.uint8, "single": np.float32, "double": np.float64,
             # four 32-bit words per element: arrays of this precision get a trailing axis of 4
             "uint4x32": np.dtype((np.uint32, (4,)))}
 

@@ -55,15 +55,27 @@ const char* Emitter::ctype(Prec p) {
     case Prec::Single: return "float";
     case Prec::Double: return "double";
     case Prec::Uint4x32: return "b200_u4x32";
-    case Prec::Fp8: break;
+    case Prec::Fp8: return "unsigned char";   // the 8 bits; arithmetic widens them (see convert / binop)
   }
-  throw Error(-4, "precision fp8 is not supported by the b200 backend");
+  throw Error(-3, "b200ir: unknown precision");
 }
 
 // Ops.c_convert_precision (arrayjit/lib/ops.ml:798-863) for the device spellings.
 std::pair<std::string, std::string> Emitter::convert(Prec from, Prec to) {
   if (from == to) return {"", ""};
-  if (from == Prec::Fp8 || to == Prec::Fp8) throw Error(-4, "precision fp8 is not supported by the b200 backend");
+  if (from == Prec::Fp8 || to == Prec::Fp8) {
+    // through single precision, as Ops.c_convert_precision spells it (arrayjit/lib/ops.ml:798-863);
+    // an 8-bit value is its code inside expressions
+    if (to == Prec::Uint4x32) return {"b200_word_to_u4x32((b200_u32)(", "))"};
+    if (from == Prec::Uint4x32) throw Error(-4, "unsupported uint4x32 conversion");
+    if (to == Prec::Fp8) {
+      // (rounded floats of 16-bit precisions are floats already)
+      if (from == Prec::Single || lowp(from)) return {"b200_f2fp8(", ")"};
+      return {"b200_f2fp8((float)(", "))"};
+    }
+    auto out = convert(Prec::Single, to);
+    return {out.first + "b200_fp82f(", ")" + out.second};
+  }
   if (from == Prec::Uint4x32 || to == Prec::Uint4x32) {
     // arrayjit/lib/builtins.c:531-606
     if (to == Prec::Uint4x32) {
@@ -165,8 +177,33 @@ static unsigned int lowp_bits(double c, Prec prec) {
   return b;
 }
 
+// the reference's float -> 8-bit float narrowing (arrayjit/lib/builtins.c:688-742), for constants
+static unsigned int fp8_bits(float f) {
+  if (f == 0.0f) return 0;
+  const unsigned int sign = f < 0 ? 1u : 0u;
+  f = std::fabs(f);
+  if (std::isinf(f)) return (sign << 7) | 0x7Cu;
+  if (std::isnan(f)) return (sign << 7) | 0x7Fu;
+  int ex;
+  const float m = std::frexp(f, &ex);
+  const int e = ex + 14;
+  if (e < 0) return sign << 7;
+  if (e > 30) return (sign << 7) | 0x7Cu;
+  unsigned int bits;
+  if (e == 0) {
+    bits = (unsigned int)(f * std::ldexp(1.0f, 14) * 4.0f + 0.5f);
+    return (sign << 7) | (bits > 3u ? 3u : bits);
+  }
+  bits = (unsigned int)((m - 0.5f) * 4.0f + 0.5f);
+  return (sign << 7) | (((unsigned int)e & 0x1Fu) << 2) | (bits > 3u ? 3u : bits);
+}
+
 std::string Emitter::constant(double c, Prec prec) {
   char buf[64];
+  if (prec == Prec::Fp8) {
+    snprintf(buf, sizeof buf, "((unsigned char)0x%02xu)", fp8_bits((float)c));
+    return buf;
+  }
   if (prec == Prec::Uint4x32) {
     snprintf(buf, sizeof buf, "%a", c);
     return std::string("b200_f64_to_u4x32(") + buf + ")";
@@ -289,11 +326,17 @@ std::string Emitter::binop(Prec prec, const std::string& op, const std::string& 
     if (prec != Prec::Uint4x32) throw Error(-4, "threefry4x32 outside a uint4x32 context");
     return (op == "threefry4x32_crypto" ? "b200_threefry_crypto(" : "b200_threefry_light(") + a + ", " + b + ")";
   }
+  // 8-bit floats: widen, operate in float, narrow -- every time (arrayjit/lib/cc_backend.ml:169-322)
+  if (prec == Prec::Fp8) return "b200_f2fp8(" + binop_plain(Prec::Single, op, "b200_fp82f(" + a + ")", "b200_fp82f(" + b + ")") + ")";
   if (lowp(prec) && selects_exactly(op)) return binop_plain(Prec::Single, op, a, b);
   if (lowp(prec)) return std::string(round_fn(prec)) + binop_plain(Prec::Single, op, a, b) + ")";
   return binop_plain(prec, op, a, b);
 }
 std::string Emitter::unop(Prec prec, const std::string& op, const std::string& a) {
+  if (prec == Prec::Fp8) {
+    if (op == "id") return a;
+    return "b200_f2fp8(" + unop_plain(Prec::Single, op, "b200_fp82f(" + a + ")") + ")";
+  }
   if (lowp(prec)) {
     // a 16-bit result keeps 8 (bf16) or 11 (half) significant bits: the hardware
     // approximations of tanh / exp / log (relative error below 2^-10) round to the same value
@@ -309,6 +352,8 @@ std::string Emitter::unop(Prec prec, const std::string& op, const std::string& a
 }
 std::string Emitter::ternop(Prec prec, const std::string& op, const std::string& a, const std::string& b,
                             const std::string& c) {
+  if (prec == Prec::Fp8)
+    return "b200_f2fp8(" + ternop_plain(Prec::Single, op, "b200_fp82f(" + a + ")", "b200_fp82f(" + b + ")", "b200_fp82f(" + c + ")") + ")";
   if (lowp(prec) && selects_exactly(op)) return ternop_plain(Prec::Single, op, a, b, c);
   if (lowp(prec)) return std::string(round_fn(prec)) + ternop_plain(Prec::Single, op, a, b, c) + ")";
   return ternop_plain(prec, op, a, b, c);
@@ -498,6 +543,8 @@ Emitter::Res Emitter::scalar(Prec prec, const Scalar& e) {
           case Prec::Uint64: r.expr = "(b200_u64)b200_uniform_int64(" + a.expr + ", 0)"; break;
           case Prec::Bfloat16: r.expr = load_wrap(prec, "b200_uniform1_bfloat16(" + a.expr + ")"); break;
           case Prec::Half: r.expr = load_wrap(prec, "b200_uniform_half(" + a.expr + ", 0)"); break;
+          case Prec::Fp8:
+          case Prec::Byte: r.expr = "((unsigned char)((" + a.expr + ").v[0] & 0xFFu))"; break;   // builtins.c:415-418
           default: throw Error(-4, "uint4x32_to_prec_uniform1 into an unsupported precision");
         }
         return r;
@@ -517,7 +564,11 @@ Emitter::Res Emitter::scalar(Prec prec, const Scalar& e) {
       if (is_where) {
         // the condition keeps its own precision: compare it there, select in `prec`
         std::string cond = a.expr;
-        r.expr = "((" + cond + ") != 0 ? (" + b.expr + ") : (" + c.expr + "))";
+        if (e.args[0].prec == Prec::Fp8) cond = "b200_fp82f(" + cond + ")";   // a code is compared as the number it stands for
+        if (prec == Prec::Fp8)   // the selected value is widened and narrowed like any other result
+          r.expr = "b200_f2fp8((" + cond + ") != 0 ? b200_fp82f(" + b.expr + ") : b200_fp82f(" + c.expr + "))";
+        else
+          r.expr = "((" + cond + ") != 0 ? (" + b.expr + ") : (" + c.expr + "))";
       } else {
         r.expr = ternop(prec, e.op, a.expr, b.expr, c.expr);
       }
@@ -603,6 +654,8 @@ std::string Emitter::stmt(const Stmt& s, int ind) {
           case Prec::Int64: fn = "b200_uniform_int64("; want = 2; break;
           case Prec::Bfloat16: fn = "b200_uniform_bfloat16("; want = 8; break;
           case Prec::Half: fn = "b200_uniform_half("; want = 8; break;
+          case Prec::Fp8:
+          case Prec::Byte: fn = "b200_uniform_byte("; want = 16; break;
           default: throw Error(-4, "uint4x32_to_prec_uniform into an unsupported precision");
         }
         if (s.vec_len != want && s.vec_len != 1) throw Error(-3, "b200ir: vector length does not match the precision");

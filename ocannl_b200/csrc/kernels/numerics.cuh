@@ -43,6 +43,40 @@ __device__ __forceinline__ unsigned short b200_f2h(float f) {
   return h;
 }
 
+// 8-bit floats, 1-5-2 (arrayjit/lib/builtins.c:643-742).  The narrowing repeats the reference's steps
+// one by one, because it is not a plain rounding: the significand frexpf returns in [0.5, 1) goes
+// to (m - 0.5) * 4 in [0, 2), a half is added and the sum truncated, so normal numbers only ever
+// get mantissa codes 0, 1, 2, and widening a code then narrowing it is not always the identity.
+// An 8-bit value therefore travels through expressions as its CODE, never as a float.
+__device__ __forceinline__ float b200_fp82f(unsigned char c) {
+  if (c == 0) return 0.0f;
+  const b200_u32 sign = (c >> 7) & 1u, e = (c >> 2) & 0x1Fu, m = c & 3u;
+  if (e == 0x1Fu) return m == 0 ? (sign ? -B200_INF : B200_INF) : B200_NAN;
+  const float r = e == 0 ? ldexpf((float)m / 4.0f, -14) : (1.0f + (float)m * 0.25f) * ldexpf(1.0f, (int)e - 15);
+  return sign ? -r : r;
+}
+__device__ __forceinline__ unsigned char b200_f2fp8(float f) {
+  if (f == 0.0f) return 0;
+  const b200_u32 sign = f < 0 ? 1u : 0u;
+  f = fabsf(f);
+  if (isinf(f)) return (unsigned char)((sign << 7) | 0x7Cu);
+  if (isnan(f)) return (unsigned char)((sign << 7) | 0x7Fu);
+  int ex;
+  const float m = frexpf(f, &ex);
+  const int e = ex + 14;
+  if (e < 0) return (unsigned char)(sign << 7);
+  if (e > 30) return (unsigned char)((sign << 7) | 0x7Cu);
+  b200_u32 bits;
+  if (e == 0) {
+    bits = (b200_u32)(f * 16384.0f * 4.0f + 0.5f);
+    if (bits > 3u) bits = 3u;
+    return (unsigned char)((sign << 7) | bits);
+  }
+  bits = (b200_u32)((m - 0.5f) * 4.0f + 0.5f);
+  if (bits > 3u) bits = 3u;
+  return (unsigned char)((sign << 7) | (((b200_u32)e & 0x1Fu) << 2) | bits);
+}
+
 // "Rounded floats": the value of a bf16 / half number kept in a float register.
 __device__ __forceinline__ float b200_rbf(float f) {
   b200_u32 u;
@@ -200,6 +234,11 @@ __device__ __forceinline__ unsigned short b200_uniform_half(b200_u4x32 x, int i)
 __device__ __forceinline__ unsigned short b200_uniform1_bfloat16(b200_u4x32 x) { return b200_bf16_bits_rne(b200_u32_uniform(x.v[0])); }
 
 // ---- warp-level combine used by cooperative (one warp per output element) reductions
+// byte i of the 16 bytes of a uint4x32 (arrayjit/lib/builtins.c:518-528: the 8-bit "uniform" values)
+__device__ __forceinline__ unsigned char b200_uniform_byte(b200_u4x32 x, int i) {
+  return (unsigned char)(x.v[i >> 2] >> (8 * (i & 3)));
+}
+
 __device__ __forceinline__ float b200_warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -204,4 +204,51 @@ static inline half8_t uint4x32_to_half_uniform_vec(uint4x32_t x) {
   return r;
 }
 
+
+/* ---- 8-bit floats, 1-5-2 (arrayjit/lib/builtins.c:643-742).  The reference's narrowing is restated
+ * step for step, quirks included, because results must carry the same bits: the significand that
+ * frexpf returns in [0.5, 1) is mapped to (m - 0.5) * 4 in [0, 2) and rounded by adding a half and
+ * truncating, so only the codes with mantissa 0, 1 and 2 are ever produced for normal numbers, and
+ * widening a code and narrowing it again is not always the identity (mantissa 2 comes back as 1). */
+static inline float fp8_to_single(uint8_t c) {
+  if (c == 0) return 0.0f;
+  const uint32_t sign = (c >> 7) & 1u, e = (c >> 2) & 0x1Fu, m = c & 3u;
+  float r;
+  if (e == 0x1Fu) r = m == 0 ? INFINITY : NAN;
+  else if (e == 0) r = ldexpf((float)m / 4.0f, -14);
+  else r = (1.0f + (float)m * 0.25f) * ldexpf(1.0f, (int)e - 15);
+  if (e == 0x1Fu && m != 0) return r;          /* NaN keeps no sign */
+  return sign ? -r : r;
+}
+static inline uint8_t single_to_fp8(float f) {
+  if (f == 0.0f) return 0;
+  const uint32_t sign = f < 0 ? 1u : 0u;
+  f = fabsf(f);
+  if (isinf(f)) return (uint8_t)((sign << 7) | 0x7Cu);
+  if (isnan(f)) return (uint8_t)((sign << 7) | 0x7Fu);
+  int ex;
+  float m = frexpf(f, &ex);
+  const int e = ex + 14;
+  if (e < 0) return (uint8_t)(sign << 7);
+  if (e > 30) return (uint8_t)((sign << 7) | 0x7Cu);
+  uint32_t bits;
+  if (e == 0) {
+    bits = (uint32_t)(f * ldexpf(1.0f, 14) * 4.0f + 0.5f);
+    if (bits > 3u) bits = 3u;
+    return (uint8_t)((sign << 7) | bits);
+  }
+  bits = (uint32_t)((m - 0.5f) * 4.0f + 0.5f);
+  if (bits > 3u) bits = 3u;
+  return (uint8_t)((sign << 7) | (((uint32_t)e & 0x1Fu) << 2) | bits);
+}
+typedef struct { uint8_t v[16]; } uint8x16_t;
+static inline uint8_t uint4x32_to_fp8_uniform(uint4x32_t x) { return (uint8_t)(x.v[0] & 0xFFu); }
+static inline uint8_t uint4x32_to_byte_uniform(uint4x32_t x) { return (uint8_t)(x.v[0] & 0xFFu); }
+static inline uint8x16_t uint4x32_to_fp8_uniform_vec(uint4x32_t x) {
+  uint8x16_t r;
+  for (int i = 0; i < 16; ++i) r.v[i] = (uint8_t)(x.v[i / 4] >> (8 * (i % 4)));
+  return r;
+}
+static inline uint4x32_t fp8_to_uint4x32(uint8_t x) { return uint16_to_uint4x32((uint16_t)x); }
+
 #endif

@@ -70,7 +70,7 @@ def operator_table(n: int, prec: str = "single") -> Routine:
     `b_<op>[i] := op(x[i], y[i])`, where / fma / mul3 with a third input.  `mod` (C `%`) is only
     defined for integer precisions, whose `y` must hold no zero; `log`, `log2`, `sqrt`, `recip_sqrt` read |x| + 0.5."""
     r = Routine("operator_table_%s_%d" % (prec, n))
-    integer = prec in ("int32", "uint32", "int64", "byte")
+    integer = prec in ("int32", "uint32", "int64", "byte")     # (fp8 operations are float operations)
     x = r.tn("x", prec, [n], read_only=True)
     y = r.tn("y", prec, [n], read_only=True)
     z = r.tn("z", prec, [n], read_only=True)

@@ -146,7 +146,11 @@ def _port_lib(tmp_path_factory=None):
                 'void p_uni_hf(uint4x32_t x, void* out){half8_t r = uint4x32_to_half_uniform_vec(x); memcpy(out, &r, 16);}\n'
                 'int32x4_t p_uni_i(uint4x32_t x){return uint4x32_to_int32_uniform_vec(x);}\n'
                 'uint16_t p_uni1_bf(uint4x32_t x){return uint4x32_to_bfloat16_uniform(x);}\n'
-                'double p_uni1_d(uint4x32_t x){return uint4x32_to_double_uniform(x);}\n')
+                'double p_uni1_d(uint4x32_t x){return uint4x32_to_double_uniform(x);}\n'
+                'float p_fp8s(uint8_t c){return fp8_to_single(c);}\n'
+                'uint8_t p_sfp8(float f){return single_to_fp8(f);}\n'
+                'void p_sfp8_many(const float* f, uint8_t* out, int n){for (int i = 0; i < n; ++i) out[i] = single_to_fp8(f[i]);}\n'
+                'void p_uni_fp8(uint4x32_t x, void* out){uint8x16_t r = uint4x32_to_fp8_uniform_vec(x); memcpy(out, &r, 16);}\n')
     subprocess.run(["gcc", "-O2", "-shared", "-fPIC", "-I", os.path.dirname(os.path.dirname(src)), src, "-o", so, "-lm"],
                    check=True)
     return ctypes.CDLL(so)
@@ -186,6 +190,32 @@ def test_port_matches_reference_builtins():
     for x in [0, 1, 255, 256, 2**31, 2**32 - 1] + [int(v) for v in rng.integers(0, 2**32, 100)]:
         assert ref.uint32_to_single_uniform(x) == port.p_uni(x)
         assert list(ref.uint32_to_uint4x32(x).v) == list(port.p_widen(x).v)
+
+
+def test_port_fp8_matches_reference_builtins():
+    """The 8-bit float conversions (arrayjit/lib/builtins.c:643-742), bit for bit: every code
+    widened, and a sweep of floats narrowed -- every code's own value, the midpoints and
+    neighbourhoods between codes, subnormals, overflow, infinities and NaN."""
+    ref, port = _ref_lib(), _port_lib()
+    for lib_, w, n in ((ref, "fp8_to_single", "single_to_fp8"), (port, "p_fp8s", "p_sfp8")):
+        getattr(lib_, w).restype = ctypes.c_float
+        getattr(lib_, w).argtypes = [ctypes.c_uint8]
+        getattr(lib_, n).restype = ctypes.c_uint8
+        getattr(lib_, n).argtypes = [ctypes.c_float]
+    wide = []
+    for c in range(256):
+        a, b = ref.fp8_to_single(c), port.p_fp8s(c)
+        assert (np.isnan(a) and np.isnan(b)) or np.float32(a).tobytes() == np.float32(b).tobytes(), c
+        wide.append(a)
+    fin = np.float32([v for v in wide if np.isfinite(v)])
+    rng = np.random.default_rng(3)
+    sweep = np.concatenate([fin, fin * np.float32(1.0625), fin * np.float32(0.9375), fin * np.float32(1.125),
+                            rng.normal(0, 1, 4000), rng.normal(0, 1e-4, 2000), rng.normal(0, 3e4, 2000),
+                            [0.0, -0.0, 1e-8, -1e-8, 57344.0, 61440.0, 65536.0, 1e9, np.inf, -np.inf, np.nan]]).astype(np.float32)
+    for v in sweep:
+        assert ref.single_to_fp8(float(v)) == port.p_sfp8(float(v)), float(v)
+    # the quirk that matters downstream: widening and narrowing again is not the identity
+    assert port.p_sfp8(port.p_fp8s(0x3E)) == 0x3D      # 1.5 (mantissa 2) comes back with mantissa 1
 
 
 def test_port_uniform_forms_match_reference_builtins():
