@@ -1130,6 +1130,346 @@ struct Builder {
     return f;
   }
 
+  // ---- register-resident rows.  The warp-per-row kernel above lets its stages meet through memory:
+  // every stage strides the row again, decomposes indices again and reloads from L1 what the
+  // stage before stored.  When every stage is one assignment and touches the shared nodes only at
+  // "the row's element t" (t on the node's last, contiguous axis) or at one value per row, a lane
+  // instead owns R / 32 CONSECUTIVE elements of the row for the whole kernel: inputs are loaded
+  // once with 16-byte accesses into register arrays, reductions run over the lane's registers
+  // and one shuffle tree, every produced row is kept in registers for the stages after it and
+  // stored once, with 16-byte accesses.  (Softmax over 256 keys: the scores are read once, the
+  // exponentials and the weights written once each; layer norm over 512 features likewise.)
+  static StmtP rename_stmt(const StmtP& s, const std::map<std::string, std::string>& ren) {
+    auto c = std::make_shared<Stmt>(*s);
+    rename_idcs(c->idcs, ren);
+    auto it = ren.find(c->index);
+    if (it != ren.end()) c->index = it->second;
+    for (auto& x : c->items) x = rename_stmt(x, ren);
+    if (c->body) c->body = rename_stmt(c->body, ren);
+    if (c->value) c->value = rename_scalar(c->value, ren);
+    return c;
+  }
+  static void rename_idcs(Indices& idcs, const std::map<std::string, std::string>& ren) {
+    for (auto& ix : idcs) {
+      if (ix.kind == Index::Iter) {
+        auto it = ren.find(ix.sym);
+        if (it != ren.end()) ix.sym = it->second;
+      } else if (ix.kind == Index::Affine) {
+        for (auto& t : ix.terms) {
+          auto it = ren.find(t.second);
+          if (it != ren.end()) t.second = it->second;
+        }
+      }
+    }
+  }
+  static ScalarP rename_scalar(const ScalarP& e, const std::map<std::string, std::string>& ren) {
+    auto c = std::make_shared<Scalar>(*e);
+    rename_idcs(c->idcs, ren);
+    {
+      Indices one = {c->idx};
+      rename_idcs(one, ren);
+      c->idx = one[0];
+    }
+    if (c->body) c->body = rename_stmt(c->body, ren);
+    for (auto& a : c->args) a.s = rename_scalar(a.s, ren);
+    return c;
+  }
+
+  struct RegRowStage {
+    StmtP set;                       // the assignment, row symbols renamed to the canonical ones
+    bool coop = false;
+    std::string t_sym;               // pointwise: the stage's element loop
+    std::vector<std::pair<int, std::string>> scopes;   // coop: (scope id, combine op)
+    std::vector<std::string> scope_syms;               // coop: each scope's element loop
+  };
+
+  bool emit_warp_rows_reg(const std::vector<size_t>& run, size_t L, Stage* out) {
+    if (!opt.enable_pairs) return false;
+    const Piece& first = pieces[run.front()];
+    std::vector<std::string> canon;
+    int64_t rows = 1;
+    for (size_t q = 0; q < L; ++q) {
+      canon.push_back("b200_r" + std::to_string(q) + "_" + first.par[q].sym);
+      rows *= first.par[q].extent();
+    }
+    int64_t R = -1;
+    std::vector<RegRowStage> stages;
+    for (size_t i : run) {
+      if (opt.no_pairs_at.count(code.stages[i].origins.empty() ? -1 : code.stages[i].origins[0])) return false;
+      const Piece& pc = pieces[i];
+      if (!pc.any_body || pc.any_body->kind != Stmt::Set || pc.any_body->vec_len > 0) return false;
+      RegRowStage st;
+      std::map<std::string, std::string> ren;
+      for (size_t q = 0; q < L; ++q) ren[pc.par[q].sym] = canon[q];
+      st.set = rename_stmt(pc.any_body, ren);
+      if (pc.coop == 32) {
+        st.coop = true;
+        if (pc.par.size() != L) return false;
+        CoopInfo ci = find_coop(*pc.any_body, 1 << 20);
+        if (ci.sym.empty() || ci.width != 32) return false;
+        st.scopes = ci.scopes;
+        // every scope: [v := neutral;] for k = 0 .. R-1 { v := v op term }
+        bool ok = true;
+        std::function<void(const Scalar&)> rec = [&](const Scalar& e) {
+          if (e.kind == Scalar::LocalScope) {
+            const Stmt* b = e.body.get();
+            if (b->kind == Stmt::Seq) b = b->items[1].get();
+            if (b->kind != Stmt::For || b->from != 0 || b->body->kind == Stmt::For) { ok = false; return; }
+            const int64_t ext = b->to + 1;
+            if (R < 0) R = ext;
+            if (ext != R) ok = false;
+            st.scope_syms.push_back(b->index);
+            return;
+          }
+          for (auto& a : e.args) rec(*a.s);
+        };
+        rec(*st.set->value);
+        if (!ok || st.scope_syms.size() != st.scopes.size()) return false;
+      } else {
+        if (pc.coop != 0 || pc.par.size() != L + 1 || pc.ser_work != 1) return false;
+        const LoopDim& t = pc.par[L];
+        if (t.from != 0) return false;
+        if (R < 0) R = t.extent();
+        if (t.extent() != R) return false;
+        st.t_sym = t.sym;
+        bool scopes = false;
+        walk_scalar(*st.set->value, [&](const Scalar& e) { if (e.kind == Scalar::LocalScope || e.kind == Scalar::GetLocal) scopes = true; },
+                    [](const Stmt&) {});
+        if (scopes) return false;
+      }
+      stages.push_back(st);
+    }
+    if (R < 64 || R % 32 != 0) return false;
+    const int EPL = (int)(R / 32);
+    if (EPL != 2 && EPL != 4 && EPL != 8 && EPL != 16) return false;
+
+    // ---- classify every access
+    struct RowNode { Indices idcs; Prec prec; bool loaded = false, produced = false; int writer = -1; };
+    std::map<int, RowNode> rownodes;        // nodes touched at (row.., t)
+    std::map<int, std::pair<Indices, int>> scalars;   // nodes written once per row: (indices, writing stage)
+    auto uses_any = [&](const Indices& idcs, const std::set<std::string>& syms) {
+      for (auto& ix : idcs)
+        for (auto& sy : syms)
+          if (ix.uses(sy)) return true;
+      return false;
+    };
+    bool ok = true;
+    std::set<int> written_nodes;
+    for (size_t k = 0; k < stages.size(); ++k) {
+      const RegRowStage& st = stages[k];
+      std::set<std::string> tsyms(st.scope_syms.begin(), st.scope_syms.end());
+      if (!st.t_sym.empty()) tsyms.insert(st.t_sym);
+      auto row_position = [&](int tn, const Indices& idcs) {
+        // last index is exactly an element symbol, on a last axis of extent R; no other use of it
+        const Tnode& t = code.prog.tn(tn);
+        if (idcs.empty() || idcs.size() != t.dims.size()) return false;
+        const Index& last = idcs.back();
+        if (last.kind != Index::Iter || !tsyms.count(last.sym) || t.dims.back() != R) return false;
+        Indices rest(idcs.begin(), idcs.end() - 1);
+        if (uses_any(rest, tsyms)) return false;
+        for (auto& ix : rest)
+          if (ix.kind != Index::Iter && ix.kind != Index::Fixed) return false;
+        return t.prec == Prec::Single || t.prec == Prec::Bfloat16 || t.prec == Prec::Half;
+      };
+      auto note_row = [&](int tn, const Indices& idcs, bool write) {
+        Indices key(idcs.begin(), idcs.end() - 1);
+        auto it = rownodes.find(tn);
+        if (it == rownodes.end()) {
+          RowNode rn;
+          rn.idcs = key;
+          rn.prec = code.prog.tn(tn).prec;
+          it = rownodes.emplace(tn, rn).first;
+        } else {
+          if (it->second.idcs.size() != key.size()) { ok = false; return; }
+          for (size_t a = 0; a < key.size(); ++a)
+            if (key[a].kind != it->second.idcs[a].kind || key[a].sym != it->second.idcs[a].sym || key[a].fixed != it->second.idcs[a].fixed) ok = false;
+        }
+        if (write) {
+          if (it->second.produced || it->second.loaded) ok = false;    // written twice, or read before it is written
+          it->second.produced = true;
+          it->second.writer = (int)k;
+        } else if (!it->second.produced) {
+          it->second.loaded = true;
+        }
+      };
+      // reads
+      walk_scalar(*st.set->value, [&](const Scalar& e) {
+        if (e.kind == Scalar::GetDyn || e.kind == Scalar::GetMerge) { ok = false; return; }
+        if (e.kind != Scalar::Get) return;
+        if (uses_any(e.idcs, tsyms)) {
+          if (!row_position(e.tn, e.idcs)) {
+            // an element-dependent read of a node this kernel does not write may stay a plain load
+            if (written_nodes.count(e.tn)) ok = false;
+            bool later = false;
+            for (size_t k2 = k; k2 < stages.size(); ++k2) later = later || stages[k2].set->tn == e.tn;
+            if (later) ok = false;
+            return;
+          }
+          note_row(e.tn, e.idcs, false);
+        } else if (written_nodes.count(e.tn)) {
+          auto it = scalars.find(e.tn);
+          if (it == scalars.end()) { ok = false; return; }
+          if (e.idcs.size() != it->second.first.size()) { ok = false; return; }
+          for (size_t a = 0; a < e.idcs.size(); ++a)
+            if (e.idcs[a].kind != it->second.first[a].kind || e.idcs[a].sym != it->second.first[a].sym ||
+                e.idcs[a].fixed != it->second.first[a].fixed)
+              ok = false;
+        }
+      }, [](const Stmt&) {});
+      // the write
+      const Stmt& set = *st.set;
+      if (st.coop) {
+        if (uses_any(set.idcs, tsyms) || written_nodes.count(set.tn) || rownodes.count(set.tn)) ok = false;
+        for (auto& ix : set.idcs)
+          if (ix.kind != Index::Iter && ix.kind != Index::Fixed) ok = false;
+        scalars[set.tn] = {set.idcs, (int)k};
+      } else {
+        if (!row_position(set.tn, set.idcs) || written_nodes.count(set.tn)) ok = false;
+        else note_row(set.tn, set.idcs, true);
+      }
+      written_nodes.insert(set.tn);
+      if (!ok) return false;
+    }
+    // a node read at other positions by a LATER plain load after being written here was refused above;
+    // a row node that is both loaded and produced was refused as well
+
+    // ---- emit
+    Stage f;
+    f.kind = Stage::Generic;
+    f.kernel = code.stages[run.front()].kernel;
+    f.block = 256;
+    f.total = rows;
+    f.coop = 32;
+    merge_origins(f, run);
+    Emitter em(code.prog);
+    em.large_models = opt.large_models;
+    em.unroll_loops = true;
+    std::set<int> written;
+    for (size_t i : run) {
+      const Piece& pc = pieces[i];
+      em.used_nodes.insert(pc.used.begin(), pc.used.end());
+      written.insert(pc.written.begin(), pc.written.end());
+      em.uses_merge |= pc.uses_merge;
+    }
+    int max_bytes = 4;
+    auto reg = [](int tn) { return "b200_row" + std::to_string(tn); };
+    auto row_ptr = [&](int tn, const RowNode& rn) {
+      const Tnode& t = code.prog.tn(tn);
+      Indices at = rn.idcs;
+      Index zero;
+      at.push_back(zero);
+      return t.ident + " + (" + em.offset(at, t.dims) + ") + b200_t0";
+    };
+    auto ld = [&](int tn, const RowNode& rn) {
+      const std::string n = std::to_string(EPL);
+      max_bytes = std::max(max_bytes, std::min(16, EPL * prec_bytes(rn.prec)));
+      if (rn.prec == Prec::Single) return "    b200_ld_row<" + n + ">(" + row_ptr(tn, rn) + ", " + reg(tn) + ");\n";
+      return "    b200_ld_row16<" + n + ", " + (rn.prec == Prec::Half ? "true" : "false") + ">(" + row_ptr(tn, rn) + ", " + reg(tn) + ");\n";
+    };
+    auto stv = [&](int tn, const RowNode& rn) {
+      const std::string n = std::to_string(EPL);
+      max_bytes = std::max(max_bytes, std::min(16, EPL * prec_bytes(rn.prec)));
+      if (rn.prec == Prec::Single) return "    b200_st_row<" + n + ">(" + row_ptr(tn, rn) + ", " + reg(tn) + ");\n";
+      return "    b200_st_row16<" + n + ", " + (rn.prec == Prec::Half ? "true" : "false") + ">(" + row_ptr(tn, rn) + ", " + reg(tn) + ");\n";
+    };
+    std::string text, decls;
+    for (auto& kv : rownodes) decls += "    float " + reg(kv.first) + "[" + std::to_string(EPL) + "];\n";
+    std::set<int> have;
+    auto forwards = [&]() {
+      em.row_forwards.clear();
+      for (auto& kv : rownodes) {
+        Indices idcs = kv.second.idcs;
+        Index any;
+        idcs.push_back(any);
+        em.row_forwards.push_back({kv.first, idcs, (int)idcs.size() - 1, reg(kv.first), " - b200_t0"});
+      }
+    };
+    forwards();
+    for (size_t k = 0; k < stages.size(); ++k) {
+      const RegRowStage& st = stages[k];
+      const Stmt& set = *st.set;
+      const Tnode& T = code.prog.tn(set.tn);
+      // rows this stage reads that are not in registers yet
+      walk_scalar(*set.value, [&](const Scalar& e) {
+        if (e.kind != Scalar::Get) return;
+        auto it = rownodes.find(e.tn);
+        if (it == rownodes.end() || it->second.produced || have.count(e.tn)) return;
+        bool positional = !e.idcs.empty() && e.idcs.back().kind == Index::Iter &&
+                          (e.idcs.back().sym == st.t_sym || std::count(st.scope_syms.begin(), st.scope_syms.end(), e.idcs.back().sym));
+        if (!positional) return;
+        text += ld(e.tn, it->second);
+        have.insert(e.tn);
+      }, [](const Stmt&) {});
+      if (st.coop) {
+        text += "    {\n";
+        size_t si = 0;
+        std::function<void(const Scalar&)> rec = [&](const Scalar& e) {
+          if (e.kind == Scalar::LocalScope) {
+            std::string op;
+            for (auto& sc : st.scopes)
+              if (sc.first == e.scope_id) op = sc.second;
+            const Prec p = code.prog.tn(e.tn).prec;
+            const Stmt* b = e.body.get();
+            if (b->kind == Stmt::Seq) b = b->items[1].get();
+            const std::string name = em.scope_name(e.scope_id, e.tn);
+            const double neutral = op == "add" ? 0.0 : (op == "max" ? -INFINITY : INFINITY);
+            text += "      " + std::string(Emitter::ctype(p)) + " " + name + " = " + em.constant(neutral, p) + ";\n";
+            text += "#pragma unroll\n      for (unsigned int b200_e = 0; b200_e < " + std::to_string(EPL) + "u; ++b200_e) {\n"
+                    "        const unsigned int " + b->index + " = b200_t0 + b200_e;\n" + em.stmt(*b->body, 8) + "      }\n";
+            text += "      " + name + " = b200_warp_" + (op == "add" ? std::string("sum") : op) + "(" + name + ");\n";
+            em.scope_subst[e.scope_id] = name;
+            ++si;
+            return;
+          }
+          for (auto& a : e.args) rec(*a.s);
+        };
+        rec(*set.value);
+        Emitter::Res v = em.scalar(T.prec, *set.value);
+        em.scope_subst.clear();
+        const std::string sname = "b200_val" + std::to_string(set.tn);
+        decls += "    " + std::string(Emitter::rtype(T.prec)) + " " + sname + ";\n";
+        text += "      " + sname + " = " + v.expr + ";\n";
+        text += "      if (b200_t == 0u) " + T.ident + "[" + em.offset(set.idcs, T.dims) + "] = " + Emitter::store_wrap(T.prec, sname) + ";\n";
+        text += "    }\n";
+        em.forwarded[set.tn] = {set.idcs, sname};     // every lane holds the value after the shuffle tree
+      } else {
+        em.set_redirect[set.tn] = {set.idcs, reg(set.tn) + "[b200_e]"};
+        text += "#pragma unroll\n    for (unsigned int b200_e = 0; b200_e < " + std::to_string(EPL) + "u; ++b200_e) {\n"
+                "      const unsigned int " + st.t_sym + " = b200_t0 + b200_e;\n" + em.stmt(set, 6) + "    }\n";
+        em.set_redirect.erase(set.tn);
+        text += stv(set.tn, rownodes[set.tn]);
+        have.insert(set.tn);
+      }
+    }
+    f.min_align = max_bytes;
+    std::string statics = static_prologue(text, em, 2);
+    std::ostringstream k_src;
+    k_src << "extern \"C\" __global__ void __launch_bounds__(" << f.block << ") " << f.kernel << "(";
+    emit_params(k_src, f, em, written);
+    k_src << ") {\n" << kGridEntry << statics
+          << "  const unsigned int b200_t = threadIdx.x & 31u;\n  const unsigned int b200_t0 = b200_t * " << EPL << "u;\n"
+          << "  const unsigned long long b200_warp = ((unsigned long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;\n"
+          << "  const unsigned long long b200_nwarps = ((unsigned long long)gridDim.x * blockDim.x) >> 5;\n"
+          << "  for (unsigned long long b200_row = b200_warp; b200_row < " << rows << "ull; b200_row += b200_nwarps) {\n";
+    {
+      std::string rem = "b200_row";
+      for (size_t q = L; q-- > 0;) {
+        const std::string ext = std::to_string(first.par[q].extent()) + "ull";
+        k_src << "    const unsigned int " << canon[q] << " = (unsigned int)" << (q == 0 ? rem : "(" + rem + " % " + ext + ")") << ";\n";
+        if (q != 0) {
+          k_src << "    const unsigned long long b200_q" << q << " = " << rem << " / " << ext << ";\n";
+          rem = "b200_q" + std::to_string(q);
+        }
+      }
+    }
+    k_src << decls << text << "  }\n}\n\n";
+    src << k_src.str();
+    f.note = "row-fused " + std::to_string(run.size()) + " stages, one warp per row, rows in registers (" + std::to_string(EPL) +
+             " elements per lane)";
+    *out = f;
+    return true;
+  }
+
   // Row fusion.  Consecutive stages whose outermost parallel loop has the same extent, and which
   // hand data to one another only within one iteration of that loop (every node written by one
   // of them and touched by another is indexed by the row symbol on one fixed axis, nowhere else),
@@ -1312,7 +1652,9 @@ struct Builder {
           }
           // a trailing pointwise stage gains nothing from the warp form unless it follows a reduction
           if (run.size() >= 2 && has_coop && rows >= 128) {
-            out.push_back(emit_warp_rows(run, L));
+            Stage reg_form;
+            if (emit_warp_rows_reg(run, L, &reg_form)) out.push_back(reg_form);
+            else out.push_back(emit_warp_rows(run, L));
             i = run.back() + 1;
             continue;
           }

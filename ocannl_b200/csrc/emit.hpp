@@ -47,6 +47,7 @@ struct Emitter {
     Indices idcs;
     int n_axis;
     std::string name;
+    std::string index_shift;   // appended to the index on n_axis ("" or e.g. " - b200_t0": the array holds a slice)
   };
   std::vector<RowForward> row_forwards;
   std::map<std::string, std::string> row_ren;

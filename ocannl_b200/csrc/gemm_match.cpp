@@ -767,7 +767,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
         if (!ok) break;
         em.row_ren = ren;
         em.row_forwards.clear();
-        for (auto& r : rownodes) em.row_forwards.push_back({r.tn, r.canon, r.n_axis, r.name});
+        for (auto& r : rownodes) em.row_forwards.push_back({r.tn, r.canon, r.n_axis, r.name, ""});
         em.unroll_loops = true;
         std::string code = "  {\n    float b200_part = 0.0f;\n    if (b200_row_ok) {\n";
         for (size_t i = 0; i < row_loops.size(); ++i)
@@ -826,7 +826,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
       const std::string name = "b200_f" + std::to_string(fo.set->tn);
       em.row_ren = ren;
       em.row_forwards.clear();
-      for (auto& r : rownodes) em.row_forwards.push_back({r.tn, r.canon, r.n_axis, r.name});
+      for (auto& r : rownodes) em.row_forwards.push_back({r.tn, r.canon, r.n_axis, r.name, ""});
       em.unroll_loops = true;
       const auto saved_redirect = em.set_redirect;
       em.set_redirect[fo.set->tn] = {fo.set->idcs, na >= 0 ? name + "[" + col_loop + "]" : name};

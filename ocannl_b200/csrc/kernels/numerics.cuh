@@ -233,12 +233,85 @@ __device__ __forceinline__ unsigned short b200_uniform_bfloat16(b200_u4x32 x, in
 __device__ __forceinline__ unsigned short b200_uniform_half(b200_u4x32 x, int i) { return b200_f2h(b200_uniform_16(x, i)); }
 __device__ __forceinline__ unsigned short b200_uniform1_bfloat16(b200_u4x32 x) { return b200_bf16_bits_rne(b200_u32_uniform(x.v[0])); }
 
-// ---- warp-level combine used by cooperative (one warp per output element) reductions
 // byte i of the 16 bytes of a uint4x32 (arrayjit/lib/builtins.c:518-528: the 8-bit "uniform" values)
 __device__ __forceinline__ unsigned char b200_uniform_byte(b200_u4x32 x, int i) {
   return (unsigned char)(x.v[i >> 2] >> (8 * (i & 3)));
 }
 
+// ---- a lane's share of a row: N consecutive elements, moved with the widest accesses their size
+//      allows (16, 8 or 4 bytes; the caller guarantees that alignment).  Values of the 16-bit
+//      formats are widened to the floats that hold them inside expressions.
+template <int BYTES>
+__device__ __forceinline__ void b200_ld_words(const void* p, b200_u32* w) {
+  if constexpr (BYTES % 16 == 0) {
+#pragma unroll
+    for (int i = 0; i < BYTES / 16; ++i) {
+      const uint4 q = ((const uint4*)p)[i];
+      w[4 * i] = q.x; w[4 * i + 1] = q.y; w[4 * i + 2] = q.z; w[4 * i + 3] = q.w;
+    }
+  } else if constexpr (BYTES % 8 == 0) {
+#pragma unroll
+    for (int i = 0; i < BYTES / 8; ++i) {
+      const uint2 q = ((const uint2*)p)[i];
+      w[2 * i] = q.x; w[2 * i + 1] = q.y;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < BYTES / 4; ++i) w[i] = ((const b200_u32*)p)[i];
+  }
+}
+template <int BYTES>
+__device__ __forceinline__ void b200_st_words(void* p, const b200_u32* w) {
+  if constexpr (BYTES % 16 == 0) {
+#pragma unroll
+    for (int i = 0; i < BYTES / 16; ++i) ((uint4*)p)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+  } else if constexpr (BYTES % 8 == 0) {
+#pragma unroll
+    for (int i = 0; i < BYTES / 8; ++i) ((uint2*)p)[i] = make_uint2(w[2 * i], w[2 * i + 1]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < BYTES / 4; ++i) ((b200_u32*)p)[i] = w[i];
+  }
+}
+template <int N>
+__device__ __forceinline__ void b200_ld_row(const float* p, float* r) {
+  b200_u32 w[N];
+  b200_ld_words<4 * N>(p, w);
+#pragma unroll
+  for (int i = 0; i < N; ++i) r[i] = __uint_as_float(w[i]);
+}
+template <int N>
+__device__ __forceinline__ void b200_st_row(float* p, const float* r) {
+  b200_u32 w[N];
+#pragma unroll
+  for (int i = 0; i < N; ++i) w[i] = __float_as_uint(r[i]);
+  b200_st_words<4 * N>(p, w);
+}
+// 16-bit rows: `half` chooses the format
+template <int N, bool HALF>
+__device__ __forceinline__ void b200_ld_row16(const unsigned short* p, float* r) {
+  b200_u32 w[N / 2];
+  b200_ld_words<2 * N>(p, w);
+#pragma unroll
+  for (int i = 0; i < N / 2; ++i) {
+    if constexpr (HALF) {
+      r[2 * i] = b200_h2f((unsigned short)w[i]);
+      r[2 * i + 1] = b200_h2f((unsigned short)(w[i] >> 16));
+    } else {
+      r[2 * i] = __uint_as_float(w[i] << 16);
+      r[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+  }
+}
+template <int N, bool HALF>
+__device__ __forceinline__ void b200_st_row16(unsigned short* p, const float* r) {
+  b200_u32 w[N / 2];
+#pragma unroll
+  for (int i = 0; i < N / 2; ++i) w[i] = HALF ? b200_pack_hf(r[2 * i], r[2 * i + 1]) : b200_pack_bf(r[2 * i], r[2 * i + 1]);
+  b200_st_words<2 * N>(p, w);
+}
+
+// ---- warp-level combine used by cooperative (one warp per output element) reductions
 __device__ __forceinline__ float b200_warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -111,7 +111,9 @@ def test_operator_table_fp8(device, options):
     result with the reference's own -- lossy, not idempotent -- conversion
     (arrayjit/lib/builtins.c:643-742), so values travel as codes and every result is compared bit for
     bit.  For the libm functions a result may fall on the other side of a narrowing threshold when
-    the device's function differs in its last bit: one code in a thousand is allowed there."""
+    the device's function differs in its last bit (tanh of a large argument is 1 on one side and
+    the float below 1 on the other, and those narrow to different codes): one result in a hundred
+    is allowed there -- the inputs are 256 codes, so one deviating argument shows up many times."""
     n = 4096
     ir = R.operator_table(n, "fp8")
     g = np.random.default_rng(11)
@@ -127,6 +129,6 @@ def test_operator_table_fp8(device, options):
             continue
         same = got[t.ident] == want[t.ident]
         if t.ident in libm:
-            assert same.mean() >= 0.999, (t.ident, float(same.mean()))
+            assert same.mean() >= 0.99, (t.ident, float(same.mean()))
         else:
             assert same.all(), (t.ident, np.argwhere(~same)[:4].ravel(), got[t.ident][~same][:4], want[t.ident][~same][:4])
