@@ -384,6 +384,52 @@ def train_step(dev, dist, rank, world, rows, total_rows, K, Wm):
             "kernels_per_step": int(kernels), "loss_after": loss}
 
 
+def probe_attention_scores(dev):
+    """The decoder's score contraction as a routine of its own (64 sequences, 256 positions, 8 heads
+    of 64), with its mask epilogue, with the scaling only, and bare: what the `where(mask, ..)`
+    costs the epilogue.  A small case for profilers and for the numbers quoted beside the kernel."""
+    import math
+    from ocannl_b200 import backend as bk
+    from ocannl_b200 import workloads as W
+    from ocannl_b200.low_level import Const, Routine, Seq, Set, loops, where
+    B, S, H, E = 64, 256, 8, 64
+    out = {}
+    for variant in ("mask", "scale", "bare"):
+        r = Routine("scores_" + variant)
+        q = r.tn("q", "bfloat16", [B, S, H, E], read_only=True)
+        k = r.tn("k", "bfloat16", [B, S, H, E], read_only=True)
+        mask = r.tn("mask", "single", [S, S], read_only=True)
+        scores = r.tn("scores", "single", [B, S, H, S])
+        b, s_, h, t, e = r.syms(5)
+        acc = W.reduce_scope(r, "qk", "single", [(e, E)], lambda: (q[b, s_, h, e], k[b, t, h, e]), orig=(b, s_, h, t))
+        val = where(mask[s_, t], acc / math.sqrt(E), Const(-1e9)) if variant == "mask" else (acc / math.sqrt(E) if variant == "scale" else acc)
+        r.body = Seq([loops([(b, B), (s_, S), (h, H), (t, S)], Set(scores, (b, s_, h, t), val))])
+        code = bk.Code(r)
+        rt = bk.Context(dev).link(code)
+        g = np.random.default_rng(0)
+        rt.context.from_host("q", W.store("bfloat16", g.standard_normal((B, S, H, E), np.float32)))
+        rt.context.from_host("k", W.store("bfloat16", g.standard_normal((B, S, H, E), np.float32)))
+        if variant == "mask":
+            rt.context.from_host("mask", (np.arange(S)[:, None] >= np.arange(S)[None, :]).astype(np.float32))
+        for _ in range(3):
+            rt.run()
+        dev.await_()
+        e0 = dev.all_work()
+        for _ in range(10):
+            rt.run()
+        e1 = dev.all_work()
+        e1.sync()
+        ms = e0.elapsed_ms(e1) / 10
+        nbytes = 2 * B * S * H * E * 2 + B * S * H * S * 4
+        out[variant] = {"us": round(1e3 * ms, 2), "gbs": round(nbytes / ms / 1e6, 1), "note": rt.info()["stages"][0]["note"]}
+        pools = {p for p, _, _ in rt.context.arrays.values()}
+        rt.free()
+        code.free()
+        for p in pools:
+            dev.free_pool(p)
+    return out
+
+
 def oracle_rate(ir, inputs, units, statics=None, what=""):
     """Seconds of one oracle run of `ir` (one host thread) -> units per second, with the sample stated."""
     from oracle.run_c import OracleRoutine
@@ -569,6 +615,7 @@ def main():
     ap.add_argument("--no-configs", action="store_true", help="skip the configs 1, 2 and 4 section")
     ap.add_argument("--sweep-size", type=int, default=0,
                     help="run only the batch-8 contraction of this M=N=K (a small case for profilers) and exit")
+    ap.add_argument("--probe", default="", help="'attention_scores': time the decoder's score contraction alone and exit")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -593,6 +640,9 @@ def main():
     dev = bk.Device(local)
     if args.sweep_size:
         print(json.dumps({"contraction_sweep": contraction_sweep(dev, pk, (args.sweep_size,))}))
+        return
+    if args.probe == "attention_scores":
+        print(json.dumps({"attention_scores": probe_attention_scores(dev)}))
         return
     total_rows, K, Wm = args.rows, max(1, args.steps), max(3, args.warmup)
     if total_rows % world != 0:

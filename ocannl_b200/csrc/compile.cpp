@@ -260,6 +260,7 @@ struct Piece {
   int coop = 0;
   bool pairs = false;
   int64_t ser_work = 1;
+  std::vector<int> staged;   // small read-only nodes the kernel first copies into shared memory
 };
 
 struct Builder {
@@ -847,6 +848,54 @@ struct Builder {
       st.total /= 2;      // one thread per pair
       st.min_align = 8;   // pairs are read and written as 4- and 8-byte words
     }
+    // Small tables read over and over.  A read-only node of at most 32 KB that the stage reads inside
+    // a reduction or serial loop, many times per element (the 512 x 27 embedding table of a one-hot
+    // contraction with K = 27: rows of 54 bytes, no tensor-map can describe them) is copied into
+    // shared memory once per block; the strided reads then hit shared-memory banks instead of L1
+    // sectors.  Such a stage keeps its own kernel (few blocks, each looping over many elements).
+    std::vector<int> staged;
+    if (opt.enable_coop && !scatter && !pairs && ci.sym.empty() && body->kind == Stmt::Set && st.total > 0) {
+      int64_t work = st.total;
+      for (auto& d : st.ser) work *= std::max<int64_t>(1, d.extent());
+      std::set<std::string> inner_syms;
+      for (auto& d : st.ser) inner_syms.insert(d.sym);
+      walk_stmt(*body, [](const Scalar&) {}, [&](const Stmt& x) { if (x.kind == Stmt::For) inner_syms.insert(x.index); });
+      int64_t inner_iters = 1;
+      walk_stmt(*body, [](const Scalar&) {}, [&](const Stmt& x) { if (x.kind == Stmt::For) inner_iters *= std::max<int64_t>(1, x.to - x.from + 1); });
+      std::set<int> cand;
+      size_t bytes = 0;
+      walk_scalar(*body->value, [&](const Scalar& e) {
+        if (e.kind != Scalar::Get) return;
+        const Tnode& t = code.prog.tn(e.tn);
+        if (!t.read_only || t.mode == Mode::Virtual || written.count(e.tn) || t.bytes() > 32768 || t.prec == Prec::Uint4x32) return;
+        bool in_loop = false;
+        for (auto& ix : e.idcs)
+          for (auto& sy : inner_syms) in_loop = in_loop || ix.uses(sy);
+        if (in_loop && work * inner_iters >= 256 * t.num_elems()) cand.insert(e.tn);
+      }, [](const Stmt&) {});
+      // first the nodes indexed by the innermost parallel loop: their reads differ from thread to
+      // thread (a read that is the same for a whole warp is one broadcast access anyway)
+      std::vector<int> order(cand.begin(), cand.end());
+      auto strided = [&](int tn) {
+        bool u = false;
+        walk_scalar(*body->value, [&](const Scalar& e) {
+          if (e.kind == Scalar::Get && e.tn == tn && !st.par.empty())
+            for (auto& ix : e.idcs) u = u || ix.uses(st.par.back().sym);
+        }, [](const Stmt&) {});
+        return u;
+      };
+      std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return strided(a) > strided(b); });
+      for (int tn : order) {
+        if (bytes + (size_t)code.prog.tn(tn).bytes() > 40960) continue;
+        bytes += (size_t)code.prog.tn(tn).bytes();
+        staged.push_back(tn);
+        em.node_alias[tn] = "b200_sm_" + code.prog.tn(tn).ident;
+      }
+      if (!staged.empty() && inner_iters < 8) {   // nothing is re-read often enough
+        staged.clear();
+        em.node_alias.clear();
+      }
+    }
     std::string inner;
     int ind = 4 + 2 * (int)st.ser.size();
     if (!ci.sym.empty()) {
@@ -916,6 +965,14 @@ struct Builder {
       pc.per_row = st.total / pc.rows * ser_work;
     }
     if (!scatter) pc.any_body = body;
+    if (!staged.empty()) {      // keeps a kernel of its own
+      pc.staged = staged;
+      pc.fusable = false;
+      pc.body = nullptr;
+      pc.any_body = nullptr;
+      st.grid_override = 148 * 4;
+      st.block = 512;
+    }
     pc.par = st.par;
     pc.coop = st.coop;
     pc.pairs = pairs;
@@ -923,7 +980,7 @@ struct Builder {
     std::ostringstream note;
     note << "par=" << st.par.size() << " ser=" << st.ser.size()
          << (st.coop > 32 ? " block-per-element" : st.coop ? " warp-per-element" : "") << (pairs ? " pairs" : "")
-         << (scatter ? " scatter accumulation (atomic adds)" : "");
+         << (scatter ? " scatter accumulation (atomic adds)" : "") << (staged.empty() ? "" : " small table staged in shared memory");
     st.note = note.str();
     pieces[code.stages.size()] = pc;
     st.writes.assign(written.begin(), written.end());
@@ -941,6 +998,14 @@ struct Builder {
     k_src << "extern \"C\" __global__ void __launch_bounds__(" << st.block << ") " << st.kernel << "(";
     emit_params(k_src, st, em, pc.written);
     k_src << ") {\n" << kGridEntry << statics;
+    for (int tn : pc.staged) {
+      const Tnode& t = code.prog.tn(tn);
+      const std::string sm = "b200_sm_" + t.ident;
+      k_src << "  __shared__ " << Emitter::ctype(t.prec) << " " << sm << "[" << t.num_elems() << "];\n"
+            << "  for (unsigned int b200_i = threadIdx.x; b200_i < " << t.num_elems() << "u; b200_i += blockDim.x) " << sm
+            << "[b200_i] = " << t.ident << "[b200_i];\n";
+    }
+    if (!pc.staged.empty()) k_src << "  __syncthreads();\n";
     if (st.coop > 32) {
       k_src << "  __shared__ double b200_red[32];\n";
       k_src << "  const unsigned int b200_t = threadIdx.x;\n";

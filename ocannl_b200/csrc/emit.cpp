@@ -482,6 +482,10 @@ Emitter::Res Emitter::scalar(Prec prec, const Scalar& e) {
         uses_merge = true;
       }
       std::string name = e.kind == Scalar::GetMerge ? "merge_buffer" : t.ident;
+      if (e.kind == Scalar::Get) {
+        auto al = node_alias.find(e.tn);
+        if (al != node_alias.end()) name = al->second;
+      }
       ++direct_reads;
       r.expr = cv.first + load_wrap(t.prec, name + "[" + offset(e.idcs, t.dims) + "]") + cv.second;
       return r;

@@ -52,6 +52,8 @@ struct Emitter {
   std::vector<RowForward> row_forwards;
   std::map<std::string, std::string> row_ren;
   bool unroll_loops = false;   // `#pragma unroll` before every emitted loop (register arrays stay registers)
+  // nodes read through another name (a copy staged in shared memory)
+  std::map<int, std::string> node_alias;
   // nodes whose loads may use the read-only data path
   std::set<int> readonly_nodes;
   // cooperative reductions: scope id -> lane-strided loop symbol (see compile.cpp)

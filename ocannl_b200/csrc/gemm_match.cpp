@@ -983,7 +983,8 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
      << "__device__ __forceinline__ void b200_tmem_ld_chunk(unsigned int taddr, unsigned int* r);\n"
      << "__device__ __forceinline__ void b200_epilogue_row(unsigned int* b200_r, unsigned int b200_b0, unsigned int b200_b1, "
         "unsigned int b200_m, bool b200_row_ok, unsigned int b200_n0, unsigned int b200_N, uint4* b200_stage, "
-        "bool b200_has_next, unsigned int b200_next_taddr, b200_in_tiles& b200_t, unsigned int b200_slot, unsigned int b200_nslots"
+        "bool b200_has_next, unsigned int b200_next_taddr, b200_in_tiles& b200_t, unsigned int b200_slot, unsigned int b200_nslots, "
+        "bool b200_nx_ok, unsigned int b200_nx_b0, unsigned int b200_nx_b1, unsigned int b200_nx_m, bool b200_nx_row_ok, unsigned int b200_nx_n0"
      << params << ") {\n"
      << statics_prologue;
   fn << "  const unsigned int b200_lane = threadIdx.x & 31u;\n";
@@ -1018,8 +1019,12 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   recover(dn, "b200_n");
   fn << ep.str() << body << "    }\n  }\n";
   // the accumulator chunk is consumed: start fetching the next one while this one is stored
+  // ... or, after the tile's last chunk, the operand tiles of the first chunk of this warp's NEXT
+  // tile: their latency then hides behind this chunk's stores and the wait for the next accumulator
   fn << "  B200_TRE(13);\n  if (b200_has_next) {\n    b200_tmem_ld_chunk(b200_next_taddr, b200_r);\n"
-     << "    b200_epilogue_load(b200_t, b200_b0, b200_b1, b200_m, b200_row_ok, b200_n0 + B200_EPI_CHUNK, b200_N" << args << ");\n  }\n";
+     << "    b200_epilogue_load(b200_t, b200_b0, b200_b1, b200_m, b200_row_ok, b200_n0 + B200_EPI_CHUNK, b200_N" << args << ");\n"
+     << "  } else if (b200_nx_ok) {\n"
+     << "    b200_epilogue_load(b200_t, b200_nx_b0, b200_nx_b1, b200_nx_m, b200_nx_row_ok, b200_nx_n0, b200_N" << args << ");\n  }\n";
   // ---- store the register tiles.  A thread owns one row of the chunk, so storing from
   //      registers would touch 32 different lines per instruction; when the chunk is whole,
   //      contiguous and every row is 16-byte aligned, the warp transposes the chunk through a
@@ -1228,7 +1233,7 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   o << "#define B200_EPI_PARAMS " << params << "\n";
   o << "#define B200_EPILOGUE_ROWS b200_epilogue_rows(b200_tiles, b200_b0, b200_b1, b200_m, b200_m < shape.M" << args << ");\n";
   o << "#define B200_EPILOGUE_LOAD b200_epilogue_load(b200_tiles, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_pn0, shape.N" << args << ");\n";
-  o << "#define B200_EPILOGUE_ROW b200_epilogue_row(b200_r, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_n0, shape.N, b200_stage, b200_has_next, b200_next_taddr, b200_tiles, b200_slot, b200_nslots" << args << ");\n";
+  o << "#define B200_EPILOGUE_ROW b200_epilogue_row(b200_r, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_n0, shape.N, b200_stage, b200_has_next, b200_next_taddr, b200_tiles, b200_slot, b200_nslots, b200_nx_ok, b200_nx_b0, b200_nx_b1, b200_nx_m, b200_nx_m < shape.M, b200_nx_n0" << args << ");\n";
   o << kGemmSource << "\n";
   std::ostringstream note;
   note << "tcgen05 " << (g.in_prec == Prec::Single ? "tf32 " : "") << bm << "x" << bn << "x" << bk << (pair ? " (CTA pair, cta_group::2)" : "") << " stages=" << stages

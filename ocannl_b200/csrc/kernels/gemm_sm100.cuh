@@ -445,29 +445,47 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
     // this warp's 4 KB staging tile (transposes a chunk so that stores cover whole row segments)
     uint4* b200_stage = (uint4*)(smem_gen + B200_STAGES * B200_STAGE_BYTES + 256 + ew * (unsigned int)B200_STAGING_BYTES);
     unsigned int acc = 0, acc_phase = 0;
-    for (unsigned int unit = worker; unit < total_units; unit += n_workers) {
-      const unsigned int tile = unit % total_tiles;
+    // (batch, row, first column) of the part of a unit's tile that this thread works on
+    auto b200_coords = [&](unsigned int u, unsigned int& tile, unsigned int& b0, unsigned int& b1, unsigned int& mt, unsigned int& nt) {
+      tile = u % total_tiles;
       const unsigned int bidx = tile / tiles_per_batch;
       const unsigned int t = tile - bidx * tiles_per_batch;
       const unsigned int group = t / (B200_RASTER * shape.tiles_n);
       const unsigned int first_m = group * B200_RASTER;
       const unsigned int rows = min((unsigned int)B200_RASTER, shape.tiles_m - first_m);
       const unsigned int r = t - group * B200_RASTER * shape.tiles_n;
-      const unsigned int mt = first_m + r % rows;
-      const unsigned int nt = r / rows;
-      const unsigned int b200_b0 = bidx / shape.B1, b200_b1 = bidx - b200_b0 * shape.B1;
+      mt = first_m + r % rows;
+      nt = r / rows;
+      b0 = bidx / shape.B1;
+      b1 = bidx - b0 * shape.B1;
+    };
+    // operand tiles of the epilogue (bias, mask, residual rows ...): loaded for a tile's first chunk
+    // before its accumulator is waited for -- by the previous tile's last chunk when there was one
+    b200_in_tiles b200_tiles;
+    bool b200_prefetched = false;
+    for (unsigned int unit = worker; unit < total_units; unit += n_workers) {
+      unsigned int tile, b200_b0, b200_b1, mt, nt;
+      b200_coords(unit, tile, b200_b0, b200_b1, mt, nt);
       const unsigned int b200_m = mt * B200_BM + cta_rank * B200_CTA_M + quarter * 32u + lane;
       // one scratch slot per (tile, CTA, epilogue warp) for epilogues that end in a grid-wide sum
       const unsigned int b200_slot = (tile * (1u + B200_CTA_PAIR) + cta_rank) * B200_EPI_WARPS + ew;
       const unsigned int b200_nslots = total_tiles * (1u + B200_CTA_PAIR) * B200_EPI_WARPS;
-      // while the tensor cores are still busy with this tile, load the epilogue's operands (bias,
-      // mask, residual rows ...) of the first chunk this warp owns
-      b200_in_tiles b200_tiles;
+      // this warp's share of the next tile, for the prefetch at the end of this one
+      bool b200_nx_ok = false;
+      unsigned int b200_nx_b0 = 0, b200_nx_b1 = 0, b200_nx_m = 0, b200_nx_n0 = 0;
+      if (unit + n_workers < total_units) {
+        unsigned int ntile, nmt, nnt;
+        b200_coords(unit + n_workers, ntile, b200_nx_b0, b200_nx_b1, nmt, nnt);
+        b200_nx_m = nmt * B200_BM + cta_rank * B200_CTA_M + quarter * 32u + lane;
+        b200_nx_n0 = nnt * B200_BN + col_half * cols_per_warp;
+        b200_nx_ok = b200_nx_n0 < shape.N;
+      }
       B200_EPILOGUE_ROWS
-      {
+      if (!b200_prefetched) {
         const unsigned int b200_pn0 = nt * B200_BN + col_half * cols_per_warp;
         if (b200_pn0 < shape.N) { B200_EPILOGUE_LOAD }
       }
+      b200_prefetched = b200_nx_ok && (nt * B200_BN + col_half * cols_per_warp < shape.N);
       if (!b200_wait(bar_acc_full + 8u * acc, acc_phase, abort_flag, status, 4u)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (warp == 2 && lane == 0) { if (unit == worker) B200_TR(8); else if (unit == worker + n_workers) B200_TR(10); }
