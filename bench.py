@@ -267,7 +267,7 @@ def _time_routine(dev, rt, code, runs, pk, statics=None, flush_pool=None):
         e = {"kernel": s["kernel"] or "memset", "kind": s["kind"], "ms": round(ms, 5), "bytes": s.get("bytes", 0)}
         if ms > 0:
             e["gbs"] = round(s.get("bytes", 0) / ms / 1e6, 1)
-            if s["kind"] == "gemm":
+            if s["kind"] in ("gemm", "attention"):
                 e["tflops"] = round(s["flops"] / ms / 1e9, 1)
         out.append(e)
     return total / runs, out
@@ -315,20 +315,28 @@ def other_configs(dev, pk):
         ms, st, nk = run(W.makemore_forward(wprec=wp), inp, 30)
         res["makemore_forward_" + wp] = {"ms_per_step": ms, "samples_per_s": 4096 / (ms / 1e3), "kernels": nk,
                                          "stages": st}
-    # config 4: decoder-only transformer forward, batch 64 x 256 tokens
-    ir = W.transformer_forward()
+    # config 4: decoder-only transformer forward, batch 64 x 256 tokens.  Twice: with the attention
+    # chain's intermediate nodes (scores, exponentials, weights: 335 MB per layer) held by the context,
+    # so that the fused attention stage must write them, and with those nodes routine-local, where it
+    # writes none of them.
     inp = dict(W.transformer_params(), **W.transformer_inputs())
-    ms, st, nk = run(ir, inp, 5)
-    flops = sum(s_["flops"] for s_ in bk.Code(ir).info()["stages"] if s_["kind"] == "gemm")
-    top = sorted(st, key=lambda e: -e["ms"])[:8]
-    gen = [e for e in st if e["kind"] == "generic" and e["ms"] > 0]
-    res["decoder_forward"] = {
-        "ms_per_step": ms, "samples_per_s": 64 / (ms / 1e3), "tokens_per_s": 64 * 256 / (ms / 1e3), "kernels": nk,
-        "contraction_tflops_over_whole_step": flops / ms / 1e9, "top_stages": top,
-        "generic_stage_time_ms": round(sum(e["ms"] for e in gen), 4),
-        "contraction_stage_time_ms": round(sum(e["ms"] for e in st if e["kind"] == "gemm"), 4),
-        "generic_gbs_weighted": round(sum(e["bytes"] for e in gen) / max(sum(e["ms"] for e in gen), 1e-9) / 1e6, 1),
-        "hbm_peak_gbs": pk["hbm"]}
+    for key, mode in (("decoder_forward", "ctx"), ("decoder_forward_local_attention_nodes", "local")):
+        ir = W.transformer_forward(attn_nodes=mode)
+        ms, st, nk = run(ir, inp, 5)
+        flops = sum(s_["flops"] for s_ in bk.Code(ir).info()["stages"] if s_["kind"] in ("gemm", "attention"))
+        top = sorted(st, key=lambda e: -e["ms"])[:8]
+        gen = [e for e in st if e["kind"] == "generic" and e["ms"] > 0]
+        att = [e for e in st if e["kind"] == "attention" and e["ms"] > 0]
+        res[key] = {
+            "ms_per_step": ms, "samples_per_s": 64 / (ms / 1e3), "tokens_per_s": 64 * 256 / (ms / 1e3), "kernels": nk,
+            "attention_nodes": "held by the context (written)" if mode == "ctx" else "routine-local (never written)",
+            "contraction_tflops_over_whole_step": flops / ms / 1e9, "top_stages": top,
+            "generic_stage_time_ms": round(sum(e["ms"] for e in gen), 4),
+            "contraction_stage_time_ms": round(sum(e["ms"] for e in st if e["kind"] == "gemm"), 4),
+            "attention_stage_time_ms": round(sum(e["ms"] for e in att), 4),
+            "attention_stage_gbs": round(sum(e["bytes"] for e in att) / max(sum(e["ms"] for e in att), 1e-9) / 1e6, 1),
+            "generic_gbs_weighted": round(sum(e["bytes"] for e in gen) / max(sum(e["ms"] for e in gen), 1e-9) / 1e6, 1),
+            "hbm_peak_gbs": pk["hbm"]}
     dev.free_pool(flush_pool)
     return res
 
@@ -422,6 +430,41 @@ def probe_attention_scores(dev):
         ms = e0.elapsed_ms(e1) / 10
         nbytes = 2 * B * S * H * E * 2 + B * S * H * S * 4
         out[variant] = {"us": round(1e3 * ms, 2), "gbs": round(nbytes / ms / 1e6, 1), "note": rt.info()["stages"][0]["note"]}
+        pools = {p for p, _, _ in rt.context.arrays.values()}
+        rt.free()
+        code.free()
+        for p in pools:
+            dev.free_pool(p)
+    return out
+
+
+def probe_attention(dev, batch=64, heads=8, seq=256):
+    """One attention layer of the decoder as a routine of its own (64 sequences, 256 positions, 8
+    heads of 64): the fused stage with the intermediate nodes held by the context (all written) and
+    routine-local (none written), and the separate stages (`attn=0`).  A small case for profilers and
+    for the numbers quoted beside the kernel."""
+    from ocannl_b200 import backend as bk
+    from ocannl_b200 import workloads as W
+    out = {}
+    inputs = W.attention_inputs(batch, heads, seq, seq)
+    for key, mode, options in (("fused, nodes kept", "ctx", None), ("fused, nodes local", "local", None),
+                               ("separate stages, nodes kept", "ctx", "attn=0")):
+        code = bk.Code(W.attention(batch, heads, seq, seq, row_mode=mode), options)
+        rt = bk.Context(dev).link(code)
+        for k, v in inputs.items():
+            rt.context.from_host(k, v)
+        for _ in range(3):
+            rt.run()
+        dev.await_()
+        e0 = dev.all_work()
+        for _ in range(10):
+            rt.run()
+        e1 = dev.all_work()
+        e1.sync()
+        ms = e0.elapsed_ms(e1) / 10
+        st = rt.info()["stages"]
+        out[key] = {"us": round(1e3 * ms, 2), "kernels": rt.kernels_per_run(), "bytes": sum(s_["bytes"] for s_ in st),
+                    "gbs": round(sum(s_["bytes"] for s_ in st) / ms / 1e6, 1), "notes": [s_["note"] for s_ in st]}
         pools = {p for p, _, _ in rt.context.arrays.values()}
         rt.free()
         code.free()
@@ -615,7 +658,8 @@ def main():
     ap.add_argument("--no-configs", action="store_true", help="skip the configs 1, 2 and 4 section")
     ap.add_argument("--sweep-size", type=int, default=0,
                     help="run only the batch-8 contraction of this M=N=K (a small case for profilers) and exit")
-    ap.add_argument("--probe", default="", help="'attention_scores': time the decoder's score contraction alone and exit")
+    ap.add_argument("--probe", default="", help="'attention_scores': time the decoder's score contraction alone and exit; "
+                    "'attention' / 'attention_small': one attention layer alone (64 x 8 or 8 x 8 (batch, head) pairs)")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -640,6 +684,9 @@ def main():
     dev = bk.Device(local)
     if args.sweep_size:
         print(json.dumps({"contraction_sweep": contraction_sweep(dev, pk, (args.sweep_size,))}))
+        return
+    if args.probe in ("attention", "attention_small"):
+        print(json.dumps({args.probe: probe_attention(dev, batch=64 if args.probe == "attention" else 8)}))
         return
     if args.probe == "attention_scores":
         print(json.dumps({"attention_scores": probe_attention_scores(dev)}))

@@ -21,10 +21,11 @@ OUT = os.path.join(HERE, "_build")
 LIB = os.path.join(HERE, "libb200.so")
 CUDA = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
-HOST_SOURCES = ["ir.cpp", "emit.cpp", "compile.cpp", "gemm_match.cpp", "driver.cpp", "runtime.cpp",
+HOST_SOURCES = ["ir.cpp", "emit.cpp", "compile.cpp", "gemm_match.cpp", "attn_match.cpp", "driver.cpp", "runtime.cpp",
                 "gemm_launch.cpp", "api.cpp"]
 CUDA_SOURCES = ["sum_static.cu"]
-EMBED = {"kNumericsSource": "kernels/numerics.cuh", "kGemmSource": "kernels/gemm_sm100.cuh"}
+EMBED = {"kNumericsSource": "kernels/numerics.cuh", "kTcSource": "kernels/tc_sm100.cuh",
+         "kGemmSource": "kernels/gemm_sm100.cuh", "kAttnSource": "kernels/attn_sm100.cuh"}
 
 
 def _embed() -> str:

@@ -447,6 +447,7 @@ int b200_compile(const char* name, const char* ir, size_t len, const char* optio
         std::string k = kv.substr(0, eq), v = eq == std::string::npos ? "1" : kv.substr(eq + 1);
         bool on = v != "0";
         if (k == "gemm") opt.enable_gemm = on;
+        else if (k == "attn") opt.enable_attn = on;
         else if (k == "coop") opt.enable_coop = on;
         else if (k == "fuse") opt.enable_fuse = on;
         else if (k == "pairs") opt.enable_pairs = on;
@@ -473,7 +474,7 @@ std::unique_ptr<b200_code> build_code(const std::string& name, const std::string
   for (auto& s : code->code.stages) any_generic |= s.kind == Stage::Generic;
   if (any_generic) code->cubin = &compile_cubin(code->code.source, code->code.prog.name);
   for (auto& s : code->code.stages)
-    if (s.kind == Stage::Gemm) code->gemm_cubins.push_back(&compile_cubin(s.gemm_source, s.kernel));
+    if (s.own_module()) code->gemm_cubins.push_back(&compile_cubin(s.gemm_source, s.kernel));
     else code->gemm_cubins.push_back(nullptr);
   return code;
 }
@@ -512,7 +513,7 @@ int b200_code_source(b200_code* code, int stage, char* buf, size_t cap, size_t* 
     const std::string* s = &code->code.source;
     if (stage >= 0) {
       if (stage >= (int)code->code.stages.size()) throw Error(B200_E_INVALID, "stage out of range");
-      if (code->code.stages[stage].kind == Stage::Gemm) s = &code->code.stages[stage].gemm_source;
+      if (code->code.stages[stage].own_module()) s = &code->code.stages[stage].gemm_source;
     }
     if (needed) *needed = s->size() + 1;
     if (buf && cap) copy_out(*s, buf, cap);

@@ -17,6 +17,9 @@
 
 namespace b200 {
 
+bool match_attention(const Program& P, const std::vector<StmtP>& flat, size_t at, const CompileOptions& opt, int* n_absorbed,
+                     Stage* out);
+std::string attn_translation_unit(const Program& P, Stage& st, const std::string& kernel_name);
 bool match_gemm(const Program& P, const std::vector<LoopDim>& nest, const Stmt& body, bool zeroed_before,
                 const CompileOptions& opt, const std::vector<Follower>& followers, int* n_fused,
                 Stage* out);  // gemm_match.cpp
@@ -211,7 +214,7 @@ std::string Code::describe() const {
   for (size_t i = 0; i < stages.size(); ++i) {
     const Stage& s = stages[i];
     if (i) o << ",";
-    o << "{\"kind\":\"" << (s.kind == Stage::Memset ? "memset" : s.kind == Stage::Gemm ? "gemm" : "generic") << "\"";
+    o << "{\"kind\":\"" << (s.kind == Stage::Memset ? "memset" : s.kind == Stage::Gemm ? "gemm" : s.kind == Stage::Attn ? "attention" : "generic") << "\"";
     o << ",\"kernel\":\"" << s.kernel << "\",\"total\":" << s.total << ",\"coop\":" << s.coop;
     if (s.kind == Stage::Gemm) {
       o << ",\"m\":" << s.gemm.m.extent << ",\"n\":" << s.gemm.n.extent << ",\"k\":" << s.gemm.k.extent;
@@ -220,12 +223,19 @@ std::string Code::describe() const {
       o << ",\"batch\":" << b << ",\"a_kmajor\":" << (s.gemm.a_kmajor ? 1 : 0) << ",\"b_kmajor\":" << (s.gemm.b_kmajor ? 1 : 0)
         << ",\"accumulate\":" << (s.gemm.accumulate ? 1 : 0) << ",\"flops\":" << s.gemm.flops();
     }
+    if (s.kind == Stage::Attn) {
+      const AttnPlan& a = s.attn;
+      // both contractions: queries x keys x head dimension, twice
+      o << ",\"queries\":" << a.S << ",\"keys\":" << a.T << ",\"head_dim\":" << a.E << ",\"batch\":" << a.B0 * a.B1
+        << ",\"flops\":" << 4.0 * (double)(a.B0 * a.B1) * (double)a.S * (double)a.T * (double)a.E;
+    }
     if (s.kind != Stage::Memset) {
       // bytes of every node the stage touches, each counted once: the stage's algorithmic traffic
       long long bytes = 0;
       for (auto& a : s.args)
         if (a.kind == KArg::Node) bytes += prog.tn(a.tn).bytes();
       if (s.kind == Stage::Gemm) bytes += prog.tn(s.gemm.a_tn).bytes() + prog.tn(s.gemm.b_tn).bytes();
+      if (s.kind == Stage::Attn) bytes += prog.tn(s.attn.q_tn).bytes() + prog.tn(s.attn.k_tn).bytes() + prog.tn(s.attn.v_tn).bytes();
       o << ",\"bytes\":" << bytes;
     } else {
       o << ",\"bytes\":" << prog.tn(s.memset_tn).bytes();
@@ -2047,6 +2057,21 @@ struct Builder {
           zero_read.insert(e.tn);
       }, [](const Stmt&) {});
       for (int w : writes_now) zeroed.erase(w);
+      if (opt.enable_attn && gemm_at(i) && body->kind == Stmt::Set && i + 6 <= flat.size()) {
+        // scores, softmax and weights . values as one kernel
+        bool allowed = true;
+        for (size_t k = i; k < i + 6; ++k) allowed = allowed && gemm_at(k);
+        Stage a;
+        int n_abs = 0;
+        if (allowed && match_attention(code.prog, flat, i, opt, &n_abs, &a)) {
+          for (int w : a.writes) zeroed.erase(w);
+          a.kernel = kernel_name();
+          a.gemm_source = attn_translation_unit(code.prog, a, a.kernel);
+          code.stages.push_back(a);
+          i += (size_t)n_abs - 1;
+          return;
+        }
+      }
       if (gemm_at(i) && body->kind == Stmt::Set) {
         Stage g;
         int n_fused = 0;
@@ -2074,8 +2099,18 @@ struct Builder {
     }
     emit_kernels();
     code.source = src.str();
+    // routine-local nodes that some stage touches get scratch (a node whose every use was fused
+    // away, such as the score matrix of a fused attention stage, needs none)
+    std::set<int> touched;
+    for (auto& st : code.stages) {
+      if (st.kind == Stage::Memset) touched.insert(st.memset_tn);
+      for (auto& a : st.args)
+        if (a.kind == KArg::Node) touched.insert(a.tn);
+      if (st.kind == Stage::Gemm) { touched.insert(st.gemm.a_tn); touched.insert(st.gemm.b_tn); touched.insert(st.gemm.d_tn); }
+      if (st.kind == Stage::Attn) { touched.insert(st.attn.q_tn); touched.insert(st.attn.k_tn); touched.insert(st.attn.v_tn); }
+    }
     for (auto& t : code.prog.tnodes)
-      if (t.mode == Mode::Local) code.local_nodes.push_back(t.id);
+      if (t.mode == Mode::Local && touched.count(t.id)) code.local_nodes.push_back(t.id);
   }
 };
 

@@ -45,8 +45,23 @@ struct GemmPlan {
   double flops() const;
 };
 
+// The fused attention chain (attn_match.cpp): operand layouts for the three tensor maps and the
+// generated device functions.  Strides are in elements.
+struct AttnPlan {
+  int q_tn = -1, k_tn = -1, v_tn = -1;
+  int64_t q_off = 0, k_off = 0, v_off = 0;
+  int64_t S = 0, T = 0, E = 0, B0 = 1, B1 = 1;   // queries, keys, head dimension, batch extents (outer, inner)
+  int64_t q_row = 0, k_row = 0, v_row = 0;      // stride of the query / key position
+  int64_t q_b0 = 0, q_b1 = 0, k_b0 = 0, k_b1 = 0, v_b0 = 0, v_b1 = 0;
+  Prec in_prec = Prec::Bfloat16;
+  int out_bytes = 2;
+  int n_cond = 0;          // operands of the score expression handed to the kernel as one bit per element
+  std::string code;
+};
+
 struct Stage {
-  enum Kind { Memset, Generic, Gemm } kind = Generic;
+  enum Kind { Memset, Generic, Gemm, Attn } kind = Generic;
+  bool own_module() const { return kind == Gemm || kind == Attn; }   // compiled as a translation unit of its own
   int memset_tn = -1;
   std::string kernel;            // kernel symbol in the routine's module
   std::vector<KArg> args;
@@ -57,6 +72,7 @@ struct Stage {
   int coop = 0;                  // >0: lanes cooperating on one output element (row reductions)
   int grid_override = 0;         // >0: launch exactly this many blocks (first pass of a grid-wide reduction)
   GemmPlan gemm;
+  AttnPlan attn;
   std::string gemm_source;       // full translation unit of this stage's contraction kernel
   std::string epi_params, epi_args;  // epilogue plumbing: extra kernel parameters / call arguments
   int tile_m = 0, tile_n = 0, tile_k = 0;
@@ -94,6 +110,7 @@ struct CompileOptions {
   bool enable_fuse = true;   // several small stages in one single-block kernel
   bool enable_splitk = true; // few-tile accumulations split K over the idle SMs (fp32 atomic adds: order not fixed)
   bool enable_pairs = true;  // contraction epilogues over pairs of columns with packed 16-bit arithmetic
+  bool enable_attn = true;   // the attention chain as one fused kernel
   bool enable_tf32 = true;   // single-precision operands of a contraction go through the tensor cores as tf32
   bool large_models = false;
   // Top-level statements (by index) that must not use the forms with alignment demands: the pair
@@ -107,6 +124,8 @@ Code compile_program(Program prog, const CompileOptions& opt);
 
 // The numeric helper prelude shared by every generated kernel (embedded at build time).
 extern const char* kNumericsSource;
+extern const char* kTcSource;
 extern const char* kGemmSource;
+extern const char* kAttnSource;
 
 }  // namespace b200

@@ -246,7 +246,7 @@ static std::string binop_plain(Prec prec, const std::string& op, const std::stri
   if (op == "add") return "(" + a + " + " + b + ")";
   if (op == "sub") return "(" + a + " - " + b + ")";
   if (op == "mul") return "(" + a + " * " + b + ")";
-  if (op == "div") return "(" + a + " / " + b + ")";
+  if (op == "div") return (!integ && !dbl) ? "b200_fdiv(" + a + ", " + b + ")" : "(" + a + " / " + b + ")";
   if (op == "pow") {
     if (integ) throw Error(-4, "pow is not defined for integer precisions");
     return (dbl ? "pow(" : "powf(") + a + ", " + b + ")";
@@ -329,6 +329,14 @@ std::string Emitter::binop(Prec prec, const std::string& op, const std::string& 
   // 8-bit floats: widen, operate in float, narrow -- every time (arrayjit/lib/cc_backend.ml:169-322)
   if (prec == Prec::Fp8) return "b200_f2fp8(" + binop_plain(Prec::Single, op, "b200_fp82f(" + a + ")", "b200_fp82f(" + b + ")") + ")";
   if (lowp(prec) && selects_exactly(op)) return binop_plain(Prec::Single, op, a, b);
+  if (op == "div" && (lowp(prec) || prec == Prec::Single)) {
+    // a divisor that the caller prepared once for many numerators (see b200_divisor in numerics.cuh)
+    auto it = divisor_vars.find(b);
+    if (it != divisor_vars.end()) {
+      const std::string q = "b200_div_by(" + a + ", " + it->second + ")";
+      return lowp(prec) ? std::string(round_fn(prec)) + q + ")" : q;
+    }
+  }
   if (lowp(prec)) return std::string(round_fn(prec)) + binop_plain(Prec::Single, op, a, b) + ")";
   return binop_plain(prec, op, a, b);
 }

@@ -52,6 +52,9 @@ struct Emitter {
   std::vector<RowForward> row_forwards;
   std::map<std::string, std::string> row_ren;
   bool unroll_loops = false;   // `#pragma unroll` before every emitted loop (register arrays stay registers)
+  // divisors prepared once for many numerators: emitted text of the divisor -> name of a b200_divisor
+  // variable in scope; a single-precision (or 16-bit) division by exactly that text uses it
+  std::map<std::string, std::string> divisor_vars;
   // nodes read through another name (a copy staged in shared memory)
   std::map<int, std::string> node_alias;
   // nodes whose loads may use the read-only data path

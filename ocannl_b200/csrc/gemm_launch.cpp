@@ -152,3 +152,85 @@ void gemm_enqueue(b200_routine* r, int si) {
 }
 
 void gemm_release(GemmLaunch* g) { delete g; }
+
+// ---- fused attention stages: three tensor maps (queries and keys k-major, values n-major), one
+//      CTA per (batch, head, 128 queries)
+
+// must match b200_attn_shape in kernels/attn_sm100.cuh
+struct AttnShape {
+  unsigned int S, B0, B1, tiles_s;
+};
+
+struct AttnLaunch {
+  CUtensorMap map_q, map_k, map_v;
+  AttnShape shape;
+  unsigned int grid = 1;
+  CUdeviceptr status = 0;
+};
+
+AttnLaunch* attn_prepare(b200_routine* r, int si) {
+  const Stage& st = r->code->code.stages[si];
+  const AttnPlan& a = st.attn;
+  const Program& P = r->code->code.prog;
+  auto ptr = [&](int tn) {
+    auto it = r->node_ptr.find(tn);
+    if (it == r->node_ptr.end()) throw Error(B200_E_USER, "link: node '" + P.tn(tn).ident + "' has no buffer binding");
+    return it->second;
+  };
+  const int eb = prec_bytes(a.in_prec);
+  const CUdeviceptr q = ptr(a.q_tn) + (CUdeviceptr)(a.q_off * eb), k = ptr(a.k_tn) + (CUdeviceptr)(a.k_off * eb),
+                    v = ptr(a.v_tn) + (CUdeviceptr)(a.v_off * eb);
+  if ((q | k | v) & 15)
+    throw Error(B200_E_INVALID, "link: internal error: an attention stage was kept for operands that are not 16-byte aligned");
+  auto* L = new AttnLaunch();
+  try {
+    // in the terms of encode_operand: the head dimension is "k" of the first contraction (unit stride);
+    // the values are the n-major B operand of the second one (n = head dimension, k = key position)
+    std::vector<GemmDim> batch;
+    if (a.B0 > 1 || a.B1 > 1) {
+      GemmDim b0, b1;
+      b0.extent = a.B0;
+      b1.extent = a.B1;
+      batch = {b0, b1};
+    }
+    auto strides = [&](int64_t s0, int64_t s1) {
+      return batch.empty() ? std::vector<int64_t>{} : std::vector<int64_t>{a.B0 > 1 ? s0 : 0, a.B1 > 1 ? s1 : 0};
+    };
+    GemmDim qs, ks, ed, td;
+    qs.extent = a.S;
+    ks.extent = a.T;
+    ed.extent = a.E;
+    td.extent = a.T;
+    encode_operand(&L->map_q, q, a.in_prec, true, qs, a.q_row, ed, 1, batch, strides(a.q_b0, a.q_b1), 128, (int)a.E);
+    encode_operand(&L->map_k, k, a.in_prec, true, ks, a.k_row, ed, 1, batch, strides(a.k_b0, a.k_b1), (int)a.T, (int)a.E);
+    encode_operand(&L->map_v, v, a.in_prec, false, ed, 1, td, a.v_row, batch, strides(a.v_b0, a.v_b1), (int)a.E, (int)a.T);
+  } catch (...) {
+    delete L;
+    throw;
+  }
+  L->shape.S = (unsigned)a.S;
+  L->shape.B0 = (unsigned)a.B0;
+  L->shape.B1 = (unsigned)a.B1;
+  L->shape.tiles_s = (unsigned)((a.S + 127) / 128);
+  L->grid = L->shape.tiles_s * L->shape.B0 * L->shape.B1;
+  cu_check(cu().cuFuncSetAttribute_(r->fns[si], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, st.smem_bytes),
+           "cuFuncSetAttribute(max dynamic shared memory)");
+  L->status = r->dev->status_dev;
+  return L;
+}
+
+void attn_enqueue(b200_routine* r, int si) {
+  const Stage& st = r->code->code.stages[si];
+  AttnLaunch* L = r->attn[si];
+  std::vector<void*> args;
+  args.push_back(&L->map_q);
+  args.push_back(&L->map_k);
+  args.push_back(&L->map_v);
+  args.push_back(&L->shape);
+  args.push_back(&L->status);
+  std::vector<CUdeviceptr>& vals = r->arg_values[si];
+  for (size_t a = 0; a < vals.size(); ++a) args.push_back(&vals[a]);
+  launch_kernel(r->dev, r->fns[si], L->grid, (unsigned)st.block, 1, (unsigned)st.smem_bytes, args.data(), "cuLaunchKernelEx(attention)", 1u);
+}
+
+void attn_release(AttnLaunch* a) { delete a; }

@@ -1234,7 +1234,7 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   o << "#define B200_EPILOGUE_ROWS b200_epilogue_rows(b200_tiles, b200_b0, b200_b1, b200_m, b200_m < shape.M" << args << ");\n";
   o << "#define B200_EPILOGUE_LOAD b200_epilogue_load(b200_tiles, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_pn0, shape.N" << args << ");\n";
   o << "#define B200_EPILOGUE_ROW b200_epilogue_row(b200_r, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_n0, shape.N, b200_stage, b200_has_next, b200_next_taddr, b200_tiles, b200_slot, b200_nslots, b200_nx_ok, b200_nx_b0, b200_nx_b1, b200_nx_m, b200_nx_m < shape.M, b200_nx_n0" << args << ");\n";
-  o << kGemmSource << "\n";
+  o << kTcSource << "\n" << kGemmSource << "\n";
   std::ostringstream note;
   note << "tcgen05 " << (g.in_prec == Prec::Single ? "tf32 " : "") << bm << "x" << bn << "x" << bk << (pair ? " (CTA pair, cta_group::2)" : "") << " stages=" << stages
        << " epi_warps=" << epi_warps << (g.split_k > 1 ? " split_k=" + std::to_string(g.split_k) : std::string())

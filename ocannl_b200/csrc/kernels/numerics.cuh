@@ -311,6 +311,41 @@ __device__ __forceinline__ void b200_st_row16(unsigned short* p, const float* r)
   b200_st_words<2 * N>(p, w);
 }
 
+// IEEE single-precision division.  A zero over a finite non-zero value is a signed zero; giving
+// the division sequence a numerator of one in that case (and selecting the zero afterwards) keeps
+// such lanes -- the masked entries of a softmax row -- off the sequence's slow path, which the whole
+// warp would otherwise wait for.  No branch: neighbouring divisions still overlap.
+__device__ __forceinline__ float b200_fdiv(float a, float b) {
+  const bool zero = a == 0.0f && b != 0.0f && b == b;
+  const float q = (zero ? 1.0f : a) / b;
+  return zero ? a * copysignf(1.0f, b) : q;
+}
+// One divisor for many numerators (a softmax row's sum).  With r = RN(1 / b): q0 = RN(a r) is within
+// one unit in the last place of a / b, the remainder a - q0 b is exact in one fused multiply-add, and
+// RN(q0 + remainder r) is the correctly rounded quotient (Markstein's correction step, the one the
+// division sequence itself uses) as long as nothing overflows or falls below the normal range;
+// quotients below the normal range may differ in their last place.  Divisors outside [2^-60, 2^60]
+// take the plain division.
+struct b200_divisor {
+  float b, r;
+  bool fast;
+};
+__device__ __forceinline__ b200_divisor b200_divisor_of(float b) {
+  b200_divisor d;
+  d.b = b;
+  d.r = 1.0f / b;
+  const float m = fabsf(b);
+  d.fast = m >= 0x1p-60f && m <= 0x1p+60f;
+  return d;
+}
+// the short sequence; the caller has checked d.fast
+__device__ __forceinline__ float b200_div_by(float a, const b200_divisor& d) {
+  const float q0 = a * d.r;
+  const float rem = fmaf(-q0, d.b, a);
+  const float q = fmaf(rem, d.r, q0);
+  return fabsf(q0) == B200_INF ? q0 : q;   // an infinite numerator (or an overflow) stays infinite
+}
+
 // ---- warp-level combine used by cooperative (one warp per output element) reductions
 __device__ __forceinline__ float b200_warp_sum(float v) {
 #pragma unroll

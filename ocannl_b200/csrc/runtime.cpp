@@ -36,6 +36,10 @@ void b200_dev::check_status() {
             status_host[2], status_host[3], status_host[4], status_host[5], status_host[6], status_host[7], status_host[8],
             status_host[9], status_host[10], status_host[11], status_host[12], status_host[16 + 3], status_host[16 + 4],
             status_host[16 + 13], status_host[16 + 14], status_host[16 + 15], status_host[16 + 5]);
+    fprintf(stderr, "[b200 trace] attention CTA, ns since its start: setup %u, q and k landed %u, scores ready %u, pass 1 %u, pass 2 %u, "
+                    "pass 3 %u, second mma issued %u, weights copied %u, output ready %u, stored %u\n",
+            status_host[40], status_host[41], status_host[42], status_host[43], status_host[44], status_host[45], status_host[46],
+            status_host[47], status_host[48], status_host[49]);
   }
   if (status_host && status_host[0] != 0) {
     unsigned int code = status_host[0], where = status_host[1];
@@ -71,6 +75,13 @@ static bool misaligned_stages(const b200_code* c, const std::map<int, CUdevicept
       const CUdeviceptr a = at(st.gemm.a_tn) + (CUdeviceptr)(st.gemm.a_off * eb), b = at(st.gemm.b_tn) + (CUdeviceptr)(st.gemm.b_off * eb);
       (void)P;
       if ((a & 15) || (b & 15))
+        for (int o : st.origins) any |= no_gemm_at->insert(o).second;
+    } else if (st.kind == Stage::Attn) {
+      // tensor maps over the queries, keys and values; 16-byte row stores into every node it writes
+      bool bad = ((at(st.attn.q_tn) | at(st.attn.k_tn) | at(st.attn.v_tn)) & 15) != 0;
+      for (auto& a : st.args)
+        if (a.kind == KArg::Node && (at(a.tn) & 15) != 0) bad = true;
+      if (bad)
         for (int o : st.origins) any |= no_gemm_at->insert(o).second;
     }
   }
@@ -152,6 +163,7 @@ void b200_routine::link(b200_dev* d, b200_code* c, const b200_binding* b, int n)
   fns.assign(ns, nullptr);
   arg_values.assign(ns, {});
   gemm.assign(ns, nullptr);
+  attn.assign(ns, nullptr);
   gemm_modules.assign(ns, nullptr);
   for (size_t i = 0; i < ns; ++i) {
     const Stage& st = c->code.stages[i];
@@ -182,7 +194,8 @@ void b200_routine::link(b200_dev* d, b200_code* c, const b200_binding* b, int n)
     } else {
       cu_check(cu().cuModuleLoadData_(&gemm_modules[i], c->gemm_cubins[i]->data()), "cuModuleLoadData(gemm)");
       cu_check(cu().cuModuleGetFunction_(&fns[i], gemm_modules[i], st.kernel.c_str()), "cuModuleGetFunction(gemm)");
-      gemm[i] = gemm_prepare(this, (int)i);
+      if (st.kind == Stage::Attn) attn[i] = attn_prepare(this, (int)i);
+      else gemm[i] = gemm_prepare(this, (int)i);
     }
   }
 }
@@ -291,8 +304,9 @@ void b200_routine::enqueue_stages() {
       return;
     }
     if (st.kind == Stage::Generic && st.total <= 0) return;
-    if (st.kind == Stage::Gemm) {
-      gemm_enqueue(this, (int)i);
+    if (st.kind == Stage::Gemm || st.kind == Stage::Attn) {
+      if (st.kind == Stage::Gemm) gemm_enqueue(this, (int)i);
+      else attn_enqueue(this, (int)i);
       dev->n_launches++;
       return;
     }
@@ -424,6 +438,7 @@ void b200_routine::destroy() {
   }
   buckets.clear();
   for (auto* g : gemm) gemm_release(g);
+  for (auto* a : attn) attn_release(a);
   for (auto m : gemm_modules)
     if (m) cu().cuModuleUnload_(m);
   if (module) cu().cuModuleUnload_(module);

@@ -116,6 +116,7 @@ struct b200_code {
 std::unique_ptr<b200_code> build_code(const std::string& name, const std::string& ir_text, const b200::CompileOptions& opt);
 
 struct GemmLaunch;  // gemm_launch.cpp
+struct AttnLaunch;  // gemm_launch.cpp
 
 struct b200_routine {
   b200_dev* dev = nullptr;
@@ -125,6 +126,7 @@ struct b200_routine {
   std::vector<CUfunction> fns;                     // per stage
   std::vector<std::vector<CUdeviceptr>> arg_values;  // per stage, one per KArg
   std::vector<GemmLaunch*> gemm;                   // per stage
+  std::vector<AttnLaunch*> attn;                   // per stage (fused attention stages)
   std::map<int, CUdeviceptr> node_ptr;
   CUdeviceptr scratch = 0;                         // routine-local nodes
   size_t scratch_bytes = 0;
@@ -159,6 +161,10 @@ struct b200_routine {
 GemmLaunch* gemm_prepare(b200_routine* r, int stage_index);
 void gemm_enqueue(b200_routine* r, int stage_index);
 void gemm_release(GemmLaunch* g);
+// Fused attention stages (gemm_launch.cpp)
+AttnLaunch* attn_prepare(b200_routine* r, int stage_index);
+void attn_enqueue(b200_routine* r, int stage_index);
+void attn_release(AttnLaunch* a);
 
 // One kernel launch on the device's stream, marked for programmatic stream serialisation
 // (runtime.cpp).

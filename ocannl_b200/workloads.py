@@ -482,14 +482,18 @@ def transformer_inputs(batch=64, seq=256, vocab=27, seed=9):
 
 
 def transformer_forward(batch=64, seq=256, layers=6, d_model=512, heads=8, d_head=64, d_ff=2048, vocab=27,
-                        wprec="bfloat16", act="gelu", eps=1e-5) -> Routine:
+                        wprec="bfloat16", act="gelu", eps=1e-5, attn_nodes="ctx") -> Routine:
     """Forward of `Nn_blocks.decoder_only` (lib/nn_blocks.ml:274-296): per layer masked
     multi-head attention (:209-236: q/k/v projections, scores `s | h d ; t | h d => s | t -> h`
     scaled by 1/sqrt(d), `where mask scores -1e9`, softmax over t as in :137-143, `attn +* v`,
     `w_o`), residual, layer_norm as written in :251-258 (`(x - sum_d x) / d`, summed squares),
     FFN (`mlp` with one hidden layer, :119-126), residual, layer_norm; then a linear head.
-    bf16 weights and activations, fp32 accumulators, fp32 softmax and layer-norm statistics."""
+    bf16 weights and activations, fp32 accumulators, fp32 softmax and layer-norm statistics.
+    `attn_nodes` is the memory class of the attention chain's intermediate nodes (scores, max,
+    exponentials, sum, weights): "ctx" when the context holds them, "local" when they are
+    routine-local (the class `C_syntax.compile_proc` gives a node that one routine alone uses)."""
     r = Routine("decoder_fwd_b%d_s%d_l%d" % (batch, seq, layers))
+    AM = attn_nodes
     B, S, D, H, E, F, V = batch, seq, d_model, heads, d_head, d_ff, vocab
     P = wprec
     tokens = r.tn("tokens", P, [B, S, V], read_only=True)
@@ -530,24 +534,24 @@ def transformer_forward(batch=64, seq=256, layers=6, d_model=512, heads=8, d_hea
             xin = x
             body.append(loops([(b, B), (s, S), (h, H), (e, E)], Set(out, (b, s, h, e), reduce_scope(
                 r, out.ident + "_mm", "single", [(i, D)], lambda: (w[h, e, i], xin[b, s, i]), orig=(b, s, h, e)))))
-        scores = r.tn(p + "scores", "single", [B, S, H, S])
+        scores = r.tn(p + "scores", "single", [B, S, H, S], mode=AM)
         b, s, h, t, e = r.syms(5)
         body.append(loops([(b, B), (s, S), (h, H), (t, S)], Set(scores, (b, s, h, t), where(
             mask[s, t],
             reduce_scope(r, p + "qk", "single", [(e, E)], lambda: (q[b, s, h, e], k[b, t, h, e]), orig=(b, s, h, t))
             / math.sqrt(E), Const(-1e9)))))
-        mx = r.tn(p + "max", "single", [B, S, H, 1])
+        mx = r.tn(p + "max", "single", [B, S, H, 1], mode=AM)
         b, s, h, t = r.syms(4)
         body.append(loops([(b, B), (s, S), (h, H)], Set(mx, (b, s, h, 0), reduce_scope(
             r, p + "n_max", "single", [(t, S)], lambda: scores[b, s, h, t], op="max"))))
-        ex = r.tn(p + "exp_vals", "single", [B, S, H, S])
+        ex = r.tn(p + "exp_vals", "single", [B, S, H, S], mode=AM)
         b, s, h, t = r.syms(4)
         body.append(loops([(b, B), (s, S), (h, H), (t, S)], Set(ex, (b, s, h, t), un("exp", scores[b, s, h, t] - mx[b, s, h, 0]))))
-        sm = r.tn(p + "sum_exp", "single", [B, S, H, 1])
+        sm = r.tn(p + "sum_exp", "single", [B, S, H, 1], mode=AM)
         b, s, h, t = r.syms(4)
         body.append(loops([(b, B), (s, S), (h, H)], Set(sm, (b, s, h, 0), reduce_scope(
             r, p + "n_sumexp", "single", [(t, S)], lambda: ex[b, s, h, t], op="add"))))
-        attn = r.tn(p + "attn", P, [B, S, H, S])
+        attn = r.tn(p + "attn", P, [B, S, H, S], mode=AM)
         b, s, h, t = r.syms(4)
         body.append(loops([(b, B), (s, S), (h, H), (t, S)], Set(attn, (b, s, h, t), ex[b, s, h, t] / sm[b, s, h, 0])))
         av = r.tn(p + "av", P, [B, S, H, E])
@@ -591,6 +595,60 @@ def transformer_forward(batch=64, seq=256, layers=6, d_model=512, heads=8, d_hea
     body.append(Comment("end"))
     r.body = Seq(body)
     return r
+
+
+# ------------------------------------------------------------------ attention chain
+def attention(batch: int, heads: int, queries: int, keys: int, prec: str = "bfloat16", mask: bool = True,
+              row_mode: str = "ctx", out_prec: str = None, d_head: int = 64) -> Routine:
+    """The six statements `multi_head_attention` lowers to (lib/nn_blocks.ml:222-236 with the softmax
+    of :137-143), on q [b, s, h, e], k and v [b, t, h, e]: scaled scores (masked by `where` when
+    `mask`), row max, exponentials, row sum, weights, weights . values.  `row_mode` is the memory
+    class of the five intermediate nodes ("ctx": kept by the context, "local": routine-local)."""
+    r = Routine("attention_b%d_h%d_s%d_t%d" % (batch, heads, queries, keys))
+    B, H, S, T, E = batch, heads, queries, keys, d_head
+    q = r.tn("q", prec, [B, S, H, E], read_only=True)
+    k = r.tn("k", prec, [B, T, H, E], read_only=True)
+    v = r.tn("v", prec, [B, T, H, E], read_only=True)
+    m = r.tn("mask", "single", [S, T], read_only=True) if mask else None
+    scores = r.tn("scores", "single", [B, S, H, T], mode=row_mode)
+    mx = r.tn("max", "single", [B, S, H, 1], mode=row_mode)
+    ex = r.tn("exp_vals", "single", [B, S, H, T], mode=row_mode)
+    sm = r.tn("sum_exp", "single", [B, S, H, 1], mode=row_mode)
+    w = r.tn("attn", prec, [B, S, H, T], mode=row_mode)
+    av = r.tn("av", out_prec or prec, [B, S, H, E])
+    body = []
+    b, s, h, t, e = r.syms(5)
+    qk = reduce_scope(r, "qk", "single", [(e, E)], lambda: (q[b, s, h, e], k[b, t, h, e]), orig=(b, s, h, t)) / math.sqrt(E)
+    body.append(loops([(b, B), (s, S), (h, H), (t, T)], Set(scores, (b, s, h, t), where(m[s, t], qk, Const(-1e9)) if mask else qk)))
+    b, s, h, t = r.syms(4)
+    body.append(loops([(b, B), (s, S), (h, H)], Set(mx, (b, s, h, 0), reduce_scope(
+        r, "n_max", "single", [(t, T)], lambda: scores[b, s, h, t], op="max"))))
+    b, s, h, t = r.syms(4)
+    body.append(loops([(b, B), (s, S), (h, H), (t, T)], Set(ex, (b, s, h, t), un("exp", scores[b, s, h, t] - mx[b, s, h, 0]))))
+    b, s, h, t = r.syms(4)
+    body.append(loops([(b, B), (s, S), (h, H)], Set(sm, (b, s, h, 0), reduce_scope(
+        r, "n_sumexp", "single", [(t, T)], lambda: ex[b, s, h, t], op="add"))))
+    b, s, h, t = r.syms(4)
+    body.append(loops([(b, B), (s, S), (h, H), (t, T)], Set(w, (b, s, h, t), ex[b, s, h, t] / sm[b, s, h, 0])))
+    b, s, h, e, t = r.syms(5)
+    body.append(loops([(b, B), (s, S), (h, H), (e, E)], Set(av, (b, s, h, e), reduce_scope(
+        r, "n_av", "single", [(t, T)], lambda: (w[b, s, h, t], v[b, t, h, e]), orig=(b, s, h, e)))))
+    r.body = Seq(body)
+    return r
+
+
+def attention_inputs(batch: int, heads: int, queries: int, keys: int, prec: str = "bfloat16", seed: int = 31, d_head: int = 64):
+    rng = np.random.default_rng(seed)
+    out = {n: store(prec, rng.standard_normal(shape).astype(np.float32))
+           for n, shape in (("q", (batch, queries, heads, d_head)), ("k", (batch, keys, heads, d_head)),
+                            ("v", (batch, keys, heads, d_head)))}
+    # a causal band shifted so that every row keeps at least one key, plus a few holes
+    s_idx, t_idx = np.arange(queries)[:, None], np.arange(keys)[None, :]
+    mask = (t_idx <= (s_idx * keys) // max(queries, 1)).astype(np.float32)
+    mask[rng.integers(0, queries, 16), rng.integers(0, keys, 16)] = 0.0
+    mask[:, 0] = 1.0
+    out["mask"] = mask
+    return out
 
 
 # ------------------------------------------------------------------ config 5 (ii): forward + backward, SGD

@@ -212,3 +212,7 @@ def embedding_lookup(ids_count: int, vocab: int = 4, embed: int = 3, prec: str =
     guard = _force(binop("and", _force(binop("and", _force(lower, D), _force(upper, D)), D), _force(integral, D)), D)
     r.body = loops([(b, ids_count), (o, embed)], Set(emb, (b, o), where(guard, GetDynamic(c, (o, 0), 1, idv()), Const(0.0, prec))))
     return r
+
+
+# the attention chain lives with the workloads (bench.py's probe runs it too)
+from ocannl_b200.workloads import attention, attention_inputs  # noqa: E402,F401

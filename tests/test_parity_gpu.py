@@ -264,7 +264,8 @@ def test_mlp_forward_bf16(device, rows):
     compare(ir, got, want, rtol=2e-2, atol=2e-3)
 
 
-@pytest.mark.parametrize("act,options", [("gelu", None), ("relu", None), ("gelu", "fuse=0 pairs=0")])
+@pytest.mark.parametrize("act,options", [("gelu", None), ("relu", "attn=0"), ("gelu", "fuse=0 pairs=0"),
+                                         ("gelu", "attn=0 fuse=0 pairs=0")])
 def test_decoder_only_forward(device, act, options):
     """Config 4 at reduced width (2 sequences of 128 tokens, 2 layers, 2 heads of 64, d_model 128):
     every stage of the decoder block — batched strided q.k^T and attn.v contractions on the
@@ -278,13 +279,17 @@ def test_decoder_only_forward(device, act, options):
     got, info = run_device(device, ir, inputs, options=options)
     kinds = [s["kind"] for s in info["stages"]]
     notes = [s["note"] or "" for s in info["stages"]]
-    if options is None:       # softmax and layer norm chains run as one warp-per-row kernel each
-        assert sum("one warp per row" in n for n in notes) >= 2 * 3, notes
+    fused_attention = "attn=0" not in (options or "")
+    if "fuse=0" not in (options or ""):   # layer norm (and, apart from the fused attention stage, softmax) chains: one warp-per-row kernel each
+        assert sum("one warp per row" in n for n in notes) >= 2 * (2 if fused_attention else 3), notes
     else:
         assert not any("row-fused" in n or "pairs" in n for n in notes), notes
-    assert kinds.count("gemm") >= 2 * 7, kinds      # q, k, v, q.k^T, attn.v, w_o, ffn, ffn_out per layer
+    # q, k, v, q.k^T, attn.v, w_o, ffn, ffn_out per layer; the fused attention stage holds q.k^T and attn.v
+    assert kinds.count("attention") == (2 if fused_attention else 0), kinds
+    assert kinds.count("gemm") + 2 * kinds.count("attention") >= 2 * 7, kinds
     gemms = [s for s in info["stages"] if s["kind"] == "gemm"]
-    assert any(s["batch"] == 4 and not s["b_kmajor"] for s in gemms)      # attn.v: (b, h) batch, v is n-major
+    if not fused_attention:
+        assert any(s["batch"] == 4 and not s["b_kmajor"] for s in gemms)      # attn.v: (b, h) batch, v is n-major
     compare(ir, got, want, rtol=2e-2, atol=2e-2)
 
 

@@ -44,18 +44,37 @@ def test_training_plan_split_k_and_dropped_zero_outs():
 
 
 def test_decoder_plan_fuses_softmax_and_layer_norm():
-    st = _plan(W.transformer_forward(batch=2, seq=128, layers=2, d_model=128, heads=2, d_head=64, d_ff=256))
+    small = dict(batch=2, seq=128, layers=2, d_model=128, heads=2, d_head=64, d_ff=256)
+    # without the fused attention stage: softmax + 2 layer norms per layer, each a 4-stage warp-per-row kernel
+    st = _plan(W.transformer_forward(**small), "attn=0")
     notes = [s["note"] or "" for s in st]
-    assert sum("row-fused 4 stages, one warp per row" in n for n in notes) == 2 * 3, notes   # softmax + 2 layer norms per layer
-    unfused = _plan(W.transformer_forward(batch=2, seq=128, layers=2, d_model=128, heads=2, d_head=64, d_ff=256), "fuse=0")
+    assert sum("row-fused 4 stages, one warp per row" in n for n in notes) == 2 * 3, notes
+    unfused = _plan(W.transformer_forward(**small), "attn=0 fuse=0")
     assert len(unfused) == len(st) + 2 * 3 * 3
     # the (head, d) columns of the q / k / v projections are one contiguous n axis: stored through the staging tile
-    code = bk.Code(W.transformer_forward(batch=2, seq=128, layers=2, d_model=128, heads=2, d_head=64, d_ff=256))
+    code = bk.Code(W.transformer_forward(**small))
     try:
         first_gemm = [i for i, s in enumerate(st) if s["kind"] == "gemm"][0]
         assert "b200_stage[" in code.source(first_gemm)
     finally:
         code.free()
+
+
+def test_decoder_plan_takes_the_attention_chain_as_one_stage():
+    small = dict(batch=2, seq=128, layers=2, d_model=128, heads=2, d_head=64, d_ff=256)
+    apart = _plan(W.transformer_forward(**small), "attn=0")
+    st = _plan(W.transformer_forward(**small))
+    attn = [s for s in st if s["kind"] == "attention"]
+    assert len(attn) == 2, [s["kind"] for s in st]
+    # scores contraction + softmax kernel + weights . values contraction become one launch per layer
+    assert len(st) == len(apart) - 2 * 2
+    assert all("3 of the 3 row nodes written" in s["note"] for s in attn)     # the context holds every node
+    # routine-local intermediates that nobody reads are not written, and get no scratch
+    local = _plan(W.transformer_forward(attn_nodes="local", **small))
+    assert all("0 of the 3 row nodes written" in s["note"] for s in local if s["kind"] == "attention")
+    # forms the fused kernel does not cover stay with the separate stages: 96 keys, a head dimension of 32
+    assert not any(s["kind"] == "attention" for s in _plan(W.transformer_forward(batch=2, seq=96, layers=1, d_model=128, heads=2, d_head=64, d_ff=256)))
+    assert not any(s["kind"] == "attention" for s in _plan(W.transformer_forward(batch=2, seq=128, layers=1, d_model=64, heads=2, d_head=32, d_ff=256)))
 
 
 def test_random_number_routine_plan():
