@@ -546,7 +546,7 @@ bool match_attention(const Program& P, const std::vector<StmtP>& flat, size_t at
   // E1: the score of one column.  Operands that run along t and vary with s come from register
   // tiles; those that are only ever the condition of a `where` (masks) come as one bit per element.
   std::string score_loads, score_decls, cond_rows;
-  int n_cond = 0;
+  int n_cond = 0, n_tiles_used = 0;
   {
     ScalarP v1 = rename_scalar(s1.value, ren1);
     // every position an operand is read at, and whether it is a `where` condition there
@@ -599,6 +599,7 @@ bool match_attention(const Program& P, const std::vector<StmtP>& flat, size_t at
                      (eb == 4 ? "__uint_as_float(b200_w[b200_j])" : "(unsigned short)(b200_w[b200_j >> 1] >> (16 * (b200_j & 1)))") +
                      ";\n  }\n";
     }
+    n_tiles_used = n_tiles;
     em.scope_subst[r1.scope_id] = "b200_acc";
     const int reads_before = em.direct_reads;
     Emitter::Res r = em.scalar(Prec::Single, *v1);
@@ -745,6 +746,23 @@ bool match_attention(const Program& P, const std::vector<StmtP>& flat, size_t at
   a.in_prec = Q.prec;
   a.out_bytes = prec_bytes(O.prec);
   a.n_cond = n_cond;
+  a.n_tiles = n_tiles_used;
+  {
+    auto fill = [&](AttnPlan::RowNode& rn, int tn, const Indices& idcs) {
+      std::map<std::string, int64_t> stx;
+      int64_t off = 0;
+      strides_of(P.tn(tn), idcs, stx, off);
+      rn.keep = written.count(tn) > 0;
+      rn.tn = tn;
+      rn.off = off;
+      rn.row = stx[kS];
+      rn.b0 = stx.count(kB0) ? stx[kB0] : 0;
+      rn.b1 = stx.count(kB1) ? stx[kB1] : 0;
+    };
+    fill(a.scores, s1.tn, scores_idcs);
+    fill(a.exps, s3.tn, exp_idcs);
+    fill(a.weights, s5.tn, w_idcs);
+  }
   a.code = fn.str();
   for (int c : chain)
     if (written.count(c)) st.writes.push_back(c);
@@ -767,7 +785,9 @@ std::string attn_translation_unit(const Program&, Stage& st, const std::string& 
   o << kNumericsSource << "\n#define B200_ELEM_BYTES 2\n#define B200_CTA_PAIR 0\n" << kTcSource << "\n";
   o << "#define B200_ATTN_NAME " << kernel_name << "\n#define B200_T " << a.T << "\n#define B200_E " << a.E << "\n#define B200_IDESC1 "
     << idesc1 << "u\n#define B200_IDESC2 " << idesc2 << "u\n#define B200_HALF " << (a.in_prec == Prec::Half ? 1 : 0)
-    << "\n#define B200_OUT_BYTES " << a.out_bytes << "\n#define B200_ATTN_NCOND " << a.n_cond << "\n#define B200_ATTN_PARAMS " << st.epi_params << "\n#define B200_ATTN_ARGS "
+    << "\n#define B200_OUT_BYTES " << a.out_bytes << "\n#define B200_ATTN_NCOND " << a.n_cond << "\n#define B200_ATTN_NTILES " << a.n_tiles
+    << "\n#define B200_KEEP_SCORES " << (a.scores.keep ? 1 : 0) << "\n#define B200_KEEP_EXP " << (a.exps.keep ? 1 : 0)
+    << "\n#define B200_KEEP_W " << (a.weights.keep ? 1 : 0) << "\n#define B200_ATTN_PARAMS " << st.epi_params << "\n#define B200_ATTN_ARGS "
     << st.epi_args << "\n";
   o << kAttnSource << "\n" << a.code << "\n";
   const int64_t ra0 = 128 * a.E * 2 + a.T * a.E * 2, p = 128 * a.T * 2;

@@ -56,6 +56,14 @@ struct AttnPlan {
   Prec in_prec = Prec::Bfloat16;
   int out_bytes = 2;
   int n_cond = 0;          // operands of the score expression handed to the kernel as one bit per element
+  int n_tiles = 0;         // operands of the score expression loaded through the staging tile
+  // the three row nodes (scores, exponentials, weights): written by TMA stores when the routine keeps them
+  struct RowNode {
+    bool keep = false;
+    int tn = -1;
+    int64_t off = 0, row = 0, b0 = 0, b1 = 0;   // element offset and strides of (query position, outer batch, inner batch)
+  };
+  RowNode scores, exps, weights;
   std::string code;
 };
 

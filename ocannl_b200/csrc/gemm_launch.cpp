@@ -20,7 +20,7 @@ struct GemmLaunch {
 
 static void encode_operand(CUtensorMap* map, CUdeviceptr base, Prec prec, bool kmajor, const GemmDim& mn, int64_t mn_stride,
                            const GemmDim& k, int64_t k_stride, const std::vector<GemmDim>& batch,
-                           const std::vector<int64_t>& batch_stride, int tile_mn, int tile_k) {
+                           const std::vector<int64_t>& batch_stride, int tile_mn, int tile_k, int inner_box = 0) {
   const int eb = prec_bytes(prec);
   CUtensorMapDataType dt = prec == Prec::Bfloat16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                            : prec == Prec::Half   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
@@ -28,7 +28,7 @@ static void encode_operand(CUtensorMap* map, CUdeviceptr base, Prec prec, bool k
   const int row_elems = 128 / eb;
   cuuint64_t dims[4];
   cuuint64_t strides[3];
-  cuuint32_t box[4] = {(cuuint32_t)row_elems, 1, 1, 1};
+  cuuint32_t box[4] = {(cuuint32_t)(inner_box > 0 ? inner_box : row_elems), 1, 1, 1};   // inner_box: a box narrower than one 128-byte swizzle row
   cuuint32_t estr[4] = {1, 1, 1, 1};
   if (kmajor) {
     dims[0] = (cuuint64_t)k.extent;
@@ -162,7 +162,7 @@ struct AttnShape {
 };
 
 struct AttnLaunch {
-  CUtensorMap map_q, map_k, map_v;
+  CUtensorMap map_q, map_k, map_v, map_scores, map_exp, map_w;
   AttnShape shape;
   unsigned int grid = 1;
   CUdeviceptr status = 0;
@@ -204,6 +204,20 @@ AttnLaunch* attn_prepare(b200_routine* r, int si) {
     encode_operand(&L->map_q, q, a.in_prec, true, qs, a.q_row, ed, 1, batch, strides(a.q_b0, a.q_b1), 128, (int)a.E);
     encode_operand(&L->map_k, k, a.in_prec, true, ks, a.k_row, ed, 1, batch, strides(a.k_b0, a.k_b1), (int)a.T, (int)a.E);
     encode_operand(&L->map_v, v, a.in_prec, false, ed, 1, td, a.v_row, batch, strides(a.v_b0, a.v_b1), (int)a.E, (int)a.T);
+    // the row nodes the routine keeps, as destinations of TMA stores: [key, query, inner batch, outer batch],
+    // a 32 x 32 box of single-precision values per chunk, a 64 x 128 box of 16-bit weights per block of keys
+    auto rows = [&](CUtensorMap* m, const AttnPlan::RowNode& rn, Prec prec, int box_t, int box_s) {
+      if (!rn.keep) { *m = L->map_q; return; }   // never used by the kernel
+      const CUdeviceptr base = ptr(rn.tn) + (CUdeviceptr)(rn.off * prec_bytes(prec));
+      if (base & 15) throw Error(B200_E_INVALID, "link: internal error: an attention stage was kept for a row node that is not 16-byte aligned");
+      GemmDim keys, qrows;
+      keys.extent = a.T;
+      qrows.extent = a.S;
+      encode_operand(m, base, prec, true, qrows, rn.row, keys, 1, batch, strides(rn.b0, rn.b1), box_s, box_t, box_t);
+    };
+    rows(&L->map_scores, a.scores, Prec::Single, 32, 32);
+    rows(&L->map_exp, a.exps, Prec::Single, 32, 32);
+    rows(&L->map_w, a.weights, a.in_prec, 64, 128);
   } catch (...) {
     delete L;
     throw;
@@ -226,6 +240,9 @@ void attn_enqueue(b200_routine* r, int si) {
   args.push_back(&L->map_q);
   args.push_back(&L->map_k);
   args.push_back(&L->map_v);
+  args.push_back(&L->map_scores);
+  args.push_back(&L->map_exp);
+  args.push_back(&L->map_w);
   args.push_back(&L->shape);
   args.push_back(&L->status);
   std::vector<CUdeviceptr>& vals = r->arg_values[si];

@@ -19,6 +19,8 @@
 //   B200_HALF            1: the weights are IEEE half, 0: bfloat16
 //   B200_OUT_BYTES       element size of the output node (2 or 4)
 //   B200_ATTN_NCOND      operands of the score expression that are only tested against zero (masks)
+//   B200_ATTN_NTILES     operands of the score expression loaded a chunk at a time through the staging tile
+//   B200_KEEP_SCORES / B200_KEEP_EXP / B200_KEEP_W   1: the routine keeps that node (it is written, by TMA stores)
 //   B200_ATTN_PARAMS / B200_ATTN_ARGS    node pointers of the generated code
 // and the generated functions b200_attn_score_chunk, b200_attn_exp_chunk, b200_attn_weight_chunk,
 // b200_attn_out_chunk, b200_attn_row_max, b200_attn_row_sum and b200_attn_rows (see attn_match.cpp).
@@ -42,6 +44,8 @@ struct b200_attn_shape {
 #define B200_RA0 (B200_Q_BYTES + B200_K_BYTES)
 #define B200_RA1 (B200_RA0 > B200_P_BYTES ? B200_RA0 : B200_P_BYTES)
 #define B200_REGION_A (B200_RA1 > 8 * B200_STAGE_WARP_BYTES ? B200_RA1 : 8 * B200_STAGE_WARP_BYTES)
+// staging tiles per warp for the TMA stores of the first two passes (region A is free of operands then)
+#define B200_STAGE_BUFS ((B200_REGION_A >= 16 * B200_STAGE_WARP_BYTES && B200_ATTN_NTILES == 0) ? 2 : 1)
 #define B200_ATTN_TMEM_COLS (B200_T < 64 ? 64 : B200_T)
 #define B200_HALF_COLS (B200_T / 2)
 
@@ -68,6 +72,32 @@ __device__ __forceinline__ void b200_attn_store_chunk(uint4* stage, const unsign
     if (dst) *(uint4*)(dst + 16ull * c) = q;
   }
   __syncwarp();
+}
+
+// A chunk of 32 rows x 32 single-precision columns that the warp holds one row per lane goes to
+// global memory as ONE TMA store: the lanes write their rows into a 4 KB tile in the 128-byte
+// swizzle the tensor map describes, lane 0 issues the copy and moves on; rows beyond the node's
+// extent are clipped by the copy engine.  The tile may be written again once the copy has read it
+// (b200_attn_tile_free).
+__device__ __forceinline__ void b200_tma_store_4d(const b200_tmap* map, unsigned int src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"((unsigned long long)map),
+               "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// waits until at most PENDING of this thread's copy groups still read shared memory
+template <int PENDING>
+__device__ __forceinline__ void b200_tma_store_read_wait() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(PENDING) : "memory");
+}
+__device__ __forceinline__ void b200_attn_tma_store_chunk(unsigned char* tile, const unsigned int* u, const b200_tmap* map, int t0, int s0,
+                                                          int b1, int b0, unsigned int lane) {
+  uint4* st = (uint4*)tile;
+#pragma unroll
+  for (unsigned int g = 0; g < 8u; ++g) st[lane * 8u + (g ^ (lane & 7u))] = make_uint4(u[4 * g], u[4 * g + 1], u[4 * g + 2], u[4 * g + 3]);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncwarp();
+  if (lane == 0) b200_tma_store_4d(map, b200_smem_addr(tile), t0, s0, b1, b0);
 }
 
 // The reverse: loads a chunk of 32 rows x (4 * WORDS) bytes with whole-row-segment accesses and
@@ -148,7 +178,9 @@ __device__ __forceinline__ void b200_attn_out_chunk(const b200_attn_row& row, un
 
 extern "C" __global__ void __launch_bounds__(B200_ATTN_THREADS, 2)
 B200_ATTN_NAME(const __grid_constant__ b200_tmap map_q, const __grid_constant__ b200_tmap map_k,
-               const __grid_constant__ b200_tmap map_v, const b200_attn_shape shape, unsigned int* status B200_ATTN_PARAMS) {
+               const __grid_constant__ b200_tmap map_v, const __grid_constant__ b200_tmap map_scores,
+               const __grid_constant__ b200_tmap map_exp, const __grid_constant__ b200_tmap map_w, const b200_attn_shape shape,
+               unsigned int* status B200_ATTN_PARAMS) {
   extern __shared__ unsigned char b200_dyn_smem[];
   const unsigned int smem_base = (b200_smem_addr(b200_dyn_smem) + 1023u) & ~1023u;
   unsigned char* smem_gen = b200_dyn_smem + (smem_base - b200_smem_addr(b200_dyn_smem));
@@ -169,6 +201,15 @@ B200_ATTN_NAME(const __grid_constant__ b200_tmap map_q, const __grid_constant__ 
 #endif
 
   if (threadIdx.x == 32) {
+#if B200_KEEP_SCORES
+    asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_scores) : "memory");
+#endif
+#if B200_KEEP_EXP
+    asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_exp) : "memory");
+#endif
+#if B200_KEEP_W
+    asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_w) : "memory");
+#endif
     asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_q) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_k) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_v) : "memory");
@@ -225,7 +266,11 @@ B200_ATTN_NAME(const __grid_constant__ b200_tmap map_q, const __grid_constant__ 
   row.s = s0 + quarter * 32u + lane;
   row.ok = row.s < shape.S;
   row.lane = lane;
-  row.stage = (uint4*)(smem_gen + warp * B200_STAGE_WARP_BYTES);
+  // this warp's staging tiles (B200_STAGE_BUFS of 4 KB each, 1024-byte aligned)
+  unsigned char* const my_tiles = smem_gen + warp * (B200_STAGE_BUFS * B200_STAGE_WARP_BYTES);
+  row.stage = (uint4*)my_tiles;
+  unsigned int n_stores = 0;   // chunks this warp has handed to the copy engine
+  (void)n_stores;
   const unsigned int r_in_tile = quarter * 32u + lane;
   const unsigned int col0 = half * B200_HALF_COLS;
   const unsigned int taddr = tmem_base + ((quarter * 32u) << 16);
@@ -262,13 +307,26 @@ B200_ATTN_NAME(const __grid_constant__ b200_tmap map_q, const __grid_constant__ 
     for (unsigned int c = 0; c < B200_HALF_COLS; c += 32u) {
       const unsigned int t0 = col0 + c;
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#if B200_ATTN_NTILES > 0 && B200_KEEP_SCORES
+      // the operand tiles of this chunk pass through the staging tile the previous chunk's store reads
+      if (lane == 0) b200_tma_store_read_wait<0>();
+      __syncwarp();
+#endif
       b200_attn_score_chunk(row, t0, acc, x, cond, c >> 2 B200_ATTN_ARGS);
       if (c + 32u < B200_HALF_COLS) b200_tmem_ld32(taddr + t0 + 32u, acc);
       unsigned int u[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) { mx4[j & 3] = fmaxf(mx4[j & 3], x[j]); u[j] = __float_as_uint(x[j]); }
       b200_tmem_st32(taddr + t0, u);
-      if (__any_sync(0xffffffffu, p_scores != 0ull)) b200_attn_store_chunk<32>(row.stage, u, p_scores ? p_scores + 4ull * t0 : 0ull, lane);
+#if B200_KEEP_SCORES
+      if (n_stores >= B200_STAGE_BUFS) {
+        if (lane == 0) b200_tma_store_read_wait<B200_STAGE_BUFS - 1>();
+        __syncwarp();
+      }
+      b200_attn_tma_store_chunk(my_tiles + (n_stores % B200_STAGE_BUFS) * B200_STAGE_WARP_BYTES, u, &map_scores, (int)t0,
+                                (int)(s0 + quarter * 32u), (int)b1, (int)b0, lane);
+      ++n_stores;
+#endif
     }
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     red[half * 128u + r_in_tile] = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
@@ -297,11 +355,22 @@ B200_ATTN_NAME(const __grid_constant__ b200_tmap map_q, const __grid_constant__ 
 #pragma unroll
       for (int j = 0; j < 32; ++j) { sum4[j & 3] += x[j]; u[j] = __float_as_uint(x[j]); }
       b200_tmem_st32(taddr + t0, u);
-      if (__any_sync(0xffffffffu, p_exp != 0ull)) b200_attn_store_chunk<32>(row.stage, u, p_exp ? p_exp + 4ull * t0 : 0ull, lane);
+#if B200_KEEP_EXP
+      if (n_stores >= B200_STAGE_BUFS) {
+        if (lane == 0) b200_tma_store_read_wait<B200_STAGE_BUFS - 1>();
+        __syncwarp();
+      }
+      b200_attn_tma_store_chunk(my_tiles + (n_stores % B200_STAGE_BUFS) * B200_STAGE_WARP_BYTES, u, &map_exp, (int)t0,
+                                (int)(s0 + quarter * 32u), (int)b1, (int)b0, lane);
+      ++n_stores;
+#endif
     }
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     red[half * 128u + r_in_tile] = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
   }
+#if B200_KEEP_SCORES || B200_KEEP_EXP
+  if (lane == 0) b200_tma_store_read_wait<0>();   // the copy engine has read every staging tile: region A may change hands
+#endif
   B200_ATR(4);   // pass 2 done
   __syncthreads();   // also: every warp is done with its staging tile, region A may take the weights
   if (live) {
@@ -349,23 +418,15 @@ B200_ATTN_NAME(const __grid_constant__ b200_tmap map_q, const __grid_constant__ 
       b200_umma_commit(bar_o);
     }
     B200_ATR(6);   // second MMA issued
+#if B200_KEEP_W
+    // the weights go to global memory straight from the operand tile, one TMA store per block of
+    // 64 keys, while the tensor cores read the same tile
+#pragma unroll
+    for (unsigned int kb = 0; kb < B200_T / 64; ++kb) b200_tma_store_4d(&map_w, p_at + kb * (128u * 128u), (int)(kb * 64u), (int)s0, (int)b1, (int)b0);
+    b200_tma_store_read_wait<0>();
+#endif
   }
   __syncwarp();
-  if (live && __any_sync(0xffffffffu, p_w != 0ull)) {
-    // the weights go to global memory straight from the operand tile while the tensor cores read
-    // it: a warp writes one row (2 * T bytes) per step, each 16-byte piece from its swizzled place;
-    // the two warps of a lane quarter take 16 rows each
-    constexpr unsigned int PIECES = B200_T / 8;          // 16-byte pieces per row
-    for (unsigned int i = 0; i < 16u; ++i) {
-      const unsigned int r = half * 16u + i;
-      const unsigned long long dst = __shfl_sync(0xffffffffu, p_w, r);
-      const unsigned int rt = quarter * 32u + r;
-      for (unsigned int pc = lane; pc < PIECES; pc += 32u) {
-        const uint4 q = *(const uint4*)(smem_gen + (pc >> 3) * (128u * 128u) + rt * 128u + (((pc & 7u) ^ (rt & 7u)) << 4));
-        if (dst) *(uint4*)(dst + 16ull * pc) = q;
-      }
-    }
-  }
   B200_ATR(7);   // weights copied out
   live = live && b200_wait(bar_o, 0u, abort_flag, status, 14u);
   B200_ATR(8);   // output accumulators ready
