@@ -547,6 +547,7 @@ bool match_attention(const Program& P, const std::vector<StmtP>& flat, size_t at
   // tiles; those that are only ever the condition of a `where` (masks) come as one bit per element.
   std::string score_loads, score_decls, cond_rows;
   int n_cond = 0, n_tiles_used = 0;
+  std::vector<int> cond_tns;
   {
     ScalarP v1 = rename_scalar(s1.value, ren1);
     // every position an operand is read at, and whether it is a `where` condition there
@@ -578,14 +579,22 @@ bool match_attention(const Program& P, const std::vector<StmtP>& flat, size_t at
       bool have = false;
       for (auto& lt : em.load_tiles) have = have || (lt.tn == e.tn && same_idcs(lt.idcs, e.idcs));
       if (have) continue;
-      bool cond_only = t.prec == Prec::Single && n_cond < 2;
+      // a mask: only ever a `where` condition.  It reaches the kernel packed to one bit per element (a
+      // stage of its own makes the bits); a row's bits must start on a word boundary
+      bool cond_only = n_cond < 2 && st[kT] == 1 && off % 32 == 0;
+      for (auto& kv : st)
+        if (kv.first != kT && kv.second % 32 != 0) cond_only = false;
       for (auto& o : reads)
         if (o.get->tn == e.tn && same_idcs(o.get->idcs, e.idcs) && !o.cond) cond_only = false;
       if (cond_only) {
-        // bit (4 * l + k) of the thread's half row sits in word k, bit l; chunk c covers l = c / 4 .. c / 4 + 7
-        const std::string w = "cond[" + std::to_string(4 * n_cond) + " + (b200_j & 3)]";
-        em.load_tiles.push_back({e.tn, e.idcs, "(((" + w + " >> (sh + (unsigned int)(b200_j >> 2))) & 1u) ? 1.0f : 0.0f)"});
-        cond_rows += "  p[" + std::to_string(n_cond) + "] = row.ok ? " + row_ptr(e.tn, e.idcs, kT) + " : 0ull;\n";
+        // (the tile expression stands for the node's storage bits: one and zero in its format)
+        const std::string one = t.prec == Prec::Single ? "1.0f : 0.0f" : t.prec == Prec::Bfloat16 ? "(unsigned short)0x3F80 : (unsigned short)0"
+                                                                                                   : "(unsigned short)0x3C00 : (unsigned short)0";
+        em.load_tiles.push_back({e.tn, e.idcs, "(((cw[" + std::to_string(n_cond) + "] >> b200_j) & 1u) ? " + one + ")"});
+        // the row's first bit, as a byte address
+        cond_rows += "  p[" + std::to_string(n_cond) + "] = row.ok ? (unsigned long long)b200_bits" + std::to_string(n_cond) + " + ((unsigned long long)(" +
+                     em.offset(zero_t(e.idcs, kT), t.dims) + ") >> 3) : 0ull;\n";
+        cond_tns.push_back(e.tn);
         ++n_cond;
         continue;
       }
@@ -608,7 +617,7 @@ bool match_attention(const Program& P, const std::vector<StmtP>& flat, size_t at
     // unless the expression reads memory itself: no branch per element
     const std::string guard1 = em.direct_reads > reads_before ? "row.ok ? (float)(" + r.expr + ") : 0.f" : "(float)(" + r.expr + ")";
     fn << "__device__ __forceinline__ void b200_attn_score_chunk(const b200_attn_row& row, unsigned int t0, const unsigned int* acc, float* x, "
-          "const unsigned int* cond, unsigned int sh B200_ATTN_PARAMS) {\n"
+          "const unsigned int* cw B200_ATTN_PARAMS) {\n"
        << syms << score_decls << score_loads
        << "#pragma unroll\n  for (int b200_j = 0; b200_j < 32; ++b200_j) {\n    const unsigned int b200_t = t0 + (unsigned int)b200_j; (void)b200_t;\n"
        << "    const float b200_acc = __uint_as_float(acc[b200_j]);\n"
@@ -727,6 +736,11 @@ bool match_attention(const Program& P, const std::vector<StmtP>& flat, size_t at
     args += ", " + t.ident;
     kargs.push_back({KArg::Node, t.id});
   }
+  for (int c = 0; c < n_cond; ++c) {
+    params += ", const unsigned char* __restrict__ b200_bits" + std::to_string(c);
+    args += ", b200_bits" + std::to_string(c);
+    kargs.push_back({KArg::Scratch, 0});   // the planner assigns the offset of the packed bits
+  }
 
   Stage st;
   st.kind = Stage::Attn;
@@ -746,6 +760,7 @@ bool match_attention(const Program& P, const std::vector<StmtP>& flat, size_t at
   a.in_prec = Q.prec;
   a.out_bytes = prec_bytes(O.prec);
   a.n_cond = n_cond;
+  a.cond_tns = cond_tns;
   a.n_tiles = n_tiles_used;
   {
     auto fill = [&](AttnPlan::RowNode& rn, int tn, const Indices& idcs) {

@@ -1851,6 +1851,40 @@ struct Builder {
     return out;
   }
 
+  // A node that a later stage only tests against zero (the mask of an attention stage), packed to
+  // one bit per element in element order: bit (i % 32) of word (i / 32) = (node[i] != 0).  The bits
+  // live in the routine's scratch; for a read-only node they are made once per run and shared by
+  // every stage that asks for them.  Returns the byte offset in the reduction scratch.
+  std::map<int, size_t> packed_bits;
+  size_t pack_bits_stage(int tn) {
+    const Tnode& t = code.prog.tn(tn);
+    if (t.read_only) {
+      auto it = packed_bits.find(tn);
+      if (it != packed_bits.end()) return it->second;
+    }
+    const long long words = (t.num_elems() + 31) / 32;
+    const size_t off = code.reduce_scratch_bytes;
+    code.reduce_scratch_bytes = (code.reduce_scratch_bytes + (size_t)words * 4 + 255) & ~(size_t)255;
+    Stage st;
+    st.kind = Stage::Generic;
+    st.kernel = kernel_name();
+    st.args = {{KArg::Node, tn}, {KArg::Scratch, (int)off}};
+    st.total = words * 32;
+    st.block = 256;
+    st.note = "one bit per element: (value != 0), for the stages that only test this node";
+    src << "extern \"C\" __global__ void __launch_bounds__(256) " << st.kernel << "(const " << Emitter::ctype(t.prec) << "* __restrict__ "
+        << t.ident << ", unsigned char* b200_bits) {\n" << kGridEntry
+        << "  unsigned int* b200_words = (unsigned int*)b200_bits;\n"
+        << "  for (unsigned long long b200_i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; b200_i < " << words * 32
+        << "ull; b200_i += (unsigned long long)gridDim.x * blockDim.x) {\n"
+        << "    const bool b200_nz = b200_i < " << t.num_elems() << "ull && " << Emitter::load_wrap(t.prec, t.ident + "[b200_i]") << " != 0;\n"
+        << "    const unsigned int b200_w = __ballot_sync(0xffffffffu, b200_nz);\n"
+        << "    if ((threadIdx.x & 31u) == 0u) b200_words[b200_i >> 5] = b200_w;\n  }\n}\n\n";
+    code.stages.push_back(st);
+    if (t.read_only) packed_bits[tn] = off;
+    return off;
+  }
+
   // an epilogue that ends in a grid-wide sum keeps its per-warp partials and its ticket in the
   // routine's reduction scratch (zeroed at link; the kernel resets its ticket itself)
   void assign_epilogue_scratch(Stage& g) {
@@ -2065,6 +2099,12 @@ struct Builder {
         int n_abs = 0;
         if (allowed && match_attention(code.prog, flat, i, opt, &n_abs, &a)) {
           for (int w : a.writes) zeroed.erase(w);
+          // masks as bits: one packing stage per mask node (shared when the node is read-only)
+          {
+            size_t k = 0;
+            for (auto& arg : a.args)
+              if (arg.kind == KArg::Scratch) arg.tn = (int)pack_bits_stage(a.attn.cond_tns.at(k++));
+          }
           a.kernel = kernel_name();
           a.gemm_source = attn_translation_unit(code.prog, a, a.kernel);
           code.stages.push_back(a);

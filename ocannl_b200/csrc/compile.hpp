@@ -56,6 +56,7 @@ struct AttnPlan {
   Prec in_prec = Prec::Bfloat16;
   int out_bytes = 2;
   int n_cond = 0;          // operands of the score expression handed to the kernel as one bit per element
+  std::vector<int> cond_tns;   // their nodes, in the order of the stage's scratch arguments (the packed bits)
   int n_tiles = 0;         // operands of the score expression loaded through the staging tile
   // the three row nodes (scores, exponentials, weights): written by TMA stores when the routine keeps them
   struct RowNode {

@@ -125,24 +125,6 @@ __device__ __forceinline__ void b200_attn_load_chunk(uint4* stage, unsigned int*
   __syncwarp();
 }
 
-// An operand of the score expression that is only tested against zero (the mask of `where`) is
-// reduced to one bit per element before the scores exist: for each of the warp's 32 rows the lanes
-// read the row's B200_HALF_COLS columns of this warp's half with one 16-byte access each and four
-// ballots hand the row's bits to the lane that owns the row.  bits[k] bit l = column 4 * l + k.
-__device__ __forceinline__ void b200_attn_cond_bits(unsigned long long row_ptr, unsigned int lane, unsigned int* bits) {
-  constexpr unsigned int LANES = B200_HALF_COLS / 4;
-  bits[0] = bits[1] = bits[2] = bits[3] = 0u;
-#pragma unroll 16
-  for (unsigned int r = 0; r < 32u; ++r) {
-    const unsigned long long src = __shfl_sync(0xffffffffu, row_ptr, r);
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (src && lane < LANES) v = *(const float4*)(src + 16ull * lane);
-    const unsigned int b0 = __ballot_sync(0xffffffffu, v.x != 0.f), b1 = __ballot_sync(0xffffffffu, v.y != 0.f),
-                       b2 = __ballot_sync(0xffffffffu, v.z != 0.f), b3 = __ballot_sync(0xffffffffu, v.w != 0.f);
-    if (lane == r) { bits[0] = b0; bits[1] = b1; bits[2] = b2; bits[3] = b3; }
-  }
-}
-
 // Developer aid: with -DB200_TRACE, thread 0 of one CTA (B200_TRACE_CTA, default 0) records nanoseconds
 // since its start at a few points into words 40.. of the device status buffer.
 #ifdef B200_TRACE
@@ -169,7 +151,7 @@ __device__ __forceinline__ void b200_attn_rows(const b200_attn_row& row, unsigne
                                                unsigned long long& p_out B200_ATTN_PARAMS);
 __device__ __forceinline__ void b200_attn_cond_rows(const b200_attn_row& row, unsigned long long* p B200_ATTN_PARAMS);
 __device__ __forceinline__ void b200_attn_score_chunk(const b200_attn_row& row, unsigned int t0, const unsigned int* acc, float* x,
-                                                      const unsigned int* cond, unsigned int sh B200_ATTN_PARAMS);
+                                                      const unsigned int* cw B200_ATTN_PARAMS);
 __device__ __forceinline__ float b200_attn_row_max(const b200_attn_row& row, float reduced B200_ATTN_PARAMS);
 __device__ __forceinline__ void b200_attn_exp_chunk(const b200_attn_row& row, unsigned int t0, float* x, float mx B200_ATTN_PARAMS);
 __device__ __forceinline__ float b200_attn_row_sum(const b200_attn_row& row, float reduced B200_ATTN_PARAMS);
@@ -278,17 +260,21 @@ B200_ATTN_NAME(const __grid_constant__ b200_tmap map_q, const __grid_constant__ 
   unsigned long long p_scores, p_exp, p_w, p_max, p_sum, p_out;
   b200_attn_rows(row, p_scores, p_exp, p_w, p_max, p_sum, p_out B200_ATTN_ARGS);
 
-  // condition operands (masks) as bits, fetched while the queries and keys are still on their way
+  // Operands of the score expression that are only tested against zero (masks) arrive packed to one
+  // bit per element: this thread's half row is B200_HALF_COLS / 32 words, fetched while the queries
+  // and keys are still on their way.  cond[4 * i + k] bit j = column 32 * k + j of the half.
 #if B200_ATTN_NCOND > 0
   unsigned int cond[4 * B200_ATTN_NCOND];
   {
     unsigned long long cp[B200_ATTN_NCOND];
     b200_attn_cond_rows(row, cp B200_ATTN_ARGS);
 #pragma unroll
-    for (int i = 0; i < B200_ATTN_NCOND; ++i) b200_attn_cond_bits(cp[i] ? cp[i] + 4ull * col0 : 0ull, lane, cond + 4 * i);
+    for (int i = 0; i < B200_ATTN_NCOND; ++i) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        cond[4 * i + k] = (cp[i] && k < (int)(B200_HALF_COLS / 32)) ? ((const unsigned int*)(cp[i] + col0 / 8u))[k] : 0u;
+    }
   }
-#else
-  unsigned int cond[1] = {0u};
 #endif
 
   bool live = b200_wait(bar_s, 0u, abort_flag, status, 12u);
@@ -312,7 +298,15 @@ B200_ATTN_NAME(const __grid_constant__ b200_tmap map_q, const __grid_constant__ 
       if (lane == 0) b200_tma_store_read_wait<0>();
       __syncwarp();
 #endif
-      b200_attn_score_chunk(row, t0, acc, x, cond, c >> 2 B200_ATTN_ARGS);
+      unsigned int cw[B200_ATTN_NCOND > 0 ? B200_ATTN_NCOND : 1];
+#if B200_ATTN_NCOND > 0
+#pragma unroll
+      for (int i = 0; i < B200_ATTN_NCOND; ++i)   // this chunk's word (selects: the word index is not a compile-time constant)
+        cw[i] = c == 0u ? cond[4 * i] : c == 32u ? cond[4 * i + 1] : c == 64u ? cond[4 * i + 2] : cond[4 * i + 3];
+#else
+      cw[0] = 0u;
+#endif
+      b200_attn_score_chunk(row, t0, acc, x, cw B200_ATTN_ARGS);
       if (c + 32u < B200_HALF_COLS) b200_tmem_ld32(taddr + t0 + 32u, acc);
       unsigned int u[32];
 #pragma unroll
