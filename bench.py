@@ -473,6 +473,53 @@ def probe_attention(dev, batch=64, heads=8, seq=256):
     return out
 
 
+def probe_ffn(dev, batch=64, seq=256, d_model=512, d_ff=2048):
+    """The first feed-forward contraction of a decoder layer as a routine of its own: 16384 rows,
+    K = 512, N = 2048, bias, the pre-activation kept in single precision and the composed GELU
+    written as bfloat16 -- a contraction whose epilogue outweighs its main loop.  A small case for
+    profilers."""
+    from ocannl_b200 import backend as bk
+    from ocannl_b200 import workloads as W
+    from ocannl_b200.low_level import Routine, Seq, Set, loops
+    r = Routine("ffn_in_b%d_s%d" % (batch, seq))
+    x = r.tn("x", "bfloat16", [batch, seq, d_model], read_only=True)
+    w = r.tn("w", "bfloat16", [d_ff, d_model], read_only=True)
+    bias = r.tn("b", "bfloat16", [d_ff], read_only=True)
+    z = r.tn("z", "single", [batch, seq, d_ff])
+    h = r.tn("h", "bfloat16", [batch, seq, d_ff])
+    b, s_, j, i = r.syms(4)
+    pre = W.reduce_scope(r, "n_ffn", "single", [(i, d_model)], lambda: (w[j, i], x[b, s_, i]), orig=(b, s_, j)) + bias[j]
+    b2, s2, j2 = r.syms(3)
+    r.body = Seq([loops([(b, batch), (s_, seq), (j, d_ff)], Set(z, (b, s_, j), pre)),
+                  loops([(b2, batch), (s2, seq), (j2, d_ff)], Set(h, (b2, s2, j2), W.gelu_tanh(z[b2, s2, j2])))])
+    code = bk.Code(r)
+    rt = bk.Context(dev).link(code)
+    g = np.random.default_rng(0)
+    rt.context.from_host("x", W.store("bfloat16", g.standard_normal((batch, seq, d_model), np.float32)))
+    rt.context.from_host("w", W.store("bfloat16", (g.standard_normal((d_ff, d_model), np.float32) / np.sqrt(d_model)).astype(np.float32)))
+    rt.context.from_host("b", W.store("bfloat16", g.standard_normal((d_ff,), np.float32)))
+    for _ in range(3):
+        rt.run()
+    dev.await_()
+    e0 = dev.all_work()
+    for _ in range(10):
+        rt.run()
+    e1 = dev.all_work()
+    e1.sync()
+    ms = e0.elapsed_ms(e1) / 10
+    st = rt.info()["stages"]
+    flops = 2.0 * batch * seq * d_model * d_ff
+    out = {"us": round(1e3 * ms, 2), "kernels": rt.kernels_per_run(), "tflops": round(flops / ms / 1e9, 1),
+           "bytes": sum(s_["bytes"] for s_ in st), "gbs": round(sum(s_["bytes"] for s_ in st) / ms / 1e6, 1),
+           "notes": [s_["note"] for s_ in st]}
+    pools = {p for p, _, _ in rt.context.arrays.values()}
+    rt.free()
+    code.free()
+    for p in pools:
+        dev.free_pool(p)
+    return out
+
+
 def oracle_rate(ir, inputs, units, statics=None, what=""):
     """Seconds of one oracle run of `ir` (one host thread) -> units per second, with the sample stated."""
     from oracle.run_c import OracleRoutine
@@ -659,7 +706,8 @@ def main():
     ap.add_argument("--sweep-size", type=int, default=0,
                     help="run only the batch-8 contraction of this M=N=K (a small case for profilers) and exit")
     ap.add_argument("--probe", default="", help="'attention_scores': time the decoder's score contraction alone and exit; "
-                    "'attention' / 'attention_small': one attention layer alone (64 x 8 or 8 x 8 (batch, head) pairs)")
+                    "'attention' / 'attention_small': one attention layer alone (64 x 8 or 8 x 8 (batch, head) pairs); "
+                    "'ffn': a decoder layer's first feed-forward contraction alone")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -687,6 +735,9 @@ def main():
         return
     if args.probe in ("attention", "attention_small"):
         print(json.dumps({args.probe: probe_attention(dev, batch=64 if args.probe == "attention" else 8)}))
+        return
+    if args.probe == "ffn":
+        print(json.dumps({"ffn": probe_ffn(dev)}))
         return
     if args.probe == "attention_scores":
         print(json.dumps({"attention_scores": probe_attention_scores(dev)}))

@@ -90,8 +90,9 @@ int b200_set_async_uploads(b200_dev* dev, int on);
 /* ---- routines: Lowered_backend.{compile, link} (arrayjit/lib/backend_impl.ml:334-367;
  *      cuda: arrayjit/lib/cuda_backend.ml:898-928 compile, :983-1066 link and launch).
  *      b200_compile is device independent.  `options` is a space-separated list of
- *      key=value pairs (gemm, coop, fuse, pairs, splitk, tf32, large_models; each 0|1); NULL for defaults.
- *      gemm: tensor-core contractions; coop: cooperative reductions; fuse: several stages per
+ *      key=value pairs (gemm, attn, coop, fuse, pairs, splitk, tf32, large_models; each 0|1); NULL for defaults.
+ *      gemm: tensor-core contractions; attn: the attention chain (scores, softmax, weights . values,
+ *      lib/nn_blocks.ml:222-236) as one kernel; coop: cooperative reductions; fuse: several stages per
  *      launch; pairs: two neighbouring elements per thread with packed 16-bit arithmetic; splitk:
  *      few-tile fp32 accumulations split over K (atomic adds, order not fixed); tf32: contractions of
  *      single-precision operands on the tensor cores as tf32 (10-bit mantissas, fp32 sums; with
