@@ -66,8 +66,10 @@ def test_decoder_plan_takes_the_attention_chain_as_one_stage():
     st = _plan(W.transformer_forward(**small))
     attn = [s for s in st if s["kind"] == "attention"]
     assert len(attn) == 2, [s["kind"] for s in st]
-    # scores contraction + softmax kernel + weights . values contraction become one launch per layer
-    assert len(st) == len(apart) - 2 * 2
+    # scores contraction + softmax kernel + weights . values contraction become one launch per layer;
+    # one more stage packs the (read-only) mask to bits, once for both layers
+    assert len(st) == len(apart) - 2 * 2 + 1
+    assert sum("one bit per element" in s["note"] for s in st) == 1
     assert all("3 of the 3 row nodes written" in s["note"] for s in attn)     # the context holds every node
     # routine-local intermediates that nobody reads are not written, and get no scratch
     local = _plan(W.transformer_forward(attn_nodes="local", **small))
