@@ -90,13 +90,15 @@ int b200_set_async_uploads(b200_dev* dev, int on);
 /* ---- routines: Lowered_backend.{compile, link} (arrayjit/lib/backend_impl.ml:334-367;
  *      cuda: arrayjit/lib/cuda_backend.ml:898-928 compile, :983-1066 link and launch).
  *      b200_compile is device independent.  `options` is a space-separated list of
- *      key=value pairs (gemm, attn, coop, fuse, pairs, splitk, tf32, large_models; each 0|1); NULL for defaults.
+ *      key=value pairs (gemm, attn, coop, fuse, pairs, splitk, tf32, large_models, bounds; each 0|1); NULL for defaults.
  *      gemm: tensor-core contractions; attn: the attention chain (scores, softmax, weights . values,
  *      lib/nn_blocks.ml:222-236) as one kernel; coop: cooperative reductions; fuse: several stages per
  *      launch; pairs: two neighbouring elements per thread with packed 16-bit arithmetic; splitk:
  *      few-tile fp32 accumulations split over K (atomic adds, order not fixed); tf32: contractions of
  *      single-precision operands on the tensor cores as tf32 (10-bit mantissas, fp32 sums; with
- *      tf32=0 they stay on the exact generic kernels). */
+ *      tf32=0 they stay on the exact generic kernels); bounds: a range-checked build of the generated
+ *      kernels (generic kernels only): an access outside a node is skipped and the next wait returns
+ *      B200_E_DEVICE naming the node id and the element. */
 int b200_compile(const char* name, const char* b200ir, size_t len, const char* options, b200_code** out);
 int b200_code_info(b200_code* code, char* json, size_t cap);
 int b200_code_source(b200_code* code, int stage, char* buf, size_t cap, size_t* needed);

@@ -454,9 +454,11 @@ int b200_compile(const char* name, const char* ir, size_t len, const char* optio
         else if (k == "splitk") opt.enable_splitk = on;
         else if (k == "tf32") opt.enable_tf32 = on;
         else if (k == "large_models") opt.large_models = on;
+        else if (k == "bounds") opt.bounds = on;
         else throw Error(B200_E_INVALID, "unknown compile option '" + k + "'");
       }
     }
+    if (opt.bounds) opt.enable_gemm = opt.enable_attn = opt.enable_pairs = false;   // the checked accesses are the generic kernels'
     *out = build_code(name ? name : "", std::string(ir, len), opt).release();
   });
 }

@@ -1895,6 +1895,50 @@ struct Builder {
     code.reduce_scratch_bytes = (code.reduce_scratch_bytes + 255) & ~(size_t)255;
   }
 
+  // Range-checked build.  Every generic kernel's node pointers are renamed and shadowed by a
+  // b200_checked proxy of the node's size (kernels/numerics.cuh), so that each `node[offset]` the
+  // emitters wrote is compared with the number of elements the node has; the kernels get the device
+  // status word as a last parameter.
+  void apply_bounds() {
+    std::string text = code.source;
+    for (auto& st : code.stages) {
+      if (st.kind != Stage::Generic || st.kernel.empty()) continue;
+      const std::string head = " " + st.kernel + "(";
+      size_t h = text.find(head);
+      if (h == std::string::npos) continue;
+      const size_t p0 = h + head.size();
+      const size_t p1 = text.find(") {\n", p0);
+      if (p1 == std::string::npos) continue;
+      std::string params = text.substr(p0, p1 - p0), proxies;
+      for (auto& t : code.prog.tnodes) {
+        if (t.mode == Mode::Virtual) continue;
+        // "<type>* [__restrict__ ]ident" followed by ',' or the end
+        for (const std::string sep : {std::string("* __restrict__ "), std::string("* ")}) {
+          const std::string needle = sep + t.ident;
+          size_t q = 0;
+          while ((q = params.find(needle, q)) != std::string::npos) {
+            const size_t end = q + needle.size();
+            if (end != params.size() && params[end] != ',') { q = end; continue; }
+            size_t b = params.rfind(',', q);
+            b = b == std::string::npos ? 0 : b + 1;
+            while (b < q && params[b] == ' ') ++b;
+            const std::string type = params.substr(b, q - b);
+            params.insert(end, "__p");
+            proxies += "  const b200_checked<" + type + "> " + t.ident + " = {" + t.ident + "__p, " + std::to_string(t.num_elems()) +
+                       "ull, b200_status, " + std::to_string(t.id) + "u};\n";
+            q = end + 3;
+          }
+        }
+      }
+      params += (params.empty() ? "" : ", ") + std::string("unsigned int* b200_status");
+      text.replace(p0, p1 - p0, params);
+      const size_t body = text.find(") {\n", p0) + 4;
+      text.insert(body, proxies);
+      st.args.push_back({KArg::Status, -1});
+    }
+    code.source = text;
+  }
+
   void memset_stage(int tn) {
     Stage st;
     st.kind = Stage::Memset;
@@ -2139,6 +2183,7 @@ struct Builder {
     }
     emit_kernels();
     code.source = src.str();
+    if (opt.bounds) apply_bounds();
     // routine-local nodes that some stage touches get scratch (a node whose every use was fused
     // away, such as the score matrix of a fused attention stage, needs none)
     std::set<int> touched;

@@ -20,7 +20,7 @@ struct LoopDim {
 // One kernel argument: a tensor node pointer (in-context node, or a routine-local node that
 // lives in the routine's scratch slab), the static-index table, or the merge buffer.
 struct KArg {
-  enum Kind { Node, Statics, Merge, Scratch } kind;
+  enum Kind { Node, Statics, Merge, Scratch, Status } kind;   // Status: the device status word (range-checked builds)
   int tn = -1;  // node id; for Scratch: byte offset into the routine's reduction scratch
 };
 
@@ -122,6 +122,10 @@ struct CompileOptions {
   bool enable_attn = true;   // the attention chain as one fused kernel
   bool enable_tf32 = true;   // single-precision operands of a contraction go through the tensor cores as tf32
   bool large_models = false;
+  // Range-checked build: every access a generated kernel makes to a node is checked against the node's
+  // size; an access outside it is skipped and reported through the device status word.  Implies the
+  // generic kernels (no tensor-core stages, no pair or register-row forms).
+  bool bounds = false;
   // Top-level statements (by index) that must not use the forms with alignment demands: the pair
   // form of generic stages (8-byte accesses) / the TMA-fed contraction kernel (16-byte operand
   // bases).  Filled when a routine is linked to buffers at element-size-aligned offsets, as

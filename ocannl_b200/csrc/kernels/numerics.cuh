@@ -346,6 +346,29 @@ __device__ __forceinline__ float b200_div_by(float a, const b200_divisor& d) {
   return fabsf(q0) == B200_INF ? q0 : q;   // an infinite numerator (or an overflow) stays infinite
 }
 
+// ---- range-checked node accesses (routines compiled with bounds=1).  The proxy stands where the
+//      node's pointer stood: node[i] with i outside the node records (code 2, node id, index) in the
+//      device status word and lands on a sink instead of memory the node does not own.
+__device__ unsigned long long b200_sink_words[4];
+template <typename T>
+struct b200_checked {
+  T* p;
+  unsigned long long n;
+  unsigned int* status;
+  unsigned int node;
+  __device__ __forceinline__ T& operator[](unsigned long long i) const {
+    if (i < n) return p[i];
+    if (atomicCAS(status, 0u, 2u) == 0u) {
+      status[1] = node;
+      status[2] = (unsigned int)i;
+      status[3] = (unsigned int)(i >> 32);
+      __threadfence_system();
+    }
+    return *(T*)b200_sink_words;
+  }
+  __device__ __forceinline__ T* operator+(unsigned long long i) const { return &(*this)[i]; }
+};
+
 // ---- warp-level combine used by cooperative (one warp per output element) reductions
 __device__ __forceinline__ float b200_warp_sum(float v) {
 #pragma unroll

@@ -43,8 +43,12 @@ void b200_dev::check_status() {
   }
   if (status_host && status_host[0] != 0) {
     unsigned int code = status_host[0], where = status_host[1];
+    const unsigned long long index = (unsigned long long)status_host[2] | ((unsigned long long)status_host[3] << 32);
     status_host[0] = 0;
     status_host[1] = 0;
+    if (code == 2u)
+      throw Error(B200_E_DEVICE, "range-checked build: an access to node id " + std::to_string(where) + " at element " +
+                                     std::to_string(index) + " lies outside the node (skipped)");
     throw Error(B200_E_DEVICE, "a kernel gave up a bounded wait (code " + std::to_string(code) + ", site " +
                                    std::to_string(where) + ")");
   }
@@ -180,6 +184,8 @@ void b200_routine::link(b200_dev* d, b200_code* c, const b200_binding* b, int n)
           throw Error(B200_E_INVALID, "link: internal error: stage '" + st.kernel + "' kept a form that needs " +
                                           std::to_string(st.min_align) + "-byte alignment for node '" + P.tn(a.tn).ident + "'");
         arg_values[i].push_back(it->second);
+      } else if (a.kind == KArg::Status) {
+        arg_values[i].push_back(dev->status_dev);
       } else if (a.kind == KArg::Statics) {
         arg_values[i].push_back(statics_dev);
       } else if (a.kind == KArg::Scratch) {

@@ -123,3 +123,19 @@ def test_plan_pool_segments_layout():
     with pytest.raises(bk.UserError, match="per-pool cap"):
         bk.plan_pool_segments([(200, 4)], cap=100)
     assert bk.plan_pool_segments([]) == ([], [])
+
+
+def test_range_checked_build_wraps_every_node_pointer():
+    """`bounds=1`: generic kernels only, each node pointer shadowed by a checked proxy of the node's
+    size, the device status word as a last parameter."""
+    ir = W.mlp_train_update(rows=64, dims=(32, 64, 64, 10))
+    code = bk.Code(ir, "bounds=1")
+    try:
+        st = code.info()["stages"]
+        assert all(s["kind"] in ("generic", "memset") for s in st), st
+        src = code.source(-1)
+        kernels = src.count('extern "C" __global__')
+        assert kernels >= 1 and src.count("unsigned int* b200_status)") == kernels
+        assert "const b200_checked<const unsigned short> x = {x__p, 2048ull, b200_status" in src
+    finally:
+        code.free()
