@@ -68,6 +68,14 @@ struct AttnPlan {
   std::string code;
 };
 
+// An output of a contraction epilogue described to the TMA unit: [n, m, inner batch, outer batch].
+// Offsets and strides in elements.
+struct OutMap {
+  int tn = -1;
+  int64_t off = 0, m_stride = 0, b0_stride = 0, b1_stride = 0;
+  int elem_bytes = 4;
+};
+
 struct Stage {
   enum Kind { Memset, Generic, Gemm, Attn } kind = Generic;
   bool own_module() const { return kind == Gemm || kind == Attn; }   // compiled as a translation unit of its own
@@ -84,6 +92,9 @@ struct Stage {
   AttnPlan attn;
   std::string gemm_source;       // full translation unit of this stage's contraction kernel
   std::string epi_params, epi_args;  // epilogue plumbing: extra kernel parameters / call arguments
+  std::string epi_prologue;          // declarations at the top of the kernel's epilogue role (pointers to the output maps)
+  std::vector<OutMap> out_maps;      // outputs that leave as TMA stores, in the order of the kernel's map parameters
+  int epi_chunk = 32;                // columns per epilogue step (the inner box of the output maps)
   int tile_m = 0, tile_n = 0, tile_k = 0;
   int min_align = 0;             // >0: every node the stage touches must be bound at a multiple of this many bytes
   int cta_pair = 0;              // 1: two CTAs of a cluster share one tile_m x tile_n tile (cta_group::2)

@@ -8,11 +8,12 @@ using namespace b200;
 
 // must match b200_gemm_shape in kernels/gemm_sm100.cuh
 struct GemmShape {
-  unsigned int M, N, K, B0, B1, a_b0, a_b1, b_b0, b_b1, tiles_m, tiles_n;
+  unsigned int M, N, K, B0, B1, a_b0, a_b1, b_b0, b_b1, tiles_m, tiles_n, tma_out;
 };
 
 struct GemmLaunch {
   CUtensorMap map_a, map_b;
+  std::vector<CUtensorMap> out_maps;   // the epilogue's outputs as TMA store destinations
   GemmShape shape;
   unsigned int grid = 1;
   CUdeviceptr status = 0;
@@ -108,6 +109,37 @@ GemmLaunch* gemm_prepare(b200_routine* r, int si) {
     s.B1 = (unsigned)g.batch[0].extent;
     s.a_b1 = g.batch[0].sa != 0; s.b_b1 = g.batch[0].sb != 0;
   }
+  // The outputs as TMA store destinations: [n, m, inner batch, outer batch], a box of 32 rows x one
+  // epilogue chunk, swizzled like the staging tile (128 / 64 / 32 bytes per row).  If any of them
+  // cannot be described (an address that is not 16-byte aligned), the kernel keeps to plain stores.
+  s.tma_out = 0;
+  if (!st.out_maps.empty()) {
+    bool ok = true;
+    L->out_maps.resize(st.out_maps.size());
+    for (size_t k = 0; ok && k < st.out_maps.size(); ++k) {
+      const OutMap& om = st.out_maps[k];
+      const CUdeviceptr base = ptr(om.tn) + (CUdeviceptr)(om.off * om.elem_bytes);
+      const int row_bytes = st.epi_chunk * om.elem_bytes;
+      if ((base & 15) || !(row_bytes == 32 || row_bytes == 64 || row_bytes == 128)) { ok = false; break; }
+      cuuint64_t dims[4] = {(cuuint64_t)g.n.extent, (cuuint64_t)g.m.extent, 1, 1};
+      cuuint64_t strides[3] = {(cuuint64_t)om.m_stride * om.elem_bytes, 0, 0};
+      const cuuint64_t filler = ((dims[0] * om.elem_bytes + 15) / 16) * 16;
+      strides[1] = strides[2] = filler;
+      if (nb == 2) {
+        dims[2] = (cuuint64_t)g.batch[1].extent; strides[1] = (cuuint64_t)om.b1_stride * om.elem_bytes;
+        dims[3] = (cuuint64_t)g.batch[0].extent; strides[2] = (cuuint64_t)om.b0_stride * om.elem_bytes;
+      } else if (nb == 1) {
+        dims[2] = (cuuint64_t)g.batch[0].extent; strides[1] = (cuuint64_t)om.b1_stride * om.elem_bytes;
+      }
+      cuuint32_t box[4] = {(cuuint32_t)st.epi_chunk, 32, 1, 1}, estr[4] = {1, 1, 1, 1};
+      const CUtensorMapSwizzle swz = row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+      const CUtensorMapDataType dt = om.elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
+      ok = cu().cuTensorMapEncodeTiled_(&L->out_maps[k], dt, 4, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
+    if (!ok) L->out_maps.assign(st.out_maps.size(), L->map_a);   // placeholders the kernel never uses
+    s.tma_out = ok ? 1u : 0u;
+  }
   s.tiles_m = (s.M + st.tile_m - 1) / st.tile_m;
   s.tiles_n = (s.N + st.tile_n - 1) / st.tile_n;
   unsigned long long tiles = (unsigned long long)s.tiles_m * s.tiles_n * s.B0 * s.B1 * (unsigned long long)(g.split_k > 0 ? g.split_k : 1);
@@ -147,6 +179,7 @@ void gemm_enqueue(b200_routine* r, int si) {
   args.push_back(&L->status);
   std::vector<CUdeviceptr>& vals = r->arg_values[si];
   for (size_t a = 0; a < vals.size(); ++a) args.push_back(&vals[a]);
+  for (auto& m : L->out_maps) args.push_back(&m);
   launch_kernel(r->dev, r->fns[si], L->grid, (unsigned)st.block, 1, (unsigned)st.smem_bytes, args.data(), "cuLaunchKernelEx(contraction)",
                 st.cta_pair ? 2u : 1u);
 }

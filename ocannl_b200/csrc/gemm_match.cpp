@@ -372,6 +372,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
     std::string arr;
     bool unit_n = false;   // the node's last axis is the n symbol: a chunk is contiguous
     std::string row_off;   // element offset of column n = 0 of this row
+    int tma = -1;          // index of the tensor map that stores this node's chunks (-1: none)
   };
   std::vector<Out> outs;
   // The n axis may be several merged loop symbols (the (head, d) of an attention projection).  A
@@ -872,6 +873,57 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   *n_fused = fused;
   if (pair_fail) return false;
 
+  // ---- outputs as TMA stores.  A chunk (32 rows of the warp x the chunk's columns) that sits in the
+  // staging tile leaves with one copy instruction when the node is a regular [batch.., m, n] array
+  // for this contraction: the m symbols (and each batch group's) compose to one stride, everything is
+  // 16-byte aligned.  All of the stage's row-contiguous outputs must qualify (the staging tiles are
+  // then managed for the copy engine), and partial tiles that are added to the output do not.
+  std::vector<OutMap> out_maps;
+  if (g.split_k == 1 && !(form_b && g.accumulate)) {
+    bool all = true;
+    std::vector<OutMap> maps;
+    for (auto& o : outs) {
+      const Tnode& t = P.tn(o.tn);
+      const int ebytes = prec_bytes(t.prec);
+      if (!(o.unit_n && (ebytes == 4 || ebytes == 2))) continue;   // stored element by element, no staging tile
+      std::map<std::string, int64_t> st_;
+      int64_t off = 0;
+      if (!strides_of(t, o.idcs, st_, off)) { all = false; break; }
+      auto group_stride = [&](const Dim& d, int64_t* stride) {
+        // outer to inner: each symbol's stride is the next one's stride times its extent
+        int64_t inner = -1;
+        for (size_t i = d.syms.size(); i-- > 0;) {
+          const int64_t s_ = st_.count(d.syms[i].first) ? st_[d.syms[i].first] : 0;
+          if (i + 1 == d.syms.size()) inner = s_;
+          else if (s_ != st_[d.syms[i + 1].first] * d.syms[i + 1].second) return false;
+        }
+        *stride = inner;
+        return inner > 0;
+      };
+      OutMap m;
+      m.tn = o.tn;
+      m.off = off;
+      int64_t n_stride = 0;
+      if (!group_stride(dm, &m.m_stride) || !group_stride(dn, &n_stride) || n_stride != 1) { all = false; break; }
+      if (gb.size() == 2) { if (!group_stride(gb[0], &m.b0_stride) || !group_stride(gb[1], &m.b1_stride)) { all = false; break; } }
+      else if (gb.size() == 1) { if (!group_stride(gb[0], &m.b1_stride)) { all = false; break; } }
+      for (int64_t v : {m.off, m.m_stride, m.b0_stride, m.b1_stride})
+        if ((v * ebytes) % 16 != 0) all = false;
+      for (auto& kv : st_) {   // no symbol beyond (batch, m, n) may move the address
+        bool known_sym = false;
+        for (auto* d : {&dm, &dn}) for (auto& sy : d->syms) known_sym |= sy.first == kv.first;
+        for (auto& d : gb) for (auto& sy : d.syms) known_sym |= sy.first == kv.first;
+        if (!known_sym && kv.second != 0) all = false;
+      }
+      if (!all) break;
+      m.elem_bytes = ebytes;
+      o.tma = (int)maps.size();
+      maps.push_back(m);
+    }
+    if (all) out_maps = maps;
+    else for (auto& o : outs) o.tma = -1;
+  }
+
   std::ostringstream fn;
   // parameters of the epilogue: the nodes it touches (+ static table)
   std::string params, args;
@@ -913,6 +965,15 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
     kargs.push_back({KArg::Scratch, 0});   // the planner assigns the offset into the routine's reduction scratch
   }
   if (em.uses_merge) return false;
+  // tensor maps of the outputs: kernel parameters by value, pointers everywhere else
+  std::string params_k = params, map_prologue;
+  for (size_t k = 0; k < out_maps.size(); ++k) {
+    const std::string nm = "b200_omap" + std::to_string(k);
+    params_k += ", const __grid_constant__ b200_tmap " + nm + "_k";
+    params += ", const b200_tmap* " + nm;
+    args += ", " + nm;
+    map_prologue += "    const b200_tmap* " + nm + " = &" + nm + "_k;\n";
+  }
 
   std::string ptr_code;
   for (auto& o : outs) {
@@ -984,7 +1045,8 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
      << "__device__ __forceinline__ void b200_epilogue_row(unsigned int* b200_r, unsigned int b200_b0, unsigned int b200_b1, "
         "unsigned int b200_m, bool b200_row_ok, unsigned int b200_n0, unsigned int b200_N, uint4* b200_stage, "
         "bool b200_has_next, unsigned int b200_next_taddr, b200_in_tiles& b200_t, unsigned int b200_slot, unsigned int b200_nslots, "
-        "bool b200_nx_ok, unsigned int b200_nx_b0, unsigned int b200_nx_b1, unsigned int b200_nx_m, bool b200_nx_row_ok, unsigned int b200_nx_n0"
+        "bool b200_nx_ok, unsigned int b200_nx_b0, unsigned int b200_nx_b1, unsigned int b200_nx_m, bool b200_nx_row_ok, unsigned int b200_nx_n0, "
+        "unsigned int& b200_nst, bool b200_tma"
      << params << ") {\n"
      << statics_prologue;
   fn << "  const unsigned int b200_lane = threadIdx.x & 31u;\n";
@@ -1024,7 +1086,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   fn << "  B200_TRE(13);\n  if (b200_has_next) {\n    b200_tmem_ld_chunk(b200_next_taddr, b200_r);\n"
      << "    b200_epilogue_load(b200_t, b200_b0, b200_b1, b200_m, b200_row_ok, b200_n0 + B200_EPI_CHUNK, b200_N" << args << ");\n"
      << "  } else if (b200_nx_ok) {\n"
-     << "    b200_epilogue_load(b200_t, b200_nx_b0, b200_nx_b1, b200_nx_m, b200_nx_row_ok, b200_nx_n0, b200_N" << args << ");\n  }\n";
+     << "    b200_epilogue_load(b200_t, b200_nx_b0, b200_nx_b1, b200_nx_m, b200_nx_row_ok, b200_nx_n0, b200_N" << args << ");\n  }\n  B200_TRE(10);\n";
   // ---- store the register tiles.  A thread owns one row of the chunk, so storing from
   //      registers would touch 32 different lines per instruction; when the chunk is whole,
   //      contiguous and every row is 16-byte aligned, the warp transposes the chunk through a
@@ -1038,10 +1100,11 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
       fn << "  {\n    " << T << "* b200_p = b200_row_ok ? (" << t.ident << " + (" << o.row_off << ") + b200_n0) : (" << T << "*)0;\n";
       if (vec) {
         const std::string V = ebytes == 4 ? "4" : "8";  // elements per 16 bytes
-        fn << "    const bool b200_fast = (b200_n0 + B200_EPI_CHUNK <= b200_N) && __all_sync(0xffffffffu, (((unsigned long long)b200_p) & 15ull) == 0ull);\n"
-           << "    if (b200_fast) {\n"
-           << "      constexpr int G = B200_EPI_CHUNK / " << V << ";   // 16-byte groups per row\n"
-           << "#pragma unroll\n      for (int g = 0; g < G; ++g) {\n        uint4 q;\n";
+        std::ostringstream fnx;   // the chunk into the staging tile `b200_tile`
+        std::ostringstream& fn_outer = fn;
+        {
+        std::ostringstream& fn = fnx;
+        fn << "#pragma unroll\n      for (int g = 0; g < G; ++g) {\n        uint4 q;\n";
         if (pair && ebytes == 4) {
           fn << "        q.x = __float_as_uint(" << o.arr << "[2 * g].x); q.y = __float_as_uint(" << o.arr << "[2 * g].y);\n"
              << "        q.z = __float_as_uint(" << o.arr << "[2 * g + 1].x); q.w = __float_as_uint(" << o.arr << "[2 * g + 1].y);\n";
@@ -1058,8 +1121,24 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
              << "        q.z = " << pk << o.arr << "[8 * g + 4], " << o.arr << "[8 * g + 5]);\n"
              << "        q.w = " << pk << o.arr << "[8 * g + 6], " << o.arr << "[8 * g + 7]);\n";
         }
-        fn << "        b200_stage[b200_lane * G + (g ^ B200_STAGE_KEY(b200_lane, G))] = q;\n      }\n"
-           << "      __syncwarp();\n      B200_TRE(14);\n"
+        fn << "        b200_tile[b200_lane * G + (g ^ B200_STAGE_KEY(b200_lane, G))] = q;\n      }\n";
+        }
+        fn_outer << "    constexpr int G = B200_EPI_CHUNK / " << V << ";   // 16-byte groups per row\n";
+        if (o.tma >= 0)
+          fn_outer << "    if (b200_tma) {\n"
+                   << "      // one TMA store per chunk: the copy engine clips rows and columns beyond the node\n"
+                   << "      uint4* b200_tile = b200_stage + (b200_nst % B200_STAGING_TILES) * (B200_STAGING_BYTES / 16);\n"
+                   << "      if (b200_nst >= B200_STAGING_TILES) {\n        if (b200_lane == 0) b200_tma_store_read_wait<B200_STAGING_TILES - 1>();\n        __syncwarp();\n      }\n      B200_TRE(9);\n"
+                   << fnx.str()
+                   << "      B200_TRE(12);\n      asm volatile(\"fence.proxy.async.shared::cta;\" ::: \"memory\");\n      __syncwarp();\n      B200_TRE(11);\n"
+                   << "      if (b200_lane == 0) b200_tma_store_4d(b200_omap" << o.tma << ", b200_smem_addr(b200_tile), (int)b200_n0, (int)(b200_m - b200_lane), (int)b200_b1, (int)b200_b0);\n"
+                   << "      ++b200_nst;\n      B200_TRE(14);\n    } else {\n";
+        else
+          fn_outer << "    {\n";
+        fn << "    const bool b200_fast = (b200_n0 + B200_EPI_CHUNK <= b200_N) && __all_sync(0xffffffffu, (((unsigned long long)b200_p) & 15ull) == 0ull);\n"
+           << "    if (b200_fast) {\n      uint4* b200_tile = b200_stage;\n"
+           << fnx.str()
+           << "      B200_TRE(9);\n      __syncwarp();\n      B200_TRE(14);\n"
            << "#pragma unroll\n      for (int it = 0; it < G; ++it) {\n"
            << "        const unsigned int r = it * (32 / G) + b200_lane / G, c = b200_lane % G;\n"
            << "        const unsigned long long dst = b200_t.r" << o.tn << "[it];\n"
@@ -1067,7 +1146,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
            << (reds ? "        if (dst) b200_red_add_v4(dst + (unsigned long long)b200_n0 * "
                     : "        if (dst) *(uint4*)(dst + (unsigned long long)b200_n0 * ")
            << ebytes << (reds ? "ull + 16ull * c, q);\n      }\n" : "ull + 16ull * c) = q;\n      }\n")
-           << "      __syncwarp();\n"
+           << "      B200_TRE(12);\n      __syncwarp();\n      B200_TRE(11);\n"
            << "    } else if (b200_row_ok) {\n";
       } else {
         fn << "    if (b200_row_ok) {\n";
@@ -1082,7 +1161,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
                      : ebytes == 4 ? "((b200_j & 1) ? " + o.arr + "[b200_j >> 1].y : " + o.arr + "[b200_j >> 1].x)"
                                    : "(unsigned short)(" + o.arr + "[b200_j >> 1] >> (16 * (b200_j & 1)))")
            << ";\n";
-      fn << "    }\n  }\n";
+      fn << "    }\n" << (vec ? "    }\n" : "") << "  }\n";
     } else {
       // general position: recompute the offset per column
       fn << "#pragma unroll\n  for (int b200_j = 0; b200_j < B200_EPI_CHUNK; ++b200_j) {\n"
@@ -1109,8 +1188,10 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   out->epi_tiles = (int)outs.size() + n_in_tiles;
   out->epi_out_bytes = 2;
   for (auto& o : outs) out->epi_out_bytes = std::max(out->epi_out_bytes, std::min(4, prec_bytes(P.tn(o.tn).prec)));
-  out->epi_params = params;
+  out->epi_params = params_k;
   out->epi_args = args;
+  out->epi_prologue = map_prologue;
+  out->out_maps = out_maps;
   out->row_followers = row_fused;
   out->epi_scratch_bytes = scratch_bytes;
   return true;
@@ -1199,14 +1280,19 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   // by latency, not issue rate; light epilogues (few register tiles) get 16 warps, which fits
   // the register file at <= 112 registers per thread.
   // columns per epilogue step: more columns = more independent work per thread (the epilogue
-  // is latency-bound) but more registers
-  int chunk = (bn >= 32 && st.epi_tiles <= 2) ? 32 : 16;
+  // is latency-bound) and half as many stores to issue; one CTA of 320 threads per SM leaves each
+  // thread 200 registers, enough for the register tiles of 32 columns
+  int chunk = bn >= 32 ? 32 : 16;
   if (st.row_followers > 0) chunk = bn;   // the whole row in one chunk
   const bool light = false;  // 16 warps measured slower: the register cap (96) makes the epilogue spill
   int epi_warps = light ? 16 : (bn >= 128 ? 8 : 4);
-  const int staging = 32 * chunk * st.epi_out_bytes;   // per warp
-  // 227 KB per CTA: ring + alignment slack + barriers + one staging tile per epilogue warp
-  int stages = (227 * 1024 - 1024 - 256 - epi_warps * staging) / stage_bytes;
+  const int staging = 32 * chunk * st.epi_out_bytes;   // one staging tile
+  // outputs that leave as TMA stores alternate between two tiles per warp (the copy engine reads one
+  // while the warp fills the other) when that leaves the ring at least four slots
+  int staging_tiles = 1;
+  if (!st.out_maps.empty() && (227 * 1024 - 1024 - 256 - epi_warps * staging * 2) / stage_bytes >= 4) staging_tiles = 2;
+  // 227 KB per CTA: ring + alignment slack + barriers + the staging tiles of the epilogue warps
+  int stages = (227 * 1024 - 1024 - 256 - epi_warps * staging * staging_tiles) / stage_bytes;
   if (stages > 8) stages = 8;
   if (stages < 2) stages = 2;
   int tmem_cols = 32;
@@ -1226,15 +1312,14 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
     << (g.a_kmajor ? 1 : 0) << "\n#define B200_B_KMAJOR " << (g.b_kmajor ? 1 : 0) << "\n#define B200_IDESC " << idesc
     << "u\n#define B200_TMEM_COLS " << tmem_cols << "\n#define B200_RASTER " << raster << "\n#define B200_CTA_PAIR "
     << (pair ? 1 : 0) << "\n#define B200_SPLITK " << g.split_k << "\n";
-  // columns per epilogue step: 32 when the epilogue keeps few register tiles, else 16 so that
-  // the tiles and the double-buffered accumulator chunk stay in registers
-  o << "#define B200_EPI_CHUNK " << chunk << "\n#define B200_STAGING_BYTES " << staging << "\n";
-  o << g.epilogue << "\n";
+  o << "#define B200_EPI_CHUNK " << chunk << "\n#define B200_STAGING_BYTES " << staging << "\n#define B200_STAGING_TILES " << staging_tiles << "\n";
+  o << "#define B200_EPI_PROLOGUE " << [&] { std::string p = st.epi_prologue; for (auto& c : p) if (c == '\n') c = ' '; return p; }() << "\n";
+  o << kTcSource << "\n" << g.epilogue << "\n";
   o << "#define B200_EPI_PARAMS " << params << "\n";
   o << "#define B200_EPILOGUE_ROWS b200_epilogue_rows(b200_tiles, b200_b0, b200_b1, b200_m, b200_m < shape.M" << args << ");\n";
   o << "#define B200_EPILOGUE_LOAD b200_epilogue_load(b200_tiles, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_pn0, shape.N" << args << ");\n";
-  o << "#define B200_EPILOGUE_ROW b200_epilogue_row(b200_r, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_n0, shape.N, b200_stage, b200_has_next, b200_next_taddr, b200_tiles, b200_slot, b200_nslots, b200_nx_ok, b200_nx_b0, b200_nx_b1, b200_nx_m, b200_nx_m < shape.M, b200_nx_n0" << args << ");\n";
-  o << kTcSource << "\n" << kGemmSource << "\n";
+  o << "#define B200_EPILOGUE_ROW b200_epilogue_row(b200_r, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_n0, shape.N, b200_stage, b200_has_next, b200_next_taddr, b200_tiles, b200_slot, b200_nslots, b200_nx_ok, b200_nx_b0, b200_nx_b1, b200_nx_m, b200_nx_m < shape.M, b200_nx_n0, b200_nst, shape.tma_out != 0u" << args << ");\n";
+  o << kGemmSource << "\n";
   std::ostringstream note;
   note << "tcgen05 " << (g.in_prec == Prec::Single ? "tf32 " : "") << bm << "x" << bn << "x" << bk << (pair ? " (CTA pair, cta_group::2)" : "") << " stages=" << stages
        << " epi_warps=" << epi_warps << (g.split_k > 1 ? " split_k=" + std::to_string(g.split_k) : std::string())
@@ -1251,7 +1336,8 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   st.cta_pair = pair ? 1 : 0;
   st.box_m = 128;
   st.box_n = pair ? bn / 2 : bn;
-  st.smem_bytes = stages * stage_bytes + 1024 + 256 + epi_warps * staging;
+  st.smem_bytes = stages * stage_bytes + 1024 + 256 + epi_warps * staging * staging_tiles;
+  st.epi_chunk = chunk;
   return o.str();
 }
 

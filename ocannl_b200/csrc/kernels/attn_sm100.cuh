@@ -79,17 +79,6 @@ __device__ __forceinline__ void b200_attn_store_chunk(uint4* stage, const unsign
 // swizzle the tensor map describes, lane 0 issues the copy and moves on; rows beyond the node's
 // extent are clipped by the copy engine.  The tile may be written again once the copy has read it
 // (b200_attn_tile_free).
-__device__ __forceinline__ void b200_tma_store_4d(const b200_tmap* map, unsigned int src, int c0, int c1, int c2, int c3) {
-  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"((unsigned long long)map),
-               "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-               : "memory");
-  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-}
-// waits until at most PENDING of this thread's copy groups still read shared memory
-template <int PENDING>
-__device__ __forceinline__ void b200_tma_store_read_wait() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(PENDING) : "memory");
-}
 __device__ __forceinline__ void b200_attn_tma_store_chunk(unsigned char* tile, const unsigned int* u, const b200_tmap* map, int t0, int s0,
                                                           int b1, int b0, unsigned int lane) {
   uint4* st = (uint4*)tile;

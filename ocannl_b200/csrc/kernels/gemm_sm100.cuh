@@ -20,7 +20,9 @@
 //   B200_ELEM_BYTES           operand element size
 //   B200_STAGES               ring depth
 //   B200_EPI_WARPS            4, 8 or 16 (a multiple of 4: one warp per TMEM lane quarter and column part)
-//   B200_STAGING_BYTES        bytes of the per-warp staging tile (32 rows x chunk columns of the widest output)
+//   B200_STAGING_BYTES        bytes of one staging tile (32 rows x chunk columns of the widest output)
+//   B200_STAGING_TILES        staging tiles per epilogue warp (2 when outputs leave as TMA stores and shared memory allows)
+//   B200_EPI_PROLOGUE         declarations at the top of the epilogue role (pointers to the output tensor maps)
 //   B200_A_KMAJOR/B_KMAJOR    1: k is the contiguous axis of the operand, 0: m/n is
 //   B200_IDESC                tcgen05 instruction descriptor (formats, majors, M, N)
 //   B200_TMEM_COLS            power of two >= 2*B200_BN (and >= 32)
@@ -38,6 +40,7 @@ struct b200_gemm_shape {
   unsigned int a_b0, a_b1;      // 1 when the operand varies along that batch axis
   unsigned int b_b0, b_b1;
   unsigned int tiles_m, tiles_n;
+  unsigned int tma_out;         // != 0: the epilogue's row-contiguous outputs leave as TMA stores (their maps are valid)
 };
 
 
@@ -93,8 +96,9 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
   const unsigned int smem_base = (b200_smem_addr(b200_dyn_smem) + 1023u) & ~1023u;
   unsigned char* smem_gen = b200_dyn_smem + (smem_base - b200_smem_addr(b200_dyn_smem));
   const unsigned int tiles_at = smem_base;
-  // barriers and bookkeeping live after the ring
-  unsigned long long* bars = (unsigned long long*)(smem_gen + B200_STAGES * B200_STAGE_BYTES);
+  // the epilogue warps' staging tiles follow the ring (1024-byte aligned, as the swizzled TMA stores want);
+  // barriers and bookkeeping live after them
+  unsigned long long* bars = (unsigned long long*)(smem_gen + B200_STAGES * B200_STAGE_BYTES + B200_EPI_WARPS * B200_STAGING_TILES * B200_STAGING_BYTES);
   const unsigned int bar_full = b200_smem_addr(bars);                          // [STAGES]
   const unsigned int bar_empty = bar_full + 8u * B200_STAGES;                  // [STAGES]
   const unsigned int bar_acc_full = bar_empty + 8u * B200_STAGES;              // [2]
@@ -262,7 +266,9 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
     const unsigned int col_half = ew >> 2;            // which part of the tile's columns this warp owns
     const unsigned int cols_per_warp = B200_BN / (B200_EPI_WARPS / 4);
     // this warp's 4 KB staging tile (transposes a chunk so that stores cover whole row segments)
-    uint4* b200_stage = (uint4*)(smem_gen + B200_STAGES * B200_STAGE_BYTES + 256 + ew * (unsigned int)B200_STAGING_BYTES);
+    uint4* b200_stage = (uint4*)(smem_gen + B200_STAGES * B200_STAGE_BYTES + ew * (unsigned int)(B200_STAGING_TILES * B200_STAGING_BYTES));
+    unsigned int b200_nst = 0;   // chunks this warp has handed to the copy engine
+    B200_EPI_PROLOGUE
     unsigned int acc = 0, acc_phase = 0;
     // (batch, row, first column) of the part of a unit's tile that this thread works on
     auto b200_coords = [&](unsigned int u, unsigned int& tile, unsigned int& b0, unsigned int& b1, unsigned int& mt, unsigned int& nt) {
@@ -345,6 +351,8 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
       B200_TRE(5);   // release of the accumulator buffer
 #endif
     }
+    // the copy engine has read this warp's staging tiles before the CTA gives its shared memory back
+    if (lane == 0) b200_tma_store_read_wait<0>();
 #ifdef B200_TRACE
     b200_tre(0, true, status);
 #endif

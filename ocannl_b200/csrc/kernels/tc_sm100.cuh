@@ -205,4 +205,19 @@ __device__ __forceinline__ void b200_tmem_st32(unsigned int taddr, const unsigne
       : "memory");
 }
 
+// TMA store of a shared-memory tile (laid out as the tensor map's swizzle says) to global memory;
+// elements outside the tensor are clipped by the copy engine.  One thread issues; the tile may be
+// written again once b200_tma_store_read_wait says the copy has read it.
+__device__ __forceinline__ void b200_tma_store_4d(const b200_tmap* map, unsigned int src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"((unsigned long long)map),
+               "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// waits until at most PENDING of this thread's copy groups still read shared memory
+template <int PENDING>
+__device__ __forceinline__ void b200_tma_store_read_wait() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(PENDING) : "memory");
+}
+
 #endif  // B200_TC_SM100_CUH

@@ -36,6 +36,9 @@ void b200_dev::check_status() {
             status_host[2], status_host[3], status_host[4], status_host[5], status_host[6], status_host[7], status_host[8],
             status_host[9], status_host[10], status_host[11], status_host[12], status_host[16 + 3], status_host[16 + 4],
             status_host[16 + 13], status_host[16 + 14], status_host[16 + 15], status_host[16 + 5]);
+    fprintf(stderr, "[b200 trace] epilogue store blocks, cycles: next-chunk loads %u, staging writes %u, first warp sync %u, staged reads + global stores %u, "
+                    "second warp sync %u\n",
+            status_host[16 + 10], status_host[16 + 9], status_host[16 + 14], status_host[16 + 12], status_host[16 + 11]);
     fprintf(stderr, "[b200 trace] attention CTA, ns since its start: setup %u, q and k landed %u, scores ready %u, pass 1 %u, pass 2 %u, "
                     "pass 3 %u, second mma issued %u, weights copied %u, output ready %u, stored %u\n",
             status_host[40], status_host[41], status_host[42], status_host[43], status_host[44], status_host[45], status_host[46],
