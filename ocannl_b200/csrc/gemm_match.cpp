@@ -973,6 +973,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
     params += ", const b200_tmap* " + nm;
     args += ", " + nm;
     map_prologue += "    const b200_tmap* " + nm + " = &" + nm + "_k;\n";
+    map_prologue += "    if (ew == " + std::to_string(k % 4) + "u && lane == 0) asm volatile(\"prefetch.tensormap [%0];\" ::\"l\"((unsigned long long)" + nm + ") : \"memory\");\n";
   }
 
   std::string ptr_code;

@@ -341,9 +341,9 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
 #if B200_CTA_PAIR
-      if (lane == 0) b200_mbar_arrive_cluster(b200_map_to_cta(bar_acc_empty + 8u * acc, 0u));
+      if (lane == 0) b200_mbar_arrive_cluster_relaxed(b200_map_to_cta(bar_acc_empty + 8u * acc, 0u));
 #else
-      if (lane == 0) b200_mbar_arrive(bar_acc_empty + 8u * acc);
+      if (lane == 0) b200_mbar_arrive_relaxed(bar_acc_empty + 8u * acc);
 #endif
       if (warp == 2 && lane == 0) { if (unit == worker) B200_TR(9); else if (unit == worker + n_workers) B200_TR(11); }
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }

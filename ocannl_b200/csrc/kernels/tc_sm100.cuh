@@ -98,6 +98,15 @@ __device__ __forceinline__ unsigned int b200_map_to_cta(unsigned int addr, unsig
 __device__ __forceinline__ void b200_mbar_arrive_cluster(unsigned int cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// Arrivals that order nothing in memory: the epilogue hands an accumulator buffer back after its
+// tensor-memory loads have completed (tcgen05.wait::ld), and must not wait for the loads of its next
+// operand tiles, which a releasing arrival would do.
+__device__ __forceinline__ void b200_mbar_arrive_relaxed(unsigned int bar) {
+  asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void b200_mbar_arrive_cluster_relaxed(unsigned int cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 __device__ __forceinline__ void b200_cluster_sync() {
 #if B200_CTA_PAIR
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
