@@ -1092,6 +1092,66 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   //      registers would touch 32 different lines per instruction; when the chunk is whole,
   //      contiguous and every row is 16-byte aligned, the warp transposes the chunk through a
   //      swizzled shared-memory staging tile and writes whole row segments instead.
+  // the chunk of one output into the staging tile `b200_tile` (G 16-byte groups per row)
+  auto sts_code = [&](const Out& o) {
+    const Tnode& t = P.tn(o.tn);
+    const int ebytes = prec_bytes(t.prec);
+    std::ostringstream fn;
+    fn << "#pragma unroll\n      for (int g = 0; g < G; ++g) {\n        uint4 q;\n";
+    if (pair && ebytes == 4) {
+      fn << "        q.x = __float_as_uint(" << o.arr << "[2 * g].x); q.y = __float_as_uint(" << o.arr << "[2 * g].y);\n"
+         << "        q.z = __float_as_uint(" << o.arr << "[2 * g + 1].x); q.w = __float_as_uint(" << o.arr << "[2 * g + 1].y);\n";
+    } else if (pair) {
+      fn << "        q.x = " << o.arr << "[4 * g]; q.y = " << o.arr << "[4 * g + 1]; q.z = " << o.arr << "[4 * g + 2]; q.w = "
+         << o.arr << "[4 * g + 3];\n";
+    } else if (ebytes == 4) {
+      fn << "        q.x = b200_bits32(" << o.arr << "[4 * g]); q.y = b200_bits32(" << o.arr << "[4 * g + 1]);\n"
+         << "        q.z = b200_bits32(" << o.arr << "[4 * g + 2]); q.w = b200_bits32(" << o.arr << "[4 * g + 3]);\n";
+    } else {
+      const std::string pk = t.prec == Prec::Bfloat16 ? "b200_pack_bf(" : "b200_pack_hf(";
+      fn << "        q.x = " << pk << o.arr << "[8 * g], " << o.arr << "[8 * g + 1]);\n"
+         << "        q.y = " << pk << o.arr << "[8 * g + 2], " << o.arr << "[8 * g + 3]);\n"
+         << "        q.z = " << pk << o.arr << "[8 * g + 4], " << o.arr << "[8 * g + 5]);\n"
+         << "        q.w = " << pk << o.arr << "[8 * g + 6], " << o.arr << "[8 * g + 7]);\n";
+    }
+    fn << "        b200_tile[b200_lane * G + (g ^ B200_STAGE_KEY(b200_lane, G))] = q;\n      }\n";
+    return fn.str();
+  };
+  // Outputs that leave as TMA stores: all of a chunk's tiles are staged (one staging tile each, in
+  // groups of B200_STAGING_TILES), made visible to the copy engine with one fence, and issued together
+  // by lane 0.  The tiles were read by the previous chunk's copies while this chunk was computed,
+  // so the wait before staging is normally over already.
+  {
+    std::vector<const Out*> tma_outs;
+    for (auto& o : outs)
+      if (o.tma >= 0) tma_outs.push_back(&o);
+    if (!tma_outs.empty()) {
+      fn << "  if (b200_tma) {\n";
+      // groups of at most two outputs (B200_STAGING_TILES is 1 or 2: the group size adapts at compile time of the kernel)
+      fn << "    constexpr unsigned int b200_group = B200_STAGING_TILES;\n";
+      for (size_t k0 = 0; k0 < tma_outs.size(); ++k0) {
+        const Out& o = *tma_outs[k0];
+        const int ebytes = prec_bytes(P.tn(o.tn).prec);
+        const std::string slot = "(" + std::to_string(k0) + "u % b200_group)";
+        fn << "    if (" << slot << " == 0u) {\n"
+           << "      if (b200_nst) {\n        if (b200_lane == 0) b200_tma_store_read_wait<0>();\n        __syncwarp();\n      }\n      B200_TRE(9);\n    }\n"
+           << "    {\n      constexpr int G = B200_EPI_CHUNK / " << (ebytes == 4 ? "4" : "8") << ";\n"
+           << "      uint4* b200_tile = b200_stage + " << slot << " * (B200_STAGING_BYTES / 16);\n"
+           << sts_code(o) << "    }\n";
+        // the group is complete: fence, then lane 0 issues its copies and commits them as one group
+        fn << "    if (" << slot << " == b200_group - 1u || " << (k0 + 1 == tma_outs.size() ? "true" : "false") << ") {\n"
+           << "      B200_TRE(12);\n      asm volatile(\"fence.proxy.async.shared::cta;\" ::: \"memory\");\n      __syncwarp();\n      B200_TRE(11);\n"
+           << "      if (b200_lane == 0) {\n";
+        // every output of this group: from the first of the group to k0
+        fn << "        constexpr unsigned int b200_first = " << k0 << "u - " << slot << ";\n";
+        for (size_t k = 0; k <= k0; ++k)
+          fn << "        if (" << k << "u >= b200_first) b200_tma_store_4d_nc(b200_omap" << tma_outs[k]->tma << ", b200_smem_addr(b200_stage + (" << k
+             << "u % b200_group) * (B200_STAGING_BYTES / 16)), (int)b200_n0, (int)(b200_m - b200_lane), (int)b200_b1, (int)b200_b0);\n";
+        fn << "        b200_tma_commit();\n      }\n      b200_nst = 1u;\n      B200_TRE(14);\n    }\n";
+      }
+      fn << "  }\n";
+    }
+  }
   for (auto& o : outs) {
     const Tnode& t = P.tn(o.tn);
     const int ebytes = prec_bytes(t.prec);
@@ -1101,44 +1161,12 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
       fn << "  {\n    " << T << "* b200_p = b200_row_ok ? (" << t.ident << " + (" << o.row_off << ") + b200_n0) : (" << T << "*)0;\n";
       if (vec) {
         const std::string V = ebytes == 4 ? "4" : "8";  // elements per 16 bytes
-        std::ostringstream fnx;   // the chunk into the staging tile `b200_tile`
-        std::ostringstream& fn_outer = fn;
-        {
-        std::ostringstream& fn = fnx;
-        fn << "#pragma unroll\n      for (int g = 0; g < G; ++g) {\n        uint4 q;\n";
-        if (pair && ebytes == 4) {
-          fn << "        q.x = __float_as_uint(" << o.arr << "[2 * g].x); q.y = __float_as_uint(" << o.arr << "[2 * g].y);\n"
-             << "        q.z = __float_as_uint(" << o.arr << "[2 * g + 1].x); q.w = __float_as_uint(" << o.arr << "[2 * g + 1].y);\n";
-        } else if (pair) {
-          fn << "        q.x = " << o.arr << "[4 * g]; q.y = " << o.arr << "[4 * g + 1]; q.z = " << o.arr << "[4 * g + 2]; q.w = "
-             << o.arr << "[4 * g + 3];\n";
-        } else if (ebytes == 4) {
-          fn << "        q.x = b200_bits32(" << o.arr << "[4 * g]); q.y = b200_bits32(" << o.arr << "[4 * g + 1]);\n"
-             << "        q.z = b200_bits32(" << o.arr << "[4 * g + 2]); q.w = b200_bits32(" << o.arr << "[4 * g + 3]);\n";
-        } else {
-          const std::string pk = t.prec == Prec::Bfloat16 ? "b200_pack_bf(" : "b200_pack_hf(";
-          fn << "        q.x = " << pk << o.arr << "[8 * g], " << o.arr << "[8 * g + 1]);\n"
-             << "        q.y = " << pk << o.arr << "[8 * g + 2], " << o.arr << "[8 * g + 3]);\n"
-             << "        q.z = " << pk << o.arr << "[8 * g + 4], " << o.arr << "[8 * g + 5]);\n"
-             << "        q.w = " << pk << o.arr << "[8 * g + 6], " << o.arr << "[8 * g + 7]);\n";
-        }
-        fn << "        b200_tile[b200_lane * G + (g ^ B200_STAGE_KEY(b200_lane, G))] = q;\n      }\n";
-        }
-        fn_outer << "    constexpr int G = B200_EPI_CHUNK / " << V << ";   // 16-byte groups per row\n";
-        if (o.tma >= 0)
-          fn_outer << "    if (b200_tma) {\n"
-                   << "      // one TMA store per chunk: the copy engine clips rows and columns beyond the node\n"
-                   << "      uint4* b200_tile = b200_stage + (b200_nst % B200_STAGING_TILES) * (B200_STAGING_BYTES / 16);\n"
-                   << "      if (b200_nst >= B200_STAGING_TILES) {\n        if (b200_lane == 0) b200_tma_store_read_wait<B200_STAGING_TILES - 1>();\n        __syncwarp();\n      }\n      B200_TRE(9);\n"
-                   << fnx.str()
-                   << "      B200_TRE(12);\n      asm volatile(\"fence.proxy.async.shared::cta;\" ::: \"memory\");\n      __syncwarp();\n      B200_TRE(11);\n"
-                   << "      if (b200_lane == 0) b200_tma_store_4d(b200_omap" << o.tma << ", b200_smem_addr(b200_tile), (int)b200_n0, (int)(b200_m - b200_lane), (int)b200_b1, (int)b200_b0);\n"
-                   << "      ++b200_nst;\n      B200_TRE(14);\n    } else {\n";
-        else
-          fn_outer << "    {\n";
+        fn << "    constexpr int G = B200_EPI_CHUNK / " << V << ";   // 16-byte groups per row\n";
+        if (o.tma >= 0) fn << "    if (!b200_tma) {\n";
+        else fn << "    {\n";
         fn << "    const bool b200_fast = (b200_n0 + B200_EPI_CHUNK <= b200_N) && __all_sync(0xffffffffu, (((unsigned long long)b200_p) & 15ull) == 0ull);\n"
            << "    if (b200_fast) {\n      uint4* b200_tile = b200_stage;\n"
-           << fnx.str()
+           << sts_code(o)
            << "      B200_TRE(9);\n      __syncwarp();\n      B200_TRE(14);\n"
            << "#pragma unroll\n      for (int it = 0; it < G; ++it) {\n"
            << "        const unsigned int r = it * (32 / G) + b200_lane / G, c = b200_lane % G;\n"

@@ -223,6 +223,13 @@ __device__ __forceinline__ void b200_tma_store_4d(const b200_tmap* map, unsigned
                : "memory");
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
+// the same without closing the group: several copies, then one b200_tma_commit
+__device__ __forceinline__ void b200_tma_store_4d_nc(const b200_tmap* map, unsigned int src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"((unsigned long long)map),
+               "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void b200_tma_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // waits until at most PENDING of this thread's copy groups still read shared memory
 template <int PENDING>
 __device__ __forceinline__ void b200_tma_store_read_wait() {
