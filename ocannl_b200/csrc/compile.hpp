@@ -94,6 +94,7 @@ struct Stage {
   std::string epi_params, epi_args;  // epilogue plumbing: extra kernel parameters / call arguments
   std::string epi_prologue;          // declarations at the top of the kernel's epilogue role (pointers to the output maps)
   std::vector<OutMap> out_maps;      // outputs that leave as TMA stores, in the order of the kernel's map parameters
+  std::vector<OutMap> in_maps;       // a row operand of the epilogue that arrives by TMA loads (its map precedes the outputs')
   int epi_chunk = 32;                // columns per epilogue step (the inner box of the output maps)
   int tile_m = 0, tile_n = 0, tile_k = 0;
   int min_align = 0;             // >0: every node the stage touches must be bound at a multiple of this many bytes

@@ -14,6 +14,7 @@ struct GemmShape {
 struct GemmLaunch {
   CUtensorMap map_a, map_b;
   std::vector<CUtensorMap> out_maps;   // the epilogue's outputs as TMA store destinations
+  std::vector<CUtensorMap> in_maps;    // a row operand of the epilogue as a TMA load source
   GemmShape shape;
   unsigned int grid = 1;
   CUdeviceptr status = 0;
@@ -115,12 +116,10 @@ GemmLaunch* gemm_prepare(b200_routine* r, int si) {
   s.tma_out = 0;
   if (!st.out_maps.empty()) {
     bool ok = true;
-    L->out_maps.resize(st.out_maps.size());
-    for (size_t k = 0; ok && k < st.out_maps.size(); ++k) {
-      const OutMap& om = st.out_maps[k];
+    auto encode = [&](const OutMap& om, CUtensorMap* map) {
       const CUdeviceptr base = ptr(om.tn) + (CUdeviceptr)(om.off * om.elem_bytes);
       const int row_bytes = st.epi_chunk * om.elem_bytes;
-      if ((base & 15) || !(row_bytes == 32 || row_bytes == 64 || row_bytes == 128)) { ok = false; break; }
+      if ((base & 15) || !(row_bytes == 32 || row_bytes == 64 || row_bytes == 128)) return false;
       cuuint64_t dims[4] = {(cuuint64_t)g.n.extent, (cuuint64_t)g.m.extent, 1, 1};
       cuuint64_t strides[3] = {(cuuint64_t)om.m_stride * om.elem_bytes, 0, 0};
       const cuuint64_t filler = ((dims[0] * om.elem_bytes + 15) / 16) * 16;
@@ -134,11 +133,20 @@ GemmLaunch* gemm_prepare(b200_routine* r, int si) {
       cuuint32_t box[4] = {(cuuint32_t)st.epi_chunk, 32, 1, 1}, estr[4] = {1, 1, 1, 1};
       const CUtensorMapSwizzle swz = row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
       const CUtensorMapDataType dt = om.elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
-      ok = cu().cuTensorMapEncodeTiled_(&L->out_maps[k], dt, 4, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
-                                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+      return cu().cuTensorMapEncodeTiled_(map, dt, 4, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                                          CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    };
+    L->out_maps.resize(st.out_maps.size());
+    for (size_t k = 0; ok && k < st.out_maps.size(); ++k) ok = encode(st.out_maps[k], &L->out_maps[k]);
+    L->in_maps.resize(st.in_maps.size());
+    for (size_t k = 0; ok && k < st.in_maps.size(); ++k) ok = encode(st.in_maps[k], &L->in_maps[k]);
+    if (!ok) {   // placeholders the kernel never uses
+      L->out_maps.assign(st.out_maps.size(), L->map_a);
+      L->in_maps.assign(st.in_maps.size(), L->map_a);
     }
-    if (!ok) L->out_maps.assign(st.out_maps.size(), L->map_a);   // placeholders the kernel never uses
     s.tma_out = ok ? 1u : 0u;
+  } else {
+    L->in_maps.assign(st.in_maps.size(), L->map_a);
   }
   s.tiles_m = (s.M + st.tile_m - 1) / st.tile_m;
   s.tiles_n = (s.N + st.tile_n - 1) / st.tile_n;
@@ -179,6 +187,7 @@ void gemm_enqueue(b200_routine* r, int si) {
   args.push_back(&L->status);
   std::vector<CUdeviceptr>& vals = r->arg_values[si];
   for (size_t a = 0; a < vals.size(); ++a) args.push_back(&vals[a]);
+  for (auto& m : L->in_maps) args.push_back(&m);
   for (auto& m : L->out_maps) args.push_back(&m);
   launch_kernel(r->dev, r->fns[si], L->grid, (unsigned)st.block, 1, (unsigned)st.smem_bytes, args.data(), "cuLaunchKernelEx(contraction)",
                 st.cta_pair ? 2u : 1u);

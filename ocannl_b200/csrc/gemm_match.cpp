@@ -427,6 +427,47 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
     outs.push_back(o);
   };
 
+  // A node as a regular [batch.., m, n] array for this contraction, for the TMA unit: the m symbols
+  // (and each batch group's) compose to one stride, n is contiguous, everything 16-byte aligned,
+  // and no other symbol moves the address.
+  auto make_map = [&](int tn, const Indices& idcs, OutMap* m) {
+    const Tnode& t = P.tn(tn);
+    const int ebytes = prec_bytes(t.prec);
+    std::map<std::string, int64_t> st_;
+    int64_t off = 0;
+    if (!strides_of(t, idcs, st_, off)) return false;
+    auto group_stride = [&](const Dim& d, int64_t* stride) {
+      // outer to inner: each symbol's stride is the next one's stride times its extent
+      int64_t inner = -1;
+      for (size_t i = d.syms.size(); i-- > 0;) {
+        const int64_t s_ = st_.count(d.syms[i].first) ? st_[d.syms[i].first] : 0;
+        if (i + 1 == d.syms.size()) inner = s_;
+        else if (s_ != st_[d.syms[i + 1].first] * d.syms[i + 1].second) return false;
+      }
+      *stride = inner;
+      return inner > 0;
+    };
+    m->tn = tn;
+    m->off = off;
+    int64_t n_stride = 0;
+    if (!group_stride(dm, &m->m_stride) || !group_stride(dn, &n_stride) || n_stride != 1) return false;
+    if (gb.size() == 2) { if (!group_stride(gb[0], &m->b0_stride) || !group_stride(gb[1], &m->b1_stride)) return false; }
+    else if (gb.size() == 1) { if (!group_stride(gb[0], &m->b1_stride)) return false; }
+    for (int64_t v : {m->off, m->m_stride, m->b0_stride, m->b1_stride})
+      if ((v * ebytes) % 16 != 0) return false;
+    for (auto& kv : st_) {
+      bool known_sym = false;
+      for (auto* d : {&dm, &dn}) for (auto& sy : d->syms) known_sym |= sy.first == kv.first;
+      for (auto& d : gb) for (auto& sy : d.syms) known_sym |= sy.first == kv.first;
+      if (!known_sym && kv.second != 0) return false;
+    }
+    m->elem_bytes = ebytes;
+    return true;
+  };
+  const bool g_split_free = true;    // (split-K is decided later; a stage that adds partial tiles never gets the TMA flag)
+  std::vector<OutMap> in_maps;       // row operands of the epilogue that arrive by TMA (at most one)
+  std::string tma_in_wait;           // code at the top of the epilogue step that takes the operand's chunk out of its tile
+
   // ---- operands of the epilogue that run along n (bias[n], mask[s, n], a residual x[b, s, n]):
   //      pre-loaded into a register tile with 16-byte loads, so that the per-column code has no
   //      dependent global load in it
@@ -464,21 +505,46 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
             const std::string T = Emitter::ctype(t.prec);
             const bool f32 = t.prec == Prec::Single;
             std::ostringstream lc;
+            // a 16-byte piece `q` (index v of the chunk's row) into the tile's entries
+            std::string unpack;
+            if (!pair && f32)
+              unpack = "        " + arr + "[4 * v] = __uint_as_float(q.x); " + arr + "[4 * v + 1] = __uint_as_float(q.y);\n"
+                       "        " + arr + "[4 * v + 2] = __uint_as_float(q.z); " + arr + "[4 * v + 3] = __uint_as_float(q.w);\n";
+            else if (!pair)
+              unpack = "        " + arr + "[8 * v] = (unsigned short)q.x; " + arr + "[8 * v + 1] = (unsigned short)(q.x >> 16);\n"
+                       "        " + arr + "[8 * v + 2] = (unsigned short)q.y; " + arr + "[8 * v + 3] = (unsigned short)(q.y >> 16);\n"
+                       "        " + arr + "[8 * v + 4] = (unsigned short)q.z; " + arr + "[8 * v + 5] = (unsigned short)(q.z >> 16);\n"
+                       "        " + arr + "[8 * v + 6] = (unsigned short)q.w; " + arr + "[8 * v + 7] = (unsigned short)(q.w >> 16);\n";
+            else if (f32)
+              unpack = "        " + arr + "[2 * v] = b200_f2{__uint_as_float(q.x), __uint_as_float(q.y)};\n"
+                       "        " + arr + "[2 * v + 1] = b200_f2{__uint_as_float(q.z), __uint_as_float(q.w)};\n";
+            else
+              unpack = "        " + arr + "[4 * v] = q.x; " + arr + "[4 * v + 1] = q.y; " + arr + "[4 * v + 2] = q.z; " + arr + "[4 * v + 3] = q.w;\n";
+            const std::string V16 = f32 ? "4" : "8";   // elements per 16 bytes
+            // An operand that varies with the row (a residual, a mask): per-thread row loads touch 32
+            // lines per instruction.  When the node is a regular array for this contraction its chunk
+            // (32 rows x the chunk's columns) arrives by one TMA load into a per-warp tile, a chunk
+            // ahead like the register loads, and every lane takes its row out of the swizzled tile.
+            OutMap imap;
+            const bool by_tma = in_maps.empty() && g_split_free && make_map(e.tn, canon, &imap);
+            if (by_tma) {
+              in_maps.push_back(imap);
+              lc << "  if (b200_es.tma) {\n    if ((threadIdx.x & 31u) == 0u) {\n"
+                 << "      b200_mbar_expect_tx(b200_es.lbar, 32u * B200_EPI_CHUNK * " << prec_bytes(t.prec) << "u);\n"
+                 << "      b200_tma_load_4d(b200_smem_addr(b200_es.ltile), b200_imap0, b200_es.lbar, (int)b200_n0, (int)(b200_m - (threadIdx.x & 31u)), (int)b200_b1, (int)b200_b0);\n"
+                 << "    }\n  } else\n";
+              tma_in_wait = "  if (b200_es.tma) {\n    b200_wait(b200_es.lbar, b200_es.lph, b200_es.abort_flag, b200_es.status, 5u);\n    b200_es.lph ^= 1u;\n"
+                            "    constexpr int G = B200_EPI_CHUNK / " + V16 + ";\n#pragma unroll\n    for (int v = 0; v < G; ++v) {\n"
+                            "        const uint4 q = b200_es.ltile[b200_lane * G + (v ^ B200_STAGE_KEY(b200_lane, G))];\n" + unpack +
+                            "    }\n    __syncwarp();\n  }\n";
+            }
             if (!pair) {
             tile_decls += std::string("  ") + T + " " + member + "[B200_EPI_CHUNK];\n";
             lc << "  if (b200_row_ok) {\n"
                << "    const " << T << "* b200_p = " << t.ident << " + (" << em.offset(row, t.dims) << ") + b200_n0;\n"
                << "    if (b200_n0 + B200_EPI_CHUNK <= b200_N && (((unsigned long long)b200_p) & 15ull) == 0ull) {\n"
-               << "#pragma unroll\n      for (int v = 0; v < B200_EPI_CHUNK / " << (f32 ? 4 : 8) << "; ++v) {\n"
-               << "        const uint4 q = ((const uint4*)b200_p)[v];\n";
-            if (f32)
-              lc << "        " << arr << "[4 * v] = __uint_as_float(q.x); " << arr << "[4 * v + 1] = __uint_as_float(q.y);\n"
-                 << "        " << arr << "[4 * v + 2] = __uint_as_float(q.z); " << arr << "[4 * v + 3] = __uint_as_float(q.w);\n";
-            else
-              lc << "        " << arr << "[8 * v] = (unsigned short)q.x; " << arr << "[8 * v + 1] = (unsigned short)(q.x >> 16);\n"
-                 << "        " << arr << "[8 * v + 2] = (unsigned short)q.y; " << arr << "[8 * v + 3] = (unsigned short)(q.y >> 16);\n"
-                 << "        " << arr << "[8 * v + 4] = (unsigned short)q.z; " << arr << "[8 * v + 5] = (unsigned short)(q.z >> 16);\n"
-                 << "        " << arr << "[8 * v + 6] = (unsigned short)q.w; " << arr << "[8 * v + 7] = (unsigned short)(q.w >> 16);\n";
+               << "#pragma unroll\n      for (int v = 0; v < B200_EPI_CHUNK / " << V16 << "; ++v) {\n"
+               << "        const uint4 q = ((const uint4*)b200_p)[v];\n" << unpack;
             lc << "      }\n    } else {\n#pragma unroll\n      for (int j = 0; j < B200_EPI_CHUNK; ++j) " << arr
                << "[j] = (b200_n0 + (unsigned int)j < b200_N) ? b200_p[j] : (" << T << ")0;\n    }\n  }\n";
             } else {
@@ -487,14 +553,8 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
             lc << "  if (b200_row_ok) {\n"
                << "    const " << T << "* b200_p = " << t.ident << " + (" << em.offset(row, t.dims) << ") + b200_n0;\n"
                << "    if (b200_n0 + B200_EPI_CHUNK <= b200_N && (((unsigned long long)b200_p) & 15ull) == 0ull) {\n"
-               << "#pragma unroll\n      for (int v = 0; v < B200_EPI_CHUNK / " << (f32 ? 4 : 8) << "; ++v) {\n"
-               << "        const uint4 q = ((const uint4*)b200_p)[v];\n";
-            if (f32)
-              lc << "        " << arr << "[2 * v] = b200_f2{__uint_as_float(q.x), __uint_as_float(q.y)};\n"
-                 << "        " << arr << "[2 * v + 1] = b200_f2{__uint_as_float(q.z), __uint_as_float(q.w)};\n";
-            else
-              lc << "        " << arr << "[4 * v] = q.x; " << arr << "[4 * v + 1] = q.y; " << arr << "[4 * v + 2] = q.z; " << arr
-                 << "[4 * v + 3] = q.w;\n";
+               << "#pragma unroll\n      for (int v = 0; v < B200_EPI_CHUNK / " << V16 << "; ++v) {\n"
+               << "        const uint4 q = ((const uint4*)b200_p)[v];\n" << unpack;
             lc << "      }\n    } else {\n#pragma unroll\n      for (int j = 0; j < B200_EPI_CHUNK / 2; ++j) {\n"
                << "        const " << T << " b200_e0 = (b200_n0 + 2u * (unsigned int)j < b200_N) ? b200_p[2 * j] : (" << T << ")0;\n"
                << "        const " << T << " b200_e1 = (b200_n0 + 2u * (unsigned int)j + 1u < b200_N) ? b200_p[2 * j + 1] : (" << T << ")0;\n";
@@ -883,40 +943,10 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
     bool all = true;
     std::vector<OutMap> maps;
     for (auto& o : outs) {
-      const Tnode& t = P.tn(o.tn);
-      const int ebytes = prec_bytes(t.prec);
+      const int ebytes = prec_bytes(P.tn(o.tn).prec);
       if (!(o.unit_n && (ebytes == 4 || ebytes == 2))) continue;   // stored element by element, no staging tile
-      std::map<std::string, int64_t> st_;
-      int64_t off = 0;
-      if (!strides_of(t, o.idcs, st_, off)) { all = false; break; }
-      auto group_stride = [&](const Dim& d, int64_t* stride) {
-        // outer to inner: each symbol's stride is the next one's stride times its extent
-        int64_t inner = -1;
-        for (size_t i = d.syms.size(); i-- > 0;) {
-          const int64_t s_ = st_.count(d.syms[i].first) ? st_[d.syms[i].first] : 0;
-          if (i + 1 == d.syms.size()) inner = s_;
-          else if (s_ != st_[d.syms[i + 1].first] * d.syms[i + 1].second) return false;
-        }
-        *stride = inner;
-        return inner > 0;
-      };
       OutMap m;
-      m.tn = o.tn;
-      m.off = off;
-      int64_t n_stride = 0;
-      if (!group_stride(dm, &m.m_stride) || !group_stride(dn, &n_stride) || n_stride != 1) { all = false; break; }
-      if (gb.size() == 2) { if (!group_stride(gb[0], &m.b0_stride) || !group_stride(gb[1], &m.b1_stride)) { all = false; break; } }
-      else if (gb.size() == 1) { if (!group_stride(gb[0], &m.b1_stride)) { all = false; break; } }
-      for (int64_t v : {m.off, m.m_stride, m.b0_stride, m.b1_stride})
-        if ((v * ebytes) % 16 != 0) all = false;
-      for (auto& kv : st_) {   // no symbol beyond (batch, m, n) may move the address
-        bool known_sym = false;
-        for (auto* d : {&dm, &dn}) for (auto& sy : d->syms) known_sym |= sy.first == kv.first;
-        for (auto& d : gb) for (auto& sy : d.syms) known_sym |= sy.first == kv.first;
-        if (!known_sym && kv.second != 0) all = false;
-      }
-      if (!all) break;
-      m.elem_bytes = ebytes;
+      if (!make_map(o.tn, o.idcs, &m)) { all = false; break; }
       o.tma = (int)maps.size();
       maps.push_back(m);
     }
@@ -967,6 +997,13 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   if (em.uses_merge) return false;
   // tensor maps of the outputs: kernel parameters by value, pointers everywhere else
   std::string params_k = params, map_prologue;
+  if (!in_maps.empty()) {
+    params_k += ", const __grid_constant__ b200_tmap b200_imap0_k";
+    params += ", const b200_tmap* b200_imap0";
+    args += ", b200_imap0";
+    map_prologue += "    const b200_tmap* b200_imap0 = &b200_imap0_k;\n";
+    map_prologue += "    if (ew == 3u && lane == 0) asm volatile(\"prefetch.tensormap [%0];\" ::\"l\"((unsigned long long)b200_imap0) : \"memory\");\n";
+  }
   for (size_t k = 0; k < out_maps.size(); ++k) {
     const std::string nm = "b200_omap" + std::to_string(k);
     params_k += ", const __grid_constant__ b200_tmap " + nm + "_k";
@@ -996,7 +1033,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
     // the stores).  Parameters mirror the epilogue's so that one argument list serves both.
     fn << "struct b200_in_tiles {\n" << tile_decls << (tile_decls.empty() ? "  int none;\n" : "") << "};\n"
        << "__device__ __forceinline__ void b200_epilogue_load(b200_in_tiles& b200_t, unsigned int b200_b0, unsigned int b200_b1, "
-          "unsigned int b200_m, bool b200_row_ok, unsigned int b200_n0, unsigned int b200_N"
+          "unsigned int b200_m, bool b200_row_ok, unsigned int b200_n0, unsigned int b200_N, b200_epi_state& b200_es"
        << params << ") {\n";
     if (!load_code.empty()) {
       fn << statics_prologue;
@@ -1047,10 +1084,10 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
         "unsigned int b200_m, bool b200_row_ok, unsigned int b200_n0, unsigned int b200_N, uint4* b200_stage, "
         "bool b200_has_next, unsigned int b200_next_taddr, b200_in_tiles& b200_t, unsigned int b200_slot, unsigned int b200_nslots, "
         "bool b200_nx_ok, unsigned int b200_nx_b0, unsigned int b200_nx_b1, unsigned int b200_nx_m, bool b200_nx_row_ok, unsigned int b200_nx_n0, "
-        "unsigned int& b200_nst, bool b200_tma"
+        "b200_epi_state& b200_es"
      << params << ") {\n"
      << statics_prologue;
-  fn << "  const unsigned int b200_lane = threadIdx.x & 31u;\n";
+  fn << "  const unsigned int b200_lane = threadIdx.x & 31u;\n" << tma_in_wait;
   {
     // batch axes: gb[0] is the outer one
     ep.str("");
@@ -1085,9 +1122,9 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   // ... or, after the tile's last chunk, the operand tiles of the first chunk of this warp's NEXT
   // tile: their latency then hides behind this chunk's stores and the wait for the next accumulator
   fn << "  B200_TRE(13);\n  if (b200_has_next) {\n    b200_tmem_ld_chunk(b200_next_taddr, b200_r);\n"
-     << "    b200_epilogue_load(b200_t, b200_b0, b200_b1, b200_m, b200_row_ok, b200_n0 + B200_EPI_CHUNK, b200_N" << args << ");\n"
+     << "    b200_epilogue_load(b200_t, b200_b0, b200_b1, b200_m, b200_row_ok, b200_n0 + B200_EPI_CHUNK, b200_N, b200_es" << args << ");\n"
      << "  } else if (b200_nx_ok) {\n"
-     << "    b200_epilogue_load(b200_t, b200_nx_b0, b200_nx_b1, b200_nx_m, b200_nx_row_ok, b200_nx_n0, b200_N" << args << ");\n  }\n  B200_TRE(10);\n";
+     << "    b200_epilogue_load(b200_t, b200_nx_b0, b200_nx_b1, b200_nx_m, b200_nx_row_ok, b200_nx_n0, b200_N, b200_es" << args << ");\n  }\n  B200_TRE(10);\n";
   // ---- store the register tiles.  A thread owns one row of the chunk, so storing from
   //      registers would touch 32 different lines per instruction; when the chunk is whole,
   //      contiguous and every row is 16-byte aligned, the warp transposes the chunk through a
@@ -1126,7 +1163,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
     for (auto& o : outs)
       if (o.tma >= 0) tma_outs.push_back(&o);
     if (!tma_outs.empty()) {
-      fn << "  if (b200_tma) {\n";
+      fn << "  if (b200_es.tma) {\n";
       // groups of at most two outputs (B200_STAGING_TILES is 1 or 2: the group size adapts at compile time of the kernel)
       fn << "    constexpr unsigned int b200_group = B200_STAGING_TILES;\n";
       for (size_t k0 = 0; k0 < tma_outs.size(); ++k0) {
@@ -1134,7 +1171,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
         const int ebytes = prec_bytes(P.tn(o.tn).prec);
         const std::string slot = "(" + std::to_string(k0) + "u % b200_group)";
         fn << "    if (" << slot << " == 0u) {\n"
-           << "      if (b200_nst) {\n        if (b200_lane == 0) b200_tma_store_read_wait<0>();\n        __syncwarp();\n      }\n      B200_TRE(9);\n    }\n"
+           << "      if (b200_es.nst) {\n        if (b200_lane == 0) b200_tma_store_read_wait<0>();\n        __syncwarp();\n      }\n      B200_TRE(9);\n    }\n"
            << "    {\n      constexpr int G = B200_EPI_CHUNK / " << (ebytes == 4 ? "4" : "8") << ";\n"
            << "      uint4* b200_tile = b200_stage + " << slot << " * (B200_STAGING_BYTES / 16);\n"
            << sts_code(o) << "    }\n";
@@ -1147,7 +1184,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
         for (size_t k = 0; k <= k0; ++k)
           fn << "        if (" << k << "u >= b200_first) b200_tma_store_4d_nc(b200_omap" << tma_outs[k]->tma << ", b200_smem_addr(b200_stage + (" << k
              << "u % b200_group) * (B200_STAGING_BYTES / 16)), (int)b200_n0, (int)(b200_m - b200_lane), (int)b200_b1, (int)b200_b0);\n";
-        fn << "        b200_tma_commit();\n      }\n      b200_nst = 1u;\n      B200_TRE(14);\n    }\n";
+        fn << "        b200_tma_commit();\n      }\n      b200_es.nst = 1u;\n      B200_TRE(14);\n    }\n";
       }
       fn << "  }\n";
     }
@@ -1162,7 +1199,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
       if (vec) {
         const std::string V = ebytes == 4 ? "4" : "8";  // elements per 16 bytes
         fn << "    constexpr int G = B200_EPI_CHUNK / " << V << ";   // 16-byte groups per row\n";
-        if (o.tma >= 0) fn << "    if (!b200_tma) {\n";
+        if (o.tma >= 0) fn << "    if (!b200_es.tma) {\n";
         else fn << "    {\n";
         fn << "    const bool b200_fast = (b200_n0 + B200_EPI_CHUNK <= b200_N) && __all_sync(0xffffffffu, (((unsigned long long)b200_p) & 15ull) == 0ull);\n"
            << "    if (b200_fast) {\n      uint4* b200_tile = b200_stage;\n"
@@ -1221,6 +1258,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
   out->epi_args = args;
   out->epi_prologue = map_prologue;
   out->out_maps = out_maps;
+  out->in_maps = in_maps;
   out->row_followers = row_fused;
   out->epi_scratch_bytes = scratch_bytes;
   return true;
@@ -1316,12 +1354,13 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   const bool light = false;  // 16 warps measured slower: the register cap (96) makes the epilogue spill
   int epi_warps = light ? 16 : (bn >= 128 ? 8 : 4);
   const int staging = 32 * chunk * st.epi_out_bytes;   // one staging tile
+  const int load_tile = st.in_maps.empty() ? 0 : 32 * chunk * st.in_maps[0].elem_bytes;   // a row operand's chunk, per warp
   // outputs that leave as TMA stores alternate between two tiles per warp (the copy engine reads one
   // while the warp fills the other) when that leaves the ring at least four slots
   int staging_tiles = 1;
-  if (!st.out_maps.empty() && (227 * 1024 - 1024 - 256 - epi_warps * staging * 2) / stage_bytes >= 4) staging_tiles = 2;
+  if (!st.out_maps.empty() && (227 * 1024 - 1024 - 512 - epi_warps * (staging * 2 + load_tile)) / stage_bytes >= 4) staging_tiles = 2;
   // 227 KB per CTA: ring + alignment slack + barriers + the staging tiles of the epilogue warps
-  int stages = (227 * 1024 - 1024 - 256 - epi_warps * staging * staging_tiles) / stage_bytes;
+  int stages = (227 * 1024 - 1024 - 512 - epi_warps * (staging * staging_tiles + load_tile)) / stage_bytes;
   if (stages > 8) stages = 8;
   if (stages < 2) stages = 2;
   int tmem_cols = 32;
@@ -1341,13 +1380,13 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
     << (g.a_kmajor ? 1 : 0) << "\n#define B200_B_KMAJOR " << (g.b_kmajor ? 1 : 0) << "\n#define B200_IDESC " << idesc
     << "u\n#define B200_TMEM_COLS " << tmem_cols << "\n#define B200_RASTER " << raster << "\n#define B200_CTA_PAIR "
     << (pair ? 1 : 0) << "\n#define B200_SPLITK " << g.split_k << "\n";
-  o << "#define B200_EPI_CHUNK " << chunk << "\n#define B200_STAGING_BYTES " << staging << "\n#define B200_STAGING_TILES " << staging_tiles << "\n";
+  o << "#define B200_EPI_CHUNK " << chunk << "\n#define B200_STAGING_BYTES " << staging << "\n#define B200_STAGING_TILES " << staging_tiles << "\n#define B200_LOAD_TILE_BYTES " << load_tile << "\n";
   o << "#define B200_EPI_PROLOGUE " << [&] { std::string p = st.epi_prologue; for (auto& c : p) if (c == '\n') c = ' '; return p; }() << "\n";
   o << kTcSource << "\n" << g.epilogue << "\n";
   o << "#define B200_EPI_PARAMS " << params << "\n";
   o << "#define B200_EPILOGUE_ROWS b200_epilogue_rows(b200_tiles, b200_b0, b200_b1, b200_m, b200_m < shape.M" << args << ");\n";
-  o << "#define B200_EPILOGUE_LOAD b200_epilogue_load(b200_tiles, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_pn0, shape.N" << args << ");\n";
-  o << "#define B200_EPILOGUE_ROW b200_epilogue_row(b200_r, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_n0, shape.N, b200_stage, b200_has_next, b200_next_taddr, b200_tiles, b200_slot, b200_nslots, b200_nx_ok, b200_nx_b0, b200_nx_b1, b200_nx_m, b200_nx_m < shape.M, b200_nx_n0, b200_nst, shape.tma_out != 0u" << args << ");\n";
+  o << "#define B200_EPILOGUE_LOAD b200_epilogue_load(b200_tiles, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_pn0, shape.N, b200_es" << args << ");\n";
+  o << "#define B200_EPILOGUE_ROW b200_epilogue_row(b200_r, b200_b0, b200_b1, b200_m, b200_m < shape.M, b200_n0, shape.N, b200_stage, b200_has_next, b200_next_taddr, b200_tiles, b200_slot, b200_nslots, b200_nx_ok, b200_nx_b0, b200_nx_b1, b200_nx_m, b200_nx_m < shape.M, b200_nx_n0, b200_es" << args << ");\n";
   o << kGemmSource << "\n";
   std::ostringstream note;
   note << "tcgen05 " << (g.in_prec == Prec::Single ? "tf32 " : "") << bm << "x" << bn << "x" << bk << (pair ? " (CTA pair, cta_group::2)" : "") << " stages=" << stages
@@ -1365,7 +1404,7 @@ std::string gemm_translation_unit(const Program& P, Stage& st, const std::string
   st.cta_pair = pair ? 1 : 0;
   st.box_m = 128;
   st.box_n = pair ? bn / 2 : bn;
-  st.smem_bytes = stages * stage_bytes + 1024 + 256 + epi_warps * staging * staging_tiles;
+  st.smem_bytes = stages * stage_bytes + 1024 + 512 + epi_warps * (staging * staging_tiles + load_tile);
   st.epi_chunk = chunk;
   return o.str();
 }

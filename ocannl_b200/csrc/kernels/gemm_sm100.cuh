@@ -23,6 +23,7 @@
 //   B200_STAGING_BYTES        bytes of one staging tile (32 rows x chunk columns of the widest output)
 //   B200_STAGING_TILES        staging tiles per epilogue warp (2 when outputs leave as TMA stores and shared memory allows)
 //   B200_EPI_PROLOGUE         declarations at the top of the epilogue role (pointers to the output tensor maps)
+//   B200_LOAD_TILE_BYTES      bytes of the per-warp tile that receives a row operand's chunk by TMA (0: none)
 //   B200_A_KMAJOR/B_KMAJOR    1: k is the contiguous axis of the operand, 0: m/n is
 //   B200_IDESC                tcgen05 instruction descriptor (formats, majors, M, N)
 //   B200_TMEM_COLS            power of two >= 2*B200_BN (and >= 32)
@@ -98,12 +99,14 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
   const unsigned int tiles_at = smem_base;
   // the epilogue warps' staging tiles follow the ring (1024-byte aligned, as the swizzled TMA stores want);
   // barriers and bookkeeping live after them
-  unsigned long long* bars = (unsigned long long*)(smem_gen + B200_STAGES * B200_STAGE_BYTES + B200_EPI_WARPS * B200_STAGING_TILES * B200_STAGING_BYTES);
+  unsigned long long* bars = (unsigned long long*)(smem_gen + B200_STAGES * B200_STAGE_BYTES +
+                                                   B200_EPI_WARPS * (B200_STAGING_TILES * B200_STAGING_BYTES + B200_LOAD_TILE_BYTES));
   const unsigned int bar_full = b200_smem_addr(bars);                          // [STAGES]
   const unsigned int bar_empty = bar_full + 8u * B200_STAGES;                  // [STAGES]
   const unsigned int bar_acc_full = bar_empty + 8u * B200_STAGES;              // [2]
   const unsigned int bar_acc_empty = bar_acc_full + 16u;                       // [2]
-  volatile unsigned int* tmem_slot = (volatile unsigned int*)(bars + 2 * B200_STAGES + 4);
+  const unsigned int bar_load = bar_acc_empty + 16u;                           // [EPI_WARPS]: row operands loaded by TMA
+  volatile unsigned int* tmem_slot = (volatile unsigned int*)(bars + 2 * B200_STAGES + 4 + B200_EPI_WARPS);
   volatile unsigned int* abort_flag = tmem_slot + 1;
 
   // the next kernel in the stream may be placed as soon as every CTA of this one is running
@@ -130,6 +133,7 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
       // the leader's accumulator buffer is free again when the epilogue warps of both CTAs are done with it
       b200_mbar_init(bar_acc_empty + 8u * a, B200_EPI_WARPS * (1 + B200_CTA_PAIR));
     }
+    for (unsigned int w = 0; w < B200_EPI_WARPS; ++w) b200_mbar_init(bar_load + 8u * w, 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -267,7 +271,16 @@ B200_GEMM_NAME(const __grid_constant__ b200_tmap map_a, const __grid_constant__ 
     const unsigned int cols_per_warp = B200_BN / (B200_EPI_WARPS / 4);
     // this warp's 4 KB staging tile (transposes a chunk so that stores cover whole row segments)
     uint4* b200_stage = (uint4*)(smem_gen + B200_STAGES * B200_STAGE_BYTES + ew * (unsigned int)(B200_STAGING_TILES * B200_STAGING_BYTES));
-    unsigned int b200_nst = 0;   // chunks this warp has handed to the copy engine
+    b200_epi_state b200_es;
+    b200_es.tma = shape.tma_out != 0u;
+    b200_es.nst = 0u;
+    // the tile and barrier of a row operand that arrives by TMA (B200_LOAD_TILE_BYTES is 0 without one)
+    b200_es.ltile = (uint4*)(smem_gen + B200_STAGES * B200_STAGE_BYTES + B200_EPI_WARPS * B200_STAGING_TILES * B200_STAGING_BYTES +
+                             ew * (unsigned int)B200_LOAD_TILE_BYTES);
+    b200_es.lbar = bar_load + 8u * ew;
+    b200_es.lph = 0u;
+    b200_es.abort_flag = abort_flag;
+    b200_es.status = status;
     B200_EPI_PROLOGUE
     unsigned int acc = 0, acc_phase = 0;
     // (batch, row, first column) of the part of a unit's tile that this thread works on

@@ -236,4 +236,15 @@ __device__ __forceinline__ void b200_tma_store_read_wait() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(PENDING) : "memory");
 }
 
+// Per-warp state of a contraction epilogue that the generated code shares with the kernel.
+struct b200_epi_state {
+  bool tma;                            // outputs leave as TMA stores, row operands arrive as TMA loads (the maps are valid)
+  unsigned int nst;                    // != 0: this warp has copies in flight that read its staging tiles
+  uint4* ltile;                        // tile that receives a row operand's chunk (32 rows, swizzled like a staging tile)
+  unsigned int lbar;                   // its barrier (shared-memory address)
+  unsigned int lph;                    // parity of the next completion to wait for
+  volatile unsigned int* abort_flag;   // the CTA's abort flag and the device status word, for the bounded wait
+  unsigned int* status;
+};
+
 #endif  // B200_TC_SM100_CUH
