@@ -1509,8 +1509,34 @@ struct Builder {
         em.forwarded[set.tn] = {set.idcs, sname};     // every lane holds the value after the shuffle tree
       } else {
         em.set_redirect[set.tn] = {set.idcs, reg(set.tn) + "[b200_e]"};
-        text += "#pragma unroll\n    for (unsigned int b200_e = 0; b200_e < " + std::to_string(EPL) + "u; ++b200_e) {\n"
-                "      const unsigned int " + st.t_sym + " = b200_t0 + b200_e;\n" + em.stmt(set, 6) + "    }\n";
+        const std::string loop_head = "#pragma unroll\n    for (unsigned int b200_e = 0; b200_e < " + std::to_string(EPL) + "u; ++b200_e) {\n"
+                                      "      const unsigned int " + st.t_sym + " = b200_t0 + b200_e;\n";
+        // divisors that are the same for the whole row (a standard deviation, a sum) are prepared
+        // once: reciprocal and range check per row, a short exact sequence per element
+        std::vector<std::string> probe;
+        em.divisor_probe = &probe;
+        const std::string body_plain = em.stmt(set, 6);
+        em.divisor_probe = nullptr;
+        std::vector<std::string> inv;
+        for (auto& d : probe)
+          if (d.find('[') == std::string::npos && d.find(st.t_sym) == std::string::npos && d.find("b200_e") == std::string::npos &&
+              std::find(inv.begin(), inv.end(), d) == inv.end())
+            inv.push_back(d);
+        if (!inv.empty()) {
+          std::string all_fast;
+          text += "    {\n";
+          for (size_t q = 0; q < inv.size(); ++q) {
+            const std::string nm = "b200_dv" + std::to_string(set.tn) + "_" + std::to_string(q);
+            text += "    const b200_divisor " + nm + " = b200_divisor_of(" + inv[q] + ");\n";
+            em.divisor_vars[inv[q]] = nm;
+            all_fast += (q ? " && " : "") + nm + ".fast";
+          }
+          const std::string body_fast = em.stmt(set, 6);
+          em.divisor_vars.clear();
+          text += "    if (" + all_fast + ") {\n" + loop_head + body_fast + "    }\n    } else {\n" + loop_head + body_plain + "    }\n    }\n    }\n";
+        } else {
+          text += loop_head + body_plain + "    }\n";
+        }
         em.set_redirect.erase(set.tn);
         text += stv(set.tn, rownodes[set.tn]);
         have.insert(set.tn);

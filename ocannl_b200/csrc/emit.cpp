@@ -330,6 +330,18 @@ std::string Emitter::binop(Prec prec, const std::string& op, const std::string& 
   if (prec == Prec::Fp8) return "b200_f2fp8(" + binop_plain(Prec::Single, op, "b200_fp82f(" + a + ")", "b200_fp82f(" + b + ")") + ")";
   if (lowp(prec) && selects_exactly(op)) return binop_plain(Prec::Single, op, a, b);
   if (op == "div" && (lowp(prec) || prec == Prec::Single)) {
+    {
+      // a power of two: the quotient is the product with its reciprocal, bit for bit
+      int e2 = 0;
+      char tail = 0;
+      if (sscanf(b.c_str(), "0x1p%d%c", &e2, &tail) == 2 && tail == 'f' && b.size() <= 10 && e2 > -100 && e2 < 100) {
+        char r[32];
+        snprintf(r, sizeof r, "0x1p%+df", -e2);
+        const std::string q = "(" + a + " * " + r + ")";
+        return lowp(prec) ? std::string(round_fn(prec)) + q + ")" : q;
+      }
+    }
+    if (divisor_probe) divisor_probe->push_back(b);
     // a divisor that the caller prepared once for many numerators (see b200_divisor in numerics.cuh)
     auto it = divisor_vars.find(b);
     if (it != divisor_vars.end()) {

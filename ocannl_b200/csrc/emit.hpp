@@ -55,6 +55,9 @@ struct Emitter {
   // divisors prepared once for many numerators: emitted text of the divisor -> name of a b200_divisor
   // variable in scope; a single-precision (or 16-bit) division by exactly that text uses it
   std::map<std::string, std::string> divisor_vars;
+  // when set, the emitted text of every single-precision divisor is appended here (a caller that
+  // wants to prepare row-invariant divisors emits once to see them)
+  std::vector<std::string>* divisor_probe = nullptr;
   // nodes read through another name (a copy staged in shared memory)
   std::map<int, std::string> node_alias;
   // nodes whose loads may use the read-only data path
