@@ -853,9 +853,52 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
         if (!v.defs.empty()) { em.scope_subst.erase(gscope->scope_id); break; }
         em.used_nodes.insert(fo.set->tn);
         row_written.insert(fo.set->tn);
-        code += "        " + T.ident + "[" + em.offset(fo.set->idcs, T.dims) + "] = " + Emitter::store_wrap(T.prec, v.expr) + ";\n"
-                "        *b200_ticket = 0u;\n      }\n    }\n  }\n";
+        const std::string gv = "b200_g" + std::to_string(fo.set->tn);
+        code += "        const " + std::string(Emitter::rtype(T.prec)) + " " + gv + " = " + v.expr + ";\n"
+                "        " + T.ident + "[" + em.offset(fo.set->idcs, T.dims) + "] = " + Emitter::store_wrap(T.prec, gv) + ";\n";
         em.scope_subst.erase(gscope->scope_id);
+        // Scalar assignments that follow the sum (a mean: total / batch) run right here, in the one
+        // thread that holds the total: they read it (and one another) from registers and otherwise
+        // only nodes this stage does not write.
+        {
+          const auto saved_fwd = em.forwarded;
+          em.forwarded[fo.set->tn] = {fo.set->idcs, gv};
+          std::set<int> stage_writes = row_written;
+          for (auto& o : outs) stage_writes.insert(o.tn);
+          stage_writes.insert(fo.set->tn);
+          for (size_t fj = fi + 1; fj < followers.size(); ++fj) {
+            const Follower& ft = followers[fj];
+            if (!ft.set || ft.set->kind != Stmt::Set || ft.set->vec_len > 0 || !ft.nest.empty()) break;
+            const Tnode& T2 = P.tn(ft.set->tn);
+            if (T2.mode == Mode::Virtual || T2.prec == Prec::Uint4x32 || stage_writes.count(ft.set->tn) || em.used_nodes.count(ft.set->tn)) break;
+            bool fine = true;
+            for (auto& ix : ft.set->idcs) if (ix.kind != Index::Fixed) fine = false;
+            walk_scalar_simple(*ft.set->value, [&](const Scalar& e) {
+              if (e.kind == Scalar::LocalScope || e.kind == Scalar::GetLocal || e.kind == Scalar::GetMerge || e.kind == Scalar::GetDyn) fine = false;
+              if (e.kind == Scalar::Get) {
+                for (auto& ix : e.idcs) if (ix.kind != Index::Fixed) fine = false;
+                auto fw = em.forwarded.find(e.tn);
+                const bool forwarded_here = fw != em.forwarded.end() && fw->second.first.size() == e.idcs.size() &&
+                                            std::equal(e.idcs.begin(), e.idcs.end(), fw->second.first.begin(),
+                                                       [](const Index& a, const Index& b) { return a.kind == b.kind && a.fixed == b.fixed; });
+                if (stage_writes.count(e.tn) && !forwarded_here) fine = false;   // another CTA may still be writing it
+              }
+            });
+            if (!fine) break;
+            Emitter::Res w = em.scalar(T2.prec, *ft.set->value);
+            if (!w.defs.empty()) break;
+            const std::string tv = "b200_g" + std::to_string(ft.set->tn);
+            code += "        const " + std::string(Emitter::rtype(T2.prec)) + " " + tv + " = " + w.expr + ";\n"
+                    "        " + T2.ident + "[" + em.offset(ft.set->idcs, T2.dims) + "] = " + Emitter::store_wrap(T2.prec, tv) + ";\n";
+            em.used_nodes.insert(ft.set->tn);
+            row_written.insert(ft.set->tn);
+            stage_writes.insert(ft.set->tn);
+            em.forwarded[ft.set->tn] = {ft.set->idcs, tv};
+            ++row_fused;
+          }
+          em.forwarded = saved_fwd;
+        }
+        code += "        *b200_ticket = 0u;\n      }\n    }\n  }\n";
         em.unroll_loops = false;
         final_code = code;
         // slots: one per epilogue warp of every tile (4 warps per 128-row tile)
