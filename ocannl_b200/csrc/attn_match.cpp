@@ -523,9 +523,12 @@ bool match_attention(const Program& P, const std::vector<StmtP>& flat, size_t at
       rows_body += std::string("  ") + var + " = 0ull;\n";
     }
   };
-  ptr_line("p_scores", s1.tn, scores_idcs, kT);
-  ptr_line("p_exp", s3.tn, exp_idcs, kT);
-  ptr_line("p_w", s5.tn, w_idcs, kT);
+  // (scores, exponentials and weights leave through tensor maps: kept ones are recorded, no pointer is needed)
+  for (int tn : {s1.tn, s3.tn, s5.tn})
+    if (kept(tn)) {
+      written.insert(tn);
+      em.used_nodes.insert(tn);   // stays a parameter: link checks its binding and alignment through it
+    }
   ptr_line("p_max", s2.tn, max_idcs, kT);
   ptr_line("p_sum", s4.tn, sum_idcs, kT);
   ptr_line("p_out", s6.tn, out_idcs, kE);
@@ -721,8 +724,8 @@ bool match_attention(const Program& P, const std::vector<StmtP>& flat, size_t at
          << (O.prec == Prec::Bfloat16 ? "b200_pack_bf" : "b200_pack_hf") << "(b200_a[2 * b200_j], b200_a[2 * b200_j + 1]);\n}\n";
     em.scope_subst.clear();
   }
-  fn << "__device__ __forceinline__ void b200_attn_rows(const b200_attn_row& row, unsigned long long& p_scores, unsigned long long& p_exp, "
-        "unsigned long long& p_w, unsigned long long& p_max, unsigned long long& p_sum, unsigned long long& p_out B200_ATTN_PARAMS) {\n"
+  fn << "__device__ __forceinline__ void b200_attn_rows(const b200_attn_row& row, unsigned long long& p_max, unsigned long long& p_sum, "
+        "unsigned long long& p_out B200_ATTN_PARAMS) {\n"
      << syms << rows_body << "}\n";
   if (em.uses_merge || em.uses_statics) return false;
 

@@ -464,7 +464,6 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
     m->elem_bytes = ebytes;
     return true;
   };
-  const bool g_split_free = true;    // (split-K is decided later; a stage that adds partial tiles never gets the TMA flag)
   std::vector<OutMap> in_maps;       // row operands of the epilogue that arrive by TMA (at most one)
   std::string tma_in_wait;           // code at the top of the epilogue step that takes the operand's chunk out of its tile
 
@@ -526,7 +525,7 @@ static bool match_gemm_mode(const Program& P, const std::vector<LoopDim>& nest, 
             // (32 rows x the chunk's columns) arrives by one TMA load into a per-warp tile, a chunk
             // ahead like the register loads, and every lane takes its row out of the swizzled tile.
             OutMap imap;
-            const bool by_tma = in_maps.empty() && g_split_free && make_map(e.tn, canon, &imap);
+            const bool by_tma = in_maps.empty() && make_map(e.tn, canon, &imap);   // (a stage that adds partial tiles never gets the TMA flag)
             if (by_tma) {
               in_maps.push_back(imap);
               lc << "  if (b200_es.tma) {\n    if ((threadIdx.x & 31u) == 0u) {\n"

@@ -10,7 +10,7 @@
 // the halves meet through shared memory -- the weights are written to shared memory in the
 // operand layout of the tensor cores and a second tcgen05.mma forms the 128 x 64 output.  Scores,
 // exponentials and weights are written to global memory only when the routine keeps those nodes
-// (their row pointers are non-null); max and sum likewise.
+// (as TMA stores); max and sum likewise (their row pointers are non-null then).
 //
 // The translation unit that includes this text defines
 //   B200_ATTN_NAME       kernel symbol
@@ -23,7 +23,7 @@
 //   B200_KEEP_SCORES / B200_KEEP_EXP / B200_KEEP_W   1: the routine keeps that node (it is written, by TMA stores)
 //   B200_ATTN_PARAMS / B200_ATTN_ARGS    node pointers of the generated code
 // and the generated functions b200_attn_score_chunk, b200_attn_exp_chunk, b200_attn_weight_chunk,
-// b200_attn_out_chunk, b200_attn_row_max, b200_attn_row_sum and b200_attn_rows (see attn_match.cpp).
+// b200_attn_out_chunk, b200_attn_row_max, b200_attn_row_sum, b200_attn_cond_rows and b200_attn_rows (see attn_match.cpp).
 #ifndef B200_ATTN_SM100_CUH
 #define B200_ATTN_SM100_CUH
 
@@ -135,8 +135,7 @@ struct b200_attn_row {
 
 // generated per routine (defined after this text)
 __device__ __forceinline__ float b200_attn_max_init();
-__device__ __forceinline__ void b200_attn_rows(const b200_attn_row& row, unsigned long long& p_scores, unsigned long long& p_exp,
-                                               unsigned long long& p_w, unsigned long long& p_max, unsigned long long& p_sum,
+__device__ __forceinline__ void b200_attn_rows(const b200_attn_row& row, unsigned long long& p_max, unsigned long long& p_sum,
                                                unsigned long long& p_out B200_ATTN_PARAMS);
 __device__ __forceinline__ void b200_attn_cond_rows(const b200_attn_row& row, unsigned long long* p B200_ATTN_PARAMS);
 __device__ __forceinline__ void b200_attn_score_chunk(const b200_attn_row& row, unsigned int t0, const unsigned int* acc, float* x,
@@ -245,9 +244,10 @@ B200_ATTN_NAME(const __grid_constant__ b200_tmap map_q, const __grid_constant__ 
   const unsigned int r_in_tile = quarter * 32u + lane;
   const unsigned int col0 = half * B200_HALF_COLS;
   const unsigned int taddr = tmem_base + ((quarter * 32u) << 16);
-  // row pointers of the nodes this routine keeps (byte address of column 0 of this thread's row; 0: not written)
-  unsigned long long p_scores, p_exp, p_w, p_max, p_sum, p_out;
-  b200_attn_rows(row, p_scores, p_exp, p_w, p_max, p_sum, p_out B200_ATTN_ARGS);
+  // row pointers of the per-row nodes this routine keeps and of the output (byte address of this thread's
+  // row; 0: not written); scores, exponentials and weights leave through their tensor maps
+  unsigned long long p_max, p_sum, p_out;
+  b200_attn_rows(row, p_max, p_sum, p_out B200_ATTN_ARGS);
 
   // Operands of the score expression that are only tested against zero (masks) arrive packed to one
   // bit per element: this thread's half row is B200_HALF_COLS / 32 words, fetched while the queries
