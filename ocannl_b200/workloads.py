@@ -599,13 +599,17 @@ def transformer_forward(batch=64, seq=256, layers=6, d_model=512, heads=8, d_hea
 
 # ------------------------------------------------------------------ attention chain
 def attention(batch: int, heads: int, queries: int, keys: int, prec: str = "bfloat16", mask: bool = True,
-              row_mode: str = "ctx", out_prec: str = None, d_head: int = 64) -> Routine:
+              row_mode: str = "ctx", out_prec: str = None, d_head: int = 64, odd_first: bool = False) -> Routine:
     """The six statements `multi_head_attention` lowers to (lib/nn_blocks.ml:222-236 with the softmax
     of :137-143), on q [b, s, h, e], k and v [b, t, h, e]: scaled scores (masked by `where` when
     `mask`), row max, exponentials, row sum, weights, weights . values.  `row_mode` is the memory
-    class of the five intermediate nodes ("ctx": kept by the context, "local": routine-local)."""
+    class of the five intermediate nodes ("ctx": kept by the context, "local": routine-local).
+    `odd_first` declares a three-element node ahead of the operands, so that an allocator that aligns
+    to the element size only (the reference's) places everything behind it off the 16-byte grid."""
     r = Routine("attention_b%d_h%d_s%d_t%d" % (batch, heads, queries, keys))
     B, H, S, T, E = batch, heads, queries, keys, d_head
+    if odd_first:
+        r.tn("odd", prec, [3], read_only=True)
     q = r.tn("q", prec, [B, S, H, E], read_only=True)
     k = r.tn("k", prec, [B, T, H, E], read_only=True)
     v = r.tn("v", prec, [B, T, H, E], read_only=True)

@@ -86,3 +86,28 @@ def test_two_runs_in_a_row_and_graph_replay(device):
     got, _ = run_device(device, ir, inputs, statics=({}, {}, {}), graph=True)
     compare(ir, got, want, 2e-2, 2e-2, only=["av"])
     compare(ir, got, want, 1e-5, 8e-5, only=["scores"])
+
+
+def test_operands_off_the_16_byte_grid_fall_back_to_the_separate_stages(device):
+    """Under the reference's packing a three-element node ahead of q, k and v leaves them 6 bytes off
+    the 16-byte grid: no tensor map can describe them, the statements are planned again without the
+    fused stage (and without the tensor-core contractions) at link, and the results do not change."""
+    ir = R.attention(1, 2, 128, 128, odd_first=True)
+    inputs = R.attention_inputs(1, 2, 128, 128)
+    inputs["odd"] = np.zeros(3, np.uint16)
+    want = run_oracle(ir, inputs)
+    code = bk.Code(ir)
+    assert any(s["kind"] == "attention" for s in code.info()["stages"])
+    rt = bk.Context(device, packing="reference").link(code)
+    assert not any(s["kind"] in ("attention", "gemm") for s in rt.info()["stages"]), rt.info()
+    for name, v in inputs.items():
+        rt.context.from_host(name, v)
+    rt.run()
+    device.await_()
+    got = {t.ident: rt.context.to_host(t.ident) for t in ir.params()}
+    rt.free()
+    code.free()
+    for p in {p for p, _, _ in rt.context.arrays.values()}:
+        device.free_pool(p)
+    compare(ir, got, want, 1e-5, 8e-5, only=["scores", "max"])
+    compare(ir, got, want, 2e-2, 2e-2, only=["av"])
