@@ -283,6 +283,20 @@ module Fresh () : Backend_impl.Lowered_backend = struct
     check (c_used_memory device.dev.handle n);
     Unsigned.Size_t.to_int !@n
 
+  (* Compile options of the library ("key=0|1 ..."), from ocannl_config entries b200_<key> (as the cc
+     backend reads cc_backend_* there, utils.ml:242); absent entries keep the library's defaults. *)
+  let compile_options =
+    lazy
+      (let keys = [ "gemm"; "attn"; "tf32"; "splitk"; "coop"; "fuse"; "pairs"; "bounds" ] in
+       let set =
+         List.filter_map keys ~f:(fun k ->
+             match Utils.get_global_arg ~default:"" ~arg_name:("b200_" ^ k) with
+             | "" -> None
+             | v -> Some (k ^ "=" ^ if String.(v = "true" || v = "1") then "1" else "0"))
+       in
+       let set = if Utils.settings.large_models then "large_models=1" :: set else set in
+       if List.is_empty set then None else Some (String.concat ~sep:" " set))
+
   (* compile / link (backend_impl.ml:334-367) *)
   let compile ~name bindings (lowered : Low_level.optimized) =
     let params =
@@ -291,7 +305,7 @@ module Fresh () : Backend_impl.Lowered_backend = struct
     in
     let text = Ser.optimized ~name ~bindings ~in_ctx:(fun tn -> Tn.is_in_context_force tn 3363) lowered in
     let h = allocate vp null in
-    check (c_compile name text (Unsigned.Size_t.of_int (String.length text)) None h);
+    check (c_compile name text (Unsigned.Size_t.of_int (String.length text)) (Lazy.force compile_options) h);
     { handle = !@h; name; params; statics = Indexing.bound_symbols bindings }
 
   let compile_batch ~names bindings lowereds =
