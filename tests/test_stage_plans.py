@@ -139,3 +139,28 @@ def test_range_checked_build_wraps_every_node_pointer():
         assert "const b200_checked<const unsigned short> x = {x__p, 2048ull, b200_status" in src
     finally:
         code.free()
+
+
+def test_contraction_epilogues_use_the_copy_engine_where_the_layout_allows():
+    """Outputs that are regular [batch.., m, n] arrays with 16-byte row strides leave as TMA stores, a
+    residual arrives by TMA loads; ten- or 27-column rows (40 / 108 bytes) keep the plain stores."""
+    def sources(ir):
+        code = bk.Code(ir)
+        try:
+            return [(s, code.source(i)) for i, s in enumerate(code.info()["stages"]) if s["kind"] == "gemm"]
+        finally:
+            code.free()
+
+    mlp = sources(W.mlp_forward(rows=8192))
+    assert len(mlp) == 3
+    assert all("b200_tma_store_4d_nc(b200_omap0" in src for _, src in mlp[:2])          # the two hidden layers
+    assert "b200_omap0" not in mlp[2][1]                                                 # logits: rows of 10 floats
+    dec = sources(W.transformer_forward(batch=8, layers=1))
+    with_residual = [src for _, src in dec if "b200_imap0" in src]
+    assert len(with_residual) == 2                                                       # w_o and the second feed-forward contraction
+    assert all("b200_tma_load_4d(b200_smem_addr(b200_es.ltile), b200_imap0" in src for src in with_residual)
+    assert dec[-1][0]["n"] == 27 and "b200_omap" not in dec[-1][1]                        # the head: rows of 27 floats
+    # partial tiles that are added to the output (split-K) do not go through the copy engine
+    train = sources(W.mlp_train_update(rows=8192))
+    split = [src for s, src in train if "split_k" in s["note"]]
+    assert split and all("b200_omap" not in src for src in split)
