@@ -520,6 +520,60 @@ def probe_ffn(dev, batch=64, seq=256, d_model=512, d_ff=2048):
     return out
 
 
+def probe_layer_norm(dev, batch=64, seq=256, d_model=512, eps=1e-5):
+    """One layer norm of the decoder as a routine of its own (`layer_norm`, lib/nn_blocks.ml:251-258, on
+    16384 rows of 512 bf16 features: row sum, centring, root of the summed squares, scale and shift).
+    A small case for profilers."""
+    from ocannl_b200 import backend as bk
+    from ocannl_b200 import workloads as W
+    from ocannl_b200.low_level import Routine, Seq, Set, loops, un
+    r = Routine("layer_norm_b%d_s%d" % (batch, seq))
+    B, S, D = batch, seq, d_model
+    src = r.tn("x", "bfloat16", [B, S, D], read_only=True)
+    out = r.tn("y", "bfloat16", [B, S, D])
+    ssum = r.tn("sum", "single", [B, S, 1])
+    cen = r.tn("centered", "single", [B, S, D])
+    std = r.tn("std", "single", [B, S, 1])
+    gamma = r.tn("gamma", "single", [D], read_only=True)
+    beta = r.tn("beta", "single", [D], read_only=True)
+    body = []
+    b, s_, d = r.syms(3)
+    body.append(loops([(b, B), (s_, S)], Set(ssum, (b, s_, 0), W.reduce_scope(r, "n_sum", "single", [(d, D)], lambda: src[b, s_, d], op="add"))))
+    b, s_, d = r.syms(3)
+    body.append(loops([(b, B), (s_, S), (d, D)], Set(cen, (b, s_, d), (src[b, s_, d] - ssum[b, s_, 0]) / float(D))))
+    b, s_, d = r.syms(3)
+    body.append(loops([(b, B), (s_, S)], Set(std, (b, s_, 0), un("sqrt", W.reduce_scope(
+        r, "n_var", "single", [(d, D)], lambda: cen[b, s_, d] * cen[b, s_, d], op="add") + eps))))
+    b, s_, d = r.syms(3)
+    body.append(loops([(b, B), (s_, S), (d, D)], Set(out, (b, s_, d), (gamma[d] * (cen[b, s_, d] / std[b, s_, 0])) + beta[d])))
+    r.body = Seq(body)
+    code = bk.Code(r)
+    rt = bk.Context(dev).link(code)
+    g = np.random.default_rng(0)
+    rt.context.from_host("x", W.store("bfloat16", g.standard_normal((B, S, D), np.float32)))
+    rt.context.from_host("gamma", np.ones(D, np.float32))
+    rt.context.from_host("beta", np.zeros(D, np.float32))
+    for _ in range(3):
+        rt.run()
+    dev.await_()
+    e0 = dev.all_work()
+    for _ in range(10):
+        rt.run()
+    e1 = dev.all_work()
+    e1.sync()
+    ms = e0.elapsed_ms(e1) / 10
+    st = rt.info()["stages"]
+    nbytes = sum(s_i["bytes"] for s_i in st)
+    out_ = {"us": round(1e3 * ms, 2), "kernels": rt.kernels_per_run(), "bytes": nbytes, "gbs": round(nbytes / ms / 1e6, 1),
+            "notes": [s_i["note"] for s_i in st]}
+    pools = {p for p, _, _ in rt.context.arrays.values()}
+    rt.free()
+    code.free()
+    for p in pools:
+        dev.free_pool(p)
+    return out_
+
+
 def oracle_rate(ir, inputs, units, statics=None, what=""):
     """Seconds of one oracle run of `ir` (one host thread) -> units per second, with the sample stated."""
     from oracle.run_c import OracleRoutine
@@ -707,7 +761,7 @@ def main():
                     help="run only the batch-8 contraction of this M=N=K (a small case for profilers) and exit")
     ap.add_argument("--probe", default="", help="'attention_scores': time the decoder's score contraction alone and exit; "
                     "'attention' / 'attention_small': one attention layer alone (64 x 8 or 8 x 8 (batch, head) pairs); "
-                    "'ffn': a decoder layer's first feed-forward contraction alone")
+                    "'ffn': a decoder layer's first feed-forward contraction alone; 'layer_norm': one layer norm alone")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -735,6 +789,9 @@ def main():
         return
     if args.probe in ("attention", "attention_small"):
         print(json.dumps({args.probe: probe_attention(dev, batch=64 if args.probe == "attention" else 8)}))
+        return
+    if args.probe == "layer_norm":
+        print(json.dumps({"layer_norm": probe_layer_norm(dev)}))
         return
     if args.probe == "ffn":
         print(json.dumps({"ffn": probe_ffn(dev)}))

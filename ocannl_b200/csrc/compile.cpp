@@ -1428,27 +1428,48 @@ struct Builder {
     }
     int max_bytes = 4;
     auto reg = [](int tn) { return "b200_row" + std::to_string(tn); };
+    // Which elements of a row a lane owns.  Four at a time, dealt round the warp (element
+    // (k * 32 + lane) * 4 + j in register 4 k + j) when the lane's share is a multiple of four: every
+    // access of the warp then covers one contiguous stretch of the row.  A share of two elements stays
+    // consecutive (lane * 2 + e).
+    const bool dealt = EPL % 4 == 0;
+    const std::string own = dealt ? "(((b200_e >> 2) * 32u + b200_t) * 4u + (b200_e & 3u))" : "(b200_t0 + b200_e)";
     auto row_ptr = [&](int tn, const RowNode& rn) {
       const Tnode& t = code.prog.tn(tn);
       Indices at = rn.idcs;
       Index zero;
       at.push_back(zero);
-      return t.ident + " + (" + em.offset(at, t.dims) + ") + b200_t0";
+      return t.ident + " + (" + em.offset(at, t.dims) + ")" + (dealt ? "" : " + b200_t0");
     };
     auto ld = [&](int tn, const RowNode& rn) {
       const std::string n = std::to_string(EPL);
-      max_bytes = std::max(max_bytes, std::min(16, EPL * prec_bytes(rn.prec)));
-      if (rn.prec == Prec::Single) return "    b200_ld_row<" + n + ">(" + row_ptr(tn, rn) + ", " + reg(tn) + ");\n";
-      return "    b200_ld_row16<" + n + ", " + (rn.prec == Prec::Half ? "true" : "false") + ">(" + row_ptr(tn, rn) + ", " + reg(tn) + ");\n";
+      max_bytes = std::max(max_bytes, dealt ? 4 * prec_bytes(rn.prec) : std::min(16, EPL * prec_bytes(rn.prec)));
+      const std::string lane = dealt ? "b200_t, " : "";
+      if (rn.prec == Prec::Single) return std::string("    b200_ld_row") + (dealt ? "v<" : "<") + n + ">(" + row_ptr(tn, rn) + ", " + lane + reg(tn) + ");\n";
+      return std::string("    b200_ld_row") + (dealt ? "v16<" : "16<") + n + ", " + (rn.prec == Prec::Half ? "true" : "false") + ">(" + row_ptr(tn, rn) + ", " + lane + reg(tn) + ");\n";
     };
     auto stv = [&](int tn, const RowNode& rn) {
       const std::string n = std::to_string(EPL);
-      max_bytes = std::max(max_bytes, std::min(16, EPL * prec_bytes(rn.prec)));
-      if (rn.prec == Prec::Single) return "    b200_st_row<" + n + ">(" + row_ptr(tn, rn) + ", " + reg(tn) + ");\n";
-      return "    b200_st_row16<" + n + ", " + (rn.prec == Prec::Half ? "true" : "false") + ">(" + row_ptr(tn, rn) + ", " + reg(tn) + ");\n";
+      max_bytes = std::max(max_bytes, dealt ? 4 * prec_bytes(rn.prec) : std::min(16, EPL * prec_bytes(rn.prec)));
+      const std::string lane = dealt ? "b200_t, " : "";
+      if (rn.prec == Prec::Single) return std::string("    b200_st_row") + (dealt ? "v<" : "<") + n + ">(" + row_ptr(tn, rn) + ", " + lane + reg(tn) + ");\n";
+      return std::string("    b200_st_row") + (dealt ? "v16<" : "16<") + n + ", " + (rn.prec == Prec::Half ? "true" : "false") + ">(" + row_ptr(tn, rn) + ", " + lane + reg(tn) + ");\n";
     };
-    std::string text, decls;
-    for (auto& kv : rownodes) decls += "    float " + reg(kv.first) + "[" + std::to_string(EPL) + "];\n";
+    // rows that are the same for every row of the kernel (a scale, a shift: no row symbol in their
+    // position) are loaded once per warp, before the loop over the warp's rows
+    auto row_invariant = [&](const RowNode& rn) {
+      if (rn.produced) return false;
+      for (auto& ix : rn.idcs)
+        if (ix.kind != Index::Fixed) return false;
+      return true;
+    };
+    std::string text, decls, pre_decls, pre_text;
+    bool any_invariant = false;
+    for (auto& kv : rownodes) {
+      const std::string d = "    float " + reg(kv.first) + "[" + std::to_string(EPL) + "];\n";
+      if (row_invariant(kv.second)) { pre_decls += d; any_invariant = true; }
+      else decls += d;
+    }
     std::set<int> have;
     auto forwards = [&]() {
       em.row_forwards.clear();
@@ -1456,7 +1477,7 @@ struct Builder {
         Indices idcs = kv.second.idcs;
         Index any;
         idcs.push_back(any);
-        em.row_forwards.push_back({kv.first, idcs, (int)idcs.size() - 1, reg(kv.first), " - b200_t0"});
+        em.row_forwards.push_back({kv.first, idcs, (int)idcs.size() - 1, reg(kv.first), " - b200_t0", "b200_e"});   // (every element loop below runs over b200_e)
       }
     };
     forwards();
@@ -1472,7 +1493,8 @@ struct Builder {
         bool positional = !e.idcs.empty() && e.idcs.back().kind == Index::Iter &&
                           (e.idcs.back().sym == st.t_sym || std::count(st.scope_syms.begin(), st.scope_syms.end(), e.idcs.back().sym));
         if (!positional) return;
-        text += ld(e.tn, it->second);
+        if (row_invariant(it->second)) pre_text += ld(e.tn, it->second);
+        else text += ld(e.tn, it->second);
         have.insert(e.tn);
       }, [](const Stmt&) {});
       if (st.coop) {
@@ -1490,7 +1512,7 @@ struct Builder {
             const double neutral = op == "add" ? 0.0 : (op == "max" ? -INFINITY : INFINITY);
             text += "      " + std::string(Emitter::ctype(p)) + " " + name + " = " + em.constant(neutral, p) + ";\n";
             text += "#pragma unroll\n      for (unsigned int b200_e = 0; b200_e < " + std::to_string(EPL) + "u; ++b200_e) {\n"
-                    "        const unsigned int " + b->index + " = b200_t0 + b200_e;\n" + em.stmt(*b->body, 8) + "      }\n";
+                    "        const unsigned int " + b->index + " = " + own + ";\n" + em.stmt(*b->body, 8) + "      }\n";
             text += "      " + name + " = b200_warp_" + (op == "add" ? std::string("sum") : op) + "(" + name + ");\n";
             em.scope_subst[e.scope_id] = name;
             ++si;
@@ -1510,7 +1532,7 @@ struct Builder {
       } else {
         em.set_redirect[set.tn] = {set.idcs, reg(set.tn) + "[b200_e]"};
         const std::string loop_head = "#pragma unroll\n    for (unsigned int b200_e = 0; b200_e < " + std::to_string(EPL) + "u; ++b200_e) {\n"
-                                      "      const unsigned int " + st.t_sym + " = b200_t0 + b200_e;\n";
+                                      "      const unsigned int " + st.t_sym + " = " + own + ";\n";
         // divisors that are the same for the whole row (a standard deviation, a sum) are prepared
         // once: reciprocal and range check per row, a short exact sequence per element
         std::vector<std::string> probe;
@@ -1551,6 +1573,7 @@ struct Builder {
           << "  const unsigned int b200_t = threadIdx.x & 31u;\n  const unsigned int b200_t0 = b200_t * " << EPL << "u;\n"
           << "  const unsigned long long b200_warp = ((unsigned long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;\n"
           << "  const unsigned long long b200_nwarps = ((unsigned long long)gridDim.x * blockDim.x) >> 5;\n"
+          << pre_decls << pre_text
           << "  for (unsigned long long b200_row = b200_warp; b200_row < " << rows << "ull; b200_row += b200_nwarps) {\n";
     {
       std::string rem = "b200_row";
@@ -1565,8 +1588,11 @@ struct Builder {
     }
     k_src << decls << text << "  }\n}\n\n";
     src << k_src.str();
+    // with rows loaded once per warp, a warp takes several rows: as many blocks as stay resident on 148
+    // SMs (three of 256 threads at this kernel's register use), each warp striding over the rows
+    if (any_invariant && rows >= 2 * 148 * 3 * 8) f.grid_override = 148 * 3;
     f.note = "row-fused " + std::to_string(run.size()) + " stages, one warp per row, rows in registers (" + std::to_string(EPL) +
-             " elements per lane)";
+             " elements per lane" + (dealt ? ", dealt four at a time" : "") + ")";
     *out = f;
     return true;
   }

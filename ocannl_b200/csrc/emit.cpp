@@ -475,7 +475,7 @@ Emitter::Res Emitter::scalar(Prec prec, const Scalar& e) {
           for (size_t a = 0; ok && a < e.idcs.size(); ++a) {
             Index x = e.idcs[a];
             if ((int)a == rf.n_axis) {
-              if (x.kind == Index::Iter) sub = "[" + x.sym + rf.index_shift + "]";
+              if (x.kind == Index::Iter) sub = rf.fixed_index.empty() ? "[" + x.sym + rf.index_shift + "]" : "[" + rf.fixed_index + "]";
               else if (x.kind == Index::Fixed && rf.index_shift.empty()) sub = "[" + std::to_string(x.fixed) + "]";
               else ok = false;
             } else {

@@ -48,6 +48,7 @@ struct Emitter {
     int n_axis;
     std::string name;
     std::string index_shift;   // appended to the index on n_axis ("" or e.g. " - b200_t0": the array holds a slice)
+    std::string fixed_index;   // non-empty: the register index of the element the current loop is at, whatever the symbol
   };
   std::vector<RowForward> row_forwards;
   std::map<std::string, std::string> row_ren;

@@ -311,6 +311,51 @@ __device__ __forceinline__ void b200_st_row16(unsigned short* p, const float* r)
   b200_st_words<2 * N>(p, w);
 }
 
+// Rows whose elements are dealt to the lanes four at a time: lane l owns elements
+// (k * 32 + l) * 4 + j  (j < 4, k < N / 4), register e = 4 k + j.  Every access of a warp then
+// covers one contiguous stretch of the row (512 bytes of floats, 256 bytes of 16-bit values)
+// instead of 32 pieces a lane's share apart.
+template <int N>
+__device__ __forceinline__ void b200_ld_rowv(const float* p, unsigned int lane, float* r) {
+#pragma unroll
+  for (int k = 0; k < N / 4; ++k) {
+    const uint4 q = ((const uint4*)p)[k * 32 + lane];
+    r[4 * k] = __uint_as_float(q.x); r[4 * k + 1] = __uint_as_float(q.y);
+    r[4 * k + 2] = __uint_as_float(q.z); r[4 * k + 3] = __uint_as_float(q.w);
+  }
+}
+template <int N>
+__device__ __forceinline__ void b200_st_rowv(float* p, unsigned int lane, const float* r) {
+#pragma unroll
+  for (int k = 0; k < N / 4; ++k)
+    ((uint4*)p)[k * 32 + lane] = make_uint4(__float_as_uint(r[4 * k]), __float_as_uint(r[4 * k + 1]), __float_as_uint(r[4 * k + 2]),
+                                            __float_as_uint(r[4 * k + 3]));
+}
+template <int N, bool HALF>
+__device__ __forceinline__ void b200_ld_rowv16(const unsigned short* p, unsigned int lane, float* r) {
+#pragma unroll
+  for (int k = 0; k < N / 4; ++k) {
+    const uint2 q = ((const uint2*)p)[k * 32 + lane];
+    if constexpr (HALF) {
+      r[4 * k] = b200_h2f((unsigned short)q.x); r[4 * k + 1] = b200_h2f((unsigned short)(q.x >> 16));
+      r[4 * k + 2] = b200_h2f((unsigned short)q.y); r[4 * k + 3] = b200_h2f((unsigned short)(q.y >> 16));
+    } else {
+      r[4 * k] = __uint_as_float(q.x << 16); r[4 * k + 1] = __uint_as_float(q.x & 0xFFFF0000u);
+      r[4 * k + 2] = __uint_as_float(q.y << 16); r[4 * k + 3] = __uint_as_float(q.y & 0xFFFF0000u);
+    }
+  }
+}
+template <int N, bool HALF>
+__device__ __forceinline__ void b200_st_rowv16(unsigned short* p, unsigned int lane, const float* r) {
+#pragma unroll
+  for (int k = 0; k < N / 4; ++k) {
+    uint2 q;
+    q.x = HALF ? b200_pack_hf(r[4 * k], r[4 * k + 1]) : b200_pack_bf(r[4 * k], r[4 * k + 1]);
+    q.y = HALF ? b200_pack_hf(r[4 * k + 2], r[4 * k + 3]) : b200_pack_bf(r[4 * k + 2], r[4 * k + 3]);
+    ((uint2*)p)[k * 32 + lane] = q;
+  }
+}
+
 // IEEE single-precision division.  A zero over a finite non-zero value is a signed zero; giving
 // the division sequence a numerator of one in that case (and selecting the zero afterwards) keeps
 // such lanes -- the masked entries of a softmax row -- off the sequence's slow path, which the whole
