@@ -472,10 +472,10 @@ bool match_attention(const Program& P, const std::vector<StmtP>& flat, size_t at
     });
     return ok;
   };
-  Indices scores_red = scores_idcs, exp_red = exp_idcs, w_red = w_idcs;   // as read inside the reductions (t = the loop)
-  if (!reads_ok(s1.value, ren1, {}) || !reads_ok(s2.value, ren2, {{s1.tn, scores_red}}) ||
-      !reads_ok(s3.value, ren3, {{s1.tn, scores_idcs}, {s2.tn, max_idcs}}) || !reads_ok(s4.value, ren4, {{s3.tn, exp_red}}) ||
-      !reads_ok(s5.value, ren5, {{s3.tn, exp_idcs}, {s4.tn, sum_idcs}}) || !reads_ok(s6.value, ren6, {{s5.tn, w_red}}))
+  // (inside the reductions the loop symbol is renamed to the key position, so the reads there equal the canonical ones)
+  if (!reads_ok(s1.value, ren1, {}) || !reads_ok(s2.value, ren2, {{s1.tn, scores_idcs}}) ||
+      !reads_ok(s3.value, ren3, {{s1.tn, scores_idcs}, {s2.tn, max_idcs}}) || !reads_ok(s4.value, ren4, {{s3.tn, exp_idcs}}) ||
+      !reads_ok(s5.value, ren5, {{s3.tn, exp_idcs}, {s4.tn, sum_idcs}}) || !reads_ok(s6.value, ren6, {{s5.tn, w_idcs}}))
     return false;
 
   // ---- which nodes of the chain must reach memory

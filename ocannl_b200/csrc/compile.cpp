@@ -1965,7 +1965,7 @@ struct Builder {
       for (auto& t : code.prog.tnodes) {
         if (t.mode == Mode::Virtual) continue;
         // "<type>* [__restrict__ ]ident" followed by ',' or the end
-        for (const std::string sep : {std::string("* __restrict__ "), std::string("* ")}) {
+        for (const std::string& sep : {std::string("* __restrict__ "), std::string("* ")}) {
           const std::string needle = sep + t.ident;
           size_t q = 0;
           while ((q = params.find(needle, q)) != std::string::npos) {
