@@ -164,3 +164,17 @@ def test_contraction_epilogues_use_the_copy_engine_where_the_layout_allows():
     train = sources(W.mlp_train_update(rows=8192))
     split = [src for s, src in train if "split_k" in s["note"]]
     assert split and all("b200_omap" not in src for src in split)
+
+
+def test_attention_stage_writes_a_local_node_that_a_later_statement_reads():
+    """A routine-local node of the attention chain is left unwritten only when nothing after the chain
+    reads it: here the weights are read by one more statement, the scores and exponentials are not."""
+    from ocannl_b200.low_level import Set, loops
+    ir = W.attention(2, 2, 128, 128, row_mode="local")
+    attn = [t for t in ir.tnodes if t.ident == "attn"][0]
+    twice = ir.tn("twice", "bfloat16", [2, 128, 2, 128])
+    b, s, h, t = ir.syms(4)
+    ir.body.items.append(loops([(b, 2), (s, 128), (h, 2), (t, 128)], Set(twice, (b, s, h, t), attn[b, s, h, t] + attn[b, s, h, t])))
+    st = _plan(ir)
+    notes = [x["note"] for x in st if x["kind"] == "attention"]
+    assert notes and "1 of the 3 row nodes written" in notes[0], [x["note"] for x in st]
