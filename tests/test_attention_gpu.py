@@ -111,3 +111,21 @@ def test_operands_off_the_16_byte_grid_fall_back_to_the_separate_stages(device):
         device.free_pool(p)
     compare(ir, got, want, 1e-5, 8e-5, only=["scores", "max"])
     compare(ir, got, want, 2e-2, 2e-2, only=["av"])
+
+
+def test_local_weights_with_a_later_reader_are_written(device):
+    """Routine-local intermediate nodes, but one more statement reads the weights after the chain: the
+    fused stage must write that node (into the routine's scratch) and only that one."""
+    from ocannl_b200.low_level import Set, loops
+    ir = R.attention(2, 2, 128, 128, row_mode="local")
+    attn = [t for t in ir.tnodes if t.ident == "attn"][0]
+    twice = ir.tn("twice", "bfloat16", [2, 128, 2, 128])
+    b, s, h, t = ir.syms(4)
+    ir.body.items.append(loops([(b, 2), (s, 128), (h, 2), (t, 128)], Set(twice, (b, s, h, t), attn[b, s, h, t] + attn[b, s, h, t])))
+    inputs = R.attention_inputs(2, 2, 128, 128)
+    got, info = run_device(device, ir, inputs)
+    note = [s_["note"] for s_ in info["stages"] if s_["kind"] == "attention"][0]
+    assert "1 of the 3 row nodes written" in note
+    want = run_oracle(ir, inputs)
+    compare(ir, got, want, 2.2 * 2.0 ** -7, 1e-30, only=["twice"])
+    compare(ir, got, want, 2e-2, 2e-2, only=["av"])
