@@ -819,7 +819,11 @@ def main():
     # ---- roofline of the dominant kernel
     stages, shares = fwd["stage_info"], fwd["stage_ms"]
     gemm_idx = [i for i, s_ in enumerate(stages) if s_["kind"] == "gemm"]
-    dom = max(gemm_idx, key=lambda i: shares[i])
+    # the dominant kernel: the longest contraction stage; stages within 5 % of it (the two hidden layers
+    # trade places from run to run) are told apart by their algorithmic work, so that the line names the
+    # same kernel every time
+    longest = max(shares[i] for i in gemm_idx)
+    dom = max((i for i in gemm_idx if shares[i] >= 0.95 * longest), key=lambda i: stages[i]["flops"])
     dom_ms = shares[dom]
     achieved = stages[dom]["flops"] / dom_ms / 1e9
     shape = {k: stages[dom][k] for k in ("m", "n", "k", "batch")}
